@@ -1,0 +1,143 @@
+"""In-tree native build for the B200 kernel library and the C++ runtime.
+
+Everything is compiled for sm_100a only (``-gencode arch=compute_100a,code=sm_100a``)
+and the products stay inside the package directory so that a snapshot of the
+repository carries them:
+
+* ``lib/libb200_kernels.so``  - every ``csrc/kernels/*.cu`` and ``csrc/comm/*.cu``;
+  plain C entry points, loaded with ctypes (no torch headers, so a kernel edit
+  rebuilds in seconds).
+* ``lib/libb200_core.so`` + ``pocketllm_cpp`` pybind module - the C++ runtime
+  (block pool/table, scheduler, command channel, readers, tokenizer, sampler).
+* ``bin/pocketllm_engine`` - the native executable.
+
+The reference builds its native plane with CMake for sm_75
+(cpp_engine/CMakeLists.txt:95-100) and its torch extensions with setup.py
+(setup.py:49-87); this module replaces both.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import os
+import shlex
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+OBJ = PKG / "build"
+LIB = PKG / "lib"
+BIN = PKG / "bin"
+
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+CXX = os.environ.get("CXX", "g++")
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ARCH + ["-lineinfo", "-O3", "-std=c++17", "--use_fast_math", "-Xcompiler", "-fPIC",
+                     "-Xcompiler", "-fvisibility=default", "--expt-relaxed-constexpr"]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-pthread"]
+
+
+def _run(cmd: list[str]) -> None:
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write("FAILED: " + " ".join(shlex.quote(c) for c in cmd) + "\n")
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError(f"native build failed: {cmd[0]} {cmd[-1]}")
+
+
+def _deps_mtime(src: Path) -> float:
+    """Newest mtime among the source and every header under csrc/ (coarse but safe)."""
+    newest = src.stat().st_mtime
+    for pat in ("**/*.h", "**/*.hpp", "**/*.cuh", "**/*.inc"):
+        for h in CSRC.glob(pat):
+            newest = max(newest, h.stat().st_mtime)
+    return newest
+
+
+def _needs(src: Path, obj: Path) -> bool:
+    return (not obj.exists()) or obj.stat().st_mtime < _deps_mtime(src)
+
+
+def _compile_cu(src: Path) -> Path:
+    obj = OBJ / (src.stem + ".cu.o")
+    if _needs(src, obj):
+        _run([NVCC, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)])
+    return obj
+
+
+def _compile_cpp(src: Path, extra: list[str] | None = None, tag: str = "") -> Path:
+    obj = OBJ / (src.stem + tag + ".cpp.o")
+    if _needs(src, obj):
+        _run([CXX, *CXX_FLAGS, *(extra or []), "-I", str(CSRC), "-I", "/usr/local/cuda/include",
+              "-c", str(src), "-o", str(obj)])
+    return obj
+
+
+def build_kernels(jobs: int | None = None) -> Path:
+    OBJ.mkdir(exist_ok=True)
+    LIB.mkdir(exist_ok=True)
+    srcs = sorted(list((CSRC / "kernels").glob("*.cu")) + list((CSRC / "comm").glob("*.cu")))
+    out = LIB / "libb200_kernels.so"
+    with cf.ThreadPoolExecutor(max_workers=jobs or os.cpu_count() or 4) as ex:
+        objs = list(ex.map(_compile_cu, srcs))
+    if (not out.exists()) or any(o.stat().st_mtime > out.stat().st_mtime for o in objs):
+        _run([NVCC, *ARCH, "-shared", "-o", str(out), *map(str, objs), "-lcudart_static", "-lpthread",
+              "-ldl", "-lrt"])
+    return out
+
+
+def build_core(jobs: int | None = None) -> dict[str, Path]:
+    """C++ runtime library, pybind module and the engine executable."""
+    OBJ.mkdir(exist_ok=True)
+    LIB.mkdir(exist_ok=True)
+    BIN.mkdir(exist_ok=True)
+    products: dict[str, Path] = {}
+    core_srcs = sorted((CSRC / "core").glob("*.cpp"))
+    if not core_srcs:
+        return products
+    with cf.ThreadPoolExecutor(max_workers=jobs or os.cpu_count() or 4) as ex:
+        core_objs = list(ex.map(_compile_cpp, core_srcs))
+    core_lib = LIB / "libb200_core.so"
+    if (not core_lib.exists()) or any(o.stat().st_mtime > core_lib.stat().st_mtime for o in core_objs):
+        _run([CXX, "-shared", "-o", str(core_lib), *map(str, core_objs), "-pthread"])
+    products["core"] = core_lib
+
+    bind_src = CSRC / "bindings" / "core_bindings.cpp"
+    if bind_src.exists():
+        import pybind11
+
+        ext = sysconfig.get_config_var("EXT_SUFFIX")
+        mod = PKG / f"pocketllm_cpp{ext}"
+        inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"]]
+        bobj = _compile_cpp(bind_src, inc)
+        if (not mod.exists()) or bobj.stat().st_mtime > mod.stat().st_mtime or \
+                core_lib.stat().st_mtime > mod.stat().st_mtime:
+            _run([CXX, "-shared", "-o", str(mod), str(bobj), *map(str, core_objs), "-pthread"])
+        products["pybind"] = mod
+
+    main_src = CSRC / "engine" / "main.cpp"
+    if main_src.exists():
+        eng_srcs = sorted((CSRC / "engine").glob("*.cpp"))
+        eng_objs = [_compile_cpp(s, tag=".eng") for s in eng_srcs]
+        exe = BIN / "pocketllm_engine"
+        kern = LIB / "libb200_kernels.so"
+        if (not exe.exists()) or any(o.stat().st_mtime > exe.stat().st_mtime for o in eng_objs + core_objs) \
+                or (kern.exists() and kern.stat().st_mtime > exe.stat().st_mtime):
+            _run([CXX, "-o", str(exe), *map(str, eng_objs), *map(str, core_objs), "-L", str(LIB),
+                  "-lb200_kernels", f"-Wl,-rpath,$ORIGIN/../lib", "-L/usr/local/cuda/lib64",
+                  "-lcudart", "-ldl", "-pthread"])
+        products["engine"] = exe
+    return products
+
+
+def build_all() -> dict[str, Path]:
+    out = {"kernels": build_kernels()}
+    out.update(build_core())
+    return out
+
+
+if __name__ == "__main__":
+    for k, v in build_all().items():
+        print(f"built {k}: {v}")

@@ -1,0 +1,451 @@
+// Weight-decoding tensor-core GEMM for sm_100a:  Y[T, N] = X[T, K] * W[N, K]^T.
+//
+// Design (one persistent CTA per SM, 14 warps, warp-specialised):
+//   * W is the UMMA "A" operand (M = 128 output features per tile) and the
+//     activations are the "B" operand (N = BN tokens, 16..256), so the same
+//     kernel serves prefill (BN = 256) and decode batches (BN = 16..64) while
+//     the weight tile is always a full 128-row MMA.
+//   * warp 4 streams raw weight bytes and bf16 activations with TMA
+//     (cp.async.bulk.tensor, destination = this CTA only, never multicast);
+//   * warps 6..13 decode the raw weight tile (FP8 E4M3 with one scale per
+//     128x128 block) into bf16, written in the 128-byte-swizzled K-major layout
+//     the tensor core reads; the quantised matrix is never expanded in HBM;
+//   * warp 5 issues tcgen05.mma (kind::f16, fp32 accumulate in TMEM, two
+//     accumulator buffers) and commits stage/accumulator barriers;
+//   * warps 0..3 drain TMEM with tcgen05.ld and store bf16 (+residual) or fp32
+//     split-K partials.
+// Every mbarrier wait is bounded; on expiry the CTA records an error code and
+// unwinds through the common exit (TMEM is always freed).
+//
+// Reference behaviour covered: FP8 block-128 weight x 16-bit activation
+// projections of the Qwen path (cpp_engine/backends/cuda/kernels/qwen_half_ops.cu:988-1199,
+// dequant + cublasGemmEx at :1349) and dense bf16 projections
+// (cpp_engine/backends/cuda/kernels/bf16_ops.cu:30-167).
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include "../ptx/sm100.cuh"
+#include "tma_host.h"
+#include "ops.h"
+
+namespace b200 {
+
+constexpr int BM = 128;      // output features per tile (UMMA M)
+constexpr int BK = 64;       // K elements per pipeline stage (one 128-byte swizzle row of bf16)
+constexpr int NUM_EPI_WARPS = 4;
+constexpr int TMA_WARP = 4;
+constexpr int MMA_WARP = 5;
+constexpr int DEC_WARP0 = 6;
+constexpr int NUM_DEC_WARPS = 8;
+constexpr int NUM_THREADS = (DEC_WARP0 + NUM_DEC_WARPS) * 32;  // 448
+
+enum WFormat : int { WF_BF16 = 0, WF_FP8_B128 = 1 };
+
+struct GemmParams {
+  int T, N, K;
+  int m_tiles, n_tiles, splits, kb_total;
+  const float* scales;  // [ceil(N/128), scale_ld] fp32 (FP8 only)
+  int scale_ld;
+  __nv_bfloat16* out;        // [T, ldo] (splits == 1)
+  float* out_f32;            // [splits, T, ldo] partials (splits > 1) or fp32 result
+  const __nv_bfloat16* residual;  // optional [T, ldo], added in the epilogue (splits == 1)
+  int ldo;
+  int* status;
+};
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;       // 16 KB decoded bf16 weights
+  static constexpr int X_BYTES = BN * BK * 2;       // activations
+  static constexpr int RAW_BYTES = BM * BK;         // 8 KB raw fp8
+  static constexpr int STAGE_BYTES = A_BYTES + X_BYTES + RAW_BYTES;
+  static constexpr int BUDGET = 232448 - 1024 /*align slack*/ - 512 /*barriers*/;
+  static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + 512;
+};
+
+// 4 fp8 bytes stored as (w0, w2, w1, w3) -> two bf16x2 words (w0,w1), (w2,w3),
+// each still scaled by 2^-120; the caller multiplies by scale * 2^120.
+__device__ __forceinline__ void fp8x4_to_bf16x4_raw(uint32_t q, uint32_t& w01, uint32_t& w23) {
+  w23 = (q & 0x80008000u) | ((q & 0x7F007F00u) >> 4);
+  uint32_t q2 = q << 8;
+  w01 = (q2 & 0x80008000u) | ((q2 & 0x7F007F00u) >> 4);
+}
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+template <int BN, int WFMT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                 GemmParams p) {
+  using L = SmemLayout<BN>;
+  constexpr int S = L::STAGES;
+  constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+  extern __shared__ uint8_t smem_raw_base[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_base) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sX = sA + S * L::A_BYTES;
+  uint8_t* sRaw = sX + S * L::X_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sRaw + S * L::RAW_BYTES);
+  uint64_t* tma_full = bars;            // [S]
+  uint64_t* a_full = bars + S;          // [S]
+  uint64_t* empty = bars + 2 * S;       // [S]
+  uint64_t* acc_full = bars + 3 * S;    // [2]
+  uint64_t* acc_empty = bars + 3 * S + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * S + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&tma_full[s], 1);
+      mbar_init(&a_full[s], NUM_DEC_WARPS);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], NUM_EPI_WARPS * 32);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == MMA_WARP) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == TMA_WARP && lane == 0) {
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_work = p.m_tiles * p.n_tiles * p.splits;
+  const int kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
+
+  if (warp == TMA_WARP) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
+        const int m_tile = w % p.m_tiles;
+        const int rest = w / p.m_tiles;
+        const int n_tile = rest % p.n_tiles;
+        const int split = rest / p.n_tiles;
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(p.kb_total, kb0 + kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1)) {
+            atomicExch(p.status, ERR_WAIT_STAGE);
+            *abort_flag = 1;
+            break;
+          }
+          if (WFMT == WF_BF16) {
+            mbar_expect_tx(&tma_full[s], L::A_BYTES + L::X_BYTES);
+            tma_load_2d(sA + s * L::A_BYTES, &tmW, &tma_full[s], kb * BK, m_tile * BM);
+          } else {
+            mbar_expect_tx(&tma_full[s], L::RAW_BYTES + L::X_BYTES);
+            tma_load_2d(sRaw + s * L::RAW_BYTES, &tmW, &tma_full[s], kb * BK, m_tile * BM);
+          }
+          tma_load_2d(sX + s * L::X_BYTES, &tmX, &tma_full[s], kb * BK, n_tile * BN);
+        }
+      }
+    }
+  } else if (warp == MMA_WARP) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      uint32_t it = 0;
+      uint32_t tile_i = 0;
+      for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x, ++tile_i) {
+        const int split = (w / p.m_tiles) / p.n_tiles;
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(p.kb_total, kb0 + kb_per_split);
+        const int buf = tile_i & 1;
+        const uint32_t acc_ph = (tile_i >> 1) & 1;
+        if (!mbar_wait(&acc_empty[buf], acc_ph ^ 1)) {
+          atomicExch(p.status, ERR_WAIT_ACC);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        bool failed = false;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait(&tma_full[s], ph)) {
+            atomicExch(p.status, ERR_WAIT_TMA);
+            failed = true;
+            break;
+          }
+          if (WFMT != WF_BF16) {
+            if (!mbar_wait(&a_full[s], ph)) {
+              atomicExch(p.status, ERR_WAIT_DEQUANT);
+              failed = true;
+              break;
+            }
+          }
+          tc_fence_after();
+          const uint64_t da = umma_desc_sw128(sA + s * L::A_BYTES);
+          const uint64_t db = umma_desc_sw128(sX + s * L::X_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // advance 16 bf16 = 32 bytes inside the swizzle row: +2 in 16-byte units
+            umma_bf16_ss(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+        }
+        if (failed) {
+          *abort_flag = 1;
+          break;
+        }
+        umma_commit(&acc_full[buf]);
+      }
+    }
+  } else if (warp >= DEC_WARP0) {
+    // ------------------------------------------------- weight decode (FP8 -> bf16)
+    if (WFMT == WF_FP8_B128) {
+      const int d = threadIdx.x - DEC_WARP0 * 32;  // 0..255
+      uint32_t it = 0;
+      for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
+        const int m_tile = w % p.m_tiles;
+        const int split = (w / p.m_tiles) / p.n_tiles;
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(p.kb_total, kb0 + kb_per_split);
+        const float* srow = p.scales + (size_t)m_tile * p.scale_ld;
+        bool failed = false;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          const float sc = __ldg(srow + (kb >> 1)) * 0x1p120f;
+          bool ok = mbar_wait(&tma_full[s], ph);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) {
+            if (lane == 0) atomicExch(p.status, ERR_WAIT_TMA);
+            failed = true;
+            break;
+          }
+          __nv_bfloat162 sc2 = __float2bfloat162_rn(sc);
+          const uint32_t scw = *reinterpret_cast<uint32_t*>(&sc2);
+          const uint8_t* raw = sRaw + s * L::RAW_BYTES;
+          uint8_t* A = sA + s * L::A_BYTES;
+#pragma unroll
+          for (int rep = 0; rep < 2; ++rep) {
+            const int i = d + rep * 256;
+            const int r = i >> 2, c = i & 3;
+            const uint4 q = *reinterpret_cast<const uint4*>(raw + r * BK + c * 16);
+            uint4 o0, o1;
+            fp8x4_to_bf16x4_raw(q.x, o0.x, o0.y);
+            fp8x4_to_bf16x4_raw(q.y, o0.z, o0.w);
+            fp8x4_to_bf16x4_raw(q.z, o1.x, o1.y);
+            fp8x4_to_bf16x4_raw(q.w, o1.z, o1.w);
+            o0.x = bf16x2_mul(o0.x, scw); o0.y = bf16x2_mul(o0.y, scw);
+            o0.z = bf16x2_mul(o0.z, scw); o0.w = bf16x2_mul(o0.w, scw);
+            o1.x = bf16x2_mul(o1.x, scw); o1.y = bf16x2_mul(o1.y, scw);
+            o1.z = bf16x2_mul(o1.z, scw); o1.w = bf16x2_mul(o1.w, scw);
+            uint8_t* rowp = A + (r >> 3) * 1024 + (r & 7) * 128;
+            const int sw = r & 7;
+            *reinterpret_cast<uint4*>(rowp + (((2 * c) ^ sw) << 4)) = o0;
+            *reinterpret_cast<uint4*>(rowp + (((2 * c + 1) ^ sw) << 4)) = o1;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&a_full[s]);
+        }
+        if (failed) {
+          *abort_flag = 1;
+          break;
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    uint32_t tile_i = 0;
+    const int row_in_tile = warp * 32 + lane;  // TMEM lane == output feature within the tile
+    for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x, ++tile_i) {
+      const int m_tile = w % p.m_tiles;
+      const int rest = w / p.m_tiles;
+      const int n_tile = rest % p.n_tiles;
+      const int split = rest / p.n_tiles;
+      const int buf = tile_i & 1;
+      const uint32_t acc_ph = (tile_i >> 1) & 1;
+      bool ok = mbar_wait(&acc_full[buf], acc_ph);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) atomicExch(p.status, ERR_WAIT_ACC);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      const int f = m_tile * BM + row_in_tile;
+      const bool f_ok = f < p.N;
+      const uint32_t taddr = tmem_base + (uint32_t(warp * 32) << 16) + buf * BN;
+      constexpr int CH = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += CH) {
+        uint32_t v[32];
+        if (CH == 32) {
+          tmem_ld_32x32(taddr + c0, v);
+        } else {
+          uint32_t v16[16];
+          tmem_ld_32x16(taddr + c0, v16);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = v16[j];
+        }
+        tmem_ld_wait();
+        const int t0 = n_tile * BN + c0;
+        if (f_ok) {
+          if (p.splits > 1 || p.out == nullptr) {
+            float* o = p.out_f32 + ((size_t)split * p.T + t0) * p.ldo + f;
+#pragma unroll
+            for (int j = 0; j < CH; ++j)
+              if (t0 + j < p.T) o[(size_t)j * p.ldo] = __uint_as_float(v[j]);
+          } else if (p.residual) {
+            const __nv_bfloat16* r = p.residual + (size_t)t0 * p.ldo + f;
+            __nv_bfloat16* o = p.out + (size_t)t0 * p.ldo + f;
+#pragma unroll
+            for (int j = 0; j < CH; ++j)
+              if (t0 + j < p.T)
+                o[(size_t)j * p.ldo] =
+                    __float2bfloat16(__uint_as_float(v[j]) + __bfloat162float(r[(size_t)j * p.ldo]));
+          } else {
+            __nv_bfloat16* o = p.out + (size_t)t0 * p.ldo + f;
+#pragma unroll
+            for (int j = 0; j < CH; ++j)
+              if (t0 + j < p.T) o[(size_t)j * p.ldo] = __float2bfloat16(__uint_as_float(v[j]));
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  // Common exit: every thread arrives here, then the allocating warp frees TMEM.
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // Give copies that may still be in flight time to land before smem is released.
+    uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == MMA_WARP) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// Sum split-K partials (+ optional residual) into bf16.
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, int splits, size_t n,
+                                     const __nv_bfloat16* __restrict__ residual,
+                                     __nv_bfloat16* __restrict__ out) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float acc = residual ? __bfloat162float(residual[i]) : 0.f;
+  for (int s = 0; s < splits; ++s) acc += part[(size_t)s * n + i];
+  out[i] = __float2bfloat16(acc);
+}
+
+template <int BN, int WFMT>
+static int launch_one(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p,
+                      cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_wdec_kernel<BN, WFMT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int total = p.m_tiles * p.n_tiles * p.splits;
+  const int grid = total < sm_count() ? total : sm_count();
+  gemm_wdec_kernel<BN, WFMT><<<grid, NUM_THREADS, L::TOTAL, stream>>>(tmW, tmX, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_gemm_pick_bn(int T) {
+  if (T <= 16) return 16;
+  if (T <= 32) return 32;
+  if (T <= 64) return 64;
+  if (T <= 128) return 128;
+  return 256;
+}
+
+// wfmt: 0 = bf16 weights [N, K]; 1 = FP8 E4M3 weights [N, K] (bytes stored in
+// the (w0,w2,w1,w3) order produced by b200_prepack_fp8) with fp32 scales
+// [ceil(N/128), ceil(K/128)].
+// splits == 1: writes bf16 `out` (adds `residual` when given), or fp32 `out_f32` when out == null.
+// splits  > 1: writes fp32 partials to out_f32 [splits, T, N] (caller reduces).
+extern "C" int b200_gemm_wdec(int wfmt, const void* W, const float* scales, const void* X,
+                              void* out_bf16, float* out_f32, const void* residual, int T, int N,
+                              int K, int splits, int* status, cudaStream_t stream) {
+  if (T <= 0 || N <= 0 || K <= 0 || (K % 16) != 0 || splits < 1) return -ERR_BAD_ARG;
+  const int BN = b200_gemm_pick_bn(T);
+  GemmParams p;
+  p.T = T; p.N = N; p.K = K;
+  p.m_tiles = (N + BM - 1) / BM;
+  p.n_tiles = (T + BN - 1) / BN;
+  p.kb_total = (K + BK - 1) / BK;
+  if (splits > p.kb_total) splits = p.kb_total;
+  p.splits = splits;
+  p.scales = scales;
+  p.scale_ld = (K + 127) / 128;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out_bf16);
+  p.out_f32 = out_f32;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.ldo = N;
+  p.status = status;
+  if ((splits > 1 || !out_bf16) && !out_f32) return -ERR_BAD_ARG;
+
+  CUtensorMap tmW, tmX;
+  bool ok;
+  if (wfmt == WF_BF16)
+    ok = make_tmap_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, N, K, (uint64_t)K * 2, BM, BK,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+  else
+    ok = make_tmap_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, N, K, (uint64_t)K, BM, BK,
+                      CU_TENSOR_MAP_SWIZZLE_NONE);
+  ok = ok && make_tmap_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, T, K, (uint64_t)K * 2, BN, BK,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!ok) return -ERR_BAD_ARG;
+
+#define B200_DISPATCH(BN_)                                                       \
+  case BN_:                                                                      \
+    return wfmt == WF_BF16 ? launch_one<BN_, WF_BF16>(tmW, tmX, p, stream)       \
+                           : launch_one<BN_, WF_FP8_B128>(tmW, tmX, p, stream);
+  switch (BN) {
+    B200_DISPATCH(16)
+    B200_DISPATCH(32)
+    B200_DISPATCH(64)
+    B200_DISPATCH(128)
+    B200_DISPATCH(256)
+  }
+#undef B200_DISPATCH
+  return -ERR_BAD_ARG;
+}
+
+extern "C" int b200_splitk_reduce(const float* part, int splits, long long n, const void* residual,
+                                  void* out_bf16, cudaStream_t stream) {
+  const int threads = 256;
+  const long long blocks = (n + threads - 1) / threads;
+  splitk_reduce_kernel<<<(unsigned)blocks, threads, 0, stream>>>(
+      part, splits, (size_t)n, reinterpret_cast<const __nv_bfloat16*>(residual),
+      reinterpret_cast<__nv_bfloat16*>(out_bf16));
+  return (int)cudaGetLastError();
+}
