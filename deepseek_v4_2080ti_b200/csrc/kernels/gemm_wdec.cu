@@ -62,6 +62,10 @@ struct SmemLayout {
   static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + 512;
+  // Decode warps work in GROUPS independent groups, each owning every GROUPS-th
+  // pipeline stage, so barrier/fence latency of one stage overlaps another's ALU work.
+  static constexpr int GROUPS = STAGES >= 6 ? 4 : 2;
+  static constexpr int WARPS_PER_GROUP = NUM_DEC_WARPS / GROUPS;
 };
 
 // 4 fp8 bytes stored as (w0, w2, w1, w3) -> two bf16x2 words (w0,w1), (w2,w3),
@@ -105,7 +109,7 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&tma_full[s], 1);
-      mbar_init(&a_full[s], NUM_DEC_WARPS);
+      mbar_init(&a_full[s], L::WARPS_PER_GROUP);
       mbar_init(&empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -216,7 +220,13 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   } else if (warp >= DEC_WARP0) {
     // ------------------------------------------------- weight decode (FP8 -> bf16)
     if (WFMT == WF_FP8_B128) {
-      const int d = threadIdx.x - DEC_WARP0 * 32;  // 0..255
+      constexpr int G = L::GROUPS;
+      constexpr int WPG = L::WARPS_PER_GROUP;
+      constexpr int GT = WPG * 32;             // threads per group
+      constexpr int REPS = (BM * 4) / GT;      // 16-byte chunks per thread per stage
+      const int dw = warp - DEC_WARP0;
+      const int grp = dw / WPG;
+      const int d = (dw % WPG) * 32 + lane;    // 0..GT-1
       uint32_t it = 0;
       for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
         const int m_tile = w % p.m_tiles;
@@ -226,6 +236,7 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         const float* srow = p.scales + (size_t)m_tile * p.scale_ld;
         bool failed = false;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          if ((int)(it % G) != grp) continue;
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
           const float sc = __ldg(srow + (kb >> 1)) * 0x1p120f;
@@ -240,16 +251,21 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           const uint32_t scw = *reinterpret_cast<uint32_t*>(&sc2);
           const uint8_t* raw = sRaw + s * L::RAW_BYTES;
           uint8_t* A = sA + s * L::A_BYTES;
+          uint4 q[REPS];
 #pragma unroll
-          for (int rep = 0; rep < 2; ++rep) {
-            const int i = d + rep * 256;
+          for (int rep = 0; rep < REPS; ++rep) {
+            const int i = d + rep * GT;
+            q[rep] = *reinterpret_cast<const uint4*>(raw + (i >> 2) * BK + (i & 3) * 16);
+          }
+#pragma unroll
+          for (int rep = 0; rep < REPS; ++rep) {
+            const int i = d + rep * GT;
             const int r = i >> 2, c = i & 3;
-            const uint4 q = *reinterpret_cast<const uint4*>(raw + r * BK + c * 16);
             uint4 o0, o1;
-            fp8x4_to_bf16x4_raw(q.x, o0.x, o0.y);
-            fp8x4_to_bf16x4_raw(q.y, o0.z, o0.w);
-            fp8x4_to_bf16x4_raw(q.z, o1.x, o1.y);
-            fp8x4_to_bf16x4_raw(q.w, o1.z, o1.w);
+            fp8x4_to_bf16x4_raw(q[rep].x, o0.x, o0.y);
+            fp8x4_to_bf16x4_raw(q[rep].y, o0.z, o0.w);
+            fp8x4_to_bf16x4_raw(q[rep].z, o1.x, o1.y);
+            fp8x4_to_bf16x4_raw(q[rep].w, o1.z, o1.w);
             o0.x = bf16x2_mul(o0.x, scw); o0.y = bf16x2_mul(o0.y, scw);
             o0.z = bf16x2_mul(o0.z, scw); o0.w = bf16x2_mul(o0.w, scw);
             o1.x = bf16x2_mul(o1.x, scw); o1.y = bf16x2_mul(o1.y, scw);

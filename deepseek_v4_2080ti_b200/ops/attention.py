@@ -1,0 +1,114 @@
+"""GQA attention over a paged KV cache (head_dim 128): fused q/k norm + partial RoPE + cache
+append, tcgen05 flash prefill, split-context decode.  Cache layout:
+``[num_blocks, kv_heads, block_size, 128]`` bf16, zero-initialised.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+
+_f = ctypes.c_float
+D = 128
+
+
+def rope_inv_freq(rot: int, theta: float, device) -> torch.Tensor:
+    return (1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float64) / rot))).float().to(device)
+
+
+def qk_norm_rope_append(q_src, q_off, q_head_stride, gate_in_q, k_src, k_off, v_src, v_off, q_gamma, k_gamma,
+                        unit_offset, eps, inv_freq, rot, positions, slots, k_cache, v_cache, n_q_heads, n_kv_heads,
+                        mscale: float = 1.0):
+    """Normalise + rotate q and k, split the q||gate layout, and write K/V rows into the paged cache.
+
+    ``*_src`` are 2-D bf16 tensors (often the same fused-projection output) addressed as
+    ``src[t, off + head * stride + d]``. Returns (q [T, Hq, 128], gate [T, Hq, 128] or None).
+    """
+    t = q_src.shape[0]
+    bs = k_cache.shape[2]
+    q_out = torch.empty(t, n_q_heads, D, dtype=torch.bfloat16, device=q_src.device)
+    gate_out = torch.empty_like(q_out) if gate_in_q else None
+    rc = _lib.lib().b200_qk_norm_rope_append(
+        _lib.ptr(q_src), q_src.stride(0), q_off, q_head_stride, int(gate_in_q),
+        _lib.ptr(k_src), k_src.stride(0), k_off, _lib.ptr(v_src), v_src.stride(0), v_off,
+        _lib.ptr(q_gamma), _lib.ptr(k_gamma), int(unit_offset), _f(eps), _lib.ptr(inv_freq), rot, _f(mscale),
+        _lib.ptr(positions), _lib.ptr(slots), _lib.ptr(q_out), _lib.ptr(gate_out), _lib.ptr(k_cache),
+        _lib.ptr(v_cache), bs, t, n_q_heads, n_kv_heads, _lib.stream())
+    _lib.check(rc, "qk_norm_rope_append")
+    return q_out, gate_out
+
+
+def prefill(q, k_cache, v_cache, block_table, q_start, q_len, kv_len, max_q_len, gate=None, scale=None):
+    """Causal attention of new query rows against the paged cache (which already holds their K/V).
+
+    q: [T, Hq, 128]; block_table [B, max_blocks] int32; q_start/q_len/kv_len [B] int32 device tensors.
+    """
+    t, hq, d = q.shape
+    assert d == D
+    nb, hkv, bs, _ = k_cache.shape
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    rc = _lib.lib().b200_gqa_prefill(
+        _lib.ptr(q), _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(out), _lib.ptr(gate), _lib.ptr(block_table),
+        _lib.ptr(q_start), _lib.ptr(q_len), _lib.ptr(kv_len), block_table.shape[0], int(max_q_len), t,
+        block_table.shape[1], nb, bs, hq, hkv, _f(scale), _lib.ptr(_lib.status_word(q.device)), _lib.stream())
+    _lib.check(rc, "gqa_prefill")
+    return out
+
+
+_dec_ws: dict[int, torch.Tensor] = {}
+
+
+def decode(q, k_cache, v_cache, block_table, kv_len, gate=None, scale=None, splits: int | None = None,
+           max_kv_len: int | None = None):
+    """One query row per sequence. q: [B, Hq, 128]."""
+    b, hq, d = q.shape
+    nb, hkv, bs, _ = k_cache.shape
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    if splits is None:
+        ctx = max_kv_len if max_kv_len is not None else block_table.shape[1] * bs
+        splits = max(1, min(64, (2 * 148) // max(1, b * hkv), (ctx + 255) // 256))
+    ws = None
+    if splits > 1:
+        need = b * hq * splits * (D + 2)
+        dev = q.device.index or 0
+        ws = _dec_ws.get(dev)
+        if ws is None or ws.numel() < need:
+            ws = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device)
+            _dec_ws[dev] = ws
+    rc = _lib.lib().b200_gqa_decode(_lib.ptr(q), _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(out), _lib.ptr(gate),
+                                    _lib.ptr(block_table), _lib.ptr(kv_len), _lib.ptr(ws), b, block_table.shape[1],
+                                    bs, hq, hkv, splits, _f(scale), _lib.stream())
+    _lib.check(rc, "gqa_decode")
+    return out
+
+
+# ---------------------------------------------------------------- fp32 oracles
+def rope_ref(x, positions, inv_freq, rot):
+    """Half-split rotation over the first ``rot`` dims. x: [T, H, D] fp32."""
+    half = rot // 2
+    ang = positions.double()[:, None] * inv_freq.double()[None, :]
+    cos, sin = ang.cos().float()[:, None, :], ang.sin().float()[:, None, :]
+    a, b = x[..., :half], x[..., half:rot]
+    return torch.cat([a * cos - b * sin, b * cos + a * sin, x[..., rot:]], -1)
+
+
+def attention_ref(q, k, v, causal_offset: int, gate=None, scale=None):
+    """q [Tq, Hq, D], k/v [Tk, Hkv, D] fp32; query i sees keys <= causal_offset + i."""
+    tq, hq, d = q.shape
+    tk, hkv, _ = k.shape
+    g = hq // hkv
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    kk = k.float().repeat_interleave(g, 1)
+    vv = v.float().repeat_interleave(g, 1)
+    s = torch.einsum("qhd,khd->hqk", q.float(), kk) * scale
+    mask = torch.arange(tk, device=q.device)[None, :] > (causal_offset + torch.arange(tq, device=q.device))[:, None]
+    s = s.masked_fill(mask[None], float("-inf"))
+    o = torch.einsum("hqk,khd->qhd", s.softmax(-1), vv)
+    if gate is not None:
+        o = o * torch.sigmoid(gate.float())
+    return o

@@ -1,0 +1,69 @@
+"""Gated DeltaNet kernels (csrc/kernels/gdn.cu): chunked scan for prefill, single step for decode."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+_ll = ctypes.c_longlong
+_ws: dict[int, torch.Tensor] = {}
+
+
+def _workspace(n: int, device) -> torch.Tensor:
+    dev = torch.device(device).index or 0
+    ws = _ws.get(dev)
+    if ws is None or ws.numel() < n:
+        ws = torch.empty(n, dtype=torch.float32, device=device)
+        _ws[dev] = ws
+    return ws
+
+
+def chunked(mixed, q_off, k_off, v_off, g, beta, state, hv, hk):
+    """mixed [T, ld] bf16 (q|k|v after conv), g/beta [T, Hv] fp32, state [Hv,128,128] fp32 (in place)."""
+    t = mixed.shape[0]
+    out = torch.empty(t, hv, 128, dtype=torch.bfloat16, device=mixed.device)
+    L = _lib.lib()
+    L.b200_gdn_workspace_floats.restype = ctypes.c_longlong
+    ws = _workspace(int(L.b200_gdn_workspace_floats(t, hv)), mixed.device)
+    rc = L.b200_gdn_chunked(_lib.ptr(mixed), mixed.stride(0), q_off, k_off, v_off, _lib.ptr(g), _lib.ptr(beta),
+                            _lib.ptr(state), _lib.ptr(out), _lib.ptr(ws), t, hv, hk, _lib.stream())
+    _lib.check(rc, "gdn_chunked")
+    return out
+
+
+def step(states, slot_ids, mixed, q_off, k_off, v_off, g, beta, hv, hk):
+    """states [slots, Hv, 128, 128] fp32 in place; mixed [B, ld]; returns [B, Hv, 128] bf16."""
+    b = mixed.shape[0]
+    out = torch.empty(b, hv, 128, dtype=torch.bfloat16, device=mixed.device)
+    rc = _lib.lib().b200_gdn_step(_lib.ptr(states), _ll(states.stride(0)), _lib.ptr(slot_ids), _lib.ptr(mixed),
+                                  mixed.stride(0), q_off, k_off, v_off, _lib.ptr(g), _lib.ptr(beta), _lib.ptr(out),
+                                  b, hv, hk, _lib.stream())
+    _lib.check(rc, "gdn_step")
+    return out
+
+
+def recurrent_ref(q, k, v, g, beta, state):
+    """fp32 oracle, token by token. q,k [T,Hk,128]; v [T,Hv,128]; g,beta [T,Hv]; state [Hv,128,128] (dk, dv).
+
+    Same recurrence as the reference's step kernel (cpp_engine/backends/cuda/kernels/qwen_half_ops.cu:2282-2347).
+    """
+    t, hk, dk = q.shape
+    hv = v.shape[1]
+    rep = hv // hk
+    qf = q.float()
+    kf = k.float()
+    qf = qf * torch.rsqrt(qf.pow(2).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5
+    kf = kf * torch.rsqrt(kf.pow(2).sum(-1, keepdim=True) + 1e-6)
+    qf = qf.repeat_interleave(rep, 1)
+    kf = kf.repeat_interleave(rep, 1)
+    s = state.float().clone()
+    outs = []
+    for i in range(t):
+        s = s * torch.exp(g[i].float())[:, None, None]
+        kv_mem = torch.einsum("hkv,hk->hv", s, kf[i])
+        delta = (v[i].float() - kv_mem) * beta[i].float()[:, None]
+        s = s + kf[i][:, :, None] * delta[:, None, :]
+        outs.append(torch.einsum("hkv,hk->hv", s, qf[i]))
+    return torch.stack(outs), s
