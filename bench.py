@@ -1,0 +1,195 @@
+#!/usr/bin/env python
+"""Headline benchmark: prefill and decode tokens/s of the Qwen3.8-27B-FP8-shaped hybrid model
+(64 layers, hidden 5120, 48 Gated-DeltaNet + 16 gated-GQA layers, FP8 E4M3 128x128 block-scaled
+weights, bf16 activations) with synthetic random-init weights and random-token prompts.
+
+One step = one request: prefill of ``--prompt`` tokens, then ``--decode`` greedy tokens at batch 1
+over the paged KV cache (+ an optional batch-32 decode phase reported separately).  Phases are
+device-timed with CUDA events, max over ranks; ``value`` is prefill tokens/s (the reference's
+headline number, docs/benchmarking.md:21-32 convention: first generated token belongs to prefill).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+N > 1 is launched by ``python -m torch.distributed.run --nproc-per-node N`` (tensor parallel over NCCL/NVLink).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PUBLISHED_PREFILL_TPS = 1811.1   # reference, 8,192-token prompt, 4x RTX 2080 Ti (cpp_engine/include/qwen_engine.hpp:54-55)
+PUBLISHED_DECODE_TPS = 37.12     # reference, batch-1 decode, same hardware (docs/models/qwen3.8-27b-fp8.md:71)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--prompt", type=int, default=8192)
+    ap.add_argument("--decode", type=int, default=256)
+    ap.add_argument("--batch-decode", type=int, default=32, help="extra batched decode phase (0 = skip)")
+    ap.add_argument("--layers", type=int, default=64, help="debug only; the reported config is 64")
+    ap.add_argument("--chunk", type=int, default=8192)
+    return ap.parse_args()
+
+
+def run_reference(args) -> None:
+    from baseline import reference_arm
+    print(json.dumps(reference_arm.run(args)), flush=True)
+
+
+def main() -> None:
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    import torch
+    import torch.distributed as dist
+
+    from deepseek_v4_2080ti_b200.models import qwen_hybrid as qh
+    from deepseek_v4_2080ti_b200.ops import _lib
+    from deepseek_v4_2080ti_b200.parallel import tp
+    from deepseek_v4_2080ti_b200.utils.clocks import ClockSampler
+
+    rank, world, local = tp.init_distributed()
+    assert world == args.gpus or world == 1, (world, args.gpus)
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    comm = tp.TPComm() if world > 1 else None
+
+    cfg = qh.QwenHybridConfig.config2()
+    if args.layers != 64:
+        cfg = qh.QwenHybridConfig(num_hidden_layers=args.layers)
+    bdec = args.batch_decode
+    max_slots = max(1, bdec) + 1
+    t0 = time.time()
+    weights = qh.QwenHybridWeights(cfg, qh.synth_state(cfg, 0, dev), dev, rank, world)
+    rt = qh.QwenHybridRuntime(cfg, weights, max_slots=max_slots, max_context=args.prompt + args.decode + 64,
+                              comm=comm, num_blocks=((args.prompt + args.decode + 64 + 63) // 64) * 2 + max_slots * 8 + 2)
+    torch.cuda.synchronize()
+    if rank == 0:
+        print(f"[bench] weights {weights.nbytes() / 1e9:.2f} GB/rank built in {time.time() - t0:.1f}s", file=sys.stderr)
+
+    gen = torch.Generator().manual_seed(1)
+    prompt_host = torch.randint(0, cfg.vocab_size, (args.prompt,), generator=gen, dtype=torch.int32).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def one_request(timed: bool):
+        """prefill + batch-1 decode of one request through the runtime; returns (prefill_ms, decode_ms, launches)."""
+        slot = rt.allocate()
+        e0, e1, e2 = ev(), ev(), ev()
+        e0.record()
+        ids = prompt_host.to(dev, non_blocking=True)          # H2D of this step's input from pinned memory
+        tok = rt.prefill(slot, ids, args.chunk)
+        first = int(tok.item())                                # D2H of the step's result
+        e1.record()
+        launches = rt.launches
+        toks = [first]
+        for _ in range(args.decode - 1):
+            tok = rt.decode([slot], tok.to(torch.int32))
+            launches += rt.launches
+        last = int(tok.item())
+        e2.record()
+        torch.cuda.synchronize()
+        rt.free(slot)
+        return e0.elapsed_time(e1), e1.elapsed_time(e2), launches, (first, last)
+
+    def batch_decode_phase(steps: int):
+        """bdec sequences with short prompts decoding together; returns ms per step."""
+        slots = [rt.allocate() for _ in range(bdec)]
+        firsts = []
+        for i, s in enumerate(slots):
+            p = torch.randint(0, cfg.vocab_size, (64,), generator=gen, dtype=torch.int32).to(dev)
+            firsts.append(rt.prefill(s, p))
+        cur = torch.cat(firsts).to(torch.int32)
+        for _ in range(3):
+            cur = rt.decode(slots, cur).to(torch.int32).clone()
+        barrier()
+        e0, e1 = ev(), ev()
+        e0.record()
+        for _ in range(steps):
+            cur = rt.decode(slots, cur).to(torch.int32).clone()
+        e1.record()
+        torch.cuda.synchronize()
+        for s in slots:
+            rt.free(s)
+        return e0.elapsed_time(e1) / steps
+
+    for _ in range(args.warmup):
+        one_request(False)
+    barrier()
+    pre_ms, dec_ms, launches, step_ms = [], [], 0, []
+    with ClockSampler(local) as clk:
+        barrier()
+        w0 = time.time()
+        for _ in range(args.steps):
+            p, d, l, _ = one_request(True)
+            pre_ms.append(p)
+            dec_ms.append(d)
+            launches += l
+        barrier()
+        wall = time.time() - w0
+        bd_ms = batch_decode_phase(64) if bdec > 0 else None
+    _lib.check_status()
+    clocks = clk.summary()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    pre = max_over_ranks(sum(pre_ms) / len(pre_ms))
+    dec = max_over_ranks(sum(dec_ms) / len(dec_ms))
+    wall_step = max_over_ranks(wall / args.steps * 1e3)
+    prefill_tps = args.prompt / (pre / 1e3)
+    decode_tps = (args.decode - 1) / (dec / 1e3)
+    if rank == 0:
+        rec = {
+            "metric": "prefill_tok_s", "value": round(prefill_tps, 1), "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(pre + dec, 3),
+            "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": round(prefill_tps / PUBLISHED_PREFILL_TPS, 2), "dtype": "bf16",
+            "data": "synthetic (random-init FP8 block-128 weights, random token ids)", "impl": "b200",
+            "prefill_ms": round(pre, 3), "decode_tok_s": round(decode_tps, 2),
+            "decode_ms_per_token": round(dec / (args.decode - 1), 4),
+            "decode_vs_baseline": round(decode_tps / PUBLISHED_DECODE_TPS, 2),
+            "config": {"model": "Qwen3.8-27B-FP8-shaped hybrid (64L, hidden 5120, 48 GDN + 16 gated GQA, vocab 151936)"
+                       if args.layers == 64 else f"DEBUG {args.layers} layers",
+                       "global_batch": 1, "seq_len": args.prompt, "decode_tokens": args.decode,
+                       "parallelism": f"tp{world}", "weights": "fp8_e4m3_block128", "kv_cache": "bf16 paged (block 64)",
+                       "l2_policy": "inputs larger than L2: every step streams the full weight set (>= 3 GB/rank)"},
+            "e2e": {"value": round(args.prompt / (pre / 1e3), 1), "unit": "tok/s",
+                    "what": "QwenHybridRuntime.prefill incl. H2D of prompt ids from pinned memory and D2H of the next token",
+                    "h2d_bytes_per_step": int(prompt_host.numel() * 4), "d2h_bytes_per_step": 4 * args.decode,
+                    "wall_ms_per_step": round(wall_step, 3)},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        if bd_ms is not None:
+            bd = max_over_ranks(bd_ms)
+            rec["decode_batch"] = {"batch": bdec, "ms_per_step": round(bd, 4), "tok_s": round(bdec / (bd / 1e3), 1)}
+        print(json.dumps(rec), flush=True)
+    elif bd_ms is not None:
+        max_over_ranks(bd_ms)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

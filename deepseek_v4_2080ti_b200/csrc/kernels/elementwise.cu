@@ -124,7 +124,7 @@ __global__ void rmsnorm_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfloat1
 // Per-head norm over head_dim (<= 256, % 8 == 0) with a SiLU gate: one warp per (row, head).
 __global__ void gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate,
                                      const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ out,
-                                     size_t nrows, int dim, float eps) {
+                                     size_t nrows, int dim, float eps, int heads, size_t gate_ld) {
   const size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= nrows) return;
   const int lane = threadIdx.x & 31;
@@ -143,7 +143,8 @@ __global__ void gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const 
   if (act) {
     bf16x8 g, z;
     g.u = *reinterpret_cast<const uint4*>(gamma + v * 8);
-    z.u = *reinterpret_cast<const uint4*>(gate + row * dim + v * 8);
+    // gate row (t, head) may live inside a wider projection output: gate + t * gate_ld + head * dim
+    z.u = *reinterpret_cast<const uint4*>(gate + (row / heads) * gate_ld + (row % heads) * dim + v * 8);
     float gf[8], zf[8], o[8];
     g.unpack(gf);
     z.unpack(zf);
@@ -411,12 +412,12 @@ int b200_rmsnorm(void* x, const void* delta, const float* partials, int splits, 
 }
 
 int b200_gated_rmsnorm(const void* x, const void* gate, const void* gamma, void* out, long long nrows,
-                       int dim, float eps, cudaStream_t stream) {
+                       int dim, float eps, int heads, long long gate_ld, cudaStream_t stream) {
   if (dim % 8 || dim > 256) return -6;
   const int wpb = 8;
   gated_rmsnorm_kernel<<<(unsigned)((nrows + wpb - 1) / wpb), wpb * 32, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(gate),
-      reinterpret_cast<const __nv_bfloat16*>(gamma), reinterpret_cast<__nv_bfloat16*>(out), (size_t)nrows, dim, eps);
+      reinterpret_cast<const __nv_bfloat16*>(gamma), reinterpret_cast<__nv_bfloat16*>(out), (size_t)nrows, dim, eps, heads, (size_t)gate_ld);
   return rc();
 }
 

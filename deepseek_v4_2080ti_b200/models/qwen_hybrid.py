@@ -1,0 +1,620 @@
+"""Qwen-style hybrid runtime: Gated DeltaNet layers interleaved with gated full GQA attention.
+
+Covers what the reference's native ``QwenEngine`` does (cpp_engine/engine/qwen_engine.cpp:
+``run_chunk`` :4089-4269, ``layer_forward`` :3159-3313, ``linear_attention`` :2297-2540,
+``full_attention`` :2544-3155): FP8 block-128 weights, bf16 activations, paged KV cache,
+per-slot recurrent state, chunked prefill, batched decode, vocab-parallel embedding/head and
+tensor-parallel sharding of heads and MLP.  Every op on the forward path is one of this
+package's sm_100a kernels; decode steps are replayed from CUDA graphs.
+"""
+from __future__ import annotations
+
+import json
+import math
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Callable, Iterator
+
+import torch
+
+from ..formats import fp8 as fp8fmt
+from ..ops import _lib, attention, basic, gdn, gemm
+from ..ops.gemm import PackedLinear
+
+
+# ------------------------------------------------------------------ config
+@dataclass
+class QwenHybridConfig:
+    vocab_size: int = 151936
+    hidden_size: int = 5120
+    intermediate_size: int = 17408
+    num_hidden_layers: int = 64
+    num_attention_heads: int = 40
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    attn_output_gate: bool = True
+    linear_num_key_heads: int = 16
+    linear_num_value_heads: int = 32
+    linear_key_head_dim: int = 128
+    linear_value_head_dim: int = 128
+    linear_conv_kernel_dim: int = 4
+    max_position_embeddings: int = 262144
+    rms_norm_eps: float = 1e-6
+    partial_rotary_factor: float = 0.25
+    rope_theta: float = 1e7
+    full_attention_interval: int = 4
+    layer_types: list[str] = field(default_factory=list)
+
+    def __post_init__(self):
+        if not self.layer_types:
+            self.layer_types = [
+                "full_attention" if (i + 1) % self.full_attention_interval == 0 else "linear_attention"
+                for i in range(self.num_hidden_layers)
+            ]
+        assert len(self.layer_types) == self.num_hidden_layers
+        assert self.head_dim == 128 and self.linear_key_head_dim == 128 and self.linear_value_head_dim == 128, \
+            "kernels are specialised for 128-wide heads"
+
+    @property
+    def rotary_dim(self) -> int:
+        return int(self.head_dim * self.partial_rotary_factor)
+
+    @staticmethod
+    def from_json(path: str | Path) -> "QwenHybridConfig":
+        """HF-style config.json (``Qwen3_5ForConditionalGeneration`` with ``text_config``), as parsed by
+        cpp_engine/core/qwen_config.cpp:150-240."""
+        raw = json.loads(Path(path).read_text())
+        tc = raw.get("text_config", raw)
+        rp = tc.get("rope_parameters", {}) or {}
+        known = {f for f in QwenHybridConfig.__dataclass_fields__}
+        kw = {k: v for k, v in tc.items() if k in known}
+        if "rope_theta" in rp:
+            kw["rope_theta"] = float(rp["rope_theta"])
+        if "partial_rotary_factor" in rp:
+            kw["partial_rotary_factor"] = float(rp["partial_rotary_factor"])
+        return QwenHybridConfig(**kw)
+
+    def to_json(self) -> str:
+        tc = {k: getattr(self, k) for k in self.__dataclass_fields__ if k not in ("rope_theta", "full_attention_interval")}
+        tc["model_type"] = "qwen3_5_text"
+        tc["rope_parameters"] = {"rope_type": "default", "rope_theta": self.rope_theta}
+        return json.dumps({"architectures": ["Qwen3_5ForConditionalGeneration"], "model_type": "qwen3_5",
+                           "text_config": tc}, indent=1)
+
+    @staticmethod
+    def config2() -> "QwenHybridConfig":
+        """The 27B-class benchmark shape: 64 layers, hidden 5120, 48 GDN + 16 gated-GQA layers."""
+        return QwenHybridConfig()
+
+    @staticmethod
+    def tiny(layers: int = 4, hidden: int = 256, vocab: int = 512) -> "QwenHybridConfig":
+        return QwenHybridConfig(vocab_size=vocab, hidden_size=hidden, intermediate_size=384, num_hidden_layers=layers,
+                                num_attention_heads=4, num_key_value_heads=2, linear_num_key_heads=2,
+                                linear_num_value_heads=4, max_position_embeddings=8192, full_attention_interval=2)
+
+
+# ------------------------------------------------------- synthetic checkpoints
+FP8_SUFFIXES = ("in_proj_qkv", "in_proj_z", "out_proj", "q_proj", "k_proj", "v_proj", "o_proj", "gate_proj",
+                "up_proj", "down_proj")
+
+
+def tensor_specs(cfg: QwenHybridConfig) -> list[tuple[str, tuple[int, ...], str]]:
+    """(name, shape, kind) for every checkpoint tensor, in the reference's naming
+    (cpp_engine/tests/qwen_parity_fixture.hpp:117-170). kind: fp8 | bf16 | norm | a_log | dt_bias."""
+    h, inter = cfg.hidden_size, cfg.intermediate_size
+    kd = cfg.linear_num_key_heads * cfg.linear_key_head_dim
+    vd = cfg.linear_num_value_heads * cfg.linear_value_head_dim
+    hv = cfg.linear_num_value_heads
+    qd = cfg.num_attention_heads * cfg.head_dim
+    kvd = cfg.num_key_value_heads * cfg.head_dim
+    out: list[tuple[str, tuple[int, ...], str]] = [
+        ("model.language_model.embed_tokens.weight", (cfg.vocab_size, h), "bf16"),
+        ("model.language_model.norm.weight", (h,), "norm"),
+        ("lm_head.weight", (cfg.vocab_size, h), "bf16"),
+    ]
+    for i, lt in enumerate(cfg.layer_types):
+        p = f"model.language_model.layers.{i}."
+        out += [(p + "input_layernorm.weight", (h,), "norm"), (p + "post_attention_layernorm.weight", (h,), "norm")]
+        if lt == "linear_attention":
+            a = p + "linear_attn."
+            out += [(a + "in_proj_qkv.weight", (2 * kd + vd, h), "fp8"), (a + "in_proj_z.weight", (vd, h), "fp8"),
+                    (a + "out_proj.weight", (h, vd), "fp8"), (a + "in_proj_a.weight", (hv, h), "bf16"),
+                    (a + "in_proj_b.weight", (hv, h), "bf16"), (a + "conv1d.weight", (2 * kd + vd, 1, cfg.linear_conv_kernel_dim), "conv"),
+                    (a + "A_log", (hv,), "a_log"), (a + "dt_bias", (hv,), "dt_bias"),
+                    (a + "norm.weight", (cfg.linear_value_head_dim,), "norm1")]
+        else:
+            a = p + "self_attn."
+            q_out = qd * (2 if cfg.attn_output_gate else 1)
+            out += [(a + "q_proj.weight", (q_out, h), "fp8"), (a + "k_proj.weight", (kvd, h), "fp8"),
+                    (a + "v_proj.weight", (kvd, h), "fp8"), (a + "o_proj.weight", (h, qd), "fp8"),
+                    (a + "q_norm.weight", (cfg.head_dim,), "norm"), (a + "k_norm.weight", (cfg.head_dim,), "norm")]
+        m = p + "mlp."
+        out += [(m + "gate_proj.weight", (inter, h), "fp8"), (m + "up_proj.weight", (inter, h), "fp8"),
+                (m + "down_proj.weight", (h, inter), "fp8")]
+    return out
+
+
+def synth_state(cfg: QwenHybridConfig, seed: int = 0, device: str | torch.device = "cpu",
+                std: float = 0.02) -> Iterator[tuple[str, torch.Tensor]]:
+    """Seeded random-init checkpoint tensors in checkpoint dtypes: N(0, std) weights quantised to
+    FP8 E4M3 with bf16 128x128 ``weight_scale_inv``; (1+gamma) norms near 0; plain norms near 1."""
+    gen = torch.Generator(device=device)
+    for idx, (name, shape, kind) in enumerate(tensor_specs(cfg)):
+        gen.manual_seed(seed * 1_000_003 + idx)
+        if kind == "fp8":
+            w = torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std
+            q, s = fp8fmt.quantize_block128(w)
+            del w
+            yield name, q
+            yield name + "_scale_inv", s
+        elif kind == "bf16":
+            yield name, (torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std).bfloat16()
+        elif kind == "conv":
+            yield name, (torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * 0.3).bfloat16()
+        elif kind == "norm":
+            yield name, (torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * 0.05).bfloat16()
+        elif kind == "norm1":
+            yield name, (1.0 + torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * 0.05).bfloat16()
+        elif kind == "a_log":
+            yield name, torch.log(torch.rand(shape, generator=gen, device=device) * 3.0 + 0.5).bfloat16()
+        elif kind == "dt_bias":
+            yield name, (torch.rand(shape, generator=gen, device=device) * 2.0 - 1.0).bfloat16()
+        else:
+            raise ValueError(kind)
+
+
+# ------------------------------------------------------------------ weights
+def _shard_rows(t: torch.Tensor, rank: int, world: int, group: int = 1) -> torch.Tensor:
+    n = t.shape[0] // world
+    assert n * world == t.shape[0] and n % group == 0
+    return t[rank * n:(rank + 1) * n]
+
+
+def _shard_scale_rows(s: torch.Tensor, rows: int, rank: int, world: int) -> torch.Tensor:
+    n = rows // world
+    assert n % 128 == 0 or world == 1, "TP shard of an FP8 matrix must keep whole 128-row scale blocks"
+    return s[rank * n // 128:(rank * n + n + 127) // 128]
+
+
+@dataclass
+class LayerWeights:
+    kind: str
+    in_ln: torch.Tensor
+    post_ln: torch.Tensor
+    proj: PackedLinear            # linear: qkv|z ; full: q(|gate)|k|v
+    out: PackedLinear             # out_proj / o_proj (row-parallel)
+    gate_up: PackedLinear
+    down: PackedLinear            # row-parallel
+    ab: PackedLinear | None = None
+    conv_w: torch.Tensor | None = None
+    a_log: torch.Tensor | None = None
+    dt_bias: torch.Tensor | None = None
+    gdn_norm: torch.Tensor | None = None
+    q_norm: torch.Tensor | None = None
+    k_norm: torch.Tensor | None = None
+
+
+class QwenHybridWeights:
+    """Device-resident, TP-sharded, kernel-ready weights built from (name, tensor) pairs."""
+
+    def __init__(self, cfg: QwenHybridConfig, state: Iterator[tuple[str, torch.Tensor]], device, tp_rank: int = 0,
+                 tp_world: int = 1):
+        self.cfg, self.device, self.rank, self.world = cfg, torch.device(device), tp_rank, tp_world
+        self.layers: list[LayerWeights | None] = [None] * cfg.num_hidden_layers
+        self._pending: dict[str, torch.Tensor] = {}
+        self.embed = self.lm_head = self.final_norm = None
+        self.vocab_lo = self.vocab_hi = 0
+        for name, t in state:
+            self._pending[name] = t
+            self._try_finish(name)
+        missing = [i for i, l in enumerate(self.layers) if l is None]
+        if missing or self.embed is None or self.lm_head is None or self.final_norm is None:
+            raise ValueError(f"checkpoint incomplete: layers {missing[:4]}... pending {list(self._pending)[:6]}")
+
+    # -- helpers
+    def _dev(self, t):
+        return t.to(self.device, non_blocking=True)
+
+    def _fp8(self, base: str):
+        return self._pending.pop(base + ".weight"), self._pending.pop(base + ".weight_scale_inv")
+
+    def _col_fp8(self, parts: list[tuple[torch.Tensor, torch.Tensor, int]]) -> PackedLinear:
+        """Concatenate column-parallel FP8 pieces (each already row-sharded) along N."""
+        ws, ss = [], []
+        for w, s, rows_total in parts:
+            ws.append(self._dev(w))
+            ss.append(self._dev(s))
+        w = torch.cat(ws, 0) if len(ws) > 1 else ws[0]
+        s = torch.cat(ss, 0) if len(ss) > 1 else ss[0]
+        return PackedLinear.from_fp8(w.contiguous(), s.contiguous())
+
+    def _rows_fp8(self, w, s, group_rows: int | None = None):
+        """Row (output-feature) shard of an FP8 matrix + its scale rows."""
+        if self.world == 1:
+            return w, s, w.shape[0]
+        n = w.shape[0] // self.world
+        assert n % 128 == 0, f"TP row shard {n} is not a multiple of the 128-row scale block"
+        r = self.rank
+        return w[r * n:(r + 1) * n], s[r * n // 128:(r + 1) * n // 128], w.shape[0]
+
+    def _cols_fp8(self, w, s) -> PackedLinear:
+        """Column (input-feature) shard for row-parallel matrices."""
+        if self.world > 1:
+            k = w.shape[1] // self.world
+            assert k % 128 == 0
+            r = self.rank
+            w, s = w[:, r * k:(r + 1) * k], s[:, r * k // 128:(r + 1) * k // 128]
+        return PackedLinear.from_fp8(self._dev(w).contiguous(), self._dev(s).contiguous())
+
+    def _try_finish(self, name: str) -> None:
+        cfg, P = self.cfg, self._pending
+        if name == "model.language_model.embed_tokens.weight":
+            t = P.pop(name)
+            n = (cfg.vocab_size + self.world - 1) // self.world
+            self.vocab_lo, self.vocab_hi = self.rank * n, min(cfg.vocab_size, (self.rank + 1) * n)
+            self.embed = self._dev(t[self.vocab_lo:self.vocab_hi]).contiguous()
+            return
+        if name == "lm_head.weight":
+            t = P.pop(name)
+            n = (cfg.vocab_size + self.world - 1) // self.world
+            lo, hi = self.rank * n, min(cfg.vocab_size, (self.rank + 1) * n)
+            self.lm_head = PackedLinear.from_bf16(self._dev(t[lo:hi]))
+            self.head_lo = lo
+            return
+        if name == "model.language_model.norm.weight":
+            self.final_norm = self._dev(P.pop(name))
+            return
+        if not name.startswith("model.language_model.layers."):
+            return
+        i = int(name.split(".")[3])
+        if self.layers[i] is not None:
+            return
+        p = f"model.language_model.layers.{i}."
+        lt = cfg.layer_types[i]
+        need = [p + "input_layernorm.weight", p + "post_attention_layernorm.weight"]
+        for m in ("gate_proj", "up_proj", "down_proj"):
+            need += [p + f"mlp.{m}.weight", p + f"mlp.{m}.weight_scale_inv"]
+        if lt == "linear_attention":
+            a = p + "linear_attn."
+            for m in ("in_proj_qkv", "in_proj_z", "out_proj"):
+                need += [a + m + ".weight", a + m + ".weight_scale_inv"]
+            need += [a + "in_proj_a.weight", a + "in_proj_b.weight", a + "conv1d.weight", a + "A_log", a + "dt_bias",
+                     a + "norm.weight"]
+        else:
+            a = p + "self_attn."
+            for m in ("q_proj", "k_proj", "v_proj", "o_proj"):
+                need += [a + m + ".weight", a + m + ".weight_scale_inv"]
+            need += [a + "q_norm.weight", a + "k_norm.weight"]
+        if not all(n in P for n in need):
+            return
+        W, R = self.world, self.rank
+        in_ln, post_ln = self._dev(P.pop(need[0])), self._dev(P.pop(need[1]))
+        g = self._rows_fp8(*self._fp8(p + "mlp.gate_proj"))
+        u = self._rows_fp8(*self._fp8(p + "mlp.up_proj"))
+        gate_up = self._col_fp8([g, u])
+        down = self._cols_fp8(*self._fp8(p + "mlp.down_proj"))
+        if lt == "linear_attention":
+            a = p + "linear_attn."
+            kd = cfg.linear_num_key_heads * 128
+            vd = cfg.linear_num_value_heads * 128
+            wq, sq = self._fp8(a + "in_proj_qkv")
+            pieces = []
+            conv = P.pop(a + "conv1d.weight").reshape(2 * kd + vd, -1)
+            conv_parts = []
+            for lo, n in ((0, kd), (kd, kd), (2 * kd, vd)):
+                per = n // W
+                assert per % 128 == 0
+                pieces.append((wq[lo + R * per:lo + (R + 1) * per], sq[(lo + R * per) // 128:(lo + (R + 1) * per) // 128], n))
+                conv_parts.append(conv[lo + R * per:lo + (R + 1) * per])
+            pieces.append(self._rows_fp8(*self._fp8(a + "in_proj_z")))
+            proj = self._col_fp8(pieces)
+            out = self._cols_fp8(*self._fp8(a + "out_proj"))
+            hv = cfg.linear_num_value_heads // W
+            wa = _shard_rows(P.pop(a + "in_proj_a.weight"), R, W)
+            wb = _shard_rows(P.pop(a + "in_proj_b.weight"), R, W)
+            ab = PackedLinear.from_bf16(self._dev(torch.cat([wa, wb], 0)))
+            self.layers[i] = LayerWeights(
+                "linear", in_ln, post_ln, proj, out, gate_up, down, ab=ab,
+                conv_w=self._dev(torch.cat(conv_parts, 0)).contiguous(),
+                a_log=self._dev(_shard_rows(P.pop(a + "A_log"), R, W)).float().contiguous(),
+                dt_bias=self._dev(_shard_rows(P.pop(a + "dt_bias"), R, W)).float().contiguous(),
+                gdn_norm=self._dev(P.pop(a + "norm.weight")))
+            assert hv * W == cfg.linear_num_value_heads
+        else:
+            a = p + "self_attn."
+            pieces = [self._rows_fp8(*self._fp8(a + "q_proj")), self._rows_fp8(*self._fp8(a + "k_proj")),
+                      self._rows_fp8(*self._fp8(a + "v_proj"))]
+            proj = self._col_fp8(pieces)
+            out = self._cols_fp8(*self._fp8(a + "o_proj"))
+            self.layers[i] = LayerWeights("full", in_ln, post_ln, proj, out, gate_up, down,
+                                          q_norm=self._dev(P.pop(a + "q_norm.weight")),
+                                          k_norm=self._dev(P.pop(a + "k_norm.weight")))
+
+    def nbytes(self) -> int:
+        n = self.embed.numel() * 2 + self.lm_head.nbytes()
+        for l in self.layers:
+            n += l.proj.nbytes() + l.out.nbytes() + l.gate_up.nbytes() + l.down.nbytes()
+            if l.ab is not None:
+                n += l.ab.nbytes()
+        return n
+
+
+# ------------------------------------------------------------------ runtime
+class NoComm:
+    """Single-rank stand-in for the tensor-parallel communicator."""
+    world, rank = 1, 0
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        return t
+
+    def argmax_merge(self, idx: torch.Tensor, val: torch.Tensor) -> torch.Tensor:
+        return idx
+
+
+@dataclass
+class SeqState:
+    slot: int
+    blocks: list[int] = field(default_factory=list)
+    length: int = 0
+
+
+class QwenHybridRuntime:
+    """Owns weights, the paged KV pool, per-slot recurrent state and the forward passes."""
+
+    def __init__(self, cfg: QwenHybridConfig, weights: QwenHybridWeights, max_slots: int = 1,
+                 max_context: int = 8192 + 512, block_size: int = 64, comm=None, num_blocks: int | None = None):
+        self.cfg, self.w, self.device = cfg, weights, weights.device
+        self.comm = comm or NoComm()
+        W = self.comm.world
+        assert W == weights.world
+        self.hq = cfg.num_attention_heads // W
+        self.hkv = max(1, cfg.num_key_value_heads // W)
+        assert cfg.num_key_value_heads % W == 0, "kv heads must divide over the TP group"
+        self.hk_lin = cfg.linear_num_key_heads // W
+        self.hv_lin = cfg.linear_num_value_heads // W
+        self.kd, self.vd = self.hk_lin * 128, self.hv_lin * 128
+        self.block_size = block_size
+        self.max_slots = max_slots
+        self.max_blocks_per_seq = (max_context + block_size - 1) // block_size
+        self.num_blocks = num_blocks or (self.max_blocks_per_seq * max_slots + 1)
+        self.full_layers = [i for i, t in enumerate(cfg.layer_types) if t == "full_attention"]
+        self.lin_layers = [i for i, t in enumerate(cfg.layer_types) if t == "linear_attention"]
+        dev = self.device
+        nf, nl = len(self.full_layers), len(self.lin_layers)
+        # block 0 is a scratch block: padded rows of a decode batch write their K/V there
+        self.k_cache = torch.zeros(nf, self.num_blocks, self.hkv, block_size, 128, dtype=torch.bfloat16, device=dev)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        self.states = torch.zeros(max_slots, nl, self.hv_lin, 128, 128, dtype=torch.float32, device=dev)
+        self.tails = torch.zeros(max_slots, nl, cfg.linear_conv_kernel_dim - 1, 2 * self.kd + self.vd,
+                                 dtype=torch.bfloat16, device=dev)
+        self.inv_freq = attention.rope_inv_freq(cfg.rotary_dim, cfg.rope_theta, dev)
+        self.free_blocks = list(range(self.num_blocks - 1, 0, -1))
+        self.free_slots = list(range(max_slots - 1, -1, -1))
+        self.seqs: dict[int, SeqState] = {}
+        self.block_table = torch.zeros(max_slots, self.max_blocks_per_seq, dtype=torch.int32, device=dev)
+        self._bt_host = torch.zeros(max_slots, self.max_blocks_per_seq, dtype=torch.int32)
+        self._graphs: dict[int, tuple] = {}
+        self.launches = 0  # kernels launched by the last forward (for the bench record)
+
+    # ---- slot / block management (host side)
+    def allocate(self) -> int:
+        slot = self.free_slots.pop()
+        self.seqs[slot] = SeqState(slot)
+        self.states[slot].zero_()
+        self.tails[slot].zero_()
+        return slot
+
+    def free(self, slot: int) -> None:
+        st = self.seqs.pop(slot)
+        self.free_blocks.extend(reversed(st.blocks))
+        self.free_slots.append(slot)
+
+    def _ensure_blocks(self, st: SeqState, new_len: int) -> None:
+        need = (new_len + self.block_size - 1) // self.block_size
+        if need > self.max_blocks_per_seq:
+            raise RuntimeError("sequence exceeds max_context")
+        changed = False
+        while len(st.blocks) < need:
+            if not self.free_blocks:
+                raise RuntimeError("KV cache exhausted")
+            b = self.free_blocks.pop()
+            self._bt_host[st.slot, len(st.blocks)] = b
+            st.blocks.append(b)
+            changed = True
+        if changed:
+            self.block_table[st.slot].copy_(self._bt_host[st.slot], non_blocking=True)
+
+    # ---- layer bodies
+    def _mlp(self, lw: LayerWeights, h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        x = basic.add_rmsnorm(h, delta, lw.post_ln, cfg.rms_norm_eps, True)
+        gu = gemm.linear(x, lw.gate_up)
+        act = basic.silu_mul(gu)
+        out = gemm.linear(act, lw.down)
+        return self.comm.all_reduce(out)
+
+    def _linear_attn(self, li: int, lw: LayerWeights, x: torch.Tensor, t: int, slots_t: torch.Tensor | None,
+                     slot: int | None) -> torch.Tensor:
+        cfg = self.cfg
+        proj = gemm.linear(x, lw.proj)                       # [T, 2kd + vd + vd]
+        ab = gemm.linear(x, lw.ab)                           # [T, 2 hv]
+        cw = 2 * self.kd + self.vd
+        idx = self.lin_layers.index(li)
+        g, beta = basic.gdn_gates(ab, 0, self.hv_lin, lw.a_log, lw.dt_bias, self.hv_lin)
+        if slot is not None:   # one sequence, T consecutive tokens
+            mixed = basic.conv_silu(proj[:, :cw], lw.conv_w, self.tails[slot, idx])
+            core = gdn.chunked(mixed, 0, self.kd, 2 * self.kd, g, beta, self.states[slot, idx], self.hv_lin, self.hk_lin)
+        else:                  # one token per sequence
+            mixed = basic.conv_silu_step(proj[:, :cw], lw.conv_w, self.tails[:, idx], slots_t)
+            core = gdn.step(self.states[:, idx], slots_t, mixed, 0, self.kd, 2 * self.kd, g, beta, self.hv_lin, self.hk_lin)
+        z = proj[:, cw:].unflatten(1, (self.hv_lin, 128))
+        y = basic.gated_rmsnorm(core, z, lw.gdn_norm, cfg.rms_norm_eps)
+        out = gemm.linear(y.view(t, self.vd), lw.out)
+        return self.comm.all_reduce(out)
+
+    def _full_attn(self, li: int, lw: LayerWeights, x: torch.Tensor, t: int, positions, kv_slots, meta) -> torch.Tensor:
+        cfg = self.cfg
+        idx = self.full_layers.index(li)
+        proj = gemm.linear(x, lw.proj)
+        gate_mul = 2 if cfg.attn_output_gate else 1
+        qw = self.hq * 128 * gate_mul
+        kc, vc = self.k_cache[idx], self.v_cache[idx]
+        q, gate = attention.qk_norm_rope_append(
+            proj, 0, 128 * gate_mul, cfg.attn_output_gate, proj, qw, proj, qw + self.hkv * 128, lw.q_norm, lw.k_norm,
+            True, cfg.rms_norm_eps, self.inv_freq, cfg.rotary_dim, positions, kv_slots, kc, vc, self.hq, self.hkv)
+        if meta["mode"] == "prefill":
+            o = attention.prefill(q, kc, vc, meta["block_table"], meta["q_start"], meta["q_len"], meta["kv_len"],
+                                  meta["max_q_len"], gate=gate)
+        else:
+            o = attention.decode(q, kc, vc, meta["block_table"], meta["kv_len"], gate=gate,
+                                 max_kv_len=meta["max_kv_len"])
+        out = gemm.linear(o.view(t, self.hq * 128), lw.out)
+        return self.comm.all_reduce(out)
+
+    def _embed(self, ids: torch.Tensor) -> torch.Tensor:
+        h = basic.embedding(ids, self.w.embed, self.w.vocab_lo, self.w.vocab_hi)
+        return self.comm.all_reduce(h)
+
+    def _forward(self, ids, positions, kv_slots, meta, slot, slots_t, logits_rows: torch.Tensor | None):
+        cfg, w = self.cfg, self.w
+        t = ids.numel()
+        h = self._embed(ids)
+        delta = None
+        for i, lw in enumerate(w.layers):
+            if delta is None:
+                x = basic.rmsnorm(h, lw.in_ln, cfg.rms_norm_eps, True)
+            else:
+                x = basic.add_rmsnorm(h, delta, lw.in_ln, cfg.rms_norm_eps, True)
+            if lw.kind == "linear":
+                d_attn = self._linear_attn(i, lw, x, t, slots_t, slot)
+            else:
+                d_attn = self._full_attn(i, lw, x, t, positions, kv_slots, meta)
+            delta = self._mlp(lw, h, d_attn)
+        if logits_rows is not None:
+            basic.add_(h, delta)
+            hs = h.index_select(0, logits_rows)
+            x = basic.rmsnorm(hs, w.final_norm, cfg.rms_norm_eps, True)
+        else:
+            x = basic.add_rmsnorm(h, delta, w.final_norm, cfg.rms_norm_eps, True)
+        logits = gemm.linear(x, w.lm_head, out_f32=True)
+        return logits
+
+    def _next_tokens(self, logits: torch.Tensor) -> torch.Tensor:
+        idx, val = basic.argmax(logits, self.w.head_lo, True)
+        return self.comm.argmax_merge(idx, val)
+
+    # ---- public: prefill one sequence (chunked), returns the next token id tensor [1] (device)
+    @torch.no_grad()
+    def prefill(self, slot: int, token_ids: torch.Tensor, chunk: int = 8192) -> torch.Tensor:
+        """token_ids: int32 device tensor [T]. Appends to the slot's context. Returns greedy next token."""
+        st = self.seqs[slot]
+        l0 = _lib.LAUNCHES
+        nxt = None
+        total = token_ids.numel()
+        for s in range(0, total, chunk):
+            ids = token_ids[s:s + chunk]
+            t = ids.numel()
+            self._ensure_blocks(st, st.length + t)
+            pos = torch.arange(st.length, st.length + t, dtype=torch.int32, device=self.device)
+            bt_row = self.block_table[slot]
+            kv_slots = (bt_row[(pos // self.block_size).long()] * self.block_size + pos % self.block_size).to(torch.int32)
+            i32 = lambda v: torch.tensor([v], dtype=torch.int32, device=self.device)
+            meta = {"mode": "prefill", "block_table": self.block_table[slot:slot + 1], "q_start": i32(0),
+                    "q_len": i32(t), "kv_len": i32(st.length + t), "max_q_len": t}
+            last = s + t >= total
+            rows = torch.tensor([t - 1], dtype=torch.int64, device=self.device)
+            logits = self._forward(ids, pos, kv_slots, meta, slot, None, rows)
+            st.length += t
+            if last:
+                nxt = self._next_tokens(logits)
+        self.launches = _lib.LAUNCHES - l0
+        return nxt
+
+    # ---- public: one decode step for a batch of slots
+    def _decode_buffers(self, b: int):
+        dev = self.device
+        return {
+            "ids": torch.zeros(b, dtype=torch.int32, device=dev),
+            "pos": torch.zeros(b, dtype=torch.int32, device=dev),
+            "kv_slots": torch.zeros(b, dtype=torch.int32, device=dev),
+            "slots": torch.zeros(b, dtype=torch.int32, device=dev),
+            "kv_len": torch.ones(b, dtype=torch.int32, device=dev),
+            "bt": torch.zeros(b, self.max_blocks_per_seq, dtype=torch.int32, device=dev),
+        }
+
+    def _decode_body(self, buf, max_kv_len: int) -> torch.Tensor:
+        meta = {"mode": "decode", "block_table": buf["bt"], "kv_len": buf["kv_len"], "max_kv_len": max_kv_len}
+        logits = self._forward(buf["ids"], buf["pos"], buf["kv_slots"], meta, None, buf["slots"], None)
+        return self._next_tokens(logits)
+
+    @torch.no_grad()
+    def decode(self, slots: list[int], token_ids: torch.Tensor, use_graph: bool = True) -> torch.Tensor:
+        """One new token for each slot. token_ids: int32 device tensor [B]. Returns next tokens [B] (device)."""
+        b = len(slots)
+        sts = [self.seqs[s] for s in slots]
+        for st in sts:
+            self._ensure_blocks(st, st.length + 1)
+        max_len = max(st.length for st in sts) + 1
+        bucket = 1 << max(10, (max_len - 1).bit_length())  # context bucket fixes the decode-attention split count
+        key = (b, bucket)
+        entry = self._graphs.get(key)
+        if entry is None:
+            entry = {"buf": self._decode_buffers(b), "graph": None, "out": None}
+            self._graphs[key] = entry
+        buf = entry["buf"]
+        host = torch.tensor([[st.length, st.length + 1, st.slot,
+                              st.blocks[st.length // self.block_size] * self.block_size + st.length % self.block_size]
+                             for st in sts], dtype=torch.int32)
+        dev = host.to(self.device, non_blocking=True)
+        buf["ids"].copy_(token_ids)
+        buf["pos"].copy_(dev[:, 0])
+        buf["kv_len"].copy_(dev[:, 1])
+        buf["slots"].copy_(dev[:, 2])
+        buf["kv_slots"].copy_(dev[:, 3])
+        buf["bt"].copy_(self.block_table[buf["slots"].long()])
+        if not use_graph:
+            l0 = _lib.LAUNCHES
+            out = self._decode_body(buf, bucket)
+            self.launches = _lib.LAUNCHES - l0
+        else:
+            if entry["graph"] is None:
+                # warm-up outside capture (lazy kernel attribute set-up, workspaces), on state copies
+                saved = (self.states.clone(), self.tails.clone())
+                self._decode_body(buf, bucket)
+                torch.cuda.synchronize()
+                self.states.copy_(saved[0])
+                self.tails.copy_(saved[1])
+                del saved
+                gph = torch.cuda.CUDAGraph()
+                l0 = _lib.LAUNCHES
+                with torch.cuda.graph(gph):
+                    entry["out"] = self._decode_body(buf, bucket)
+                entry["graph"] = gph
+                entry["launches"] = _lib.LAUNCHES - l0
+                # capture does not execute: run the step now
+            entry["graph"].replay()
+            self.launches = entry["launches"]
+            out = entry["out"]
+        for st in sts:
+            st.length += 1
+        return out
+
+    @torch.no_grad()
+    def generate(self, prompt: torch.Tensor, max_new_tokens: int, chunk: int = 8192, eos: int | None = None) -> list[int]:
+        slot = self.allocate()
+        try:
+            tok = self.prefill(slot, prompt.to(self.device, torch.int32), chunk)
+            out = [int(tok.item())]
+            while len(out) < max_new_tokens and (eos is None or out[-1] != eos):
+                tok = self.decode([slot], tok.to(torch.int32))
+                out.append(int(tok.item()))
+            return out
+        finally:
+            self.free(slot)
+
+
+def build_synthetic(cfg: QwenHybridConfig, device="cuda", seed: int = 0, tp_rank: int = 0, tp_world: int = 1,
+                    **rt_kwargs) -> QwenHybridRuntime:
+    """Random-init model of the given shape, generated on the device with the checkpoint writer's generator."""
+    w = QwenHybridWeights(cfg, synth_state(cfg, seed, device), device, tp_rank, tp_world)
+    return QwenHybridRuntime(cfg, w, **rt_kwargs)

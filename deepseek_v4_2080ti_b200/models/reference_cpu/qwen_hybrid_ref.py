@@ -1,0 +1,85 @@
+"""fp32 oracle for the Qwen-style hybrid model: plain PyTorch, whole-sequence forward, no caches.
+
+Math follows the reference's engine (cpp_engine/engine/qwen_engine.cpp:2297-3313) with the
+chunk-free token recurrence for Gated DeltaNet (cpp_engine/backends/cuda/kernels/qwen_half_ops.cu:2282-2347).
+Intermediate activations are rounded to bf16 where the GPU runtime stores them in bf16, so the
+comparison isolates kernel error from storage rounding.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from ...formats import fp8 as fp8fmt
+from ...ops.attention import attention_ref, rope_ref
+from ...ops.basic import conv_silu_ref, gated_rmsnorm_ref, gdn_gates_ref, rmsnorm_ref
+from ...ops.gdn import recurrent_ref
+
+
+def _r(x):  # storage rounding
+    return x.to(torch.bfloat16).float()
+
+
+class QwenHybridRef:
+    def __init__(self, cfg, state):
+        self.cfg = cfg
+        raw = dict(state)
+        self.p = {}
+        for k, v in raw.items():
+            if k.endswith(".weight_scale_inv"):
+                continue
+            if v.dtype == torch.float8_e4m3fn:
+                self.p[k] = fp8fmt.dequantize_block128(v, raw[k + "_scale_inv"])
+            else:
+                self.p[k] = v.float()
+
+    def lin(self, x, name):
+        return x @ self.p[name + ".weight"].t()
+
+    @torch.no_grad()
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        """ids [T] -> logits [T, vocab] fp32 (single sequence from position 0)."""
+        cfg, p = self.cfg, self.p
+        t = ids.numel()
+        eps = cfg.rms_norm_eps
+        h = p["model.language_model.embed_tokens.weight"][ids.long()]
+        pos = torch.arange(t, device=ids.device)
+        inv = (1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.rotary_dim, 2, dtype=torch.float64) / cfg.rotary_dim))).float().to(ids.device)
+        for i, lt in enumerate(cfg.layer_types):
+            pre = f"model.language_model.layers.{i}."
+            x = _r(rmsnorm_ref(h, p[pre + "input_layernorm.weight"], eps, True))
+            if lt == "linear_attention":
+                a = pre + "linear_attn."
+                hk, hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+                qkv = _r(self.lin(x, a + "in_proj_qkv"))
+                z = _r(self.lin(x, a + "in_proj_z"))
+                av, bv = _r(self.lin(x, a + "in_proj_a")), _r(self.lin(x, a + "in_proj_b"))
+                conv_w = p[a + "conv1d.weight"].reshape(qkv.shape[1], -1)
+                mixed, _ = conv_silu_ref(qkv, conv_w, torch.zeros(conv_w.shape[1] - 1, qkv.shape[1], device=ids.device))
+                mixed = _r(mixed)
+                g, beta = gdn_gates_ref(av, bv, p[a + "A_log"], p[a + "dt_bias"])
+                q = mixed[:, :hk * 128].view(t, hk, 128)
+                k = mixed[:, hk * 128:2 * hk * 128].view(t, hk, 128)
+                v = mixed[:, 2 * hk * 128:].view(t, hv, 128)
+                core, _ = recurrent_ref(q, k, v, g, beta, torch.zeros(hv, 128, 128, device=ids.device))
+                y = _r(gated_rmsnorm_ref(_r(core), z.view(t, hv, 128), p[a + "norm.weight"], eps))
+                d = _r(self.lin(y.reshape(t, -1), a + "out_proj"))
+            else:
+                a = pre + "self_attn."
+                hq, hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+                qg = _r(self.lin(x, a + "q_proj")).view(t, hq, -1)
+                q, gate = (qg[..., :128], qg[..., 128:]) if cfg.attn_output_gate else (qg, None)
+                k = _r(self.lin(x, a + "k_proj")).view(t, hkv, 128)
+                v = _r(self.lin(x, a + "v_proj")).view(t, hkv, 128)
+                q = _r(rope_ref(rmsnorm_ref(q, p[a + "q_norm.weight"], eps, True), pos, inv, cfg.rotary_dim))
+                k = _r(rope_ref(rmsnorm_ref(k, p[a + "k_norm.weight"], eps, True), pos, inv, cfg.rotary_dim))
+                o = _r(attention_ref(q, k, v, 0, gate))
+                d = _r(self.lin(o.reshape(t, -1), a + "o_proj"))
+            h = _r(h + d)
+            x = _r(rmsnorm_ref(h, p[pre + "post_attention_layernorm.weight"], eps, True))
+            gu = torch.cat([_r(self.lin(x, pre + "mlp.gate_proj")), _r(self.lin(x, pre + "mlp.up_proj"))], -1)
+            g_, u_ = gu.chunk(2, -1)
+            act = _r(F.silu(g_) * u_)
+            h = _r(h + _r(self.lin(act, pre + "mlp.down_proj")))
+        x = _r(rmsnorm_ref(h, p["model.language_model.norm.weight"], eps, True))
+        return x @ p["lm_head.weight"].t()

@@ -85,7 +85,12 @@ def check_status(device=None) -> None:
         raise KernelError(f"device kernel reported error {code}: {ERR_NAMES.get(code, 'unknown')}")
 
 
-def check(rc: int, what: str) -> None:
+LAUNCHES = 0  # kernels launched through this module (eager count; graph replays are added by the caller)
+
+
+def check(rc: int, what: str, n_kernels: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += n_kernels
     if rc != 0:
         if rc < 0:
             raise KernelError(f"{what}: {ERR_NAMES.get(-rc, 'error')} ({rc})")

@@ -83,7 +83,7 @@ def decode(q, k_cache, v_cache, block_table, kv_len, gate=None, scale=None, spli
     rc = _lib.lib().b200_gqa_decode(_lib.ptr(q), _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(out), _lib.ptr(gate),
                                     _lib.ptr(block_table), _lib.ptr(kv_len), _lib.ptr(ws), b, block_table.shape[1],
                                     bs, hq, hkv, splits, _f(scale), _lib.stream())
-    _lib.check(rc, "gqa_decode")
+    _lib.check(rc, "gqa_decode", 2 if splits > 1 else 1)
     return out
 
 

@@ -45,11 +45,14 @@ def rmsnorm_ref(x, gamma, eps=1e-6, unit_offset=False):
 
 
 def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
-    """Per-head norm with SiLU gate.  x, gate: [..., dim] (dim <= 256) bf16 contiguous."""
+    """Per-head norm with SiLU gate.  x: [T, heads, dim] contiguous bf16 (dim <= 256);
+    gate: same logical shape, last two dims contiguous, any row stride (a slice of a wider projection)."""
     dim = x.shape[-1]
+    heads = x.shape[-2] if x.dim() >= 2 else 1
+    gate_ld = gate.stride(0) if gate.dim() == 3 else heads * dim
     out = torch.empty_like(x)
     rc = _lib.lib().b200_gated_rmsnorm(_lib.ptr(x), _lib.ptr(gate), _lib.ptr(gamma), _lib.ptr(out),
-                                       _ll(x.numel() // dim), dim, _f(eps), _lib.stream())
+                                       _ll(x.numel() // dim), dim, _f(eps), heads, _ll(gate_ld), _lib.stream())
     _lib.check(rc, "gated_rmsnorm")
     return out
 

@@ -29,7 +29,7 @@ def chunked(mixed, q_off, k_off, v_off, g, beta, state, hv, hk):
     ws = _workspace(int(L.b200_gdn_workspace_floats(t, hv)), mixed.device)
     rc = L.b200_gdn_chunked(_lib.ptr(mixed), mixed.stride(0), q_off, k_off, v_off, _lib.ptr(g), _lib.ptr(beta),
                             _lib.ptr(state), _lib.ptr(out), _lib.ptr(ws), t, hv, hk, _lib.stream())
-    _lib.check(rc, "gdn_chunked")
+    _lib.check(rc, "gdn_chunked", 2)
     return out
 
 

@@ -1,0 +1,73 @@
+"""End-to-end Qwen-style hybrid runtime vs the fp32 oracle on a tiny synthetic checkpoint,
+plus engine-mode invariants (chunked == unchunked prefill, graph == eager decode, batched == serial)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _build(layers=4, seed=0, **kw):
+    from deepseek_v4_2080ti_b200.models import qwen_hybrid as qh
+    cfg = qh.QwenHybridConfig.tiny(layers=layers)
+    state = list(qh.synth_state(cfg, seed, "cuda", std=0.05))
+    w = qh.QwenHybridWeights(cfg, iter(state), "cuda")
+    rt = qh.QwenHybridRuntime(cfg, w, **kw)
+    return cfg, state, rt
+
+
+def test_logits_match_fp32_oracle():
+    from deepseek_v4_2080ti_b200.models.reference_cpu.qwen_hybrid_ref import QwenHybridRef
+    from deepseek_v4_2080ti_b200.ops import _lib
+    cfg, state, rt = _build()
+    ref = QwenHybridRef(cfg, state)
+    torch.manual_seed(1)
+    ids = torch.randint(0, cfg.vocab_size, (150,), device="cuda", dtype=torch.int32)
+    want = ref.forward(ids)
+    slot = rt.allocate()
+    # drive the internals to get full logits for the last row
+    nxt = rt.prefill(slot, ids)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert int(nxt.item()) == int(want[-1].argmax().item())
+    # decode continues the same greedy stream as the oracle run on the extended prompt
+    toks = [int(nxt.item())]
+    cur = nxt
+    for _ in range(5):
+        cur = rt.decode([slot], cur.to(torch.int32))
+        toks.append(int(cur.item()))
+    ext = torch.cat([ids, torch.tensor(toks[:-1], device="cuda", dtype=torch.int32)])
+    want2 = ref.forward(ext)
+    agree = sum(int(want2[149 + i].argmax().item()) == toks[i] for i in range(6))
+    assert agree >= 5, (agree, toks)
+
+
+def test_chunked_prefill_equals_unchunked():
+    cfg, state, rt = _build(max_slots=2)
+    torch.manual_seed(2)
+    ids = torch.randint(0, cfg.vocab_size, (333,), device="cuda", dtype=torch.int32)
+    a, b = rt.allocate(), rt.allocate()
+    na = rt.prefill(a, ids)
+    nb = rt.prefill(b, ids, chunk=100)
+    assert int(na.item()) == int(nb.item())
+    da = rt.decode([a], na.to(torch.int32), use_graph=False)
+    db = rt.decode([b], nb.to(torch.int32), use_graph=True)
+    assert int(da.item()) == int(db.item())
+
+
+def test_batched_decode_equals_serial():
+    cfg, state, rt = _build(max_slots=3)
+    torch.manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), device="cuda", dtype=torch.int32) for n in (40, 90, 17)]
+    slots = [rt.allocate() for _ in prompts]
+    firsts = [rt.prefill(s, p) for s, p in zip(slots, prompts)]
+    cur = torch.cat(firsts).to(torch.int32)
+    batched = []
+    for _ in range(4):
+        cur = rt.decode(slots, cur).to(torch.int32).clone()
+        batched.append(cur.tolist())
+    for s in slots:
+        rt.free(s)
+    # serial reruns
+    for i, p in enumerate(prompts):
+        out = rt.generate(p, 5)
+        assert out[1:] == [step[i] for step in batched], (i, out, batched)
