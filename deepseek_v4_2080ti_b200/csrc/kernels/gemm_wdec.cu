@@ -419,6 +419,11 @@ extern "C" int b200_gemm_wdec(int wfmt, const void* W, const float* scales, cons
   p.n_tiles = (T + BN - 1) / BN;
   p.kb_total = (K + BK - 1) / BK;
   if (splits > p.kb_total) splits = p.kb_total;
+  {
+    // no split may end up with an empty K range (its accumulator would never be written)
+    const int per = (p.kb_total + splits - 1) / splits;
+    splits = (p.kb_total + per - 1) / per;
+  }
   p.splits = splits;
   p.scales = scales;
   p.scale_ld = (K + 127) / 128;

@@ -102,6 +102,10 @@ def linear(x: torch.Tensor, w: PackedLinear, residual: torch.Tensor | None = Non
                               None, _lib.ptr(residual), t, n, k, 1, _lib.ptr(st), _lib.stream())
         _lib.check(rc, "gemm_wdec")
         return out
+    kb = (k + 63) // 64
+    splits = min(splits, kb)
+    per = (kb + splits - 1) // splits
+    splits = (kb + per - 1) // per          # same rule as the launcher: no empty split
     ws = _workspace(splits * t * n, x.device)
     rc = L.b200_gemm_wdec(w.wfmt, _lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(x), None, _lib.ptr(ws),
                           None, t, n, k, splits, _lib.ptr(st), _lib.stream())
