@@ -470,3 +470,58 @@ extern "C" int b200_splitk_reduce(const float* part, int splits, long long n, co
       reinterpret_cast<__nv_bfloat16*>(out_bf16));
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free split-K entry point (contract in no_alloc.h).
+// The scratch is a device array inside this translation unit.  In host code the
+// name `g_noalloc_scratch` is only a handle; the address a kernel can use comes
+// from cudaGetSymbolAddress, looked up once per device with that device current.
+#include "no_alloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[B200_NOALLOC_MAX_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" long long b200_gemm_wdec_noalloc_max_floats(void) { return B200_NOALLOC_MAX_FLOATS; }
+
+extern "C" int b200_gemm_wdec_splitk_noalloc(int wfmt, const void* W, const float* scales, const void* X,
+                                             void* out_bf16, const void* residual, int T, int N, int K,
+                                             int splits, int* status, cudaStream_t stream) {
+  if (T <= 0 || N <= 0 || K <= 0 || splits < 1 || !out_bf16) return -ERR_BAD_ARG;
+  // same split normalisation as b200_gemm_wdec, done here so the size check sees the real count
+  const int kb_total = (K + BK - 1) / BK;
+  if (splits > kb_total) splits = kb_total;
+  const int per = (kb_total + splits - 1) / splits;
+  splits = (kb_total + per - 1) / per;
+  const long long need = (long long)splits * T * N;
+  if (need > B200_NOALLOC_MAX_FLOATS) {
+    fprintf(stderr,
+            "[b200] gemm_wdec_splitk_noalloc: splits*T*N = %d*%d*%d = %lld floats exceeds the built-in scratch "
+            "of %lld floats; use fewer splits or the workspace entry point b200_gemm_wdec\n",
+            splits, T, N, need, (long long)B200_NOALLOC_MAX_FLOATS);
+    return B200_ERR_SCRATCH_TOO_SMALL;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return -ERR_BAD_ARG;
+  if (!g_noalloc_ptr[dev]) {
+    // first call on this device: resolve the array's device address (device `dev` is current)
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (!ptr) return -ERR_BAD_ARG;
+    g_noalloc_ptr[dev] = ptr;
+  }
+  float* scratch = g_noalloc_ptr[dev];
+  if (splits == 1) {
+    // nothing to reduce: the plain epilogue writes bf16 (+ residual) directly
+    return b200_gemm_wdec(wfmt, W, scales, X, out_bf16, nullptr, residual, T, N, K, 1, status, stream);
+  }
+  int rc = b200_gemm_wdec(wfmt, W, scales, X, nullptr, scratch, nullptr, T, N, K, splits, status, stream);
+  if (rc != 0) return rc;
+  return b200_splitk_reduce(scratch, splits, (long long)T * N, residual, out_bf16, stream);
+}
