@@ -43,6 +43,7 @@ enum WFormat : int { WF_BF16 = 0, WF_FP8_B128 = 1 };
 struct GemmParams {
   int T, N, K;
   int m_tiles, n_tiles, splits, kb_total;
+  const uint8_t* w_tiled;  // FP8 only: [m_tiles][kb_total][128 rows][64 bytes], bytes pre-shuffled
   const float* scales;  // [ceil(N/128), scale_ld] fp32 (FP8 only)
   int scale_ld;
   __nv_bfloat16* out;        // [T, ldo] (splits == 1)
@@ -158,8 +159,10 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             mbar_expect_tx(&tma_full[s], L::A_BYTES + L::X_BYTES);
             tma_load_2d(sA + s * L::A_BYTES, &tmW, &tma_full[s], kb * BK, m_tile * BM);
           } else {
+            // FP8 weights are stored tile-major: one contiguous 8 KB block per (m_tile, kb)
             mbar_expect_tx(&tma_full[s], L::RAW_BYTES + L::X_BYTES);
-            tma_load_2d(sRaw + s * L::RAW_BYTES, &tmW, &tma_full[s], kb * BK, m_tile * BM);
+            bulk_load(sRaw + s * L::RAW_BYTES,
+                      p.w_tiled + ((size_t)m_tile * p.kb_total + kb) * L::RAW_BYTES, L::RAW_BYTES, &tma_full[s]);
           }
           tma_load_2d(sX + s * L::X_BYTES, &tmX, &tma_full[s], kb * BK, n_tile * BN);
         }
@@ -234,12 +237,27 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         const int kb0 = split * kb_per_split;
         const int kb1 = min(p.kb_total, kb0 + kb_per_split);
         const float* srow = p.scales + (size_t)m_tile * p.scale_ld;
+        // Block scales of this tile's K range, fetched once per tile and spread over the lanes
+        // (lane l holds entries l, l+32, ...): a per-stage global load would put an L2 round trip
+        // on the critical path of every stage.
+        const int sc_lo = kb0 >> 1;
+        const int nsc = (kb1 > kb0) ? (((kb1 - 1) >> 1) - sc_lo + 1) : 0;
+        float my_sc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int idx = j * 32 + lane;
+          my_sc[j] = (idx < nsc) ? __ldg(srow + sc_lo + idx) * 0x1p120f : 0.f;
+        }
         bool failed = false;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           if ((int)(it % G) != grp) continue;
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          const float sc = __ldg(srow + (kb >> 1)) * 0x1p120f;
+          const int si = (kb >> 1) - sc_lo;
+          float scv = my_sc[0];
+#pragma unroll
+          for (int j = 1; j < 8; ++j) scv = (si >> 5) == j ? my_sc[j] : scv;
+          const float sc = __shfl_sync(0xffffffffu, scv, si & 31);
           bool ok = mbar_wait(&tma_full[s], ph);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) {
@@ -403,9 +421,9 @@ extern "C" int b200_gemm_pick_bn(int T) {
   return 256;
 }
 
-// wfmt: 0 = bf16 weights [N, K]; 1 = FP8 E4M3 weights [N, K] (bytes stored in
-// the (w0,w2,w1,w3) order produced by b200_prepack_fp8) with fp32 scales
-// [ceil(N/128), ceil(K/128)].
+// wfmt: 0 = bf16 weights [N, K]; 1 = FP8 E4M3 weights in the tile-major layout
+// [ceil(N/128)][ceil(K/64)][128 rows][64 bytes] (zero padded; each 4-byte group stored as
+// (w0,w2,w1,w3)) with fp32 scales [ceil(N/128), ceil(K/128)].
 // splits == 1: writes bf16 `out` (adds `residual` when given), or fp32 `out_f32` when out == null.
 // splits  > 1: writes fp32 partials to out_f32 [splits, T, N] (caller reduces).
 extern "C" int b200_gemm_wdec(int wfmt, const void* W, const float* scales, const void* X,
@@ -433,17 +451,23 @@ extern "C" int b200_gemm_wdec(int wfmt, const void* W, const float* scales, cons
   p.ldo = N;
   p.status = status;
   if ((splits > 1 || !out_bf16) && !out_f32) return -ERR_BAD_ARG;
+  if (wfmt != WF_BF16) {
+    // the decode warps keep at most 256 block scales (K range of 32768) per tile in registers
+    const int per = (p.kb_total + splits - 1) / splits;
+    if (per / 2 + 2 > 256) return -ERR_BAD_ARG;
+  }
 
   CUtensorMap tmW, tmX;
-  bool ok;
-  if (wfmt == WF_BF16)
-    ok = make_tmap_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, N, K, (uint64_t)K * 2, BM, BK,
-                      CU_TENSOR_MAP_SWIZZLE_128B);
-  else
-    ok = make_tmap_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, N, K, (uint64_t)K, BM, BK,
-                      CU_TENSOR_MAP_SWIZZLE_NONE);
-  ok = ok && make_tmap_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, T, K, (uint64_t)K * 2, BN, BK,
-                          CU_TENSOR_MAP_SWIZZLE_128B);
+  bool ok = make_tmap_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, T, K, (uint64_t)K * 2, BN, BK,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
+  p.w_tiled = nullptr;
+  if (wfmt == WF_BF16) {
+    ok = ok && make_tmap_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, N, K, (uint64_t)K * 2, BM, BK,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    p.w_tiled = reinterpret_cast<const uint8_t*>(W);   // fetched with untiled bulk copies, no tensor map
+    tmW = tmX;
+  }
   if (!ok) return -ERR_BAD_ARG;
 
 #define B200_DISPATCH(BN_)                                                       \

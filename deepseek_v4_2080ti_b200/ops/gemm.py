@@ -20,15 +20,24 @@ NUM_SMS = 148
 
 
 def prepack_fp8(w: torch.Tensor) -> torch.Tensor:
-    """Reorder every 4 consecutive fp8 bytes (w0,w1,w2,w3) -> (w0,w2,w1,w3).
+    """FP8 weight [N, K] -> the kernel's tile-major layout [ceil(N/128), ceil(K/64), 128, 64] (uint8).
 
-    The decode warps turn one 32-bit word into two bf16x2 words with shifts and masks only;
-    this byte order makes those words come out as (w0,w1) and (w2,w3).
+    Two transformations, both done once at load time:
+    * every 4 consecutive bytes (w0,w1,w2,w3) are stored as (w0,w2,w1,w3): the decode warps turn one
+      32-bit word into two bf16x2 words with shifts and masks only, and this order makes those words
+      come out as (w0,w1) and (w2,w3);
+    * each [128 rows x 64 bytes] pipeline-stage tile is contiguous (8 KB), so a stage is fetched with a
+      single bulk copy instead of 128 separate 64-byte rows.
     """
     u = w.view(torch.uint8)
     n, k = u.shape
-    assert k % 4 == 0
-    return u.view(n, k // 4, 4)[:, :, [0, 2, 1, 3]].contiguous().view(n, k)
+    npad, kpad = (n + 127) // 128 * 128, (k + 63) // 64 * 64
+    if (npad, kpad) != (n, k):
+        full = torch.zeros(npad, kpad, dtype=torch.uint8, device=u.device)
+        full[:n, :k] = u
+        u = full
+    u = u.view(npad, kpad // 4, 4)[:, :, [0, 2, 1, 3]].reshape(npad // 128, 128, kpad // 64, 64)
+    return u.permute(0, 2, 1, 3).contiguous()
 
 
 @dataclass
