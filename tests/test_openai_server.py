@@ -1,0 +1,103 @@
+"""OpenAI-compatible server against a fake backend: routes, SSE, error mapping, metrics, cancel."""
+import http.client
+import json
+import threading
+
+import pytest
+
+from pocketllm import EngineArgs
+from pocketllm.backends.native_backend import NativeBackend
+from pocketllm.server.metrics import Metrics
+from pocketllm.server.openai import error_status, make_server
+from tests.test_public_api import FakeRuntime
+
+
+@pytest.fixture()
+def server():
+    backend = NativeBackend(EngineArgs(model="fake"), runtime=FakeRuntime())
+    httpd, state = make_server(backend, "127.0.0.1", 0, "fake-model")
+    t = threading.Thread(target=httpd.serve_forever, kwargs={"poll_interval": 0.05}, daemon=True)
+    t.start()
+    yield httpd.server_address[1], state
+    httpd.shutdown()
+    httpd.server_close()
+
+
+def call(port, method, path, body=None):
+    c = http.client.HTTPConnection("127.0.0.1", port, timeout=10)
+    data = None if body is None else json.dumps(body)
+    c.request(method, path, body=data, headers={"Content-Type": "application/json"} if data else {})
+    r = c.getresponse()
+    raw = r.read()
+    c.close()
+    return r.status, raw
+
+
+def test_health_models_metrics(server):
+    port, _ = server
+    st, raw = call(port, "GET", "/health")
+    assert st == 200 and json.loads(raw)["ready"] is True
+    assert call(port, "GET", "/ready")[0] == 200 and call(port, "GET", "/alive")[0] == 200
+    st, raw = call(port, "GET", "/v1/models")
+    assert json.loads(raw)["data"][0]["id"] == "fake-model"
+    assert call(port, "GET", "/nope")[0] == 404
+    st, raw = call(port, "GET", "/metrics")
+    assert st == 200 and b"pocketllm_requests_in_flight" in raw
+
+
+def test_completion_and_chat(server):
+    port, _ = server
+    st, raw = call(port, "POST", "/v1/completions", {"prompt": "A", "max_tokens": 3})
+    body = json.loads(raw)
+    assert st == 200 and body["choices"][0]["text"] == "BCD" and body["usage"]["completion_tokens"] == 3
+    assert "prefill_tps" in body["timings"]
+    st, raw = call(port, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "max_tokens": 2})
+    body = json.loads(raw)
+    assert st == 200 and body["object"] == "chat.completion" and body["choices"][0]["message"]["role"] == "assistant"
+    st, raw = call(port, "GET", "/metrics")
+    assert b'pocketllm_requests_total{route="/v1/completions"} 1' in raw
+
+
+def test_error_mapping(server):
+    port, _ = server
+    assert call(port, "POST", "/v1/completions", {"prompt": ""})[0] == 400
+    assert call(port, "POST", "/v1/completions", {"prompt": "A", "temperature": 0.9})[0] == 501
+    st, raw = call(port, "POST", "/v1/chat/completions", {"messages": []})
+    assert st == 400 and json.loads(raw)["error"]["type"] == "invalid_request_error"
+    c = http.client.HTTPConnection("127.0.0.1", port, timeout=10)
+    c.request("POST", "/v1/completions", body="{not json", headers={"Content-Type": "application/json"})
+    assert c.getresponse().status == 400
+    from pocketllm import BackendUnavailableError, RequestCancelledError
+    assert error_status(BackendUnavailableError("x")) == 503 and error_status(RequestCancelledError("x")) == 499
+    assert error_status(RuntimeError("x")) == 500
+
+
+def test_sse_stream(server):
+    port, _ = server
+    st, raw = call(port, "POST", "/v1/chat/completions",
+                   {"messages": [{"role": "user", "content": "x"}], "max_tokens": 3, "stream": True})
+    assert st == 200
+    events = [l[6:] for l in raw.decode().split("\n\n") if l.startswith("data: ")]
+    assert events[-1] == "[DONE]"
+    chunks = [json.loads(e) for e in events[:-1]]
+    assert chunks[0]["choices"][0]["delta"]["role"] == "assistant"
+    text = "".join(c["choices"][0]["delta"].get("content", "") for c in chunks)
+    assert len(text) == 3
+    assert chunks[-1]["choices"][0]["finish_reason"] == "length" and chunks[-1]["usage"]["completion_tokens"] == 3
+
+
+def test_cancel_unknown_request_and_options(server):
+    port, _ = server
+    st, raw = call(port, "DELETE", "/v1/requests/nope")
+    assert st == 404 and json.loads(raw)["cancelled"] is False
+    assert call(port, "OPTIONS", "/v1/chat/completions")[0] == 204
+
+
+def test_metrics_registry_quantiles():
+    m = Metrics()
+    for v in range(1, 101):
+        m.observe("lat", float(v))
+    m.inc("n", labels={"a": 'x"y'})
+    text = m.render()
+    assert 'pocketllm_lat{quantile="0.5"} 50.5' in text and "pocketllm_lat_count 100" in text
+    assert 'a="x\\"y"' in text

@@ -1,0 +1,231 @@
+"""Typed API, protocol normalisation and backend contract with a fake runtime (no GPU, no torch import)."""
+import json
+import sys
+
+import pytest
+
+import pocketllm
+from pocketllm import (ConfigurationError, EngineArgs, GenerationRequest, SamplingParams, TimingMetrics,
+                       UnsupportedFeatureError, Usage)
+from pocketllm.backends.native_backend import NativeBackend
+from pocketllm.protocol import chat as chatmod
+from pocketllm.protocol.prompt import TokenizerHandle
+from pocketllm.protocol.requests import build_chat_request, build_completion_request
+
+
+class FakeRuntime:
+    """Echo model: next token = (last token + 1) % 250; records every call in order."""
+    eos_token_ids = (249,)
+    max_context = 64
+    supports_sampling = False
+
+    def __init__(self):
+        self.calls = []
+        self.slots = set()
+        self.last = {}
+
+    def allocate(self):
+        s = len(self.calls)
+        self.slots.add(s)
+        self.calls.append(("allocate", s))
+        return s
+
+    def free(self, slot):
+        self.slots.discard(slot)
+        self.calls.append(("free", slot))
+
+    def prefill_tokens(self, slot, prompt, chunk, sp):
+        self.calls.append(("prefill", slot, len(prompt), chunk))
+        self.last[slot] = (prompt[-1] + 1) % 250
+        return self.last[slot]
+
+    def decode_tokens(self, slots, toks, sp):
+        self.calls.append(("decode", tuple(slots), tuple(toks)))
+        out = []
+        for s, t in zip(slots, toks):
+            self.last[s] = (t + 1) % 250
+            out.append(self.last[s])
+        return out
+
+
+def make_backend(**kw):
+    rt = FakeRuntime()
+    return NativeBackend(EngineArgs(model="fake", **kw), runtime=rt), rt
+
+
+def test_import_does_not_pull_torch():
+    import subprocess
+    code = "import sys, pocketllm; from pocketllm import EngineArgs, SamplingParams; assert 'torch' not in sys.modules"
+    assert subprocess.run([sys.executable, "-c", code], cwd=".").returncode == 0
+
+
+def test_engine_args_validation():
+    with pytest.raises(ConfigurationError):
+        EngineArgs(model="m", backend="nope")
+    with pytest.raises(ConfigurationError):
+        EngineArgs(model="m", tensor_parallel_size=2, tensor_parallel_rank=2)
+    with pytest.raises(ConfigurationError):
+        EngineArgs(model="m", kv_cache_dtype="fp3")
+    assert EngineArgs(model="m", backend="CPP").backend == "cpp"
+
+
+def test_engine_args_from_env(monkeypatch):
+    monkeypatch.setenv("POCKETLLM_CHECKPOINT", "/ckpt")
+    monkeypatch.setenv("POCKETLLM_TP_SIZE", "4")
+    monkeypatch.setenv("TP_RANK", "3")
+    monkeypatch.setenv("POCKETLLM_BACKEND_OPTIONS", json.dumps({"pd_mode": "serial"}))
+    a = EngineArgs.from_env()
+    assert (a.model, a.tensor_parallel_size, a.tensor_parallel_rank, a.backend_options) == ("/ckpt", 4, 3, {"pd_mode": "serial"})
+    monkeypatch.setenv("POCKETLLM_TP_SIZE", "x")
+    with pytest.raises(ConfigurationError):
+        EngineArgs.from_env()
+
+
+def test_sampling_params():
+    sp = SamplingParams.from_openai({"max_completion_tokens": 7, "temperature": 0, "stop": "END"})
+    assert sp.greedy and sp.max_tokens == 7 and sp.stop == ("END",)
+    assert not SamplingParams(temperature=0.8).greedy
+    for bad in ({"top_p": 0}, {"temperature": -1}, {"n": 2}, {"max_tokens": 0}, {"top_logprobs": 99}):
+        with pytest.raises(ConfigurationError):
+            SamplingParams.from_openai(bad)
+    with pytest.raises(ConfigurationError):
+        SamplingParams(stop=[str(i) for i in range(17)])
+
+
+def test_timing_convention_first_token_counts_as_prefill():
+    tm = TimingMetrics(prefill_seconds=2.0, decode_seconds=1.0)
+    tp = tm.throughput(Usage(prompt_tokens=100, completion_tokens=11))
+    assert tp["prefill_tps"] == 50.0 and tp["decode_tps"] == 10.0
+
+
+def test_request_validation():
+    with pytest.raises(ConfigurationError):
+        GenerationRequest()
+    with pytest.raises(ConfigurationError):
+        GenerationRequest(prompt_tokens=[])
+    with pytest.raises(ConfigurationError):
+        GenerationRequest(prompt_tokens=[1, -2])
+    assert GenerationRequest(prompt_tokens=(1, 2)).prompt_tokens == [1, 2]
+
+
+def test_chat_normalisation():
+    body = {"messages": [{"role": "developer", "content": [{"type": "text", "text": "be "}, {"type": "text", "text": "brief"}]},
+                         {"role": "user", "content": "hi"}],
+            "tools": [{"type": "function", "function": {"name": "get", "parameters": {"type": "object"}}}],
+            "tool_choice": {"type": "function", "function": {"name": "get"}}, "reasoning_effort": "high", "stream": True}
+    c = chatmod.ChatRequest.from_body(body)
+    assert c.messages[0] == {"role": "system", "content": "be brief"}
+    assert c.thinking and c.reasoning_effort == "high" and c.stream
+    assert "get" in c.tool_instruction
+    assert c.messages_with_instruction()[0]["content"].endswith("get.")
+    with pytest.raises(ConfigurationError):
+        chatmod.ChatRequest.from_body({"messages": [{"role": "robot", "content": "x"}]})
+    with pytest.raises(ConfigurationError):
+        chatmod.ChatRequest.from_body({"messages": [{"role": "user", "content": [{"type": "image_url"}]}]})
+    with pytest.raises(ConfigurationError):
+        chatmod.ChatRequest.from_body({"messages": [{"role": "user", "content": "x"}], "tools": [{"function": {"name": "a"}}],
+                                       "tool_choice": {"function": {"name": "b"}}})
+
+
+def test_stop_reasoning_and_tool_extraction():
+    assert chatmod.truncate_at_stop("abcENDdef", ["zzz", "END"]) == ("abc", True)
+    assert chatmod.held_back_suffix("hello EN", ["END"]) == 2
+    assert chatmod.split_reasoning("<think>plan</think>answer") == ("plan", "answer")
+    assert chatmod.split_reasoning("plan</think> answer") == ("plan", "answer")
+    rest, calls = chatmod.extract_tool_calls('ok <tool_call>{"name": "get", "arguments": {"x": 1}}</tool_call>')
+    assert rest == "ok" and calls[0]["function"]["name"] == "get" and json.loads(calls[0]["function"]["arguments"]) == {"x": 1}
+
+
+def test_request_builders_with_byte_tokenizer():
+    tok = TokenizerHandle(None, "bytes")
+    req, chat = build_chat_request({"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3}, tok)
+    assert tok.decode(req.prompt_tokens).endswith("<|assistant|>\n") and req.sampling_params.max_tokens == 3
+    r2 = build_completion_request({"prompt": [1, 2, 3]}, tok)
+    assert r2.prompt_tokens == [1, 2, 3]
+    with pytest.raises(ConfigurationError):
+        build_completion_request({"prompt": ""}, tok)
+
+
+def test_backend_generate_order_and_eos():
+    b, rt = make_backend()
+    res = b.generate([GenerationRequest(prompt_tokens=[10, 245], sampling_params=SamplingParams(max_tokens=10))])[0]
+    # 246 247 248 then 249 == eos -> stop, eos not returned
+    assert res.token_ids == [246, 247, 248] and res.finish_reason == "stop"
+    assert res.usage.prompt_tokens == 2 and res.usage.completion_tokens == 3
+    kinds = [c[0] for c in rt.calls]
+    assert kinds == ["allocate", "prefill", "decode", "decode", "decode", "free"]
+    assert not rt.slots
+
+
+def test_backend_length_stop_strings_and_context_clamp():
+    b, rt = make_backend()
+    r = b.generate([GenerationRequest(prompt_tokens=[64], sampling_params=SamplingParams(max_tokens=4))])[0]
+    assert r.token_ids == [65, 66, 67, 68] and r.finish_reason == "length" and r.text == "ABCD"
+    r = b.generate([GenerationRequest(prompt_tokens=[64], sampling_params=SamplingParams(max_tokens=20, stop=("CD",)))])[0]
+    assert r.text == "AB" and r.finish_reason == "stop"
+    long_prompt = list(range(60))
+    r = b.generate([GenerationRequest(prompt_tokens=long_prompt, sampling_params=SamplingParams(max_tokens=50))])[0]
+    assert len(r.token_ids) == 4           # clamped by max_context 64
+    with pytest.raises(ConfigurationError):
+        b.generate([GenerationRequest(prompt_tokens=list(range(64)))])
+
+
+def test_backend_rejects_unsupported_features():
+    b, _ = make_backend()
+    with pytest.raises(UnsupportedFeatureError):
+        b.generate([GenerationRequest(prompt_tokens=[1], sampling_params=SamplingParams(temperature=0.7))])
+    with pytest.raises(UnsupportedFeatureError):
+        b.generate([GenerationRequest(prompt_tokens=[1], sampling_params=SamplingParams(logprobs=True))])
+
+
+def test_stream_events_and_llm_facade():
+    b, _ = make_backend()
+    llm = pocketllm.LLM(backend=b)
+    evs = list(llm.generate_stream([72], SamplingParams(max_tokens=3)))
+    assert "".join(e.text for e in evs) == "IJK"
+    assert evs[-1].finish_reason == "length" and evs[-1].usage.completion_tokens == 3
+    out = llm.generate(["A", "B"], SamplingParams(max_tokens=1))
+    assert [o.text for o in out] == ["B", "C"]
+    assert llm.health().ready
+    llm.close()
+    assert llm.health().status == "closed"
+
+
+def test_tp_fanout_order_matches_local_calls():
+    """Rank 0 must send each command to the workers before running it locally."""
+    log = []
+
+    class Chan:
+        world = 2
+
+        def send(self, op, *payload):
+            log.append(("send", op))
+
+    rt = FakeRuntime()
+    orig_prefill, orig_decode = rt.prefill_tokens, rt.decode_tokens
+    rt.prefill_tokens = lambda *a: (log.append(("local", 3)), orig_prefill(*a))[1]
+    rt.decode_tokens = lambda *a: (log.append(("local", 4)), orig_decode(*a))[1]
+    b = NativeBackend(EngineArgs(model="fake", tensor_parallel_size=2), runtime=rt, channel=Chan())
+    b.generate([GenerationRequest(prompt_tokens=[5], sampling_params=SamplingParams(max_tokens=3))])
+    ops = [x for x in log if x[1] in (3, 4)]
+    assert ops == [("send", 3), ("local", 3), ("send", 4), ("local", 4), ("send", 4), ("local", 4)]
+
+
+def test_worker_loop_mirrors_commands_and_survives_errors():
+    from pocketllm.backends.native_backend import OP_ALLOC, OP_DECODE, OP_FREE, OP_PREFILL, OP_STOP
+
+    class Chan:
+        world = 2
+
+        def __init__(self, msgs):
+            self.msgs = list(msgs)
+
+        def recv(self):
+            return self.msgs.pop(0)
+
+    rt = FakeRuntime()
+    msgs = [(OP_ALLOC,), (OP_PREFILL, 0, 8192, [1, 2]), (OP_DECODE, 0, 3), (OP_DECODE, 99, "bad"), (OP_FREE, 0), (OP_STOP,)]
+    b = NativeBackend(EngineArgs(model="fake", tensor_parallel_size=2, tensor_parallel_rank=1), runtime=rt, channel=Chan(msgs))
+    b.run_worker()
+    assert [c[0] for c in rt.calls] == ["allocate", "prefill", "decode", "decode", "free"] or \
+        [c[0] for c in rt.calls] == ["allocate", "prefill", "decode", "free"]
