@@ -1,0 +1,146 @@
+"""Build a model runtime from ``EngineArgs``: pick the model family from the checkpoint, shard it
+for this rank, open the rank-0 -> workers command channel.
+
+Model strings:
+  ``synthetic:qwen-tiny`` / ``synthetic:qwen-27b``  random-init models generated on the device
+  a directory with ``config.json`` + safetensors      Qwen-style hybrid FP8 checkpoints
+  a ``.gguf`` file or bundle                          MoE families (routed by ``general.architecture``)
+"""
+from __future__ import annotations
+
+import os
+from typing import Any
+
+import torch
+
+from ..models import qwen_hybrid as qh
+from ..parallel import tp
+
+
+class Channel:
+    """Rank 0 -> workers command fan-out over the C++ ``CmdChannel`` (unix socket, int32 words)."""
+
+    def __init__(self, base_path: str, rank: int, world: int, timeout_ms: int = 600000):
+        from .. import pocketllm_cpp as cpp
+        self.world, self.rank = world, rank
+        self._ch = cpp.CmdChannel()
+        if not self._ch.open(base_path, rank, world, timeout_ms, 50):
+            raise RuntimeError(f"command channel could not be opened at {base_path}.cmdsock (rank {rank}/{world})")
+
+    def send(self, op: int, *payload) -> None:
+        words = [int(op)]
+        for p in payload:
+            if isinstance(p, (list, tuple)):
+                words.append(len(p))
+                words.extend(int(x) for x in p)
+            else:
+                words.append(int(p))
+        if not self._ch.broadcast(words):
+            raise RuntimeError("a worker rank closed its command channel")
+
+    def recv(self):
+        w = self._ch.receive(-1)
+        if w is None:
+            return (0,)                          # rank 0 went away: stop
+        op = w[0]
+        if op == 3:                              # prefill: slot, chunk, n, tokens...
+            return (op, w[1], w[2], list(w[4:4 + w[3]]))
+        return tuple(w)
+
+
+class RuntimeAdapter:
+    """The surface ``NativeBackend`` drives, over a ``QwenHybridRuntime``."""
+    supports_sampling = False
+    supports_prefix_cache = False
+    speculative_methods: tuple[str, ...] = ()
+
+    def __init__(self, rt: qh.QwenHybridRuntime, max_context: int, eos_token_ids=()):
+        self.rt, self.max_context, self.eos_token_ids = rt, max_context, tuple(eos_token_ids)
+        self.last_cached_tokens = 0
+
+    def allocate(self) -> int:
+        return self.rt.allocate()
+
+    def free(self, slot: int) -> None:
+        self.rt.free(slot)
+
+    def prefill_tokens(self, slot: int, prompt: list[int], chunk: int, sp: Any) -> int:
+        ids = torch.tensor(prompt, dtype=torch.int32).pin_memory().to(self.rt.device, non_blocking=True)
+        return int(self.rt.prefill(slot, ids, chunk).item())
+
+    def decode_tokens(self, slots: list[int], toks: list[int], sp: Any) -> list[int]:
+        t = torch.tensor(toks, dtype=torch.int32, device=self.rt.device)
+        return [int(x) for x in self.rt.decode(slots, t).tolist()]
+
+    def generate_batch(self, prompts, max_new, eos_ids, max_batch):
+        """Greedy continuous batching: admit up to ``max_batch`` sequences, decode them together."""
+        import time
+        results: list[Any] = [None] * len(prompts)
+        pending = list(range(len(prompts)))[::-1]
+        active: dict[int, dict] = {}
+        while pending or active:
+            while pending and len(active) < min(max_batch, self.rt.max_slots):
+                i = pending.pop()
+                t0 = time.perf_counter()
+                slot = self.rt.allocate()
+                first = self.prefill_tokens(slot, prompts[i], 8192, None)
+                active[i] = {"slot": slot, "out": [first], "t0": t0, "t1": time.perf_counter()}
+            done = [i for i, a in active.items() if a["out"][-1] in eos_ids or len(a["out"]) >= max_new[i]]
+            for i in done:
+                a = active.pop(i)
+                self.rt.free(a["slot"])
+                eos = a["out"][-1] in eos_ids
+                ids = a["out"][:-1] if eos else a["out"]
+                now = time.perf_counter()
+                results[i] = (ids, "stop" if eos else "length",
+                              {"prefill_seconds": a["t1"] - a["t0"], "decode_seconds": now - a["t1"],
+                               "total_seconds": now - a["t0"], "ttft_seconds": a["t1"] - a["t0"]})
+            if active:
+                order = list(active)
+                nxt = self.decode_tokens([active[i]["slot"] for i in order], [active[i]["out"][-1] for i in order], None)
+                for i, t in zip(order, nxt):
+                    active[i]["out"].append(t)
+        return results
+
+    def stats(self) -> dict:
+        return {"kv_blocks_free": len(self.rt.free_blocks), "kv_blocks_total": self.rt.num_blocks - 1,
+                "slots_free": len(self.rt.free_slots)}
+
+
+def _device(args) -> torch.device:
+    if args.device is not None:
+        return torch.device(args.device if isinstance(args.device, str) else f"cuda:{args.device}")
+    return torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+
+
+def load_runtime(args):
+    """Returns (adapter, chat-template family or None, command channel)."""
+    world, rank = args.tensor_parallel_size, args.tensor_parallel_rank
+    dev = _device(args)
+    torch.cuda.set_device(dev)
+    comm = None
+    channel = None
+    if world > 1:
+        os.environ.setdefault("RANK", str(rank))
+        os.environ.setdefault("WORLD_SIZE", str(world))
+        os.environ.setdefault("LOCAL_RANK", str(dev.index or 0))
+        tp.init_distributed("nccl")
+        comm = tp.TPComm()
+        base = os.environ.get("POCKETLLM_NCCL_ID_PATH") or f"/tmp/pocketllm-{os.environ.get('MASTER_PORT', '0')}"
+        channel = Channel(base, rank, world)
+    model = args.model
+    max_ctx = args.max_model_len or 8192 + 512
+    slots = max(1, args.max_batch_size)
+    if model.startswith("synthetic:"):
+        name = model.split(":", 1)[1]
+        cfg = qh.QwenHybridConfig.tiny() if name in ("qwen-tiny", "tiny") else qh.QwenHybridConfig.config2()
+        state = qh.synth_state(cfg, 0, dev, std=0.05 if "tiny" in name else 0.02)
+    else:
+        cfg_path = args.config_path or os.path.join(args.checkpoint_dir, "config.json")
+        cfg = qh.QwenHybridConfig.from_json(cfg_path)
+        from ..formats import safetensors_io
+        state = safetensors_io.read_checkpoint(args.checkpoint_dir)
+    weights = qh.QwenHybridWeights(cfg, state, dev, rank, world)
+    rt = qh.QwenHybridRuntime(cfg, weights, max_slots=slots, max_context=max_ctx, comm=comm)
+    from pocketllm.backends.native_backend import NullChannel
+    return RuntimeAdapter(rt, max_ctx), None, channel or NullChannel()
