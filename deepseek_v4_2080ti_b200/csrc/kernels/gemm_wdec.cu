@@ -23,9 +23,11 @@
 // (cpp_engine/backends/cuda/kernels/bf16_ops.cu:30-167).
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
+#include <string.h>
 #include "../ptx/sm100.cuh"
 #include "tma_host.h"
 #include "ops.h"
+#include "../comm/comm.h"
 
 namespace b200 {
 
@@ -51,6 +53,11 @@ struct GemmParams {
   const __nv_bfloat16* residual;  // optional [T, ldo], added in the epilogue (splits == 1)
   int ldo;
   int* status;
+  // Fused all-reduce (row-parallel GEMM under tensor parallelism): when ar_mode == 1 the epilogue
+  // pushes this rank's partial tile to every peer, waits for theirs and stores the sum.
+  int ar_mode;
+  unsigned long long ar_budget_ns;
+  B200Comm comm;
 };
 
 template <int BN>
@@ -132,6 +139,7 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const uint32_t ar_epoch_at_entry = p.ar_mode ? p.comm.ctrl[0] + 1 : 0;
 
   const int total_work = p.m_tiles * p.n_tiles * p.splits;
   const int kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
@@ -307,6 +315,7 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     // ---------------------------------------------------------------- epilogue
     uint32_t tile_i = 0;
     const int row_in_tile = warp * 32 + lane;  // TMEM lane == output feature within the tile
+    const uint32_t ar_epoch = p.ar_mode ? p.comm.ctrl[0] + 1 : 0;   // read before any CTA can finish
     for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x, ++tile_i) {
       const int m_tile = w % p.m_tiles;
       const int rest = w / p.m_tiles;
@@ -326,6 +335,90 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       const bool f_ok = f < p.N;
       const uint32_t taddr = tmem_base + (uint32_t(warp * 32) << 16) + buf * BN;
       constexpr int CH = BN >= 32 ? 32 : 16;
+      if (p.ar_mode == 1) {
+        // ---- fused one-shot all-reduce over peer memory -------------------------------------
+        const B200Comm& cm = p.comm;
+        const int parity = ar_epoch & 1;
+        const size_t slot = ((size_t)parity * B200_MAX_RANKS + cm.rank) * cm.slot_elems;
+        // pass 1: push my partial tile (bf16 on the wire) into every peer's slot for source = me
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          uint32_t v[32];
+          if (CH == 32) {
+            tmem_ld_32x32(taddr + c0, v);
+          } else {
+            uint32_t v16[16];
+            tmem_ld_32x16(taddr + c0, v16);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = v16[j];
+          }
+          tmem_ld_wait();
+          const int t0 = n_tile * BN + c0;
+          if (f_ok) {
+            for (int r = 0; r < cm.world; ++r) {
+              if (r == cm.rank) continue;
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cm.data[r]) + slot + (size_t)t0 * p.ldo + f;
+#pragma unroll
+              for (int j = 0; j < CH; ++j)
+                if (t0 + j < p.T) dst[(size_t)j * p.ldo] = __float2bfloat16(__uint_as_float(v[j]));
+            }
+          }
+        }
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        // one thread per peer: raise my flag for this tile there, then wait for the peer's flag here
+        const int et = threadIdx.x;  // 0..127 inside the epilogue group
+        if (et < cm.world && et != cm.rank) {
+          uint32_t* theirs = cm.flags[et] + ((size_t)parity * B200_MAX_RANKS + cm.rank) * B200_FLAGS_PER_SLOT + w;
+          const uint32_t* mine = cm.flags[cm.rank] + ((size_t)parity * B200_MAX_RANKS + et) * B200_FLAGS_PER_SLOT + w;
+          st_release_sys(theirs, ar_epoch);
+          if (!wait_flag_ge(mine, ar_epoch, p.ar_budget_ns)) {
+            atomicExch(p.status, ERR_WAIT_PEER);
+            *abort_flag = 1;
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*abort_flag) break;
+        // pass 2: own fp32 accumulator + peers' bf16 partials (fixed rank order) (+ residual) -> out
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          uint32_t v[32];
+          if (CH == 32) {
+            tmem_ld_32x32(taddr + c0, v);
+          } else {
+            uint32_t v16[16];
+            tmem_ld_32x16(taddr + c0, v16);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = v16[j];
+          }
+          tmem_ld_wait();
+          const int t0 = n_tile * BN + c0;
+          if (f_ok) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              if (t0 + j < p.T) {
+                const size_t off = (size_t)(t0 + j) * p.ldo + f;
+                float acc = 0.f;
+                for (int r = 0; r < cm.world; ++r) {
+                  if (r == cm.rank) {
+                    // round my own part the way the peers see it, so every rank computes the same sum
+                    acc += __bfloat162float(__float2bfloat16(__uint_as_float(v[j])));
+                  } else {
+                    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(cm.data[cm.rank]) +
+                                               ((size_t)parity * B200_MAX_RANKS + r) * cm.slot_elems + off;
+                    acc += __bfloat162float(*src);
+                  }
+                }
+                if (p.residual) acc += __bfloat162float(p.residual[off]);
+                p.out[off] = __float2bfloat16(acc);
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&acc_empty[buf]);
+        continue;
+      }
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += CH) {
         uint32_t v[32];
@@ -379,6 +472,16 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (p.ar_mode && threadIdx.x == 0) {
+    // the last CTA to leave publishes the new epoch (every CTA read the old one before the first barrier)
+    __threadfence();
+    const uint32_t done = atomicAdd(&p.comm.ctrl[1], 1u) + 1;
+    if (done == gridDim.x) {
+      p.comm.ctrl[1] = 0;
+      __threadfence();
+      atomicExch(&p.comm.ctrl[0], ar_epoch_at_entry);
+    }
+  }
 }
 
 // Sum split-K partials (+ optional residual) into bf16.
@@ -412,6 +515,11 @@ static int launch_one(const CUtensorMap& tmW, const CUtensorMap& tmX, const Gemm
 }  // namespace b200
 
 using namespace b200;
+
+// Set by b200_gemm_wdec_allreduce around its call into the common launcher (host threads that launch
+// GEMMs concurrently must serialise fused all-reduce calls; one engine thread per process does).
+static const B200Comm* g_ar_comm = nullptr;
+static unsigned long long g_ar_budget = 0;
 
 extern "C" int b200_gemm_pick_bn(int T) {
   if (T <= 16) return 16;
@@ -450,6 +558,15 @@ extern "C" int b200_gemm_wdec(int wfmt, const void* W, const float* scales, cons
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.ldo = N;
   p.status = status;
+  p.ar_mode = 0;
+  p.ar_budget_ns = 0;
+  memset(&p.comm, 0, sizeof(p.comm));
+  if (g_ar_comm) {
+    if (splits != 1 || !out_bf16) return -ERR_BAD_ARG;
+    p.ar_mode = 1;
+    p.ar_budget_ns = g_ar_budget;
+    p.comm = *g_ar_comm;
+  }
   if ((splits > 1 || !out_bf16) && !out_f32) return -ERR_BAD_ARG;
   if (wfmt != WF_BF16) {
     // the decode warps keep at most 256 block scales (K range of 32768) per tile in registers
@@ -483,6 +600,25 @@ extern "C" int b200_gemm_wdec(int wfmt, const void* W, const float* scales, cons
   }
 #undef B200_DISPATCH
   return -ERR_BAD_ARG;
+}
+
+// Row-parallel GEMM fused with a one-shot all-reduce over peer memory: every rank calls this with its
+// K-shard of W and X; all ranks end with out = sum_r X_r W_r^T (+ residual). T*N <= comm->slot_elems and
+// ceil(N/128) * ceil(T/BN) <= B200_FLAGS_PER_SLOT. With world == 1 this is the plain GEMM.
+extern "C" int b200_gemm_wdec_allreduce(int wfmt, const void* W, const float* scales, const void* X,
+                                        void* out_bf16, const void* residual, int T, int N, int K,
+                                        const B200Comm* comm, unsigned long long budget_ns, int* status,
+                                        cudaStream_t stream) {
+  if (!comm || comm->world <= 1)
+    return b200_gemm_wdec(wfmt, W, scales, X, out_bf16, nullptr, residual, T, N, K, 1, status, stream);
+  if ((unsigned long long)T * N > comm->slot_elems) return -ERR_BAD_ARG;
+  const int BN = b200_gemm_pick_bn(T);
+  if ((long long)((N + BM - 1) / BM) * ((T + BN - 1) / BN) > B200_FLAGS_PER_SLOT) return -ERR_BAD_ARG;
+  g_ar_comm = comm;
+  g_ar_budget = budget_ns ? budget_ns : B200_WAIT_BUDGET_NS;
+  const int rc = b200_gemm_wdec(wfmt, W, scales, X, out_bf16, nullptr, residual, T, N, K, 1, status, stream);
+  g_ar_comm = nullptr;
+  return rc;
 }
 
 extern "C" int b200_splitk_reduce(const float* part, int splits, long long n, const void* residual,
