@@ -37,12 +37,15 @@ def parse():
     ap.add_argument("--batch-decode", type=int, default=32, help="extra batched decode phase (0 = skip)")
     ap.add_argument("--layers", type=int, default=64, help="debug only; the reported config is 64")
     ap.add_argument("--chunk", type=int, default=8192)
+    ap.add_argument("--tiny", action="store_true", help="debug only: 4-layer hidden-256 model")
     return ap.parse_args()
 
 
 def run_reference(args) -> None:
     from baseline import reference_arm
-    print(json.dumps(reference_arm.run(args)), flush=True)
+    rec = reference_arm.run(args)
+    if rec:   # ranks other than 0 of a multi-rank run return nothing
+        print(json.dumps(rec), flush=True)
 
 
 def main() -> None:

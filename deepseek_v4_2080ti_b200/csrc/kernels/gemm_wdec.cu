@@ -53,6 +53,11 @@ struct GemmParams {
   const __nv_bfloat16* residual;  // optional [T, ldo], added in the epilogue (splits == 1)
   int ldo;
   int* status;
+  // In-kernel split-K fix-up (splits > 1 with `out` set): every split writes its fp32 partial to
+  // out_f32, then bumps tile_counters[tile]; the CTA that arrives last sums the partials in split
+  // order (so the result does not depend on which CTA is last), adds the residual, stores bf16 and
+  // resets the counter.  tile_counters must be zero before the first use.
+  int* tile_counters;
   // Fused all-reduce (row-parallel GEMM under tensor parallelism): when ar_mode == 1 the epilogue
   // pushes this rank's partial tile to every peer, waits for theirs and stores the sum.
   int ar_mode;
@@ -60,20 +65,29 @@ struct GemmParams {
   B200Comm comm;
 };
 
-template <int BN>
+// Shared memory holds two rings.  The "raw" ring (SR stages) receives what TMA brings: the
+// activation tile plus either the raw FP8 weight tile or, for bf16 weights, the ready-to-use
+// weight tile.  The "decoded" ring (SA stages, FP8 only) holds bf16 weight tiles written by the
+// decode warps.  Raw FP8 stages are small (8 KB), so the raw ring is deep enough (up to 16
+// stages, >= 100 KB per SM in flight) to keep HBM busy in the weight-streaming decode regime,
+// while the 16 KB decoded tiles only need enough stages to overlap decode with the MMA.
+template <int BN, int WFMT>
 struct SmemLayout {
-  static constexpr int A_BYTES = BM * BK * 2;       // 16 KB decoded bf16 weights
+  static constexpr int A_BYTES = BM * BK * 2;       // 16 KB bf16 weights (decoded, or loaded for WF_BF16)
   static constexpr int X_BYTES = BN * BK * 2;       // activations
   static constexpr int RAW_BYTES = BM * BK;         // 8 KB raw fp8
-  static constexpr int STAGE_BYTES = A_BYTES + X_BYTES + RAW_BYTES;
   static constexpr int BUDGET = 232448 - 1024 /*align slack*/ - 512 /*barriers*/;
-  static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + 512;
-  // Decode warps work in GROUPS independent groups, each owning every GROUPS-th
-  // pipeline stage, so barrier/fence latency of one stage overlaps another's ALU work.
-  static constexpr int GROUPS = STAGES >= 6 ? 4 : 2;
+  static constexpr int SA = (WFMT == WF_BF16) ? 0 : 4;
+  static constexpr int W_STAGE_BYTES = (WFMT == WF_BF16) ? A_BYTES : RAW_BYTES;
+  static constexpr int STAGE_BYTES = W_STAGE_BYTES + X_BYTES;
+  static constexpr int SR_RAW = (BUDGET - SA * A_BYTES) / STAGE_BYTES;
+  static constexpr int SR = SR_RAW > 16 ? 16 : SR_RAW;
+  static constexpr int TOTAL = SR * STAGE_BYTES + SA * A_BYTES + 1024 + 512;
+  // Decode warps work in GROUPS independent groups; group g owns decoded slot g and every
+  // GROUPS-th k-block, so barrier/fence latency of one stage overlaps another's ALU work.
+  static constexpr int GROUPS = 4;
   static constexpr int WARPS_PER_GROUP = NUM_DEC_WARPS / GROUPS;
+  static_assert(SR >= 2, "pipeline needs at least two raw stages");
 };
 
 // 4 fp8 bytes stored as (w0, w2, w1, w3) -> two bf16x2 words (w0,w1), (w2,w3),
@@ -93,23 +107,28 @@ template <int BN, int WFMT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                  GemmParams p) {
-  using L = SmemLayout<BN>;
-  constexpr int S = L::STAGES;
+  using L = SmemLayout<BN, WFMT>;
+  constexpr int S = L::SR;                       // raw ring depth
+  constexpr int SA = L::SA;                      // decoded ring depth (0 for bf16 weights)
+  constexpr int SAB = SA > 0 ? SA : 1;
   constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
   extern __shared__ uint8_t smem_raw_base[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_base) + 1023) &
                                              ~uintptr_t(1023));
+  // bf16 weights: sA is the raw ring itself (S stages); FP8: sA is the decoded ring (SA stages)
   uint8_t* sA = smem;
-  uint8_t* sX = sA + S * L::A_BYTES;
+  uint8_t* sX = sA + (WFMT == WF_BF16 ? S : SA) * L::A_BYTES;
   uint8_t* sRaw = sX + S * L::X_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sRaw + S * L::RAW_BYTES);
-  uint64_t* tma_full = bars;            // [S]
-  uint64_t* a_full = bars + S;          // [S]
-  uint64_t* empty = bars + 2 * S;       // [S]
-  uint64_t* acc_full = bars + 3 * S;    // [2]
-  uint64_t* acc_empty = bars + 3 * S + 2;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * S + 4);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sRaw + (WFMT == WF_BF16 ? 0 : S * L::RAW_BYTES));
+  uint64_t* tma_full = bars;                  // [S]   raw stage landed
+  uint64_t* empty = bars + S;                 // [S]   k-block consumed (MMA commit): raw stage and decoded slot
+  uint64_t* a_full = bars + 2 * S;            // [SAB] decoded tile written
+  uint64_t* acc_full = bars + 2 * S + SAB;       // [2]
+  uint64_t* acc_empty = bars + 2 * S + SAB + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + SAB + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* fix_last = const_cast<int*>(abort_flag) + 1;   // split-K fix-up: "this CTA finishes the tile"
+  volatile int* epi_abort = reinterpret_cast<volatile int*>(fix_last + 1);  // written by epilogue threads only
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -117,14 +136,17 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&tma_full[s], 1);
-      mbar_init(&a_full[s], L::WARPS_PER_GROUP);
       mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < SAB; ++s) {
+      mbar_init(&a_full[s], L::WARPS_PER_GROUP);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], NUM_EPI_WARPS * 32);
     }
     *abort_flag = 0;
+    *epi_abort = 0;
     mbar_fence_init();
   }
   if (warp == MMA_WARP) {
@@ -173,6 +195,7 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
                       p.w_tiled + ((size_t)m_tile * p.kb_total + kb) * L::RAW_BYTES, L::RAW_BYTES, &tma_full[s]);
           }
           tma_load_2d(sX + s * L::X_BYTES, &tmX, &tma_full[s], kb * BK, n_tile * BN);
+
         }
       }
     }
@@ -204,21 +227,25 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             failed = true;
             break;
           }
+          const int sa = (WFMT == WF_BF16) ? s : (int)(it % SAB);
           if (WFMT != WF_BF16) {
-            if (!mbar_wait(&a_full[s], ph)) {
+            if (!mbar_wait(&a_full[sa], (it / SAB) & 1)) {
               atomicExch(p.status, ERR_WAIT_DEQUANT);
               failed = true;
               break;
             }
           }
           tc_fence_after();
-          const uint64_t da = umma_desc_sw128(sA + s * L::A_BYTES);
+          const uint64_t da = umma_desc_sw128(sA + sa * L::A_BYTES);
           const uint64_t db = umma_desc_sw128(sX + s * L::X_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             // advance 16 bf16 = 32 bytes inside the swizzle row: +2 in 16-byte units
             umma_bf16_ss(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
+          // One commit per k-block frees the raw stage for the producer and, SA k-blocks later, the
+          // decoded slot for the decode warps (they wait on the same barrier): tcgen05.commit occupies
+          // the tensor pipe for a few hundred cycles, so a second commit per k-block would cap the rate.
           umma_commit(&empty[s]);
         }
         if (failed) {
@@ -230,8 +257,9 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
   } else if (warp >= DEC_WARP0) {
     // ------------------------------------------------- weight decode (FP8 -> bf16)
-    if (WFMT == WF_FP8_B128) {
+    if constexpr (WFMT == WF_FP8_B128) {
       constexpr int G = L::GROUPS;
+      static_assert(G == SAB, "one decode group per decoded slot");
       constexpr int WPG = L::WARPS_PER_GROUP;
       constexpr int GT = WPG * 32;             // threads per group
       constexpr int REPS = (BM * 4) / GT;      // 16-byte chunks per thread per stage
@@ -267,21 +295,28 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           for (int j = 1; j < 8; ++j) scv = (si >> 5) == j ? my_sc[j] : scv;
           const float sc = __shfl_sync(0xffffffffu, scv, si & 31);
           bool ok = mbar_wait(&tma_full[s], ph);
+          if (it >= (uint32_t)SAB) {
+            // decoded slot `grp` was last read by the MMAs of k-block it - SA
+            const uint32_t prev = it - SAB;
+            ok = ok && mbar_wait(&empty[prev % S], (prev / S) & 1);
+          }
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) {
             if (lane == 0) atomicExch(p.status, ERR_WAIT_TMA);
             failed = true;
             break;
           }
+          tc_fence_after();
           __nv_bfloat162 sc2 = __float2bfloat162_rn(sc);
           const uint32_t scw = *reinterpret_cast<uint32_t*>(&sc2);
           const uint8_t* raw = sRaw + s * L::RAW_BYTES;
-          uint8_t* A = sA + s * L::A_BYTES;
+          uint8_t* A = sA + grp * L::A_BYTES;
           uint4 q[REPS];
 #pragma unroll
           for (int rep = 0; rep < REPS; ++rep) {
             const int i = d + rep * GT;
-            q[rep] = *reinterpret_cast<const uint4*>(raw + (i >> 2) * BK + (i & 3) * 16);
+            const int rr = i >> 2;
+            q[rep] = *reinterpret_cast<const uint4*>(raw + rr * BK + (((i & 3) ^ ((rr >> 1) & 3)) << 4));
           }
 #pragma unroll
           for (int rep = 0; rep < REPS; ++rep) {
@@ -303,7 +338,7 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           }
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&a_full[s]);
+          if (lane == 0) mbar_arrive(&a_full[grp]);
         }
         if (failed) {
           *abort_flag = 1;
@@ -316,7 +351,17 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     uint32_t tile_i = 0;
     const int row_in_tile = warp * 32 + lane;  // TMEM lane == output feature within the tile
     const uint32_t ar_epoch = p.ar_mode ? p.comm.ctrl[0] + 1 : 0;   // read before any CTA can finish
-    for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x, ++tile_i) {
+    // Modes whose epilogue uses a named barrier must leave the loop together: the decision to stop is
+    // taken from epi_abort, which only epilogue threads write and always before a barrier.
+    const bool sync_mode = p.ar_mode != 0 || (p.splits > 1 && p.out != nullptr);
+    for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++tile_i) {
+      if (sync_mode) {
+        if (threadIdx.x == 0 && *abort_flag) *epi_abort = 1;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*epi_abort) break;
+      } else if (*abort_flag) {
+        break;
+      }
       const int m_tile = w % p.m_tiles;
       const int rest = w / p.m_tiles;
       const int n_tile = rest % p.n_tiles;
@@ -328,7 +373,12 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       if (!ok) {
         if (lane == 0) atomicExch(p.status, ERR_WAIT_ACC);
         *abort_flag = 1;
-        break;
+        if (!sync_mode) break;
+        *epi_abort = 1;
+      }
+      if (sync_mode) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*epi_abort) break;
       }
       tc_fence_after();
       const int f = m_tile * BM + row_in_tile;
@@ -375,10 +425,11 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           if (!wait_flag_ge(mine, ar_epoch, p.ar_budget_ns)) {
             atomicExch(p.status, ERR_WAIT_PEER);
             *abort_flag = 1;
+            *epi_abort = 1;
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*abort_flag) break;
+        if (*epi_abort) break;
         // pass 2: own fp32 accumulator + peers' bf16 partials (fixed rank order) (+ residual) -> out
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += CH) {
@@ -456,6 +507,31 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[buf]);
+      if (p.splits > 1 && p.out != nullptr) {
+        // ---- split-K fix-up by the last-arriving CTA of this output tile
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int tile_id = n_tile * p.m_tiles + m_tile;
+        if (threadIdx.x == 0) {
+          const int prev = atomicAdd(&p.tile_counters[tile_id], 1);
+          *fix_last = (prev == p.splits - 1);
+          if (prev == p.splits - 1) p.tile_counters[tile_id] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*fix_last && f_ok) {
+          __threadfence();
+          const int t_lo = n_tile * BN;
+          const int t_hi = min(p.T, t_lo + BN);
+          for (int t = t_lo; t < t_hi; ++t) {
+            const size_t off = (size_t)t * p.ldo + f;
+            float acc = p.residual ? __bfloat162float(p.residual[off]) : 0.f;
+            for (int sp = 0; sp < p.splits; ++sp)
+              acc += __ldcg(p.out_f32 + (size_t)sp * p.T * p.ldo + off);
+            p.out[off] = __float2bfloat16(acc);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // fix_last is rewritten by the next tile
+      }
     }
   }
 
@@ -498,7 +574,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ part, int splits,
 template <int BN, int WFMT>
 static int launch_one(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p,
                       cudaStream_t stream) {
-  using L = SmemLayout<BN>;
+  using L = SmemLayout<BN, WFMT>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_wdec_kernel<BN, WFMT>,
@@ -531,12 +607,28 @@ extern "C" int b200_gemm_pick_bn(int T) {
 
 // wfmt: 0 = bf16 weights [N, K]; 1 = FP8 E4M3 weights in the tile-major layout
 // [ceil(N/128)][ceil(K/64)][128 rows][64 bytes] (zero padded; each 4-byte group stored as
-// (w0,w2,w1,w3)) with fp32 scales [ceil(N/128), ceil(K/128)].
+// (w0,w2,w1,w3); the four 16-byte chunks of row r stored at chunk index c ^ ((r >> 1) & 3), which is
+// the 64-byte shared-memory swizzle, so that the same bytes can also feed FP8 tensor-core tiles
+// directly, see gemm_w8a8s.cu) with fp32 scales [ceil(N/128), ceil(K/128)].
 // splits == 1: writes bf16 `out` (adds `residual` when given), or fp32 `out_f32` when out == null.
 // splits  > 1: writes fp32 partials to out_f32 [splits, T, N] (caller reduces).
+extern "C" int b200_gemm_wdec_ex(int wfmt, const void* W, const float* scales, const void* X,
+                                 void* out_bf16, float* out_f32, const void* residual, int T, int N,
+                                 int K, int splits, int* tile_counters, int* status, cudaStream_t stream);
+
 extern "C" int b200_gemm_wdec(int wfmt, const void* W, const float* scales, const void* X,
                               void* out_bf16, float* out_f32, const void* residual, int T, int N,
                               int K, int splits, int* status, cudaStream_t stream) {
+  return b200_gemm_wdec_ex(wfmt, W, scales, X, out_bf16, out_f32, residual, T, N, K, splits, nullptr, status,
+                           stream);
+}
+
+// As b200_gemm_wdec, plus the in-kernel split-K fix-up: with splits > 1, out_bf16, out_f32 (scratch
+// for splits*T*N floats) and tile_counters (ceil(N/128)*ceil(T/BN) zeroed ints, left zeroed) all set,
+// the kernel itself reduces the partials and writes bf16 (+ residual); no second launch is needed.
+extern "C" int b200_gemm_wdec_ex(int wfmt, const void* W, const float* scales, const void* X,
+                                 void* out_bf16, float* out_f32, const void* residual, int T, int N,
+                                 int K, int splits, int* tile_counters, int* status, cudaStream_t stream) {
   if (T <= 0 || N <= 0 || K <= 0 || (K % 16) != 0 || splits < 1) return -ERR_BAD_ARG;
   const int BN = b200_gemm_pick_bn(T);
   GemmParams p;
@@ -558,6 +650,8 @@ extern "C" int b200_gemm_wdec(int wfmt, const void* W, const float* scales, cons
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.ldo = N;
   p.status = status;
+  p.tile_counters = tile_counters;
+  if (splits > 1 && out_bf16 && !tile_counters) return -ERR_BAD_ARG;
   p.ar_mode = 0;
   p.ar_budget_ns = 0;
   memset(&p.comm, 0, sizeof(p.comm));

@@ -51,24 +51,37 @@ def write_file(path: str, tensors: dict[str, torch.Tensor], metadata: dict[str, 
 
 def write_checkpoint(directory: str, state: Iterable[tuple[str, torch.Tensor]], shard_bytes: int = 4 << 30,
                      config_json: str | None = None) -> list[str]:
-    """Stream (name, tensor) pairs into ``model-0000i-of-0000N.safetensors`` shards + index (+ config.json)."""
+    """Stream (name, tensor) pairs into ``model-0000i.safetensors`` shards + index (+ config.json).
+    A shard is written as soon as it is full, so host memory holds one shard at a time."""
     os.makedirs(directory, exist_ok=True)
-    shards: list[dict[str, torch.Tensor]] = [{}]
+    files: list[str] = []
+    weight_map: dict[str, str] = {}
+    total = 0
+    cur: dict[str, torch.Tensor] = {}
     size = 0
+
+    def flush() -> None:
+        nonlocal cur, size, total
+        if not cur:
+            return
+        fn = f"model-{len(files) + 1:05d}.safetensors"
+        total += write_file(os.path.join(directory, fn), cur, {"format": "pt"})
+        files.append(fn)
+        for k in cur:
+            weight_map[k] = fn
+        cur, size = {}, 0
+
     for name, t in state:
         n = t.numel() * t.element_size()
         if size and size + n > shard_bytes:
-            shards.append({})
-            size = 0
-        shards[-1][name] = t.cpu()
+            flush()
+        cur[name] = t.cpu()
         size += n
-    files, weight_map, total = [], {}, 0
-    for i, sh in enumerate(shards):
-        fn = "model.safetensors" if len(shards) == 1 else f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
-        total += write_file(os.path.join(directory, fn), sh, {"format": "pt"})
-        files.append(fn)
-        for k in sh:
-            weight_map[k] = fn
+    flush()
+    if len(files) == 1:
+        os.replace(os.path.join(directory, files[0]), os.path.join(directory, "model.safetensors"))
+        files = ["model.safetensors"]
+        weight_map = {k: "model.safetensors" for k in weight_map}
     with open(os.path.join(directory, "model.safetensors.index.json"), "w") as f:
         json.dump({"metadata": {"total_size": total}, "weight_map": weight_map}, f)
     if config_json is not None:

@@ -38,6 +38,31 @@ def add_rmsnorm(resid: torch.Tensor, delta: torch.Tensor | None, gamma: torch.Te
     return out
 
 
+def rmsnorm_split(resid: torch.Tensor, delta: torch.Tensor | None, gamma: torch.Tensor, terms: int, eps: float = 1e-6,
+                  unit_offset: bool = False, want_bf16: bool = True):
+    """(resid += delta in place when delta is given) -> (norm(resid) bf16 or None, (xq, inv_c)): the norm output
+    also as E4M3 terms for ``gemm.linear_stream`` (csrc/kernels/decode_fused.cu)."""
+    rows, cols = resid.shape
+    out = torch.empty_like(resid) if want_bf16 else None
+    xq = torch.empty(rows * terms, cols, dtype=torch.uint8, device=resid.device)
+    inv_c = torch.empty(rows, dtype=torch.float32, device=resid.device)
+    rc = _lib.lib().b200_rmsnorm_split(_lib.ptr(resid), _lib.ptr(delta), _lib.ptr(gamma), _lib.ptr(out), _lib.ptr(xq),
+                                       _lib.ptr(inv_c), rows, cols, _f(eps), int(unit_offset), terms, _lib.stream())
+    _lib.check(rc, "rmsnorm_split")
+    return out, (xq, inv_c)
+
+
+def silu_mul_split(gu: torch.Tensor, terms: int):
+    """gu [T, 2I] (gate | up) -> E4M3 terms of silu(gate) * up for ``gemm.linear_stream``: (xq [T*terms, I], inv_c [T])."""
+    t, two_i = gu.shape
+    inter = two_i // 2
+    xq = torch.empty(t * terms, inter, dtype=torch.uint8, device=gu.device)
+    inv_c = torch.empty(t, dtype=torch.float32, device=gu.device)
+    rc = _lib.lib().b200_silu_mul_split(_lib.ptr(gu), _lib.ptr(xq), _lib.ptr(inv_c), t, inter, terms, _lib.stream())
+    _lib.check(rc, "silu_mul_split")
+    return xq, inv_c
+
+
 def rmsnorm_ref(x, gamma, eps=1e-6, unit_offset=False):
     xf = x.float()
     g = gamma.float()

@@ -44,6 +44,24 @@ def step(states, slot_ids, mixed, q_off, k_off, v_off, g, beta, hv, hk):
     return out
 
 
+def decode_fused(proj, x, w_ab, a_log, dt_bias, conv_w, tails, states, slot_ids, gamma, hv, hk, eps=1e-6):
+    """Whole Gated-DeltaNet token mixer of a decode step in one launch (csrc/kernels/decode_fused.cu).
+
+    proj [B, 2kd+2vd] bf16 = q|k|v|z projection output; x [B, hidden] bf16 normed layer input; w_ab [2Hv, hidden]
+    bf16 (a rows, then b rows); conv_w [2kd+vd, 4] bf16; tails [slots, 3, 2kd+vd] bf16 and states
+    [slots, Hv, 128, 128] fp32 are updated in place for ``slot_ids`` (int32 [B]).  Returns [B, Hv*128] bf16
+    (gated-RMSNorm output, the input of the output projection)."""
+    b = proj.shape[0]
+    out = torch.empty(b, hv * 128, dtype=torch.bfloat16, device=proj.device)
+    rc = _lib.lib().b200_gdn_decode_fused(
+        _lib.ptr(proj), proj.stride(0), _lib.ptr(x), x.shape[1], _lib.ptr(w_ab), _lib.ptr(a_log), _lib.ptr(dt_bias),
+        _lib.ptr(conv_w), conv_w.shape[1], _lib.ptr(tails), _ll(tails.stride(0)), _lib.ptr(states),
+        _ll(states.stride(0)), _lib.ptr(slot_ids), _lib.ptr(gamma), _lib.ptr(out), b, hv, hk, ctypes.c_float(eps),
+        _lib.stream())
+    _lib.check(rc, "gdn_decode_fused")
+    return out
+
+
 def recurrent_ref(q, k, v, g, beta, state):
     """fp32 oracle, token by token. q,k [T,Hk,128]; v [T,Hv,128]; g,beta [T,Hv]; state [Hv,128,128] (dk, dv).
 

@@ -27,7 +27,10 @@ def prepack_fp8(w: torch.Tensor) -> torch.Tensor:
       32-bit word into two bf16x2 words with shifts and masks only, and this order makes those words
       come out as (w0,w1) and (w2,w3);
     * each [128 rows x 64 bytes] pipeline-stage tile is contiguous (8 KB), so a stage is fetched with a
-      single bulk copy instead of 128 separate 64-byte rows.
+      single bulk copy instead of 128 separate 64-byte rows;
+    * inside a tile the four 16-byte chunks of row r are stored at chunk index ``c ^ ((r >> 1) & 3)``
+      (the 64-byte shared-memory swizzle), so the bulk copy lands in the layout an FP8 tensor-core
+      operand descriptor expects and the small-batch kernel can use the bytes without touching them.
     """
     u = w.view(torch.uint8)
     n, k = u.shape
@@ -37,7 +40,13 @@ def prepack_fp8(w: torch.Tensor) -> torch.Tensor:
         full[:n, :k] = u
         u = full
     u = u.view(npad, kpad // 4, 4)[:, :, [0, 2, 1, 3]].reshape(npad // 128, 128, kpad // 64, 64)
-    return u.permute(0, 2, 1, 3).contiguous()
+    u = u.permute(0, 2, 1, 3).contiguous()                       # [mt, kb, 128 rows, 64 bytes]
+    # 64-byte swizzle: 16-byte chunk c of row r is stored at chunk c ^ ((r >> 1) & 3)
+    r = torch.arange(128, device=u.device)
+    c = torch.arange(4, device=u.device)
+    src_chunk = c[None, :] ^ ((r[:, None] >> 1) & 3)             # physical chunk p holds logical chunk p ^ s
+    idx = (src_chunk[:, :, None] * 16 + torch.arange(16, device=u.device)[None, None, :]).reshape(128, 64)
+    return torch.gather(u, 3, idx[None, None].expand(u.shape[0], u.shape[1], 128, 64)).contiguous()
 
 
 @dataclass
@@ -63,37 +72,137 @@ class PackedLinear:
         return self.weight.numel() * self.weight.element_size() + (0 if self.scales is None else self.scales.numel() * 4)
 
 
-_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_workspaces: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+MAX_TILE_COUNTERS = 1 << 16
 
 
-def _workspace(nfloats: int, device) -> torch.Tensor:
-    key = (torch.device(device).index or 0, 0)
+def _workspace(nfloats: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """(fp32 split-K scratch, zeroed int32 tile counters) of the device; grown on demand, never shrunk.
+    The kernel leaves the counters at zero, so they are cleared only when allocated."""
+    key = torch.device(device).index or 0
     ws = _workspaces.get(key)
-    if ws is None or ws.numel() < nfloats:
-        ws = torch.empty(max(nfloats, 1 << 22), dtype=torch.float32, device=device)
+    if ws is None or ws[0].numel() < nfloats:
+        ws = (torch.empty(max(nfloats, 1 << 22), dtype=torch.float32, device=device),
+              ws[1] if ws is not None else torch.zeros(MAX_TILE_COUNTERS, dtype=torch.int32, device=device))
         _workspaces[key] = ws
     return ws
 
 
+def _bn(t: int) -> int:
+    return 16 if t <= 16 else 32 if t <= 32 else 64 if t <= 64 else 128 if t <= 128 else 256
+
+
 def pick_splits(t: int, n: int, k: int) -> int:
-    """Split K when the tile grid alone cannot fill the 148 SMs (small-batch decode)."""
-    bn = 16 if t <= 16 else 32 if t <= 32 else 64 if t <= 64 else 128 if t <= 128 else 256
-    tiles = ((n + 127) // 128) * ((t + bn - 1) // bn)
-    if tiles >= NUM_SMS or t > 128:
+    """Split K when the tile grid alone cannot fill the 148 SMs evenly (small-batch decode).
+
+    The persistent grid runs ceil(units / 148) waves of (tile, split) units; the split count that wastes
+    the least of the last wave wins, subject to at least 8 k-blocks (512 columns) per split so the
+    pipeline fill is amortised, and to a bound on the fp32 partial traffic for larger T."""
+    if t > 128:
         return 1
+    tiles = ((n + 127) // 128) * ((t + _bn(t) - 1) // _bn(t))
     kb = (k + 63) // 64
-    s = max(1, min(NUM_SMS // tiles, kb // 8))
-    return s
+    max_s = max(1, min(kb // 8, 16 if t <= 16 else 8 if t <= 64 else 4))
+    best, best_eff = 1, 0.0
+    for s in range(1, max_s + 1):
+        per = (kb + s - 1) // s
+        s_eff = (kb + per - 1) // per
+        if s_eff != s:
+            continue
+        units = tiles * s
+        waves = (units + NUM_SMS - 1) // NUM_SMS
+        # the longest split sets the pace of a wave
+        eff = (tiles * kb) / (waves * NUM_SMS * per)
+        if eff > best_eff + 0.02:
+            best, best_eff = s, eff
+    return best
+
+
+STREAM_MAX_T = 32   # token counts served by the weight-streaming FP8 kernel (csrc/kernels/gemm_w8a8s.cu)
+
+
+def stream_layout(t: int) -> tuple[int, int]:
+    """(MMA N, number of E4M3 terms per activation) the streaming kernel uses for ``t`` tokens."""
+    if t <= 5:
+        return 16, 3
+    if t <= 8:
+        return 16, 2
+    if t <= 16:
+        return 32, 2
+    return 64, 2
+
+
+def pick_splits_stream(n: int, k: int) -> int:
+    """Split count for the streaming kernel: units are (128-row tile, run of 128-wide K blocks).
+    Every unit ends with a fix-up (fence, counter, reduction by the last arriver), so the smallest
+    split count that fills at least 85% of the waves wins; more splits only when they gain > 5%."""
+    tiles = (n + 127) // 128
+    kblk = k // 128
+    best, best_eff = 1, 0.0
+    for s in range(1, max(1, min(kblk // 4, 16)) + 1):
+        per = (kblk + s - 1) // s
+        if (kblk + per - 1) // per != s:
+            continue
+        waves = (tiles * s + NUM_SMS - 1) // NUM_SMS
+        eff = (tiles * kblk) / (waves * NUM_SMS * per)
+        if eff > best_eff + 0.05:
+            best, best_eff = s, eff
+        if best_eff >= 0.85:
+            break
+    return best
+
+
+def split_activations(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [T, K] -> (uint8 [T*terms, K] E4M3 terms, fp32 [T] inverse row scales) for ``linear_stream``."""
+    t, k = x.shape
+    _, terms = stream_layout(t)
+    xq = torch.empty(t * terms, k, dtype=torch.uint8, device=x.device)
+    inv_c = torch.empty(t, dtype=torch.float32, device=x.device)
+    rc = _lib.lib().b200_act_split_e4m3(_lib.ptr(x), t, k, terms, _lib.ptr(xq), _lib.ptr(inv_c), _lib.stream())
+    _lib.check(rc, "act_split_e4m3")
+    return xq, inv_c
+
+
+def linear_stream(x: torch.Tensor, w: PackedLinear, residual: torch.Tensor | None = None,
+                  out: torch.Tensor | None = None, splits: int | None = None,
+                  xsplit: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
+    """Small-batch (T <= 32) FP8 projection: weights go from HBM to the tensor core untouched, the
+    activations are split into E4M3 terms instead.  ``xsplit`` reuses a previous ``split_activations(x)``."""
+    xq, inv_c = xsplit if xsplit is not None else split_activations(x)
+    t, k = inv_c.numel(), xq.shape[1]        # x itself may be None when the split is supplied
+    n = w.n
+    dev = xq.device
+    assert w.wfmt == WF_FP8_B128 and t <= STREAM_MAX_T and k % 128 == 0 and k == w.k
+    if out is None:
+        out = torch.empty(t, n, dtype=torch.bfloat16, device=dev)
+    if splits is None:
+        splits = pick_splits_stream(n, k)
+    kblk = k // 128
+    splits = max(1, min(splits, kblk))
+    per = (kblk + splits - 1) // splits
+    splits = (kblk + per - 1) // per
+    if (n + 127) // 128 > MAX_TILE_COUNTERS:
+        splits = 1
+    ws, counters = _workspace(splits * t * n, dev) if splits > 1 else (None, None)
+    rc = _lib.lib().b200_gemm_w8a8s(_lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(xq), _lib.ptr(inv_c),
+                                    _lib.ptr(out), _lib.ptr(residual), t, n, k, splits, _lib.ptr(ws),
+                                    _lib.ptr(counters), _lib.ptr(_lib.status_word(dev)), _lib.stream())
+    _lib.check(rc, "gemm_w8a8s")
+    return out
 
 
 def linear(x: torch.Tensor, w: PackedLinear, residual: torch.Tensor | None = None,
            out: torch.Tensor | None = None, splits: int | None = None,
-           out_f32: bool = False) -> torch.Tensor:
-    """``x [T, K] bf16`` -> ``[T, N]`` bf16 (or fp32 when ``out_f32``)."""
+           out_f32: bool = False, stream: bool | None = None) -> torch.Tensor:
+    """``x [T, K] bf16`` -> ``[T, N]`` bf16 (or fp32 when ``out_f32``).  FP8 weights with T <= 32 go to the
+    weight-streaming kernel (``stream=False`` forces the decode-warp kernel); split-K partials are
+    reduced inside the kernel by the last-arriving CTA of each output tile."""
     assert x.dtype == torch.bfloat16 and x.is_cuda and x.dim() == 2 and x.is_contiguous()
     t, k = x.shape
     assert k == w.k, (k, w.k)
     n = w.n
+    if w.wfmt == WF_FP8_B128 and t <= STREAM_MAX_T and k % 128 == 0 and not out_f32 and stream is not False:
+        return linear_stream(x, w, residual, out, splits)
     if splits is None:
         splits = 1 if out_f32 else pick_splits(t, n, k)
     L = _lib.lib()
@@ -106,22 +215,23 @@ def linear(x: torch.Tensor, w: PackedLinear, residual: torch.Tensor | None = Non
         return o32
     if out is None:
         out = torch.empty(t, n, dtype=torch.bfloat16, device=x.device)
+    kb = (k + 63) // 64
+    splits = max(1, min(splits, kb))
+    per = (kb + splits - 1) // splits
+    splits = (kb + per - 1) // per          # same rule as the launcher: no empty split
+    tiles = ((n + 127) // 128) * ((t + _bn(t) - 1) // _bn(t))
+    if splits > 1 and tiles > MAX_TILE_COUNTERS:
+        splits = 1
     if splits <= 1:
         rc = L.b200_gemm_wdec(w.wfmt, _lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(x), _lib.ptr(out),
                               None, _lib.ptr(residual), t, n, k, 1, _lib.ptr(st), _lib.stream())
         _lib.check(rc, "gemm_wdec")
         return out
-    kb = (k + 63) // 64
-    splits = min(splits, kb)
-    per = (kb + splits - 1) // splits
-    splits = (kb + per - 1) // per          # same rule as the launcher: no empty split
-    ws = _workspace(splits * t * n, x.device)
-    rc = L.b200_gemm_wdec(w.wfmt, _lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(x), None, _lib.ptr(ws),
-                          None, t, n, k, splits, _lib.ptr(st), _lib.stream())
+    ws, counters = _workspace(splits * t * n, x.device)
+    rc = L.b200_gemm_wdec_ex(w.wfmt, _lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(x), _lib.ptr(out),
+                             _lib.ptr(ws), _lib.ptr(residual), t, n, k, splits, _lib.ptr(counters),
+                             _lib.ptr(st), _lib.stream())
     _lib.check(rc, "gemm_wdec(split-k)")
-    rc = L.b200_splitk_reduce(_lib.ptr(ws), splits, ctypes.c_longlong(t * n), _lib.ptr(residual),
-                              _lib.ptr(out), _lib.stream())
-    _lib.check(rc, "splitk_reduce")
     return out
 
 

@@ -45,6 +45,8 @@ def main():
     ap.add_argument("--k", type=int, default=5120)
     ap.add_argument("--fmt", default="fp8")
     ap.add_argument("--splits", type=int, default=None)
+    ap.add_argument("--kernel", default="auto", choices=["auto", "decode_warps", "stream", "stream_presplit"],
+                    help="gemm: which kernel serves small T (stream_presplit times the GEMM without the activation split)")
     ap.add_argument("--hq", type=int, default=40)
     ap.add_argument("--hkv", type=int, default=8)
     ap.add_argument("--hv", type=int, default=32)
@@ -68,11 +70,16 @@ def main():
             pl = gemm.PackedLinear.from_bf16(w.bfloat16())
         del w
         out = torch.empty(a.t, a.n, dtype=torch.bfloat16, device="cuda")
-        fn = lambda: gemm.linear(x, pl, out=out, splits=a.splits)
+        if a.kernel == "stream_presplit":
+            xs = gemm.split_activations(x)
+            fn = lambda: gemm.linear_stream(x, pl, out=out, splits=a.splits, xsplit=xs)
+        else:
+            st = {"auto": None, "decode_warps": False, "stream": True}[a.kernel]
+            fn = lambda: gemm.linear(x, pl, out=out, splits=a.splits, stream=st)
         med, best = timeit(fn, a.iters, a.warmup)
         flops = 2.0 * a.t * a.n * a.k
         byts = pl.nbytes() + x.numel() * 2 + out.numel() * 2
-        rec.update(t=a.t, n=a.n, k=a.k, fmt=a.fmt, ms=med, ms_best=best, tflops=flops / med / 1e9, gbs=byts / med / 1e6)
+        rec.update(t=a.t, n=a.n, k=a.k, fmt=a.fmt, kernel=a.kernel, ms=med, ms_best=best, tflops=flops / med / 1e9, gbs=byts / med / 1e6)
     elif a.op == "attn_prefill":
         bs = 64
         nb = (a.ctx + bs - 1) // bs
