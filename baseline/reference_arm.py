@@ -96,7 +96,9 @@ def run(args) -> dict:
 
     ctx = args.prompt + args.decode + 64
     id_path = os.path.join(work, f"nccl_id_{os.getpid() if world == 1 else tag}")
-    cmd = [EXE, "--ckpt", work, "--smoke-forward", "--qwen-persistent-stdin", "--max-context", str(ctx),
+    # --smoke-layers: the executable runs ONE layer unless told otherwise (main.cpp:35); ask for all of them
+    cmd = [EXE, "--ckpt", work, "--smoke-forward", "--smoke-layers", str(cfg.num_hidden_layers),
+           "--qwen-persistent-stdin", "--max-context", str(ctx),
            "--qwen-no-prefix-cache", "--prefill-chunk-tokens", str(args.chunk), "--tp-world", str(world),
            "--tp-rank", str(rank), "--device", str(local)]
     if world > 1:
@@ -138,7 +140,7 @@ def run(args) -> dict:
     dec = sum(dec_s) / len(dec_s)
     prefill_tps = args.prompt / pre
     decode_tps = (args.decode - 1) / dec
-    m = re.search(r"tokens=([0-9,]+)", timed[-1])
+    m = re.search(r"(?<![a-z_])tokens=([0-9,]+)", timed[-1])
     toks = m.group(1).split(",") if m else []
     return {
         "impl": "reference", "metric": "prefill_tok_s", "value": round(prefill_tps, 1), "unit": "tok/s",
@@ -155,5 +157,5 @@ def run(args) -> dict:
         "e2e": {"value": round(prefill_tps, 1), "unit": "tok/s",
                 "what": "the engine's own request path: token ids in over stdin, H2D inside prefill, next token read back",
                 "h2d_bytes_per_step": args.prompt * 4, "d2h_bytes_per_step": 4 * args.decode},
-        "checkpoint_write_s": round(ckpt_s, 1), "wall_s": round(wall, 1), "first_tokens": toks[:8],
+        "checkpoint_write_s": round(ckpt_s, 1), "wall_s": round(wall, 1), "first_tokens": [int(t) for t in toks[:16]],
     }

@@ -65,23 +65,32 @@ def main() -> None:
     assert world == args.gpus or world == 1, (world, args.gpus)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    comm = tp.TPComm() if world > 1 else None
-
     cfg = qh.QwenHybridConfig.config2()
-    if args.layers != 64:
+    if args.tiny:
+        cfg = qh.QwenHybridConfig.tiny(layers=4)
+    elif args.layers != 64:
         cfg = qh.QwenHybridConfig(num_hidden_layers=args.layers)
+    comm = None
+    if world > 1:
+        # peer-memory collectives; the GEMM-epilogue all-reduce pushes every tile to every peer, so its slot is
+        # sized for whole prefill chunks only at 2 ranks (larger groups reduce big payloads over NCCL/NVLS)
+        rows = args.chunk if world == 2 else 512
+        comm = tp.PeerComm(slot_elems=rows * cfg.hidden_size)
     bdec = args.batch_decode
     max_slots = max(1, bdec) + 1
     t0 = time.time()
     weights = qh.QwenHybridWeights(cfg, qh.synth_state(cfg, 0, dev), dev, rank, world)
-    rt = qh.QwenHybridRuntime(cfg, weights, max_slots=max_slots, max_context=args.prompt + args.decode + 64,
-                              comm=comm, num_blocks=((args.prompt + args.decode + 64 + 63) // 64) * 2 + max_slots * 8 + 2)
+    max_ctx = args.prompt + args.decode + 64
+    rt = qh.QwenHybridRuntime(cfg, weights, max_slots=max_slots, max_context=max_ctx, comm=comm,
+                              num_blocks=((max_ctx + 63) // 64) * 2 + max_slots * 8 + 2)
     torch.cuda.synchronize()
     if rank == 0:
         print(f"[bench] weights {weights.nbytes() / 1e9:.2f} GB/rank built in {time.time() - t0:.1f}s", file=sys.stderr)
 
     gen = torch.Generator().manual_seed(1)
-    prompt_host = torch.randint(0, cfg.vocab_size, (args.prompt,), generator=gen, dtype=torch.int32).pin_memory()
+    prompt_host = torch.randint(0, cfg.vocab_size, (args.prompt,), generator=gen, dtype=torch.int32)
+    prompt_dev = prompt_host.to(dev)
+    prompt_list = prompt_host.tolist()
 
     def barrier():
         if world > 1:
@@ -90,25 +99,39 @@ def main() -> None:
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
-    def one_request(timed: bool):
-        """prefill + batch-1 decode of one request through the runtime; returns (prefill_ms, decode_ms, launches)."""
+    def device_request():
+        """Kernel-only timing: inputs already on the device, tokens fed back on the device, nothing read by the
+        host inside the timed region.  Returns (prefill_ms, decode_ms, launches)."""
         slot = rt.allocate()
         e0, e1, e2 = ev(), ev(), ev()
         e0.record()
-        ids = prompt_host.to(dev, non_blocking=True)          # H2D of this step's input from pinned memory
-        tok = rt.prefill(slot, ids, args.chunk)
-        first = int(tok.item())                                # D2H of the step's result
+        tok = rt.prefill(slot, prompt_dev, args.chunk)
         e1.record()
         launches = rt.launches
-        toks = [first]
         for _ in range(args.decode - 1):
             tok = rt.decode([slot], tok.to(torch.int32))
             launches += rt.launches
-        last = int(tok.item())
         e2.record()
         torch.cuda.synchronize()
         rt.free(slot)
-        return e0.elapsed_time(e1), e1.elapsed_time(e2), launches, (first, last)
+        return e0.elapsed_time(e1), e1.elapsed_time(e2), launches
+
+    # ---- end-to-end arm: the public API (pocketllm.LLM over the engine backend) on the same runtime.  Every request
+    # carries its prompt as host token ids (copied to the device from pinned memory inside the call) and every
+    # generated token is read back to the host.
+    from pocketllm import LLM, SamplingParams
+    from pocketllm.api.types import EngineArgs
+    from pocketllm.backends.native_backend import NativeBackend
+    from deepseek_v4_2080ti_b200.runtime.loader import RuntimeAdapter
+
+    llm = LLM(backend=NativeBackend(EngineArgs(model="synthetic:bench", max_model_len=max_ctx,
+                                                prefill_chunk_tokens=args.chunk, tensor_parallel_size=1),
+                                    runtime=RuntimeAdapter(rt, max_ctx)))
+    sp = SamplingParams(max_tokens=args.decode, temperature=0.0)
+
+    def api_request():
+        res = llm.generate([{"prompt_token_ids": prompt_list}], sp)[0]
+        return res.timings.prefill_seconds * 1e3, res.timings.decode_seconds * 1e3, len(res.token_ids)
 
     def batch_decode_phase(steps: int):
         """bdec sequences with short prompts decoding together; returns ms per step."""
@@ -132,17 +155,25 @@ def main() -> None:
         return e0.elapsed_time(e1) / steps
 
     for _ in range(args.warmup):
-        one_request(False)
+        device_request()
+    api_request()
     barrier()
-    pre_ms, dec_ms, launches, step_ms = [], [], 0, []
+    pre_ms, dec_ms, launches = [], [], 0
+    api_pre, api_dec = [], []
     with ClockSampler(local) as clk:
         barrier()
-        w0 = time.time()
         for _ in range(args.steps):
-            p, d, l, _ = one_request(True)
+            p, d, l = device_request()
             pre_ms.append(p)
             dec_ms.append(d)
             launches += l
+        barrier()
+        w0 = time.time()
+        for _ in range(args.steps):
+            p, d, n = api_request()
+            assert n == args.decode, n
+            api_pre.append(p)
+            api_dec.append(d)
         barrier()
         wall = time.time() - w0
         bd_ms = batch_decode_phase(64) if bdec > 0 else None
@@ -156,12 +187,18 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    pre = max_over_ranks(sum(pre_ms) / len(pre_ms))
-    dec = max_over_ranks(sum(dec_ms) / len(dec_ms))
+    mean = lambda v: sum(v) / len(v)
+    pre = max_over_ranks(mean(pre_ms))
+    dec = max_over_ranks(mean(dec_ms))
+    e_pre = max_over_ranks(mean(api_pre))
+    e_dec = max_over_ranks(mean(api_dec))
     wall_step = max_over_ranks(wall / args.steps * 1e3)
     prefill_tps = args.prompt / (pre / 1e3)
     decode_tps = (args.decode - 1) / (dec / 1e3)
     if rank == 0:
+        model = "Qwen3.8-27B-FP8-shaped hybrid (64L, hidden 5120, 48 GDN + 16 gated GQA, vocab 151936)"
+        if args.tiny or args.layers != 64:
+            model = f"DEBUG {cfg.num_hidden_layers} layers hidden {cfg.hidden_size}"
         rec = {
             "metric": "prefill_tok_s", "value": round(prefill_tps, 1), "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(pre + dec, 3),
@@ -171,25 +208,28 @@ def main() -> None:
             "prefill_ms": round(pre, 3), "decode_tok_s": round(decode_tps, 2),
             "decode_ms_per_token": round(dec / (args.decode - 1), 4),
             "decode_vs_baseline": round(decode_tps / PUBLISHED_DECODE_TPS, 2),
-            "config": {"model": "Qwen3.8-27B-FP8-shaped hybrid (64L, hidden 5120, 48 GDN + 16 gated GQA, vocab 151936)"
-                       if args.layers == 64 else f"DEBUG {args.layers} layers",
-                       "global_batch": 1, "seq_len": args.prompt, "decode_tokens": args.decode,
+            "config": {"model": model, "global_batch": 1, "seq_len": args.prompt, "decode_tokens": args.decode,
                        "parallelism": f"tp{world}", "weights": "fp8_e4m3_block128", "kv_cache": "bf16 paged (block 64)",
                        "l2_policy": "inputs larger than L2: every step streams the full weight set (>= 3 GB/rank)"},
-            "e2e": {"value": round(args.prompt / (pre / 1e3), 1), "unit": "tok/s",
-                    "what": "QwenHybridRuntime.prefill incl. H2D of prompt ids from pinned memory and D2H of the next token",
-                    "h2d_bytes_per_step": int(prompt_host.numel() * 4), "d2h_bytes_per_step": 4 * args.decode,
-                    "wall_ms_per_step": round(wall_step, 3)},
+            "e2e": {"value": round(args.prompt / (e_pre / 1e3), 1), "unit": "tok/s",
+                    "decode_tok_s": round((args.decode - 1) / (e_dec / 1e3), 2),
+                    "what": "pocketllm.LLM.generate on host token ids: list -> pinned tensor -> H2D inside the call, "
+                            "every generated token read back (D2H) before the next decode step; host clock",
+                    "h2d_bytes_per_step": int(prompt_host.numel() * 4 + (args.decode - 1) * 4),
+                    "d2h_bytes_per_step": 4 * args.decode, "wall_ms_per_step": round(wall_step, 3)},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
         if bd_ms is not None:
             bd = max_over_ranks(bd_ms)
             rec["decode_batch"] = {"batch": bdec, "ms_per_step": round(bd, 4), "tok_s": round(bdec / (bd / 1e3), 1)}
+        if comm is not None:
+            rec["fused_collective_calls"] = int(comm.fused_calls)
         print(json.dumps(rec), flush=True)
     elif bd_ms is not None:
         max_over_ranks(bd_ms)
     if world > 1:
+        comm.close()
         dist.barrier()
         dist.destroy_process_group()
 

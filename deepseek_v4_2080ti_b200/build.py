@@ -9,6 +9,7 @@ repository carries them:
   rebuilds in seconds).
 * ``lib/libb200_core.so`` + ``pocketllm_cpp`` pybind module - the C++ runtime
   (block pool/table, scheduler, command channel, readers, tokenizer, sampler).
+* ``lib/libb200_cpu.so`` - AVX2 multi-threaded host kernels (FP4 routed experts on the CPU).
 * ``bin/pocketllm_engine`` - the native executable.
 
 The reference builds its native plane with CMake for sm_75
@@ -132,9 +133,27 @@ def build_core(jobs: int | None = None) -> dict[str, Path]:
     return products
 
 
+def build_cpu() -> Path | None:
+    """AVX2 multi-threaded host kernels (csrc/cpu): the CPU oracle path for FP4 routed experts."""
+    OBJ.mkdir(exist_ok=True)
+    LIB.mkdir(exist_ok=True)
+    srcs = sorted((CSRC / "cpu").glob("*.cpp"))
+    if not srcs:
+        return None
+    flags = ["-O3", "-mavx2", "-mfma"]
+    objs = [_compile_cpp(s, flags, tag=".cpu") for s in srcs]
+    out = LIB / "libb200_cpu.so"
+    if (not out.exists()) or any(o.stat().st_mtime > out.stat().st_mtime for o in objs):
+        _run([CXX, "-shared", "-o", str(out), *map(str, objs), "-pthread"])
+    return out
+
+
 def build_all() -> dict[str, Path]:
     out = {"kernels": build_kernels()}
     out.update(build_core())
+    cpu = build_cpu()
+    if cpu is not None:
+        out["cpu"] = cpu
     return out
 
 

@@ -11,6 +11,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include "ops.h"
+#include "launch.h"
 
 namespace {
 
@@ -36,6 +37,8 @@ __global__ void __launch_bounds__(THREADS)
 gqa_decode_kernel(DecodeParams p) {
   __shared__ float s_m[NSTATE][G], s_l[NSTATE][G];
   __shared__ float s_o[NSTATE][G][D];
+  b200::pdl_grid_trigger();
+  b200::pdl_grid_wait();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int half = lane >> 4, dl = lane & 15;
@@ -140,6 +143,8 @@ gqa_decode_kernel(DecodeParams p) {
 
 __global__ void gqa_decode_merge_kernel(const float* __restrict__ partial, int splits,
                                         const __nv_bfloat16* __restrict__ gate, __nv_bfloat16* __restrict__ out) {
+  b200::pdl_grid_trigger();
+  b200::pdl_grid_wait();
   const size_t bh = blockIdx.x;  // b * Hq + hq
   const int d = threadIdx.x;
   const float* base = partial + bh * splits * (D + 2);
@@ -185,17 +190,20 @@ extern "C" int b200_gqa_decode(const void* q, const void* k_cache, const void* v
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   if (splits > 1 && !workspace) return -6;
   dim3 grid(splits, n_kv_heads, batch);
+  cudaError_t e = cudaSuccess;
   switch (G) {
-    case 1: gqa_decode_kernel<1><<<grid, THREADS, 0, stream>>>(p); break;
-    case 2: gqa_decode_kernel<2><<<grid, THREADS, 0, stream>>>(p); break;
-    case 3: gqa_decode_kernel<3><<<grid, THREADS, 0, stream>>>(p); break;
-    case 4: gqa_decode_kernel<4><<<grid, THREADS, 0, stream>>>(p); break;
-    case 5: gqa_decode_kernel<5><<<grid, THREADS, 0, stream>>>(p); break;
-    case 6: gqa_decode_kernel<6><<<grid, THREADS, 0, stream>>>(p); break;
-    case 8: gqa_decode_kernel<8><<<grid, THREADS, 0, stream>>>(p); break;
+    case 1: e = b200::launch_pdl(gqa_decode_kernel<1>, grid, dim3(THREADS), 0, stream, p); break;
+    case 2: e = b200::launch_pdl(gqa_decode_kernel<2>, grid, dim3(THREADS), 0, stream, p); break;
+    case 3: e = b200::launch_pdl(gqa_decode_kernel<3>, grid, dim3(THREADS), 0, stream, p); break;
+    case 4: e = b200::launch_pdl(gqa_decode_kernel<4>, grid, dim3(THREADS), 0, stream, p); break;
+    case 5: e = b200::launch_pdl(gqa_decode_kernel<5>, grid, dim3(THREADS), 0, stream, p); break;
+    case 6: e = b200::launch_pdl(gqa_decode_kernel<6>, grid, dim3(THREADS), 0, stream, p); break;
+    case 8: e = b200::launch_pdl(gqa_decode_kernel<8>, grid, dim3(THREADS), 0, stream, p); break;
     default: return -6;
   }
+  if (e != cudaSuccess) return (int)e;
   if (splits > 1)
-    gqa_decode_merge_kernel<<<batch * n_q_heads, D, 0, stream>>>(workspace, splits, p.gate, p.out);
-  return (int)cudaGetLastError();
+    e = b200::launch_pdl(gqa_decode_merge_kernel, dim3(batch * n_q_heads), dim3(D), 0, stream,
+                         (const float*)workspace, splits, p.gate, p.out);
+  return (int)e;
 }

@@ -15,6 +15,7 @@
 #include <cuda_fp8.h>
 #include <stdint.h>
 #include "ops.h"
+#include "launch.h"
 
 namespace {
 
@@ -73,29 +74,41 @@ __device__ __forceinline__ float conv_step(const GdnDecodeParams& p, __nv_bfloat
   return bf16_round(silu_f(acc));
 }
 
-// grid (Hk, B); block = 128 * (Hv / Hk) threads: group v (128 threads) serves value head kh*R + v, thread j of a
-// group owns state column j.  The q/k channels of key head kh are convolved once, by group 0.
-template <int KW, int R>
-__global__ void __launch_bounds__(128 * R)
+// grid (Hk, B); block = 128 * R * RG threads (R = Hv / Hk value heads per key head, RG row groups).
+// Thread (grp, rg, j) owns rows [rg*128/RG, (rg+1)*128/RG) of state column j of value head kh*R + grp; the row
+// groups cut the serial length of the recurrence per thread, their partial dot products meet in shared memory.
+// The q/k channels of key head kh are convolved once, by the threads with grp == 0 and rg == 0.
+template <int KW, int R, int RG>
+__global__ void __launch_bounds__(128 * R * RG)
 gdn_decode_fused_kernel(GdnDecodeParams p) {
+  constexpr int ROWS = DK / RG;
+  constexpr int WPH = 4 * RG;              // warps per value head
   __shared__ float sq[DK], sk[DK];
-  __shared__ float red[4 * R * 2 + 8];
+  __shared__ float s_v[R][DV];
+  __shared__ float s_part[R][RG][DV];
+  __shared__ float red_ab[R][WPH][2];
+  __shared__ float red_qk[8];
+  __shared__ float red_o[R][4];
   __shared__ float s_gate[R][2];
+  b200::pdl_grid_trigger();
+  b200::pdl_grid_wait();
   const int kh = blockIdx.x, b = blockIdx.y;
-  const int grp = threadIdx.x >> 7, j = threadIdx.x & 127;
+  const int j = threadIdx.x & 127;
+  const int rg = (threadIdx.x >> 7) % RG;
+  const int grp = threadIdx.x / (128 * RG);
   const int h = kh * R + grp;
   const int kd = p.Hk * DK, vd = p.Hv * DV, C = 2 * kd + vd;
   const int slot = p.slot_ids ? p.slot_ids[b] : b;
   __nv_bfloat16* tail = p.tails + (size_t)slot * p.tail_stride;
   const __nv_bfloat16* row = p.proj + (size_t)b * p.ldp;
 
-  // ---- a/b projections of this value head: two dot products of length hidden over the group's 128 threads
+  // ---- a/b projections of this value head: two dot products of length hidden over the head's 128*RG threads
   {
     const __nv_bfloat16* xr = p.x + (size_t)b * p.hidden;
     const __nv_bfloat16* wa = p.w_ab + (size_t)h * p.hidden;
     const __nv_bfloat16* wb = p.w_ab + (size_t)(p.Hv + h) * p.hidden;
     float da = 0.f, db = 0.f;
-    for (int i = j * 8; i < p.hidden; i += 128 * 8) {
+    for (int i = (rg * 128 + j) * 8; i < p.hidden; i += 128 * RG * 8) {
       const uint4 xv = *reinterpret_cast<const uint4*>(xr + i);
       const uint4 av = *reinterpret_cast<const uint4*>(wa + i);
       const uint4 bv = *reinterpret_cast<const uint4*>(wb + i);
@@ -111,70 +124,90 @@ gdn_decode_fused_kernel(GdnDecodeParams p) {
     }
     da = warp_sum(da);
     db = warp_sum(db);
-    const int wg = j >> 5;   // warp within the group
     if ((j & 31) == 0) {
-      red[(grp * 4 + wg) * 2] = da;
-      red[(grp * 4 + wg) * 2 + 1] = db;
+      red_ab[grp][rg * 4 + (j >> 5)][0] = da;
+      red_ab[grp][rg * 4 + (j >> 5)][1] = db;
     }
   }
-  // ---- conv step: q/k channels by group 0, v channel by every group
+  // ---- conv step (row group 0 only): q/k channels by value head 0 of the block, v channel by every head
   float qv = 0.f, kv = 0.f;
-  if (grp == 0) {
-    qv = conv_step<KW>(p, tail, C, kh * DK + j, __bfloat162float(row[kh * DK + j]), true);
-    kv = conv_step<KW>(p, tail, C, kd + kh * DK + j, __bfloat162float(row[kd + kh * DK + j]), true);
-    float qs = warp_sum(qv * qv), ks = warp_sum(kv * kv);
-    if ((j & 31) == 0) {
-      red[8 * R + (j >> 5)] = qs;
-      red[8 * R + 4 + (j >> 5)] = ks;
+  if (rg == 0) {
+    if (grp == 0) {
+      qv = conv_step<KW>(p, tail, C, kh * DK + j, __bfloat162float(row[kh * DK + j]), true);
+      kv = conv_step<KW>(p, tail, C, kd + kh * DK + j, __bfloat162float(row[kd + kh * DK + j]), true);
+      const float qs = warp_sum(qv * qv), ks = warp_sum(kv * kv);
+      if ((j & 31) == 0) {
+        red_qk[j >> 5] = qs;
+        red_qk[4 + (j >> 5)] = ks;
+      }
     }
+    s_v[grp][j] = conv_step<KW>(p, tail, C, 2 * kd + h * DV + j, __bfloat162float(row[2 * kd + h * DV + j]), true);
   }
-  const float vv = conv_step<KW>(p, tail, C, 2 * kd + h * DV + j, __bfloat162float(row[2 * kd + h * DV + j]), true);
   __syncthreads();
-  if (j == 0) {
+  if (rg == 0 && j == 0) {
+    float a = 0.f, bb = 0.f;
+#pragma unroll
+    for (int w = 0; w < WPH; ++w) {
+      a += red_ab[grp][w][0];
+      bb += red_ab[grp][w][1];
+    }
     // the unfused path rounds the a/b projection outputs to bf16 before the gate math
-    const float a = bf16_round(red[(grp * 4) * 2] + red[(grp * 4 + 1) * 2] + red[(grp * 4 + 2) * 2] + red[(grp * 4 + 3) * 2]);
-    const float bb = bf16_round(red[(grp * 4) * 2 + 1] + red[(grp * 4 + 1) * 2 + 1] + red[(grp * 4 + 2) * 2 + 1] +
-                                red[(grp * 4 + 3) * 2 + 1]);
+    a = bf16_round(a);
+    bb = bf16_round(bb);
     const float av = a + p.dt_bias[h];
     const float sp = av > 20.f ? av : log1pf(expf(av));
     s_gate[grp][0] = __expf(-expf(p.a_log[h]) * sp);   // decay = exp(g)
     s_gate[grp][1] = sigmoid_f(bb);
   }
-  if (grp == 0) {
-    const float qn = rsqrtf(red[8 * R] + red[8 * R + 1] + red[8 * R + 2] + red[8 * R + 3] + 1e-6f);
-    const float kn = rsqrtf(red[8 * R + 4] + red[8 * R + 5] + red[8 * R + 6] + red[8 * R + 7] + 1e-6f);
+  if (grp == 0 && rg == 0) {
+    const float qn = rsqrtf(red_qk[0] + red_qk[1] + red_qk[2] + red_qk[3] + 1e-6f);
+    const float kn = rsqrtf(red_qk[4] + red_qk[5] + red_qk[6] + red_qk[7] + 1e-6f);
     sq[j] = qv * qn * p.q_scale;
     sk[j] = kv * kn;
   }
   __syncthreads();
-  // ---- gated delta rule on state column j of head h
-  float* S = p.states + (size_t)slot * p.state_stride + (size_t)h * DK * DV;
+  // ---- gated delta rule on rows [rg*ROWS, (rg+1)*ROWS) of state column j of head h
+  float* S = p.states + (size_t)slot * p.state_stride + (size_t)h * DK * DV + (size_t)rg * ROWS * DV;
   const float decay = s_gate[grp][0], bt = s_gate[grp][1];
-  float col[DK];
+  float col[ROWS];
+  float part = 0.f;
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+    col[i] = S[(size_t)i * DV + j] * decay;
+    part += col[i] * sk[rg * ROWS + i];
+  }
+  s_part[grp][rg][j] = part;
+  __syncthreads();
   float kv_mem = 0.f;
 #pragma unroll
-  for (int i = 0; i < DK; ++i) {
-    col[i] = S[(size_t)i * DV + j] * decay;
-    kv_mem += col[i] * sk[i];
-  }
-  const float delta = (vv - kv_mem) * bt;
-  float o = 0.f;
+  for (int g2 = 0; g2 < RG; ++g2) kv_mem += s_part[grp][g2][j];
+  const float delta = (s_v[grp][j] - kv_mem) * bt;
+  __syncthreads();   // s_part is reused for the read-out partials
+  part = 0.f;
 #pragma unroll
-  for (int i = 0; i < DK; ++i) {
-    col[i] += sk[i] * delta;
+  for (int i = 0; i < ROWS; ++i) {
+    col[i] += sk[rg * ROWS + i] * delta;
     S[(size_t)i * DV + j] = col[i];
-    o += col[i] * sq[i];
+    part += col[i] * sq[rg * ROWS + i];
   }
-  // ---- per-head gated RMSNorm (the unfused path stores o as bf16 first)
-  o = bf16_round(o);
-  float ss = warp_sum(o * o);
-  __syncthreads();   // red[] is reused
-  if ((j & 31) == 0) red[grp * 4 + (j >> 5)] = ss;
+  s_part[grp][rg][j] = part;
   __syncthreads();
-  const float inv = rsqrtf((red[grp * 4] + red[grp * 4 + 1] + red[grp * 4 + 2] + red[grp * 4 + 3]) / (float)DV + p.eps);
-  const float z = __bfloat162float(row[2 * kd + vd + h * DV + j]);
-  const float y = o * inv * __bfloat162float(p.gamma[j]) * silu_f(z);
-  p.out[((size_t)b * p.Hv + h) * DV + j] = __float2bfloat16(y);
+  // ---- per-head gated RMSNorm by row group 0 (the unfused path stores o as bf16 first)
+  float o = 0.f;
+  if (rg == 0) {
+#pragma unroll
+    for (int g2 = 0; g2 < RG; ++g2) o += s_part[grp][g2][j];
+    o = bf16_round(o);
+    const float ss = warp_sum(o * o);
+    if ((j & 31) == 0) red_o[grp][j >> 5] = ss;
+  }
+  __syncthreads();
+  if (rg == 0) {
+    const float inv = rsqrtf((red_o[grp][0] + red_o[grp][1] + red_o[grp][2] + red_o[grp][3]) / (float)DV + p.eps);
+    const float z = __bfloat162float(row[2 * kd + vd + h * DV + j]);
+    const float y = o * inv * __bfloat162float(p.gamma[j]) * silu_f(z);
+    p.out[((size_t)b * p.Hv + h) * DV + j] = __float2bfloat16(y);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -237,6 +270,8 @@ __global__ void rmsnorm_split_kernel(__nv_bfloat16* __restrict__ x, const __nv_b
                                      uint8_t* __restrict__ xq, float* __restrict__ inv_c, int cols, float eps,
                                      int unit_offset) {
   __shared__ float red[32];
+  b200::pdl_grid_trigger();   // the GEMM that follows may start streaming its weights now
+  b200::pdl_grid_wait();
   const size_t row = blockIdx.x;
   float cache[MAXV][4];
   float ss = 0.f;
@@ -305,6 +340,8 @@ template <int MAXV, int TERMS>
 __global__ void silu_mul_split_kernel(const __nv_bfloat16* __restrict__ gu, int inter, uint8_t* __restrict__ xq,
                                       float* __restrict__ inv_c) {
   __shared__ float red[32];
+  b200::pdl_grid_trigger();   // the GEMM that follows may start streaming its weights now
+  b200::pdl_grid_wait();
   const size_t row = blockIdx.x;
   const __nv_bfloat16* g = gu + row * 2 * (size_t)inter;
   const __nv_bfloat16* u = g + inter;
@@ -376,12 +413,11 @@ int b200_gdn_decode_fused(const void* proj, int ldp, const void* x, int hidden, 
   p.q_scale = rsqrtf((float)DK);
   const dim3 grid(Hk, B);
   switch (Hv / Hk) {
-    case 1: gdn_decode_fused_kernel<4, 1><<<grid, 128, 0, stream>>>(p); break;
-    case 2: gdn_decode_fused_kernel<4, 2><<<grid, 256, 0, stream>>>(p); break;
-    case 4: gdn_decode_fused_kernel<4, 4><<<grid, 512, 0, stream>>>(p); break;
+    case 1: return (int)b200::launch_pdl(gdn_decode_fused_kernel<4, 1, 4>, grid, dim3(512), 0, stream, p);
+    case 2: return (int)b200::launch_pdl(gdn_decode_fused_kernel<4, 2, 4>, grid, dim3(1024), 0, stream, p);
+    case 4: return (int)b200::launch_pdl(gdn_decode_fused_kernel<4, 4, 2>, grid, dim3(1024), 0, stream, p);
     default: return -6;
   }
-  return (int)cudaGetLastError();
 }
 
 // x[T, cols] (+= delta, written back when delta is given) -> out = rmsnorm(x) * gamma (bf16, optional) and the
@@ -395,9 +431,11 @@ int b200_rmsnorm_split(void* x, const void* delta, const void* gamma, void* out,
   auto* op = reinterpret_cast<__nv_bfloat16*>(out);
   auto* qp = reinterpret_cast<uint8_t*>(xq);
   const int threads = cols <= 4096 ? 256 : 512;
-  if (terms == 3) rmsnorm_split_kernel<8, 3><<<T, threads, 0, stream>>>(xp, dp, gp, op, qp, inv_c, cols, eps, unit_offset);
-  else rmsnorm_split_kernel<8, 2><<<T, threads, 0, stream>>>(xp, dp, gp, op, qp, inv_c, cols, eps, unit_offset);
-  return (int)cudaGetLastError();
+  if (terms == 3)
+    return (int)b200::launch_pdl(rmsnorm_split_kernel<8, 3>, dim3(T), dim3(threads), 0, stream, xp, dp, gp, op, qp, inv_c,
+                                 cols, eps, unit_offset);
+  return (int)b200::launch_pdl(rmsnorm_split_kernel<8, 2>, dim3(T), dim3(threads), 0, stream, xp, dp, gp, op, qp, inv_c,
+                               cols, eps, unit_offset);
 }
 
 // gu[T, 2*inter] (gate | up) -> E4M3 terms of bf16(silu(gate) * up): xq [T*terms, inter], inv_c [T].
@@ -405,9 +443,8 @@ int b200_silu_mul_split(const void* gu, void* xq, float* inv_c, int T, int inter
   if (T <= 0 || inter <= 0 || inter % 4 != 0 || inter > 4 * 8 * 1024 || (terms != 2 && terms != 3)) return -6;
   auto* gp = reinterpret_cast<const __nv_bfloat16*>(gu);
   auto* qp = reinterpret_cast<uint8_t*>(xq);
-  if (terms == 3) silu_mul_split_kernel<8, 3><<<T, 1024, 0, stream>>>(gp, inter, qp, inv_c);
-  else silu_mul_split_kernel<8, 2><<<T, 1024, 0, stream>>>(gp, inter, qp, inv_c);
-  return (int)cudaGetLastError();
+  if (terms == 3) return (int)b200::launch_pdl(silu_mul_split_kernel<8, 3>, dim3(T), dim3(1024), 0, stream, gp, inter, qp, inv_c);
+  return (int)b200::launch_pdl(silu_mul_split_kernel<8, 2>, dim3(T), dim3(1024), 0, stream, gp, inter, qp, inv_c);
 }
 
 }  // extern "C"

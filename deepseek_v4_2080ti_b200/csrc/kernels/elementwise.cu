@@ -383,6 +383,63 @@ __global__ void argmax_kernel(const T* __restrict__ logits, int ld, int n, int i
   }
 }
 
+// Two-stage variant for few rows over a wide vocabulary: grid (chunks, rows) writes one (value, index) pair
+// per chunk, a second small launch reduces the pairs.  A single block per row would leave 147 SMs idle.
+constexpr int kArgmaxChunks = 64;
+constexpr int kArgmaxMaxRows = 64;
+__device__ float g_argmax_val[kArgmaxMaxRows * kArgmaxChunks];
+__device__ int g_argmax_idx[kArgmaxMaxRows * kArgmaxChunks];
+
+template <typename T>
+__global__ void argmax_chunk_kernel(const T* __restrict__ logits, int ld, int n, int chunk) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  const T* row = logits + (size_t)blockIdx.y * ld;
+  const int lo = blockIdx.x * chunk, hi = min(n, lo + chunk);
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = (float)row[i];
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+    g_argmax_val[blockIdx.y * kArgmaxChunks + blockIdx.x] = best;
+    g_argmax_idx[blockIdx.y * kArgmaxChunks + blockIdx.x] = bi;
+  }
+}
+
+__global__ void argmax_final_kernel(int chunks, int index_offset, int* __restrict__ out_idx,
+                                    float* __restrict__ out_val) {
+  const int r = blockIdx.x, lane = threadIdx.x;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = lane; c < chunks; c += 32) {
+    const float v = g_argmax_val[r * kArgmaxChunks + c];
+    const int i = g_argmax_idx[r * kArgmaxChunks + c];
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if (lane == 0) {
+    out_idx[r] = bi + index_offset;
+    if (out_val) out_val[r] = best;
+  }
+}
+
 inline int rc() { return (int)cudaGetLastError(); }
 
 }  // namespace
@@ -500,6 +557,15 @@ int b200_gdn_gates(const void* ab, int ld, int a_off, int b_off, const float* a_
 
 int b200_argmax(const void* logits, int is_f32, int ld, int n, int rows, int index_offset, int* out_idx,
                 float* out_val, cudaStream_t stream) {
+  if (rows <= kArgmaxMaxRows && n >= 8192) {
+    const int chunk = (n + kArgmaxChunks - 1) / kArgmaxChunks;
+    const int chunks = (n + chunk - 1) / chunk;
+    const dim3 grid(chunks, rows);
+    if (is_f32) argmax_chunk_kernel<float><<<grid, 256, 0, stream>>>(reinterpret_cast<const float*>(logits), ld, n, chunk);
+    else argmax_chunk_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(logits), ld, n, chunk);
+    argmax_final_kernel<<<rows, 32, 0, stream>>>(chunks, index_offset, out_idx, out_val);
+    return rc();
+  }
   if (is_f32)
     argmax_kernel<float><<<rows, 1024, 0, stream>>>(reinterpret_cast<const float*>(logits), ld, n, index_offset,
                                                     out_idx, out_val);

@@ -26,6 +26,7 @@
 #include "../ptx/sm100.cuh"
 #include "tma_host.h"
 #include "ops.h"
+#include "launch.h"
 
 namespace b200 {
 namespace w8s {
@@ -112,6 +113,7 @@ gemm_w8a8s_kernel(const __grid_constant__ CUtensorMap tmX, Params p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();   // the next kernel may be scheduled; it waits for this grid before touching memory
 
   const int total_work = p.m_tiles * p.splits;
   const int per_split = (p.kblk_total + p.splits - 1) / p.splits;
@@ -119,6 +121,23 @@ gemm_w8a8s_kernel(const __grid_constant__ CUtensorMap tmX, Params p) {
   if (warp == 4) {
     // ------------------------------------------------------------ copy producer
     if (lane == 0) {
+      // The weights do not depend on the previous kernel of the stream, the activations do.  When launched
+      // as a programmatic dependent the producer therefore fills the ring with weight tiles first (up to S
+      // blocks, ~190 KB per SM), waits for the predecessor, and only then fetches the activation tiles.
+      const int pre = [&] {
+        int n = 0;
+        for (int w = blockIdx.x; w < total_work && n < S; w += gridDim.x) {
+          const int m_tile = w % p.m_tiles, split = w / p.m_tiles;
+          const int c0 = split * per_split, c1 = min(p.kblk_total, c0 + per_split);
+          for (int c = c0; c < c1 && n < S; ++c, ++n) {
+            mbar_expect_tx(&full[n], 2 * (W_BYTES + L::X_BYTES));
+            bulk_load(sW + n * 2 * W_BYTES, p.w_tiled + ((size_t)m_tile * p.kblk_total + c) * (2 * W_BYTES),
+                      2 * W_BYTES, &full[n]);
+          }
+        }
+        return n;
+      }();
+      pdl_wait();
       uint32_t blk = 0;
       for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
         const int m_tile = w % p.m_tiles;
@@ -128,14 +147,16 @@ gemm_w8a8s_kernel(const __grid_constant__ CUtensorMap tmX, Params p) {
         const uint8_t* wsrc = p.w_tiled + ((size_t)m_tile * p.kblk_total + c0) * (2 * W_BYTES);
         for (int c = c0; c < c1; ++c, ++blk, wsrc += 2 * W_BYTES) {
           const int b = blk % S;
-          if (!mbar_wait(&done[b], ((blk / S) & 1) ^ 1)) {
-            atomicExch(p.status, ERR_WAIT_STAGE);
-            *abort_flag = 1;
-            break;
+          if ((int)blk >= pre) {
+            if (!mbar_wait(&done[b], ((blk / S) & 1) ^ 1)) {
+              atomicExch(p.status, ERR_WAIT_STAGE);
+              *abort_flag = 1;
+              break;
+            }
+            mbar_expect_tx(&full[b], 2 * (W_BYTES + L::X_BYTES));
+            // the two 64-byte-wide weight tiles of a K block are adjacent in memory: one 16 KB copy
+            bulk_load(sW + b * 2 * W_BYTES, wsrc, 2 * W_BYTES, &full[b]);
           }
-          mbar_expect_tx(&full[b], 2 * (W_BYTES + L::X_BYTES));
-          // the two 64-byte-wide weight tiles of a K block are adjacent in memory: one 16 KB copy
-          bulk_load(sW + b * 2 * W_BYTES, wsrc, 2 * W_BYTES, &full[b]);
           tma_load_2d(sX + (2 * b) * L::X_BYTES, &tmX, &full[b], c * 128, 0);
           tma_load_2d(sX + (2 * b + 1) * L::X_BYTES, &tmX, &full[b], c * 128 + 64, 0);
         }
@@ -183,6 +204,7 @@ gemm_w8a8s_kernel(const __grid_constant__ CUtensorMap tmX, Params p) {
     // ---------------------------------------------------------------- epilogue
     const int row = warp * 32 + lane;
     const bool sync_mode = p.splits > 1;
+    pdl_wait();   // everything this role reads (inv_c, residual) or writes belongs after the previous kernel
     uint32_t blk = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
       if (sync_mode) {
@@ -305,6 +327,8 @@ template <int TERMS>
 __global__ void __launch_bounds__(256)
 act_split_e4m3_kernel(const __nv_bfloat16* __restrict__ x, int K, uint8_t* __restrict__ xq,
                       float* __restrict__ inv_c) {
+  pdl_launch_dependents();   // the GEMM that follows may start streaming its weights now
+  pdl_wait();
   const int t = blockIdx.x;
   const __nv_bfloat16* xr = x + (size_t)t * K;
   __shared__ float red[8];
@@ -355,8 +379,18 @@ static int launch(const CUtensorMap& tmX, const Params& p, cudaStream_t stream) 
   }
   const int total = p.m_tiles * p.splits;
   const int grid = total < sm_count() ? total : sm_count();
-  gemm_w8a8s_kernel<BN, TERMS><<<grid, THREADS, L::TOTAL, stream>>>(tmX, p);
-  return (int)cudaGetLastError();
+  // programmatic dependent launch: start while the kernel that produces the activations is still running
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = L::TOTAL;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, gemm_w8a8s_kernel<BN, TERMS>, tmX, p);
 }
 
 }  // namespace w8s
@@ -380,9 +414,9 @@ extern "C" int b200_act_split_e4m3(const void* x_bf16, int T, int K, int terms, 
                                    cudaStream_t stream) {
   if (T <= 0 || K <= 0 || (K % 4) != 0 || (terms != 2 && terms != 3)) return -ERR_BAD_ARG;
   const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(x_bf16);
-  if (terms == 3) w8s::act_split_e4m3_kernel<3><<<T, 256, 0, stream>>>(x, K, reinterpret_cast<uint8_t*>(xq), inv_c);
-  else w8s::act_split_e4m3_kernel<2><<<T, 256, 0, stream>>>(x, K, reinterpret_cast<uint8_t*>(xq), inv_c);
-  return (int)cudaGetLastError();
+  if (terms == 3)
+    return (int)launch_pdl(w8s::act_split_e4m3_kernel<3>, dim3(T), dim3(256), 0, stream, x, K, reinterpret_cast<uint8_t*>(xq), inv_c);
+  return (int)launch_pdl(w8s::act_split_e4m3_kernel<2>, dim3(T), dim3(256), 0, stream, x, K, reinterpret_cast<uint8_t*>(xq), inv_c);
 }
 
 // Y = X W^T with pre-split activations (b200_act_split_e4m3 with the layout of b200_gemm_w8a8s_layout(T)).

@@ -30,6 +30,13 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute may
+// start while its predecessor in the stream is still running; pdl_wait() blocks the calling thread until the
+// predecessor grid has completed and its writes are visible, pdl_launch_dependents() lets the successor start
+// early.  Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Error codes written to the kernel's status word (0 = ok).
 enum : int {
   ERR_NONE = 0,

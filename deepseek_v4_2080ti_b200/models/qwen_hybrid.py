@@ -429,13 +429,20 @@ class QwenHybridRuntime:
             self.block_table[st.slot].copy_(self._bt_host[st.slot], non_blocking=True)
 
     # ---- layer bodies
+    def _row_parallel(self, x: torch.Tensor, w: PackedLinear) -> torch.Tensor:
+        """Row-parallel projection: this rank's K-shard GEMM + sum over ranks.  With a peer-memory communicator the
+        reduction happens in the GEMM epilogue (tile by tile over NVLink); otherwise GEMM then all-reduce."""
+        fused = getattr(self.comm, "linear_allreduce", None)
+        if fused is not None and self.comm.world > 1:
+            return fused(x, w)
+        return self.comm.all_reduce(gemm.linear(x, w))
+
     def _mlp(self, lw: LayerWeights, h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
         x = basic.add_rmsnorm(h, delta, lw.post_ln, cfg.rms_norm_eps, True)
         gu = gemm.linear(x, lw.gate_up)
         act = basic.silu_mul(gu)
-        out = gemm.linear(act, lw.down)
-        return self.comm.all_reduce(out)
+        return self._row_parallel(act, lw.down)
 
     def _linear_attn(self, li: int, lw: LayerWeights, x: torch.Tensor, t: int, slots_t: torch.Tensor | None,
                      slot: int | None) -> torch.Tensor:
@@ -453,8 +460,7 @@ class QwenHybridRuntime:
             core = gdn.step(self.states[:, idx], slots_t, mixed, 0, self.kd, 2 * self.kd, g, beta, self.hv_lin, self.hk_lin)
         z = proj[:, cw:].unflatten(1, (self.hv_lin, 128))
         y = basic.gated_rmsnorm(core, z, lw.gdn_norm, cfg.rms_norm_eps)
-        out = gemm.linear(y.view(t, self.vd), lw.out)
-        return self.comm.all_reduce(out)
+        return self._row_parallel(y.view(t, self.vd), lw.out)
 
     def _full_attn(self, li: int, lw: LayerWeights, x: torch.Tensor, t: int, positions, kv_slots, meta) -> torch.Tensor:
         cfg = self.cfg
@@ -472,8 +478,7 @@ class QwenHybridRuntime:
         else:
             o = attention.decode(q, kc, vc, meta["block_table"], meta["kv_len"], gate=gate,
                                  max_kv_len=meta["max_kv_len"])
-        out = gemm.linear(o.view(t, self.hq * 128), lw.out)
-        return self.comm.all_reduce(out)
+        return self._row_parallel(o.view(t, self.hq * 128), lw.out)
 
     def _embed(self, ids: torch.Tensor) -> torch.Tensor:
         h = basic.embedding(ids, self.w.embed, self.w.vocab_lo, self.w.vocab_hi)

@@ -59,3 +59,151 @@ class TPComm:
     def barrier(self) -> None:
         if self.world > 1:
             dist.barrier(group=self.group)
+
+
+# ----------------------------------------------------------------------------- peer-memory communicator
+import ctypes  # noqa: E402
+
+from ..ops import _lib  # noqa: E402
+
+MAX_RANKS = 8
+
+
+class _CommStruct(ctypes.Structure):
+    """Mirror of ``B200Comm`` (csrc/comm/comm.h)."""
+    _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int), ("slot_elems", ctypes.c_ulonglong),
+                ("flags", ctypes.c_void_p * MAX_RANKS), ("ctrl", ctypes.c_void_p),
+                ("data", ctypes.c_void_p * MAX_RANKS)]
+
+
+class CollectiveTimeoutError(RuntimeError):
+    """A bounded device-side wait on a peer's flag expired (the peer is late, gone, or out of step)."""
+
+
+class PeerComm(TPComm):
+    """Tensor-parallel communicator over NVLink peer memory.
+
+    Every rank allocates one symmetric buffer (flags | control words | data slots), exports it with CUDA IPC
+    and maps every peer's buffer; collectives are then done by this package's kernels with plain peer stores
+    and loads (no NCCL on the hot path):
+
+    * ``all_reduce``           one-shot all-reduce for payloads up to ``slot_elems`` bf16 values
+    * ``argmax_merge``         (value, index) winners of the vocabulary shards
+    * ``linear_allreduce``     row-parallel GEMM whose epilogue pushes each finished tile to the peers and
+                               sums theirs (csrc/kernels/gemm_wdec.cu, ``ar_mode``)
+
+    Larger payloads and anything else fall back to the NCCL group.  Device waits are bounded
+    (``budget_ms``); on expiry the kernels set the status word and ``check()`` raises
+    ``CollectiveTimeoutError``.  The reference's counterpart is its CUDA-IPC one-shot all-reduce with NCCL
+    fallback, fixed at four ranks (src/models/deepseek_v4/runtime.py:206-268, 4211-4217).
+    """
+
+    def __init__(self, group=None, slot_elems: int = 1 << 20, budget_ms: float = 2000.0):
+        super().__init__(group)
+        assert self.world <= MAX_RANKS
+        self.slot_elems = int(slot_elems)
+        self.budget_ns = int(budget_ms * 1e6)
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        L = _lib.lib()
+        L.b200_comm_buffer_bytes.restype = ctypes.c_ulonglong
+        nbytes = L.b200_comm_buffer_bytes(ctypes.c_ulonglong(self.slot_elems))
+        base = ctypes.c_void_p()
+        rc = L.b200_comm_alloc(ctypes.c_ulonglong(nbytes), ctypes.byref(base))
+        if rc != 0:
+            raise RuntimeError(f"symmetric buffer allocation failed: CUDA error {rc}")
+        self._base = base
+        handle = ctypes.create_string_buffer(64)
+        rc = L.b200_comm_ipc_handle(base, handle)
+        if rc != 0:
+            raise RuntimeError(f"cudaIpcGetMemHandle failed: {rc}")
+        handles: list = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=self.group)
+        self._peers: list[ctypes.c_void_p] = []
+        bases = (ctypes.c_void_p * MAX_RANKS)()
+        for r in range(self.world):
+            if r == self.rank:
+                bases[r] = base.value
+                continue
+            p = ctypes.c_void_p()
+            rc = L.b200_comm_ipc_open(ctypes.c_char_p(handles[r]), ctypes.byref(p))
+            if rc != 0:
+                raise RuntimeError(f"cudaIpcOpenMemHandle(rank {r}) failed: {rc}")
+            self._peers.append(p)
+            bases[r] = p.value
+        self.c = _CommStruct()
+        rc = L.b200_comm_init(ctypes.byref(self.c), self.rank, self.world, bases, ctypes.c_ulonglong(self.slot_elems))
+        if rc != 0:
+            raise RuntimeError(f"comm init failed: {rc}")
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        self.fused_calls = 0
+
+    def _cref(self):
+        return ctypes.byref(self.c)
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return t
+        if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.numel() > self.slot_elems:
+            return super().all_reduce(t)
+        rc = _lib.lib().b200_allreduce_oneshot(self._cref(), _lib.ptr(t), ctypes.c_longlong(t.numel()),
+                                               _lib.ptr(_lib.status_word(t.device)), ctypes.c_ulonglong(self.budget_ns),
+                                               _lib.stream())
+        _lib.check(rc, "allreduce_oneshot")
+        self.fused_calls += 1
+        self.bytes_reduced += t.numel() * 2
+        return t
+
+    def argmax_merge(self, idx: torch.Tensor, val: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return idx
+        rows = idx.numel()
+        if rows * 4 > self.slot_elems:
+            return super().argmax_merge(idx, val)
+        out = torch.empty(rows, dtype=torch.int32, device=idx.device)
+        rc = _lib.lib().b200_argmax_merge(self._cref(), _lib.ptr(val.float().contiguous()),
+                                          _lib.ptr(idx.to(torch.int32).contiguous()), rows, _lib.ptr(out),
+                                          _lib.ptr(_lib.status_word(idx.device)), ctypes.c_ulonglong(self.budget_ns),
+                                          _lib.stream())
+        _lib.check(rc, "argmax_merge")
+        return out
+
+    def linear_allreduce(self, x: torch.Tensor, w, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``sum_r x_r @ w_r^T`` (+ residual): this rank's K-shard GEMM with the all-reduce done in its epilogue."""
+        from ..ops import gemm
+
+        t, k = x.shape
+        n = w.n
+        bn = gemm._bn(t)
+        tiles = ((n + 127) // 128) * ((t + bn - 1) // bn)
+        if self.world == 1 or t * n > self.slot_elems or tiles > 4096:
+            return self.all_reduce(gemm.linear(x, w, residual=None)) if residual is None else \
+                self.all_reduce(gemm.linear(x, w)).add_(residual)
+        out = torch.empty(t, n, dtype=torch.bfloat16, device=x.device)
+        rc = _lib.lib().b200_gemm_wdec_allreduce(w.wfmt, _lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(x),
+                                                 _lib.ptr(out), _lib.ptr(residual), t, n, k, self._cref(),
+                                                 ctypes.c_ulonglong(self.budget_ns),
+                                                 _lib.ptr(_lib.status_word(x.device)), _lib.stream())
+        _lib.check(rc, "gemm_wdec_allreduce")
+        self.fused_calls += 1
+        return out
+
+    def check(self) -> None:
+        try:
+            _lib.check_status(self.device)
+        except _lib.KernelError as e:
+            if "peer flag" in str(e):
+                raise CollectiveTimeoutError(str(e)) from e
+            raise
+
+    def close(self) -> None:
+        L = _lib.lib()
+        torch.cuda.synchronize()
+        if dist.is_initialized():
+            dist.barrier(group=self.group)
+        for p in self._peers:
+            L.b200_comm_ipc_close(p)
+        self._peers = []
+        if self._base is not None:
+            L.b200_comm_free(self._base)
+            self._base = None

@@ -1,0 +1,52 @@
+"""One eager decode step of the 27B-shaped hybrid model between cudaProfilerStart/Stop, for a per-kernel
+launch list:
+
+  ncu --profile-from-start off --metrics gpu__time_duration.sum --clock-control none --csv \\
+      --log-file launches.csv python -m deepseek_v4_2080ti_b200.utils.decode_profile --batch 1 --layers 8
+
+Without ncu it prints the CUDA-event time of the step (eager launches, so launch gaps are included)."""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--context", type=int, default=512)
+    a = ap.parse_args()
+    from ..models import qwen_hybrid as qh
+    from ..ops import _lib
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = qh.QwenHybridConfig(num_hidden_layers=a.layers)
+    w = qh.QwenHybridWeights(cfg, qh.synth_state(cfg, 0, dev), dev)
+    rt = qh.QwenHybridRuntime(cfg, w, max_slots=a.batch, max_context=a.context + 64)
+    gen = torch.Generator().manual_seed(1)
+    slots, cur = [], []
+    for _ in range(a.batch):
+        s = rt.allocate()
+        p = torch.randint(0, cfg.vocab_size, (a.context,), generator=gen, dtype=torch.int32).to(dev)
+        cur.append(rt.prefill(s, p))
+        slots.append(s)
+    tok = torch.cat(cur).to(torch.int32)
+    for _ in range(2):
+        tok = rt.decode(slots, tok, use_graph=False).to(torch.int32)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.cudart().cudaProfilerStart()
+    e0.record()
+    tok = rt.decode(slots, tok, use_graph=False).to(torch.int32)
+    e1.record()
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStop()
+    _lib.check_status()
+    print(json.dumps({"batch": a.batch, "layers": a.layers, "eager_step_ms": e0.elapsed_time(e1), "launches": rt.launches}))
+
+
+if __name__ == "__main__":
+    main()

@@ -94,3 +94,13 @@ def test_gdn_gates():
     wg, wb = basic.gdn_gates_ref(ab[:, :32], ab[:, 32:], a_log, dtb)
     _close(g, wg, 1e-3)
     _close(beta, wb, 1e-3)
+
+
+def test_argmax_two_stage_wide_vocabulary():
+    """Few rows over a wide vocabulary go through the chunked two-launch arg-max; ties resolve to the lowest index."""
+    torch.manual_seed(11)
+    logits = torch.randn(3, 151936, device="cuda")
+    logits[1, 70000] = logits[1, 140000] = 50.0
+    idx, val = basic.argmax(logits, 1000, True)
+    assert idx.tolist() == [int(logits[0].argmax()) + 1000, 71000, int(logits[2].argmax()) + 1000]
+    assert torch.equal(val, logits.max(-1).values)
