@@ -98,6 +98,7 @@ def test_gdn_gates():
 
 def test_argmax_two_stage_wide_vocabulary():
     """Few rows over a wide vocabulary go through the chunked two-launch arg-max; ties resolve to the lowest index."""
+    from deepseek_v4_2080ti_b200.ops import basic
     torch.manual_seed(11)
     logits = torch.randn(3, 151936, device="cuda")
     logits[1, 70000] = logits[1, 140000] = 50.0
