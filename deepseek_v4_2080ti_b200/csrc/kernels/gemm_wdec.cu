@@ -40,7 +40,13 @@ constexpr int DEC_WARP0 = 6;
 constexpr int NUM_DEC_WARPS = 8;
 constexpr int NUM_THREADS = (DEC_WARP0 + NUM_DEC_WARPS) * 32;  // 448
 
-enum WFormat : int { WF_BF16 = 0, WF_FP8_B128 = 1 };
+// WF_FP4: E2M1 nibbles (low nibble first) with one UE8M0 scale per 32 inputs, stored tile-major as
+// [m_tile][kb][128 rows x 32 code bytes | 128 rows x 2 scale bytes] (4352 bytes per stage).
+enum WFormat : int { WF_BF16 = 0, WF_FP8_B128 = 1, WF_FP4 = 2 };
+
+__host__ __device__ constexpr int raw_stage_bytes(int wfmt) {
+  return wfmt == WF_FP8_B128 ? 128 * 64 : wfmt == WF_FP4 ? 128 * 32 + 128 * 2 : 0;
+}
 
 struct GemmParams {
   int T, N, K;
@@ -58,6 +64,13 @@ struct GemmParams {
   // order (so the result does not depend on which CTA is last), adds the residual, stores bf16 and
   // resets the counter.  tile_counters must be zero before the first use.
   int* tile_counters;
+  // Grouped mode (routed experts): work_table[i] = {group, m_tile, first row, rows (<= BN)} and *num_work entries,
+  // both written on the device by the routing kernels; group g uses weights at w_tiled + g * w_group_stride
+  // (bf16: rows g*N.. of the weight tensor map) and scales at scales + g * scale_group_stride.  splits == 1.
+  const int4* work_table;
+  const int* num_work;
+  size_t w_group_stride;
+  size_t scale_group_stride;
   // Fused all-reduce (row-parallel GEMM under tensor parallelism): when ar_mode == 1 the epilogue
   // pushes this rank's partial tile to every peer, waits for theirs and stores the sum.
   int ar_mode;
@@ -71,11 +84,33 @@ struct GemmParams {
 // decode warps.  Raw FP8 stages are small (8 KB), so the raw ring is deep enough (up to 16
 // stages, >= 100 KB per SM in flight) to keep HBM busy in the weight-streaming decode regime,
 // while the 16 KB decoded tiles only need enough stages to overlap decode with the MMA.
+struct Work {
+  int group, m_tile, row0, rows, split;
+};
+
+template <int BN>
+__device__ __forceinline__ Work get_work(const GemmParams& p, int w) {
+  Work k;
+  if (p.work_table) {
+    const int4 e = p.work_table[w];
+    k.group = e.x; k.m_tile = e.y; k.row0 = e.z; k.rows = e.w; k.split = 0;
+  } else {
+    k.group = 0;
+    k.m_tile = w % p.m_tiles;
+    const int rest = w / p.m_tiles;
+    const int n_tile = rest % p.n_tiles;
+    k.split = rest / p.n_tiles;
+    k.row0 = n_tile * BN;
+    k.rows = min(BN, p.T - k.row0);
+  }
+  return k;
+}
+
 template <int BN, int WFMT>
 struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;       // 16 KB bf16 weights (decoded, or loaded for WF_BF16)
   static constexpr int X_BYTES = BN * BK * 2;       // activations
-  static constexpr int RAW_BYTES = BM * BK;         // 8 KB raw fp8
+  static constexpr int RAW_BYTES = raw_stage_bytes(WFMT) ? raw_stage_bytes(WFMT) : BM * BK;   // raw quantised tile
   static constexpr int BUDGET = 232448 - 1024 /*align slack*/ - 512 /*barriers*/;
   static constexpr int SA = (WFMT == WF_BF16) ? 0 : 4;
   static constexpr int W_STAGE_BYTES = (WFMT == WF_BF16) ? A_BYTES : RAW_BYTES;
@@ -163,7 +198,7 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t ar_epoch_at_entry = p.ar_mode ? p.comm.ctrl[0] + 1 : 0;
 
-  const int total_work = p.m_tiles * p.n_tiles * p.splits;
+  const int total_work = p.work_table ? *p.num_work : p.m_tiles * p.n_tiles * p.splits;
   const int kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
 
   if (warp == TMA_WARP) {
@@ -171,12 +206,11 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     if (lane == 0) {
       uint32_t it = 0;
       for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
-        const int m_tile = w % p.m_tiles;
-        const int rest = w / p.m_tiles;
-        const int n_tile = rest % p.n_tiles;
-        const int split = rest / p.n_tiles;
-        const int kb0 = split * kb_per_split;
+        const Work wk = get_work<BN>(p, w);
+        const int m_tile = wk.m_tile;
+        const int kb0 = wk.split * kb_per_split;
         const int kb1 = min(p.kb_total, kb0 + kb_per_split);
+        const uint8_t* wbase = p.w_tiled + (size_t)wk.group * p.w_group_stride;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
@@ -187,14 +221,14 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           }
           if (WFMT == WF_BF16) {
             mbar_expect_tx(&tma_full[s], L::A_BYTES + L::X_BYTES);
-            tma_load_2d(sA + s * L::A_BYTES, &tmW, &tma_full[s], kb * BK, m_tile * BM);
+            tma_load_2d(sA + s * L::A_BYTES, &tmW, &tma_full[s], kb * BK, wk.group * p.N + m_tile * BM);
           } else {
             // FP8 weights are stored tile-major: one contiguous 8 KB block per (m_tile, kb)
             mbar_expect_tx(&tma_full[s], L::RAW_BYTES + L::X_BYTES);
             bulk_load(sRaw + s * L::RAW_BYTES,
-                      p.w_tiled + ((size_t)m_tile * p.kb_total + kb) * L::RAW_BYTES, L::RAW_BYTES, &tma_full[s]);
+                      wbase + ((size_t)m_tile * p.kb_total + kb) * L::RAW_BYTES, L::RAW_BYTES, &tma_full[s]);
           }
-          tma_load_2d(sX + s * L::X_BYTES, &tmX, &tma_full[s], kb * BK, n_tile * BN);
+          tma_load_2d(sX + s * L::X_BYTES, &tmX, &tma_full[s], kb * BK, wk.row0);
 
         }
       }
@@ -206,7 +240,7 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       uint32_t it = 0;
       uint32_t tile_i = 0;
       for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x, ++tile_i) {
-        const int split = (w / p.m_tiles) / p.n_tiles;
+        const int split = get_work<BN>(p, w).split;
         const int kb0 = split * kb_per_split;
         const int kb1 = min(p.kb_total, kb0 + kb_per_split);
         const int buf = tile_i & 1;
@@ -257,43 +291,49 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
   } else if (warp >= DEC_WARP0) {
     // ------------------------------------------------- weight decode (FP8 -> bf16)
-    if constexpr (WFMT == WF_FP8_B128) {
+    if constexpr (WFMT != WF_BF16) {
       constexpr int G = L::GROUPS;
       static_assert(G == SAB, "one decode group per decoded slot");
       constexpr int WPG = L::WARPS_PER_GROUP;
       constexpr int GT = WPG * 32;             // threads per group
-      constexpr int REPS = (BM * 4) / GT;      // 16-byte chunks per thread per stage
       const int dw = warp - DEC_WARP0;
       const int grp = dw / WPG;
       const int d = (dw % WPG) * 32 + lane;    // 0..GT-1
       uint32_t it = 0;
       for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
-        const int m_tile = w % p.m_tiles;
-        const int split = (w / p.m_tiles) / p.n_tiles;
-        const int kb0 = split * kb_per_split;
+        const Work wk = get_work<BN>(p, w);
+        const int m_tile = wk.m_tile;
+        const int kb0 = wk.split * kb_per_split;
         const int kb1 = min(p.kb_total, kb0 + kb_per_split);
-        const float* srow = p.scales + (size_t)m_tile * p.scale_ld;
-        // Block scales of this tile's K range, fetched once per tile and spread over the lanes
+        // FP8: block scales of this tile's K range, fetched once per tile and spread over the lanes
         // (lane l holds entries l, l+32, ...): a per-stage global load would put an L2 round trip
         // on the critical path of every stage.
         const int sc_lo = kb0 >> 1;
-        const int nsc = (kb1 > kb0) ? (((kb1 - 1) >> 1) - sc_lo + 1) : 0;
         float my_sc[8];
+        if constexpr (WFMT == WF_FP8_B128) {
+          const float* srow = p.scales + (size_t)wk.group * p.scale_group_stride + (size_t)m_tile * p.scale_ld;
+          const int nsc = (kb1 > kb0) ? (((kb1 - 1) >> 1) - sc_lo + 1) : 0;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int idx = j * 32 + lane;
-          my_sc[j] = (idx < nsc) ? __ldg(srow + sc_lo + idx) * 0x1p120f : 0.f;
+          for (int j = 0; j < 8; ++j) {
+            const int idx = j * 32 + lane;
+            my_sc[j] = (idx < nsc) ? __ldg(srow + sc_lo + idx) * 0x1p120f : 0.f;
+          }
         }
         bool failed = false;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           if ((int)(it % G) != grp) continue;
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          const int si = (kb >> 1) - sc_lo;
-          float scv = my_sc[0];
+          uint32_t scw = 0;
+          if constexpr (WFMT == WF_FP8_B128) {
+            const int si = (kb >> 1) - sc_lo;
+            float scv = my_sc[0];
 #pragma unroll
-          for (int j = 1; j < 8; ++j) scv = (si >> 5) == j ? my_sc[j] : scv;
-          const float sc = __shfl_sync(0xffffffffu, scv, si & 31);
+            for (int j = 1; j < 8; ++j) scv = (si >> 5) == j ? my_sc[j] : scv;
+            const float sc = __shfl_sync(0xffffffffu, scv, si & 31);
+            __nv_bfloat162 sc2 = __float2bfloat162_rn(sc);
+            scw = *reinterpret_cast<uint32_t*>(&sc2);
+          }
           bool ok = mbar_wait(&tma_full[s], ph);
           if (it >= (uint32_t)SAB) {
             // decoded slot `grp` was last read by the MMAs of k-block it - SA
@@ -307,34 +347,66 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             break;
           }
           tc_fence_after();
-          __nv_bfloat162 sc2 = __float2bfloat162_rn(sc);
-          const uint32_t scw = *reinterpret_cast<uint32_t*>(&sc2);
           const uint8_t* raw = sRaw + s * L::RAW_BYTES;
           uint8_t* A = sA + grp * L::A_BYTES;
-          uint4 q[REPS];
+          if constexpr (WFMT == WF_FP8_B128) {
+            constexpr int REPS = (BM * 4) / GT;      // 16-byte chunks (16 values) per thread per stage
+            uint4 q[REPS];
 #pragma unroll
-          for (int rep = 0; rep < REPS; ++rep) {
-            const int i = d + rep * GT;
-            const int rr = i >> 2;
-            q[rep] = *reinterpret_cast<const uint4*>(raw + rr * BK + (((i & 3) ^ ((rr >> 1) & 3)) << 4));
-          }
+            for (int rep = 0; rep < REPS; ++rep) {
+              const int i = d + rep * GT;
+              const int rr = i >> 2;
+              q[rep] = *reinterpret_cast<const uint4*>(raw + rr * BK + (((i & 3) ^ ((rr >> 1) & 3)) << 4));
+            }
 #pragma unroll
-          for (int rep = 0; rep < REPS; ++rep) {
-            const int i = d + rep * GT;
-            const int r = i >> 2, c = i & 3;
-            uint4 o0, o1;
-            fp8x4_to_bf16x4_raw(q[rep].x, o0.x, o0.y);
-            fp8x4_to_bf16x4_raw(q[rep].y, o0.z, o0.w);
-            fp8x4_to_bf16x4_raw(q[rep].z, o1.x, o1.y);
-            fp8x4_to_bf16x4_raw(q[rep].w, o1.z, o1.w);
-            o0.x = bf16x2_mul(o0.x, scw); o0.y = bf16x2_mul(o0.y, scw);
-            o0.z = bf16x2_mul(o0.z, scw); o0.w = bf16x2_mul(o0.w, scw);
-            o1.x = bf16x2_mul(o1.x, scw); o1.y = bf16x2_mul(o1.y, scw);
-            o1.z = bf16x2_mul(o1.z, scw); o1.w = bf16x2_mul(o1.w, scw);
-            uint8_t* rowp = A + (r >> 3) * 1024 + (r & 7) * 128;
-            const int sw = r & 7;
-            *reinterpret_cast<uint4*>(rowp + (((2 * c) ^ sw) << 4)) = o0;
-            *reinterpret_cast<uint4*>(rowp + (((2 * c + 1) ^ sw) << 4)) = o1;
+            for (int rep = 0; rep < REPS; ++rep) {
+              const int i = d + rep * GT;
+              const int r = i >> 2, c = i & 3;
+              uint4 o0, o1;
+              fp8x4_to_bf16x4_raw(q[rep].x, o0.x, o0.y);
+              fp8x4_to_bf16x4_raw(q[rep].y, o0.z, o0.w);
+              fp8x4_to_bf16x4_raw(q[rep].z, o1.x, o1.y);
+              fp8x4_to_bf16x4_raw(q[rep].w, o1.z, o1.w);
+              o0.x = bf16x2_mul(o0.x, scw); o0.y = bf16x2_mul(o0.y, scw);
+              o0.z = bf16x2_mul(o0.z, scw); o0.w = bf16x2_mul(o0.w, scw);
+              o1.x = bf16x2_mul(o1.x, scw); o1.y = bf16x2_mul(o1.y, scw);
+              o1.z = bf16x2_mul(o1.z, scw); o1.w = bf16x2_mul(o1.w, scw);
+              uint8_t* rowp = A + (r >> 3) * 1024 + (r & 7) * 128;
+              const int sw = r & 7;
+              *reinterpret_cast<uint4*>(rowp + (((2 * c) ^ sw) << 4)) = o0;
+              *reinterpret_cast<uint4*>(rowp + (((2 * c + 1) ^ sw) << 4)) = o1;
+            }
+          } else if constexpr (WFMT == WF_FP4) {
+            // 128 rows x 32 code bytes, then 128 x 2 scale bytes; a 16-byte chunk = 32 values = one scale group.
+            constexpr int REPS = (BM * 2) / GT;
+            const uint8_t* sc_bytes = raw + BM * 32;
+#pragma unroll
+            for (int rep = 0; rep < REPS; ++rep) {
+              const int i = d + rep * GT;
+              const int r = i >> 1, hh = i & 1;       // row, which half of the 64-wide K tile
+              const uint4 qv = *reinterpret_cast<const uint4*>(raw + r * 32 + hh * 16);
+              // The code bits placed at exponent/mantissa positions of a bf16 read as value * 2^-126, so the
+              // multiplier is 2^(e-127) * 2^126 = 2^(e-1): a bf16 with biased exponent e + 126, built directly.
+              const uint32_t e = sc_bytes[r * 2 + hh];
+              const uint32_t s1 = min(e + 126u, 254u) << 7;
+              const uint32_t sw2 = s1 | (s1 << 16);
+              const uint32_t qq[4] = {qv.x, qv.y, qv.z, qv.w};
+              uint8_t* rowp = A + (r >> 3) * 1024 + (r & 7) * 128;
+              const int sw = r & 7;
+#pragma unroll
+              for (int wd = 0; wd < 4; ++wd) {        // 4 bytes = 8 values = one 16-byte output chunk
+                uint4 o;
+                uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                  const uint32_t by = (qq[wd] >> (8 * b)) & 0xFFu;
+                  const uint32_t t = by | (by << 12);   // low nibble at bits 0..3, high nibble at bits 16..19
+                  const uint32_t v = ((t & 0x00070007u) << 6) | ((t & 0x00080008u) << 12);
+                  ow[b] = bf16x2_mul(v, sw2);
+                }
+                *reinterpret_cast<uint4*>(rowp + (((hh * 4 + wd) ^ sw) << 4)) = o;
+              }
+            }
           }
           fence_proxy_async_smem();
           __syncwarp();
@@ -362,10 +434,10 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       } else if (*abort_flag) {
         break;
       }
-      const int m_tile = w % p.m_tiles;
-      const int rest = w / p.m_tiles;
-      const int n_tile = rest % p.n_tiles;
-      const int split = rest / p.n_tiles;
+      const Work wk = get_work<BN>(p, w);
+      const int m_tile = wk.m_tile;
+      const int split = wk.split;
+      const int n_tile = wk.row0 / BN;     // dense mode only (fix-up counters, all-reduce flags)
       const int buf = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
       bool ok = mbar_wait(&acc_full[buf], acc_ph);
@@ -390,7 +462,9 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         const B200Comm& cm = p.comm;
         const int parity = ar_epoch & 1;
         const size_t slot = ((size_t)parity * B200_MAX_RANKS + cm.rank) * cm.slot_elems;
-        // pass 1: push my partial tile (bf16 on the wire) into every peer's slot for source = me
+        // pass 1a: my partial tile as bf16 into my own slot for source = me (local memory; a thread owns one
+        // feature, so these are 2-byte stores 64 bytes wide per warp - fine locally, far too fine for NVLink)
+        __nv_bfloat16* mine_slot = reinterpret_cast<__nv_bfloat16*>(cm.data[cm.rank]) + slot;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += CH) {
           uint32_t v[32];
@@ -403,14 +477,30 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             for (int j = 0; j < 16; ++j) v[j] = v16[j];
           }
           tmem_ld_wait();
-          const int t0 = n_tile * BN + c0;
+          const int t0 = wk.row0 + c0;
           if (f_ok) {
+            __nv_bfloat16* dst = mine_slot + (size_t)t0 * p.ldo + f;
+#pragma unroll
+            for (int j = 0; j < CH; ++j)
+              if (c0 + j < wk.rows) dst[(size_t)j * p.ldo] = __float2bfloat16(__uint_as_float(v[j]));
+          }
+        }
+        __threadfence_block();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        // pass 1b: push the tile to every peer's slot for source = me with 16-byte accesses: 16 threads cover the
+        // 256 contiguous bytes of one token row, so NVLink sees 256-byte runs instead of 64-byte fragments
+        {
+          const int et = threadIdx.x;            // 0..127
+          const int chunk = et & 15, trow = et >> 4;
+          const int fc = m_tile * BM + chunk * 8;
+          if (fc < p.N) {
             for (int r = 0; r < cm.world; ++r) {
               if (r == cm.rank) continue;
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cm.data[r]) + slot + (size_t)t0 * p.ldo + f;
-#pragma unroll
-              for (int j = 0; j < CH; ++j)
-                if (t0 + j < p.T) dst[(size_t)j * p.ldo] = __float2bfloat16(__uint_as_float(v[j]));
+              __nv_bfloat16* peer_slot = reinterpret_cast<__nv_bfloat16*>(cm.data[r]) + slot;
+              for (int tt = trow; tt < wk.rows; tt += 8) {
+                const size_t off = (size_t)(wk.row0 + tt) * p.ldo + fc;
+                *reinterpret_cast<uint4*>(peer_slot + off) = __ldcg(reinterpret_cast<const uint4*>(mine_slot + off));
+              }
             }
           }
         }
@@ -443,11 +533,11 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             for (int j = 0; j < 16; ++j) v[j] = v16[j];
           }
           tmem_ld_wait();
-          const int t0 = n_tile * BN + c0;
+          const int t0 = wk.row0 + c0;
           if (f_ok) {
 #pragma unroll
             for (int j = 0; j < CH; ++j) {
-              if (t0 + j < p.T) {
+              if (c0 + j < wk.rows) {
                 const size_t off = (size_t)(t0 + j) * p.ldo + f;
                 float acc = 0.f;
                 for (int r = 0; r < cm.world; ++r) {
@@ -482,26 +572,26 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           for (int j = 0; j < 16; ++j) v[j] = v16[j];
         }
         tmem_ld_wait();
-        const int t0 = n_tile * BN + c0;
+        const int t0 = wk.row0 + c0;
         if (f_ok) {
           if (p.splits > 1 || p.out == nullptr) {
             float* o = p.out_f32 + ((size_t)split * p.T + t0) * p.ldo + f;
 #pragma unroll
             for (int j = 0; j < CH; ++j)
-              if (t0 + j < p.T) o[(size_t)j * p.ldo] = __uint_as_float(v[j]);
+              if (c0 + j < wk.rows) o[(size_t)j * p.ldo] = __uint_as_float(v[j]);
           } else if (p.residual) {
             const __nv_bfloat16* r = p.residual + (size_t)t0 * p.ldo + f;
             __nv_bfloat16* o = p.out + (size_t)t0 * p.ldo + f;
 #pragma unroll
             for (int j = 0; j < CH; ++j)
-              if (t0 + j < p.T)
+              if (c0 + j < wk.rows)
                 o[(size_t)j * p.ldo] =
                     __float2bfloat16(__uint_as_float(v[j]) + __bfloat162float(r[(size_t)j * p.ldo]));
           } else {
             __nv_bfloat16* o = p.out + (size_t)t0 * p.ldo + f;
 #pragma unroll
             for (int j = 0; j < CH; ++j)
-              if (t0 + j < p.T) o[(size_t)j * p.ldo] = __float2bfloat16(__uint_as_float(v[j]));
+              if (c0 + j < wk.rows) o[(size_t)j * p.ldo] = __float2bfloat16(__uint_as_float(v[j]));
           }
         }
       }
@@ -520,8 +610,8 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*fix_last && f_ok) {
           __threadfence();
-          const int t_lo = n_tile * BN;
-          const int t_hi = min(p.T, t_lo + BN);
+          const int t_lo = wk.row0;
+          const int t_hi = wk.row0 + wk.rows;
           for (int t = t_lo; t < t_hi; ++t) {
             const size_t off = (size_t)t * p.ldo + f;
             float acc = p.residual ? __bfloat162float(p.residual[off]) : 0.f;
@@ -582,7 +672,7 @@ static int launch_one(const CUtensorMap& tmW, const CUtensorMap& tmX, const Gemm
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int total = p.m_tiles * p.n_tiles * p.splits;
+  const int total = p.work_table ? sm_count() : p.m_tiles * p.n_tiles * p.splits;
   const int grid = total < sm_count() ? total : sm_count();
   gemm_wdec_kernel<BN, WFMT><<<grid, NUM_THREADS, L::TOTAL, stream>>>(tmW, tmX, p);
   return (int)cudaGetLastError();
@@ -651,6 +741,10 @@ extern "C" int b200_gemm_wdec_ex(int wfmt, const void* W, const float* scales, c
   p.ldo = N;
   p.status = status;
   p.tile_counters = tile_counters;
+  p.work_table = nullptr;
+  p.num_work = nullptr;
+  p.w_group_stride = 0;
+  p.scale_group_stride = 0;
   if (splits > 1 && out_bf16 && !tile_counters) return -ERR_BAD_ARG;
   p.ar_mode = 0;
   p.ar_budget_ns = 0;
@@ -662,11 +756,12 @@ extern "C" int b200_gemm_wdec_ex(int wfmt, const void* W, const float* scales, c
     p.comm = *g_ar_comm;
   }
   if ((splits > 1 || !out_bf16) && !out_f32) return -ERR_BAD_ARG;
-  if (wfmt != WF_BF16) {
+  if (wfmt == WF_FP8_B128) {
     // the decode warps keep at most 256 block scales (K range of 32768) per tile in registers
     const int per = (p.kb_total + splits - 1) / splits;
     if (per / 2 + 2 > 256) return -ERR_BAD_ARG;
   }
+  if (wfmt == WF_FP4 && (K % 64) != 0) return -ERR_BAD_ARG;
 
   CUtensorMap tmW, tmX;
   bool ok = make_tmap_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, T, K, (uint64_t)K * 2, BN, BK,
@@ -681,10 +776,12 @@ extern "C" int b200_gemm_wdec_ex(int wfmt, const void* W, const float* scales, c
   }
   if (!ok) return -ERR_BAD_ARG;
 
-#define B200_DISPATCH(BN_)                                                       \
-  case BN_:                                                                      \
-    return wfmt == WF_BF16 ? launch_one<BN_, WF_BF16>(tmW, tmX, p, stream)       \
-                           : launch_one<BN_, WF_FP8_B128>(tmW, tmX, p, stream);
+#define B200_DISPATCH(BN_)                                                             \
+  case BN_:                                                                            \
+    return wfmt == WF_BF16       ? launch_one<BN_, WF_BF16>(tmW, tmX, p, stream)       \
+           : wfmt == WF_FP8_B128 ? launch_one<BN_, WF_FP8_B128>(tmW, tmX, p, stream)   \
+           : wfmt == WF_FP4      ? launch_one<BN_, WF_FP4>(tmW, tmX, p, stream)        \
+                                 : -ERR_BAD_ARG;
   switch (BN) {
     B200_DISPATCH(16)
     B200_DISPATCH(32)
@@ -693,6 +790,65 @@ extern "C" int b200_gemm_wdec_ex(int wfmt, const void* W, const float* scales, c
     B200_DISPATCH(256)
   }
 #undef B200_DISPATCH
+  return -ERR_BAD_ARG;
+}
+
+// Grouped GEMM over ragged row segments (routed experts): out[r, :] = X[r, :] * W_g^T for every row r of the
+// segment the device-side work table assigns to group g.  X / out: [rows_total, K] / [rows_total, N] bf16 with the
+// rows of one group contiguous; W: `groups` matrices of N x K back to back (tile-major packed for FP8 / FP4, plain
+// [groups * N, K] for bf16, N % 128 == 0); scales (FP8): [groups][ceil(N/128)][K/128] fp32.
+// work_table / num_work are produced on the device (b200_moe_build_work); bn is the token tile (16..256) the
+// table was built for.  No host synchronisation is needed between routing and this call.
+extern "C" int b200_gemm_wdec_grouped(int wfmt, const void* W, const float* scales, const void* X, void* out_bf16,
+                                      int rows_total, int N, int K, int groups, const void* work_table,
+                                      const int* num_work, int bn, int* status, cudaStream_t stream) {
+  if (rows_total <= 0 || N <= 0 || K <= 0 || (K % 16) != 0 || groups <= 0 || !work_table || !num_work || !out_bf16)
+    return -ERR_BAD_ARG;
+  if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return -ERR_BAD_ARG;
+  if (wfmt == WF_BF16 && (N % BM) != 0) return -ERR_BAD_ARG;
+  if (wfmt == WF_FP4 && (K % 64) != 0) return -ERR_BAD_ARG;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.T = rows_total; p.N = N; p.K = K;
+  p.m_tiles = (N + BM - 1) / BM;
+  p.n_tiles = 1;
+  p.kb_total = (K + BK - 1) / BK;
+  p.splits = 1;
+  p.scales = scales;
+  p.scale_ld = (K + 127) / 128;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out_bf16);
+  p.ldo = N;
+  p.status = status;
+  p.work_table = reinterpret_cast<const int4*>(work_table);
+  p.num_work = num_work;
+  p.w_group_stride = (size_t)p.m_tiles * p.kb_total * raw_stage_bytes(wfmt);
+  p.scale_group_stride = (size_t)p.m_tiles * p.scale_ld;
+  if (wfmt == WF_FP8_B128 && p.kb_total / 2 + 2 > 256) return -ERR_BAD_ARG;
+  CUtensorMap tmW, tmX;
+  bool ok = make_tmap_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, rows_total, K, (uint64_t)K * 2, bn, BK,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
+  if (wfmt == WF_BF16) {
+    ok = ok && make_tmap_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, (uint64_t)groups * N, K, (uint64_t)K * 2, BM,
+                            BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    p.w_tiled = reinterpret_cast<const uint8_t*>(W);
+    tmW = tmX;
+  }
+  if (!ok) return -ERR_BAD_ARG;
+#define B200_DISPATCH_G(BN_)                                                           \
+  case BN_:                                                                            \
+    return wfmt == WF_BF16       ? launch_one<BN_, WF_BF16>(tmW, tmX, p, stream)       \
+           : wfmt == WF_FP8_B128 ? launch_one<BN_, WF_FP8_B128>(tmW, tmX, p, stream)   \
+           : wfmt == WF_FP4      ? launch_one<BN_, WF_FP4>(tmW, tmX, p, stream)        \
+                                 : -ERR_BAD_ARG;
+  switch (bn) {
+    B200_DISPATCH_G(16)
+    B200_DISPATCH_G(32)
+    B200_DISPATCH_G(64)
+    B200_DISPATCH_G(128)
+    B200_DISPATCH_G(256)
+  }
+#undef B200_DISPATCH_G
   return -ERR_BAD_ARG;
 }
 
@@ -705,7 +861,7 @@ extern "C" int b200_gemm_wdec_allreduce(int wfmt, const void* W, const float* sc
                                         cudaStream_t stream) {
   if (!comm || comm->world <= 1)
     return b200_gemm_wdec(wfmt, W, scales, X, out_bf16, nullptr, residual, T, N, K, 1, status, stream);
-  if ((unsigned long long)T * N > comm->slot_elems) return -ERR_BAD_ARG;
+  if ((unsigned long long)T * N > comm->slot_elems || (N % 8) != 0) return -ERR_BAD_ARG;
   const int BN = b200_gemm_pick_bn(T);
   if ((long long)((N + BM - 1) / BM) * ((T + BN - 1) / BN) > B200_FLAGS_PER_SLOT) return -ERR_BAD_ARG;
   g_ar_comm = comm;

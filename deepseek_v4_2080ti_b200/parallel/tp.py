@@ -176,7 +176,7 @@ class PeerComm(TPComm):
         n = w.n
         bn = gemm._bn(t)
         tiles = ((n + 127) // 128) * ((t + bn - 1) // bn)
-        if self.world == 1 or t * n > self.slot_elems or tiles > 4096:
+        if self.world == 1 or t * n > self.slot_elems or tiles > 4096 or n % 8:
             return self.all_reduce(gemm.linear(x, w, residual=None)) if residual is None else \
                 self.all_reduce(gemm.linear(x, w)).add_(residual)
         out = torch.empty(t, n, dtype=torch.bfloat16, device=x.device)
