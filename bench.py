@@ -72,10 +72,9 @@ def main() -> None:
         cfg = qh.QwenHybridConfig(num_hidden_layers=args.layers)
     comm = None
     if world > 1:
-        # peer-memory collectives; the GEMM-epilogue all-reduce pushes every tile to every peer, so its slot is
-        # sized for whole prefill chunks only at 2 ranks (larger groups reduce big payloads over NCCL/NVLS)
-        rows = args.chunk if world == 2 else 512
-        comm = tp.PeerComm(slot_elems=rows * cfg.hidden_size)
+        # peer-memory collectives: row-parallel GEMMs reduce in their epilogue (one-shot pushes at 2 ranks and for decode
+        # batches, owner-reduces two-shot beyond); the slot holds one whole prefill chunk of hidden states
+        comm = tp.PeerComm(slot_elems=args.chunk * cfg.hidden_size)
     bdec = args.batch_decode
     max_slots = max(1, bdec) + 1
     t0 = time.time()

@@ -149,7 +149,8 @@ argmax_merge_kernel(B200Comm c, const float* val, const int* idx, int rows, int*
 extern "C" {
 
 unsigned long long b200_comm_buffer_bytes(unsigned long long slot_elems) {
-  return kFlagWords * 4 + 256 + 2ull * B200_MAX_RANKS * slot_elems * 2;   // flags | ctrl (256 B) | data
+  // flags (2 banks) | ctrl (256 B) | data | result (2 buffers)
+  return 2 * kFlagWords * 4 + 256 + 2ull * B200_MAX_RANKS * slot_elems * 2 + 2ull * slot_elems * 2;
 }
 
 int b200_comm_alloc(unsigned long long bytes, void** out) {
@@ -192,9 +193,11 @@ int b200_comm_init(B200Comm* c, int rank, int world, void* const* bases, unsigne
   for (int r = 0; r < world; ++r) {
     uint8_t* b = reinterpret_cast<uint8_t*>(bases[r]);
     c->flags[r] = reinterpret_cast<uint32_t*>(b);
-    c->data[r] = b + kFlagWords * 4 + 256;
+    c->flags2[r] = reinterpret_cast<uint32_t*>(b + kFlagWords * 4);
+    c->data[r] = b + 2 * kFlagWords * 4 + 256;
+    c->result[r] = b + 2 * kFlagWords * 4 + 256 + 2ull * B200_MAX_RANKS * slot_elems * 2;
   }
-  c->ctrl = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(bases[rank]) + kFlagWords * 4);
+  c->ctrl = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(bases[rank]) + 2 * kFlagWords * 4);
   return 0;
 }
 

@@ -2,9 +2,11 @@
 //
 // Every rank owns one "symmetric" buffer of identical layout and holds a pointer to every
 // peer's buffer (CUDA IPC across processes, or plain peer access inside one process).
-//   flags  : uint32 [2 parities][MAX_RANKS sources][FLAGS_PER_SLOT]   written by peers, read locally
+//   flags  : uint32 [2 banks][2 parities][MAX_RANKS sources][FLAGS_PER_SLOT]   written by peers, read locally
+//            (bank 0: "partial tile arrived", bank 1: "reduced tile arrived")
 //   ctrl   : uint32 [16]   [0] = epoch of the last finished collective, [1] = CTA exit counter
 //   data   : bf16   [2 parities][MAX_RANKS sources][slot_elems]        written by peers, read locally
+//   result : bf16   [2 buffers][slot_elems]   reduced outputs of the two-shot GEMM epilogue, written by tile owners
 // A collective call number ("epoch") is kept on the device so CUDA-graph replays advance it
 // without any host-side argument changing; all ranks issue identical call sequences, so their
 // epochs agree.  Parity = epoch & 1 selects the buffer half: a peer can only be one call ahead.
@@ -23,6 +25,8 @@ struct B200Comm {
   uint32_t* flags[B200_MAX_RANKS];      // base of rank r's flag region (peer-mapped)
   uint32_t* ctrl;                       // local control words
   void* data[B200_MAX_RANKS];           // base of rank r's data region (peer-mapped)
+  uint32_t* flags2[B200_MAX_RANKS];     // second flag bank of rank r
+  void* result[B200_MAX_RANKS];         // base of rank r's result region
 };
 
 #ifdef __cplusplus

@@ -71,9 +71,14 @@ struct GemmParams {
   const int* num_work;
   size_t w_group_stride;
   size_t scale_group_stride;
-  // Fused all-reduce (row-parallel GEMM under tensor parallelism): when ar_mode == 1 the epilogue
-  // pushes this rank's partial tile to every peer, waits for theirs and stores the sum.
+  // Fused all-reduce (row-parallel GEMM under tensor parallelism).
+  // ar_mode == 1 (one-shot): the epilogue pushes this rank's partial tile to every peer, waits for theirs and
+  //   stores the sum; every tile crosses NVLink world-1 times per rank.
+  // ar_mode == 2 (two-shot): tile w is owned by rank w % world; the others push their partial only to the owner,
+  //   the owner reduces and pushes the finished tile into every rank's result region (`out` points into this
+  //   rank's).  Traffic per rank is 2 (world-1)/world of the output instead of (world-1) times it.
   int ar_mode;
+  size_t result_off;   // element offset of the output inside every rank's result region (two-shot)
   unsigned long long ar_budget_ns;
   B200Comm comm;
 };
@@ -457,14 +462,24 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       const bool f_ok = f < p.N;
       const uint32_t taddr = tmem_base + (uint32_t(warp * 32) << 16) + buf * BN;
       constexpr int CH = BN >= 32 ? 32 : 16;
-      if (p.ar_mode == 1) {
-        // ---- fused one-shot all-reduce over peer memory -------------------------------------
+      if (p.ar_mode != 0) {
+        // ---- fused all-reduce over peer memory --------------------------------------------------
+        // The accumulator is first written as bf16 into this rank's own slot (a thread owns one feature, so these
+        // are 2-byte stores, 64 bytes wide per warp: fine locally, far too fine for NVLink).  Everything that
+        // crosses NVLink or is summed afterwards uses the transposed mapping: 16 threads cover the 256 contiguous
+        // bytes of one token row with 16-byte accesses, several rows in flight per thread.
         const B200Comm& cm = p.comm;
         const int parity = ar_epoch & 1;
-        const size_t slot = ((size_t)parity * B200_MAX_RANKS + cm.rank) * cm.slot_elems;
-        // pass 1a: my partial tile as bf16 into my own slot for source = me (local memory; a thread owns one
-        // feature, so these are 2-byte stores 64 bytes wide per warp - fine locally, far too fine for NVLink)
-        __nv_bfloat16* mine_slot = reinterpret_cast<__nv_bfloat16*>(cm.data[cm.rank]) + slot;
+        const bool two_shot = p.ar_mode == 2;
+        const int owner = two_shot ? (w % cm.world) : cm.rank;
+        const bool reduce_here = owner == cm.rank;
+        const size_t slot_elems = cm.slot_elems;
+        const size_t my_slot = ((size_t)parity * B200_MAX_RANKS + cm.rank) * slot_elems;
+        __nv_bfloat16* mine_slot = reinterpret_cast<__nv_bfloat16*>(cm.data[cm.rank]) + my_slot;
+        const int et = threadIdx.x;            // 0..127 inside the epilogue group
+        const int chunk = et & 15, trow = et >> 4;
+        const int fc = m_tile * BM + chunk * 8;
+        // pass 1a: accumulator -> my slot; after it the TMEM buffer can be handed back to the MMA warp
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += CH) {
           uint32_t v[32];
@@ -485,79 +500,121 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
               if (c0 + j < wk.rows) dst[(size_t)j * p.ldo] = __float2bfloat16(__uint_as_float(v[j]));
           }
         }
+        tc_fence_before();
+        mbar_arrive(&acc_empty[buf]);
         __threadfence_block();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        // pass 1b: push the tile to every peer's slot for source = me with 16-byte accesses: 16 threads cover the
-        // 256 contiguous bytes of one token row, so NVLink sees 256-byte runs instead of 64-byte fragments
-        {
-          const int et = threadIdx.x;            // 0..127
-          const int chunk = et & 15, trow = et >> 4;
-          const int fc = m_tile * BM + chunk * 8;
-          if (fc < p.N) {
-            for (int r = 0; r < cm.world; ++r) {
-              if (r == cm.rank) continue;
-              __nv_bfloat16* peer_slot = reinterpret_cast<__nv_bfloat16*>(cm.data[r]) + slot;
-              for (int tt = trow; tt < wk.rows; tt += 8) {
-                const size_t off = (size_t)(wk.row0 + tt) * p.ldo + fc;
-                *reinterpret_cast<uint4*>(peer_slot + off) = __ldcg(reinterpret_cast<const uint4*>(mine_slot + off));
-              }
+        // pass 1b: push my partial to every peer (one-shot) or to the tile's owner (two-shot), 4 rows per thread in flight
+        if (fc < p.N && !(two_shot && reduce_here)) {
+          for (int r = 0; r < cm.world; ++r) {
+            if (r == cm.rank || (two_shot && r != owner)) continue;
+            __nv_bfloat16* peer_slot = reinterpret_cast<__nv_bfloat16*>(cm.data[r]) + my_slot;
+            for (int tt = trow; tt < wk.rows; tt += 32) {
+              uint4 q[4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u)
+                if (tt + 8 * u < wk.rows)
+                  q[u] = __ldcg(reinterpret_cast<const uint4*>(mine_slot + (size_t)(wk.row0 + tt + 8 * u) * p.ldo + fc));
+#pragma unroll
+              for (int u = 0; u < 4; ++u)
+                if (tt + 8 * u < wk.rows)
+                  *reinterpret_cast<uint4*>(peer_slot + (size_t)(wk.row0 + tt + 8 * u) * p.ldo + fc) = q[u];
             }
           }
+          __threadfence_system();
         }
-        __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        // one thread per peer: raise my flag for this tile there, then wait for the peer's flag here
-        const int et = threadIdx.x;  // 0..127 inside the epilogue group
+        // flags: tell the consumer(s) that my partial is there; whoever reduces waits for everyone else's
         if (et < cm.world && et != cm.rank) {
-          uint32_t* theirs = cm.flags[et] + ((size_t)parity * B200_MAX_RANKS + cm.rank) * B200_FLAGS_PER_SLOT + w;
-          const uint32_t* mine = cm.flags[cm.rank] + ((size_t)parity * B200_MAX_RANKS + et) * B200_FLAGS_PER_SLOT + w;
-          st_release_sys(theirs, ar_epoch);
-          if (!wait_flag_ge(mine, ar_epoch, p.ar_budget_ns)) {
-            atomicExch(p.status, ERR_WAIT_PEER);
-            *abort_flag = 1;
-            *epi_abort = 1;
+          if (!two_shot || (et == owner && !reduce_here))
+            st_release_sys(cm.flags[et] + ((size_t)parity * B200_MAX_RANKS + cm.rank) * B200_FLAGS_PER_SLOT + w, ar_epoch);
+          if (reduce_here) {
+            const uint32_t* mine = cm.flags[cm.rank] + ((size_t)parity * B200_MAX_RANKS + et) * B200_FLAGS_PER_SLOT + w;
+            if (!wait_flag_ge(mine, ar_epoch, p.ar_budget_ns)) {
+              atomicExch(p.status, ERR_WAIT_PEER);
+              *abort_flag = 1;
+              *epi_abort = 1;
+            }
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*epi_abort) break;
-        // pass 2: own fp32 accumulator + peers' bf16 partials (fixed rank order) (+ residual) -> out
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += CH) {
-          uint32_t v[32];
-          if (CH == 32) {
-            tmem_ld_32x32(taddr + c0, v);
-          } else {
-            uint32_t v16[16];
-            tmem_ld_32x16(taddr + c0, v16);
+        if (reduce_here && fc < p.N) {
+          // pass 2: sum the bf16 partials of all ranks in rank order (+ residual); every rank that reduces a tile
+          // reads the same bits in the same order, so the result is identical everywhere.  Two-shot: the owner also
+          // stores the finished rows straight into every peer's result region.
+          const __nv_bfloat16* slots0 = reinterpret_cast<const __nv_bfloat16*>(cm.data[cm.rank]) +
+                                        (size_t)parity * B200_MAX_RANKS * slot_elems;
+          constexpr int ROWS = 4;   // token rows in flight per thread
+          for (int tt = trow; tt < wk.rows; tt += 8 * ROWS) {
+            float acc[ROWS][8];
+            size_t off[ROWS];
+            bool live[ROWS];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = v16[j];
-          }
-          tmem_ld_wait();
-          const int t0 = wk.row0 + c0;
-          if (f_ok) {
+            for (int u = 0; u < ROWS; ++u) {
+              live[u] = tt + 8 * u < wk.rows;
+              off[u] = (size_t)(wk.row0 + tt + 8 * u) * p.ldo + fc;
 #pragma unroll
-            for (int j = 0; j < CH; ++j) {
-              if (c0 + j < wk.rows) {
-                const size_t off = (size_t)(t0 + j) * p.ldo + f;
-                float acc = 0.f;
-                for (int r = 0; r < cm.world; ++r) {
-                  if (r == cm.rank) {
-                    // round my own part the way the peers see it, so every rank computes the same sum
-                    acc += __bfloat162float(__float2bfloat16(__uint_as_float(v[j])));
-                  } else {
-                    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(cm.data[cm.rank]) +
-                                               ((size_t)parity * B200_MAX_RANKS + r) * cm.slot_elems + off;
-                    acc += __bfloat162float(*src);
-                  }
+              for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+            }
+            if (p.residual) {
+              uint4 q[ROWS];
+#pragma unroll
+              for (int u = 0; u < ROWS; ++u)
+                if (live[u]) q[u] = *reinterpret_cast<const uint4*>(p.residual + off[u]);
+#pragma unroll
+              for (int u = 0; u < ROWS; ++u) {
+                if (!live[u]) continue;
+                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&q[u]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 fv = __bfloat1622float2(h2[e]);
+                  acc[u][2 * e] = fv.x;
+                  acc[u][2 * e + 1] = fv.y;
                 }
-                if (p.residual) acc += __bfloat162float(p.residual[off]);
-                p.out[off] = __float2bfloat16(acc);
+              }
+            }
+#pragma unroll 2
+            for (int r = 0; r < cm.world; ++r) {
+              uint4 q[ROWS];
+              const __nv_bfloat16* sl = slots0 + (size_t)r * slot_elems;
+#pragma unroll
+              for (int u = 0; u < ROWS; ++u)
+                if (live[u]) q[u] = __ldcg(reinterpret_cast<const uint4*>(sl + off[u]));
+#pragma unroll
+              for (int u = 0; u < ROWS; ++u) {
+                if (!live[u]) continue;
+                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&q[u]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 fv = __bfloat1622float2(h2[e]);
+                  acc[u][2 * e] += fv.x;
+                  acc[u][2 * e + 1] += fv.y;
+                }
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < ROWS; ++u) {
+              if (!live[u]) continue;
+              uint4 o;
+              __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(acc[u][2 * e], acc[u][2 * e + 1]);
+              *reinterpret_cast<uint4*>(p.out + off[u]) = o;
+              if (two_shot) {
+                for (int r = 0; r < cm.world; ++r)
+                  if (r != cm.rank)
+                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(cm.result[r]) + p.result_off + off[u]) = o;
               }
             }
           }
         }
-        tc_fence_before();
-        mbar_arrive(&acc_empty[buf]);
+        if (two_shot && reduce_here) {
+          __threadfence_system();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (et < cm.world && et != cm.rank)
+            st_release_sys(cm.flags2[et] + ((size_t)parity * B200_MAX_RANKS + cm.rank) * B200_FLAGS_PER_SLOT + w, ar_epoch);
+        }
         continue;
       }
 #pragma unroll 1
@@ -625,6 +682,23 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
   }
 
+  if (warp < NUM_EPI_WARPS && p.ar_mode == 2 && !*abort_flag) {
+    // two-shot: the tiles this CTA handed to other owners must have come back before the grid may finish
+    const B200Comm& cm = p.comm;
+    const uint32_t epoch = ar_epoch_at_entry;
+    const int parity = epoch & 1;
+    int n = 0;
+    for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++n) {
+      const int owner = w % cm.world;
+      if (owner == cm.rank || (n % 128) != (int)threadIdx.x) continue;
+      const uint32_t* fl = cm.flags2[cm.rank] + ((size_t)parity * B200_MAX_RANKS + owner) * B200_FLAGS_PER_SLOT + w;
+      if (!wait_flag_ge(fl, epoch, p.ar_budget_ns)) {
+        atomicExch(p.status, ERR_WAIT_PEER);
+        break;
+      }
+    }
+  }
+
   // Common exit: every thread arrives here, then the allocating warp frees TMEM.
   tc_fence_before();
   __syncthreads();
@@ -686,6 +760,8 @@ using namespace b200;
 // GEMMs concurrently must serialise fused all-reduce calls; one engine thread per process does).
 static const B200Comm* g_ar_comm = nullptr;
 static unsigned long long g_ar_budget = 0;
+static int g_ar_mode = 1;
+static size_t g_ar_result_off = 0;
 
 extern "C" int b200_gemm_pick_bn(int T) {
   if (T <= 16) return 16;
@@ -754,6 +830,8 @@ extern "C" int b200_gemm_wdec_ex(int wfmt, const void* W, const float* scales, c
     p.ar_mode = 1;
     p.ar_budget_ns = g_ar_budget;
     p.comm = *g_ar_comm;
+    p.ar_mode = g_ar_mode;
+    p.result_off = g_ar_result_off;
   }
   if ((splits > 1 || !out_bf16) && !out_f32) return -ERR_BAD_ARG;
   if (wfmt == WF_FP8_B128) {
@@ -868,6 +946,29 @@ extern "C" int b200_gemm_wdec_allreduce(int wfmt, const void* W, const float* sc
   g_ar_budget = budget_ns ? budget_ns : B200_WAIT_BUDGET_NS;
   const int rc = b200_gemm_wdec(wfmt, W, scales, X, out_bf16, nullptr, residual, T, N, K, 1, status, stream);
   g_ar_comm = nullptr;
+  return rc;
+}
+
+// Two-shot variant: tile w is reduced by rank w % world and the reduced tile is pushed into every rank's result
+// region; the output of this call is comm->result[rank] + result_index * slot_elems (bf16 [T, N]), valid until the
+// call after next that uses the same result_index.  result_index is 0 or 1.
+extern "C" int b200_gemm_wdec_allreduce2(int wfmt, const void* W, const float* scales, const void* X,
+                                         const void* residual, int T, int N, int K, const B200Comm* comm,
+                                         int result_index, unsigned long long budget_ns, int* status,
+                                         cudaStream_t stream) {
+  if (!comm || comm->world <= 1 || result_index < 0 || result_index > 1) return -ERR_BAD_ARG;
+  if ((unsigned long long)T * N > comm->slot_elems || (N % 8) != 0) return -ERR_BAD_ARG;
+  const int BN = b200_gemm_pick_bn(T);
+  if ((long long)((N + BM - 1) / BM) * ((T + BN - 1) / BN) > B200_FLAGS_PER_SLOT) return -ERR_BAD_ARG;
+  g_ar_comm = comm;
+  g_ar_budget = budget_ns ? budget_ns : B200_WAIT_BUDGET_NS;
+  g_ar_mode = 2;
+  g_ar_result_off = (size_t)result_index * comm->slot_elems;
+  void* out = reinterpret_cast<__nv_bfloat16*>(comm->result[comm->rank]) + g_ar_result_off;
+  const int rc = b200_gemm_wdec(wfmt, W, scales, X, out, nullptr, residual, T, N, K, 1, status, stream);
+  g_ar_comm = nullptr;
+  g_ar_mode = 1;
+  g_ar_result_off = 0;
   return rc;
 }
 

@@ -73,7 +73,8 @@ class _CommStruct(ctypes.Structure):
     """Mirror of ``B200Comm`` (csrc/comm/comm.h)."""
     _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int), ("slot_elems", ctypes.c_ulonglong),
                 ("flags", ctypes.c_void_p * MAX_RANKS), ("ctrl", ctypes.c_void_p),
-                ("data", ctypes.c_void_p * MAX_RANKS)]
+                ("data", ctypes.c_void_p * MAX_RANKS), ("flags2", ctypes.c_void_p * MAX_RANKS),
+                ("result", ctypes.c_void_p * MAX_RANKS)]
 
 
 class CollectiveTimeoutError(RuntimeError):
@@ -137,6 +138,7 @@ class PeerComm(TPComm):
         torch.cuda.synchronize()
         dist.barrier(group=self.group)
         self.fused_calls = 0
+        self._result_index = 0
 
     def _cref(self):
         return ctypes.byref(self.c)
@@ -168,8 +170,22 @@ class PeerComm(TPComm):
         _lib.check(rc, "argmax_merge")
         return out
 
-    def linear_allreduce(self, x: torch.Tensor, w, residual: torch.Tensor | None = None) -> torch.Tensor:
-        """``sum_r x_r @ w_r^T`` (+ residual): this rank's K-shard GEMM with the all-reduce done in its epilogue."""
+    def _result_view(self, index: int, t: int, n: int) -> torch.Tensor:
+        """bf16 [t, n] view of this rank's result buffer ``index`` inside the symmetric allocation."""
+        ptr = int(self.c.result[self.rank]) + index * self.slot_elems * 2
+
+        class _Mem:
+            __cuda_array_interface__ = {"shape": (t * n,), "typestr": "<u2", "data": (ptr, False), "version": 2}
+
+        return torch.as_tensor(_Mem(), device=self.device).view(torch.bfloat16).view(t, n)
+
+    def linear_allreduce(self, x: torch.Tensor, w, residual: torch.Tensor | None = None,
+                         two_shot: bool | None = None) -> torch.Tensor:
+        """``sum_r x_r @ w_r^T`` (+ residual): this rank's K-shard GEMM with the all-reduce done in its epilogue.
+
+        One-shot (every partial tile pushed to every peer) for small outputs and 2 ranks; two-shot (partials to
+        the tile's owner, reduced tile back to everyone) otherwise - then the result lives in the symmetric
+        buffer and stays valid until the call after next."""
         from ..ops import gemm
 
         t, k = x.shape
@@ -179,11 +195,24 @@ class PeerComm(TPComm):
         if self.world == 1 or t * n > self.slot_elems or tiles > 4096 or n % 8:
             return self.all_reduce(gemm.linear(x, w, residual=None)) if residual is None else \
                 self.all_reduce(gemm.linear(x, w)).add_(residual)
+        if two_shot is None:
+            two_shot = self.world > 2 and t > 64
+        L = _lib.lib()
+        if two_shot:
+            idx = self._result_index
+            self._result_index ^= 1
+            rc = L.b200_gemm_wdec_allreduce2(w.wfmt, _lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(x),
+                                             _lib.ptr(residual), t, n, k, self._cref(), idx,
+                                             ctypes.c_ulonglong(self.budget_ns), _lib.ptr(_lib.status_word(x.device)),
+                                             _lib.stream())
+            _lib.check(rc, "gemm_wdec_allreduce2")
+            self.fused_calls += 1
+            return self._result_view(idx, t, n)
         out = torch.empty(t, n, dtype=torch.bfloat16, device=x.device)
-        rc = _lib.lib().b200_gemm_wdec_allreduce(w.wfmt, _lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(x),
-                                                 _lib.ptr(out), _lib.ptr(residual), t, n, k, self._cref(),
-                                                 ctypes.c_ulonglong(self.budget_ns),
-                                                 _lib.ptr(_lib.status_word(x.device)), _lib.stream())
+        rc = L.b200_gemm_wdec_allreduce(w.wfmt, _lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(x),
+                                        _lib.ptr(out), _lib.ptr(residual), t, n, k, self._cref(),
+                                        ctypes.c_ulonglong(self.budget_ns),
+                                        _lib.ptr(_lib.status_word(x.device)), _lib.stream())
         _lib.check(rc, "gemm_wdec_allreduce")
         self.fused_calls += 1
         return out

@@ -1,0 +1,89 @@
+"""Row-parallel GEMM + all-reduce micro-benchmark across ranks (one process per GPU, launched with torchrun):
+
+  python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m deepseek_v4_2080ti_b200.utils.tp_microbench \\
+      --rows 8192 --out-features 5120 --in-features 17408
+
+For every variant the time is CUDA-event time on each rank, max over ranks, median of the iterations:
+  gemm        this rank's K-shard GEMM alone (no communication)
+  nccl        GEMM, then NCCL all-reduce of the bf16 output (the baseline)
+  oneshot     GEMM whose epilogue pushes each partial tile to every peer and sums (peer stores over NVLink)
+  twoshot     GEMM whose epilogue sends partials to the tile owner, which reduces and returns the tile
+Roofline per call = max(FLOPs / measured bf16 GEMM peak, bytes this rank must send / NVLink bandwidth per direction).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--rows", dest="t", type=int, default=8192)
+    ap.add_argument("--out-features", dest="n", type=int, default=5120)
+    ap.add_argument("--in-features", dest="k", type=int, default=17408, help="full K; every rank holds K / world")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--gemm-peak-tflops", type=float, default=1397.7)
+    ap.add_argument("--link-gbs", type=float, default=770.0)
+    a = ap.parse_args()
+    from ..formats import fp8 as fp8fmt
+    from ..ops import _lib, gemm
+    from ..parallel import tp
+    rank, world, local = tp.init_distributed()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    comm = tp.PeerComm(slot_elems=a.t * a.n)
+    ks = a.k // world
+    torch.manual_seed(rank)
+    w = torch.randn(a.n, ks, device=dev) * 0.02
+    q, s = fp8fmt.quantize_block128(w)
+    pl = gemm.PackedLinear.from_fp8(q, s)
+    del w
+    x = torch.randn(a.t, ks, device=dev).bfloat16()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn):
+        ts = []
+        for i in range(a.iters + 3):
+            flush.zero_()
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                ts.append(e0.elapsed_time(e1))
+        ts.sort()
+        t = torch.tensor([ts[len(ts) // 2]], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    out = {}
+    out["gemm"] = timed(lambda: gemm.linear(x, pl, stream=False))
+    out["nccl"] = timed(lambda: dist.all_reduce(gemm.linear(x, pl, stream=False)))
+    out["oneshot"] = timed(lambda: comm.linear_allreduce(x, pl, two_shot=False))
+    out["twoshot"] = timed(lambda: comm.linear_allreduce(x, pl, two_shot=True))
+    comm.check()
+    flops = 2.0 * a.t * a.n * ks
+    payload = a.t * a.n * 2
+    sent = {"oneshot": (world - 1) * payload, "twoshot": 2 * (world - 1) / world * payload,
+            "nccl": 2 * (world - 1) / world * payload}
+    if rank == 0:
+        rec = {"op": "gemm_allreduce", "world": world, "t": a.t, "n": a.n, "k_per_rank": ks, "ms": out}
+        for v in ("nccl", "oneshot", "twoshot"):
+            roof = max(flops / (a.gemm_peak_tflops * 1e9), sent[v] / (a.link_gbs * 1e6))
+            rec[f"{v}_roofline_ms"] = round(roof, 4)
+            rec[f"{v}_fraction_of_roofline"] = round(roof / out[v], 3)
+        print(json.dumps(rec), flush=True)
+    comm.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

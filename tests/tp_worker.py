@@ -60,16 +60,20 @@ def main() -> None:
         q, s = fp8fmt.quantize_block128(w[:, rank * ks:(rank + 1) * ks].contiguous())
         pl = gemm.PackedLinear.from_fp8(q, s)
         xs = x[:, rank * ks:(rank + 1) * ks].contiguous()
-        got = comm.linear_allreduce(xs, pl, residual=r)
-        got2 = comm.linear_allreduce(xs, pl, residual=r)
-        torch.cuda.synchronize()
-        comm.check()
         part = gemm.linear(xs, pl, stream=False).float()
         dist.all_reduce(part)
         want = part + r.float()
-        err = (got.float() - want).abs().max() / want.abs().max()
-        assert err < 2e-2, ("gemm_allreduce", t, n, kfull, err.item())
-        assert torch.equal(got, got2)
+        for two_shot in (False, True):
+            got = comm.linear_allreduce(xs, pl, residual=r, two_shot=two_shot).clone()
+            got2 = comm.linear_allreduce(xs, pl, residual=r, two_shot=two_shot).clone()
+            torch.cuda.synchronize()
+            comm.check()
+            err = (got.float() - want).abs().max() / want.abs().max()
+            assert err < 2e-2, ("gemm_allreduce", two_shot, t, n, kfull, err.item())
+            assert torch.equal(got, got2)
+            ref = got.clone()
+            dist.broadcast(ref, 0)
+            assert torch.equal(ref, got), ("fused all-reduce not identical across ranks", two_shot, t, n)
 
     # tensor-parallel model == single-rank model (greedy tokens)
     cfg = qh.QwenHybridConfig.tiny(layers=4)
