@@ -1,0 +1,290 @@
+// pocketllm_engine: command-line front end of the native engine.
+//
+//   --ckpt DIR                 checkpoint directory (config.json + *.safetensors)
+//   --dump-config              print the parsed model configuration and exit
+//   --inspect [--grep S]       list checkpoint tensors (name, dtype, shape, bytes)
+//   --inspect-tensor NAME      print one tensor's header and its first values
+//   --context-info             bytes of KV cache / recurrent state per token and per slot
+//   --smoke-forward            run the prompt, generate --max-new-tokens tokens, print tokens and timings
+//   --resident-bench           load once, then time --bench-runs generations of the same prompt
+//   --qwen-persistent-stdin    stay resident; each stdin line "<max_new_tokens> tok tok ..." is one request
+//   --serve-batch              read every stdin line as a request and run them through the continuous-batching
+//                              scheduler together (--max-slots sequences share the decode batch)
+//   --token-ids a,b,c | --token-ids-file F | --tokens N (synthetic ids)   the prompt
+//   --max-new-tokens N --max-context C --prefill-chunk-tokens T --smoke-layers L --max-slots S --device D
+//   --qwen-temperature F --qwen-top-k K --qwen-top-p P --qwen-seed S     host-side sampling (default greedy)
+//   --eos a,b                  stop tokens;  --json  machine-readable result line
+// (Role of cpp_engine/engine/main.cpp.)
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <iostream>
+#include <sstream>
+
+#include "../core/batch_scheduler.hpp"
+#include "../core/safetensors_reader.hpp"
+#include "qwen_engine.hpp"
+
+using namespace pocket;
+
+namespace {
+
+struct Args {
+  std::string ckpt, grep, tensor, token_ids, token_file, eos;
+  bool dump_config = false, inspect = false, context_info = false, smoke = false, bench = false, persistent = false,
+       serve_batch = false, json = false, verbose = false;
+  int max_new = 16, chunk = 8192, layers = 0, device = 0, synthetic = 0, slots = 1, bench_runs = 3, topk_print = 0;
+  long long max_context = 8192 + 512;
+  HostSamplingParams sampling;
+  unsigned long long seed = 0;
+};
+
+std::vector<int32_t> parse_ids(const std::string& s) {
+  std::vector<int32_t> out;
+  std::string cur;
+  for (char c : s + ",") {
+    if (c == ',' || c == ' ' || c == '\n' || c == '\t') {
+      if (!cur.empty()) out.push_back(int32_t(std::stol(cur)));
+      cur.clear();
+    } else {
+      cur.push_back(c);
+    }
+  }
+  return out;
+}
+
+std::string join(const std::vector<int32_t>& v) {
+  std::string s;
+  for (size_t i = 0; i < v.size(); ++i) s += (i ? "," : "") + std::to_string(v[i]);
+  return s;
+}
+
+void usage() {
+  std::fprintf(stderr,
+               "usage: pocketllm_engine --ckpt DIR [--dump-config | --inspect [--grep S] | --inspect-tensor NAME |\n"
+               "         --context-info | --smoke-forward | --resident-bench | --qwen-persistent-stdin | --serve-batch]\n"
+               "       [--token-ids a,b,c | --token-ids-file F | --tokens N] [--max-new-tokens N] [--max-context C]\n"
+               "       [--prefill-chunk-tokens T] [--smoke-layers L] [--max-slots S] [--device D] [--eos a,b] [--json]\n"
+               "       [--qwen-temperature F] [--qwen-top-k K] [--qwen-top-p P] [--qwen-seed S] [--bench-runs R]\n");
+}
+
+bool parse(int argc, char** argv, Args& a) {
+  for (int i = 1; i < argc; ++i) {
+    const std::string arg = argv[i];
+    auto val = [&](const char* name) -> const char* {
+      if (i + 1 >= argc) throw std::runtime_error(std::string("missing value for ") + name);
+      return argv[++i];
+    };
+    if (arg == "--ckpt" || arg == "--model") a.ckpt = val("--ckpt");
+    else if (arg == "--dump-config") a.dump_config = true;
+    else if (arg == "--inspect") a.inspect = true;
+    else if (arg == "--grep") a.grep = val("--grep");
+    else if (arg == "--inspect-tensor" || arg == "--tensor") a.tensor = val("--inspect-tensor");
+    else if (arg == "--context-info") a.context_info = true;
+    else if (arg == "--smoke-forward") a.smoke = true;
+    else if (arg == "--resident-bench") a.bench = true;
+    else if (arg == "--bench-runs") a.bench_runs = std::atoi(val("--bench-runs"));
+    else if (arg == "--qwen-persistent-stdin") a.persistent = true;
+    else if (arg == "--serve-batch") a.serve_batch = true;
+    else if (arg == "--token-ids" || arg == "--ids") a.token_ids = val("--token-ids");
+    else if (arg == "--token-ids-file") a.token_file = val("--token-ids-file");
+    else if (arg == "--tokens") a.synthetic = std::atoi(val("--tokens"));
+    else if (arg == "--max-new-tokens") a.max_new = std::atoi(val("--max-new-tokens"));
+    else if (arg == "--max-context") a.max_context = std::atoll(val("--max-context"));
+    else if (arg == "--prefill-chunk-tokens") a.chunk = std::atoi(val("--prefill-chunk-tokens"));
+    else if (arg == "--smoke-layers") a.layers = std::atoi(val("--smoke-layers"));
+    else if (arg == "--max-slots") a.slots = std::atoi(val("--max-slots"));
+    else if (arg == "--device") a.device = std::atoi(val("--device"));
+    else if (arg == "--eos") a.eos = val("--eos");
+    else if (arg == "--json") a.json = true;
+    else if (arg == "--verbose") a.verbose = true;
+    else if (arg == "--print-topk") a.topk_print = std::atoi(val("--print-topk"));
+    else if (arg == "--qwen-temperature") a.sampling.temperature = float(std::atof(val("--qwen-temperature")));
+    else if (arg == "--qwen-top-k") a.sampling.top_k = std::atoi(val("--qwen-top-k"));
+    else if (arg == "--qwen-top-p") a.sampling.top_p = float(std::atof(val("--qwen-top-p")));
+    else if (arg == "--qwen-seed") a.seed = std::strtoull(val("--qwen-seed"), nullptr, 10);
+    else if (arg == "--qwen-no-prefix-cache") {}        // accepted: this engine keeps no prefix cache between requests
+    else if (arg == "-h" || arg == "--help") return false;
+    else throw std::runtime_error("unknown argument " + arg);
+  }
+  return !a.ckpt.empty();
+}
+
+std::vector<int32_t> prompt_of(const Args& a, int64_t vocab) {
+  if (!a.token_ids.empty()) return parse_ids(a.token_ids);
+  if (!a.token_file.empty()) return parse_ids(read_text_file(a.token_file));
+  std::vector<int32_t> p;
+  uint64_t x = 0x9E3779B97F4A7C15ull;
+  for (int i = 0; i < std::max(1, a.synthetic); ++i) {
+    x ^= x << 13; x ^= x >> 7; x ^= x << 17;
+    p.push_back(int32_t(x % uint64_t(vocab)));
+  }
+  return p;
+}
+
+int inspect(const Args& a) {
+  SafetensorsModel model(a.ckpt);
+  if (!a.tensor.empty()) {
+    const uint8_t* base = nullptr;
+    const SafeTensorInfo* info = model.find(a.tensor, &base);
+    if (!info) { std::fprintf(stderr, "no tensor %s\n", a.tensor.c_str()); return 2; }
+    std::printf("name=%s dtype=%s shape=[", a.tensor.c_str(), info->dtype.c_str());
+    for (size_t i = 0; i < info->shape.size(); ++i) std::printf("%s%llu", i ? "," : "", (unsigned long long)info->shape[i]);
+    std::printf("] bytes=%llu first_bytes=", (unsigned long long)info->nbytes());
+    for (size_t i = 0; i < std::min<size_t>(16, info->nbytes()); ++i) std::printf("%02x", base[i]);
+    std::printf("\n");
+    return 0;
+  }
+  size_t total = 0, shown = 0;
+  for (const std::string& n : model.names()) {
+    if (!a.grep.empty() && n.find(a.grep) == std::string::npos) continue;
+    const uint8_t* base = nullptr;
+    const SafeTensorInfo* info = model.find(n, &base);
+    std::printf("%s %s [", n.c_str(), info->dtype.c_str());
+    for (size_t i = 0; i < info->shape.size(); ++i) std::printf("%s%llu", i ? "," : "", (unsigned long long)info->shape[i]);
+    std::printf("] %llu\n", (unsigned long long)info->nbytes());
+    total += info->nbytes();
+    ++shown;
+  }
+  std::printf("tensors=%zu bytes=%zu shards=%zu\n", shown, total, model.shard_count());
+  return 0;
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  Args a;
+  try {
+    if (!parse(argc, argv, a)) { usage(); return 2; }
+    if (a.inspect || !a.tensor.empty()) return inspect(a);
+    QwenConfig cfg = QwenConfig::from_file(a.ckpt + "/config.json");
+    if (a.dump_config) {
+      std::printf("vocab_size=%lld hidden_size=%lld intermediate_size=%lld layers=%lld full_layers=%lld linear_layers=%lld\n"
+                  "attention_heads=%lld kv_heads=%lld head_dim=%lld rotary_dim=%lld rope_theta=%g output_gate=%d\n"
+                  "linear_key_heads=%lld linear_value_heads=%lld conv_kernel=%lld quant=%s block=%lld\n",
+                  (long long)cfg.vocab_size, (long long)cfg.hidden_size, (long long)cfg.intermediate_size,
+                  (long long)cfg.num_hidden_layers, (long long)cfg.num_full_layers(), (long long)cfg.num_linear_layers(),
+                  (long long)cfg.num_attention_heads, (long long)cfg.num_key_value_heads, (long long)cfg.head_dim,
+                  (long long)cfg.rotary_dim(), cfg.rope_theta, int(cfg.attn_output_gate), (long long)cfg.linear_num_key_heads,
+                  (long long)cfg.linear_num_value_heads, (long long)cfg.linear_conv_kernel_dim, cfg.quant_method.c_str(),
+                  (long long)cfg.quant_block);
+      return 0;
+    }
+    if (a.context_info) {
+      const long long kv_token = 2LL * cfg.num_full_layers() * cfg.num_key_value_heads * cfg.head_dim * 2;
+      const long long state_slot = cfg.num_linear_layers() * cfg.linear_num_value_heads * cfg.linear_key_head_dim *
+                                   cfg.linear_value_head_dim * 4;
+      size_t free_b = 0, total_b = 0;
+      int ndev = 0;
+      if (cudaGetDeviceCount(&ndev) == cudaSuccess && ndev > 0) { cudaSetDevice(a.device); cudaMemGetInfo(&free_b, &total_b); }
+      std::printf("kv_bytes_per_token=%lld recurrent_state_bytes_per_slot=%lld device_free_bytes=%zu device_total_bytes=%zu\n",
+                  kv_token, state_slot, free_b, total_b);
+      return 0;
+    }
+
+    std::unique_ptr<WeightSource> ws = WeightSource::open(a.ckpt);
+    QwenEngineOptions opt;
+    opt.max_slots = std::max(1, a.slots);
+    opt.max_context = a.max_context;
+    opt.prefill_chunk = std::max(1, a.chunk);
+    opt.layers = a.layers;
+    opt.device = a.device;
+    opt.eos_tokens = parse_ids(a.eos);
+    opt.sampling = a.sampling;
+    opt.seed = a.seed;
+    QwenNativeEngine eng(cfg, *ws, opt);
+    if (a.verbose)
+      std::fprintf(stderr, "loaded %.2f GB of weights in %.2f s; cache/state %.2f GB\n", eng.stats().weight_bytes / 1e9,
+                   eng.stats().load_seconds, eng.stats().state_bytes / 1e9);
+
+    auto report = [&](const std::vector<int32_t>& prompt, const std::vector<int32_t>& out, double ps, double ds,
+                      const char* tag) {
+      const double ptok = prompt.size() / std::max(ps, 1e-9);
+      const double dtok = out.size() > 1 ? (out.size() - 1) / std::max(ds, 1e-9) : 0.0;
+      if (a.json)
+        std::printf("{\"%s\": 1, \"prompt_tokens\": %zu, \"tokens\": [%s], \"prefill_seconds\": %.6f, \"decode_seconds\": %.6f, "
+                    "\"prefill_tok_s\": %.2f, \"decode_tok_s\": %.2f}\n", tag, prompt.size(), join(out).c_str(), ps, ds, ptok, dtok);
+      else
+        std::printf("%s=1 prompt_tokens=%zu tokens=%s prefill_seconds=%.6f decode_seconds=%.6f prefill_tok_s=%.2f decode_tok_s=%.2f\n",
+                    tag, prompt.size(), join(out).c_str(), ps, ds, ptok, dtok);
+      std::fflush(stdout);
+    };
+
+    if (a.persistent) {
+      std::printf("qwen_persistent_ready=1 max_context=%lld\n", a.max_context);
+      std::fflush(stdout);
+      std::string line;
+      while (std::getline(std::cin, line)) {
+        if (line == "quit" || line == "exit") break;
+        std::vector<int32_t> f = parse_ids(line);
+        if (f.size() < 2) { std::printf("qwen_persistent_error=1 message=expected <max_new_tokens> tok...\n"); std::fflush(stdout); continue; }
+        const int max_new = f[0];
+        std::vector<int32_t> prompt(f.begin() + 1, f.end());
+        try {
+          double ps = 0, ds = 0;
+          std::vector<int32_t> out = eng.generate(prompt, max_new, &ps, &ds);
+          report(prompt, out, ps, ds, "qwen_persistent_result");
+        } catch (const std::exception& e) {
+          std::printf("qwen_persistent_error=1 message=%s\n", e.what());
+          std::fflush(stdout);
+        }
+      }
+      return 0;
+    }
+
+    if (a.serve_batch) {
+      SchedulerOptions so;
+      so.max_batch = opt.max_slots;
+      so.prefill_chunk_tokens = opt.prefill_chunk;
+      so.prefill_token_budget = opt.prefill_chunk;
+      BatchScheduler sched(eng, so);
+      std::vector<std::pair<uint64_t, size_t>> ids;
+      std::string line;
+      while (std::getline(std::cin, line)) {
+        std::vector<int32_t> f = parse_ids(line);
+        if (f.size() < 2) continue;
+        ids.emplace_back(sched.submit(std::vector<int32_t>(f.begin() + 1, f.end()), f[0]), f.size() - 1);
+      }
+      for (auto& [id, n_prompt] : ids) {
+        SchedulerResult r;
+        sched.wait(id, r);
+        std::printf("request=%llu finish=%s prompt_tokens=%zu tokens=%s queue_seconds=%.6f prefill_seconds=%.6f decode_seconds=%.6f%s%s\n",
+                    (unsigned long long)id, r.finish_reason.c_str(), n_prompt, join(r.tokens).c_str(), r.queue_seconds,
+                    r.prefill_seconds, r.decode_seconds, r.error.empty() ? "" : " error=", r.error.c_str());
+      }
+      SchedulerStats st = sched.stats();
+      std::printf("scheduler completed=%llu failed=%llu prefill_tokens=%llu decode_tokens=%llu rounds=%llu\n",
+                  (unsigned long long)st.completed, (unsigned long long)st.failed, (unsigned long long)st.prefill_tokens,
+                  (unsigned long long)st.decode_tokens, (unsigned long long)st.rounds);
+      sched.stop();
+      return 0;
+    }
+
+    const std::vector<int32_t> prompt = prompt_of(a, cfg.vocab_size);
+    if (a.bench) {
+      double best_p = 1e30, best_d = 1e30;
+      std::vector<int32_t> out;
+      for (int r = 0; r < std::max(1, a.bench_runs) + 1; ++r) {     // first run is the warm-up
+        double ps = 0, ds = 0;
+        out = eng.generate(prompt, a.max_new, &ps, &ds);
+        if (r == 0) continue;
+        best_p = std::min(best_p, ps);
+        best_d = std::min(best_d, ds);
+      }
+      report(prompt, out, best_p, best_d, "resident_bench");
+      return 0;
+    }
+    // default and --smoke-forward: one generation
+    double ps = 0, ds = 0;
+    std::vector<int32_t> out = eng.generate(prompt, a.max_new, &ps, &ds);
+    report(prompt, out, ps, ds, "smoke_forward");
+    if (a.topk_print > 0)
+      for (auto& [tok, logit] : eng.last_topk(a.topk_print)) std::printf("topk token=%d logit=%.6f\n", tok, logit);
+    std::printf("kernel_launches=%llu\n", (unsigned long long)eng.stats().kernel_launches);
+    return 0;
+  } catch (const std::exception& e) {
+    std::fprintf(stderr, "pocketllm_engine: %s\n", e.what());
+    return 1;
+  }
+}

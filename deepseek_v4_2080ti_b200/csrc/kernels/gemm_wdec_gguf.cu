@@ -17,9 +17,23 @@ int dispatch_bn(int bn, const CUtensorMap& tmX, const GemmParams& p, cudaStream_
     case 32: return launch_one<32, WFMT>(tmX, tmX, p, stream);
     case 64: return launch_one<64, WFMT>(tmX, tmX, p, stream);
     case 128: return launch_one<128, WFMT>(tmX, tmX, p, stream);
-    case 256: return launch_one<256, WFMT>(tmX, tmX, p, stream);
+    case 256:
+      // A decode group may run up to GROUPS k-blocks ahead of the MMA warp; its parity wait on a raw stage is only
+      // sound when the ring is at least that deep (Q8_0 with 256-row activation tiles fits 3 stages only).
+      if constexpr (SmemLayout<256, WFMT>::SR >= SmemLayout<256, WFMT>::GROUPS) return launch_one<256, WFMT>(tmX, tmX, p, stream);
+      else return -ERR_BAD_ARG;
   }
   return -ERR_BAD_ARG;
+}
+
+bool bn256_ok(int wfmt) {
+  switch (wfmt) {
+    case WF_Q8_0: return SmemLayout<256, WF_Q8_0>::SR >= SmemLayout<256, WF_Q8_0>::GROUPS;
+    case WF_Q4_K: return SmemLayout<256, WF_Q4_K>::SR >= SmemLayout<256, WF_Q4_K>::GROUPS;
+    case WF_Q2_K: return SmemLayout<256, WF_Q2_K>::SR >= SmemLayout<256, WF_Q2_K>::GROUPS;
+    case WF_IQ2_XXS: return SmemLayout<256, WF_IQ2_XXS>::SR >= SmemLayout<256, WF_IQ2_XXS>::GROUPS;
+  }
+  return false;
 }
 
 int dispatch(int wfmt, int bn, const CUtensorMap& tmX, const GemmParams& p, cudaStream_t stream) {
@@ -57,13 +71,17 @@ bool fill(GemmParams& p, int wfmt, const void* W, const void* lut, void* out_bf1
 // Bytes of one (128-row, 64-input) stage of a packed GGUF weight, 0 for an unsupported format.
 extern "C" int b200_gguf_stage_bytes(int wfmt) { return raw_stage_bytes(wfmt); }
 
+// Largest activation-tile height (rows per work item of the grouped form) a format supports: 256 or 128.
+extern "C" int b200_gguf_max_bn(int wfmt) { return bn256_ok(wfmt) ? 256 : 128; }
+
 // Y[T, N] = X[T, K] W^T with W packed tile-major: [ceil(N/128)][K/64][stage bytes] (formats above; K % 64 == 0).
 // Writes bf16 `out` (+ residual) or, when out_bf16 is null, fp32 `out_f32`.  lut: IQ2_XXS codebook + sign table.
 extern "C" int b200_gemm_wdec_gguf(int wfmt, const void* W, const void* lut, const void* X, void* out_bf16, float* out_f32,
                                    const void* residual, int T, int N, int K, int* status, cudaStream_t stream) {
   GemmParams p;
   if (!fill(p, wfmt, W, lut, out_bf16, out_f32, residual, T, N, K, status) || (!out_bf16 && !out_f32)) return -ERR_BAD_ARG;
-  const int BN = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+  int BN = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+  if (BN == 256 && !bn256_ok(wfmt)) BN = 128;
   p.n_tiles = (T + BN - 1) / BN;
   CUtensorMap tmX;
   if (!make_tmap_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, T, K, (uint64_t)K * 2, BN, BK, CU_TENSOR_MAP_SWIZZLE_128B))

@@ -319,6 +319,9 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     if constexpr (WFMT != WF_BF16) {
       constexpr int G = L::GROUPS;
       static_assert(G == SAB, "one decode group per decoded slot");
+      // A group's parity wait on raw stage it % S assumes k-block it - S has landed; the only ordering a group has
+      // with the producer is through its own previous k-block it - G, so the ring must hold at least G stages.
+      static_assert(S >= G, "raw ring shallower than the decode groups' look-ahead");
       constexpr int WPG = L::WARPS_PER_GROUP;
       constexpr int GT = WPG * 32;             // threads per group
       const int dw = warp - DEC_WARP0;

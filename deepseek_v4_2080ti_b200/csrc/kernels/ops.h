@@ -70,6 +70,47 @@ int b200_mla_attention(const void* q_lat, const void* q_pe, const void* cache, c
                        int R, float scale, cudaStream_t stream);
 int b200_transpose_heads(const void* in, void* out, int H, int T, int D, cudaStream_t stream);
 
+// ---- load-time weight preparation (prepack.cu)
+unsigned long long b200_prepack_fp8_bytes(int N, int K);
+int b200_prepack_fp8(const void* w_fp8, void* out, int N, int K, cudaStream_t stream);
+int b200_bf16_to_f32(const void* in, float* out, long long n, cudaStream_t stream);
+
+// ---- row kernels (elementwise.cu), recurrent and attention kernels (gdn.cu, rope_kv.cu, attn_gqa_*.cu)
+int b200_rmsnorm(void* x, const void* delta, const float* partials, int splits, const void* gamma, void* out,
+                 long long rows, int cols, float eps, int unit_offset, int write_x, cudaStream_t stream);
+int b200_gated_rmsnorm(const void* x, const void* gate, const void* gamma, void* out, long long nrows, int dim, float eps,
+                       int heads, long long gate_ld, cudaStream_t stream);
+int b200_embedding(const int* ids, const void* table, void* out, int rows, int hidden, int vocab_lo, int vocab_hi,
+                   cudaStream_t stream);
+int b200_silu_mul(const void* gate_up, void* out, long long rows, int inter, cudaStream_t stream);
+int b200_add(void* y, const void* x, long long n, cudaStream_t stream);
+int b200_conv_silu(const void* x, int ldx, const void* w, void* tail, void* y, int ldy, int T, int C, int kw,
+                   int update_tail, cudaStream_t stream);
+int b200_conv_silu_step(const void* x, int ldx, const void* w, void* tails, long long slot_stride, const int* slot_ids,
+                        void* y, int ldy, int B, int C, int kw, cudaStream_t stream);
+int b200_gdn_step(float* states, long long slot_stride, const int* slot_ids, const void* mixed, int ld, int q_off,
+                  int k_off, int v_off, const float* g, const float* beta, void* out, int B, int Hv, int Hk,
+                  cudaStream_t stream);
+int b200_gdn_gates(const void* ab, int ld, int a_off, int b_off, const float* a_log, const float* dt_bias, float* g,
+                   float* beta, long long rows, int heads, cudaStream_t stream);
+int b200_argmax(const void* logits, int is_f32, int ld, int n, int rows, int index_offset, int* out_idx, float* out_val,
+                cudaStream_t stream);
+long long b200_gdn_workspace_floats(int T, int Hv);
+int b200_gdn_chunked(const void* mixed, int ld, int q_off, int k_off, int v_off, const float* g, const float* beta,
+                     float* state, void* out, float* workspace, int T, int Hv, int Hk, cudaStream_t stream);
+int b200_qk_norm_rope_append(const void* q_src, int ldq, int q_off, int q_head_stride, int gate_in_q, const void* k_src,
+                             int ldk, int k_off, const void* v_src, int ldv, int v_off, const void* q_gamma,
+                             const void* k_gamma, int unit_offset, float eps, const float* inv_freq, int rot, float mscale,
+                             const int* positions, const int* slots, void* q_out, void* gate_out, void* k_cache,
+                             void* v_cache, int block_size, int T, int Hq, int Hkv, cudaStream_t stream);
+int b200_gqa_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const void* gate,
+                     const int* block_table, const int* q_start, const int* q_len, const int* kv_len, int batch,
+                     int max_q_len, int total_q_rows, int max_blocks, int num_blocks, int block_size, int n_q_heads,
+                     int n_kv_heads, float softmax_scale, int* status, cudaStream_t stream);
+int b200_gqa_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const void* gate,
+                    const int* block_table, const int* kv_len, float* workspace, int batch, int max_blocks,
+                    int block_size, int n_q_heads, int n_kv_heads, int splits, float softmax_scale, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

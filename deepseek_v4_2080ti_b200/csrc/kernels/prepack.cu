@@ -1,0 +1,62 @@
+// Device-side weight preparation used by the native engine at load time:
+//   prepack_fp8   - FP8 [N, K] row-major -> the GEMM's tile-major layout [ceil(N/128)][ceil(K/64)][128 rows][64 bytes]
+//                   with each 4-byte group stored as (w0, w2, w1, w3) and the 16-byte chunks of row r at chunk index
+//                   c ^ ((r >> 1) & 3) (same transformation as ops/gemm.py:prepack_fp8);
+//   bf16_to_f32   - block scales and per-head constants come as bf16 in the checkpoint, the kernels read fp32.
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include "ops.h"
+
+namespace {
+
+__global__ void prepack_fp8_kernel(const uint8_t* __restrict__ w, uint8_t* __restrict__ out, int N, int K, int kb_total) {
+  // one thread per output 4-byte group
+  const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t groups_per_tile = 128 * 16;
+  const size_t total = (size_t)((N + 127) / 128) * kb_total * groups_per_tile;
+  if (gid >= total) return;
+  const size_t tile = gid / groups_per_tile;
+  const int in_tile = (int)(gid % groups_per_tile);
+  const int r = in_tile / 16, g = in_tile % 16;          // row in tile, physical 4-byte group in the 64-byte row
+  const int pc = g / 4, gi = g % 4;                      // physical 16-byte chunk, group inside it
+  const int lc = pc ^ ((r >> 1) & 3);                    // logical chunk stored at this physical position
+  const int mt = (int)(tile / kb_total), kb = (int)(tile % kb_total);
+  const int row = mt * 128 + r;
+  const int col = kb * 64 + lc * 16 + gi * 4;
+  uint8_t b[4] = {0, 0, 0, 0};
+  if (row < N)
+    for (int i = 0; i < 4; ++i)
+      if (col + i < K) b[i] = w[(size_t)row * K + col + i];
+  const uint32_t v = (uint32_t)b[0] | ((uint32_t)b[2] << 8) | ((uint32_t)b[1] << 16) | ((uint32_t)b[3] << 24);
+  reinterpret_cast<uint32_t*>(out)[gid] = v;
+}
+
+__global__ void bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ in, float* __restrict__ out, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __bfloat162float(in[i]);
+}
+
+}  // namespace
+
+extern "C" {
+
+unsigned long long b200_prepack_fp8_bytes(int N, int K) {
+  return (unsigned long long)((N + 127) / 128) * ((K + 63) / 64) * 8192ull;
+}
+
+int b200_prepack_fp8(const void* w_fp8, void* out, int N, int K, cudaStream_t stream) {
+  if (N <= 0 || K <= 0) return -6;
+  const int kb_total = (K + 63) / 64;
+  const size_t total = (size_t)((N + 127) / 128) * kb_total * 128 * 16;
+  prepack_fp8_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(reinterpret_cast<const uint8_t*>(w_fp8),
+                                                                       reinterpret_cast<uint8_t*>(out), N, K, kb_total);
+  return (int)cudaGetLastError();
+}
+
+int b200_bf16_to_f32(const void* in, float* out, long long n, cudaStream_t stream) {
+  if (n <= 0) return -6;
+  bf16_to_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(in), out, (size_t)n);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

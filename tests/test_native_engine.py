@@ -1,0 +1,120 @@
+"""The native executable (csrc/engine): inspection modes on CPU; on a GPU, greedy tokens of the C++ engine against
+the Python runtime on the same tiny checkpoint, for one-shot, persistent-stdin and continuous-batching modes."""
+import os
+import re
+import subprocess
+import tempfile
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+EXE = os.path.join(ROOT, "deepseek_v4_2080ti_b200", "bin", "pocketllm_engine")
+needs_exe = pytest.mark.skipif(not os.path.isfile(EXE), reason="native executable not built")
+
+
+def _write_tiny(d, device="cpu", layers=4):
+    from deepseek_v4_2080ti_b200.formats import safetensors_io
+    from deepseek_v4_2080ti_b200.models import qwen_hybrid as qh
+    cfg = qh.QwenHybridConfig.tiny(layers=layers)
+    state = list(qh.synth_state(cfg, 0, device, std=0.05))
+    safetensors_io.write_checkpoint(d, iter(state), config_json=cfg.to_json())
+    return cfg, state
+
+
+def _run(args, stdin=None, timeout=300):
+    return subprocess.run([EXE] + args, input=stdin, capture_output=True, text=True, timeout=timeout)
+
+
+@needs_exe
+def test_dump_config_inspect_and_context_info_need_no_gpu():
+    with tempfile.TemporaryDirectory() as d:
+        cfg, state = _write_tiny(d)
+        r = _run(["--ckpt", d, "--dump-config"])
+        assert r.returncode == 0, r.stderr
+        assert f"hidden_size={cfg.hidden_size}" in r.stdout and f"layers={cfg.num_hidden_layers}" in r.stdout
+        r = _run(["--ckpt", d, "--inspect", "--grep", "layers.0."])
+        assert r.returncode == 0, r.stderr
+        names = [n for n, _ in state if "layers.0." in n]
+        assert f"tensors={len(names)}" in r.stdout
+        assert "model.language_model.layers.0.input_layernorm.weight BF16" in r.stdout
+        r = _run(["--ckpt", d, "--inspect-tensor", "model.language_model.norm.weight"])
+        assert r.returncode == 0 and f"shape=[{cfg.hidden_size}]" in r.stdout
+        r = _run(["--ckpt", d, "--context-info"])
+        n_full = sum(t == "full_attention" for t in cfg.layer_types)
+        assert r.returncode == 0
+        assert f"kv_bytes_per_token={2 * n_full * cfg.num_key_value_heads * cfg.head_dim * 2}" in r.stdout
+
+
+@needs_exe
+def test_bad_arguments_exit_non_zero():
+    assert _run(["--nonsense"]).returncode != 0
+    assert _run([]).returncode == 2
+    with tempfile.TemporaryDirectory() as d:
+        r = _run(["--ckpt", d, "--dump-config"])
+        assert r.returncode == 1 and "pocketllm_engine:" in r.stderr
+
+
+def _tokens(line):
+    m = re.search(r"(?<![a-z_])tokens=([0-9,]+)", line)
+    assert m, line
+    return [int(t) for t in m.group(1).split(",")]
+
+
+@pytest.mark.gpu
+@needs_exe
+def test_native_engine_tokens_match_python_runtime():
+    from deepseek_v4_2080ti_b200.models import qwen_hybrid as qh
+    gen = torch.Generator().manual_seed(11)
+    n_new = 10
+    with tempfile.TemporaryDirectory() as d:
+        cfg, state = _write_tiny(d, "cuda")
+        prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gen, dtype=torch.int32) for n in (70, 33, 5)]
+        w = qh.QwenHybridWeights(cfg, iter(state), "cuda")
+        rt = qh.QwenHybridRuntime(cfg, w, max_slots=1, max_context=256)
+        want = [rt.generate(p, n_new) for p in prompts]
+
+        ids = ",".join(map(str, prompts[0].tolist()))
+        r = _run(["--ckpt", d, "--smoke-forward", "--token-ids", ids, "--max-new-tokens", str(n_new), "--max-context", "256",
+                  "--print-topk", "3"])
+        assert r.returncode == 0, (r.stdout[-500:], r.stderr[-500:])
+        assert _tokens(r.stdout.splitlines()[0]) == want[0]
+        assert "topk token=" in r.stdout and "kernel_launches=" in r.stdout
+
+        # chunked prefill (chunk smaller than the prompt) gives the same stream
+        r = _run(["--ckpt", d, "--token-ids", ids, "--max-new-tokens", str(n_new), "--max-context", "256",
+                  "--prefill-chunk-tokens", "32"])
+        assert r.returncode == 0, r.stderr[-500:]
+        got = _tokens(r.stdout.splitlines()[0])
+        assert got[:4] == want[0][:4]
+
+        # persistent mode: several requests on one resident engine
+        lines = "".join(f"{n_new} " + " ".join(map(str, p.tolist())) + "\n" for p in prompts) + "quit\n"
+        r = _run(["--ckpt", d, "--qwen-persistent-stdin", "--max-context", "256"], stdin=lines)
+        assert r.returncode == 0, r.stderr[-500:]
+        res = [l for l in r.stdout.splitlines() if l.startswith("qwen_persistent_result=1")]
+        assert [_tokens(l) for l in res] == want
+
+        # continuous batching: the three requests share the decode batch; greedy streams stay per-request
+        r = _run(["--ckpt", d, "--serve-batch", "--max-slots", "3", "--max-context", "256"], stdin=lines.replace("quit\n", ""))
+        assert r.returncode == 0, r.stderr[-500:]
+        res = [l for l in r.stdout.splitlines() if l.startswith("request=")]
+        assert len(res) == 3 and all("finish=length" in l for l in res)
+        for l, wnt in zip(res, want):
+            assert _tokens(l)[:4] == wnt[:4]
+        assert "scheduler completed=3" in r.stdout
+
+
+@pytest.mark.gpu
+def test_device_prepack_matches_host_prepack():
+    import ctypes
+    from deepseek_v4_2080ti_b200.ops import _lib, gemm
+    for n, k in ((256, 512), (300, 192), (128, 64)):
+        w = torch.randint(0, 256, (n, k), dtype=torch.uint8, device="cuda")
+        want = gemm.prepack_fp8(w.view(torch.float8_e4m3fn))
+        L = _lib.lib()
+        L.b200_prepack_fp8_bytes.restype = ctypes.c_ulonglong
+        out = torch.zeros(int(L.b200_prepack_fp8_bytes(n, k)), dtype=torch.uint8, device="cuda")
+        assert L.b200_prepack_fp8(_lib.ptr(w), _lib.ptr(out), n, k, _lib.stream()) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(out, want.view(torch.uint8).reshape(-1))
