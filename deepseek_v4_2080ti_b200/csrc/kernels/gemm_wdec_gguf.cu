@@ -1,4 +1,4 @@
-// Entry points of the weight-decoding GEMM for GGUF block-quantised weights (Q8_0, Q4_K, Q2_K, IQ2_XXS): the raw
+// Entry points of the weight-decoding GEMM for GGUF block-quantised weights (Q8_0, Q4_K, Q5_K, Q2_K, IQ1_M, IQ2_XXS, IQ3_XXS): the raw
 // blocks are decoded in registers by the decode warps of gemm_wdec_kernel.cuh into bf16 tensor-core tiles; no
 // dequantised copy of a weight matrix ever exists in memory.
 // Reference behaviour covered: the fused dequant GEMV / GEMM family for GGUF tensors
@@ -32,6 +32,9 @@ bool bn256_ok(int wfmt) {
     case WF_Q4_K: return SmemLayout<256, WF_Q4_K>::SR >= SmemLayout<256, WF_Q4_K>::GROUPS;
     case WF_Q2_K: return SmemLayout<256, WF_Q2_K>::SR >= SmemLayout<256, WF_Q2_K>::GROUPS;
     case WF_IQ2_XXS: return SmemLayout<256, WF_IQ2_XXS>::SR >= SmemLayout<256, WF_IQ2_XXS>::GROUPS;
+    case WF_Q5_K: return SmemLayout<256, WF_Q5_K>::SR >= SmemLayout<256, WF_Q5_K>::GROUPS;
+    case WF_IQ3_XXS: return SmemLayout<256, WF_IQ3_XXS>::SR >= SmemLayout<256, WF_IQ3_XXS>::GROUPS;
+    case WF_IQ1_M: return SmemLayout<256, WF_IQ1_M>::SR >= SmemLayout<256, WF_IQ1_M>::GROUPS;
   }
   return false;
 }
@@ -42,6 +45,9 @@ int dispatch(int wfmt, int bn, const CUtensorMap& tmX, const GemmParams& p, cuda
     case WF_Q4_K: return dispatch_bn<WF_Q4_K>(bn, tmX, p, stream);
     case WF_Q2_K: return dispatch_bn<WF_Q2_K>(bn, tmX, p, stream);
     case WF_IQ2_XXS: return dispatch_bn<WF_IQ2_XXS>(bn, tmX, p, stream);
+    case WF_Q5_K: return dispatch_bn<WF_Q5_K>(bn, tmX, p, stream);
+    case WF_IQ3_XXS: return dispatch_bn<WF_IQ3_XXS>(bn, tmX, p, stream);
+    case WF_IQ1_M: return dispatch_bn<WF_IQ1_M>(bn, tmX, p, stream);
   }
   return -ERR_BAD_ARG;
 }
@@ -49,7 +55,7 @@ int dispatch(int wfmt, int bn, const CUtensorMap& tmX, const GemmParams& p, cuda
 bool fill(GemmParams& p, int wfmt, const void* W, const void* lut, void* out_bf16, float* out_f32, const void* residual,
           int T, int N, int K, int* status) {
   if (T <= 0 || N <= 0 || K <= 0 || (K % 64) != 0 || gguf_qb(wfmt) == 0) return false;
-  if (wfmt == WF_IQ2_XXS && !lut) return false;
+  if ((wfmt == WF_IQ2_XXS || wfmt == WF_IQ3_XXS || wfmt == WF_IQ1_M) && !lut) return false;
   memset(&p, 0, sizeof(p));
   p.T = T; p.N = N; p.K = K;
   p.m_tiles = (N + BM - 1) / BM;
@@ -75,7 +81,8 @@ extern "C" int b200_gguf_stage_bytes(int wfmt) { return raw_stage_bytes(wfmt); }
 extern "C" int b200_gguf_max_bn(int wfmt) { return bn256_ok(wfmt) ? 256 : 128; }
 
 // Y[T, N] = X[T, K] W^T with W packed tile-major: [ceil(N/128)][K/64][stage bytes] (formats above; K % 64 == 0).
-// Writes bf16 `out` (+ residual) or, when out_bf16 is null, fp32 `out_f32`.  lut: IQ2_XXS codebook + sign table.
+// Writes bf16 `out` (+ residual) or, when out_bf16 is null, fp32 `out_f32`.  lut: the codebook table of the IQ formats (IQ2_XXS: 256 x 8 magnitudes + 128 sign bytes; IQ3_XXS: 256 x 4
+// magnitudes + 128 sign bytes; IQ1_M: 2048 x 8 int8).
 extern "C" int b200_gemm_wdec_gguf(int wfmt, const void* W, const void* lut, const void* X, void* out_bf16, float* out_f32,
                                    const void* residual, int T, int N, int K, int* status, cudaStream_t stream) {
   GemmParams p;

@@ -52,13 +52,22 @@ constexpr int NUM_THREADS = (DEC_WARP0 + NUM_DEC_WARPS) * 32;  // 448
 //   WF_Q4_K     QB 32 (low nibble = input l, high nibble = input 32 + l), SB 8: d, dmin (fp16), sc0, m0, sc1, m1 (6-bit values)
 //   WF_Q2_K     QB 16 (four 2-bit codes per byte: inputs l, 32 + l of byte l & 15 ...), SB 8: d, dmin (fp16), four scale|min bytes
 //   WF_IQ2_XXS  QB 16 (two original 8-byte groups of 32 inputs), SB 4: d (fp16)
-enum WFormat : int { WF_BF16 = 0, WF_FP8_B128 = 1, WF_FP4 = 2, WF_Q8_0 = 3, WF_Q4_K = 4, WF_Q2_K = 5, WF_IQ2_XXS = 6 };
+//   WF_Q5_K     QB 40 (Q4_K nibbles, then two 32-bit masks holding the fifth bit of inputs l and 32 + l), SB 8 as Q4_K
+//   WF_IQ3_XXS  QB 24 (16 grid indices, then the two sign/scale words of the stage's 32-input groups), SB 4: d (fp16)
+//   WF_IQ1_M    QB 12 (8 low index bytes, then 4 bytes of high index bits / delta signs), SB 4: d (fp16), one byte per
+//               32-input group holding its two 3-bit scales
+enum WFormat : int {
+  WF_BF16 = 0, WF_FP8_B128 = 1, WF_FP4 = 2, WF_Q8_0 = 3, WF_Q4_K = 4, WF_Q2_K = 5, WF_IQ2_XXS = 6, WF_Q5_K = 7,
+  WF_IQ3_XXS = 8, WF_IQ1_M = 9
+};
 
 __host__ __device__ constexpr int gguf_qb(int wfmt) {
-  return wfmt == WF_Q8_0 ? 64 : wfmt == WF_Q4_K ? 32 : wfmt == WF_Q2_K ? 16 : wfmt == WF_IQ2_XXS ? 16 : 0;
+  return wfmt == WF_Q8_0 ? 64 : wfmt == WF_Q4_K ? 32 : wfmt == WF_Q2_K ? 16 : wfmt == WF_IQ2_XXS ? 16
+         : wfmt == WF_Q5_K ? 40 : wfmt == WF_IQ3_XXS ? 24 : wfmt == WF_IQ1_M ? 12 : 0;
 }
 __host__ __device__ constexpr int gguf_sb(int wfmt) {
-  return wfmt == WF_Q8_0 ? 4 : wfmt == WF_Q4_K ? 8 : wfmt == WF_Q2_K ? 8 : wfmt == WF_IQ2_XXS ? 4 : 0;
+  return wfmt == WF_Q8_0 ? 4 : wfmt == WF_Q4_K ? 8 : wfmt == WF_Q2_K ? 8 : wfmt == WF_IQ2_XXS ? 4
+         : wfmt == WF_Q5_K ? 8 : wfmt == WF_IQ3_XXS ? 4 : wfmt == WF_IQ1_M ? 4 : 0;
 }
 __host__ __device__ constexpr int raw_stage_bytes(int wfmt) {
   return wfmt == WF_FP8_B128 ? 128 * 64
@@ -474,6 +483,55 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
                   const int nib = e < 16 ? (by & 15) : (by >> 4);
                   const int sb = srow[4 + 2 * hh + (e >> 4)];
                   v[e] = dd * (float)(sb & 15) * (float)((nib >> (2 * hh)) & 3) - dm * (float)(sb >> 4);
+                }
+              } else if constexpr (WFMT == WF_Q5_K) {
+                const float dd = __half2float(*reinterpret_cast<const __half*>(srow));
+                const float dm = __half2float(*reinterpret_cast<const __half*>(srow + 2));
+                const float sc = dd * (float)srow[4 + 2 * hh], mn = dm * (float)srow[5 + 2 * hh];
+                const uint2 a0 = *reinterpret_cast<const uint2*>(qrow), a1 = *reinterpret_cast<const uint2*>(qrow + 8),
+                            a2 = *reinterpret_cast<const uint2*>(qrow + 16), a3 = *reinterpret_cast<const uint2*>(qrow + 24);
+                const uint32_t w8[8] = {a0.x, a0.y, a1.x, a1.y, a2.x, a2.y, a3.x, a3.y};
+                const uint32_t hm = *reinterpret_cast<const uint32_t*>(qrow + 32 + 4 * hh);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                  const uint32_t by = (w8[e >> 2] >> (8 * (e & 3))) & 0xFF;
+                  const uint32_t q5 = (hh ? (by >> 4) : (by & 15)) | (((hm >> e) & 1u) << 4);
+                  v[e] = sc * (float)q5 - mn;
+                }
+              } else if constexpr (WFMT == WF_IQ3_XXS) {
+                const float dd = __half2float(*reinterpret_cast<const __half*>(srow));
+                const uint2 gi = *reinterpret_cast<const uint2*>(qrow + hh * 8);
+                const uint32_t aux = *reinterpret_cast<const uint32_t*>(qrow + 16 + hh * 4);
+                const float db = dd * (0.5f + (float)(aux >> 28)) * 0.5f;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  const uint32_t two = ((g < 2 ? gi.x : gi.y) >> (16 * (g & 1))) & 0xFFFF;
+                  const uint32_t g0 = __ldg(reinterpret_cast<const uint32_t*>(p.lut) + (two & 0xFF));
+                  const uint32_t g1 = __ldg(reinterpret_cast<const uint32_t*>(p.lut) + (two >> 8));
+                  const uint32_t sg = __ldg(p.lut + 1024 + ((aux >> (7 * g)) & 0x7F));
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    const uint32_t gv = ((e < 4 ? g0 : g1) >> (8 * (e & 3))) & 0xFF;
+                    v[g * 8 + e] = ((sg >> e) & 1) ? -db * (float)gv : db * (float)gv;
+                  }
+                }
+              } else if constexpr (WFMT == WF_IQ1_M) {
+                const float dd = __half2float(*reinterpret_cast<const __half*>(srow));
+                const uint32_t ql = *reinterpret_cast<const uint32_t*>(qrow + hh * 4);
+                const uint32_t qh = *reinterpret_cast<const uint32_t*>(qrow + 8) >> (16 * hh);
+                const uint32_t sby = srow[2 + hh];
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  const uint32_t nib = (qh >> (4 * g)) & 0xF;
+                  const uint32_t idx = ((ql >> (8 * g)) & 0xFF) | ((nib & 7) << 8);
+                  const float dl = dd * (float)(2 * ((sby >> (3 * (g >> 1))) & 7) + 1);
+                  const float delta = (nib & 8) ? -0.125f : 0.125f;
+                  const uint2 gr = __ldg(reinterpret_cast<const uint2*>(p.lut) + idx);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    const int gv = (int)(int8_t)(((e < 4 ? gr.x : gr.y) >> (8 * (e & 3))) & 0xFF);
+                    v[g * 8 + e] = dl * ((float)gv + delta);
+                  }
                 }
               } else if constexpr (WFMT == WF_IQ2_XXS) {
                 const float dd = __half2float(*reinterpret_cast<const __half*>(srow));

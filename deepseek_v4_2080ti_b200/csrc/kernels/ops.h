@@ -103,6 +103,13 @@ int b200_qk_norm_rope_append(const void* q_src, int ldq, int q_off, int q_head_s
                              const void* k_gamma, int unit_offset, float eps, const float* inv_freq, int rot, float mscale,
                              const int* positions, const int* slots, void* q_out, void* gate_out, void* k_cache,
                              void* v_cache, int block_size, int T, int Hq, int Hkv, cudaStream_t stream);
+int b200_qk_sumsq(const void* proj, int ld, int q_off, int q_width, int k_off, int k_width, float* out, int T,
+                  cudaStream_t stream);
+int b200_qk_fullnorm_rope_append(const void* q_src, int ldq, int q_off, const void* k_src, int ldk, int k_off,
+                                 const void* v_src, int ldv, int v_off, const void* q_gamma, const void* k_gamma,
+                                 const float* row_ss, int q_full_width, int k_full_width, float eps, const float* inv_freq,
+                                 int rot, const int* positions, const int* slots, void* q_out, void* k_cache,
+                                 void* v_cache, int block_size, int T, int Hq, int Hkv, cudaStream_t stream);
 int b200_gqa_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const void* gate,
                      const int* block_table, const int* q_start, const int* q_len, const int* kv_len, int batch,
                      int max_q_len, int total_q_rows, int max_blocks, int num_blocks, int block_size, int n_q_heads,

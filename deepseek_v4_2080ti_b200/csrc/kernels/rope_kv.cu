@@ -26,6 +26,9 @@ struct RopeParams {
   __nv_bfloat16* q_out; __nv_bfloat16* gate_out;                        // [T, Hq, 128]
   __nv_bfloat16* k_cache; __nv_bfloat16* v_cache; int bs;               // [nb, Hkv, bs, 128]
   int T, Hq, Hkv;
+  // full-width mode (row_ss != null): the RMS statistic of q / k is taken over the whole projection row (all heads,
+  // all ranks) and arrives precomputed as sums of squares [T, 2]; gamma is then indexed per head.
+  const float* row_ss; float q_full_width, k_full_width; int gamma_head_stride;
 };
 
 __device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&f)[4]) {
@@ -43,12 +46,18 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&f)[4]) {
 }
 
 __device__ __forceinline__ void norm_rope(float (&x)[4], const __nv_bfloat16* gamma, int unit_offset, float eps,
-                                          const float* inv_freq, int rot, float mscale, int pos, int lane) {
+                                          const float* inv_freq, int rot, float mscale, int pos, int lane,
+                                          float full_ss = -1.f, float full_width = 1.f) {
   if (gamma) {
-    float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+    float inv;
+    if (full_ss >= 0.f) {
+      inv = rsqrtf(full_ss / full_width + eps);
+    } else {
+      float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float inv = rsqrtf(ss / (float)D + eps);
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      inv = rsqrtf(ss / (float)D + eps);
+    }
     float g[4];
     load4(gamma + lane * 4, g);
 #pragma unroll
@@ -90,7 +99,8 @@ __global__ void qk_norm_rope_append_kernel(RopeParams p) {
   if (hh < p.Hq) {
     const __nv_bfloat16* src = p.q_src + (size_t)t * p.ldq + p.q_off + (size_t)hh * p.q_head_stride;
     load4(src + lane * 4, x);
-    norm_rope(x, p.q_gamma, p.unit_offset, p.eps, p.inv_freq, p.rot, p.mscale, pos, lane);
+    norm_rope(x, p.q_gamma ? p.q_gamma + (size_t)hh * p.gamma_head_stride : nullptr, p.unit_offset, p.eps, p.inv_freq,
+              p.rot, p.mscale, pos, lane, p.row_ss ? p.row_ss[2 * t] : -1.f, p.q_full_width);
     store4(p.q_out + ((size_t)t * p.Hq + hh) * D + lane * 4, x);
     if (p.gate_in_q && p.gate_out) {
       const uint2 g = *reinterpret_cast<const uint2*>(src + D + lane * 4);
@@ -99,7 +109,8 @@ __global__ void qk_norm_rope_append_kernel(RopeParams p) {
   } else if (hh < p.Hq + p.Hkv) {
     const int h = hh - p.Hq;
     load4(p.k_src + (size_t)t * p.ldk + p.k_off + h * D + lane * 4, x);
-    norm_rope(x, p.k_gamma, p.unit_offset, p.eps, p.inv_freq, p.rot, p.mscale, pos, lane);
+    norm_rope(x, p.k_gamma ? p.k_gamma + (size_t)h * p.gamma_head_stride : nullptr, p.unit_offset, p.eps, p.inv_freq,
+              p.rot, p.mscale, pos, lane, p.row_ss ? p.row_ss[2 * t + 1] : -1.f, p.k_full_width);
     const int slot = p.slots[t];
     if (slot >= 0)
       store4(p.k_cache + (((size_t)(slot / p.bs) * p.Hkv + h) * p.bs + slot % p.bs) * D + lane * 4, x);
@@ -112,7 +123,77 @@ __global__ void qk_norm_rope_append_kernel(RopeParams p) {
   }
 }
 
+// out[t] = (sum of squares of the q columns, of the k columns) of projection row t; one block per token.
+__global__ void qk_sumsq_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int q_width, int k_off,
+                                int k_width, float* __restrict__ out) {
+  const int t = blockIdx.x;
+  const __nv_bfloat16* row = proj + (size_t)t * ld;
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < q_width; i += blockDim.x) { const float v = __bfloat162float(row[q_off + i]); sq += v * v; }
+  for (int i = threadIdx.x; i < k_width; i += blockDim.x) { const float v = __bfloat162float(row[k_off + i]); sk += v * v; }
+  __shared__ float red[2][8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { sq += __shfl_xor_sync(0xffffffffu, sq, o); sk += __shfl_xor_sync(0xffffffffu, sk, o); }
+  if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = sq; red[1][threadIdx.x >> 5] = sk; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f, b = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { a += red[0][w]; b += red[1][w]; }
+    out[2 * t] = a;
+    out[2 * t + 1] = b;
+  }
+}
+
+int launch_rope(RopeParams& p, cudaStream_t stream) {
+  const int heads = p.Hq + 2 * p.Hkv;
+  const size_t warps = (size_t)p.T * heads;
+  const int wpb = 8;
+  qk_norm_rope_append_kernel<<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
 }  // namespace
+
+// Sums of squares of the q and k parts of each projection row (fp32 [T, 2]); with tensor parallelism the caller adds
+// the ranks' partial sums before the normalisation below.
+extern "C" int b200_qk_sumsq(const void* proj, int ld, int q_off, int q_width, int k_off, int k_width, float* out, int T,
+                             cudaStream_t stream) {
+  if (T <= 0 || q_width < 0 || k_width < 0) return -6;
+  qk_sumsq_kernel<<<T, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(proj), ld, q_off, q_width, k_off, k_width, out);
+  return (int)cudaGetLastError();
+}
+
+// Full-width QK RMSNorm variant (MiniMax-style: the statistic spans the whole q / k projection row, gamma has one
+// entry per (head, dim)): row_ss holds the rows' sums of squares, q_full_width / k_full_width the element counts they
+// were taken over; gamma pointers address this rank's heads, [H, 128].  Otherwise as b200_qk_norm_rope_append.
+extern "C" int b200_qk_fullnorm_rope_append(
+    const void* q_src, int ldq, int q_off, const void* k_src, int ldk, int k_off, const void* v_src, int ldv, int v_off,
+    const void* q_gamma, const void* k_gamma, const float* row_ss, int q_full_width, int k_full_width, float eps,
+    const float* inv_freq, int rot, const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
+    int block_size, int T, int Hq, int Hkv, cudaStream_t stream) {
+  if (rot < 0 || rot > D || (rot & 7) || !row_ss || !q_gamma || !k_gamma) return -6;
+  if (rot > 0) {
+    const int partner = rot >> 3;
+    if (partner & (partner - 1)) return -6;
+  }
+  RopeParams p;
+  p.q_src = reinterpret_cast<const __nv_bfloat16*>(q_src); p.ldq = ldq; p.q_off = q_off; p.q_head_stride = D;
+  p.gate_in_q = 0;
+  p.k_src = reinterpret_cast<const __nv_bfloat16*>(k_src); p.ldk = ldk; p.k_off = k_off;
+  p.v_src = reinterpret_cast<const __nv_bfloat16*>(v_src); p.ldv = ldv; p.v_off = v_off;
+  p.q_gamma = reinterpret_cast<const __nv_bfloat16*>(q_gamma);
+  p.k_gamma = reinterpret_cast<const __nv_bfloat16*>(k_gamma);
+  p.unit_offset = 0; p.eps = eps;
+  p.inv_freq = inv_freq; p.rot = rot; p.mscale = 1.f;
+  p.positions = positions; p.slots = slots;
+  p.q_out = reinterpret_cast<__nv_bfloat16*>(q_out);
+  p.gate_out = nullptr;
+  p.k_cache = reinterpret_cast<__nv_bfloat16*>(k_cache);
+  p.v_cache = reinterpret_cast<__nv_bfloat16*>(v_cache);
+  p.bs = block_size; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
+  p.row_ss = row_ss; p.q_full_width = (float)q_full_width; p.k_full_width = (float)k_full_width; p.gamma_head_stride = D;
+  return launch_rope(p, stream);
+}
 
 extern "C" int b200_qk_norm_rope_append(
     const void* q_src, int ldq, int q_off, int q_head_stride, int gate_in_q, const void* k_src, int ldk, int k_off,
@@ -139,8 +220,6 @@ extern "C" int b200_qk_norm_rope_append(
   p.k_cache = reinterpret_cast<__nv_bfloat16*>(k_cache);
   p.v_cache = reinterpret_cast<__nv_bfloat16*>(v_cache);
   p.bs = block_size; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
-  const size_t warps = (size_t)T * (Hq + 2 * Hkv);
-  const int wpb = 8;
-  qk_norm_rope_append_kernel<<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, stream>>>(p);
-  return (int)cudaGetLastError();
+  p.row_ss = nullptr; p.q_full_width = 1.f; p.k_full_width = 1.f; p.gamma_head_stride = 0;
+  return launch_rope(p, stream);
 }

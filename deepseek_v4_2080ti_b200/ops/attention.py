@@ -41,6 +41,31 @@ def qk_norm_rope_append(q_src, q_off, q_head_stride, gate_in_q, k_src, k_off, v_
     return q_out, gate_out
 
 
+def qk_sumsq(proj: torch.Tensor, q_off: int, q_width: int, k_off: int, k_width: int) -> torch.Tensor:
+    """fp32 [T, 2]: sums of squares of the q and k column ranges of each projection row."""
+    t = proj.shape[0]
+    out = torch.empty(t, 2, dtype=torch.float32, device=proj.device)
+    rc = _lib.lib().b200_qk_sumsq(_lib.ptr(proj), proj.stride(0), q_off, q_width, k_off, k_width, _lib.ptr(out), t, _lib.stream())
+    _lib.check(rc, "qk_sumsq")
+    return out
+
+
+def qk_fullnorm_rope_append(proj, q_off, k_off, v_off, q_gamma, k_gamma, row_ss, q_full_width, k_full_width, eps, inv_freq,
+                            rot, positions, slots, k_cache, v_cache, n_q_heads, n_kv_heads):
+    """MiniMax-style attention prologue: RMSNorm whose statistic spans the whole q / k projection row (``row_ss`` holds
+    the rows' sums of squares over all ranks), per-(head, dim) gamma, half-split partial RoPE, paged K/V append."""
+    t = proj.shape[0]
+    bs = k_cache.shape[2]
+    q_out = torch.empty(t, n_q_heads, D, dtype=torch.bfloat16, device=proj.device)
+    rc = _lib.lib().b200_qk_fullnorm_rope_append(
+        _lib.ptr(proj), proj.stride(0), q_off, _lib.ptr(proj), proj.stride(0), k_off, _lib.ptr(proj), proj.stride(0), v_off,
+        _lib.ptr(q_gamma), _lib.ptr(k_gamma), _lib.ptr(row_ss), q_full_width, k_full_width, _f(eps), _lib.ptr(inv_freq), rot,
+        _lib.ptr(positions), _lib.ptr(slots), _lib.ptr(q_out), _lib.ptr(k_cache), _lib.ptr(v_cache), bs, t, n_q_heads,
+        n_kv_heads, _lib.stream())
+    _lib.check(rc, "qk_fullnorm_rope_append")
+    return q_out
+
+
 def prefill(q, k_cache, v_cache, block_table, q_start, q_len, kv_len, max_q_len, gate=None, scale=None):
     """Causal attention of new query rows against the paged cache (which already holds their K/V).
 

@@ -2,7 +2,7 @@
 
 The raw GGUF blocks are only *regrouped* at load time so that every pipeline stage of the GEMM (128 output rows x 64
 inputs) is one contiguous block ``[128 x quant bytes | 128 x scale bytes]``; the quantised codes stay as they are and
-are decoded in registers inside the kernel.  Supported: Q8_0, Q4_K, Q2_K, IQ2_XXS."""
+are decoded in registers inside the kernel.  Supported: Q8_0, Q4_K, Q5_K, Q2_K, IQ1_M, IQ2_XXS, IQ3_XXS."""
 from __future__ import annotations
 
 import ctypes
@@ -14,16 +14,32 @@ from ..formats.gguf import GGMLType
 from ..formats.gguf.quant import _unpack_scale_min_6bit, tables
 from . import _lib
 
-WF = {GGMLType.Q8_0: 3, GGMLType.Q4_K: 4, GGMLType.Q2_K: 5, GGMLType.IQ2_XXS: 6}
-_lut: dict[int, torch.Tensor] = {}
+WF = {GGMLType.Q8_0: 3, GGMLType.Q4_K: 4, GGMLType.Q2_K: 5, GGMLType.IQ2_XXS: 6, GGMLType.Q5_K: 7, GGMLType.IQ3_XXS: 8,
+      GGMLType.IQ1_M: 9}
+_lut: dict[tuple, torch.Tensor] = {}
 
 
 def codebook(device) -> torch.Tensor:
     """IQ2_XXS codebook (256 x 8 magnitudes) followed by the 128-entry sign table, as bytes on ``device``."""
-    key = torch.device(device).index or 0
+    return lut_for(GGMLType.IQ2_XXS, device)
+
+
+def lut_for(t, device) -> torch.Tensor | None:
+    """Codebook table a format's in-register decode reads (None when it needs none): IQ2_XXS 256 x 8 magnitudes +
+    128 sign bytes; IQ3_XXS 256 x 4 magnitudes + 128 sign bytes; IQ1_M 2048 x 8 int8 grid values."""
+    t = GGMLType(t)
+    if t not in (GGMLType.IQ2_XXS, GGMLType.IQ3_XXS, GGMLType.IQ1_M):
+        return None
+    key = (t, torch.device(device).index or 0)
     if key not in _lut:
-        t = tables("cpu")
-        _lut[key] = torch.cat([t["iq2xxs"].to(torch.uint8).reshape(-1), t["ksigns"]]).to(device)
+        tb = tables("cpu")
+        if t == GGMLType.IQ2_XXS:
+            v = torch.cat([tb["iq2xxs"].to(torch.uint8).reshape(-1), tb["ksigns"]])
+        elif t == GGMLType.IQ3_XXS:
+            v = torch.cat([tb["iq3xxs"].to(torch.uint8).reshape(-1), tb["ksigns"]])
+        else:
+            v = tb["iq1"].to(torch.int8).reshape(-1).view(torch.uint8)
+        _lut[key] = v.contiguous().to(device)
     return _lut[key]
 
 
@@ -75,6 +91,35 @@ def prepack(raw: torch.Tensor, t: GGMLType, k: int) -> torch.Tensor:
         q = b[:, :, 2:].reshape(n, nb * 4, 16)
         s = torch.cat([b[:, :, None, 0:2].expand(n, nb, 4, 2), b.new_zeros(n, nb, 4, 2)], -1).reshape(n, nb * 4, 4)
         return _tile(q, s)
+    if t == GGMLType.Q5_K:
+        b = raw.view(n, nb, 176)
+        sc, mn = _unpack_scale_min_6bit(b[:, :, 4:16].reshape(-1, 12))
+        sc, mn = sc.view(n, nb, 4, 2), mn.view(n, nb, 4, 2)
+        qs = b[:, :, 48:176].reshape(n, nb, 4, 32)
+        qh = b[:, :, 16:48].to(torch.int64)                                 # [n, nb, 32]: bit j = fifth bit of sub-block j
+        pw = (1 << torch.arange(32, device=raw.device, dtype=torch.int64))
+        masks = torch.stack([(((qh >> j) & 1) * pw).sum(-1) for j in range(8)], -1)      # [n, nb, 8] 32-bit masks
+        mb = torch.stack([(masks >> (8 * i)) & 0xFF for i in range(4)], -1).to(torch.uint8)   # [n, nb, 8, 4] little-endian
+        q = torch.cat([qs, mb.view(n, nb, 4, 8)], -1).reshape(n, nb * 4, 40)
+        dd = b[:, :, None, 0:4].expand(n, nb, 4, 4)
+        s = torch.cat([dd, torch.stack([sc[..., 0], mn[..., 0], sc[..., 1], mn[..., 1]], -1).to(torch.uint8)], -1)
+        return _tile(q, s.reshape(n, nb * 4, 8))
+    if t == GGMLType.IQ3_XXS:
+        b = raw.view(n, nb, 98)
+        q = torch.cat([b[:, :, 2:66].reshape(n, nb, 4, 16), b[:, :, 66:98].reshape(n, nb, 4, 8)], -1).reshape(n, nb * 4, 24)
+        s = torch.cat([b[:, :, None, 0:2].expand(n, nb, 4, 2), b.new_zeros(n, nb, 4, 2)], -1).reshape(n, nb * 4, 4)
+        return _tile(q, s)
+    if t == GGMLType.IQ1_M:
+        b = raw.view(n, nb, 56)
+        sc = b[:, :, 48:56].to(torch.int32)
+        sc16 = sc[:, :, 0::2] | (sc[:, :, 1::2] << 8)                       # [n, nb, 4]
+        dbits = sum(((sc16[:, :, i] >> 12) & 0xF) << (4 * i) for i in range(4))
+        dby = torch.stack([dbits & 0xFF, dbits >> 8], -1).to(torch.uint8)   # fp16 d, little-endian
+        s3 = torch.stack([(sc16 >> (3 * i)) & 7 for i in range(4)], -1).reshape(n, nb, 16)
+        pair = (s3[:, :, 0::2] | (s3[:, :, 1::2] << 3)).to(torch.uint8).view(n, nb, 4, 2)   # one byte per 32 inputs
+        q = torch.cat([b[:, :, 0:32].reshape(n, nb, 4, 8), b[:, :, 32:48].reshape(n, nb, 4, 4)], -1).reshape(n, nb * 4, 12)
+        s = torch.cat([dby[:, :, None, :].expand(n, nb, 4, 2), pair], -1).reshape(n, nb * 4, 4)
+        return _tile(q.contiguous(), s.contiguous())
     raise ValueError(f"{t.name} has no tensor-core decode path yet")
 
 
@@ -98,7 +143,7 @@ def linear(x: torch.Tensor, w: GGUFLinear, residual: torch.Tensor | None = None,
     assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[1] == w.k
     t = x.shape[0]
     out = torch.empty(t, w.n, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
-    lut = codebook(x.device) if w.ggml_type == GGMLType.IQ2_XXS else None
+    lut = lut_for(w.ggml_type, x.device)
     rc = _lib.lib().b200_gemm_wdec_gguf(WF[w.ggml_type], _lib.ptr(w.weight), _lib.ptr(lut), _lib.ptr(x),
                                         None if out_f32 else _lib.ptr(out), _lib.ptr(out) if out_f32 else None,
                                         _lib.ptr(residual), t, w.n, w.k, _lib.ptr(_lib.status_word(x.device)), _lib.stream())

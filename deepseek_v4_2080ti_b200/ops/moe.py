@@ -53,6 +53,15 @@ class ExpertWeights:
         return ExpertWeights(WF_FP8_B128, w, torch.stack([s.float() for s in scales]).contiguous(), n, k, len(ws))
 
     @staticmethod
+    def from_gguf(raws: list[torch.Tensor], ggml_type, n: int, k: int) -> "ExpertWeights":
+        """Raw GGUF blocks (uint8 [N, row_bytes]) of each expert -> stage-major stacks decoded inside the grouped GEMM.
+        ``scales`` carries the codebook table for the formats that need one."""
+        from . import gguf_gemm
+        w = torch.stack([gguf_gemm.prepack(r, ggml_type, k) for r in raws])
+        lut = gguf_gemm.lut_for(ggml_type, raws[0].device)
+        return ExpertWeights(gguf_gemm.WF[gguf_gemm.GGMLType(ggml_type)], w, lut, n, k, len(raws))
+
+    @staticmethod
     def from_bf16(ws: list[torch.Tensor]) -> "ExpertWeights":
         n, k = ws[0].shape
         assert n % 128 == 0, "bf16 expert matrices need a multiple of 128 output features"
@@ -72,9 +81,15 @@ def route(logits: torch.Tensor, bias: torch.Tensor | None, k: int, score_func: s
 
 
 def experts_forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, w13: ExpertWeights, w2: ExpertWeights,
-                    expert_lo: int, swiglu_limit: float = 0.0, base: torch.Tensor | None = None) -> torch.Tensor:
+                    expert_lo: int, swiglu_limit: float = 0.0, base: torch.Tensor | None = None, comm=None,
+                    residual: torch.Tensor | None = None, comm_mode: int = 0) -> torch.Tensor:
     """out[t] = base[t] + sum_k wts[t,k] * Expert_{idx[t,k]}(x[t]) over the experts [expert_lo, expert_lo + E) held here.
-    x [T, H] bf16; w13: [E] x [2I, H] (gate rows then up rows); w2: [E] x [H, I]."""
+    x [T, H] bf16; w13: [E] x [2I, H] (gate rows then up rows); w2: [E] x [H, I].
+
+    With ``comm`` (a peer-memory communicator of an expert-parallel group) the weighted combine, the sum over ranks
+    and the residual add run as one kernel over NVLink (``PeerComm.moe_combine``): every rank gets
+    ``residual + sum_ranks(base_r + local routes)``."""
+    L0 = _lib.lib()
     t, h = x.shape
     k = idx.shape[1]
     el = w13.experts
@@ -82,6 +97,8 @@ def experts_forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, w13: 
     r = t * k
     dev = x.device
     bn = gemm._bn(min(256, max(16, (r + el - 1) // el)))      # token tile sized for the average rows per expert
+    if w13.wfmt >= 3:
+        bn = min(bn, int(L0.b200_gguf_max_bn(w13.wfmt)), int(L0.b200_gguf_max_bn(w2.wfmt)))
     mt13, mt2 = (w13.n + 127) // 128, (w2.n + 127) // 128
     max_work = (mt13 + mt2) * ((r + bn - 1) // bn + el)
     i32 = lambda *s: torch.empty(*s, dtype=torch.int32, device=dev)
@@ -101,15 +118,23 @@ def experts_forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, w13: 
     st = _lib.status_word(dev)
     gu = torch.empty(r, w13.n, dtype=torch.bfloat16, device=dev)
     rc = L.b200_gemm_wdec_grouped(w13.wfmt, _lib.ptr(w13.weight), _lib.ptr(w13.scales), _lib.ptr(xs), _lib.ptr(gu), r,
-                                  w13.n, w13.k, el, _lib.ptr(work13), _lib.ptr(n13), bn, _lib.ptr(st), s)
+                                  w13.n, w13.k, el, _lib.ptr(work13), _lib.ptr(n13), bn, _lib.ptr(st), s) if w13.wfmt < 3 else \
+        L.b200_gemm_wdec_gguf_grouped(w13.wfmt, _lib.ptr(w13.weight), _lib.ptr(w13.scales), _lib.ptr(xs), _lib.ptr(gu), r,
+                                      w13.n, w13.k, el, _lib.ptr(work13), _lib.ptr(n13), bn, _lib.ptr(st), s)
     _lib.check(rc, "grouped gemm w13")
     act = torch.empty(r, inter, dtype=torch.bfloat16, device=dev)
     rc = L.b200_moe_swiglu(_lib.ptr(gu), _lib.ptr(offsets), el, _lib.ptr(act), r, inter, ctypes.c_float(swiglu_limit), s)
     _lib.check(rc, "moe_swiglu")
     y = torch.empty(r, h, dtype=torch.bfloat16, device=dev)
     rc = L.b200_gemm_wdec_grouped(w2.wfmt, _lib.ptr(w2.weight), _lib.ptr(w2.scales), _lib.ptr(act), _lib.ptr(y), r, w2.n,
-                                  w2.k, el, _lib.ptr(work2), _lib.ptr(n2), bn, _lib.ptr(st), s)
+                                  w2.k, el, _lib.ptr(work2), _lib.ptr(n2), bn, _lib.ptr(st), s) if w2.wfmt < 3 else \
+        L.b200_gemm_wdec_gguf_grouped(w2.wfmt, _lib.ptr(w2.weight), _lib.ptr(w2.scales), _lib.ptr(act), _lib.ptr(y), r,
+                                      w2.n, w2.k, el, _lib.ptr(work2), _lib.ptr(n2), bn, _lib.ptr(st), s)
     _lib.check(rc, "grouped gemm w2")
+    if comm is not None and getattr(comm, "world", 1) > 1:
+        return comm.moe_combine(y, route_row, wts, base, residual, t, k, h, comm_mode)
+    if residual is not None:
+        base = residual if base is None else base + residual
     out = torch.empty(t, h, dtype=torch.bfloat16, device=dev)
     rc = L.b200_moe_combine(_lib.ptr(y), _lib.ptr(route_row), _lib.ptr(wts), _lib.ptr(base), _lib.ptr(out), t, k, h, s)
     _lib.check(rc, "moe_combine")

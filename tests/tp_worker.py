@@ -98,6 +98,53 @@ def main() -> None:
         dist.broadcast(ref, 0)
         assert ref.tolist() == out, ("ranks disagree", name)
     assert comm.fused_calls > 0
+
+    # expert-parallel combine fused with its collective (one-shot and two-shot) against combine + NCCL
+    from deepseek_v4_2080ti_b200.ops import moe
+    for t, k, h, rows in [(1, 4, 512, 4), (37, 4, 512, 80), (300, 8, 1024, 900)]:
+        torch.manual_seed(21)                     # identical routing on every rank
+        owner = torch.randint(0, world, (t, k), device=dev)
+        wts = torch.rand(t, k, device=dev)
+        resid = torch.randn(t, h, device=dev).bfloat16()
+        torch.manual_seed(31 + rank)
+        y = torch.randn(rows, h, device=dev).bfloat16()
+        base = torch.randn(t, h, device=dev).bfloat16()
+        route_row = torch.where(owner == rank, torch.randint(0, rows, (t, k), device=dev), -1).to(torch.int32)
+        part = base.float()
+        for j in range(k):
+            sel = route_row[:, j] >= 0
+            part[sel] += wts[sel, j, None] * y[route_row[sel, j].long()].float()
+        want = part.bfloat16().float()            # the wire carries bf16 partials
+        dist.all_reduce(want)
+        want += resid.float()
+        for mode in (1, 2):
+            got = comm.moe_combine(y, route_row, wts, base, resid, t, k, h, mode)
+            torch.cuda.synchronize()
+            comm.check()
+            err = (got.float() - want).abs().max() / want.abs().max()
+            assert err < 2e-2, ("moe_combine", mode, t, err.item())
+            ref = got.clone()
+            dist.broadcast(ref, 0)
+            assert torch.equal(ref, got), ("moe_combine not identical across ranks", mode, t)
+
+    # attention-TP + expert-parallel GGUF model == single-rank model
+    from deepseek_v4_2080ti_b200.models import gqa_moe as gm
+    gcfg = gm.GqaMoeConfig(n_layers=2, hidden=512, vocab=512, n_heads=2 * world, n_kv_heads=world, n_experts=4 * world,
+                           top_k=4, moe_inter=256, context_length=512, attn_type="Q8_0", dense_type="Q4_K",
+                           gate_up_type="Q2_K", down_type="IQ2_XXS")
+    store = gm.TensorStore(list(gm.synth_tensors(gcfg, seed=9, device=dev, std=0.05)))
+    torch.manual_seed(4)
+    gprompt = torch.randint(0, gcfg.vocab, (70,), dtype=torch.int32)
+    g1 = gm.GqaMoeRuntime(gcfg, gm.GqaMoeGpuWeights(gcfg, store, dev), max_slots=1, max_context=256).generate(gprompt, 8)
+    gw = gm.GqaMoeGpuWeights(gcfg, store, dev, rank, world)
+    for c, name in ((nccl, "nccl"), (comm, "peer")):
+        out = gm.GqaMoeRuntime(gcfg, gw, max_slots=1, max_context=256, comm=c).generate(gprompt, 8, chunk=32)
+        torch.cuda.synchronize()
+        comm.check()
+        assert out[:3] == g1[:3], ("gqa_moe", name, out, g1)
+        ref = torch.tensor(out, device=dev)
+        dist.broadcast(ref, 0)
+        assert ref.tolist() == out, ("gqa_moe ranks disagree", name)
     comm.close()
     dist.barrier()
     if rank == 0:
