@@ -7,7 +7,12 @@ path is one of this package's sm_100a kernels.
 * feed-forward: dense SwiGLU for the leading layers, otherwise router top-k -> device-side plan -> grouped FP4 / FP8 /
   bf16 expert GEMMs -> weighted combine on top of the shared expert (``ops/moe.py``);
 * parallelism: attention heads and the dense / shared intermediate dimension are sharded over the tensor-parallel
-  group, routed experts are sharded by contiguous expert range; partial outputs are summed by ``comm``.
+  group, routed experts are sharded by contiguous expert range; partial outputs are summed by ``comm``;
+  optionally a layer pipeline (``parallel/pp.py``): a stage holds a contiguous layer range, receives the hidden rows
+  of a chunk from the previous stage and sends them on, and the last stage shares the next token;
+* weights: bf16 / FP8 block-128 / FP4 as above, or GGUF block formats quantised at load (``dense_quant``,
+  ``expert_format="gguf"``) and decoded inside the GEMMs - the GLM-5.2-shaped mix is Q8_0 attention projections,
+  Q4_K dense / shared feed-forward, Q2_K gate/up and IQ3_XXS down experts.
 
 Same math as ``MlaMoeRuntime`` (the host path) and ``reference_cpu/mla_moe_ref.py``; see ``mla_moe.py`` for the
 reference citations.
@@ -20,7 +25,8 @@ from typing import Iterator
 import torch
 
 from ..formats import fp8 as fp8fmt
-from ..ops import basic, gemm, mla, moe
+from ..formats import gguf as G
+from ..ops import basic, gemm, gguf_gemm, mla, moe
 from ..ops.gemm import PackedLinear
 from .mla_moe import MlaMoeConfig
 
@@ -30,6 +36,16 @@ class _NoComm:
 
     def all_reduce(self, t):
         return t
+
+
+def _mm(x: torch.Tensor, w, out_f32: bool = False) -> torch.Tensor:
+    """Projection through whichever weight container the loader produced."""
+    if isinstance(w, gguf_gemm.GGUFLinear):
+        return gguf_gemm.linear(x, w, out_f32=out_f32)
+    return gemm.linear(x, w, out_f32=out_f32)
+
+
+GLM_GGUF_MIX = {"attn": "Q8_0", "ffn": "Q4_K", "gate_up": "Q2_K", "down": "IQ3_XXS"}
 
 
 @dataclass
@@ -60,27 +76,46 @@ class GpuLayer:
 
 class MlaMoeGpuWeights:
     def __init__(self, cfg: MlaMoeConfig, state: Iterator[tuple[str, torch.Tensor]], device="cuda", rank: int = 0,
-                 world: int = 1, dense_fp8: bool = False):
+                 world: int = 1, dense_fp8: bool = False, layer_range: tuple[int, int] | None = None,
+                 gguf_mix: dict[str, str] | None = None):
+        """``rank`` / ``world``: position in the tensor/expert-parallel group (of this pipeline stage);
+        ``layer_range``: the layers this stage holds (embedding only with layer 0, norm + head only with the last);
+        ``gguf_mix``: GGUF types per weight class {"attn", "ffn", "gate_up", "down"} - quantised at load."""
         self.cfg, self.device, self.rank, self.world, self.dense_fp8 = cfg, torch.device(device), rank, world, dense_fp8
+        self.gguf_mix = gguf_mix
+        self.layer_lo, self.layer_hi = layer_range or (0, cfg.num_layers)
         assert cfg.num_heads % world == 0 and cfg.num_experts % world == 0
         self.h_local = cfg.num_heads // world
         per = cfg.num_experts // world
         self.expert_lo, self.expert_hi = rank * per, (rank + 1) * per
         sd: dict[str, torch.Tensor] = {}
         for k, v in state:
+            if k.startswith("layers."):
+                li = int(k.split(".")[1])
+                if not (self.layer_lo <= li < self.layer_hi):
+                    continue
             if ".experts." in k:
                 e = int(k.split(".experts.")[1].split(".")[0])
                 if not (self.expert_lo <= e < self.expert_hi):
                     continue
             sd[k] = v
         dev = self.device
-        self.embed = sd["embed.weight"].to(dev, torch.bfloat16).contiguous()
-        self.norm = sd["norm.weight"].to(dev, torch.bfloat16)
-        self.head = PackedLinear.from_bf16(sd["head.weight"].to(dev))
-        self.layers = [self._layer(sd, f"layers.{i}.", i < cfg.first_dense_layers) for i in range(cfg.num_layers)]
+        self.embed = sd["embed.weight"].to(dev, torch.bfloat16).contiguous() if self.layer_lo == 0 else None
+        last = self.layer_hi == cfg.num_layers
+        self.norm = sd["norm.weight"].to(dev, torch.bfloat16) if last else None
+        self.head = self._lin(sd["head.weight"], "ffn") if last else None
+        self.layers = [self._layer(sd, f"layers.{i}.", i < cfg.first_dense_layers)
+                       if self.layer_lo <= i < self.layer_hi else None for i in range(cfg.num_layers)]
 
-    def _lin(self, w: torch.Tensor) -> PackedLinear:
+    def _lin(self, w: torch.Tensor, kind: str = "ffn"):
         w = w.to(self.device)
+        if self.gguf_mix is not None:
+            t = G.GGMLType[self.gguf_mix[kind]]
+            if w.shape[1] % G.BLOCK_ELEMS[t] or w.shape[1] % 64:
+                t = G.GGMLType.Q8_0
+            if w.shape[1] % 64 == 0:
+                return gguf_gemm.GGUFLinear.from_raw(G.quantize(w.float(), t), t, w.shape[0], w.shape[1], self.device)
+            return PackedLinear.from_bf16(w)
         if self.dense_fp8 and w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0:
             q, s = fp8fmt.quantize_block128(w.float())
             return PackedLinear.from_fp8(q, s)
@@ -106,13 +141,13 @@ class MlaMoeGpuWeights:
         w_uk = wkv_b[:, :cfg.qk_nope_dim]                       # [H, N, C]
         lw = GpuLayer(
             attn_norm=b(sd[p + "attn_norm.weight"]), ffn_norm=b(sd[p + "ffn_norm.weight"]),
-            wq_a=self._lin(sd[a + "wq_a.weight"]) if cfg.q_lora_rank > 0 else None,
+            wq_a=self._lin(sd[a + "wq_a.weight"], "attn") if cfg.q_lora_rank > 0 else None,
             q_norm=b(sd[a + "q_norm.weight"]) if cfg.q_lora_rank > 0 else None,
-            wq_b=self._lin(self._rows(sd[a + ("wq_b.weight" if cfg.q_lora_rank > 0 else "wq.weight")], hq)),
-            wkv_a=self._lin(sd[a + "wkv_a.weight"]), kv_norm=b(sd[a + "kv_norm.weight"]),
+            wq_b=self._lin(self._rows(sd[a + ("wq_b.weight" if cfg.q_lora_rank > 0 else "wq.weight")], hq), "attn"),
+            wkv_a=self._lin(sd[a + "wkv_a.weight"], "attn"), kv_norm=b(sd[a + "kv_norm.weight"]),
             w_uk_t=w_uk.transpose(1, 2).reshape(self.h_local * cfg.kv_lora_rank, cfg.qk_nope_dim).contiguous(),
             w_uv=wkv_b[:, cfg.qk_nope_dim:].reshape(self.h_local * cfg.v_head_dim, cfg.kv_lora_rank).contiguous(),
-            wo=self._lin(self._cols(sd[a + "wo.weight"])))
+            wo=self._lin(self._cols(sd[a + "wo.weight"]), "attn"))
         if cfg.index_heads > 0:
             # the indexer is small and replicated: every rank scores with all index heads
             lw.idx_wq, lw.idx_wk = self._lin(sd[a + "indexer.wq_b.weight"]), self._lin(sd[a + "indexer.wk.weight"])
@@ -129,7 +164,14 @@ class MlaMoeGpuWeights:
                                                 self._rows(sd[f + "shared_experts.w3.weight"])]))
             lw.shared_down = self._lin(self._cols(sd[f + "shared_experts.w2.weight"]))
         es = range(self.expert_lo, self.expert_hi)
-        if cfg.expert_format == "fp4":
+        if self.gguf_mix is not None:
+            t13, t2 = G.GGMLType[self.gguf_mix["gate_up"]], G.GGMLType[self.gguf_mix["down"]]
+            full = lambda e, n: self._expert_f32(sd, f + f"experts.{e}.{n}")
+            lw.w13 = moe.ExpertWeights.from_gguf([G.quantize(torch.cat([full(e, "w1"), full(e, "w3")]), t13) for e in es], t13,
+                                                 2 * cfg.expert_intermediate, cfg.hidden_size)
+            lw.w2 = moe.ExpertWeights.from_gguf([G.quantize(full(e, "w2"), t2) for e in es], t2, cfg.hidden_size,
+                                                cfg.expert_intermediate)
+        elif cfg.expert_format == "fp4":
             cat13 = lambda e, suf: torch.cat([sd[f + f"experts.{e}.w1.{suf}"], sd[f + f"experts.{e}.w3.{suf}"]]).to(dev)
             lw.w13 = moe.ExpertWeights.from_fp4([cat13(e, "weight") for e in es], [cat13(e, "scale") for e in es])
             lw.w2 = moe.ExpertWeights.from_fp4([sd[f + f"experts.{e}.w2.weight"].to(dev) for e in es],
@@ -141,12 +183,26 @@ class MlaMoeGpuWeights:
         return lw
 
 
+    def _expert_f32(self, sd, base: str) -> torch.Tensor:
+        """An expert matrix as fp32 on the device, whatever the checkpoint stores (bf16, or FP4 codes + scales)."""
+        from ..formats import fp4 as fp4fmt
+        w = sd[base + ".weight"].to(self.device)
+        if self.cfg.expert_format == "fp4":
+            return fp4fmt.dequantize(w, sd[base + ".scale"].to(self.device)).float()
+        return w.float()
+
+
 class MlaMoeGpuRuntime:
     """One sequence at a time (prefill in one or more chunks, then token-by-token decode) over a paged latent cache."""
 
-    def __init__(self, cfg: MlaMoeConfig, weights: MlaMoeGpuWeights, max_context: int = 4096, block_size: int = 64, comm=None):
+    def __init__(self, cfg: MlaMoeConfig, weights: MlaMoeGpuWeights, max_context: int = 4096, block_size: int = 64, comm=None,
+                 pipeline=None):
+        """``comm``: communicator of this stage's tensor/expert-parallel group; ``pipeline``: a
+        ``parallel.pp.PipelineLink`` when the layers are cut into stages (weights loaded with the matching
+        ``layer_range``)."""
         self.cfg, self.w, self.device = cfg, weights, weights.device
         self.comm = comm or _NoComm()
+        self.pp = pipeline
         self.bs = block_size
         self.max_context = max_context
         nblk = (max_context + block_size - 1) // block_size
@@ -162,78 +218,98 @@ class MlaMoeGpuRuntime:
     def reset(self) -> None:
         self.length = 0
 
-    def _swiglu(self, x, gu: PackedLinear, down: PackedLinear):
-        return gemm.linear(basic.silu_mul(gemm.linear(x, gu)), down)
+    def _swiglu(self, x, gu, down):
+        return _mm(basic.silu_mul(_mm(x, gu)), down)
 
     def _attention(self, lw: GpuLayer, i: int, x: torch.Tensor, pos: torch.Tensor, end: int) -> torch.Tensor:
         cfg = self.cfg
         t = x.shape[0]
         hl = self.w.h_local
         eps = cfg.rms_norm_eps
-        qin = basic.rmsnorm(gemm.linear(x, lw.wq_a), lw.q_norm, eps) if lw.wq_a is not None else x
-        q = gemm.linear(qin, lw.wq_b)
-        kv = gemm.linear(x, lw.wkv_a)
-        kidx = gemm.linear(x, lw.idx_wk) if lw.idx_wk is not None else None
+        qin = basic.rmsnorm(_mm(x, lw.wq_a), lw.q_norm, eps) if lw.wq_a is not None else x
+        q = _mm(qin, lw.wq_b)
+        kv = _mm(x, lw.wkv_a)
+        kidx = _mm(x, lw.idx_wk) if lw.idx_wk is not None else None
         mla.kv_append(kv, lw.kv_norm, eps, pos, pos, cfg.rope_theta, self.cache[i], cfg.kv_lora_rank, cfg.qk_rope_dim,
                       kidx, lw.idx_knorm, self.idx_cache[i] if kidx is not None else None)
         qn_t, q_pe = mla.q_prepare(q, pos, cfg.rope_theta, hl, cfg.qk_nope_dim, cfg.qk_rope_dim)
         q_lat = mla.per_head_linear(qn_t, lw.w_uk_t)
         sel = None
         if lw.idx_wq is not None and end > cfg.index_topk:
-            qi = gemm.linear(qin, lw.idx_wq).view(t, cfg.index_heads, cfg.index_dim)
-            hw = gemm.linear(x, lw.idx_wproj, out_f32=True) * cfg.index_heads ** -0.5
+            qi = _mm(qin, lw.idx_wq).view(t, cfg.index_heads, cfg.index_dim)
+            hw = _mm(x, lw.idx_wproj, out_f32=True) * cfg.index_heads ** -0.5
             scores = mla.indexer_scores(qi, hw.contiguous(), self.idx_cache[i], self.block_table, self.bs, pos, end,
                                         cfg.index_dim ** -0.5)
             sel = mla.topk_rows(scores, (pos + 1).to(torch.int32), cfg.index_topk)
         o_lat = mla.attention(q_lat, q_pe, self.cache[i], self.block_table, self.bs, pos, cfg.kv_lora_rank, cfg.qk_rope_dim,
                               cfg.qk_head_dim ** -0.5, sel)
         o = mla.transpose_heads(mla.per_head_linear(o_lat, lw.w_uv)).view(t, hl * cfg.v_head_dim)
-        return self.comm.all_reduce(gemm.linear(o, lw.wo))
+        return self.comm.all_reduce(_mm(o, lw.wo))
 
     def _ffn(self, lw: GpuLayer, x: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
         if lw.dense_gu is not None:
             return self.comm.all_reduce(self._swiglu(x, lw.dense_gu, lw.dense_down))
-        logits = gemm.linear(x, lw.gate, out_f32=True)
+        logits = _mm(x, lw.gate, out_f32=True)
         idx, wts = moe.route(logits, lw.gate_bias, cfg.experts_per_token, cfg.score_func, cfg.norm_topk, cfg.route_scale)
         base = self._swiglu(x, lw.shared_gu, lw.shared_down) if lw.shared_gu is not None else None
+        if getattr(self.comm, "world", 1) > 1 and hasattr(self.comm, "moe_combine"):
+            # weighted combine + sum over the expert-parallel ranks in one peer-memory kernel
+            return moe.experts_forward(x, idx, wts, lw.w13, lw.w2, self.w.expert_lo, cfg.swiglu_limit, base, comm=self.comm)
         y = moe.experts_forward(x, idx, wts, lw.w13, lw.w2, self.w.expert_lo, cfg.swiglu_limit, base)
         return self.comm.all_reduce(y)
 
     @torch.no_grad()
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
-        """Append ``ids`` [T] (int32, device) to the context; returns fp32 logits [T, vocab]."""
+        """Append ``ids`` [T] (int32, device) to the context; returns fp32 logits [T, vocab] (on the last pipeline
+        stage; earlier stages send their hidden rows on and return None)."""
         cfg, w = self.cfg, self.w
         t = ids.numel()
         if self.length + t > self.max_context:
             raise RuntimeError("sequence exceeds max_context")
         pos = torch.arange(self.length, self.length + t, dtype=torch.int32, device=self.device)
         end = self.length + t
-        h = basic.embedding(ids.to(torch.int32), w.embed, 0, cfg.vocab_size)
+        if w.layer_lo == 0:
+            h = basic.embedding(ids.to(torch.int32), w.embed, 0, cfg.vocab_size)
+        else:
+            h = self.pp.recv_hidden(t, cfg.hidden_size)
         delta = None
         for i, lw in enumerate(w.layers):
+            if lw is None:
+                continue
             x = basic.rmsnorm(h, lw.attn_norm, cfg.rms_norm_eps) if delta is None else \
                 basic.add_rmsnorm(h, delta, lw.attn_norm, cfg.rms_norm_eps)
             d_attn = self._attention(lw, i, x, pos, end)
             x = basic.add_rmsnorm(h, d_attn, lw.ffn_norm, cfg.rms_norm_eps)
             delta = self._ffn(lw, x)
-        x = basic.add_rmsnorm(h, delta, w.norm, cfg.rms_norm_eps)
         self.length = end
-        return gemm.linear(x, w.head, out_f32=True)
+        if w.layer_hi < cfg.num_layers:
+            basic.add_(h, delta)
+            self.pp.send_hidden(h)
+            return None
+        x = basic.add_rmsnorm(h, delta, w.norm, cfg.rms_norm_eps)
+        return _mm(x, w.head, out_f32=True)
 
     @torch.no_grad()
     def generate(self, prompt: torch.Tensor, max_new_tokens: int, chunk: int = 2048) -> tuple[list[int], torch.Tensor]:
         self.reset()
         prompt = prompt.to(self.device, torch.int32)
+        last_stage = self.w.layer_hi == self.cfg.num_layers
         logits = None
-        for s in range(0, prompt.numel(), chunk):
-            logits = self.forward(prompt[s:s + chunk])[-1:]
+        for s in range(0, prompt.numel(), chunk):       # stages overlap: a stage starts chunk c + 1 once c is sent on
+            out = self.forward(prompt[s:s + chunk])
+            logits = out[-1:] if out is not None else None
         toks, rows = [], []
         for _ in range(max_new_tokens):
-            rows.append(logits[0])
-            nxt = basic.argmax(logits)
+            nxt = basic.argmax(logits) if last_stage else None
+            if last_stage:
+                rows.append(logits[0])
+            if self.pp is not None:
+                nxt = self.pp.share_token(nxt)
             toks.append(int(nxt.item()))
             if len(toks) == max_new_tokens:
                 break
             logits = self.forward(nxt)
-        return toks, torch.stack(rows)
+        if self.pp is not None:
+            self.pp.drain()
+        return toks, (torch.stack(rows) if rows else torch.empty(0))

@@ -102,3 +102,44 @@ def test_indexer_scores_and_sparse_attention_match_torch():
         sc = sc.masked_fill(~m[:, None, :], float("-inf"))
         want = torch.einsum("ths,sc->thc", sc.softmax(-1), keys.float()[:, :c]).permute(1, 0, 2)
         assert (o.float() - want).abs().max() < 2e-2 * want.abs().max().clamp_min(1e-3), use_sel
+
+
+def test_gguf_mix_runtime_follows_dequantised_bf16_runtime():
+    """GLM-shaped weight mix (Q8_0 attention, Q4_K dense/shared, Q2_K gate/up and IQ3_XXS down experts) decoded inside
+    the GEMMs, against the same runtime fed the dequantised weights as bf16."""
+    from deepseek_v4_2080ti_b200.formats import gguf as G
+    from deepseek_v4_2080ti_b200.models import mla_moe as mm
+    from deepseek_v4_2080ti_b200.models import mla_moe_gpu as mg
+    from deepseek_v4_2080ti_b200.ops import _lib
+    cfg = mm.MlaMoeConfig(vocab_size=512, hidden_size=256, num_layers=3, first_dense_layers=1, dense_intermediate=256,
+                          q_lora_rank=256, kv_lora_rank=128, num_heads=4, qk_nope_dim=64, qk_rope_dim=32, v_head_dim=128,
+                          index_heads=0, index_dim=0, index_topk=0, num_experts=8, experts_per_token=2,
+                          num_shared_experts=1, expert_intermediate=256, score_func="sigmoid", route_scale=2.5,
+                          expert_format="bf16")
+    state = list(mm.synth_state(cfg, seed=4, std=0.05))
+    mix = mg.GLM_GGUF_MIX
+
+    def roundtrip(name, w):
+        kind = None
+        if ".experts." in name:
+            kind = "down" if name.endswith("w2.weight") else "gate_up"
+        elif ".attn." in name and name.split(".")[-2] in ("wq_a", "wq_b", "wkv_a", "wo"):
+            kind = "attn"
+        elif ".ffn." in name and name.split(".")[-2] in ("w1", "w2", "w3") or name == "head.weight":
+            kind = "ffn"
+        if kind is None or w.dim() != 2:
+            return w
+        t = G.GGMLType[mix[kind]]
+        if w.shape[1] % G.BLOCK_ELEMS[t]:
+            t = G.GGMLType.Q8_0
+        return G.dequantize(G.quantize(w.float(), t), t, w.shape[1]).to(w.dtype)
+
+    deq = [(n, roundtrip(n, w)) for n, w in state]
+    a = mg.MlaMoeGpuRuntime(cfg, mg.MlaMoeGpuWeights(cfg, iter(state), "cuda", gguf_mix=mix), max_context=256)
+    b = mg.MlaMoeGpuRuntime(cfg, mg.MlaMoeGpuWeights(cfg, iter(deq), "cuda"), max_context=256)
+    ids = torch.randint(0, cfg.vocab_size, (60,), generator=torch.Generator().manual_seed(3)).cuda()
+    got, want = a.forward(ids).float(), b.forward(ids).float()
+    torch.cuda.synchronize()
+    _lib.check_status()
+    err = ((got - want).norm() / want.norm()).item()
+    assert err < 3e-2, err
