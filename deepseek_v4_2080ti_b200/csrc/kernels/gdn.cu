@@ -6,14 +6,20 @@
 //                   and the decayed q k^T block;
 //   * gdn_scan    - the sequential inter-chunk recurrence, one CTA per (head, 32-wide
 //                   value slice): v_new = U - W S, O = (q e^gc) S + Aqk v_new,
-//                   S = S e^gc_last + (k e^(gc_last-gc))^T v_new, state kept in shared
-//                   memory in fp32 across all chunks of the call.
+//                   S = S e^gc_last + (k e^(gc_last-gc))^T v_new.  The four products of a
+//                   chunk run on the tensor cores (m16n8k16, fp16 operands, fp32
+//                   accumulation); the state lives in fp32 accumulator registers for the
+//                   whole call and only an fp16 operand copy is refreshed per chunk; the
+//                   next chunk's operands are prefetched with cp.async while the current
+//                   one is multiplied.  The chain is latency-bound (128 dependent steps
+//                   for 8192 tokens), so the step time, not the FLOP rate, is what counts.
 // The chunked form is algebraically the recurrence
 //   S_t = e^{g_t} S_{t-1} + k_t (beta_t (v_t - (e^{g_t} S_{t-1})^T k_t))^T,  o_t = S_t^T q_t / sqrt(dk)
 // and replaces the reference's per-token serial kernels
 // (cpp_engine/backends/cuda/kernels/qwen_half_ops.cu:2282-2600, qwen_gdn_flashqla.cu:36);
 // the math oracle is the chunked PyTorch form src/models/qwen4_exp/attention.py:184-270.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 #include "ops.h"
 
@@ -74,13 +80,15 @@ gdn_step_kernel(float* __restrict__ states, size_t slot_stride, const int* __res
 
 // ------------------------------------------------------------- chunk preparation
 // Workspace rows are indexed by padded token (nchunks * 64) and value head.
+// The tensor-core operands are stored as fp16: every one of them is a product of L2-normalised vectors, decays in
+// (0, 1] and beta in (0, 1), so fp16's range is ample and its 11-bit significand matches tf32.
 struct PrepOut {
-  float* U;    // [Tp, Hv, 128]  T (beta v)
-  float* W;    // [Tp, Hv, 128]  T (beta e^gc k)
-  float* Qg;   // [Tp, Hv, 128]  q_hat * scale * e^gc
-  float* Kg;   // [Tp, Hv, 128]  k_hat * e^(gc_last - gc)
-  float* Aqk;  // [Tp, Hv, 64]   (q_hat*scale . k_hat) e^(gc_i - gc_j), j <= i
-  float* Gl;   // [nchunks, Hv]  e^gc_last
+  float* U;     // [Tp, Hv, 128]            T (beta v)
+  __half* W;    // [Tp, Hv, 128]            T (beta e^gc k)
+  __half* Qg;   // [Tp, Hv, 128]            q_hat * scale * e^gc
+  __half* KgT;  // [nchunks, Hv, 128, 64]   (k_hat * e^(gc_last - gc))^T: key dim major, token minor
+  __half* Aqk;  // [Tp, Hv, 64]             (q_hat*scale . k_hat) e^(gc_i - gc_j), j <= i
+  float* Gl;    // [nchunks, Hv]            e^gc_last
 };
 
 __global__ void __launch_bounds__(256, 2)
@@ -181,8 +189,11 @@ gdn_prepare_kernel(const __nv_bfloat16* __restrict__ mixed, int ld, int q_off, i
         sA[i * AP + j] = (j < i) ? -sbeta[i] * akk[a][b2] * dec : 0.f;
         aq_row[b2] = (j <= i) ? aqk[a][b2] * dec : 0.f;
       }
-      *reinterpret_cast<float4*>(o.Aqk + ((size_t)(t0 + i) * Hv + h) * C + 4 * tj) =
-          make_float4(aq_row[0], aq_row[1], aq_row[2], aq_row[3]);
+      __half2 h01 = __floats2half2_rn(aq_row[0], aq_row[1]), h23 = __floats2half2_rn(aq_row[2], aq_row[3]);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&h01);
+      pk.y = *reinterpret_cast<uint32_t*>(&h23);
+      *reinterpret_cast<uint2*>(o.Aqk + ((size_t)(t0 + i) * Hv + h) * C + 4 * tj) = pk;
     }
   }
   __syncthreads();
@@ -231,141 +242,235 @@ gdn_prepare_kernel(const __nv_bfloat16* __restrict__ mixed, int ld, int q_off, i
       }
     }
     const float gl = sgc[C - 1];
+    auto pack4 = [](float a, float b, float c2, float d) {
+      __half2 x = __floats2half2_rn(a, b), y = __floats2half2_rn(c2, d);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&x);
+      pk.y = *reinterpret_cast<uint32_t*>(&y);
+      return pk;
+    };
+    float kg[8][4];
 #pragma unroll
     for (int a = 0; a < 8; ++a) {
       const int i = 8 * ri + a;
       const size_t base = ((size_t)(t0 + i) * Hv + h) * DK + 4 * cj;
       *reinterpret_cast<float4*>(o.U + base) = make_float4(u[a][0], u[a][1], u[a][2], u[a][3]);
-      *reinterpret_cast<float4*>(o.W + base) = make_float4(w[a][0], w[a][1], w[a][2], w[a][3]);
+      *reinterpret_cast<uint2*>(o.W + base) = pack4(w[a][0], w[a][1], w[a][2], w[a][3]);
       const float eg = __expf(sgc[i]);
       const float ek = __expf(gl - sgc[i]);
       const float4 qv = *reinterpret_cast<const float4*>(sq + i * KP + 4 * cj);
       const float4 kv = *reinterpret_cast<const float4*>(sk + i * KP + 4 * cj);
-      *reinterpret_cast<float4*>(o.Qg + base) = make_float4(qv.x * eg, qv.y * eg, qv.z * eg, qv.w * eg);
-      *reinterpret_cast<float4*>(o.Kg + base) = make_float4(kv.x * ek, kv.y * ek, kv.z * ek, kv.w * ek);
+      *reinterpret_cast<uint2*>(o.Qg + base) = pack4(qv.x * eg, qv.y * eg, qv.z * eg, qv.w * eg);
+      kg[a][0] = kv.x * ek; kg[a][1] = kv.y * ek; kg[a][2] = kv.z * ek; kg[a][3] = kv.w * ek;
+    }
+    // transposed store: for key dim d the 8 tokens of this row group are contiguous (16 bytes)
+#pragma unroll
+    for (int d = 0; d < 4; ++d) {
+      uint4 pk;
+      __half2 p0 = __floats2half2_rn(kg[0][d], kg[1][d]), p1 = __floats2half2_rn(kg[2][d], kg[3][d]);
+      __half2 p2 = __floats2half2_rn(kg[4][d], kg[5][d]), p3 = __floats2half2_rn(kg[6][d], kg[7][d]);
+      pk.x = *reinterpret_cast<uint32_t*>(&p0); pk.y = *reinterpret_cast<uint32_t*>(&p1);
+      pk.z = *reinterpret_cast<uint32_t*>(&p2); pk.w = *reinterpret_cast<uint32_t*>(&p3);
+      *reinterpret_cast<uint4*>(o.KgT + (((size_t)c * Hv + h) * DK + 4 * cj + d) * C + 8 * ri) = pk;
     }
     if (tid == 0) o.Gl[(size_t)c * Hv + h] = __expf(gl);
   }
 }
 
 // ------------------------------------------------------------ inter-chunk scan
-constexpr int SL = 32;  // value columns per CTA
-__global__ void __launch_bounds__(256, 1)
-gdn_scan_kernel(PrepOut w, float* __restrict__ state, __nv_bfloat16* __restrict__ out, int T, int nchunks, int Hv) {
-  extern __shared__ float sm[];
-  float* sW = sm;                 // [64][KP]
-  float* sQ = sW + C * KP;        // [64][KP]
-  float* sK = sQ + C * KP;        // [64][KP]
-  float* sAq = sK + C * KP;       // [64][AP]
-  float* sS = sAq + C * AP;       // [128][SL]
-  float* sVn = sS + DK * SL;      // [64][SL]
-  const int h = blockIdx.x, sl = blockIdx.y;
-  const int tid = threadIdx.x;
-  float* Sg = state + (size_t)h * DK * DV + sl * SL;
-  for (int i = tid; i < DK * SL; i += 256) sS[i] = Sg[(size_t)(i / SL) * DV + (i % SL)];
+constexpr int SL = 32;    // value columns per CTA
+constexpr int WS = 136;   // padded row (halves) of the [64 x 128] W / Qg tiles and of the [32 x 128] state copy
+constexpr int TS = 72;    // padded row (halves) of the [. x 64] tiles (KgT, Aqk, v_new^T)
+constexpr int SCAN_BUF_HALVES = 2 * C * WS + DK * TS + C * TS;            // W, Qg, KgT, Aqk of one chunk
+constexpr int SCAN_SMEM_BYTES = (2 * SCAN_BUF_HALVES + SL * WS + SL * TS) * 2;
 
-  const int rg = tid >> 4, cg = tid & 15;  // 4 rows x 2 cols for [64 x 32] products
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst_smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// A fragment (16 rows x 16 k) of a row-major fp16 tile with row stride `ld` halves.
+__device__ __forceinline__ void load_a(uint32_t (&a)[4], const __half* tile, int ld, int row0, int k0, int g, int tig) {
+  const __half* p = tile + (size_t)(row0 + g) * ld + k0 + 2 * tig;
+  a[0] = *reinterpret_cast<const uint32_t*>(p);
+  a[1] = *reinterpret_cast<const uint32_t*>(p + 8 * ld);
+  a[2] = *reinterpret_cast<const uint32_t*>(p + 8);
+  a[3] = *reinterpret_cast<const uint32_t*>(p + 8 * ld + 8);
+}
+
+// grid (Hv, 128 / SL), 128 threads.  Warp w owns tokens [16w, 16w+16) of the chunk for v_new and O, and state rows
+// (key dims) [32w, 32w+32) for the state update.
+__global__ void __launch_bounds__(128, 1)
+gdn_scan_kernel(PrepOut w, float* __restrict__ state, __nv_bfloat16* __restrict__ out, int T, int nchunks, int Hv) {
+  extern __shared__ __align__(16) __half sh[];
+  __half* sS = sh + 2 * SCAN_BUF_HALVES;   // [SL][WS]  state^T operand copy: value column major, key dim minor
+  __half* sV = sS + SL * WS;               // [SL][TS]  v_new^T: value column major, token minor
+  const int h = blockIdx.x, sl = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
+  float* Sg = state + (size_t)h * DK * DV + sl * SL;
+
+  auto prefetch = [&](int c) {
+    __half* buf = sh + (c & 1) * SCAN_BUF_HALVES;
+    __half* bW = buf, *bQ = buf + C * WS, *bK = bQ + C * WS, *bA = bK + DK * TS;
+    const size_t t0 = (size_t)c * C;
+    for (int i = tid; i < C * 16; i += 128) {            // 64 rows x 16 copies of 16 bytes
+      const int r = i >> 4, q = i & 15;
+      const size_t src = ((t0 + r) * Hv + h) * DK + q * 8;
+      cp_async16(bW + r * WS + q * 8, w.W + src);
+      cp_async16(bQ + r * WS + q * 8, w.Qg + src);
+    }
+    for (int i = tid; i < DK * 8; i += 128) {            // 128 rows x 8 copies
+      const int r = i >> 3, q = i & 7;
+      cp_async16(bK + r * TS + q * 8, w.KgT + (((size_t)c * Hv + h) * DK + r) * C + q * 8);
+    }
+    for (int i = tid; i < C * 8; i += 128) {
+      const int r = i >> 3, q = i & 7;
+      cp_async16(bA + r * TS + q * 8, w.Aqk + ((t0 + r) * Hv + h) * C + q * 8);
+    }
+    cp_async_commit();
+  };
+
+  // state rows 32w + 16mt + g (+8), columns 8nt + 2tig (+1), in accumulator-fragment order
+  float sacc[2][4][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int m = 32 * warp + 16 * mt + g + (e >> 1) * 8, n = 8 * nt + 2 * tig + (e & 1);
+        const float v = Sg[(size_t)m * DV + n];
+        sacc[mt][nt][e] = v;
+        sS[n * WS + m] = __float2half_rn(v);
+      }
+  prefetch(0);
+
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * C;
-    __syncthreads();
-    for (int i = tid; i < C * (DK / 4); i += 256) {
-      const int r = i / (DK / 4), q4 = i % (DK / 4);
-      const size_t base = ((size_t)(t0 + r) * Hv + h) * DK + q4 * 4;
-      *reinterpret_cast<float4*>(sW + r * KP + q4 * 4) = *reinterpret_cast<const float4*>(w.W + base);
-      *reinterpret_cast<float4*>(sQ + r * KP + q4 * 4) = *reinterpret_cast<const float4*>(w.Qg + base);
-      *reinterpret_cast<float4*>(sK + r * KP + q4 * 4) = *reinterpret_cast<const float4*>(w.Kg + base);
-    }
-    for (int i = tid; i < C * C; i += 256) sAq[(i / C) * AP + (i % C)] = w.Aqk[((size_t)(t0 + i / C) * Hv + h) * C + (i % C)];
-    __syncthreads();
+    cp_async_wait_all();
+    __syncthreads();                       // chunk c landed; the state copy of chunk c-1 is complete; sV is free
+    if (c + 1 < nchunks) prefetch(c + 1);
+    const __half* buf = sh + (c & 1) * SCAN_BUF_HALVES;
+    const __half* bW = buf, *bQ = buf + C * WS, *bK = bQ + C * WS, *bA = bK + DK * TS;
+
+    float2 u[4][2];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf)
+        u[nt][hf] = *reinterpret_cast<const float2*>(w.U + ((size_t)(t0 + 16 * warp + g + 8 * hf) * Hv + h) * DV + sl * SL +
+                                                      8 * nt + 2 * tig);
     // v_new = U - W S
-    float acc[4][2];
+    float acc[4][4];
 #pragma unroll
-    for (int a = 0; a < 4; ++a) acc[a][0] = acc[a][1] = 0.f;
-    for (int k = 0; k < DK; k += 4) {
-      float4 wv[4];
+    for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-      for (int a = 0; a < 4; ++a) wv[a] = *reinterpret_cast<const float4*>(sW + (4 * rg + a) * KP + k);
-      const float2 s0 = *reinterpret_cast<const float2*>(sS + (k + 0) * SL + 2 * cg);
-      const float2 s1 = *reinterpret_cast<const float2*>(sS + (k + 1) * SL + 2 * cg);
-      const float2 s2 = *reinterpret_cast<const float2*>(sS + (k + 2) * SL + 2 * cg);
-      const float2 s3 = *reinterpret_cast<const float2*>(sS + (k + 3) * SL + 2 * cg);
+      for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
 #pragma unroll
-      for (int a = 0; a < 4; ++a) {
-        acc[a][0] += wv[a].x * s0.x + wv[a].y * s1.x + wv[a].z * s2.x + wv[a].w * s3.x;
-        acc[a][1] += wv[a].x * s0.y + wv[a].y * s1.y + wv[a].z * s2.y + wv[a].w * s3.y;
+    for (int ks = 0; ks < DK / 16; ++ks) {
+      uint32_t a[4];
+      load_a(a, bW, WS, 16 * warp, 16 * ks, g, tig);
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const __half* bp = sS + (8 * nt + g) * WS + 16 * ks + 2 * tig;
+        mma16816(acc[nt], a, *reinterpret_cast<const uint32_t*>(bp), *reinterpret_cast<const uint32_t*>(bp + 8));
       }
     }
 #pragma unroll
-    for (int a = 0; a < 4; ++a) {
-      const int r = 4 * rg + a;
-      const float2 u = *reinterpret_cast<const float2*>(w.U + ((size_t)(t0 + r) * Hv + h) * DV + sl * SL + 2 * cg);
-      sVn[r * SL + 2 * cg] = u.x - acc[a][0];
-      sVn[r * SL + 2 * cg + 1] = u.y - acc[a][1];
+    for (int nt = 0; nt < 4; ++nt) {
+      const int n = 8 * nt + 2 * tig, r = 16 * warp + g;
+      sV[n * TS + r] = __float2half_rn(u[nt][0].x - acc[nt][0]);
+      sV[(n + 1) * TS + r] = __float2half_rn(u[nt][0].y - acc[nt][1]);
+      sV[n * TS + r + 8] = __float2half_rn(u[nt][1].x - acc[nt][2]);
+      sV[(n + 1) * TS + r + 8] = __float2half_rn(u[nt][1].y - acc[nt][3]);
     }
-    __syncthreads();
-    // O = Qg S + Aqk v_new
+    // O = Qg S (needs only the old state: issued before the barrier so it overlaps the other warps' v_new)
 #pragma unroll
-    for (int a = 0; a < 4; ++a) acc[a][0] = acc[a][1] = 0.f;
-    for (int k = 0; k < DK; k += 4) {
-      float4 qv[4];
+    for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-      for (int a = 0; a < 4; ++a) qv[a] = *reinterpret_cast<const float4*>(sQ + (4 * rg + a) * KP + k);
-      const float2 s0 = *reinterpret_cast<const float2*>(sS + (k + 0) * SL + 2 * cg);
-      const float2 s1 = *reinterpret_cast<const float2*>(sS + (k + 1) * SL + 2 * cg);
-      const float2 s2 = *reinterpret_cast<const float2*>(sS + (k + 2) * SL + 2 * cg);
-      const float2 s3 = *reinterpret_cast<const float2*>(sS + (k + 3) * SL + 2 * cg);
+      for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
 #pragma unroll
-      for (int a = 0; a < 4; ++a) {
-        acc[a][0] += qv[a].x * s0.x + qv[a].y * s1.x + qv[a].z * s2.x + qv[a].w * s3.x;
-        acc[a][1] += qv[a].x * s0.y + qv[a].y * s1.y + qv[a].z * s2.y + qv[a].w * s3.y;
+    for (int ks = 0; ks < DK / 16; ++ks) {
+      uint32_t a[4];
+      load_a(a, bQ, WS, 16 * warp, 16 * ks, g, tig);
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const __half* bp = sS + (8 * nt + g) * WS + 16 * ks + 2 * tig;
+        mma16816(acc[nt], a, *reinterpret_cast<const uint32_t*>(bp), *reinterpret_cast<const uint32_t*>(bp + 8));
       }
     }
-    for (int j = 0; j < C; ++j) {
-      const float2 vn = *reinterpret_cast<const float2*>(sVn + j * SL + 2 * cg);
+    __syncthreads();                       // v_new^T complete; every warp is done reading the old state copy
+    // O += Aqk v_new
 #pragma unroll
-      for (int a = 0; a < 4; ++a) {
-        const float aq = sAq[(4 * rg + a) * AP + j];
-        acc[a][0] += aq * vn.x;
-        acc[a][1] += aq * vn.y;
+    for (int ks = 0; ks < C / 16; ++ks) {
+      uint32_t a[4];
+      load_a(a, bA, TS, 16 * warp, 16 * ks, g, tig);
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const __half* bp = sV + (8 * nt + g) * TS + 16 * ks + 2 * tig;
+        mma16816(acc[nt], a, *reinterpret_cast<const uint32_t*>(bp), *reinterpret_cast<const uint32_t*>(bp + 8));
       }
     }
 #pragma unroll
-    for (int a = 0; a < 4; ++a) {
-      const int t = t0 + 4 * rg + a;
-      if (t < T) {
-        __nv_bfloat162 ob = __floats2bfloat162_rn(acc[a][0], acc[a][1]);
-        *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)t * Hv + h) * DV + sl * SL + 2 * cg) = ob;
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int t = t0 + 16 * warp + g + 8 * hf;
+        if (t < T)
+          *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)t * Hv + h) * DV + sl * SL + 8 * nt + 2 * tig) =
+              __floats2bfloat162_rn(acc[nt][2 * hf], acc[nt][2 * hf + 1]);
+      }
+    // S = S e^gl + KgT v_new, then refresh the fp16 operand copy
+    const float gl = w.Gl[(size_t)c * Hv + h];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sacc[mt][nt][e] *= gl;
+#pragma unroll
+    for (int ks = 0; ks < C / 16; ++ks) {
+      uint32_t b0[4], b1[4];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const __half* bp = sV + (8 * nt + g) * TS + 16 * ks + 2 * tig;
+        b0[nt] = *reinterpret_cast<const uint32_t*>(bp);
+        b1[nt] = *reinterpret_cast<const uint32_t*>(bp + 8);
+      }
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        uint32_t a[4];
+        load_a(a, bK, TS, 32 * warp + 16 * mt, 16 * ks, g, tig);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) mma16816(sacc[mt][nt], a, b0[nt], b1[nt]);
       }
     }
-    __syncthreads();
-    // S = S e^gl + Kg^T v_new : thread -> 8 state rows x 2 cols
-    {
-      const float gl = w.Gl[(size_t)c * Hv + h];
-      float sacc[8][2];
 #pragma unroll
-      for (int a = 0; a < 8; ++a) {
-        const float2 s = *reinterpret_cast<const float2*>(sS + (8 * rg + a) * SL + 2 * cg);
-        sacc[a][0] = s.x * gl;
-        sacc[a][1] = s.y * gl;
-      }
-      for (int r = 0; r < C; ++r) {
-        const float2 vn = *reinterpret_cast<const float2*>(sVn + r * SL + 2 * cg);
-        const float4 k0 = *reinterpret_cast<const float4*>(sK + r * KP + 8 * rg);
-        const float4 k1 = *reinterpret_cast<const float4*>(sK + r * KP + 8 * rg + 4);
-        const float kk[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+    for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-        for (int a = 0; a < 8; ++a) {
-          sacc[a][0] += kk[a] * vn.x;
-          sacc[a][1] += kk[a] * vn.y;
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int m = 32 * warp + 16 * mt + g + (e >> 1) * 8, n = 8 * nt + 2 * tig + (e & 1);
+          sS[n * WS + m] = __float2half_rn(sacc[mt][nt][e]);
         }
-      }
-#pragma unroll
-      for (int a = 0; a < 8; ++a)
-        *reinterpret_cast<float2*>(sS + (8 * rg + a) * SL + 2 * cg) = make_float2(sacc[a][0], sacc[a][1]);
-    }
   }
-  __syncthreads();
-  for (int i = tid; i < DK * SL; i += 256) Sg[(size_t)(i / SL) * DV + (i % SL)] = sS[i];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int m = 32 * warp + 16 * mt + g + (e >> 1) * 8, n = 8 * nt + 2 * tig + (e & 1);
+        Sg[(size_t)m * DV + n] = sacc[mt][nt][e];
+      }
 }
 
 }  // namespace
@@ -376,7 +481,8 @@ extern "C" {
 long long b200_gdn_workspace_floats(int T, int Hv) {
   const long long nch = (T + C - 1) / C;
   const long long Tp = nch * C;
-  return Tp * Hv * (4LL * 128 + 64) + nch * Hv;
+  // U fp32 [Tp,Hv,128]; W, Qg, KgT fp16 [Tp,Hv,128] each; Aqk fp16 [Tp,Hv,64]; Gl fp32 [nch,Hv]
+  return Tp * Hv * (128LL + 3 * 64 + 32) + nch * Hv;
 }
 
 // mixed: [T, ld] bf16 holding q (Hk*128 at q_off), k (k_off) and v (Hv*128 at v_off) after conv+SiLU.
@@ -388,14 +494,14 @@ int b200_gdn_chunked(const void* mixed, int ld, int q_off, int k_off, int v_off,
   const size_t Tp = (size_t)nch * C;
   PrepOut o;
   o.U = workspace;
-  o.W = o.U + Tp * Hv * 128;
+  o.W = reinterpret_cast<__half*>(o.U + Tp * Hv * 128);
   o.Qg = o.W + Tp * Hv * 128;
-  o.Kg = o.Qg + Tp * Hv * 128;
-  o.Aqk = o.Kg + Tp * Hv * 128;
-  o.Gl = o.Aqk + Tp * Hv * 64;
+  o.KgT = o.Qg + Tp * Hv * 128;
+  o.Aqk = o.KgT + Tp * Hv * 128;
+  o.Gl = reinterpret_cast<float*>(o.Aqk + Tp * Hv * 64);
   const float q_scale = 0.08838834764831845f;  // 1/sqrt(128)
   const int prep_smem = (2 * C * KP + C * AP + 2 * C) * 4 + C * DV * 2;
-  const int scan_smem = (3 * C * KP + C * AP + DK * SL + C * SL) * 4;
+  const int scan_smem = SCAN_SMEM_BYTES;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gdn_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, prep_smem);
@@ -406,7 +512,7 @@ int b200_gdn_chunked(const void* mixed, int ld, int q_off, int k_off, int v_off,
   }
   gdn_prepare_kernel<<<dim3(Hv, nch), 256, prep_smem, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(mixed), ld, q_off, k_off, v_off, g, beta, o, T, Hv, Hk, q_scale);
-  gdn_scan_kernel<<<dim3(Hv, DV / SL), 256, scan_smem, stream>>>(o, state, reinterpret_cast<__nv_bfloat16*>(out), T,
+  gdn_scan_kernel<<<dim3(Hv, DV / SL), 128, scan_smem, stream>>>(o, state, reinterpret_cast<__nv_bfloat16*>(out), T,
                                                                   nch, Hv);
   return (int)cudaGetLastError();
 }

@@ -106,6 +106,17 @@ class MlaMoeGpuWeights:
         self.head = self._lin(sd["head.weight"], "ffn") if last else None
         self.layers = [self._layer(sd, f"layers.{i}.", i < cfg.first_dense_layers)
                        if self.layer_lo <= i < self.layer_hi else None for i in range(cfg.num_layers)]
+        # multi-token-prediction blocks live with the head: e_proj(norm(embed)) + h_proj(norm(hidden)) -> block -> head
+        self.mtp = []
+        if last and cfg.mtp_layers > 0 and "mtp.0.e_proj.weight" in sd:
+            b16 = lambda t: t.to(dev, torch.bfloat16).contiguous()
+            for j in range(cfg.mtp_layers):
+                p = f"mtp.{j}."
+                self.mtp.append({"e_proj": self._lin(sd[p + "e_proj.weight"], "ffn"), "h_proj": self._lin(sd[p + "h_proj.weight"], "ffn"),
+                                 "enorm": b16(sd[p + "enorm.weight"]), "hnorm": b16(sd[p + "hnorm.weight"]),
+                                 "block": self._layer(sd, p, False)})
+            if self.embed is None:
+                self.embed = sd["embed.weight"].to(dev, torch.bfloat16).contiguous()
 
     def _lin(self, w: torch.Tensor, kind: str = "ffn"):
         w = w.to(self.device)
@@ -207,8 +218,10 @@ class MlaMoeGpuRuntime:
         self.max_context = max_context
         nblk = (max_context + block_size - 1) // block_size
         rows = nblk * block_size
-        n = cfg.num_layers
+        n = cfg.num_layers + len(weights.mtp)
         d = cfg.kv_lora_rank + cfg.qk_rope_dim
+        self.mtp_length = 0
+        self.spec_stats = {"steps": 0, "drafted": 0, "accepted": 0}
         self.cache = torch.zeros(n, rows, d, dtype=torch.bfloat16, device=self.device)
         self.idx_cache = torch.zeros(n, rows, max(1, cfg.index_dim), dtype=torch.bfloat16, device=self.device)
         # identity page table: block b of the sequence is physical block b (one resident sequence)
@@ -217,6 +230,7 @@ class MlaMoeGpuRuntime:
 
     def reset(self) -> None:
         self.length = 0
+        self.mtp_length = 0
 
     def _swiglu(self, x, gu, down):
         return _mm(basic.silu_mul(_mm(x, gu)), down)
@@ -260,7 +274,74 @@ class MlaMoeGpuRuntime:
         return self.comm.all_reduce(y)
 
     @torch.no_grad()
-    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+    def mtp_draft(self, hidden: torch.Tensor, next_ids: torch.Tensor, depth: int = 0) -> torch.Tensor:
+        """Multi-token-prediction block ``depth`` over positions [mtp_length, mtp_length + T): ``hidden`` [T, H] are
+        the main model's final residual rows at those positions, ``next_ids`` [T] the tokens that follow them.
+        Returns fp32 logits [T, vocab] for the token after next.  (Reference: MTPBlock,
+        src/models/deepseek_v4/runtime.py:4610-4642, draft_with_mtp :4904.)"""
+        cfg, w = self.cfg, self.w
+        m = w.mtp[depth]
+        t = hidden.shape[0]
+        pos = torch.arange(self.mtp_length, self.mtp_length + t, dtype=torch.int32, device=self.device)
+        emb = basic.embedding(next_ids.to(torch.int32), w.embed, 0, cfg.vocab_size)
+        h = _mm(basic.rmsnorm(emb, m["enorm"], cfg.rms_norm_eps), m["e_proj"])
+        basic.add_(h, _mm(basic.rmsnorm(hidden, m["hnorm"], cfg.rms_norm_eps), m["h_proj"]))
+        lw = m["block"]
+        li = cfg.num_layers + depth
+        x = basic.rmsnorm(h, lw.attn_norm, cfg.rms_norm_eps)
+        d_attn = self._attention(lw, li, x, pos, self.mtp_length + t)
+        x = basic.add_rmsnorm(h, d_attn, lw.ffn_norm, cfg.rms_norm_eps)
+        delta = self._ffn(lw, x)
+        x = basic.add_rmsnorm(h, delta, w.norm, cfg.rms_norm_eps)
+        self.mtp_length += t
+        return _mm(x, w.head, out_f32=True)
+
+    @torch.no_grad()
+    def generate_mtp(self, prompt: torch.Tensor, max_new_tokens: int, chunk: int = 2048, draft_override=None) -> list[int]:
+        """Greedy generation with depth-1 speculative drafting: each step verifies [token, draft] in one two-row
+        pass; an accepted draft yields two tokens per pass, a rejected one rolls the latent cache back by a row.
+        The stream equals plain greedy decoding.  ``draft_override(n_emitted) -> int | None`` replaces the draft
+        (tests use it to force acceptance)."""
+        assert self.pp is None and self.w.mtp, "speculative decoding needs the MTP block and an unsplit model"
+        self.reset()
+        self.spec_stats = {"steps": 0, "drafted": 0, "accepted": 0}
+        prompt = prompt.to(self.device, torch.int32)
+        hid, logits = [], None
+        for s in range(0, prompt.numel(), chunk):
+            logits, h = self.forward(prompt[s:s + chunk], return_hidden=True)
+            hid.append(h)
+        tok = basic.argmax(logits[-1:])
+        out = [int(tok.item())]
+        d_logits = self.mtp_draft(torch.cat(hid), torch.cat([prompt[1:], tok.to(torch.int32)]))
+        draft = basic.argmax(d_logits[-1:])
+        while len(out) < max_new_tokens:
+            if draft_override is not None:
+                forced = draft_override(len(out))
+                if forced is not None:
+                    draft = torch.tensor([forced], dtype=torch.int32, device=self.device)
+            pair = torch.cat([tok.to(torch.int32), draft.to(torch.int32)])
+            logits, h = self.forward(pair, return_hidden=True)
+            nxt = basic.argmax(logits)                      # [2]: token after `tok`, token after `draft`
+            self.spec_stats["steps"] += 1
+            self.spec_stats["drafted"] += 1
+            ok = bool((nxt[0] == draft[0]).item())
+            if ok:
+                self.spec_stats["accepted"] += 1
+                out.append(int(nxt[0].item()))
+                if len(out) < max_new_tokens:
+                    out.append(int(nxt[1].item()))
+                tok = nxt[1:2]
+                d_logits = self.mtp_draft(h, nxt.to(torch.int32))
+            else:
+                self.length -= 1                            # the draft's cache row is overwritten by the next pass
+                out.append(int(nxt[0].item()))
+                tok = nxt[0:1]
+                d_logits = self.mtp_draft(h[:1], nxt[:1].to(torch.int32))
+            draft = basic.argmax(d_logits[-1:])
+        return out[:max_new_tokens]
+
+    @torch.no_grad()
+    def forward(self, ids: torch.Tensor, return_hidden: bool = False):
         """Append ``ids`` [T] (int32, device) to the context; returns fp32 logits [T, vocab] (on the last pipeline
         stage; earlier stages send their hidden rows on and return None)."""
         cfg, w = self.cfg, self.w
@@ -287,8 +368,9 @@ class MlaMoeGpuRuntime:
             basic.add_(h, delta)
             self.pp.send_hidden(h)
             return None
-        x = basic.add_rmsnorm(h, delta, w.norm, cfg.rms_norm_eps)
-        return _mm(x, w.head, out_f32=True)
+        x = basic.add_rmsnorm(h, delta, w.norm, cfg.rms_norm_eps)          # h becomes the final residual stream
+        logits = _mm(x, w.head, out_f32=True)
+        return (logits, h) if return_hidden else logits
 
     @torch.no_grad()
     def generate(self, prompt: torch.Tensor, max_new_tokens: int, chunk: int = 2048) -> tuple[list[int], torch.Tensor]:

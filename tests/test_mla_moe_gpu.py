@@ -143,3 +143,28 @@ def test_gguf_mix_runtime_follows_dequantised_bf16_runtime():
     _lib.check_status()
     err = ((got - want).norm() / want.norm()).item()
     assert err < 3e-2, err
+
+
+def test_mtp_speculative_stream_equals_greedy():
+    """Depth-1 MTP drafting: with the model's own drafts (mostly rejected on random weights) and with forced-correct
+    drafts (always accepted) the emitted stream is the plain greedy stream; accepted steps halve the pass count."""
+    import dataclasses
+    from deepseek_v4_2080ti_b200.models import mla_moe as mm
+    from deepseek_v4_2080ti_b200.models import mla_moe_gpu as mg
+    from deepseek_v4_2080ti_b200.ops import _lib
+    cfg = dataclasses.replace(_cfg(False), mtp_layers=1, expert_format="bf16")
+    state = list(mm.synth_state(cfg, seed=8, std=0.05))
+    assert any(n.startswith("mtp.0.") for n, _ in state)
+    rt = mg.MlaMoeGpuRuntime(cfg, mg.MlaMoeGpuWeights(cfg, iter(state), "cuda"), max_context=256)
+    prompt = torch.randint(0, cfg.vocab_size, (48,), generator=torch.Generator().manual_seed(9))
+    n = 12
+    want, _ = rt.generate(prompt, n)
+    got = rt.generate_mtp(prompt, n)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert got == want, (got, want)
+    assert rt.spec_stats["steps"] >= (n - 1) // 2
+    forced = rt.generate_mtp(prompt, n, draft_override=lambda k: want[k] if k < n else None)
+    _lib.check_status()
+    assert forced == want, (forced, want)
+    assert rt.spec_stats["accepted"] == rt.spec_stats["steps"] and rt.spec_stats["steps"] <= (n + 1) // 2
