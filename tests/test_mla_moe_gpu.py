@@ -119,22 +119,29 @@ def test_gguf_mix_runtime_follows_dequantised_bf16_runtime():
     state = list(mm.synth_state(cfg, seed=4, std=0.05))
     mix = mg.GLM_GGUF_MIX
 
-    def roundtrip(name, w):
-        kind = None
-        if ".experts." in name:
-            kind = "down" if name.endswith("w2.weight") else "gate_up"
-        elif ".attn." in name and name.split(".")[-2] in ("wq_a", "wq_b", "wkv_a", "wo"):
-            kind = "attn"
-        elif ".ffn." in name and name.split(".")[-2] in ("w1", "w2", "w3") or name == "head.weight":
-            kind = "ffn"
-        if kind is None or w.dim() != 2:
-            return w
+    def rt(w, kind):
+        """Quantise + dequantise on the device, in the shapes the loader quantises (the quantisers' scale search is a
+        floating-point reduction: same device and shape give the same blocks)."""
         t = G.GGMLType[mix[kind]]
         if w.shape[1] % G.BLOCK_ELEMS[t]:
             t = G.GGMLType.Q8_0
-        return G.dequantize(G.quantize(w.float(), t), t, w.shape[1]).to(w.dtype)
+        return G.dequantize(G.quantize(w.float().cuda(), t), t, w.shape[1]).to(torch.bfloat16).cpu()
 
-    deq = [(n, roundtrip(n, w)) for n, w in state]
+    sd = dict(state)
+    deq = dict(sd)
+    for n, w in sd.items():
+        leaf = n.split(".")[-2]
+        if ".attn." in n and leaf in ("wq_a", "wq_b", "wkv_a", "wo"):
+            deq[n] = rt(w, "attn")
+        elif n == "head.weight":
+            deq[n] = rt(w, "ffn")
+        elif leaf == "w2" and ".ffn." in n:
+            deq[n] = rt(w, "down" if ".experts." in n else "ffn")
+        elif leaf == "w1" and ".ffn." in n:                       # gate and up rows are quantised as one matrix
+            n3 = n.replace(".w1.", ".w3.")
+            both = rt(torch.cat([w, sd[n3]]), "gate_up" if ".experts." in n else "ffn")
+            deq[n], deq[n3] = both[:w.shape[0]].contiguous(), both[w.shape[0]:].contiguous()
+    deq = list(deq.items())
     a = mg.MlaMoeGpuRuntime(cfg, mg.MlaMoeGpuWeights(cfg, iter(state), "cuda", gguf_mix=mix), max_context=256)
     b = mg.MlaMoeGpuRuntime(cfg, mg.MlaMoeGpuWeights(cfg, iter(deq), "cuda"), max_context=256)
     ids = torch.randint(0, cfg.vocab_size, (60,), generator=torch.Generator().manual_seed(3)).cuda()
