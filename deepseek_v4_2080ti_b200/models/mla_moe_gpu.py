@@ -142,6 +142,30 @@ class MlaMoeGpuWeights:
         k = w.shape[1] // self.world
         return w[:, self.rank * k:(self.rank + 1) * k]
 
+    def _lin_cols(self, w: torch.Tensor, kind: str):
+        """Input-dimension (row-parallel) shard of a matrix.  GGUF blocks run along the input dimension, so the full
+        matrix is quantised as a checkpoint would hold it and this rank takes its run of blocks; when the shard does
+        not hold whole blocks its dequantised values are re-encoded as Q8_0 (32-wide blocks)."""
+        if self.gguf_mix is None or self.world == 1:
+            return self._lin(self._cols(w), kind)
+        w = w.to(self.device)
+        n, k = w.shape
+        kl = k // self.world
+        t = G.GGMLType[self.gguf_mix[kind]]
+        if k % G.BLOCK_ELEMS[t] or k % 64:
+            t = G.GGMLType.Q8_0
+        if k % 64:
+            return self._lin(self._cols(w), kind)
+        raw = G.quantize(w.float(), t)
+        be, bb = G.BLOCK_ELEMS[t], G.BLOCK_BYTES[t]
+        if kl % be == 0 and kl % 64 == 0:
+            part = raw.view(n, k // be, bb)[:, self.rank * kl // be:(self.rank + 1) * kl // be].reshape(n, -1).contiguous()
+            return gguf_gemm.GGUFLinear.from_raw(part, t, n, kl, self.device)
+        deq = G.dequantize(raw, t, k)[:, self.rank * kl:(self.rank + 1) * kl].contiguous()
+        if kl % 64:
+            return PackedLinear.from_bf16(deq.to(torch.bfloat16))
+        return gguf_gemm.GGUFLinear.from_raw(G.quantize(deq, G.GGMLType.Q8_0), G.GGMLType.Q8_0, n, kl, self.device)
+
     def _layer(self, sd, p: str, dense: bool) -> GpuLayer:
         cfg, dev = self.cfg, self.device
         b = lambda t: t.to(dev, torch.bfloat16).contiguous()
@@ -158,7 +182,7 @@ class MlaMoeGpuWeights:
             wkv_a=self._lin(sd[a + "wkv_a.weight"], "attn"), kv_norm=b(sd[a + "kv_norm.weight"]),
             w_uk_t=w_uk.transpose(1, 2).reshape(self.h_local * cfg.kv_lora_rank, cfg.qk_nope_dim).contiguous(),
             w_uv=wkv_b[:, cfg.qk_nope_dim:].reshape(self.h_local * cfg.v_head_dim, cfg.kv_lora_rank).contiguous(),
-            wo=self._lin(self._cols(sd[a + "wo.weight"]), "attn"))
+            wo=self._lin_cols(sd[a + "wo.weight"], "attn"))
         if cfg.index_heads > 0:
             # the indexer is small and replicated: every rank scores with all index heads
             lw.idx_wq, lw.idx_wk = self._lin(sd[a + "indexer.wq_b.weight"]), self._lin(sd[a + "indexer.wk.weight"])
@@ -166,14 +190,14 @@ class MlaMoeGpuWeights:
         f = p + "ffn."
         if dense:
             lw.dense_gu = self._lin(torch.cat([self._rows(sd[f + "w1.weight"]), self._rows(sd[f + "w3.weight"])]))
-            lw.dense_down = self._lin(self._cols(sd[f + "w2.weight"]))
+            lw.dense_down = self._lin_cols(sd[f + "w2.weight"], "ffn")
             return lw
         lw.gate = PackedLinear.from_bf16(sd[f + "gate.weight"].to(dev))
         lw.gate_bias = sd[f + "gate.bias"].to(dev, torch.float32)
         if cfg.num_shared_experts:
             lw.shared_gu = self._lin(torch.cat([self._rows(sd[f + "shared_experts.w1.weight"]),
                                                 self._rows(sd[f + "shared_experts.w3.weight"])]))
-            lw.shared_down = self._lin(self._cols(sd[f + "shared_experts.w2.weight"]))
+            lw.shared_down = self._lin_cols(sd[f + "shared_experts.w2.weight"], "ffn")
         es = range(self.expert_lo, self.expert_hi)
         if self.gguf_mix is not None:
             t13, t2 = G.GGMLType[self.gguf_mix["gate_up"]], G.GGMLType[self.gguf_mix["down"]]

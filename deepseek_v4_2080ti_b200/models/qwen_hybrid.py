@@ -389,6 +389,9 @@ class QwenHybridRuntime:
                                  dtype=torch.bfloat16, device=dev)
         self.inv_freq = attention.rope_inv_freq(cfg.rotary_dim, cfg.rope_theta, dev)
         self.free_blocks = list(range(self.num_blocks - 1, 0, -1))
+        self.block_refs = [0] * self.num_blocks        # sequences + prefix-cache entries holding each block
+        self.prefix_cache = None
+        self.prefill_tokens_computed = 0               # prompt tokens actually run through the model (cache hits skip)
         self.free_slots = list(range(max_slots - 1, -1, -1))
         self.seqs: dict[int, SeqState] = {}
         self.block_table = torch.zeros(max_slots, self.max_blocks_per_seq, dtype=torch.int32, device=dev)
@@ -410,8 +413,47 @@ class QwenHybridRuntime:
 
     def free(self, slot: int) -> None:
         st = self.seqs.pop(slot)
-        self.free_blocks.extend(reversed(st.blocks))
+        self._release_blocks(st.blocks)
         self.free_slots.append(slot)
+
+    def _release_blocks(self, blocks: list[int]) -> None:
+        for b in reversed(blocks):
+            self.block_refs[b] -= 1
+            if self.block_refs[b] == 0:
+                self.free_blocks.append(b)
+
+    def enable_prefix_cache(self, interval: int = 256, max_entries: int = 8, max_bytes: int = 8 << 30):
+        """Re-use KV blocks and recurrent-state snapshots of already-seen prompt prefixes (runtime/prefix_cache.py).
+        ``interval`` (tokens between snapshot points) must be a multiple of the KV block size."""
+        from ..runtime.prefix_cache import PrefixCache
+        if interval % self.block_size:
+            raise ValueError("snapshot interval must be a multiple of the KV block size")
+        self.prefix_cache = PrefixCache(interval, max_entries, max_bytes, release_blocks=self._release_blocks)
+        return self.prefix_cache
+
+    def _restore_prefix(self, st: SeqState, tokens: list[int]) -> None:
+        e = self.prefix_cache.lookup(tokens)
+        if e is None:
+            return
+        for i, b in enumerate(e.blocks):
+            self.block_refs[b] += 1
+            self._bt_host[st.slot, i] = b
+        st.blocks = list(e.blocks)
+        self.block_table[st.slot].copy_(self._bt_host[st.slot], non_blocking=True)
+        self.states[st.slot].copy_(e.snapshot[0])
+        self.tails[st.slot].copy_(e.snapshot[1])
+        st.length = e.tokens
+
+    def _snapshot_prefix(self, st: SeqState, tokens: list[int]) -> None:
+        n = st.length
+        if self.prefix_cache.contains(tokens, n):
+            return
+        snap = (self.states[st.slot].clone(), self.tails[st.slot].clone())
+        blocks = st.blocks[:n // self.block_size]
+        nbytes = snap[0].numel() * 4 + snap[1].numel() * 2
+        if self.prefix_cache.insert(tokens, n, blocks, snap, nbytes):
+            for b in blocks:
+                self.block_refs[b] += 1
 
     def _ensure_blocks(self, st: SeqState, new_len: int) -> None:
         need = (new_len + self.block_size - 1) // self.block_size
@@ -422,6 +464,7 @@ class QwenHybridRuntime:
             if not self.free_blocks:
                 raise RuntimeError("KV cache exhausted")
             b = self.free_blocks.pop()
+            self.block_refs[b] = 1
             self._bt_host[st.slot, len(st.blocks)] = b
             st.blocks.append(b)
             changed = True
@@ -549,14 +592,27 @@ class QwenHybridRuntime:
 
     # ---- public: prefill one sequence (chunked), returns the next token id tensor [1] (device)
     @torch.no_grad()
-    def prefill(self, slot: int, token_ids: torch.Tensor, chunk: int = 8192) -> torch.Tensor:
-        """token_ids: int32 device tensor [T]. Appends to the slot's context. Returns greedy next token."""
+    def prefill(self, slot: int, token_ids: torch.Tensor, chunk: int = 8192, host_tokens: list[int] | None = None) -> torch.Tensor:
+        """token_ids: int32 device tensor [T]. Appends to the slot's context. Returns greedy next token.
+        With the prefix cache enabled a fresh slot first resumes from the longest cached prefix of the prompt and
+        chunks are cut at the snapshot points (``host_tokens`` saves the device-to-host copy of the ids)."""
         st = self.seqs[slot]
         l0 = _lib.LAUNCHES
         nxt = None
         total = token_ids.numel()
-        for s in range(0, total, chunk):
-            ids = token_ids[s:s + chunk]
+        cuts, s = [], 0
+        if self.prefix_cache is not None and st.length == 0:
+            # fresh slot: positions equal indices into token_ids
+            host_tokens = host_tokens if host_tokens is not None else token_ids.tolist()
+            self._restore_prefix(st, host_tokens)
+            s = st.length
+            cuts = self.prefix_cache.boundaries(st.length, total)
+        while s < total:
+            e = min(total, s + chunk)
+            nxt_cut = next((c for c in cuts if c > s), None)
+            if nxt_cut is not None and nxt_cut < e:
+                e = nxt_cut
+            ids = token_ids[s:e]
             t = ids.numel()
             self._ensure_blocks(st, st.length + t)
             pos = torch.arange(st.length, st.length + t, dtype=torch.int32, device=self.device)
@@ -565,12 +621,15 @@ class QwenHybridRuntime:
             i32 = lambda v: torch.tensor([v], dtype=torch.int32, device=self.device)
             meta = {"mode": "prefill", "block_table": self.block_table[slot:slot + 1], "q_start": i32(0),
                     "q_len": i32(t), "kv_len": i32(st.length + t), "max_q_len": t}
-            last = s + t >= total
             rows = torch.tensor([t - 1], dtype=torch.int64, device=self.device)
             logits = self._forward(ids, pos, kv_slots, meta, slot, None, rows)
             st.length += t
-            if last:
+            self.prefill_tokens_computed += t
+            if e in cuts:
+                self._snapshot_prefix(st, host_tokens)
+            if e >= total:
                 nxt = self._next_tokens(logits)
+            s = e
         self.launches = _lib.LAUNCHES - l0
         return nxt
 

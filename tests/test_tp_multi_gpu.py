@@ -21,7 +21,7 @@ def test_tp_worker(world):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(29600 + world), os.path.join(HERE, "tp_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
-    assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, (r.stdout[-3000:], r.stderr[-3000:])
+    assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, (r.stdout[-3000:], r.stderr[-8000:])
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
@@ -34,4 +34,4 @@ def test_pipeline_worker(world):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(29700 + world), os.path.join(HERE, "pp_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
-    assert r.returncode == 0 and "PP_WORKER_OK" in r.stdout, (r.stdout[-3000:], r.stderr[-3000:])
+    assert r.returncode == 0 and "PP_WORKER_OK" in r.stdout, (r.stdout[-3000:], r.stderr[-8000:])
