@@ -180,10 +180,6 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   constexpr int S = L::SR;                       // raw ring depth
   constexpr int SA = L::SA;                      // decoded ring depth (0 for bf16 weights)
   constexpr int SAB = SA > 0 ? SA : 1;
-  // tcgen05.commit occupies the tensor pipe for on the order of 100 ns.  At wide token tiles the MMAs of one
-  // k-block take only ~280 ns, so k-blocks are released in pairs: the commit after an odd stage covers the even
-  // stage before it (a commit tracks every earlier MMA), and whoever waits for stage s waits on barrier s | 1.
-  constexpr bool PAIR = (S % 2 == 0) && (BN >= 128);
   constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
   extern __shared__ uint8_t smem_raw_base[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_base) + 1023) &
@@ -252,7 +248,7 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          if (!mbar_wait(&empty[PAIR ? (s | 1) : s], ph ^ 1)) {
+          if (!mbar_wait(&empty[s], ph ^ 1)) {
             atomicExch(p.status, ERR_WAIT_STAGE);
             *abort_flag = 1;
             break;
@@ -318,7 +314,7 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           // One commit per k-block frees the raw stage for the producer and, SA k-blocks later, the
           // decoded slot for the decode warps (they wait on the same barrier): tcgen05.commit occupies
           // the tensor pipe for a few hundred cycles, so a second commit per k-block would cap the rate.
-          if (!PAIR || (s & 1)) umma_commit(&empty[s]);
+          umma_commit(&empty[s]);
         }
         if (failed) {
           *abort_flag = 1;
@@ -379,7 +375,7 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           if (it >= (uint32_t)SAB) {
             // decoded slot `grp` was last read by the MMAs of k-block it - SA
             const uint32_t prev = it - SAB;
-            ok = ok && mbar_wait(&empty[PAIR ? ((prev % S) | 1) : (prev % S)], (prev / S) & 1);
+            ok = ok && mbar_wait(&empty[prev % S], (prev / S) & 1);
           }
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) {

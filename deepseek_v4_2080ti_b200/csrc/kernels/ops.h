@@ -70,6 +70,12 @@ int b200_mla_attention(const void* q_lat, const void* q_pe, const void* cache, c
                        int R, float scale, cudaStream_t stream);
 int b200_transpose_heads(const void* in, void* out, int H, int T, int D, cudaStream_t stream);
 
+// ---- sampling (sampling.cu; candidate selection by b200_topk_rows of attn_mla.cu)
+int b200_sample_candidates(const float* vals, int ld, const int* idx, int K, int rows, float temperature, float top_p,
+                           float min_p, const float* u, int* out_pos, float* out_prob, cudaStream_t stream);
+int b200_apply_penalties(float* logits, int ld, int n, int rows, const int* counts, float repetition, float presence,
+                         float frequency, cudaStream_t stream);
+
 // ---- load-time weight preparation (prepack.cu)
 unsigned long long b200_prepack_fp8_bytes(int N, int K);
 int b200_prepack_fp8(const void* w_fp8, void* out, int N, int K, cudaStream_t stream);

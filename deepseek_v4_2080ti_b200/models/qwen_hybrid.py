@@ -350,6 +350,9 @@ class NoComm:
     def argmax_merge(self, idx: torch.Tensor, val: torch.Tensor) -> torch.Tensor:
         return idx
 
+    def all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        return t.unsqueeze(0)
+
 
 @dataclass
 class SeqState:
@@ -586,13 +589,20 @@ class QwenHybridRuntime:
         x = basic.add_rmsnorm(h, delta, w.final_norm, eps, True)
         return gemm.linear(x, w.lm_head, out_f32=True)
 
-    def _next_tokens(self, logits: torch.Tensor) -> torch.Tensor:
-        idx, val = basic.argmax(logits, self.w.head_lo, True)
-        return self.comm.argmax_merge(idx, val)
+    def _next_tokens(self, logits: torch.Tensor, sampling=None, u: torch.Tensor | None = None,
+                     counts: torch.Tensor | None = None) -> torch.Tensor:
+        """Greedy arg-max over the vocabulary shards, or (``sampling``: ops.sampling.DeviceSampling, ``u``: fp32 [B]
+        uniforms) a temperature / top-k / top-p / min-p draw on the device."""
+        if sampling is None:
+            idx, val = basic.argmax(logits, self.w.head_lo, True)
+            return self.comm.argmax_merge(idx, val)
+        from ..ops import sampling as smp
+        return smp.sample(logits.float(), sampling, u.to(self.device, torch.float32), self.w.head_lo, self.comm, counts)
 
     # ---- public: prefill one sequence (chunked), returns the next token id tensor [1] (device)
     @torch.no_grad()
-    def prefill(self, slot: int, token_ids: torch.Tensor, chunk: int = 8192, host_tokens: list[int] | None = None) -> torch.Tensor:
+    def prefill(self, slot: int, token_ids: torch.Tensor, chunk: int = 8192, host_tokens: list[int] | None = None,
+                sampling=None, u: torch.Tensor | None = None, counts: torch.Tensor | None = None) -> torch.Tensor:
         """token_ids: int32 device tensor [T]. Appends to the slot's context. Returns greedy next token.
         With the prefix cache enabled a fresh slot first resumes from the longest cached prefix of the prompt and
         chunks are cut at the snapshot points (``host_tokens`` saves the device-to-host copy of the ids)."""
@@ -628,7 +638,7 @@ class QwenHybridRuntime:
             if e in cuts:
                 self._snapshot_prefix(st, host_tokens)
             if e >= total:
-                nxt = self._next_tokens(logits)
+                nxt = self._next_tokens(logits, sampling, u, counts)
             s = e
         self.launches = _lib.LAUNCHES - l0
         return nxt
@@ -651,11 +661,14 @@ class QwenHybridRuntime:
             logits = self._forward_decode(buf["ids"], buf["pos"], buf["kv_slots"], meta, buf["slots"])
         else:
             logits = self._forward(buf["ids"], buf["pos"], buf["kv_slots"], meta, None, buf["slots"], None)
+        buf["logits"] = logits          # kept for device-side sampling after the (possibly replayed) step
         return self._next_tokens(logits)
 
     @torch.no_grad()
-    def decode(self, slots: list[int], token_ids: torch.Tensor, use_graph: bool = True) -> torch.Tensor:
-        """One new token for each slot. token_ids: int32 device tensor [B]. Returns next tokens [B] (device)."""
+    def decode(self, slots: list[int], token_ids: torch.Tensor, use_graph: bool = True, sampling=None,
+               u: torch.Tensor | None = None, counts: torch.Tensor | None = None) -> torch.Tensor:
+        """One new token for each slot. token_ids: int32 device tensor [B]. Returns next tokens [B] (device): greedy,
+        or drawn on the device from the step's logits when ``sampling`` / ``u`` are given (see ``_next_tokens``)."""
         b = len(slots)
         sts = [self.seqs[s] for s in slots]
         for st in sts:
@@ -703,6 +716,8 @@ class QwenHybridRuntime:
             out = entry["out"]
         for st in sts:
             st.length += 1
+        if sampling is not None:
+            out = self._next_tokens(buf["logits"], sampling, u, counts)
         return out
 
     @torch.no_grad()

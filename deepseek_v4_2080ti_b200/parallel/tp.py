@@ -44,6 +44,14 @@ class TPComm:
             self.bytes_reduced += t.numel() * t.element_size()
         return t
 
+    def all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        """[world, *t.shape]: every rank's tensor, in rank order."""
+        if self.world == 1:
+            return t.unsqueeze(0)
+        out = torch.empty(self.world, *t.shape, dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t.contiguous(), group=self.group)
+        return out
+
     def moe_combine(self, y: torch.Tensor, route_row: torch.Tensor, wts: torch.Tensor, base: torch.Tensor | None,
                     residual: torch.Tensor | None, t: int, k: int, h: int, mode: int = 0) -> torch.Tensor:
         """Library baseline of the expert-parallel combine: local weighted combine, NCCL all-reduce, residual add."""

@@ -50,27 +50,97 @@ class Channel:
 
 class RuntimeAdapter:
     """The surface ``NativeBackend`` drives, over a ``QwenHybridRuntime``."""
-    supports_sampling = False
-    supports_prefix_cache = False
+    supports_sampling = True
+    supports_prefix_cache = True
     speculative_methods: tuple[str, ...] = ()
 
     def __init__(self, rt: qh.QwenHybridRuntime, max_context: int, eos_token_ids=()):
         self.rt, self.max_context, self.eos_token_ids = rt, max_context, tuple(eos_token_ids)
         self.last_cached_tokens = 0
+        self._rng: dict[int, torch.Generator] = {}      # per slot: the request's seeded generator
+        self._counts: dict[int, torch.Tensor] = {}      # per slot: occurrences of each local vocabulary id
+        self._seed_counter = 0
+
+    # ---- sampling state of a slot
+    def _sampling(self, slot: int, sp: Any, prompt: list[int] | None):
+        from ..ops.sampling import DeviceSampling
+        ds = DeviceSampling.from_params(sp)
+        if ds is None:
+            return None
+        if slot not in self._rng:
+            g = torch.Generator()
+            seed = getattr(sp, "seed", None)
+            if seed is None:
+                self._seed_counter += 1
+                seed = 0x5EED0000 + self._seed_counter
+            g.manual_seed(int(seed))
+            self._rng[slot] = g
+        if ds.has_penalties and slot not in self._counts:
+            w = self.rt.w
+            n_local = w.lm_head.n
+            c = torch.zeros(n_local, dtype=torch.int32, device=self.rt.device)
+            if prompt:
+                self._count(c, prompt)
+            self._counts[slot] = c
+        return ds
+
+    def _count(self, c: torch.Tensor, tokens: list[int]) -> None:
+        lo = self.rt.w.head_lo
+        ids = torch.tensor([t - lo for t in tokens if lo <= t < lo + c.numel()], dtype=torch.int64, device=c.device)
+        if ids.numel():
+            c.index_add_(0, ids, torch.ones_like(ids, dtype=torch.int32))
+
+    def _draws(self, slots: list[int]) -> torch.Tensor:
+        return torch.cat([torch.rand(1, generator=self._rng[s]) for s in slots])
 
     def allocate(self) -> int:
         return self.rt.allocate()
 
     def free(self, slot: int) -> None:
         self.rt.free(slot)
+        self._rng.pop(slot, None)
+        self._counts.pop(slot, None)
 
     def prefill_tokens(self, slot: int, prompt: list[int], chunk: int, sp: Any) -> int:
         ids = torch.tensor(prompt, dtype=torch.int32).pin_memory().to(self.rt.device, non_blocking=True)
-        return int(self.rt.prefill(slot, ids, chunk).item())
+        ds = self._sampling(slot, sp, prompt)
+        before = self.rt.prefill_tokens_computed
+        if ds is None:
+            tok = int(self.rt.prefill(slot, ids, chunk, host_tokens=prompt).item())
+        else:
+            counts = self._counts[slot][None] if slot in self._counts else None
+            tok = int(self.rt.prefill(slot, ids, chunk, host_tokens=prompt, sampling=ds, u=self._draws([slot]),
+                                      counts=counts).item())
+            if slot in self._counts:
+                self._count(self._counts[slot], [tok])
+        self.last_cached_tokens = len(prompt) - (self.rt.prefill_tokens_computed - before)
+        return tok
 
     def decode_tokens(self, slots: list[int], toks: list[int], sp: Any) -> list[int]:
+        """``sp``: one SamplingParams for the whole batch, a list with one per slot, or None (greedy)."""
         t = torch.tensor(toks, dtype=torch.int32, device=self.rt.device)
-        return [int(x) for x in self.rt.decode(slots, t).tolist()]
+        sps = sp if isinstance(sp, (list, tuple)) else [sp] * len(slots)
+        dss = [self._sampling(s, p, None) for s, p in zip(slots, sps)]
+        if all(d is None for d in dss):
+            return [int(x) for x in self.rt.decode(slots, t).tolist()]
+        if all(d == dss[0] for d in dss):
+            counts = torch.stack([self._counts[s] for s in slots]) if all(s in self._counts for s in slots) and dss[0].has_penalties else None
+            out = [int(x) for x in self.rt.decode(slots, t, sampling=dss[0], u=self._draws(slots), counts=counts).tolist()]
+        else:
+            # mixed settings in one batch: one forward pass, then one draw per row from the step's logits
+            greedy = self.rt.decode(slots, t).tolist()
+            logits = next(e for e in self.rt._graphs.values() if e["buf"]["ids"].numel() == len(slots))["buf"]["logits"]
+            out = []
+            for r, (s, d) in enumerate(zip(slots, dss)):
+                if d is None:
+                    out.append(int(greedy[r]))
+                else:
+                    c = self._counts[s][None] if s in self._counts else None
+                    out.append(int(self.rt._next_tokens(logits[r:r + 1], d, self._draws([s]), c).item()))
+        for s, tok in zip(slots, out):
+            if s in self._counts:
+                self._count(self._counts[s], [tok])
+        return out
 
     def generate_batch(self, prompts, max_new, eos_ids, max_batch):
         """Greedy continuous batching: admit up to ``max_batch`` sequences, decode them together."""

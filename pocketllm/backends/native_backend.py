@@ -19,7 +19,7 @@ from ..protocol.chat import held_back_suffix, truncate_at_stop
 from ..protocol.prompt import TokenizerHandle
 from .base import BackendBase
 
-OP_STOP, OP_ALLOC, OP_FREE, OP_PREFILL, OP_DECODE = 0, 1, 2, 3, 4
+OP_STOP, OP_ALLOC, OP_FREE, OP_PREFILL, OP_DECODE, OP_SAMPLING = 0, 1, 2, 3, 4, 5
 
 
 class NullChannel:
@@ -31,6 +31,29 @@ class NullChannel:
 
     def recv(self):  # pragma: no cover - never called at world 1
         raise BackendUnavailableError("no command channel")
+
+
+_Q = 1_000_000          # sampling settings travel as int32 words: fixed point, 6 decimals
+
+
+def _with_seed(sp):
+    import dataclasses
+    import random
+    seed = random.getrandbits(31) if sp.seed is None else int(sp.seed) & 0x7FFFFFFF    # what fits one channel word
+    return dataclasses.replace(sp, seed=seed)
+
+
+def _encode_sampling(sp) -> list[int]:
+    q = lambda x: int(round(float(x or 0.0) * _Q))
+    return [q(sp.temperature), int(sp.top_k or 0), q(sp.top_p if sp.top_p is not None else 1.0), q(sp.min_p),
+            q(sp.repetition_penalty), q(sp.presence_penalty), q(sp.frequency_penalty), int(sp.seed) & 0x7FFFFFFF]
+
+
+def _decode_sampling(w) -> Any:
+    from types import SimpleNamespace
+    return SimpleNamespace(temperature=w[0] / _Q, top_k=int(w[1]), top_p=w[2] / _Q, min_p=w[3] / _Q,
+                           repetition_penalty=w[4] / _Q, presence_penalty=w[5] / _Q, frequency_penalty=w[6] / _Q,
+                           seed=int(w[7]))
 
 
 class NativeBackend(BackendBase):
@@ -130,6 +153,11 @@ class NativeBackend(BackendBase):
             ch.send(OP_ALLOC)
             slot = rt.allocate()
             try:
+                if not sp.greedy:
+                    # worker ranks take part in the sampled draw (candidate gather over the vocabulary shards) and
+                    # must use the same settings and the same random stream: the seed is fixed here
+                    sp = _with_seed(sp)
+                    ch.send(OP_SAMPLING, slot, *_encode_sampling(sp))
                 ch.send(OP_PREFILL, slot, chunk, prompt)
                 tok = rt.prefill_tokens(slot, prompt, chunk, sp)
                 t1 = time.perf_counter()
@@ -248,6 +276,7 @@ class NativeBackend(BackendBase):
         cpp_engine/engine/deepseek_v4_engine.cpp:11143-11239)."""
         self.prepare()
         rt, ch = self.runtime, self.channel
+        slot_sp: dict[int, Any] = {}
         while True:
             op, *payload = ch.recv()
             try:
@@ -256,13 +285,16 @@ class NativeBackend(BackendBase):
                 if op == OP_ALLOC:
                     rt.allocate()
                 elif op == OP_FREE:
+                    slot_sp.pop(payload[0], None)
                     rt.free(payload[0])
+                elif op == OP_SAMPLING:
+                    slot_sp[payload[0]] = _decode_sampling(payload[1:])
                 elif op == OP_PREFILL:
                     slot, chunk, prompt = payload
-                    rt.prefill_tokens(slot, prompt, chunk, None)
+                    rt.prefill_tokens(slot, prompt, chunk, slot_sp.get(slot))
                 elif op == OP_DECODE:
                     slot, tok = payload
-                    rt.decode_tokens([slot], [tok], None)
+                    rt.decode_tokens([slot], [tok], slot_sp.get(slot))
                 else:
                     raise BackendUnavailableError(f"unknown worker opcode {op}")
             except BackendUnavailableError:
