@@ -138,11 +138,38 @@ def tensor_specs(cfg: MlaMoeConfig) -> list[tuple[str, tuple[int, ...], str]]:
     return out
 
 
-def synth_state(cfg: MlaMoeConfig, seed: int = 0, device="cpu", std: float = 0.02) -> Iterator[tuple[str, torch.Tensor]]:
+def synth_state(cfg: MlaMoeConfig, seed: int = 0, device="cpu", std: float = 0.02,
+                expert_range: tuple[int, int] | None = None, expert_pool: int | None = None,
+                layer_range: tuple[int, int] | None = None) -> Iterator[tuple[str, torch.Tensor]]:
     """Seeded random-init checkpoint tensors in checkpoint dtypes (FP4 experts come as ``.weight`` packed uint8
-    plus ``.scale`` E8M0 uint8)."""
+    plus ``.scale`` E8M0 uint8).  For full-size benchmarks a rank can restrict generation to the experts and layers
+    it holds, and draw only ``expert_pool`` distinct experts per layer (expert e re-uses the tensors of e % pool)."""
     gen = torch.Generator(device=device)
+    pool_cache: dict[str, list] = {}
     for idx, (name, shape, kind) in enumerate(tensor_specs(cfg)):
+        if layer_range is not None and name.startswith("layers."):
+            li = int(name.split(".")[1])
+            if not (layer_range[0] <= li < layer_range[1]):
+                continue
+        if kind == "expert" and ".experts." in name:
+            head, rest = name.split(".experts.")
+            e = int(rest.split(".")[0])
+            if expert_range is not None and not (expert_range[0] <= e < expert_range[1]):
+                continue
+            if expert_pool:
+                import zlib
+                key = head + ".experts." + str(e % expert_pool) + "." + rest.split(".", 1)[1]
+                if key not in pool_cache:
+                    gen.manual_seed(seed * 1_000_003 + zlib.crc32(key.encode()))
+                    w = torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std
+                    if cfg.expert_format == "fp4":
+                        q_, s_ = fp4fmt.quantize(w)
+                        pool_cache[key] = [("weight", q_), ("scale", s_)]
+                    else:
+                        pool_cache[key] = [("weight", w.bfloat16())]
+                for suffix, t in pool_cache[key]:
+                    yield name[:-len("weight")] + suffix, t
+                continue
         gen.manual_seed(seed * 1_000_003 + idx)
         if kind == "w":
             yield name, (torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std).bfloat16()
@@ -154,10 +181,11 @@ def synth_state(cfg: MlaMoeConfig, seed: int = 0, device="cpu", std: float = 0.0
             w = torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std
             if cfg.expert_format == "fp4":
                 q, s = fp4fmt.quantize(w)
-                yield name, q
-                yield name[:-len("weight")] + "scale", s
+                out = [("weight", q), ("scale", s)]
             else:
-                yield name, w.bfloat16()
+                out = [("weight", w.bfloat16())]
+            for suffix, t in out:
+                yield name[:-len("weight")] + suffix, t
         else:
             raise ValueError(kind)
 
