@@ -368,9 +368,22 @@ int b200_topk_rows(const float* vals, int ld, const int* n_valid, int rows, int 
 }
 
 // q_lat [H, T, C], q_pe [T, H, R], cache [rows, C + R]; o_lat [H, T, C].  (C, R) in {(512, 64), (64, 16)}.
+int b200_mla_attention_mma(const void* q_lat, const void* q_pe, const void* cache, const int* block_table, int max_blocks,
+                           int bs, const int* positions, const int* seq_of_token, const int* sel, int nsel, void* o_lat, int T,
+                           int H, int C, int R, float scale, cudaStream_t stream);
+
+// Tensor-core kernel (attn_mla_mma.cu): the heads of a token share one gather of its selected cache rows.
 int b200_mla_attention(const void* q_lat, const void* q_pe, const void* cache, const int* block_table, int max_blocks, int bs,
                        const int* positions, const int* seq_of_token, const int* sel, int nsel, void* o_lat, int T, int H, int C,
                        int R, float scale, cudaStream_t stream) {
+  return b200_mla_attention_mma(q_lat, q_pe, cache, block_table, max_blocks, bs, positions, seq_of_token, sel, nsel, o_lat, T, H,
+                                C, R, scale, stream);
+}
+
+// Scalar fp32 kernel, one CTA per (token, head): kept as an independent implementation for cross-checks.
+int b200_mla_attention_simt(const void* q_lat, const void* q_pe, const void* cache, const int* block_table, int max_blocks, int bs,
+                            const int* positions, const int* seq_of_token, const int* sel, int nsel, void* o_lat, int T, int H,
+                            int C, int R, float scale, cudaStream_t stream) {
   if (T <= 0 || H <= 0) return -6;
   auto ql = reinterpret_cast<const __nv_bfloat16*>(q_lat);
   auto qp = reinterpret_cast<const __nv_bfloat16*>(q_pe);

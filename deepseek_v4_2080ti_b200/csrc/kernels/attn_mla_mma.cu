@@ -1,0 +1,228 @@
+// Absorbed multi-head latent attention on the tensor cores.
+//
+// All heads of a token attend to the same latent rows (one shared KV "head" of C latent + R rope dims), so for one
+// query token the scores of up to 16 heads over a tile of keys are a [16 x (C+R)] x [(C+R) x keys] product and the
+// output a [16 x keys] x [keys x C] product: the heads are the M dimension of m16n8k16 MMAs.  One CTA handles one
+// token and one group of 16 heads: it gathers the token's selected cache rows (top-k indices of the sparse indexer, or
+// the causal prefix) tile by tile with cp.async - once for all heads of the group, double-buffered - and keeps the
+// running soft-max state and the [16 x C] output in registers.
+//   warp w: scores of keys [8w, 8w+8) of each 32-key tile; output dims [w C/4, (w+1) C/4).
+// The rows of a tile serve as the B operand twice: K-major for the scores, and through ldmatrix.trans as V.
+//
+// Reference behaviour: GLM MLA with absorbed k_b / v_b (src/models/glm_dsa/architecture.py:263-406) and the
+// DeepSeek sparse attention dispatcher (src/kernels/ops.py:982-1100), which run per-head SDPA / Triton kernels.
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include "ops.h"
+
+namespace {
+
+constexpr int KT = 32;        // keys per tile
+constexpr int HG = 16;        // heads per CTA (MMA M)
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp16(void* dst, const void* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ size_t cache_row_of(const int* bt, int bs, int pos) { return (size_t)bt[pos / bs] * bs + pos % bs; }
+
+template <int C, int R>
+struct Layout {
+  static constexpr int D = C + R;
+  static constexpr int LD = D + 8;                           // padded row (elements): 16-byte aligned, bank-skewed
+  static constexpr int Q_BYTES = HG * LD * 2;
+  static constexpr int K_BYTES = KT * LD * 2;
+  static constexpr int S_BYTES = HG * (KT + 1) * 4;
+  static constexpr int TOTAL = Q_BYTES + 2 * K_BYTES + S_BYTES + 2 * KT * 4;
+};
+
+// grid (T, ceil(H / 16)), 128 threads.
+template <int C, int R>
+__global__ void __launch_bounds__(128)
+mla_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_bfloat16* __restrict__ q_pe,
+                         const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_table, int max_blocks, int bs,
+                         const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ sel,
+                         int nsel, __nv_bfloat16* __restrict__ o_lat, int T, int H, float scale) {
+  using L = Layout<C, R>;
+  constexpr int D = L::D, LD = L::LD;
+  constexpr int NT = C / 4 / 8;                               // output n-tiles per warp
+  extern __shared__ __align__(16) uint8_t smem[];
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem);
+  __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem + L::Q_BYTES);
+  float* sS = reinterpret_cast<float*>(smem + L::Q_BYTES + 2 * L::K_BYTES);   // [16][KT + 1]
+  int* sPos = reinterpret_cast<int*>(sS + HG * (KT + 1));                      // [2][KT] key position, -1 = masked
+  const int t = blockIdx.x, h0 = blockIdx.y * HG;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
+  const int pos = positions[t];
+  const int* bt = block_table + (size_t)(seq_of_token ? seq_of_token[t] : 0) * max_blocks;
+  const int nkeys = sel ? nsel : pos + 1;
+  const int ntiles = (nkeys + KT - 1) / KT;
+
+  auto fetch = [&](int tile) {
+    __nv_bfloat16* dst = sK + (size_t)(tile & 1) * KT * LD;
+    int* dpos = sPos + (tile & 1) * KT;
+    const int k0 = tile * KT;
+    for (int i = tid; i < KT * (D / 8); i += 128) {
+      const int j = i / (D / 8), c = i % (D / 8);
+      int kp = -1;
+      if (k0 + j < nkeys) kp = sel ? sel[(size_t)t * nsel + k0 + j] : k0 + j;
+      if (kp > pos) kp = -1;
+      if (c == 0) dpos[j] = kp;
+      if (kp >= 0) cp16(dst + j * LD + c * 8, cache + cache_row_of(bt, bs, kp) * D + c * 8);
+      else *reinterpret_cast<uint4*>(dst + j * LD + c * 8) = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  // queries of this head group: rows = heads (rows past H stay zero)
+  for (int i = tid; i < HG * (D / 8); i += 128) {
+    const int r = i / (D / 8), c = i % (D / 8);
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (h0 + r < H) {
+      if (c * 8 < C) u = *reinterpret_cast<const uint4*>(q_lat + ((size_t)(h0 + r) * T + t) * C + c * 8);
+      else u = *reinterpret_cast<const uint4*>(q_pe + ((size_t)t * H + h0 + r) * R + (c * 8 - C));
+    }
+    *reinterpret_cast<uint4*>(sQ + r * LD + c * 8) = u;
+  }
+  if (ntiles > 0) fetch(0);
+
+  float o[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // rows g and g + 8
+
+  for (int tile = 0; tile < ntiles; ++tile) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                                   // tile landed; previous tile's readers are done
+    if (tile + 1 < ntiles) fetch(tile + 1);
+    const __nv_bfloat16* kt = sK + (size_t)(tile & 1) * KT * LD;
+    const int* kpos = sPos + (tile & 1) * KT;
+    // ---- scores of keys [8 warp, 8 warp + 8): S[16 x 8] = Q[16 x D] K^T
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t a[4];
+      const __nv_bfloat16* ap = sQ + g * LD + ks * 16 + 2 * tig;
+      a[0] = *reinterpret_cast<const uint32_t*>(ap);
+      a[1] = *reinterpret_cast<const uint32_t*>(ap + 8 * LD);
+      a[2] = *reinterpret_cast<const uint32_t*>(ap + 8);
+      a[3] = *reinterpret_cast<const uint32_t*>(ap + 8 * LD + 8);
+      const __nv_bfloat16* bp = kt + (8 * warp + g) * LD + ks * 16 + 2 * tig;
+      mma_bf16(s, a, *reinterpret_cast<const uint32_t*>(bp), *reinterpret_cast<const uint32_t*>(bp + 8));
+    }
+    {
+      const int kc = 8 * warp + 2 * tig;
+      const bool v0 = kpos[kc] >= 0, v1 = kpos[kc + 1] >= 0;
+      sS[g * (KT + 1) + kc] = v0 ? s[0] * scale : -INFINITY;
+      sS[g * (KT + 1) + kc + 1] = v1 ? s[1] * scale : -INFINITY;
+      sS[(g + 8) * (KT + 1) + kc] = v0 ? s[2] * scale : -INFINITY;
+      sS[(g + 8) * (KT + 1) + kc + 1] = v1 ? s[3] * scale : -INFINITY;
+    }
+    __syncthreads();
+    // ---- running soft-max of rows g and g + 8 (every lane keeps its rows' statistics)
+    float corr[2];
+    uint32_t pa[2][4];                                 // P as the A operand of two k-steps (16 keys each)
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const float* row = sS + (g + 8 * hf) * (KT + 1);
+      float mx = m_run[hf];
+#pragma unroll
+      for (int j = 0; j < KT; ++j) mx = fmaxf(mx, row[j]);
+      corr[hf] = (m_run[hf] == -INFINITY) ? 0.f : __expf(m_run[hf] - mx);
+      float sum = 0.f;
+      if (mx != -INFINITY) {
+#pragma unroll
+        for (int j = 0; j < KT; ++j) sum += __expf(row[j] - mx);
+      }
+      l_run[hf] = l_run[hf] * corr[hf] + sum;
+      m_run[hf] = mx;
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+        const int c0 = 16 * ks + 2 * tig;
+        const float e0 = mx == -INFINITY ? 0.f : __expf(row[c0] - mx), e1 = mx == -INFINITY ? 0.f : __expf(row[c0 + 1] - mx);
+        const float e2 = mx == -INFINITY ? 0.f : __expf(row[c0 + 8] - mx), e3 = mx == -INFINITY ? 0.f : __expf(row[c0 + 9] - mx);
+        pa[ks][hf] = pack_bf16(e0, e1);                // a0 (row g) / a1 (row g + 8)
+        pa[ks][2 + hf] = pack_bf16(e2, e3);            // a2 / a3: keys + 8
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      o[n][0] *= corr[0]; o[n][1] *= corr[0];
+      o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    }
+    // ---- O[16 x C/4] += P[16 x 32] V[32 x C/4]; V = the latent part of the same rows, read transposed
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+#pragma unroll
+      for (int n = 0; n < NT; n += 2) {
+        // x4: (keys 0-7, dims n), (keys 8-15, dims n), (keys 0-7, dims n+1), (keys 8-15, dims n+1)
+        const int key = 16 * ks + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int dim = warp * (C / 4) + (n + (lane >> 4)) * 8;
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, kt + key * LD + dim);
+        mma_bf16(o[n], pa[ks], b[0], b[1]);
+        mma_bf16(o[n + 1], pa[ks], b[2], b[3]);
+      }
+    }
+  }
+  // ---- normalise and store: rows = heads g, g + 8
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    const int h = h0 + g + 8 * hf;
+    if (h >= H) continue;
+    const float inv = l_run[hf] > 0.f ? 1.f / l_run[hf] : 0.f;
+    __nv_bfloat16* dst = o_lat + ((size_t)h * T + t) * C + warp * (C / 4) + 2 * tig;
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+      *reinterpret_cast<uint32_t*>(dst + 8 * n) = pack_bf16(o[n][2 * hf] * inv, o[n][2 * hf + 1] * inv);
+  }
+}
+
+template <int C, int R>
+int launch(const __nv_bfloat16* ql, const __nv_bfloat16* qp, const __nv_bfloat16* kc, const int* block_table, int max_blocks,
+           int bs, const int* positions, const int* seq_of_token, const int* sel, int nsel, __nv_bfloat16* ol, int T, int H,
+           float scale, cudaStream_t stream) {
+  using L = Layout<C, R>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(mla_attention_mma_kernel<C, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  mla_attention_mma_kernel<C, R><<<dim3(T, (H + HG - 1) / HG), 128, L::TOTAL, stream>>>(
+      ql, qp, kc, block_table, max_blocks, bs, positions, seq_of_token, sel, nsel, ol, T, H, scale);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// Same contract as b200_mla_attention (attn_mla.cu): q_lat [H, T, C], q_pe [T, H, R], cache [rows, C + R] bf16,
+// o_lat [H, T, C]; sel int32 [T, nsel] cache positions (-1 = unused) or null for the causal prefix.
+extern "C" int b200_mla_attention_mma(const void* q_lat, const void* q_pe, const void* cache, const int* block_table,
+                                      int max_blocks, int bs, const int* positions, const int* seq_of_token, const int* sel,
+                                      int nsel, void* o_lat, int T, int H, int C, int R, float scale, cudaStream_t stream) {
+  if (T <= 0 || H <= 0) return -6;
+  auto ql = reinterpret_cast<const __nv_bfloat16*>(q_lat);
+  auto qp = reinterpret_cast<const __nv_bfloat16*>(q_pe);
+  auto kc = reinterpret_cast<const __nv_bfloat16*>(cache);
+  auto ol = reinterpret_cast<__nv_bfloat16*>(o_lat);
+  if (C == 512 && R == 64)
+    return launch<512, 64>(ql, qp, kc, block_table, max_blocks, bs, positions, seq_of_token, sel, nsel, ol, T, H, scale, stream);
+  if (C == 128 && R == 32)
+    return launch<128, 32>(ql, qp, kc, block_table, max_blocks, bs, positions, seq_of_token, sel, nsel, ol, T, H, scale, stream);
+  return -6;
+}

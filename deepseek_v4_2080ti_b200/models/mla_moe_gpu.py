@@ -275,10 +275,23 @@ class MlaMoeGpuRuntime:
         sel = None
         if lw.idx_wq is not None and end > cfg.index_topk:
             qi = _mm(qin, lw.idx_wq).view(t, cfg.index_heads, cfg.index_dim)
-            hw = _mm(x, lw.idx_wproj, out_f32=True) * cfg.index_heads ** -0.5
-            scores = mla.indexer_scores(qi, hw.contiguous(), self.idx_cache[i], self.block_table, self.bs, pos, end,
-                                        cfg.index_dim ** -0.5)
-            sel = mla.topk_rows(scores, (pos + 1).to(torch.int32), cfg.index_topk)
+            hw = (_mm(x, lw.idx_wproj, out_f32=True) * cfg.index_heads ** -0.5).contiguous()
+            world = getattr(self.comm, "world", 1)
+            if world > 1 and t >= 8 * world and hasattr(self.comm, "all_gather"):
+                # the indexer weights are replicated, so its work is split by query rows: every rank scores and
+                # selects for a slice of the chunk and the selections (int32 [T, top-k]) are gathered
+                per = (t + world - 1) // world
+                lo = min(t, self.comm.rank * per)
+                hi = min(t, lo + per)
+                part = torch.full((per, cfg.index_topk), -1, dtype=torch.int32, device=self.device)
+                if hi > lo:
+                    sc = mla.indexer_scores(qi[lo:hi].contiguous(), hw[lo:hi].contiguous(), self.idx_cache[i], self.block_table,
+                                            self.bs, pos[lo:hi].contiguous(), end, cfg.index_dim ** -0.5)
+                    part[:hi - lo] = mla.topk_rows(sc, (pos[lo:hi] + 1).to(torch.int32), cfg.index_topk)
+                sel = self.comm.all_gather(part).reshape(world * per, cfg.index_topk)[:t].contiguous()
+            else:
+                scores = mla.indexer_scores(qi, hw, self.idx_cache[i], self.block_table, self.bs, pos, end, cfg.index_dim ** -0.5)
+                sel = mla.topk_rows(scores, (pos + 1).to(torch.int32), cfg.index_topk)
         o_lat = mla.attention(q_lat, q_pe, self.cache[i], self.block_table, self.bs, pos, cfg.kv_lora_rank, cfg.qk_rope_dim,
                               cfg.qk_head_dim ** -0.5, sel)
         o = mla.transpose_heads(mla.per_head_linear(o_lat, lw.w_uv)).view(t, hl * cfg.v_head_dim)

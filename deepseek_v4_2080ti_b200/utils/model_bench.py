@@ -156,22 +156,28 @@ def _mla(args, rank, world, dev, glm: bool):
     return pre_ms, dec_ms, nbytes, build_s, desc
 
 
-def _tensors(obj, seen=None):
+def _tensors(obj, seen=None, depth=0):
     """Every tensor reachable from a weights object (for the resident-bytes figure)."""
     seen = set() if seen is None else seen
+    if depth > 6 or id(obj) in seen:
+        return
     if isinstance(obj, torch.Tensor):
         if obj.data_ptr() not in seen:
             seen.add(obj.data_ptr())
             yield obj
-    elif isinstance(obj, (list, tuple)):
+        return
+    if isinstance(obj, (str, bytes, int, float, bool, type(None), torch.device, torch.dtype)):
+        return
+    seen.add(id(obj))
+    if isinstance(obj, (list, tuple)):
         for x in obj:
-            yield from _tensors(x, seen)
+            yield from _tensors(x, seen, depth + 1)
     elif isinstance(obj, dict):
         for x in obj.values():
-            yield from _tensors(x, seen)
+            yield from _tensors(x, seen, depth + 1)
     elif hasattr(obj, "__dict__"):
         for x in vars(obj).values():
-            yield from _tensors(x, seen)
+            yield from _tensors(x, seen, depth + 1)
 
 
 def main() -> None:

@@ -175,3 +175,50 @@ def test_mtp_speculative_stream_equals_greedy():
     _lib.check_status()
     assert forced == want, (forced, want)
     assert rt.spec_stats["accepted"] == rt.spec_stats["steps"] and rt.spec_stats["steps"] <= (n + 1) // 2
+
+
+@pytest.mark.parametrize("h,c,r", [(20, 512, 64), (8, 512, 64), (64, 512, 64), (5, 128, 32)])
+def test_tensor_core_attention_matches_torch_and_scalar_kernel(h, c, r):
+    """Full-size latent geometry, head counts that fill one, part of one and several 16-head groups; dense causal and
+    sparse selections with padding; against fp32 PyTorch and against the scalar kernel."""
+    import ctypes
+    from deepseek_v4_2080ti_b200.ops import _lib, mla
+    torch.manual_seed(h)
+    t, s_ctx, bs, k = 7, 300, 64, 70
+    nblk = (s_ctx + bs - 1) // bs
+    perm = torch.randperm(nblk)
+    bt = perm.to(torch.int32).cuda().view(1, nblk).contiguous()
+    cache = torch.zeros(nblk * bs, c + r, device="cuda", dtype=torch.bfloat16)
+    keys = (torch.randn(s_ctx, c + r, device="cuda") * 0.3).bfloat16()
+    phys = (perm[torch.arange(s_ctx) // bs] * bs + torch.arange(s_ctx) % bs).cuda()
+    cache[phys] = keys
+    pos = torch.tensor([299, 150, 0, 64, 31, 33, 200], dtype=torch.int32, device="cuda")
+    q_lat = (torch.randn(h, t, c, device="cuda") * 0.3).bfloat16()
+    q_pe = (torch.randn(t, h, r, device="cuda") * 0.3).bfloat16()
+    scale = (c + r) ** -0.5
+    sel = torch.full((t, k), -1, dtype=torch.int32, device="cuda")
+    for ti in range(t):
+        n = min(k - 3, int(pos[ti]) + 1)                       # some padding in every row
+        sel[ti, :n] = torch.randperm(int(pos[ti]) + 1)[:n].to(torch.int32).cuda()
+    mask = torch.arange(s_ctx, device="cuda")[None, :] <= pos[:, None]
+    q = torch.cat([q_lat.float().permute(1, 0, 2), q_pe.float()], -1)
+    for use_sel in (False, True):
+        o = mla.attention(q_lat, q_pe, cache, bt, bs, pos, c, r, scale, sel if use_sel else None)
+        o2 = torch.empty_like(o)
+        rc = _lib.lib().b200_mla_attention_simt(_lib.ptr(q_lat), _lib.ptr(q_pe), _lib.ptr(cache), _lib.ptr(bt), nblk, bs,
+                                                _lib.ptr(pos), None, _lib.ptr(sel) if use_sel else None, k if use_sel else 0,
+                                                _lib.ptr(o2), t, h, c, r, ctypes.c_float(scale), _lib.stream())
+        assert rc == 0
+        torch.cuda.synchronize()
+        _lib.check_status()
+        m = mask.clone()
+        if use_sel:
+            keep = torch.zeros(t, s_ctx, dtype=torch.bool, device="cuda")
+            for ti in range(t):
+                keep[ti, [i for i in sel[ti].tolist() if i >= 0]] = True
+            m &= keep
+        sc = (torch.einsum("thd,sd->ths", q, keys.float()) * scale).masked_fill(~m[:, None, :], float("-inf"))
+        want = torch.einsum("ths,sc->thc", sc.softmax(-1), keys.float()[:, :c]).permute(1, 0, 2)
+        tol = 2e-2 * want.abs().max().clamp_min(1e-3)
+        assert (o.float() - want).abs().max() < tol, (use_sel, "tensor-core")
+        assert (o2.float() - want).abs().max() < tol, (use_sel, "scalar")
