@@ -1,0 +1,75 @@
+"""Re-encode the matrices of a safetensors checkpoint into another weight format, shard by shard:
+
+    bf16 | fp8 (E4M3, 128x128 block scales, ``weight_scale_inv``) | fp4 (E2M1 + E8M0 per 32, ``scale``)
+
+The reference's converter turns FP4 / FP8 checkpoints into INT8 W8A8 because its GPUs have no FP8 or FP4 tensor path
+(src/cli/convert_checkpoint.py, src/models/deepseek_v4/loader.py:36-45); on B200 those formats run natively, so the
+useful directions are bf16 -> fp8 / fp4 and back."""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+
+
+def convert_tensor(name: str, w: torch.Tensor, scale: torch.Tensor | None, src: str, dst: str) -> dict[str, torch.Tensor]:
+    from ..formats import fp4 as fp4fmt
+    from ..formats import fp8 as fp8fmt
+    base = name[:-len(".weight")]
+    if src == "fp8":
+        w = fp8fmt.dequantize_block128(w, scale.float())
+    elif src == "fp4":
+        w = fp4fmt.dequantize(w, scale)
+    w = w.float()
+    if dst == "bf16":
+        return {name: w.bfloat16()}
+    if dst == "fp8":
+        q, s = fp8fmt.quantize_block128(w)
+        return {name: q, base + ".weight_scale_inv": s.bfloat16()}
+    if dst == "fp4":
+        q, s = fp4fmt.quantize(w)
+        return {name: q, base + ".scale": s}
+    raise ValueError(dst)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="convert_checkpoint")
+    ap.add_argument("src_dir")
+    ap.add_argument("dst_dir")
+    ap.add_argument("--to", choices=["bf16", "fp8", "fp4"], required=True)
+    ap.add_argument("--match", default="", help="only matrices whose name contains this (others are copied)")
+    ap.add_argument("--min-dim", type=int, default=128, help="leave smaller matrices alone")
+    a = ap.parse_args(argv)
+    from ..formats import safetensors_io as sio
+    state = dict(sio.read_checkpoint(a.src_dir))
+    out: dict[str, torch.Tensor] = {}
+    converted = 0
+    for name, w in state.items():
+        if name.endswith(".weight_scale_inv") or name.endswith(".scale"):
+            continue
+        base = name[:-len(".weight")] if name.endswith(".weight") else None
+        sc_fp8 = state.get(base + ".weight_scale_inv") if base else None
+        sc_fp4 = state.get(base + ".scale") if base else None
+        src = "fp8" if sc_fp8 is not None else "fp4" if sc_fp4 is not None else "bf16"
+        ok = base is not None and w.dim() == 2 and a.match in name and \
+            (src != "bf16" or (min(w.shape) >= a.min_dim and w.shape[1] % 128 == 0 and w.dtype in (torch.bfloat16, torch.float16, torch.float32)))
+        if not ok or src == a.to:
+            out[name] = w
+            if sc_fp8 is not None:
+                out[base + ".weight_scale_inv"] = sc_fp8
+            if sc_fp4 is not None:
+                out[base + ".scale"] = sc_fp4
+            continue
+        out.update(convert_tensor(name, w, sc_fp8 if sc_fp8 is not None else sc_fp4, src, a.to))
+        converted += 1
+    import os
+    cfg = os.path.join(a.src_dir, "config.json")
+    sio.write_checkpoint(a.dst_dir, iter(out.items()), config_json=open(cfg).read() if os.path.exists(cfg) else None)
+    print(json.dumps({"tensors": len(out), "converted": converted, "to": a.to}))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

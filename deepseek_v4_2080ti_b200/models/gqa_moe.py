@@ -75,9 +75,10 @@ class GqaMoeConfig:
                            norm_eps=float(g("attention.layer_norm_rms_epsilon", 1e-6)),
                            context_length=int(g("context_length", 8192)))
         if tensors:
-            ty = lambda n: tensors[n].ggml_type.name
-            cfg.attn_type, cfg.dense_type = ty("blk.0.attn_q.weight"), ty("output.weight")
-            cfg.gate_up_type, cfg.down_type = ty("blk.0.ffn_gate_exps.weight"), ty("blk.0.ffn_down_exps.weight")
+            ty = lambda n, d: tensors[n].ggml_type.name if n in tensors else d
+            cfg.attn_type, cfg.dense_type = ty("blk.0.attn_q.weight", cfg.attn_type), ty("output.weight", cfg.dense_type)
+            cfg.gate_up_type = ty("blk.0.ffn_gate_exps.weight", cfg.gate_up_type)
+            cfg.down_type = ty("blk.0.ffn_down_exps.weight", cfg.down_type)
         return cfg
 
 

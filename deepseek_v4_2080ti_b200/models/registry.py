@@ -1,0 +1,151 @@
+"""Model-family registry for GGUF checkpoints: detect the family from ``general.architecture``, parse its
+hyper-parameters, check the tensor inventory against the family's naming, report which tensor types the runtime can
+execute, and plan placement on a B200 box (everything resident; experts sharded by range).
+
+Reference behaviour: the MoE spec registry (src/components/moe/spec.py:80-98, registry.py:10-47), the capability table
+(capability.py:7-63) and the placement decisions (placement.py:9-56)."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+from ..formats.gguf import BLOCK_BYTES, BLOCK_ELEMS, GGMLType
+
+# GGUF types the tensor-core GEMM decodes in registers, and plain types every loader reads
+GEMM_DECODED = {GGMLType.Q8_0, GGMLType.Q4_K, GGMLType.Q5_K, GGMLType.Q2_K, GGMLType.IQ1_M, GGMLType.IQ2_XXS, GGMLType.IQ3_XXS}
+PLAIN = {GGMLType.F32, GGMLType.F16, GGMLType.BF16}
+
+
+@dataclass(frozen=True)
+class HardwareProfile:
+    gpu_count: int = 8
+    gpu_memory_gib: float = 180.0
+    name: str = "8xB200"
+
+    @property
+    def per_gpu_bytes(self) -> int:
+        return int(self.gpu_memory_gib * (1 << 30))
+
+
+@dataclass
+class PlacementDecision:
+    name: str
+    status: str                 # candidate | rejected
+    reason: str
+    bytes_per_gpu: int
+
+
+@dataclass
+class ValidationReport:
+    architecture: str
+    ok: bool
+    missing: list[str] = field(default_factory=list)
+    unexpected: list[str] = field(default_factory=list)
+    by_type: dict[str, int] = field(default_factory=dict)        # type name -> bytes
+    unsupported: dict[str, str] = field(default_factory=dict)    # tensor -> reason
+    total_bytes: int = 0
+    routed_bytes: int = 0
+
+
+@dataclass
+class ModelSpec:
+    architecture: str
+    display_name: str
+    parse_params: Callable[[dict[str, Any], dict | None], Any]
+    global_tensors: tuple[str, ...]
+    layer_tensors: Callable[[Any, int], tuple[str, ...]]         # (params, layer) -> suffixes after ``blk.N.``
+    n_layers: Callable[[Any], int]
+    routed_suffixes: tuple[str, ...]
+    build_runtime: Callable[..., Any] | None = None
+
+    def expected_names(self, params) -> list[str]:
+        out = list(self.global_tensors)
+        for i in range(self.n_layers(params)):
+            out += [f"blk.{i}.{s}" for s in self.layer_tensors(params, i)]
+        return out
+
+    def validate(self, bundle) -> ValidationReport:
+        params = self.parse_params(bundle.metadata, bundle.tensors)
+        want = set(self.expected_names(params))
+        have = set(bundle.tensors)
+        rep = ValidationReport(self.architecture, True, sorted(want - have), sorted(have - want))
+        for name, ti in bundle.tensors.items():
+            rep.by_type[ti.ggml_type.name] = rep.by_type.get(ti.ggml_type.name, 0) + ti.nbytes
+            rep.total_bytes += ti.nbytes
+            if any(name.endswith(s) for s in self.routed_suffixes):
+                rep.routed_bytes += ti.nbytes
+            status, why = capability_status(ti.ggml_type, two_d=len(ti.shape) >= 2)
+            if status != "supported":
+                rep.unsupported[name] = why
+        rep.ok = not rep.missing and not rep.unsupported
+        return rep
+
+    def placement(self, report: ValidationReport, hw: HardwareProfile = HardwareProfile(), reserve_fraction: float = 0.15
+                  ) -> list[PlacementDecision]:
+        """Experts sharded by range over the GPUs, everything else sharded or replicated (counted as replicated: the
+        upper bound).  The reference's host-staged expert placement is not needed when this fits."""
+        shared = report.total_bytes - report.routed_bytes
+        per_gpu = shared + (report.routed_bytes + hw.gpu_count - 1) // hw.gpu_count
+        usable = int(hw.per_gpu_bytes * (1.0 - reserve_fraction))
+        ok = per_gpu <= usable
+        out = [PlacementDecision("all_device_resident", "candidate" if ok else "rejected",
+                                 f"{per_gpu} bytes/GPU {'within' if ok else 'above'} the budget of {usable} bytes/GPU on {hw.name}",
+                                 per_gpu)]
+        if not ok:
+            stages = 2
+            out.append(PlacementDecision("layer_pipeline", "candidate",
+                                         f"{stages} pipeline stages halve the resident layers per GPU group", per_gpu // stages))
+        return out
+
+
+def capability_status(t: GGMLType, two_d: bool = True) -> tuple[str, str]:
+    t = GGMLType(t)
+    if t in PLAIN:
+        return "supported", "plain tensor"
+    if t in GEMM_DECODED:
+        return "supported", f"{t.name} blocks are decoded inside the tensor-core GEMM"
+    if t in BLOCK_BYTES:
+        return "deferred", f"{t.name} is readable (header and block size known) but has no GEMM decode path"
+    return "unsupported", f"unknown GGUF tensor type {int(t)}"
+
+
+# ---------------------------------------------------------------------------------------------- families
+def _minimax_params(md, tensors):
+    from .gqa_moe import GqaMoeConfig
+    return GqaMoeConfig.from_metadata(md, tensors)
+
+
+def _minimax_runtime(bundle, device="cuda", rank=0, world=1, comm=None, **kw):
+    from . import gqa_moe as gm
+    cfg = gm.GqaMoeConfig.from_metadata(bundle.metadata, bundle.tensors)
+    w = gm.GqaMoeGpuWeights(cfg, gm.TensorStore(bundle), device, rank, world)
+    return cfg, gm.GqaMoeRuntime(cfg, w, comm=comm, **kw)
+
+
+MINIMAX_LAYER = ("attn_norm.weight", "ffn_norm.weight", "attn_q.weight", "attn_k.weight", "attn_v.weight", "attn_output.weight",
+                 "attn_q_norm.weight", "attn_k_norm.weight", "ffn_gate_inp.weight", "exp_probs_b.bias", "ffn_gate_exps.weight",
+                 "ffn_up_exps.weight", "ffn_down_exps.weight")
+
+_REGISTRY: dict[str, ModelSpec] = {}
+
+
+def register(spec: ModelSpec) -> None:
+    _REGISTRY[spec.architecture] = spec
+
+
+def detect(bundle) -> ModelSpec:
+    arch = str(bundle.metadata.get("general.architecture", ""))
+    if arch not in _REGISTRY:
+        raise KeyError(f"no model family registered for GGUF architecture {arch!r} (known: {sorted(_REGISTRY)})")
+    return _REGISTRY[arch]
+
+
+def architectures() -> list[str]:
+    return sorted(_REGISTRY)
+
+
+register(ModelSpec(
+    architecture="minimax-m2", display_name="MiniMax-M2 (GQA + routed experts)", parse_params=_minimax_params,
+    global_tensors=("token_embd.weight", "output.weight", "output_norm.weight"),
+    layer_tensors=lambda p, i: MINIMAX_LAYER, n_layers=lambda p: p.n_layers,
+    routed_suffixes=("ffn_gate_exps.weight", "ffn_up_exps.weight", "ffn_down_exps.weight"), build_runtime=_minimax_runtime))
