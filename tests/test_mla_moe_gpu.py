@@ -55,7 +55,7 @@ def test_gpu_runtime_follows_host_runtime(indexer):
         # attended set of some queries; the kernels themselves are checked exactly in the tests below
         assert err < 0.3 and agree > 0.5, (err, agree)
     else:
-        assert err < 6e-2, err
+        assert err < 1e-1, err          # bf16 probabilities and activations against the fp32 host path
         assert agree > 0.85, agree
 
 
