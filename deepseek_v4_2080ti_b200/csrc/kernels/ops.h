@@ -76,6 +76,13 @@ int b200_sample_candidates(const float* vals, int ld, const int* idx, int K, int
 int b200_apply_penalties(float* logits, int ld, int n, int rows, const int* counts, float repetition, float presence,
                          float frequency, cudaStream_t stream);
 
+// ---- DeepSeek-V4 block structure (v4_ops.cu)
+int b200_hadamard128(const void* x, void* y, long long rows, cudaStream_t stream);
+int b200_hc_split_pre(const float* mixes, const void* x, const float* scale, const float* base, long long T, int D, int iters,
+                      float eps, void* y, float* post, float* comb, cudaStream_t stream);
+int b200_hc_post(const void* y, const void* residual, const float* post, const float* comb, long long T, int D, void* out,
+                 cudaStream_t stream);
+
 // ---- load-time weight preparation (prepack.cu)
 unsigned long long b200_prepack_fp8_bytes(int N, int K);
 int b200_prepack_fp8(const void* w_fp8, void* out, int N, int K, cudaStream_t stream);
