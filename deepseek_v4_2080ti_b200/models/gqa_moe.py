@@ -92,8 +92,11 @@ def synth_tensors(cfg: GqaMoeConfig, seed: int = 0, device="cpu", std: float = 0
     """(gguf name, raw bytes, ggml type, logical shape) of a seeded random checkpoint in the reference's naming.
     ``expert_pool``: quantise only that many distinct experts per layer and repeat them (full-size benchmarks: the
     IQ quantisers search a codebook per group, which dominates start-up for 256 experts x 62 layers)."""
-    gen = torch.Generator(device="cpu").manual_seed(seed)
-    rnd = lambda *s, sd=std: (torch.randn(*s, generator=gen) * sd).to(device)
+    # drawn on the target device (a 60-layer checkpoint is billions of values); every rank of a job uses the same
+    # device type and seed, so all ranks see the same tensors
+    gdev = torch.device(device)
+    gen = torch.Generator(device=gdev).manual_seed(seed)
+    rnd = lambda *s, sd=std: torch.randn(*s, generator=gen, device=gdev) * sd
     f32 = lambda w: (w.float().contiguous().view(torch.uint8), GGMLType.F32)
     h, d = cfg.hidden, cfg.head_dim
     qd, kvd = cfg.n_heads * d, cfg.n_kv_heads * d
