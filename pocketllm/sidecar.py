@@ -1,0 +1,74 @@
+"""JSON-lines helper process for native front ends that do not embed a chat-template engine: reads one request per
+line on stdin, answers one line on stdout.
+
+    {"op": "ping"}                                              -> {"ok": true}
+    {"op": "encode", "family": "deepseek_v4", "messages": [...], "tools": [...], "thinking": false,
+     "reasoning_effort": null}                                  -> {"ok": true, "prompt": "...", "token_ids": [...]?}
+    {"op": "parse", "family": "deepseek_v4", "text": "...", "thinking": false}
+                                                                -> {"ok": true, "message": {...}}
+    {"op": "shutdown"}                                          -> {"ok": true} and exit
+
+``token_ids`` are returned when a tokenizer was given (``--gguf`` with embedded BPE vocabulary).  Errors come back as
+``{"ok": false, "error": "..."}``; the process keeps serving.
+Reference behaviour: src/server/cpp_sidecar.py:59-137 (encode / parse / ping / shutdown over pipes)."""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+
+def handle(req: dict, tokenizer=None) -> dict:
+    op = req.get("op")
+    if op == "ping":
+        return {"ok": True}
+    if op == "shutdown":
+        return {"ok": True, "shutdown": True}
+    family = req.get("family", "deepseek_v4")
+    from deepseek_v4_2080ti_b200 import encoding
+    enc = {"deepseek_v4": encoding.deepseek_v4, "glm_dsa": encoding.glm_dsa, "minimax_m2": encoding.minimax_m2}.get(family)
+    if enc is None:
+        return {"ok": False, "error": f"unknown chat family {family!r}"}
+    if op == "encode":
+        kw = {}
+        if family == "deepseek_v4":
+            kw = {"tools": req.get("tools"), "thinking": bool(req.get("thinking", False)),
+                  "reasoning_effort": req.get("reasoning_effort")}
+        prompt = enc.render(req.get("messages", []), **kw)
+        out = {"ok": True, "prompt": prompt}
+        if tokenizer is not None:
+            out["token_ids"] = tokenizer.encode(prompt)
+        return out
+    if op == "parse":
+        if not hasattr(enc, "parse_completion"):
+            return {"ok": True, "message": {"role": "assistant", "content": req.get("text", "")}}
+        return {"ok": True, "message": enc.parse_completion(req.get("text", ""), thinking=bool(req.get("thinking", False)))}
+    return {"ok": False, "error": f"unknown op {op!r}"}
+
+
+def main(argv=None, stdin=None, stdout=None) -> int:
+    ap = argparse.ArgumentParser(prog="pocketllm-sidecar")
+    ap.add_argument("--gguf", default="", help="take the tokenizer from this GGUF file's metadata")
+    a = ap.parse_args(argv)
+    stdin, stdout = stdin or sys.stdin, stdout or sys.stdout
+    tok = None
+    if a.gguf:
+        from deepseek_v4_2080ti_b200.encoding.gguf_tokenizer import GGUFTokenizer
+        tok = GGUFTokenizer.from_gguf(a.gguf)
+    for line in stdin:
+        line = line.strip()
+        if not line:
+            continue
+        try:
+            resp = handle(json.loads(line), tok)
+        except Exception as exc:                       # a bad request must not end the helper
+            resp = {"ok": False, "error": f"{type(exc).__name__}: {exc}"}
+        stdout.write(json.dumps(resp, ensure_ascii=False) + "\n")
+        stdout.flush()
+        if resp.get("shutdown"):
+            break
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
