@@ -130,6 +130,20 @@ def build_core(jobs: int | None = None) -> dict[str, Path]:
                   "-lb200_kernels", f"-Wl,-rpath,$ORIGIN/../lib", "-L/usr/local/cuda/lib64",
                   "-lcudart", "-ldl", "-pthread"])
         products["engine"] = exe
+        ebind = CSRC / "bindings" / "engine_bindings.cpp"
+        if ebind.exists():
+            import pybind11
+
+            ext = sysconfig.get_config_var("EXT_SUFFIX")
+            emod = PKG / f"pocketllm_engine_cpp{ext}"
+            inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"]]
+            eobj = _compile_cpp(ebind, inc)
+            lib_objs = [o for o in eng_objs if not o.name.startswith("main.")]
+            if (not emod.exists()) or any(o.stat().st_mtime > emod.stat().st_mtime for o in [eobj, *lib_objs, *core_objs]) \
+                    or (kern.exists() and kern.stat().st_mtime > emod.stat().st_mtime):
+                _run([CXX, "-shared", "-o", str(emod), str(eobj), *map(str, lib_objs), *map(str, core_objs), "-L", str(LIB),
+                      "-lb200_kernels", "-Wl,-rpath,$ORIGIN/lib", "-L/usr/local/cuda/lib64", "-lcudart", "-ldl", "-pthread"])
+            products["engine_pybind"] = emod
     return products
 
 

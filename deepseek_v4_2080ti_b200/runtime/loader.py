@@ -177,6 +177,61 @@ class RuntimeAdapter:
                 "slots_free": len(self.rt.free_slots)}
 
 
+class CppRuntimeAdapter:
+    """The same surface over the native C++ engine (``pocketllm_engine_cpp.QwenEngine``): safetensors checkpoints,
+    one GPU, greedy decoding; batches go through the C++ continuous-batching scheduler."""
+    supports_sampling = False
+    supports_prefix_cache = False
+    speculative_methods: tuple[str, ...] = ()
+
+    def __init__(self, checkpoint_dir: str, device_index: int, max_context: int, max_slots: int, chunk: int = 8192,
+                 eos_token_ids=()):
+        from .. import pocketllm_engine_cpp as cpp
+        opt = cpp.QwenEngineOptions()
+        opt.max_slots, opt.max_context, opt.prefill_chunk, opt.device = max_slots, max_context, chunk, device_index
+        opt.eos_tokens = list(eos_token_ids)
+        self.eng = cpp.QwenEngine(checkpoint_dir, opt)
+        self.max_context, self.eos_token_ids = max_context, tuple(eos_token_ids)
+        self.last_cached_tokens = 0
+        self._sched_batch = 0
+
+    def allocate(self) -> int:
+        s = self.eng.allocate_slot()
+        if s < 0:
+            raise RuntimeError("no free slot")
+        return s
+
+    def free(self, slot: int) -> None:
+        self.eng.free_slot(slot)
+
+    def prefill_tokens(self, slot: int, prompt: list[int], chunk: int, sp: Any) -> int:
+        return int(self.eng.prefill(slot, [int(t) for t in prompt]))
+
+    def decode_tokens(self, slots: list[int], toks: list[int], sp: Any) -> list[int]:
+        return [int(t) for t in self.eng.decode_step(list(slots), [int(t) for t in toks])]
+
+    def generate_batch(self, prompts, max_new, eos_ids, max_batch):
+        if self._sched_batch != max_batch:
+            self.eng.stop_scheduler()
+            self.eng.start_scheduler(max(1, min(max_batch, self.eng.max_slots)), 8192)
+            self._sched_batch = max_batch
+        ids = [self.eng.submit([int(t) for t in p], int(n), True) for p, n in zip(prompts, max_new)]
+        out = []
+        for i in ids:
+            r = self.eng.wait(i, -1)
+            toks = list(r.tokens)
+            eos = bool(toks) and toks[-1] in eos_ids
+            out.append((toks[:-1] if eos else toks, "stop" if eos else r.finish_reason,
+                        {"prefill_seconds": r.prefill_seconds, "decode_seconds": r.decode_seconds,
+                         "total_seconds": r.queue_seconds + r.prefill_seconds + r.decode_seconds,
+                         "ttft_seconds": r.queue_seconds + r.prefill_seconds}))
+        return out
+
+    def stats(self) -> dict:
+        st = self.eng.stats()
+        return {"kv_blocks_total": self.eng.total_blocks, "kernel_launches": st.kernel_launches, "weight_bytes": st.weight_bytes}
+
+
 def _device(args) -> torch.device:
     if args.device is not None:
         return torch.device(args.device if isinstance(args.device, str) else f"cuda:{args.device}")
@@ -201,6 +256,10 @@ def load_runtime(args):
     model = args.model
     max_ctx = args.max_model_len or 8192 + 512
     slots = max(1, args.max_batch_size)
+    if getattr(args, "backend", "auto") == "cpp" and world == 1 and not model.startswith("synthetic:"):
+        from pocketllm.backends.native_backend import NullChannel
+        return CppRuntimeAdapter(args.checkpoint_dir, dev.index or 0, max_ctx, slots,
+                                 args.prefill_chunk_tokens or 8192), None, NullChannel()
     if model.startswith("synthetic:"):
         name = model.split(":", 1)[1]
         cfg = qh.QwenHybridConfig.tiny() if name in ("qwen-tiny", "tiny") else qh.QwenHybridConfig.config2()

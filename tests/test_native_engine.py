@@ -118,3 +118,39 @@ def test_device_prepack_matches_host_prepack():
         assert L.b200_prepack_fp8(_lib.ptr(w), _lib.ptr(out), n, k, _lib.stream()) == 0
         torch.cuda.synchronize()
         assert torch.equal(out, want.view(torch.uint8).reshape(-1))
+
+
+@pytest.mark.gpu
+def test_pybind_engine_and_cpp_backend_match_python_runtime():
+    """``pocketllm_engine_cpp.QwenEngine`` directly, and through ``pocketllm.LLM(backend="cpp")``."""
+    from deepseek_v4_2080ti_b200 import pocketllm_engine_cpp as cpp
+    from deepseek_v4_2080ti_b200.models import qwen_hybrid as qh
+    gen = torch.Generator().manual_seed(13)
+    with tempfile.TemporaryDirectory() as d:
+        cfg, state = _write_tiny(d, "cuda")
+        assert cpp.is_qwen3_5_checkpoint(d) in (True, False)
+        prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gen, dtype=torch.int32).tolist() for n in (50, 21)]
+        w = qh.QwenHybridWeights(cfg, iter(state), "cuda")
+        rt = qh.QwenHybridRuntime(cfg, w, max_slots=1, max_context=256)
+        want = [rt.generate(torch.tensor(p, dtype=torch.int32), 6) for p in prompts]
+        opt = cpp.QwenEngineOptions()
+        opt.max_slots, opt.max_context = 2, 256
+        eng = cpp.QwenEngine(d, opt)
+        toks, ps, ds = eng.generate(prompts[0], 6)
+        assert list(toks) == want[0] and ps > 0 and eng.stats().kernel_launches > 0
+        s = eng.allocate_slot()
+        t0 = eng.prefill(s, prompts[1])
+        assert t0 == want[1][0] and eng.slot_length(s) == len(prompts[1])
+        assert eng.decode_step([s], [t0])[0] == want[1][1]
+        eng.free_slot(s)
+        eng.start_scheduler(2, 64)
+        ids = [eng.submit(p, 6) for p in prompts]
+        res = [eng.wait(i, 60000) for i in ids]
+        assert [list(r.tokens)[:3] for r in res] == [x[:3] for x in want] and all(r.finish_reason == "length" for r in res)
+        eng.stop_scheduler()
+        del eng
+        from pocketllm import LLM, EngineArgs, SamplingParams
+        llm = LLM(EngineArgs(model=d, backend="cpp", max_model_len=256))
+        out = llm.generate([{"prompt_token_ids": prompts[0]}], SamplingParams(max_tokens=6))
+        assert list(out[0].token_ids) == want[0]
+        llm.close()
