@@ -30,6 +30,7 @@ struct DecodeParams {
   const __nv_bfloat16* gate;     // optional [B, Hq, D]
   int max_blocks, bs, Hq, Hkv, splits;
   float scale_log2;
+  int window, sinks;             // window > 0: only the first `sinks` and the last `window` keys are visible
 };
 
 template <int G>
@@ -42,7 +43,11 @@ gqa_decode_kernel(DecodeParams p) {
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int half = lane >> 4, dl = lane & 15;
-  const int kv_len = p.kv_len[b];
+  const int kv_total = p.kv_len[b];
+  // with a sliding window the visible keys are renumbered densely: [0, sinks) then the last `window` keys
+  const bool windowed = p.window > 0 && kv_total > p.sinks + p.window;
+  const int kv_len = windowed ? p.sinks + p.window : kv_total;
+  const int win_shift = kv_total - p.window - p.sinks;          // dense index j >= sinks is key j + win_shift
   const int per = (kv_len + p.splits - 1) / p.splits;
   const int k0 = split * per, k1 = min(kv_len, k0 + per);
   const int* bt = p.block_table + (size_t)b * p.max_blocks;
@@ -68,7 +73,8 @@ gqa_decode_kernel(DecodeParams p) {
     // the loop bound is warp-uniform: every lane runs the shuffles, rows past the range contribute nothing
     const int kk = base + half;
     const bool valid = kk < k1;
-    const int kc = valid ? kk : k0;
+    int kc = valid ? kk : k0;
+    if (windowed && kc >= p.sinks) kc += win_shift;
     const int blk = bt[kc / p.bs];
     const size_t row = ((size_t)(blk * p.Hkv + kvh) * p.bs + (kc % p.bs)) * D + dl * 8;
     const uint4 ku = *reinterpret_cast<const uint4*>(p.k_cache + row);
@@ -165,6 +171,8 @@ __global__ void gqa_decode_merge_kernel(const float* __restrict__ partial, int s
 
 }  // namespace
 
+static thread_local int g_window = 0, g_sinks = 0;   // set by b200_gqa_decode_ex for the launch it wraps
+
 // q/out/gate: [B, Hq, 128] bf16; caches [num_blocks, Hkv, block_size, 128]; workspace: fp32
 // [B * Hq * splits * 130] (used when splits > 1).
 extern "C" int b200_gqa_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
@@ -188,6 +196,8 @@ extern "C" int b200_gqa_decode(const void* q, const void* k_cache, const void* v
   p.Hkv = n_kv_heads;
   p.splits = splits;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.window = g_window;
+  p.sinks = g_sinks;
   if (splits > 1 && !workspace) return -6;
   dim3 grid(splits, n_kv_heads, batch);
   cudaError_t e = cudaSuccess;
@@ -206,4 +216,18 @@ extern "C" int b200_gqa_decode(const void* q, const void* k_cache, const void* v
     e = b200::launch_pdl(gqa_decode_merge_kernel, dim3(batch * n_q_heads), dim3(D), 0, stream,
                          (const float*)workspace, splits, p.gate, p.out);
   return (int)e;
+}
+
+// As b200_gqa_decode with a sliding window: each query sees the first `sinks` keys and the last `window` keys of its
+// sequence (window <= 0: every key).
+extern "C" int b200_gqa_decode_ex(const void* q, const void* k_cache, const void* v_cache, void* out, const void* gate,
+                                  const int* block_table, const int* kv_len, float* workspace, int batch, int max_blocks,
+                                  int block_size, int n_q_heads, int n_kv_heads, int splits, float softmax_scale, int window,
+                                  int sinks, cudaStream_t stream) {
+  g_window = window > 0 ? window : 0;
+  g_sinks = sinks > 0 ? sinks : 0;
+  const int rc = b200_gqa_decode(q, k_cache, v_cache, out, gate, block_table, kv_len, workspace, batch, max_blocks, block_size,
+                                 n_q_heads, n_kv_heads, splits, softmax_scale, stream);
+  g_window = g_sinks = 0;
+  return rc;
 }

@@ -45,6 +45,7 @@ struct Params {
   __nv_bfloat16* out;      // [T, Hq, D]
   const __nv_bfloat16* gate;  // optional [T, Hq, D], out *= sigmoid(gate)
   int* status;
+  int window, sinks;       // window > 0: a query at position p sees keys (p - window, p] and the first `sinks` keys
 };
 
 __device__ __forceinline__ uint64_t desc_k_sw128(const void* p) { return umma_desc_sw128(p); }
@@ -91,7 +92,16 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int q_row0 = p.q_start[b] + q0;
   const int kvh = h / (p.n_q_heads / p.n_kv_heads);
   const int pos0 = kv_len - q_len + q0;  // context position of the tile's first query row
-  int n_tiles = (min(kv_len, pos0 + BQ) + BKV - 1) / BKV;
+  // Key tiles this query tile visits.  With a sliding window the tiles wholly below every row's window are
+  // skipped, except the leading tiles that hold attention-sink keys: iteration j maps to tile_of(j).
+  const int n_tiles_all = (min(kv_len, pos0 + BQ) + BKV - 1) / BKV;
+  int n_sink_tiles = 0, first_win_tile = 0;
+  if (p.window > 0) {
+    first_win_tile = max(0, pos0 - p.window + 1) / BKV;
+    n_sink_tiles = min(first_win_tile, (p.sinks + BKV - 1) / BKV);
+  }
+  const int n_tiles = n_sink_tiles + (n_tiles_all - first_win_tile);
+  auto tile_of = [&](int j) { return j < n_sink_tiles ? j : first_win_tile + (j - n_sink_tiles); };
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -136,7 +146,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        const int key0 = j * BKV;
+        const int key0 = tile_of(j) * BKV;
         int nblk = 0;
         for (int s = 0; s < per_tile; ++s)
           if (key0 + s * bs < kv_len) ++nblk;
@@ -220,10 +230,18 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[i]) * p.scale_log2;
       }
-      const int key0 = j * BKV;
+      const int key0 = tile_of(j) * BKV;
       const int kmax = min(limit, kv_len - 1) - key0;  // keys with index > kmax are masked
+      const int klo = p.window > 0 ? limit - p.window + 1 - key0 : -(1 << 30);   // keys below klo are outside the window
       float m_tile = -INFINITY;
-      if (kmax < 127) {
+      if (klo > 0) {
+        const int ks = p.sinks - key0;                 // keys below ks are sinks and stay visible
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {
+          if (i > kmax || (i < klo && i >= ks)) s[i] = -INFINITY;
+          m_tile = fmaxf(m_tile, s[i]);
+        }
+      } else if (kmax < 127) {
 #pragma unroll
         for (int i = 0; i < 128; ++i) {
           if (i > kmax) s[i] = -INFINITY;
@@ -360,6 +378,9 @@ using namespace b200;
 // q: [T, Hq, 128] bf16; k_cache / v_cache: [num_blocks, Hkv, block_size, 128] bf16 (zero-initialised
 // at allocation); block_table: [B, max_blocks] int32; q_start/q_len/kv_len: [B] int32 (device).
 // out: [T, Hq, 128] bf16; gate optional (same shape as out). max_q_len bounds the grid.
+// Sliding-window setting of the next launch (set by b200_gqa_prefill_ex; 0 = full causal attention).
+static thread_local int g_window = 0, g_sinks = 0;
+
 extern "C" int b200_gqa_prefill(const void* q, const void* k_cache, const void* v_cache, void* out,
                                 const void* gate, const int* block_table, const int* q_start,
                                 const int* q_len, const int* kv_len, int batch, int max_q_len,
@@ -397,7 +418,25 @@ extern "C" int b200_gqa_prefill(const void* q, const void* k_cache, const void* 
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.gate = reinterpret_cast<const __nv_bfloat16*>(gate);
   p.status = status;
+  p.window = g_window;
+  p.sinks = g_sinks;
   dim3 grid((max_q_len + BQ - 1) / BQ, n_q_heads, batch);
   gqa_prefill_kernel<<<grid, NTHREADS, SMEM_BYTES, stream>>>(tmQ, tmK, tmV, p);
   return (int)cudaGetLastError();
+}
+
+// As b200_gqa_prefill, restricted to a sliding window with attention sinks: a query at position p attends to the keys
+// (p - window, p] and to the first `sinks` keys of its sequence (window <= 0: full causal attention).
+extern "C" int b200_gqa_prefill_ex(const void* q, const void* k_cache, const void* v_cache, void* out, const void* gate,
+                                   const int* block_table, const int* q_start, const int* q_len, const int* kv_len, int batch,
+                                   int max_q_len, int total_q_rows, int max_blocks, int num_blocks, int block_size,
+                                   int n_q_heads, int n_kv_heads, float softmax_scale, int window, int sinks, int* status,
+                                   cudaStream_t stream) {
+  g_window = window > 0 ? window : 0;
+  g_sinks = sinks > 0 ? sinks : 0;
+  const int rc = b200_gqa_prefill(q, k_cache, v_cache, out, gate, block_table, q_start, q_len, kv_len, batch, max_q_len,
+                                  total_q_rows, max_blocks, num_blocks, block_size, n_q_heads, n_kv_heads, softmax_scale, status,
+                                  stream);
+  g_window = g_sinks = 0;
+  return rc;
 }

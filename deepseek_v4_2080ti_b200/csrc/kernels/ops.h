@@ -127,6 +127,14 @@ int b200_gqa_prefill(const void* q, const void* k_cache, const void* v_cache, vo
                      const int* block_table, const int* q_start, const int* q_len, const int* kv_len, int batch,
                      int max_q_len, int total_q_rows, int max_blocks, int num_blocks, int block_size, int n_q_heads,
                      int n_kv_heads, float softmax_scale, int* status, cudaStream_t stream);
+int b200_gqa_prefill_ex(const void* q, const void* k_cache, const void* v_cache, void* out, const void* gate,
+                        const int* block_table, const int* q_start, const int* q_len, const int* kv_len, int batch,
+                        int max_q_len, int total_q_rows, int max_blocks, int num_blocks, int block_size, int n_q_heads,
+                        int n_kv_heads, float softmax_scale, int window, int sinks, int* status, cudaStream_t stream);
+int b200_gqa_decode_ex(const void* q, const void* k_cache, const void* v_cache, void* out, const void* gate,
+                       const int* block_table, const int* kv_len, float* workspace, int batch, int max_blocks, int block_size,
+                       int n_q_heads, int n_kv_heads, int splits, float softmax_scale, int window, int sinks,
+                       cudaStream_t stream);
 int b200_gqa_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const void* gate,
                     const int* block_table, const int* kv_len, float* workspace, int batch, int max_blocks,
                     int block_size, int n_q_heads, int n_kv_heads, int splits, float softmax_scale, cudaStream_t stream);

@@ -365,8 +365,12 @@ class QwenHybridRuntime:
     """Owns weights, the paged KV pool, per-slot recurrent state and the forward passes."""
 
     def __init__(self, cfg: QwenHybridConfig, weights: QwenHybridWeights, max_slots: int = 1,
-                 max_context: int = 8192 + 512, block_size: int = 64, comm=None, num_blocks: int | None = None):
+                 max_context: int = 8192 + 512, block_size: int = 64, comm=None, num_blocks: int | None = None,
+                 attention_window: int = 0, attention_sink_tokens: int = 0):
+        """``attention_window`` > 0 restricts the full-attention layers to a sliding window of that many keys plus
+        the first ``attention_sink_tokens`` keys (the cache still holds every position)."""
         self.cfg, self.w, self.device = cfg, weights, weights.device
+        self.attention_window, self.attention_sinks = int(attention_window), int(attention_sink_tokens)
         self.comm = comm or NoComm()
         W = self.comm.world
         assert W == weights.world
@@ -520,10 +524,10 @@ class QwenHybridRuntime:
             True, cfg.rms_norm_eps, self.inv_freq, cfg.rotary_dim, positions, kv_slots, kc, vc, self.hq, self.hkv)
         if meta["mode"] == "prefill":
             o = attention.prefill(q, kc, vc, meta["block_table"], meta["q_start"], meta["q_len"], meta["kv_len"],
-                                  meta["max_q_len"], gate=gate)
+                                  meta["max_q_len"], gate=gate, window=self.attention_window, sinks=self.attention_sinks)
         else:
             o = attention.decode(q, kc, vc, meta["block_table"], meta["kv_len"], gate=gate,
-                                 max_kv_len=meta["max_kv_len"])
+                                 max_kv_len=meta["max_kv_len"], window=self.attention_window, sinks=self.attention_sinks)
         return self._row_parallel(o.view(t, self.hq * 128), lw.out)
 
     def _embed(self, ids: torch.Tensor) -> torch.Tensor:
@@ -581,7 +585,7 @@ class QwenHybridRuntime:
                     proj, 0, 128 * gate_mul, cfg.attn_output_gate, proj, qw, proj, qw + self.hkv * 128, lw.q_norm,
                     lw.k_norm, True, eps, self.inv_freq, cfg.rotary_dim, positions, kv_slots, kc, vc, self.hq, self.hkv)
                 o = attention.decode(q, kc, vc, meta["block_table"], meta["kv_len"], gate=gate,
-                                     max_kv_len=meta["max_kv_len"])
+                                     max_kv_len=meta["max_kv_len"], window=self.attention_window, sinks=self.attention_sinks)
                 d_attn = self.comm.all_reduce(gemm.linear_stream(o.view(t, self.hq * 128), lw.out))
             _, xs2 = basic.rmsnorm_split(h, d_attn, lw.post_ln, terms, eps, True, want_bf16=False)
             gu = gemm.linear_stream(None, lw.gate_up, xsplit=xs2)

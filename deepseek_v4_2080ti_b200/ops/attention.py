@@ -66,7 +66,8 @@ def qk_fullnorm_rope_append(proj, q_off, k_off, v_off, q_gamma, k_gamma, row_ss,
     return q_out
 
 
-def prefill(q, k_cache, v_cache, block_table, q_start, q_len, kv_len, max_q_len, gate=None, scale=None):
+def prefill(q, k_cache, v_cache, block_table, q_start, q_len, kv_len, max_q_len, gate=None, scale=None, window: int = 0,
+            sinks: int = 0):
     """Causal attention of new query rows against the paged cache (which already holds their K/V).
 
     q: [T, Hq, 128]; block_table [B, max_blocks] int32; q_start/q_len/kv_len [B] int32 device tensors.
@@ -76,10 +77,11 @@ def prefill(q, k_cache, v_cache, block_table, q_start, q_len, kv_len, max_q_len,
     nb, hkv, bs, _ = k_cache.shape
     out = torch.empty_like(q)
     scale = 1.0 / math.sqrt(D) if scale is None else scale
-    rc = _lib.lib().b200_gqa_prefill(
+    rc = _lib.lib().b200_gqa_prefill_ex(
         _lib.ptr(q), _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(out), _lib.ptr(gate), _lib.ptr(block_table),
         _lib.ptr(q_start), _lib.ptr(q_len), _lib.ptr(kv_len), block_table.shape[0], int(max_q_len), t,
-        block_table.shape[1], nb, bs, hq, hkv, _f(scale), _lib.ptr(_lib.status_word(q.device)), _lib.stream())
+        block_table.shape[1], nb, bs, hq, hkv, _f(scale), int(window), int(sinks), _lib.ptr(_lib.status_word(q.device)),
+        _lib.stream())
     _lib.check(rc, "gqa_prefill")
     return out
 
@@ -88,8 +90,9 @@ _dec_ws: dict[int, torch.Tensor] = {}
 
 
 def decode(q, k_cache, v_cache, block_table, kv_len, gate=None, scale=None, splits: int | None = None,
-           max_kv_len: int | None = None):
-    """One query row per sequence. q: [B, Hq, 128]."""
+           max_kv_len: int | None = None, window: int = 0, sinks: int = 0):
+    """One query row per sequence. q: [B, Hq, 128].  ``window`` > 0: only the first ``sinks`` and the last ``window``
+    keys of each sequence are visible (sliding window with attention sinks)."""
     b, hq, d = q.shape
     nb, hkv, bs, _ = k_cache.shape
     out = torch.empty_like(q)
@@ -105,9 +108,9 @@ def decode(q, k_cache, v_cache, block_table, kv_len, gate=None, scale=None, spli
         if ws is None or ws.numel() < need:
             ws = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device)
             _dec_ws[dev] = ws
-    rc = _lib.lib().b200_gqa_decode(_lib.ptr(q), _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(out), _lib.ptr(gate),
-                                    _lib.ptr(block_table), _lib.ptr(kv_len), _lib.ptr(ws), b, block_table.shape[1],
-                                    bs, hq, hkv, splits, _f(scale), _lib.stream())
+    rc = _lib.lib().b200_gqa_decode_ex(_lib.ptr(q), _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(out), _lib.ptr(gate),
+                                       _lib.ptr(block_table), _lib.ptr(kv_len), _lib.ptr(ws), b, block_table.shape[1],
+                                       bs, hq, hkv, splits, _f(scale), int(window), int(sinks), _lib.stream())
     _lib.check(rc, "gqa_decode", 2 if splits > 1 else 1)
     return out
 

@@ -129,3 +129,39 @@ def test_qk_norm_rope_append():
     got_v = vc[(slots // bs).long(), :, (slots % bs).long()]
     assert (got_k.float() - want_k).abs().max().item() < 3e-2
     assert torch.equal(got_v, vsrc)
+
+
+@pytest.mark.parametrize("window,sinks", [(64, 0), (100, 4), (300, 130), (16, 16)])
+def test_sliding_window_with_sinks_prefill_and_decode(window, sinks):
+    """A query at position p sees keys (p - window, p] and the first `sinks` keys; prefill (with tile skipping) and
+    split-KV decode against fp32 PyTorch with the same mask, on a scrambled page table."""
+    from deepseek_v4_2080ti_b200.ops import _lib, attention
+    torch.manual_seed(window + sinks)
+    hq, hkv, bs, ctx, tq = 4, 2, 64, 700, 450
+    nblk = (ctx + bs - 1) // bs
+    perm = torch.randperm(nblk) + 1
+    bt = perm.to(torch.int32).cuda().view(1, nblk).contiguous()
+    kc = torch.zeros(nblk + 1, hkv, bs, 128, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    k = (torch.randn(ctx, hkv, 128, device="cuda") * 0.5).bfloat16()
+    v = (torch.randn(ctx, hkv, 128, device="cuda") * 0.5).bfloat16()
+    pos = torch.arange(ctx)
+    blk, off = perm[pos // bs].cuda(), (pos % bs).cuda()
+    kc[blk, :, off] = k
+    vc[blk, :, off] = v
+    q = (torch.randn(tq, hq, 128, device="cuda") * 0.5).bfloat16()
+    i32 = lambda x: torch.tensor([x], dtype=torch.int32, device="cuda")
+    out = attention.prefill(q, kc, vc, bt, i32(0), i32(tq), i32(ctx), tq, window=window, sinks=sinks)
+    qpos = torch.arange(ctx - tq, ctx, device="cuda")
+    kpos = torch.arange(ctx, device="cuda")
+    vis = (kpos[None] <= qpos[:, None]) & ((kpos[None] > qpos[:, None] - window) | (kpos[None] < sinks))
+    kk, vv = k.float().repeat_interleave(hq // hkv, 1), v.float().repeat_interleave(hq // hkv, 1)
+    sc = torch.einsum("qhd,khd->hqk", q.float(), kk) / 128 ** 0.5
+    want = torch.einsum("hqk,khd->qhd", sc.masked_fill(~vis[None], float("-inf")).softmax(-1), vv)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert (out.float() - want).abs().max() < 2e-2
+    for splits in (1, 3):
+        qd = q[-1:].contiguous()
+        od = attention.decode(qd, kc, vc, bt, i32(ctx), splits=splits, window=window, sinks=sinks)
+        assert (od.float() - want[-1:]).abs().max() < 2e-2, splits
