@@ -147,6 +147,24 @@ def build_core(jobs: int | None = None) -> dict[str, Path]:
     return products
 
 
+def build_selftest(sanitizer: str = "") -> Path:
+    """Host-only self-test of the C++ core (csrc/selftest), optionally under a sanitizer:
+    ``"address"`` (AddressSanitizer + UBSan) or ``"thread"`` (ThreadSanitizer).  Core sources are recompiled with the
+    same flags into one executable ``bin/core_selftest[_asan|_tsan]``."""
+    BIN.mkdir(exist_ok=True)
+    flags = {"": [], "address": ["-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-g"],
+             "thread": ["-fsanitize=thread", "-g"]}[sanitizer]
+    suffix = {"": "", "address": "_asan", "thread": "_tsan"}[sanitizer]
+    exe = BIN / f"core_selftest{suffix}"
+    srcs = sorted((CSRC / "core").glob("*.cpp")) + [CSRC / "selftest" / "core_selftest.cpp"]
+    cxx = CXX
+    if sanitizer and os.path.exists("/usr/bin/g++"):
+        cxx = "/usr/bin/g++"          # the distribution compiler ships the sanitizer runtimes
+    if (not exe.exists()) or any(s.stat().st_mtime > exe.stat().st_mtime for s in srcs):
+        _run([cxx, "-std=c++17", "-O1", *flags, "-I", str(CSRC), *map(str, srcs), "-o", str(exe), "-pthread"])
+    return exe
+
+
 def build_cpu() -> Path | None:
     """AVX2 multi-threaded host kernels (csrc/cpu): the CPU oracle path for FP4 routed experts."""
     OBJ.mkdir(exist_ok=True)

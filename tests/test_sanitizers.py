@@ -1,0 +1,24 @@
+"""The C++ runtime core under AddressSanitizer + UBSan and under ThreadSanitizer (host only): block pool / table,
+batch scheduler with concurrent submitters and cancellation, command channel between threads, JSON parser on hostile
+input, host sampler.  Skipped where the toolchain has no sanitizer runtime."""
+import os
+import subprocess
+
+import pytest
+
+from deepseek_v4_2080ti_b200 import build
+
+
+@pytest.mark.parametrize("sanitizer", ["", "address", "thread"])
+def test_core_selftest(sanitizer):
+    try:
+        exe = build.build_selftest(sanitizer)
+    except RuntimeError:
+        if sanitizer:
+            pytest.skip(f"no {sanitizer} sanitizer runtime in this toolchain")
+        raise
+    env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1:abort_on_error=0", UBSAN_OPTIONS="halt_on_error=1",
+               TSAN_OPTIONS="halt_on_error=1")
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=900, env=env)
+    assert r.returncode == 0 and "CORE_SELFTEST_OK" in r.stdout, (r.stdout[-500:], r.stderr[-3000:])
+    assert "ERROR: AddressSanitizer" not in r.stderr and "WARNING: ThreadSanitizer" not in r.stderr and "runtime error" not in r.stderr
