@@ -20,14 +20,17 @@ _tables: dict[str, torch.Tensor] = {}
 
 
 def tables(device="cpu") -> dict[str, torch.Tensor]:
-    """Codebooks as float32 tensors: iq2xxs [256, 8], iq3xxs [256, 4], iq1 [2048, 8]; ksigns uint8 [128]."""
+    """Codebooks as float32 tensors: iq2xxs [256, 8], iq2xs [512, 8], iq3xxs [256, 4], iq1 [2048, 8], iq4nl [16];
+    ksigns uint8 [128]."""
     if not _tables:
         try:
             from gguf import quants as gq
         except Exception as exc:  # pragma: no cover - image always has it
             raise RuntimeError("the IQ codebooks are read from the 'gguf' Python package, which is not importable") from exc
-        for cls in (gq.IQ2_XXS, gq.IQ3_XXS, gq.IQ1_M):
+        for cls in (gq.IQ2_XXS, gq.IQ2_XS, gq.IQ3_XXS, gq.IQ1_M):
             cls.init_grid()
+        _tables["iq2xs"] = torch.from_numpy(np.ascontiguousarray(gq.IQ2_XS.grid.reshape(512, 8))).float()
+        _tables["iq4nl"] = torch.tensor(list(gq.IQ4_NL.kvalues), dtype=torch.float32)
         _tables["iq2xxs"] = torch.from_numpy(np.ascontiguousarray(gq.IQ2_XXS.grid.reshape(256, 8))).float()
         _tables["iq3xxs"] = torch.from_numpy(np.ascontiguousarray(gq.IQ3_XXS.grid.reshape(256, 4))).float()
         _tables["iq1"] = torch.from_numpy(np.ascontiguousarray(gq.IQ1_M.grid.reshape(2048, 8))).float()
@@ -314,10 +317,153 @@ def _d_iq1_m(b):
     return (dl.repeat_interleave(2, 1)[..., None] * vals).reshape(n, QK_K)
 
 
+# ----------------------------------------------------------------------------- Q3_K
+# block: hmask[32] | qs[64] | scales[12] | d.  16 sub-blocks of 16; value = d * (scale6 - 32) * (q2 - (hbit ? 0 : 4)).
+# Element e = 128 h + 32 s + l takes its low bits from (qs[32 h + l] >> 2 s) & 3 and its high bit from bit (4 h + s)
+# of hmask[l].
+def _q_q3_k(w):
+    b = _blocks(w, QK_K)
+    n = b.shape[0]
+    x = b.view(n, 16, 16)
+    amax = x.abs().amax(-1)                                     # [n, 16]
+    sub = amax / 4.0                                             # q in [-4, 3]
+    d = (sub.amax(-1) / 31.0).to(torch.float16).float().clamp_min(6e-8)
+    sc = (sub / d[:, None]).round().clamp(0, 31)                 # stored + 32
+    eff = (d[:, None] * sc).clamp_min(1e-12)
+    q = (x / eff[..., None]).round().clamp(-4, 3).long() + 4     # 0..7; sub-blocks with scale 0 decode to 0 anyway
+    q = q.view(n, 2, 4, 32)                                      # [half, shift, l]
+    lo, hi = q & 3, q >> 2
+    qs = sum(lo[:, :, s_] << (2 * s_) for s_ in range(4)).to(torch.uint8).reshape(n, 64)
+    hm = sum(hi[:, h_, s_] << (4 * h_ + s_) for h_ in range(2) for s_ in range(4)).to(torch.uint8)      # [n, 32]
+    s6 = (sc.long() + 32)                                        # 6-bit codes [n, 16]
+    lsc = (s6[:, :8] & 0xF) | ((s6[:, 8:] & 0xF) << 4)
+    hsc = sum(((s6[:, 4 * j:4 * j + 4] >> 4) & 3) << (2 * j) for j in range(4))
+    scales = torch.cat([lsc, hsc], 1).to(torch.uint8)
+    return torch.cat([hm, qs, scales, _f16_bytes(d)], 1)
+
+
+def _d_q3_k(b):
+    n = b.shape[0]
+    hm, qs, sc, d = b[:, 0:32].long(), b[:, 32:96].long(), b[:, 96:108].long(), _bytes_f16(b[:, 108:110])
+    lsc = torch.stack([sc[:, :8] & 0xF, sc[:, :8] >> 4], 1).reshape(n, 16)
+    hsc = torch.stack([(sc[:, 8:12] >> (2 * j)) & 3 for j in range(4)], 1).reshape(n, 16)
+    s6 = ((lsc | (hsc << 4)) - 32).float()
+    ql = torch.stack([(qs.view(n, 2, 32) >> (2 * s_)) & 3 for s_ in range(4)], 2)            # [n, 2, 4, 32]
+    qh = torch.stack([(hm >> j) & 1 for j in range(8)], 1).view(n, 2, 4, 32)
+    q = (ql - ((qh ^ 1) << 2)).float().reshape(n, 16, 16)
+    return ((d[:, None] * s6)[..., None] * q).reshape(n, QK_K)
+
+
+# ----------------------------------------------------------------------------- Q6_K
+# block: ql[128] | qh[64] | scales[16] int8 | d.  value = d * scale * (q6 - 32); element e = 128 h + 32 g + l (g 0..3)
+# has low nibble (ql[64 h + 32 (g & 1) + l] >> 4 (g >> 1)) & 15 and high bits (qh[32 h + l] >> 2 g) & 3.
+def _q_q6_k(w):
+    b = _blocks(w, QK_K)
+    n = b.shape[0]
+    x = b.view(n, 16, 16)
+    sub = x.abs().amax(-1) / 32.0
+    d = (sub.amax(-1) / 127.0).to(torch.float16).float().clamp_min(6e-8)
+    sc = (sub / d[:, None]).round().clamp(0, 127)
+    eff = (d[:, None] * sc).clamp_min(1e-12)
+    q = ((x / eff[..., None]).round().clamp(-32, 31).long() + 32).view(n, 2, 4, 32)          # [half, g, l]
+    lo, hi = q & 0xF, q >> 4
+    ql = torch.stack([lo[:, :, 0] | (lo[:, :, 2] << 4), lo[:, :, 1] | (lo[:, :, 3] << 4)], 2).reshape(n, 128)
+    qh = sum(hi[:, :, g_] << (2 * g_) for g_ in range(4)).reshape(n, 64)
+    return torch.cat([ql.to(torch.uint8), qh.to(torch.uint8), sc.to(torch.int8).view(torch.uint8), _f16_bytes(d)], 1)
+
+
+def _d_q6_k(b):
+    n = b.shape[0]
+    ql, qh = b[:, 0:128].long().view(n, 2, 2, 32), b[:, 128:192].long().view(n, 2, 32)
+    sc, d = b[:, 192:208].contiguous().view(torch.int8).float(), _bytes_f16(b[:, 208:210])
+    lo = torch.stack([ql[:, :, 0] & 0xF, ql[:, :, 1] & 0xF, ql[:, :, 0] >> 4, ql[:, :, 1] >> 4], 2)      # [n, 2, 4, 32]
+    hi = torch.stack([(qh >> (2 * g_)) & 3 for g_ in range(4)], 2)
+    q = ((lo | (hi << 4)) - 32).float().reshape(n, 16, 16)
+    return ((d[:, None] * sc)[..., None] * q).reshape(n, QK_K)
+
+
+# ----------------------------------------------------------------------------- IQ2_XS
+# block: d | qs[32] uint16 (9-bit index into a 512 x 8 magnitude grid | 7-bit sign index << 9) | scales[8] (two 4-bit
+# scales per byte, one per 16 elements).  value = d * (0.5 + s) * 0.25 * grid * sign.
+def _q_iq2_xs(w):
+    t = tables(w.device)
+    b = _blocks(w, QK_K)
+    n = b.shape[0]
+    x = b.view(n, 16, 2, 8)
+    gmaxv = float(t["iq2xs"].max())
+    amax = x.abs().amax((1, 2, 3)).clamp_min(1e-12)
+    d = (amax / (gmaxv * 0.25 * 15.5)).to(torch.float16).float().clamp_min(6e-8)
+    s = (x.abs().amax((2, 3)) / (d[:, None] * 0.25 * gmaxv) - 0.5).round().clamp(0, 15)
+    db = d[:, None] * (0.5 + s) * 0.25
+    gi = _nearest((x.abs() / db[..., None, None]).reshape(-1, 8), t["iq2xs"]).view(n, 16, 2)
+    sidx, _ = _sign_index(x < 0, x.abs())
+    q16 = (gi | (sidx << 9)).reshape(n, 32)
+    qs = torch.stack([q16 & 0xFF, q16 >> 8], -1).to(torch.uint8).reshape(n, 64)
+    sl = s.long().view(n, 8, 2)
+    scales = (sl[..., 0] | (sl[..., 1] << 4)).to(torch.uint8)
+    return torch.cat([_f16_bytes(d), qs, scales], 1)
+
+
+def _d_iq2_xs(b):
+    t = tables(b.device)
+    n = b.shape[0]
+    d = _bytes_f16(b[:, 0:2])
+    q = b[:, 2:66].long().view(n, 32, 2)
+    q16 = q[..., 0] | (q[..., 1] << 8)
+    sc = b[:, 66:74].long()
+    s = torch.stack([sc & 0xF, sc >> 4], -1).reshape(n, 16).float()
+    db = d[:, None] * (0.5 + s) * 0.25
+    grid = t["iq2xs"][q16 & 511].view(n, 16, 2, 8)
+    signs = _signs_from_index(q16 >> 9, t["ksigns"]).view(n, 16, 2, 8)
+    return (db[..., None, None] * grid * signs).reshape(n, QK_K)
+
+
+# ----------------------------------------------------------------------------- IQ4_XS
+# block: d | scales_h uint16 (2 bits per sub-block) | scales_l[4] (4 bits per sub-block) | qs[128].  8 sub-blocks of
+# 32: value = d * (scale6 - 32) * kvalues[q4]; sub-block i keeps elements 0..15 in the low nibbles of qs[16 i ..] and
+# 16..31 in the high nibbles.
+def _q_iq4_xs(w):
+    t = tables(w.device)
+    kv = t["iq4nl"]
+    b = _blocks(w, QK_K)
+    n = b.shape[0]
+    x = b.view(n, 8, 32)
+    # the signed element of largest magnitude maps onto the codebook end of the same sign
+    idx = x.abs().argmax(-1, keepdim=True)
+    peak = x.gather(-1, idx).squeeze(-1)
+    sub = torch.where(peak < 0, peak / kv[0], peak / kv[-1])      # >= 0
+    d = (sub.amax(-1) / 31.0).to(torch.float16).float().clamp_min(6e-8)
+    ls = (sub / d[:, None]).round().clamp(0, 31)
+    eff = (d[:, None] * ls).clamp_min(1e-12)
+    q = ((x / eff[..., None]).unsqueeze(-1) - kv).abs().argmin(-1)                  # [n, 8, 32]
+    qs = (q[..., :16] | (q[..., 16:] << 4)).to(torch.uint8).reshape(n, 128)
+    s6 = ls.long() + 32
+    sl = (s6 & 0xF).view(n, 4, 2)
+    scales_l = (sl[..., 0] | (sl[..., 1] << 4)).to(torch.uint8)
+    sh = sum(((s6[:, i] >> 4) & 3) << (2 * i) for i in range(8))
+    scales_h = torch.stack([sh & 0xFF, sh >> 8], -1).to(torch.uint8)
+    return torch.cat([_f16_bytes(d), scales_h, scales_l, qs], 1)
+
+
+def _d_iq4_xs(b):
+    t = tables(b.device)
+    n = b.shape[0]
+    d = _bytes_f16(b[:, 0:2])
+    sh = b[:, 2].long() | (b[:, 3].long() << 8)
+    slb = b[:, 4:8].long()
+    sl = torch.stack([slb & 0xF, slb >> 4], -1).reshape(n, 8)
+    s6 = (sl | (torch.stack([(sh >> (2 * i)) & 3 for i in range(8)], 1) << 4)) - 32
+    qs = b[:, 8:136].long().view(n, 8, 16)
+    q = torch.cat([qs & 0xF, qs >> 4], -1)
+    return ((d[:, None] * s6.float())[..., None] * t["iq4nl"][q]).reshape(n, QK_K)
+
+
 _Q = {GGMLType.Q8_0: _q_q8_0, GGMLType.Q4_K: _q_q4_k, GGMLType.Q5_K: _q_q5_k, GGMLType.Q2_K: _q_q2_k,
-      GGMLType.IQ2_XXS: _q_iq2_xxs, GGMLType.IQ3_XXS: _q_iq3_xxs, GGMLType.IQ1_M: _q_iq1_m}
+      GGMLType.IQ2_XXS: _q_iq2_xxs, GGMLType.IQ3_XXS: _q_iq3_xxs, GGMLType.IQ1_M: _q_iq1_m, GGMLType.Q3_K: _q_q3_k,
+      GGMLType.Q6_K: _q_q6_k, GGMLType.IQ2_XS: _q_iq2_xs, GGMLType.IQ4_XS: _q_iq4_xs}
 _D = {GGMLType.Q8_0: _d_q8_0, GGMLType.Q4_K: _d_q4_k, GGMLType.Q5_K: _d_q5_k, GGMLType.Q2_K: _d_q2_k,
-      GGMLType.IQ2_XXS: _d_iq2_xxs, GGMLType.IQ3_XXS: _d_iq3_xxs, GGMLType.IQ1_M: _d_iq1_m}
+      GGMLType.IQ2_XXS: _d_iq2_xxs, GGMLType.IQ3_XXS: _d_iq3_xxs, GGMLType.IQ1_M: _d_iq1_m, GGMLType.Q3_K: _d_q3_k,
+      GGMLType.Q6_K: _d_q6_k, GGMLType.IQ2_XS: _d_iq2_xs, GGMLType.IQ4_XS: _d_iq4_xs}
 
 
 def quantize(w: torch.Tensor, t: GGMLType) -> torch.Tensor:

@@ -9,10 +9,11 @@ import torch
 from deepseek_v4_2080ti_b200.formats import gguf as G
 
 TYPES = [G.GGMLType.Q8_0, G.GGMLType.Q4_K, G.GGMLType.Q5_K, G.GGMLType.Q2_K, G.GGMLType.IQ2_XXS, G.GGMLType.IQ3_XXS,
-         G.GGMLType.IQ1_M]
-# relative L2 error bounds for N(0, sigma) inputs (bits per weight: 8.5, 4.5, 5.5, 2.6, 2.06, 3.06, 1.75)
+         G.GGMLType.IQ1_M, G.GGMLType.Q3_K, G.GGMLType.Q6_K, G.GGMLType.IQ2_XS, G.GGMLType.IQ4_XS]
+# relative L2 error bounds for N(0, sigma) inputs (bits per weight: 8.5, 4.5, 5.5, 2.6, 2.06, 3.06, 1.75, 3.4, 6.6, 2.3, 4.25)
 MAX_REL = {G.GGMLType.Q8_0: 0.01, G.GGMLType.Q4_K: 0.10, G.GGMLType.Q5_K: 0.05, G.GGMLType.Q2_K: 0.40,
-           G.GGMLType.IQ2_XXS: 0.42, G.GGMLType.IQ3_XXS: 0.25, G.GGMLType.IQ1_M: 0.60}
+           G.GGMLType.IQ2_XXS: 0.42, G.GGMLType.IQ3_XXS: 0.25, G.GGMLType.IQ1_M: 0.60, G.GGMLType.Q3_K: 0.22,
+           G.GGMLType.Q6_K: 0.03, G.GGMLType.IQ2_XS: 0.36, G.GGMLType.IQ4_XS: 0.10}
 
 
 @pytest.mark.parametrize("t", TYPES)
@@ -34,7 +35,8 @@ def test_dequantiser_matches_gguf_package_and_quantiser_tracks_input(t):
         nb = G.BLOCK_BYTES[t]
         r = rnd.view(24, -1, nb)
         for off in {G.GGMLType.Q4_K: (0, 2), G.GGMLType.Q5_K: (0, 2), G.GGMLType.Q2_K: (80, 82), G.GGMLType.IQ2_XXS: (0,),
-                    G.GGMLType.IQ3_XXS: (0,), G.GGMLType.IQ1_M: ()}[t]:
+                    G.GGMLType.IQ3_XXS: (0,), G.GGMLType.IQ1_M: (), G.GGMLType.Q3_K: (108,), G.GGMLType.Q6_K: (208,),
+                    G.GGMLType.IQ2_XS: (0,), G.GGMLType.IQ4_XS: (0,)}[t]:
             r[..., off + 1] &= 0x3F
         if t == G.GGMLType.IQ1_M:
             r[..., 55] &= 0x3F                      # top nibble of the fp16 super-scale
