@@ -18,6 +18,7 @@ from typing import Callable, Iterator
 import torch
 
 from ..formats import fp8 as fp8fmt
+from ..utils.phase_profile import PROFILER
 from ..ops import _lib, attention, basic, gdn, gemm
 from ..ops.gemm import PackedLinear
 
@@ -490,27 +491,32 @@ class QwenHybridRuntime:
     def _mlp(self, lw: LayerWeights, h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
         x = basic.add_rmsnorm(h, delta, lw.post_ln, cfg.rms_norm_eps, True)
-        gu = gemm.linear(x, lw.gate_up)
+        with PROFILER.scope("lin.gate_up"):
+            gu = gemm.linear(x, lw.gate_up)
         act = basic.silu_mul(gu)
-        return self._row_parallel(act, lw.down)
+        with PROFILER.scope("lin.down+ar.mlp"):
+            return self._row_parallel(act, lw.down)
 
     def _linear_attn(self, li: int, lw: LayerWeights, x: torch.Tensor, t: int, slots_t: torch.Tensor | None,
                      slot: int | None) -> torch.Tensor:
         cfg = self.cfg
-        proj = gemm.linear(x, lw.proj)                       # [T, 2kd + vd + vd]
+        with PROFILER.scope("lin.qkvz"):
+            proj = gemm.linear(x, lw.proj)                   # [T, 2kd + vd + vd]
         ab = gemm.linear(x, lw.ab)                           # [T, 2 hv]
         cw = 2 * self.kd + self.vd
         idx = self.lin_layers.index(li)
         g, beta = basic.gdn_gates(ab, 0, self.hv_lin, lw.a_log, lw.dt_bias, self.hv_lin)
         if slot is not None:   # one sequence, T consecutive tokens
             mixed = basic.conv_silu(proj[:, :cw], lw.conv_w, self.tails[slot, idx])
-            core = gdn.chunked(mixed, 0, self.kd, 2 * self.kd, g, beta, self.states[slot, idx], self.hv_lin, self.hk_lin)
+            with PROFILER.scope("gdn.chunked"):
+                core = gdn.chunked(mixed, 0, self.kd, 2 * self.kd, g, beta, self.states[slot, idx], self.hv_lin, self.hk_lin)
         else:                  # one token per sequence
             mixed = basic.conv_silu_step(proj[:, :cw], lw.conv_w, self.tails[:, idx], slots_t)
             core = gdn.step(self.states[:, idx], slots_t, mixed, 0, self.kd, 2 * self.kd, g, beta, self.hv_lin, self.hk_lin)
         z = proj[:, cw:].unflatten(1, (self.hv_lin, 128))
         y = basic.gated_rmsnorm(core, z, lw.gdn_norm, cfg.rms_norm_eps)
-        return self._row_parallel(y.view(t, self.vd), lw.out)
+        with PROFILER.scope("lin.out+ar.attn"):
+            return self._row_parallel(y.view(t, self.vd), lw.out)
 
     def _full_attn(self, li: int, lw: LayerWeights, x: torch.Tensor, t: int, positions, kv_slots, meta) -> torch.Tensor:
         cfg = self.cfg
@@ -523,8 +529,10 @@ class QwenHybridRuntime:
             proj, 0, 128 * gate_mul, cfg.attn_output_gate, proj, qw, proj, qw + self.hkv * 128, lw.q_norm, lw.k_norm,
             True, cfg.rms_norm_eps, self.inv_freq, cfg.rotary_dim, positions, kv_slots, kc, vc, self.hq, self.hkv)
         if meta["mode"] == "prefill":
-            o = attention.prefill(q, kc, vc, meta["block_table"], meta["q_start"], meta["q_len"], meta["kv_len"],
-                                  meta["max_q_len"], gate=gate, window=self.attention_window, sinks=self.attention_sinks)
+            with PROFILER.scope("full.attn_kernel"):
+                o = attention.prefill(q, kc, vc, meta["block_table"], meta["q_start"], meta["q_len"], meta["kv_len"],
+                                      meta["max_q_len"], gate=gate, window=self.attention_window,
+                                      sinks=self.attention_sinks)
         else:
             o = attention.decode(q, kc, vc, meta["block_table"], meta["kv_len"], gate=gate,
                                  max_kv_len=meta["max_kv_len"], window=self.attention_window, sinks=self.attention_sinks)

@@ -19,8 +19,11 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=8)
     ap.add_argument("--context", type=int, default=512)
     ap.add_argument("--prefill", type=int, default=0, help="profile one prefill of this many tokens instead of a decode step")
+    ap.add_argument("--phases", choices=["off", "range", "timed"], default="off",
+                    help="per-site phase profile of the prefill: NVTX ranges, or device-timed accumulators printed at the end")
     a = ap.parse_args()
     from ..models import qwen_hybrid as qh
+    from .phase_profile import PROFILER
     from ..ops import _lib
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -37,6 +40,7 @@ def main() -> None:
         torch.cuda.synchronize()
         s = rt.allocate()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        PROFILER.set_mode(a.phases)
         torch.cuda.cudart().cudaProfilerStart()
         e0.record()
         rt.prefill(s, p)
@@ -45,6 +49,9 @@ def main() -> None:
         torch.cuda.cudart().cudaProfilerStop()
         _lib.check_status()
         print(json.dumps({"prefill": a.prefill, "layers": a.layers, "ms": e0.elapsed_time(e1), "launches": rt.launches}))
+        if a.phases == "timed":
+            print(PROFILER.format())
+        PROFILER.set_mode("off")
         return
     slots, cur = [], []
     for _ in range(a.batch):
