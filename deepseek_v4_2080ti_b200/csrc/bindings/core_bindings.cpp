@@ -8,6 +8,8 @@
 #include <pybind11/stl.h>
 
 #include "core/batch_scheduler.hpp"
+#include "core/openai_server.hpp"
+#include "core/python_sidecar.hpp"
 #include "core/block_pool.hpp"
 #include "core/block_table.hpp"
 #include "core/cmd_channel.hpp"
@@ -294,6 +296,38 @@ PYBIND11_MODULE(pocketllm_cpp, m) {
     std::mt19937_64 rng(seed);
     return sample(logits.data(), static_cast<int>(logits.size()), p, rng, hist);
   }, py::arg("logits"), py::arg("params"), py::arg("seed") = 0, py::arg("history") = std::vector<int32_t>{});
+  py::class_<PythonSidecar>(m, "PythonSidecar")
+      .def(py::init<std::vector<std::string>, int>(), py::arg("argv"), py::arg("timeout_ms") = 30000)
+      .def("call", [](PythonSidecar& s, const std::string& request_json) {
+        std::string out;
+        { py::gil_scoped_release rel; out = s.call(Json::parse(request_json)).dump(); }
+        return out;
+      })
+      .def("ping", [](PythonSidecar& s) { py::gil_scoped_release rel; return s.ping(); })
+      .def("shutdown", [](PythonSidecar& s) { py::gil_scoped_release rel; s.shutdown(); })
+      .def_property_readonly("running", &PythonSidecar::running);
+
+  py::class_<OpenAIServerOptions>(m, "OpenAIServerOptions")
+      .def(py::init<>())
+      .def_readwrite("host", &OpenAIServerOptions::host)
+      .def_readwrite("port", &OpenAIServerOptions::port)
+      .def_readwrite("model_name", &OpenAIServerOptions::model_name)
+      .def_readwrite("chat_family", &OpenAIServerOptions::chat_family)
+      .def_readwrite("default_max_tokens", &OpenAIServerOptions::default_max_tokens)
+      .def_readwrite("sidecar_argv", &OpenAIServerOptions::sidecar_argv);
+  py::class_<OpenAIServer>(m, "OpenAIServer")
+      .def(py::init<InferenceEngine&, OpenAIServerOptions, SchedulerOptions>(), py::arg("engine"), py::arg("options"),
+           py::arg("scheduler_options") = SchedulerOptions(), py::keep_alive<1, 2>())
+      .def("start", [](OpenAIServer& s) { py::gil_scoped_release rel; s.start(); })
+      .def("stop", [](OpenAIServer& s) { py::gil_scoped_release rel; s.stop(); })
+      .def_property_readonly("port", &OpenAIServer::port)
+      .def_property_readonly("requests_served", &OpenAIServer::requests_served)
+      .def("handle", [](OpenAIServer& s, const std::string& method, const std::string& path, const std::string& body) {
+        OpenAIServer::Reply r;
+        { py::gil_scoped_release rel; r = s.handle(method, path, body); }
+        return py::make_tuple(r.status, r.content_type, r.body);
+      });
+
   m.def("parse_kv_cache_dtype", [](const std::string& s) {
     if (s == "auto" || s == "bf16" || s == "fp16") return 0;
     if (s == "fp8") return 1;

@@ -10,6 +10,10 @@
 //   --qwen-persistent-stdin    stay resident; each stdin line "<max_new_tokens> tok tok ..." is one request
 //   --serve-batch              read every stdin line as a request and run them through the continuous-batching
 //                              scheduler together (--max-slots sequences share the decode batch)
+//   --serve [--host H --port P] OpenAI-compatible HTTP server (/health, /v1/models, /v1/chat/completions, /v1/completions)
+//                              over the continuous-batching scheduler; text prompts go through the Python helper
+//                              (--python EXE, --sidecar-gguf FILE for its tokenizer, --chat-family NAME), token-id
+//                              requests need no helper
 //   --token-ids a,b,c | --token-ids-file F | --tokens N (synthetic ids)   the prompt
 //   --max-new-tokens N --max-context C --prefill-chunk-tokens T --smoke-layers L --max-slots S --device D
 //   --qwen-temperature F --qwen-top-k K --qwen-top-p P --qwen-seed S     host-side sampling (default greedy)
@@ -22,7 +26,11 @@
 #include <iostream>
 #include <sstream>
 
+#include <csignal>
+#include <unistd.h>
+
 #include "../core/batch_scheduler.hpp"
+#include "../core/openai_server.hpp"
 #include "../core/safetensors_reader.hpp"
 #include "qwen_engine.hpp"
 
@@ -31,7 +39,10 @@ using namespace pocket;
 namespace {
 
 struct Args {
-  std::string ckpt, grep, tensor, token_ids, token_file, eos;
+  std::string ckpt, grep, tensor, token_ids, token_file, eos, host = "127.0.0.1", python = "python", sidecar_gguf,
+      chat_family = "deepseek_v4", served_name = "pocketllm";
+  int port = 8000;
+  bool serve = false;
   bool dump_config = false, inspect = false, context_info = false, smoke = false, bench = false, persistent = false,
        serve_batch = false, json = false, verbose = false;
   int max_new = 16, chunk = 8192, layers = 0, device = 0, synthetic = 0, slots = 1, bench_runs = 3, topk_print = 0;
@@ -87,6 +98,13 @@ bool parse(int argc, char** argv, Args& a) {
     else if (arg == "--bench-runs") a.bench_runs = std::atoi(val("--bench-runs"));
     else if (arg == "--qwen-persistent-stdin") a.persistent = true;
     else if (arg == "--serve-batch") a.serve_batch = true;
+    else if (arg == "--serve") a.serve = true;
+    else if (arg == "--host") a.host = val("--host");
+    else if (arg == "--port") a.port = std::atoi(val("--port"));
+    else if (arg == "--python") a.python = val("--python");
+    else if (arg == "--sidecar-gguf" || arg == "--sidecar") a.sidecar_gguf = val("--sidecar-gguf");
+    else if (arg == "--chat-family") a.chat_family = val("--chat-family");
+    else if (arg == "--served-model-name") a.served_name = val("--served-model-name");
     else if (arg == "--token-ids" || arg == "--ids") a.token_ids = val("--token-ids");
     else if (arg == "--token-ids-file") a.token_file = val("--token-ids-file");
     else if (arg == "--tokens") a.synthetic = std::atoi(val("--tokens"));
@@ -230,6 +248,31 @@ int main(int argc, char** argv) {
           std::fflush(stdout);
         }
       }
+      return 0;
+    }
+
+    if (a.serve) {
+      OpenAIServerOptions so;
+      so.host = a.host;
+      so.port = a.port;
+      so.model_name = a.served_name;
+      so.chat_family = a.chat_family;
+      so.default_max_tokens = a.max_new;
+      if (!a.sidecar_gguf.empty()) so.sidecar_argv = {a.python, "-m", "pocketllm.sidecar", "--gguf", a.sidecar_gguf};
+      SchedulerOptions sched;
+      sched.max_batch = opt.max_slots;
+      sched.prefill_chunk_tokens = opt.prefill_chunk;
+      sched.prefill_token_budget = opt.prefill_chunk;
+      OpenAIServer server(eng, so, sched);
+      server.start();
+      std::printf("pocketllm_engine_serving=1 host=%s port=%d model=%s\n", a.host.c_str(), server.port(), a.served_name.c_str());
+      std::fflush(stdout);
+      static volatile std::sig_atomic_t stop_flag = 0;
+      std::signal(SIGINT, [](int) { stop_flag = 1; });
+      std::signal(SIGTERM, [](int) { stop_flag = 1; });
+      while (!stop_flag) ::usleep(100000);
+      server.stop();
+      std::printf("pocketllm_engine_stopped=1 requests=%llu\n", (unsigned long long)server.requests_served());
       return 0;
     }
 

@@ -6,6 +6,7 @@ line on stdin, answers one line on stdout.
      "reasoning_effort": null}                                  -> {"ok": true, "prompt": "...", "token_ids": [...]?}
     {"op": "parse", "family": "deepseek_v4", "text": "...", "thinking": false}
                                                                 -> {"ok": true, "message": {...}}
+    {"op": "decode", "family": "...", "token_ids": [...]}       -> {"ok": true, "text": "...", "message": {...}?}
     {"op": "shutdown"}                                          -> {"ok": true} and exit
 
 ``token_ids`` are returned when a tokenizer was given (``--gguf`` with embedded BPE vocabulary).  Errors come back as
@@ -38,6 +39,14 @@ def handle(req: dict, tokenizer=None) -> dict:
         out = {"ok": True, "prompt": prompt}
         if tokenizer is not None:
             out["token_ids"] = tokenizer.encode(prompt)
+        return out
+    if op == "decode":
+        if tokenizer is None:
+            return {"ok": False, "error": "no tokenizer: start the sidecar with --gguf"}
+        text = tokenizer.decode([int(t) for t in req.get("token_ids", [])])
+        out = {"ok": True, "text": text}
+        if hasattr(enc, "parse_completion"):
+            out["message"] = enc.parse_completion(text, thinking=bool(req.get("thinking", False)))
         return out
     if op == "parse":
         if not hasattr(enc, "parse_completion"):
