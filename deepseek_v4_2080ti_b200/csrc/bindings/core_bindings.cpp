@@ -16,6 +16,7 @@
 #include "core/gguf_reader.hpp"
 #include "core/json_lite.hpp"
 #include "core/qwen_config.hpp"
+#include "core/qwen_weight_map.hpp"
 #include "core/safetensors_reader.hpp"
 #include "core/sampler.hpp"
 #include "core/tokenizer.hpp"
@@ -327,6 +328,26 @@ PYBIND11_MODULE(pocketllm_cpp, m) {
         { py::gil_scoped_release rel; r = s.handle(method, path, body); }
         return py::make_tuple(r.status, r.content_type, r.body);
       });
+
+  m.def("qwen_expected_tensors", [](const QwenConfig& cfg) {
+    py::list out;
+    for (const QwenTensorSpec& s : qwen_expected_tensors(cfg)) {
+      py::dict d;
+      d["name"] = s.name; d["shape"] = s.shape; d["dtype"] = s.dtype; d["rule"] = to_string(s.rule); d["group"] = s.group;
+      out.append(d);
+    }
+    return out;
+  });
+  m.def("qwen_audit", [](const std::string& dir, int tp_world) {
+    SafetensorsModel model(dir);
+    const QwenConfig cfg = QwenConfig::from_file(dir + "/config.json");
+    const QwenAuditReport r = qwen_audit(model, cfg, tp_world);
+    py::dict d;
+    d["expected"] = r.expected; d["found"] = r.found; d["bytes"] = r.bytes; d["missing"] = r.missing;
+    d["unexpected"] = r.unexpected; d["wrong_shape"] = r.wrong_shape; d["wrong_dtype"] = r.wrong_dtype;
+    d["not_divisible"] = r.not_divisible; d["ok"] = r.ok(false); d["ok_strict"] = r.ok(true);
+    return d;
+  }, py::arg("checkpoint"), py::arg("tp_world") = 1);
 
   m.def("parse_kv_cache_dtype", [](const std::string& s) {
     if (s == "auto" || s == "bf16" || s == "fp16") return 0;

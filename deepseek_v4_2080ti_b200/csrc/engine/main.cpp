@@ -4,6 +4,8 @@
 //   --dump-config              print the parsed model configuration and exit
 //   --inspect [--grep S]       list checkpoint tensors (name, dtype, shape, bytes)
 //   --inspect-tensor NAME      print one tensor's header and its first values
+//   --qwen-audit [--qwen-audit-strict] [--tp-world N]   check the checkpoint against the weight map (no GPU needed):
+//                              missing / unexpected tensors, shapes, dtypes, tensor-parallel divisibility
 //   --context-info             bytes of KV cache / recurrent state per token and per slot
 //   --smoke-forward            run the prompt, generate --max-new-tokens tokens, print tokens and timings
 //   --resident-bench           load once, then time --bench-runs generations of the same prompt
@@ -31,6 +33,7 @@
 
 #include "../core/batch_scheduler.hpp"
 #include "../core/openai_server.hpp"
+#include "../core/qwen_weight_map.hpp"
 #include "../core/safetensors_reader.hpp"
 #include "qwen_engine.hpp"
 
@@ -41,8 +44,8 @@ namespace {
 struct Args {
   std::string ckpt, grep, tensor, token_ids, token_file, eos, host = "127.0.0.1", python = "python", sidecar_gguf,
       chat_family = "deepseek_v4", served_name = "pocketllm";
-  int port = 8000;
-  bool serve = false;
+  int port = 8000, tp_world = 1;
+  bool serve = false, audit = false, audit_strict = false;
   bool dump_config = false, inspect = false, context_info = false, smoke = false, bench = false, persistent = false,
        serve_batch = false, json = false, verbose = false;
   int max_new = 16, chunk = 8192, layers = 0, device = 0, synthetic = 0, slots = 1, bench_runs = 3, topk_print = 0;
@@ -99,6 +102,9 @@ bool parse(int argc, char** argv, Args& a) {
     else if (arg == "--qwen-persistent-stdin") a.persistent = true;
     else if (arg == "--serve-batch") a.serve_batch = true;
     else if (arg == "--serve") a.serve = true;
+    else if (arg == "--qwen-audit") a.audit = true;
+    else if (arg == "--qwen-audit-strict") a.audit = a.audit_strict = true;
+    else if (arg == "--tp-world") a.tp_world = std::atoi(val("--tp-world"));
     else if (arg == "--host") a.host = val("--host");
     else if (arg == "--port") a.port = std::atoi(val("--port"));
     else if (arg == "--python") a.python = val("--python");
@@ -188,6 +194,19 @@ int main(int argc, char** argv) {
                   (long long)cfg.linear_num_value_heads, (long long)cfg.linear_conv_kernel_dim, cfg.quant_method.c_str(),
                   (long long)cfg.quant_block);
       return 0;
+    }
+    if (a.audit) {
+      SafetensorsModel model(a.ckpt);
+      const QwenAuditReport r = qwen_audit(model, cfg, a.tp_world);
+      auto dump = [](const char* what, const std::vector<std::string>& v) {
+        for (const auto& n : v) std::printf("qwen_audit_%s=%s\n", what, n.c_str());
+      };
+      dump("missing", r.missing); dump("unexpected", r.unexpected); dump("wrong_shape", r.wrong_shape);
+      dump("wrong_dtype", r.wrong_dtype); dump("not_divisible", r.not_divisible);
+      std::printf("qwen_audit=1 ok=%d expected=%zu found=%zu bytes=%llu tp_world=%d missing=%zu unexpected=%zu\n",
+                  int(r.ok(a.audit_strict)), r.expected, r.found, (unsigned long long)r.bytes, a.tp_world, r.missing.size(),
+                  r.unexpected.size());
+      return r.ok(a.audit_strict) ? 0 : 3;
     }
     if (a.context_info) {
       const long long kv_token = 2LL * cfg.num_full_layers() * cfg.num_key_value_heads * cfg.head_dim * 2;

@@ -47,6 +47,43 @@ def test_dump_config_inspect_and_context_info_need_no_gpu():
 
 
 @needs_exe
+def test_weight_map_audit_finds_missing_misshaped_and_indivisible_tensors():
+    from deepseek_v4_2080ti_b200 import pocketllm_cpp as core
+    from deepseek_v4_2080ti_b200.formats import safetensors_io
+    from deepseek_v4_2080ti_b200.models import qwen_hybrid as qh
+    with tempfile.TemporaryDirectory() as d:
+        cfg, state = _write_tiny(d)
+        rep = core.qwen_audit(d, 1)
+        assert rep["ok"] and rep["ok_strict"], rep
+        assert rep["found"] == len(state) and rep["bytes"] > 0
+        specs = {s["name"]: s for s in core.qwen_expected_tensors(core.QwenConfig.from_file(os.path.join(d, "config.json")))}
+        assert set(specs) >= {n for n, _ in state}
+        assert specs["model.language_model.layers.0.mlp.down_proj.weight"]["rule"] == "row_parallel"
+        r = _run(["--ckpt", d, "--qwen-audit"])
+        assert r.returncode == 0 and "qwen_audit=1 ok=1" in r.stdout, (r.stdout[-400:], r.stderr[-400:])
+        # two ranks would split the 384-wide MLP inside a 128-row scale block (the loader refuses the same shard);
+        # the attention and DeltaNet projections divide cleanly
+        rep2 = core.qwen_audit(d, 2)
+        assert not rep2["ok"] and all(".mlp." in n for n in rep2["not_divisible"]), rep2["not_divisible"]
+        r = _run(["--ckpt", d, "--qwen-audit", "--tp-world", "3"])
+        assert r.returncode == 3 and "qwen_audit_not_divisible=" in r.stdout and "self_attn" in r.stdout
+    with tempfile.TemporaryDirectory() as d:
+        cfg = qh.QwenHybridConfig.tiny(layers=4)
+        state = list(qh.synth_state(cfg, 0, "cpu", std=0.05))
+        victim = "model.language_model.layers.1.mlp.up_proj.weight"
+        bad = [(n, t) for n, t in state if n != victim]
+        bad = [(n, t[:-1] if n.endswith("layers.0.input_layernorm.weight") else t) for n, t in bad]
+        bad.append(("model.language_model.layers.0.extra.bias", torch.zeros(4, dtype=torch.bfloat16)))
+        safetensors_io.write_checkpoint(d, iter(bad), config_json=cfg.to_json())
+        rep = core.qwen_audit(d, 1)
+        assert rep["missing"] == [victim] and not rep["ok"]
+        assert rep["wrong_shape"] == ["model.language_model.layers.0.input_layernorm.weight"]
+        assert rep["unexpected"] == ["model.language_model.layers.0.extra.bias"]
+        r = _run(["--ckpt", d, "--qwen-audit"])
+        assert r.returncode == 3 and f"qwen_audit_missing={victim}" in r.stdout
+
+
+@needs_exe
 def test_bad_arguments_exit_non_zero():
     assert _run(["--nonsense"]).returncode != 0
     assert _run([]).returncode == 2
