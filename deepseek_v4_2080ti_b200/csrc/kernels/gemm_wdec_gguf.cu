@@ -1,4 +1,4 @@
-// Entry points of the weight-decoding GEMM for GGUF block-quantised weights (Q8_0, Q4_K, Q5_K, Q2_K, IQ1_M, IQ2_XXS, IQ3_XXS): the raw
+// Entry points of the weight-decoding GEMM for GGUF block-quantised weights (Q8_0, Q4_K, Q5_K, Q6_K, Q3_K, Q2_K, IQ1_M, IQ2_XXS, IQ2_XS, IQ3_XXS, IQ4_XS): the raw
 // blocks are decoded in registers by the decode warps of gemm_wdec_kernel.cuh into bf16 tensor-core tiles; no
 // dequantised copy of a weight matrix ever exists in memory.
 // Reference behaviour covered: the fused dequant GEMV / GEMM family for GGUF tensors
@@ -35,6 +35,10 @@ bool bn256_ok(int wfmt) {
     case WF_Q5_K: return SmemLayout<256, WF_Q5_K>::SR >= SmemLayout<256, WF_Q5_K>::GROUPS;
     case WF_IQ3_XXS: return SmemLayout<256, WF_IQ3_XXS>::SR >= SmemLayout<256, WF_IQ3_XXS>::GROUPS;
     case WF_IQ1_M: return SmemLayout<256, WF_IQ1_M>::SR >= SmemLayout<256, WF_IQ1_M>::GROUPS;
+    case WF_Q6_K: return SmemLayout<256, WF_Q6_K>::SR >= SmemLayout<256, WF_Q6_K>::GROUPS;
+    case WF_Q3_K: return SmemLayout<256, WF_Q3_K>::SR >= SmemLayout<256, WF_Q3_K>::GROUPS;
+    case WF_IQ4_XS: return SmemLayout<256, WF_IQ4_XS>::SR >= SmemLayout<256, WF_IQ4_XS>::GROUPS;
+    case WF_IQ2_XS: return SmemLayout<256, WF_IQ2_XS>::SR >= SmemLayout<256, WF_IQ2_XS>::GROUPS;
   }
   return false;
 }
@@ -48,6 +52,10 @@ int dispatch(int wfmt, int bn, const CUtensorMap& tmX, const GemmParams& p, cuda
     case WF_Q5_K: return dispatch_bn<WF_Q5_K>(bn, tmX, p, stream);
     case WF_IQ3_XXS: return dispatch_bn<WF_IQ3_XXS>(bn, tmX, p, stream);
     case WF_IQ1_M: return dispatch_bn<WF_IQ1_M>(bn, tmX, p, stream);
+    case WF_Q6_K: return dispatch_bn<WF_Q6_K>(bn, tmX, p, stream);
+    case WF_Q3_K: return dispatch_bn<WF_Q3_K>(bn, tmX, p, stream);
+    case WF_IQ4_XS: return dispatch_bn<WF_IQ4_XS>(bn, tmX, p, stream);
+    case WF_IQ2_XS: return dispatch_bn<WF_IQ2_XS>(bn, tmX, p, stream);
   }
   return -ERR_BAD_ARG;
 }
@@ -55,7 +63,7 @@ int dispatch(int wfmt, int bn, const CUtensorMap& tmX, const GemmParams& p, cuda
 bool fill(GemmParams& p, int wfmt, const void* W, const void* lut, void* out_bf16, float* out_f32, const void* residual,
           int T, int N, int K, int* status) {
   if (T <= 0 || N <= 0 || K <= 0 || (K % 64) != 0 || gguf_qb(wfmt) == 0) return false;
-  if ((wfmt == WF_IQ2_XXS || wfmt == WF_IQ3_XXS || wfmt == WF_IQ1_M) && !lut) return false;
+  if ((wfmt == WF_IQ2_XXS || wfmt == WF_IQ3_XXS || wfmt == WF_IQ1_M || wfmt == WF_IQ4_XS || wfmt == WF_IQ2_XS) && !lut) return false;
   memset(&p, 0, sizeof(p));
   p.T = T; p.N = N; p.K = K;
   p.m_tiles = (N + BM - 1) / BM;

@@ -56,18 +56,28 @@ constexpr int NUM_THREADS = (DEC_WARP0 + NUM_DEC_WARPS) * 32;  // 448
 //   WF_IQ3_XXS  QB 24 (16 grid indices, then the two sign/scale words of the stage's 32-input groups), SB 4: d (fp16)
 //   WF_IQ1_M    QB 12 (8 low index bytes, then 4 bytes of high index bits / delta signs), SB 4: d (fp16), one byte per
 //               32-input group holding its two 3-bit scales
+//   WF_Q6_K     QB 48 (Q4_K-style nibbles, then per half a 64-bit word with the two high bits of input l at bits 2l),
+//               SB 8: d (fp16), 2 pad bytes, four int8 scales (one per 16 inputs)
+//   WF_Q3_K     QB 24 (per half a 64-bit word of 2-bit codes, then per half a 32-bit mask of the third bit),
+//               SB 8: d (fp16), 2 pad bytes, four signed 6-bit scales (already minus 32) as int8
+//   WF_IQ4_XS   QB 32 (the stage's two original 16-byte sub-blocks: low nibble = input l, high = input 16 + l),
+//               SB 4: d (fp16), two int8 scales (already minus 32); 16-entry int8 value table
+//   WF_IQ2_XS   QB 16 (eight original 16-bit codes: 9-bit grid index | 7-bit sign index << 9), SB 4: d (fp16), the two
+//               scale bytes (4 bits per 16 inputs); 512 x 8 magnitude grid + 128 sign bytes
 enum WFormat : int {
   WF_BF16 = 0, WF_FP8_B128 = 1, WF_FP4 = 2, WF_Q8_0 = 3, WF_Q4_K = 4, WF_Q2_K = 5, WF_IQ2_XXS = 6, WF_Q5_K = 7,
-  WF_IQ3_XXS = 8, WF_IQ1_M = 9
+  WF_IQ3_XXS = 8, WF_IQ1_M = 9, WF_Q6_K = 10, WF_Q3_K = 11, WF_IQ4_XS = 12, WF_IQ2_XS = 13
 };
 
 __host__ __device__ constexpr int gguf_qb(int wfmt) {
   return wfmt == WF_Q8_0 ? 64 : wfmt == WF_Q4_K ? 32 : wfmt == WF_Q2_K ? 16 : wfmt == WF_IQ2_XXS ? 16
-         : wfmt == WF_Q5_K ? 40 : wfmt == WF_IQ3_XXS ? 24 : wfmt == WF_IQ1_M ? 12 : 0;
+         : wfmt == WF_Q5_K ? 40 : wfmt == WF_IQ3_XXS ? 24 : wfmt == WF_IQ1_M ? 12 : wfmt == WF_Q6_K ? 48
+         : wfmt == WF_Q3_K ? 24 : wfmt == WF_IQ4_XS ? 32 : wfmt == WF_IQ2_XS ? 16 : 0;
 }
 __host__ __device__ constexpr int gguf_sb(int wfmt) {
   return wfmt == WF_Q8_0 ? 4 : wfmt == WF_Q4_K ? 8 : wfmt == WF_Q2_K ? 8 : wfmt == WF_IQ2_XXS ? 4
-         : wfmt == WF_Q5_K ? 8 : wfmt == WF_IQ3_XXS ? 4 : wfmt == WF_IQ1_M ? 4 : 0;
+         : wfmt == WF_Q5_K ? 8 : wfmt == WF_IQ3_XXS ? 4 : wfmt == WF_IQ1_M ? 4 : wfmt == WF_Q6_K ? 8 : wfmt == WF_Q3_K ? 8
+         : wfmt == WF_IQ4_XS ? 4 : wfmt == WF_IQ2_XS ? 4 : 0;
 }
 __host__ __device__ constexpr int raw_stage_bytes(int wfmt) {
   return wfmt == WF_FP8_B128 ? 128 * 64
@@ -531,6 +541,57 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
                   for (int e = 0; e < 8; ++e) {
                     const int gv = (int)(int8_t)(((e < 4 ? gr.x : gr.y) >> (8 * (e & 3))) & 0xFF);
                     v[g * 8 + e] = dl * ((float)gv + delta);
+                  }
+                }
+              } else if constexpr (WFMT == WF_Q6_K) {
+                const float dd = __half2float(*reinterpret_cast<const __half*>(srow));
+                const float s0 = dd * (float)(int8_t)srow[4 + 2 * hh], s1 = dd * (float)(int8_t)srow[5 + 2 * hh];
+                const int4 a = *reinterpret_cast<const int4*>(qrow), b = *reinterpret_cast<const int4*>(qrow + 16);
+                const int w8[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+                const uint2 hb = *reinterpret_cast<const uint2*>(qrow + 32 + 8 * hh);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                  const int by = (w8[e >> 2] >> (8 * (e & 3))) & 0xFF;
+                  const int hi = ((e < 16 ? hb.x : hb.y) >> (2 * (e & 15))) & 3;
+                  const int q6 = (hh ? (by >> 4) : (by & 15)) | (hi << 4);
+                  v[e] = (e < 16 ? s0 : s1) * (float)(q6 - 32);
+                }
+              } else if constexpr (WFMT == WF_Q3_K) {
+                const float dd = __half2float(*reinterpret_cast<const __half*>(srow));
+                const float s0 = dd * (float)(int8_t)srow[4 + 2 * hh], s1 = dd * (float)(int8_t)srow[5 + 2 * hh];
+                const uint2 lo = *reinterpret_cast<const uint2*>(qrow + 8 * hh);
+                const uint32_t hm = *reinterpret_cast<const uint32_t*>(qrow + 16 + 4 * hh);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                  const int q = (int)(((e < 16 ? lo.x : lo.y) >> (2 * (e & 15))) & 3) - (((hm >> e) & 1) ? 0 : 4);
+                  v[e] = (e < 16 ? s0 : s1) * (float)q;
+                }
+              } else if constexpr (WFMT == WF_IQ4_XS) {
+                const float dl = __half2float(*reinterpret_cast<const __half*>(srow)) * (float)(int8_t)srow[2 + hh];
+                const int4 a = *reinterpret_cast<const int4*>(qrow + 16 * hh);
+                const int w4[4] = {a.x, a.y, a.z, a.w};
+                const uint2 kv0 = __ldg(reinterpret_cast<const uint2*>(p.lut)), kv1 = __ldg(reinterpret_cast<const uint2*>(p.lut) + 1);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                  const int by = (w4[(e & 15) >> 2] >> (8 * (e & 3))) & 0xFF;
+                  const int nib = e < 16 ? (by & 15) : (by >> 4);
+                  const uint32_t word = (nib & 8) ? ((nib & 4) ? kv1.y : kv1.x) : ((nib & 4) ? kv0.y : kv0.x);
+                  v[e] = dl * (float)(int8_t)((word >> (8 * (nib & 3))) & 0xFF);
+                }
+              } else if constexpr (WFMT == WF_IQ2_XS) {
+                const float dd = __half2float(*reinterpret_cast<const __half*>(srow)) * 0.25f;
+                const uint2 qw = *reinterpret_cast<const uint2*>(qrow + hh * 8);
+                const uint32_t sby = srow[2 + hh];
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  const uint32_t code = ((g < 2 ? qw.x : qw.y) >> (16 * (g & 1))) & 0xFFFF;
+                  const float db = dd * (0.5f + (float)((sby >> (4 * (g >> 1))) & 0xF));
+                  const uint2 gr = __ldg(reinterpret_cast<const uint2*>(p.lut) + (code & 511));
+                  const uint32_t sg = __ldg(p.lut + 4096 + (code >> 9));
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    const uint32_t gv = ((e < 4 ? gr.x : gr.y) >> (8 * (e & 3))) & 0xFF;
+                    v[g * 8 + e] = ((sg >> e) & 1) ? -db * (float)gv : db * (float)gv;
                   }
                 }
               } else if constexpr (WFMT == WF_IQ2_XXS) {

@@ -12,7 +12,8 @@ from typing import Any, Callable
 from ..formats.gguf import BLOCK_BYTES, BLOCK_ELEMS, GGMLType
 
 # GGUF types the tensor-core GEMM decodes in registers, and plain types every loader reads
-GEMM_DECODED = {GGMLType.Q8_0, GGMLType.Q4_K, GGMLType.Q5_K, GGMLType.Q2_K, GGMLType.IQ1_M, GGMLType.IQ2_XXS, GGMLType.IQ3_XXS}
+GEMM_DECODED = {GGMLType.Q8_0, GGMLType.Q4_K, GGMLType.Q5_K, GGMLType.Q6_K, GGMLType.Q3_K, GGMLType.Q2_K, GGMLType.IQ1_M,
+                GGMLType.IQ2_XXS, GGMLType.IQ2_XS, GGMLType.IQ3_XXS, GGMLType.IQ4_XS}
 PLAIN = {GGMLType.F32, GGMLType.F16, GGMLType.BF16}
 
 

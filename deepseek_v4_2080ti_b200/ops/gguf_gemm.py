@@ -2,7 +2,8 @@
 
 The raw GGUF blocks are only *regrouped* at load time so that every pipeline stage of the GEMM (128 output rows x 64
 inputs) is one contiguous block ``[128 x quant bytes | 128 x scale bytes]``; the quantised codes stay as they are and
-are decoded in registers inside the kernel.  Supported: Q8_0, Q4_K, Q5_K, Q2_K, IQ1_M, IQ2_XXS, IQ3_XXS."""
+are decoded in registers inside the kernel.  Supported: Q8_0, Q4_K, Q5_K, Q6_K, Q3_K, Q2_K, IQ1_M, IQ2_XXS, IQ2_XS,
+IQ3_XXS, IQ4_XS."""
 from __future__ import annotations
 
 import ctypes
@@ -15,7 +16,8 @@ from ..formats.gguf.quant import _unpack_scale_min_6bit, tables
 from . import _lib
 
 WF = {GGMLType.Q8_0: 3, GGMLType.Q4_K: 4, GGMLType.Q2_K: 5, GGMLType.IQ2_XXS: 6, GGMLType.Q5_K: 7, GGMLType.IQ3_XXS: 8,
-      GGMLType.IQ1_M: 9}
+      GGMLType.IQ1_M: 9, GGMLType.Q6_K: 10, GGMLType.Q3_K: 11, GGMLType.IQ4_XS: 12, GGMLType.IQ2_XS: 13}
+_LUT_TYPES = (GGMLType.IQ2_XXS, GGMLType.IQ3_XXS, GGMLType.IQ1_M, GGMLType.IQ4_XS, GGMLType.IQ2_XS)
 _lut: dict[tuple, torch.Tensor] = {}
 
 
@@ -26,9 +28,10 @@ def codebook(device) -> torch.Tensor:
 
 def lut_for(t, device) -> torch.Tensor | None:
     """Codebook table a format's in-register decode reads (None when it needs none): IQ2_XXS 256 x 8 magnitudes +
-    128 sign bytes; IQ3_XXS 256 x 4 magnitudes + 128 sign bytes; IQ1_M 2048 x 8 int8 grid values."""
+    128 sign bytes; IQ3_XXS 256 x 4 magnitudes + 128 sign bytes; IQ1_M 2048 x 8 int8 grid values; IQ4_XS the 16 int8
+    code values; IQ2_XS 512 x 8 magnitudes + 128 sign bytes."""
     t = GGMLType(t)
-    if t not in (GGMLType.IQ2_XXS, GGMLType.IQ3_XXS, GGMLType.IQ1_M):
+    if t not in _LUT_TYPES:
         return None
     key = (t, torch.device(device).index or 0)
     if key not in _lut:
@@ -37,6 +40,10 @@ def lut_for(t, device) -> torch.Tensor | None:
             v = torch.cat([tb["iq2xxs"].to(torch.uint8).reshape(-1), tb["ksigns"]])
         elif t == GGMLType.IQ3_XXS:
             v = torch.cat([tb["iq3xxs"].to(torch.uint8).reshape(-1), tb["ksigns"]])
+        elif t == GGMLType.IQ4_XS:
+            v = tb["iq4nl"].to(torch.int8).reshape(-1).view(torch.uint8)
+        elif t == GGMLType.IQ2_XS:
+            v = torch.cat([tb["iq2xs"].to(torch.uint8).reshape(-1), tb["ksigns"]])
         else:
             v = tb["iq1"].to(torch.int8).reshape(-1).view(torch.uint8)
         _lut[key] = v.contiguous().to(device)
@@ -120,6 +127,52 @@ def prepack(raw: torch.Tensor, t: GGMLType, k: int) -> torch.Tensor:
         q = torch.cat([b[:, :, 0:32].reshape(n, nb, 4, 8), b[:, :, 32:48].reshape(n, nb, 4, 4)], -1).reshape(n, nb * 4, 12)
         s = torch.cat([dby[:, :, None, :].expand(n, nb, 4, 2), pair], -1).reshape(n, nb * 4, 4)
         return _tile(q.contiguous(), s.contiguous())
+    if t == GGMLType.Q6_K:
+        b = raw.view(n, nb, 210)
+        ql = b[:, :, 0:128].view(n, nb, 2, 2, 32)                           # [half, which 32 bytes, l]
+        lo = torch.stack([ql & 0xF, ql >> 4], 3)                            # [n, nb, half, p, which, l]: stage = 2 half + p
+        nib = (lo[..., 0, :] | (lo[..., 1, :] << 4)).reshape(n, nb * 4, 32)
+        qh = b[:, :, 128:192].view(n, nb, 2, 1, 32).to(torch.int64)
+        sh = torch.arange(4, device=raw.device).view(1, 1, 1, 4, 1) * 2
+        hi = ((qh >> sh) & 3).reshape(n, nb * 4, 2, 32)                     # [stage, half of stage, l] (g = 2 p + hh)
+        hw = (hi << (2 * torch.arange(32, device=raw.device))).sum(-1)      # 64-bit word per (stage, hh)
+        hb = torch.stack([(hw >> (8 * i)) & 0xFF for i in range(8)], -1).to(torch.uint8).reshape(n, nb * 4, 16)
+        q = torch.cat([nib, hb], -1)
+        dd = torch.cat([b[:, :, 208:210], b.new_zeros(n, nb, 2)], -1)[:, :, None, :].expand(n, nb, 4, 4)
+        s = torch.cat([dd, b[:, :, 192:208].view(n, nb, 4, 4)], -1).reshape(n, nb * 4, 8)
+        return _tile(q.contiguous(), s.contiguous())
+    if t == GGMLType.Q3_K:
+        b = raw.view(n, nb, 110)
+        qs = b[:, :, 32:96].view(n, nb, 2, 1, 32).to(torch.int64)
+        sh = torch.arange(4, device=raw.device).view(1, 1, 1, 4, 1) * 2
+        lo = ((qs >> sh) & 3).reshape(n, nb * 4, 2, 32)                     # element 128 half + 32 s + l -> stage 2 half + s / 2
+        lw = (lo << (2 * torch.arange(32, device=raw.device))).sum(-1)
+        lb = torch.stack([(lw >> (8 * i)) & 0xFF for i in range(8)], -1).to(torch.uint8).reshape(n, nb * 4, 16)
+        hm = b[:, :, 0:32].to(torch.int64)                                  # bit j of byte l = third bit of element 32 j + l
+        masks = torch.stack([(((hm >> j) & 1) << torch.arange(32, device=raw.device)).sum(-1) for j in range(8)], -1)
+        mb = torch.stack([(masks >> (8 * i)) & 0xFF for i in range(4)], -1).to(torch.uint8).reshape(n, nb * 4, 8)
+        q = torch.cat([lb, mb], -1)
+        sc = b[:, :, 96:108].to(torch.int64)
+        lsc = torch.stack([sc[..., :8] & 0xF, sc[..., :8] >> 4], 2).reshape(n, nb, 16)
+        hsc = torch.stack([(sc[..., 8:12] >> (2 * j)) & 3 for j in range(4)], 2).reshape(n, nb, 16)
+        s6 = ((lsc | (hsc << 4)) - 32).to(torch.int8).view(torch.uint8).view(n, nb, 4, 4)
+        dd = torch.cat([b[:, :, 108:110], b.new_zeros(n, nb, 2)], -1)[:, :, None, :].expand(n, nb, 4, 4)
+        s = torch.cat([dd, s6], -1).reshape(n, nb * 4, 8)
+        return _tile(q.contiguous(), s.contiguous())
+    if t == GGMLType.IQ4_XS:
+        b = raw.view(n, nb, 136)
+        sh = b[:, :, 2].to(torch.int64) | (b[:, :, 3].to(torch.int64) << 8)
+        slb = b[:, :, 4:8].to(torch.int64)
+        sl = torch.stack([slb & 0xF, slb >> 4], -1).reshape(n, nb, 8)
+        s6 = (sl | (torch.stack([(sh >> (2 * i)) & 3 for i in range(8)], -1) << 4)) - 32
+        q = b[:, :, 8:136].reshape(n, nb * 4, 32)
+        s = torch.cat([b[:, :, None, 0:2].expand(n, nb, 4, 2), s6.to(torch.int8).view(torch.uint8).view(n, nb, 4, 2)], -1)
+        return _tile(q, s.reshape(n, nb * 4, 4).contiguous())
+    if t == GGMLType.IQ2_XS:
+        b = raw.view(n, nb, 74)
+        q = b[:, :, 2:66].reshape(n, nb * 4, 16)
+        s = torch.cat([b[:, :, None, 0:2].expand(n, nb, 4, 2), b[:, :, 66:74].view(n, nb, 4, 2)], -1).reshape(n, nb * 4, 4)
+        return _tile(q, s.contiguous())
     raise ValueError(f"{t.name} has no tensor-core decode path yet")
 
 

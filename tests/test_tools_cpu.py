@@ -78,7 +78,7 @@ def test_registry_validates_reports_capability_and_plans_placement(capsys):
         small = spec.placement(rep, registry.HardwareProfile(1, 0.0001))
         assert small[0].status == "rejected" and small[1].name == "layer_pipeline"
         assert registry.capability_status(G.GGMLType.IQ1_M)[0] == "supported"
-        assert registry.capability_status(G.GGMLType.Q6_K)[0] == "deferred"
+        assert registry.capability_status(G.GGMLType.Q6_K)[0] == "supported"
         from deepseek_v4_2080ti_b200.cli import inspect_gguf, make_routed_source_gguf
         assert inspect_gguf.main([path, "--validate", "--placement", "--json"]) == 0
         out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
