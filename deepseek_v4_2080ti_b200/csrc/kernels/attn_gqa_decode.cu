@@ -9,6 +9,7 @@
 // (gqa_decode_split_f16 :1648, gqa_decode_merge_f16 :2457) and the paged KV
 // gather of qwen_half_ops.cu:2798 (here the kernel reads the block table itself).
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <stdint.h>
 #include "ops.h"
 #include "launch.h"
@@ -31,9 +32,29 @@ struct DecodeParams {
   int max_blocks, bs, Hq, Hkv, splits;
   float scale_log2;
   int window, sinks;             // window > 0: only the first `sinks` and the last `window` keys are visible
+  // KV 1 / 2: the caches hold E4M3 / INT8 bytes (same [num_blocks, Hkv, bs, D] layout) with one fp32 scale per
+  // (block, head, row)
+  const float* k_scale;
+  const float* v_scale;
 };
 
-template <int G>
+__device__ __forceinline__ void e4m3x8_to_float(const uint2 u, float (&f)[8]) {
+  const uint32_t w[2] = {u.x, u.y};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2_raw r = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)((w[i >> 1] >> (16 * (i & 1))) & 0xFFFF), __NV_E4M3);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&r));
+    f[2 * i] = a.x;
+    f[2 * i + 1] = a.y;
+  }
+}
+
+__device__ __forceinline__ void int8x8_to_float(const uint2 u, float (&f)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = (float)(int8_t)(((i < 4 ? u.x : u.y) >> (8 * (i & 3))) & 0xFF);
+}
+
+template <int G, int KV>
 __global__ void __launch_bounds__(THREADS)
 gqa_decode_kernel(DecodeParams p) {
   __shared__ float s_m[NSTATE][G], s_l[NSTATE][G];
@@ -77,10 +98,25 @@ gqa_decode_kernel(DecodeParams p) {
     if (windowed && kc >= p.sinks) kc += win_shift;
     const int blk = bt[kc / p.bs];
     const size_t row = ((size_t)(blk * p.Hkv + kvh) * p.bs + (kc % p.bs)) * D + dl * 8;
-    const uint4 ku = *reinterpret_cast<const uint4*>(p.k_cache + row);
-    const uint4 vu = *reinterpret_cast<const uint4*>(p.v_cache + row);
     float kf[8], vf[8];
-    {
+    float ks = 1.f;
+    if constexpr (KV != 0) {
+      const uint2 ku = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(p.k_cache) + row);
+      const uint2 vu = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(p.v_cache) + row);
+      ks = p.k_scale[row >> 7];
+      const float vs = p.v_scale[row >> 7];
+      if constexpr (KV == 1) {
+        e4m3x8_to_float(ku, kf);
+        e4m3x8_to_float(vu, vf);
+      } else {
+        int8x8_to_float(ku, kf);
+        int8x8_to_float(vu, vf);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) vf[i] *= vs;
+    } else {
+      const uint4 ku = *reinterpret_cast<const uint4*>(p.k_cache + row);
+      const uint4 vu = *reinterpret_cast<const uint4*>(p.v_cache + row);
       const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&ku);
       const __nv_bfloat162* vh = reinterpret_cast<const __nv_bfloat162*>(&vu);
 #pragma unroll
@@ -100,6 +136,7 @@ gqa_decode_kernel(DecodeParams p) {
       s += __shfl_xor_sync(0xffffffffu, s, 4);
       s += __shfl_xor_sync(0xffffffffu, s, 2);
       s += __shfl_xor_sync(0xffffffffu, s, 1);
+      if constexpr (KV != 0) s *= ks;
       if (valid) {
         const float mn = fmaxf(m[g], s);
         const float alpha = exp2f(m[g] - mn);
@@ -175,10 +212,10 @@ static thread_local int g_window = 0, g_sinks = 0;   // set by b200_gqa_decode_e
 
 // q/out/gate: [B, Hq, 128] bf16; caches [num_blocks, Hkv, block_size, 128]; workspace: fp32
 // [B * Hq * splits * 130] (used when splits > 1).
-extern "C" int b200_gqa_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
-                               const void* gate, const int* block_table, const int* kv_len, float* workspace,
-                               int batch, int max_blocks, int block_size, int n_q_heads, int n_kv_heads,
-                               int splits, float softmax_scale, cudaStream_t stream) {
+static int decode_launch(int fmt, const void* q, const void* k_cache, const void* v_cache, const float* k_scale, const float* v_scale,
+                         void* out, const void* gate, const int* block_table, const int* kv_len, float* workspace, int batch,
+                         int max_blocks, int block_size, int n_q_heads, int n_kv_heads, int splits, float softmax_scale,
+                         cudaStream_t stream) {
   if (n_q_heads % n_kv_heads || splits < 1) return -6;
   const int G = n_q_heads / n_kv_heads;
   DecodeParams p;
@@ -198,24 +235,53 @@ extern "C" int b200_gqa_decode(const void* q, const void* k_cache, const void* v
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.window = g_window;
   p.sinks = g_sinks;
+  p.k_scale = k_scale;
+  p.v_scale = v_scale;
   if (splits > 1 && !workspace) return -6;
   dim3 grid(splits, n_kv_heads, batch);
   cudaError_t e = cudaSuccess;
+#define B200_DECODE_CASE(g)                                                                                   \
+  case g:                                                                                                     \
+    e = fmt == 1   ? b200::launch_pdl(gqa_decode_kernel<g, 1>, grid, dim3(THREADS), 0, stream, p)             \
+        : fmt == 2 ? b200::launch_pdl(gqa_decode_kernel<g, 2>, grid, dim3(THREADS), 0, stream, p)             \
+                   : b200::launch_pdl(gqa_decode_kernel<g, 0>, grid, dim3(THREADS), 0, stream, p);            \
+    break;
   switch (G) {
-    case 1: e = b200::launch_pdl(gqa_decode_kernel<1>, grid, dim3(THREADS), 0, stream, p); break;
-    case 2: e = b200::launch_pdl(gqa_decode_kernel<2>, grid, dim3(THREADS), 0, stream, p); break;
-    case 3: e = b200::launch_pdl(gqa_decode_kernel<3>, grid, dim3(THREADS), 0, stream, p); break;
-    case 4: e = b200::launch_pdl(gqa_decode_kernel<4>, grid, dim3(THREADS), 0, stream, p); break;
-    case 5: e = b200::launch_pdl(gqa_decode_kernel<5>, grid, dim3(THREADS), 0, stream, p); break;
-    case 6: e = b200::launch_pdl(gqa_decode_kernel<6>, grid, dim3(THREADS), 0, stream, p); break;
-    case 8: e = b200::launch_pdl(gqa_decode_kernel<8>, grid, dim3(THREADS), 0, stream, p); break;
+    B200_DECODE_CASE(1) B200_DECODE_CASE(2) B200_DECODE_CASE(3) B200_DECODE_CASE(4) B200_DECODE_CASE(5) B200_DECODE_CASE(6)
+    B200_DECODE_CASE(8)
     default: return -6;
   }
+#undef B200_DECODE_CASE
   if (e != cudaSuccess) return (int)e;
   if (splits > 1)
     e = b200::launch_pdl(gqa_decode_merge_kernel, dim3(batch * n_q_heads), dim3(D), 0, stream,
                          (const float*)workspace, splits, p.gate, p.out);
   return (int)e;
+}
+
+extern "C" int b200_gqa_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
+                               const void* gate, const int* block_table, const int* kv_len, float* workspace,
+                               int batch, int max_blocks, int block_size, int n_q_heads, int n_kv_heads,
+                               int splits, float softmax_scale, cudaStream_t stream) {
+  return decode_launch(0, q, k_cache, v_cache, nullptr, nullptr, out, gate, block_table, kv_len, workspace, batch, max_blocks,
+                       block_size, n_q_heads, n_kv_heads, splits, softmax_scale, stream);
+}
+
+// Decode attention over an 8-bit cache (fmt 1 = E4M3, 2 = INT8) with per-(token, head) fp32 scales
+// [num_blocks, Hkv, bs]; the rows are dequantised in registers, so the kernel streams half the bytes of the bf16
+// cache.  window / sinks as below.
+extern "C" int b200_gqa_decode_kv8(int fmt, const void* q, const void* k8, const void* v8, const float* k_scale,
+                                   const float* v_scale, void* out, const void* gate, const int* block_table,
+                                   const int* kv_len, float* workspace, int batch, int max_blocks, int block_size,
+                                   int n_q_heads, int n_kv_heads, int splits, float softmax_scale, int window, int sinks,
+                                   cudaStream_t stream) {
+  if (!k_scale || !v_scale || (fmt != 1 && fmt != 2)) return -6;
+  g_window = window > 0 ? window : 0;
+  g_sinks = sinks > 0 ? sinks : 0;
+  const int rc = decode_launch(fmt, q, k8, v8, k_scale, v_scale, out, gate, block_table, kv_len, workspace, batch, max_blocks,
+                               block_size, n_q_heads, n_kv_heads, splits, softmax_scale, stream);
+  g_window = g_sinks = 0;
+  return rc;
 }
 
 // As b200_gqa_decode with a sliding window: each query sees the first `sinks` keys and the last `window` keys of its

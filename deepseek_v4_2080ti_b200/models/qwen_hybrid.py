@@ -367,9 +367,14 @@ class QwenHybridRuntime:
 
     def __init__(self, cfg: QwenHybridConfig, weights: QwenHybridWeights, max_slots: int = 1,
                  max_context: int = 8192 + 512, block_size: int = 64, comm=None, num_blocks: int | None = None,
-                 attention_window: int = 0, attention_sink_tokens: int = 0):
+                 attention_window: int = 0, attention_sink_tokens: int = 0, kv_cache_dtype: str = "bf16"):
         """``attention_window`` > 0 restricts the full-attention layers to a sliding window of that many keys plus
-        the first ``attention_sink_tokens`` keys (the cache still holds every position)."""
+        the first ``attention_sink_tokens`` keys (the cache still holds every position).  ``kv_cache_dtype`` "fp8" or
+        "int8_per_token_head" keeps the cache as E4M3 / INT8 rows with one scale per (token, head): half the bytes
+        per token, read directly by the decode kernel and staged back to bf16 per layer for the prefill kernel."""
+        if kv_cache_dtype not in ("auto", "bf16", "fp16", "fp8", "int8_per_token_head"):
+            raise ValueError(f"KV cache dtype {kv_cache_dtype!r} is not implemented (bf16, fp8, int8_per_token_head are)")
+        self.kv_cache_dtype = kv_cache_dtype if kv_cache_dtype in attention.KV8_FORMATS else "bf16"
         self.cfg, self.w, self.device = cfg, weights, weights.device
         self.attention_window, self.attention_sinks = int(attention_window), int(attention_sink_tokens)
         self.comm = comm or NoComm()
@@ -390,8 +395,23 @@ class QwenHybridRuntime:
         dev = self.device
         nf, nl = len(self.full_layers), len(self.lin_layers)
         # block 0 is a scratch block: padded rows of a decode batch write their K/V there
-        self.k_cache = torch.zeros(nf, self.num_blocks, self.hkv, block_size, 128, dtype=torch.bfloat16, device=dev)
-        self.v_cache = torch.zeros_like(self.k_cache)
+        self.kv8 = None
+        if self.kv_cache_dtype != "bf16":
+            self.kv8 = attention.Kv8Cache(self.kv_cache_dtype, nf, self.num_blocks, self.hkv, block_size, dev)
+            self.k_cache = self.v_cache = None
+            # bf16 staging: one sequence's whole context for prefill (blocks in sequence order), one row per sequence
+            # of a decode batch
+            self.stage_k = torch.zeros(self.max_blocks_per_seq, self.hkv, block_size, 128, dtype=torch.bfloat16, device=dev)
+            self.stage_v = torch.zeros_like(self.stage_k)
+            drows = max(max_slots, 64)
+            self.dstage_k = torch.zeros((drows + block_size - 1) // block_size, self.hkv, block_size, 128,
+                                        dtype=torch.bfloat16, device=dev)
+            self.dstage_v = torch.zeros_like(self.dstage_k)
+            self._ident_bt = torch.arange(self.max_blocks_per_seq, dtype=torch.int32, device=dev)[None]
+            self._rows = torch.arange(drows, dtype=torch.int32, device=dev)
+        else:
+            self.k_cache = torch.zeros(nf, self.num_blocks, self.hkv, block_size, 128, dtype=torch.bfloat16, device=dev)
+            self.v_cache = torch.zeros_like(self.k_cache)
         self.states = torch.zeros(max_slots, nl, self.hv_lin, 128, 128, dtype=torch.float32, device=dev)
         self.tails = torch.zeros(max_slots, nl, cfg.linear_conv_kernel_dim - 1, 2 * self.kd + self.vd,
                                  dtype=torch.bfloat16, device=dev)
@@ -518,24 +538,47 @@ class QwenHybridRuntime:
         with PROFILER.scope("lin.out+ar.attn"):
             return self._row_parallel(y.view(t, self.vd), lw.out)
 
-    def _full_attn(self, li: int, lw: LayerWeights, x: torch.Tensor, t: int, positions, kv_slots, meta) -> torch.Tensor:
+    def _attend(self, idx: int, lw: LayerWeights, proj: torch.Tensor, t: int, positions, kv_slots, meta, eps) -> torch.Tensor:
+        """QK-norm + RoPE + cache append + attention of one full-attention layer, for either cache dtype."""
         cfg = self.cfg
-        idx = self.full_layers.index(li)
-        proj = gemm.linear(x, lw.proj)
         gate_mul = 2 if cfg.attn_output_gate else 1
         qw = self.hq * 128 * gate_mul
-        kc, vc = self.k_cache[idx], self.v_cache[idx]
-        q, gate = attention.qk_norm_rope_append(
-            proj, 0, 128 * gate_mul, cfg.attn_output_gate, proj, qw, proj, qw + self.hkv * 128, lw.q_norm, lw.k_norm,
-            True, cfg.rms_norm_eps, self.inv_freq, cfg.rotary_dim, positions, kv_slots, kc, vc, self.hq, self.hkv)
+        win, sinks = self.attention_window, self.attention_sinks
+
+        def rope_append(slots, kc, vc):
+            return attention.qk_norm_rope_append(
+                proj, 0, 128 * gate_mul, cfg.attn_output_gate, proj, qw, proj, qw + self.hkv * 128, lw.q_norm, lw.k_norm,
+                True, eps, self.inv_freq, cfg.rotary_dim, positions, slots, kc, vc, self.hq, self.hkv)
+
+        if self.kv8 is None:
+            kc, vc = self.k_cache[idx], self.v_cache[idx]
+            q, gate = rope_append(kv_slots, kc, vc)
+            if meta["mode"] == "prefill":
+                with PROFILER.scope("full.attn_kernel"):
+                    return attention.prefill(q, kc, vc, meta["block_table"], meta["q_start"], meta["q_len"], meta["kv_len"],
+                                             meta["max_q_len"], gate=gate, window=win, sinks=sinks)
+            return attention.decode(q, kc, vc, meta["block_table"], meta["kv_len"], gate=gate, max_kv_len=meta["max_kv_len"],
+                                    window=win, sinks=sinks)
+        c = self.kv8
+        k8, v8, ks, vs = c.k[idx], c.v[idx], c.k_scale[idx], c.v_scale[idx]
         if meta["mode"] == "prefill":
+            # past rows come back dequantised, the chunk's own rows stay exact bf16; a row's position is its staging slot
+            attention.kv8_dequantize(c.fmt, k8, v8, ks, vs, meta["block_table"][0], meta["past"], self.stage_k, self.stage_v)
+            q, gate = rope_append(positions, self.stage_k, self.stage_v)
+            attention.kv8_quantize(c.fmt, self.stage_k, self.stage_v, positions, kv_slots, k8, v8, ks, vs)
             with PROFILER.scope("full.attn_kernel"):
-                o = attention.prefill(q, kc, vc, meta["block_table"], meta["q_start"], meta["q_len"], meta["kv_len"],
-                                      meta["max_q_len"], gate=gate, window=self.attention_window,
-                                      sinks=self.attention_sinks)
-        else:
-            o = attention.decode(q, kc, vc, meta["block_table"], meta["kv_len"], gate=gate,
-                                 max_kv_len=meta["max_kv_len"], window=self.attention_window, sinks=self.attention_sinks)
+                return attention.prefill(q, self.stage_k, self.stage_v, self._ident_bt, meta["q_start"], meta["q_len"],
+                                         meta["kv_len"], meta["max_q_len"], gate=gate, window=win, sinks=sinks)
+        rows = self._rows[:t]
+        q, gate = rope_append(rows, self.dstage_k, self.dstage_v)
+        attention.kv8_quantize(c.fmt, self.dstage_k, self.dstage_v, rows, kv_slots, k8, v8, ks, vs)
+        return attention.decode_kv8(c.fmt, q, k8, v8, ks, vs, meta["block_table"], meta["kv_len"], gate=gate,
+                                    max_kv_len=meta["max_kv_len"], window=win, sinks=sinks)
+
+    def _full_attn(self, li: int, lw: LayerWeights, x: torch.Tensor, t: int, positions, kv_slots, meta) -> torch.Tensor:
+        idx = self.full_layers.index(li)
+        proj = gemm.linear(x, lw.proj)
+        o = self._attend(idx, lw, proj, t, positions, kv_slots, meta, self.cfg.rms_norm_eps)
         return self._row_parallel(o.view(t, self.hq * 128), lw.out)
 
     def _embed(self, ids: torch.Tensor) -> torch.Tensor:
@@ -585,15 +628,7 @@ class QwenHybridRuntime:
                                      self.states[:, idx], slots_t, lw.gdn_norm, self.hv_lin, self.hk_lin, eps)
                 d_attn = self.comm.all_reduce(gemm.linear_stream(y, lw.out))
             else:
-                idx = self.full_layers.index(i)
-                gate_mul = 2 if cfg.attn_output_gate else 1
-                qw = self.hq * 128 * gate_mul
-                kc, vc = self.k_cache[idx], self.v_cache[idx]
-                q, gate = attention.qk_norm_rope_append(
-                    proj, 0, 128 * gate_mul, cfg.attn_output_gate, proj, qw, proj, qw + self.hkv * 128, lw.q_norm,
-                    lw.k_norm, True, eps, self.inv_freq, cfg.rotary_dim, positions, kv_slots, kc, vc, self.hq, self.hkv)
-                o = attention.decode(q, kc, vc, meta["block_table"], meta["kv_len"], gate=gate,
-                                     max_kv_len=meta["max_kv_len"], window=self.attention_window, sinks=self.attention_sinks)
+                o = self._attend(self.full_layers.index(i), lw, proj, t, positions, kv_slots, meta, eps)
                 d_attn = self.comm.all_reduce(gemm.linear_stream(o.view(t, self.hq * 128), lw.out))
             _, xs2 = basic.rmsnorm_split(h, d_attn, lw.post_ln, terms, eps, True, want_bf16=False)
             gu = gemm.linear_stream(None, lw.gate_up, xsplit=xs2)
@@ -642,9 +677,10 @@ class QwenHybridRuntime:
             kv_slots = (bt_row[(pos // self.block_size).long()] * self.block_size + pos % self.block_size).to(torch.int32)
             i32 = lambda v: torch.tensor([v], dtype=torch.int32, device=self.device)
             meta = {"mode": "prefill", "block_table": self.block_table[slot:slot + 1], "q_start": i32(0),
-                    "q_len": i32(t), "kv_len": i32(st.length + t), "max_q_len": t}
+                    "q_len": i32(t), "kv_len": i32(st.length + t), "max_q_len": t, "past": st.length}
             rows = torch.tensor([t - 1], dtype=torch.int64, device=self.device)
             logits = self._forward(ids, pos, kv_slots, meta, slot, None, rows)
+            self.last_logits = logits                  # last row of the latest chunk (fp32 [1, vocab])
             st.length += t
             self.prefill_tokens_computed += t
             if e in cuts:

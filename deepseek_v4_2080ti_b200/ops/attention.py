@@ -115,6 +115,72 @@ def decode(q, k_cache, v_cache, block_table, kv_len, gate=None, scale=None, spli
     return out
 
 
+# ---------------------------------------------------------------- 8-bit KV cache
+KV8_FORMATS = {"fp8": 1, "int8_per_token_head": 2}
+
+
+class Kv8Cache:
+    """8-bit paged cache of one attention layer set (``fmt`` "fp8" = E4M3, "int8_per_token_head" = INT8): ``k`` / ``v``
+    uint8 [L, num_blocks, Hkv, bs, 128] with one fp32 scale per (block, head, row) in ``k_scale`` / ``v_scale``
+    [L, num_blocks, Hkv, bs].  Rows reach it through a bf16 staging cache (the fused norm + RoPE kernel writes there)
+    and ``kv8_quantize``."""
+
+    def __init__(self, fmt: str, layers: int, num_blocks: int, hkv: int, block_size: int, device):
+        self.fmt = KV8_FORMATS[fmt]
+        self.k = torch.zeros(layers, num_blocks, hkv, block_size, D, dtype=torch.uint8, device=device)
+        self.v = torch.zeros_like(self.k)
+        self.k_scale = torch.zeros(layers, num_blocks, hkv, block_size, dtype=torch.float32, device=device)
+        self.v_scale = torch.zeros_like(self.k_scale)
+
+    def nbytes(self) -> int:
+        return 2 * self.k.numel() + 8 * self.k_scale.numel()
+
+
+def kv8_quantize(fmt: int, stage_k, stage_v, src_slots, dst_slots, k8, v8, k_scale, v_scale):
+    """Quantise staged rows ``src_slots`` (bf16 [nb_s, Hkv, bs_s, 128]) into rows ``dst_slots`` of the 8-bit cache."""
+    rc = _lib.lib().b200_kv8_quantize(_lib.ptr(stage_k), _lib.ptr(stage_v), _lib.ptr(src_slots), _lib.ptr(dst_slots),
+                                      _lib.ptr(k8), _lib.ptr(v8), _lib.ptr(k_scale), _lib.ptr(v_scale), stage_k.shape[2],
+                                      k8.shape[2], src_slots.numel(), k8.shape[1], int(fmt), _lib.stream())
+    _lib.check(rc, "kv8_quantize")
+
+
+def kv8_dequantize(fmt: int, k8, v8, k_scale, v_scale, block_table_row, n_tokens: int, stage_k, stage_v):
+    """Dequantise the first ``n_tokens`` positions of one sequence into the staging caches (blocks 0, 1, 2, ...)."""
+    if n_tokens <= 0:
+        return
+    assert stage_k.shape[2] == k8.shape[2] and stage_k.shape[0] * stage_k.shape[2] >= n_tokens
+    rc = _lib.lib().b200_kv8_dequantize(_lib.ptr(k8), _lib.ptr(v8), _lib.ptr(k_scale), _lib.ptr(v_scale),
+                                        _lib.ptr(block_table_row), _lib.ptr(stage_k), _lib.ptr(stage_v), k8.shape[2],
+                                        int(n_tokens), k8.shape[1], int(fmt), _lib.stream())
+    _lib.check(rc, "kv8_dequantize")
+
+
+def decode_kv8(fmt: int, q, k8, v8, k_scale, v_scale, block_table, kv_len, gate=None, scale=None, splits: int | None = None,
+               max_kv_len: int | None = None, window: int = 0, sinks: int = 0):
+    """``decode`` over an 8-bit cache; rows are dequantised in registers."""
+    b, hq, d = q.shape
+    nb, hkv, bs, _ = k8.shape
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    if splits is None:
+        ctx = max_kv_len if max_kv_len is not None else block_table.shape[1] * bs
+        splits = max(1, min(64, (2 * 148) // max(1, b * hkv), (ctx + 255) // 256))
+    ws = None
+    if splits > 1:
+        need = b * hq * splits * (D + 2)
+        dev = q.device.index or 0
+        ws = _dec_ws.get(dev)
+        if ws is None or ws.numel() < need:
+            ws = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device)
+            _dec_ws[dev] = ws
+    rc = _lib.lib().b200_gqa_decode_kv8(int(fmt), _lib.ptr(q), _lib.ptr(k8), _lib.ptr(v8), _lib.ptr(k_scale),
+                                        _lib.ptr(v_scale), _lib.ptr(out), _lib.ptr(gate), _lib.ptr(block_table),
+                                        _lib.ptr(kv_len), _lib.ptr(ws), b, block_table.shape[1], bs, hq, hkv, splits,
+                                        _f(scale), int(window), int(sinks), _lib.stream())
+    _lib.check(rc, "gqa_decode_kv8", 2 if splits > 1 else 1)
+    return out
+
+
 # ---------------------------------------------------------------- fp32 oracles
 def rope_ref(x, positions, inv_freq, rot):
     """Half-split rotation over the first ``rot`` dims. x: [T, H, D] fp32."""

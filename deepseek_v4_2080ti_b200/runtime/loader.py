@@ -272,7 +272,8 @@ def load_runtime(args):
     weights = qh.QwenHybridWeights(cfg, state, dev, rank, world)
     rt = qh.QwenHybridRuntime(cfg, weights, max_slots=slots, max_context=max_ctx, comm=comm,
                               attention_window=int(getattr(args, "attention_window", 0) or 0),
-                              attention_sink_tokens=int(getattr(args, "attention_sink_tokens", 0) or 0))
+                              attention_sink_tokens=int(getattr(args, "attention_sink_tokens", 0) or 0),
+                              kv_cache_dtype=getattr(args, "kv_cache_dtype", "auto") or "auto")
     if getattr(args, "enable_prefix_caching", False):
         # snapshot points every 2048 tokens: a snapshot copies the recurrent state of every Gated-DeltaNet layer
         # (~100 MB at the 27B shape), and chunks of 2048 keep the prefill GEMMs at full efficiency
