@@ -12,7 +12,8 @@ path is one of this package's sm_100a kernels.
   of a chunk from the previous stage and sends them on, and the last stage shares the next token;
 * weights: bf16 / FP8 block-128 / FP4 as above, or GGUF block formats quantised at load (``dense_quant``,
   ``expert_format="gguf"``) and decoded inside the GEMMs - the GLM-5.2-shaped mix is Q8_0 attention projections,
-  Q4_K dense / shared feed-forward, Q2_K gate/up and IQ3_XXS down experts.
+  Q4_K dense / shared feed-forward, Q2_K gate/up and IQ3_XXS down experts; or the blocks of a GGUF file as they are
+  (``models/mla_gguf.py`` reads a ``glm-dsa`` checkpoint into ``RawQuant`` entries).
 
 Same math as ``MlaMoeRuntime`` (the host path) and ``reference_cpu/mla_moe_ref.py``; see ``mla_moe.py`` for the
 reference citations.
@@ -28,6 +29,7 @@ from ..formats import fp8 as fp8fmt
 from ..formats import gguf as G
 from ..ops import basic, gemm, gguf_gemm, mla, moe
 from ..ops.gemm import PackedLinear
+from .mla_gguf import RawQuant
 from .mla_moe import MlaMoeConfig
 
 
@@ -118,7 +120,13 @@ class MlaMoeGpuWeights:
             if self.embed is None:
                 self.embed = sd["embed.weight"].to(dev, torch.bfloat16).contiguous()
 
-    def _lin(self, w: torch.Tensor, kind: str = "ffn"):
+    def _lin(self, w, kind: str = "ffn"):
+        """A matrix of this rank as a GEMM operand.  ``RawQuant`` rows (a GGUF file's own blocks) go to the
+        in-register-decode GEMM untouched; tensors are quantised per ``gguf_mix`` / ``dense_fp8`` or kept bf16."""
+        if isinstance(w, RawQuant):
+            if w.k % 64 == 0 and w.t in gguf_gemm.WF:
+                return gguf_gemm.GGUFLinear.from_raw(w.raw.contiguous(), w.t, w.n, w.k, self.device)
+            return PackedLinear.from_bf16(w.to(self.device).dequant().to(torch.bfloat16))
         w = w.to(self.device)
         if self.gguf_mix is not None:
             t = G.GGMLType[self.gguf_mix[kind]]
@@ -136,7 +144,18 @@ class MlaMoeGpuWeights:
         """Output-feature shard of a column-parallel matrix (``group`` rows stay together)."""
         n = w.shape[0] // self.world
         assert n * self.world == w.shape[0] and n % group == 0
+        if isinstance(w, RawQuant):
+            return w.rows(self.rank * n, (self.rank + 1) * n)
         return w[self.rank * n:(self.rank + 1) * n]
+
+    def _cat_rows(self, parts: list):
+        """Row-wise concatenation of two projections that share their input (gate | up)."""
+        if isinstance(parts[0], RawQuant):
+            joined = RawQuant.cat(parts)
+            if joined is not None:
+                return joined
+            return torch.cat([p.to(self.device).dequant() for p in parts]).to(torch.bfloat16)
+        return torch.cat(parts)
 
     def _cols(self, w: torch.Tensor) -> torch.Tensor:
         k = w.shape[1] // self.world
@@ -146,6 +165,17 @@ class MlaMoeGpuWeights:
         """Input-dimension (row-parallel) shard of a matrix.  GGUF blocks run along the input dimension, so the full
         matrix is quantised as a checkpoint would hold it and this rank takes its run of blocks; when the shard does
         not hold whole blocks its dequantised values are re-encoded as Q8_0 (32-wide blocks)."""
+        if isinstance(w, RawQuant):
+            if self.world == 1:
+                return self._lin(w, kind)
+            kl = w.k // self.world
+            part = w.cols(self.rank * kl, (self.rank + 1) * kl)
+            if part is not None and kl % 64 == 0:
+                return self._lin(part, kind)
+            deq = w.to(self.device).dequant()[:, self.rank * kl:(self.rank + 1) * kl].contiguous()
+            if kl % 64:
+                return PackedLinear.from_bf16(deq.to(torch.bfloat16))
+            return gguf_gemm.GGUFLinear.from_raw(G.quantize(deq, G.GGMLType.Q8_0), G.GGMLType.Q8_0, w.n, kl, self.device)
         if self.gguf_mix is None or self.world == 1:
             return self._lin(self._cols(w), kind)
         w = w.to(self.device)
@@ -189,17 +219,35 @@ class MlaMoeGpuWeights:
             lw.idx_knorm, lw.idx_wproj = b(sd[a + "indexer.k_norm.weight"]), self._lin(sd[a + "indexer.weights_proj.weight"])
         f = p + "ffn."
         if dense:
-            lw.dense_gu = self._lin(torch.cat([self._rows(sd[f + "w1.weight"]), self._rows(sd[f + "w3.weight"])]))
+            lw.dense_gu = self._lin(self._cat_rows([self._rows(sd[f + "w1.weight"]), self._rows(sd[f + "w3.weight"])]))
             lw.dense_down = self._lin_cols(sd[f + "w2.weight"], "ffn")
             return lw
         lw.gate = PackedLinear.from_bf16(sd[f + "gate.weight"].to(dev))
         lw.gate_bias = sd[f + "gate.bias"].to(dev, torch.float32)
         if cfg.num_shared_experts:
-            lw.shared_gu = self._lin(torch.cat([self._rows(sd[f + "shared_experts.w1.weight"]),
-                                                self._rows(sd[f + "shared_experts.w3.weight"])]))
+            lw.shared_gu = self._lin(self._cat_rows([self._rows(sd[f + "shared_experts.w1.weight"]),
+                                                     self._rows(sd[f + "shared_experts.w3.weight"])]))
             lw.shared_down = self._lin_cols(sd[f + "shared_experts.w2.weight"], "ffn")
         es = range(self.expert_lo, self.expert_hi)
-        if self.gguf_mix is not None:
+        first = sd[f + f"experts.{self.expert_lo}.w1.weight"]
+        if isinstance(first, RawQuant):
+            # a GGUF file's expert blocks as they are; gate and up stack row-wise when they share a type
+            up = sd[f + f"experts.{self.expert_lo}.w3.weight"]
+            if up.t == first.t and first.k % 64 == 0 and first.t in gguf_gemm.WF:
+                raws = [torch.cat([sd[f + f"experts.{e}.w1.weight"].raw, sd[f + f"experts.{e}.w3.weight"].raw]).to(dev) for e in es]
+                lw.w13 = moe.ExpertWeights.from_gguf(raws, first.t, 2 * cfg.expert_intermediate, cfg.hidden_size)
+            else:
+                deq = [torch.cat([sd[f + f"experts.{e}.w1.weight"].to(dev).dequant(), sd[f + f"experts.{e}.w3.weight"].to(dev).dequant()])
+                       for e in es]
+                lw.w13 = moe.ExpertWeights.from_gguf([G.quantize(x, G.GGMLType.Q8_0) for x in deq], G.GGMLType.Q8_0,
+                                                     2 * cfg.expert_intermediate, cfg.hidden_size)
+            dn = sd[f + f"experts.{self.expert_lo}.w2.weight"]
+            if dn.k % 64 == 0 and dn.t in gguf_gemm.WF:
+                lw.w2 = moe.ExpertWeights.from_gguf([sd[f + f"experts.{e}.w2.weight"].raw.to(dev) for e in es], dn.t,
+                                                    cfg.hidden_size, cfg.expert_intermediate)
+            else:
+                lw.w2 = moe.ExpertWeights.from_bf16([sd[f + f"experts.{e}.w2.weight"].to(dev).dequant().to(torch.bfloat16) for e in es])
+        elif self.gguf_mix is not None:
             t13, t2 = G.GGMLType[self.gguf_mix["gate_up"]], G.GGMLType[self.gguf_mix["down"]]
             full = lambda e, n: self._expert_f32(sd, f + f"experts.{e}.{n}")
             lw.w13 = moe.ExpertWeights.from_gguf([G.quantize(torch.cat([full(e, "w1"), full(e, "w3")]), t13) for e in es], t13,

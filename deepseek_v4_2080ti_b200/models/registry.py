@@ -58,6 +58,7 @@ class ModelSpec:
     n_layers: Callable[[Any], int]
     routed_suffixes: tuple[str, ...]
     build_runtime: Callable[..., Any] | None = None
+    optional_suffixes: tuple[str, ...] = ()                     # present in some checkpoints, not needed by the runtime
 
     def expected_names(self, params) -> list[str]:
         out = list(self.global_tensors)
@@ -69,7 +70,8 @@ class ModelSpec:
         params = self.parse_params(bundle.metadata, bundle.tensors)
         want = set(self.expected_names(params))
         have = set(bundle.tensors)
-        rep = ValidationReport(self.architecture, True, sorted(want - have), sorted(have - want))
+        extra = sorted(n for n in have - want if not n.endswith(self.optional_suffixes or ("\0",)))
+        rep = ValidationReport(self.architecture, True, sorted(want - have), extra)
         for name, ti in bundle.tensors.items():
             rep.by_type[ti.ggml_type.name] = rep.by_type.get(ti.ggml_type.name, 0) + ti.nbytes
             rep.total_bytes += ti.nbytes
@@ -123,6 +125,52 @@ def _minimax_runtime(bundle, device="cuda", rank=0, world=1, comm=None, **kw):
     return cfg, gm.GqaMoeRuntime(cfg, w, comm=comm, **kw)
 
 
+class _MlaSlotAdapter:
+    """The one-sequence MLA runtime behind the slot interface the GGUF drivers use (allocate / prefill / decode / free)."""
+
+    def __init__(self, rt):
+        self.rt = rt
+        from ..ops import basic
+        self._argmax = basic.argmax
+
+    def allocate(self) -> int:
+        self.rt.reset()
+        return 0
+
+    def free(self, slot: int) -> None:
+        self.rt.reset()
+
+    def prefill(self, slot: int, ids, chunk: int = 2048):
+        logits = None
+        for s in range(0, ids.numel(), chunk):
+            logits = self.rt.forward(ids[s:s + chunk])
+        return self._argmax(logits[-1:])
+
+    def decode(self, slots, ids):
+        return self._argmax(self.rt.forward(ids)[-1:])
+
+
+def _glm_params(md, tensors):
+    from .mla_gguf import config_from_metadata
+    return config_from_metadata(md, tensors)
+
+
+def _glm_runtime(bundle, device="cuda", rank=0, world=1, comm=None, max_slots=1, max_context=4096, **kw):
+    from . import mla_gguf as mg
+    from . import mla_moe_gpu as mm
+    from .gqa_moe import TensorStore
+    cfg = mg.config_from_metadata(bundle.metadata, bundle.tensors)
+    per = cfg.num_experts // world
+    state = mg.read_state(TensorStore(bundle), cfg, device, expert_range=(rank * per, (rank + 1) * per))
+    w = mm.MlaMoeGpuWeights(cfg, state, device, rank, world)
+    return cfg, _MlaSlotAdapter(mm.MlaMoeGpuRuntime(cfg, w, max_context=max_context, comm=comm, **kw))
+
+
+def _glm_layer_tensors(cfg, i):
+    from .mla_gguf import layer_suffixes
+    return layer_suffixes(cfg, i)
+
+
 MINIMAX_LAYER = ("attn_norm.weight", "ffn_norm.weight", "attn_q.weight", "attn_k.weight", "attn_v.weight", "attn_output.weight",
                  "attn_q_norm.weight", "attn_k_norm.weight", "ffn_gate_inp.weight", "exp_probs_b.bias", "ffn_gate_exps.weight",
                  "ffn_up_exps.weight", "ffn_down_exps.weight")
@@ -150,3 +198,10 @@ register(ModelSpec(
     global_tensors=("token_embd.weight", "output.weight", "output_norm.weight"),
     layer_tensors=lambda p, i: MINIMAX_LAYER, n_layers=lambda p: p.n_layers,
     routed_suffixes=("ffn_gate_exps.weight", "ffn_up_exps.weight", "ffn_down_exps.weight"), build_runtime=_minimax_runtime))
+
+register(ModelSpec(
+    architecture="glm-dsa", display_name="GLM-DSA (MLA + sparse indexer + routed experts)", parse_params=_glm_params,
+    global_tensors=("token_embd.weight", "output.weight", "output_norm.weight"), layer_tensors=_glm_layer_tensors,
+    n_layers=lambda p: p.num_layers + p.mtp_layers,
+    routed_suffixes=("ffn_gate_exps.weight", "ffn_up_exps.weight", "ffn_down_exps.weight"), build_runtime=_glm_runtime,
+    optional_suffixes=("indexer.k_norm.bias", "nextn.shared_head_norm.weight")))

@@ -222,3 +222,48 @@ def test_tensor_core_attention_matches_torch_and_scalar_kernel(h, c, r):
         tol = 2e-2 * want.abs().max().clamp_min(1e-3)
         assert (o.float() - want).abs().max() < tol, (use_sel, "tensor-core")
         assert (o2.float() - want).abs().max() < tol, (use_sel, "scalar")
+
+
+def test_runtime_from_gguf_file_follows_dequantised_bf16_runtime():
+    """A glm-dsa GGUF file loaded through the family registry (raw blocks straight into the decode GEMMs, indexer and
+    MTP block included) against the same runtime fed the file's dequantised tensors as bf16."""
+    import os
+    import tempfile
+    from deepseek_v4_2080ti_b200.cli import generate_gguf
+    from deepseek_v4_2080ti_b200.formats import gguf as G
+    from deepseek_v4_2080ti_b200.models import mla_gguf, registry
+    from deepseek_v4_2080ti_b200.models import mla_moe as mm
+    from deepseek_v4_2080ti_b200.models import mla_moe_gpu as mg
+    from deepseek_v4_2080ti_b200.models.gqa_moe import TensorStore
+    from deepseek_v4_2080ti_b200.ops import _lib
+    cfg = mm.MlaMoeConfig(vocab_size=512, hidden_size=256, num_layers=3, first_dense_layers=1, dense_intermediate=256,
+                          q_lora_rank=256, kv_lora_rank=128, num_heads=4, qk_nope_dim=64, qk_rope_dim=32, v_head_dim=128,
+                          index_heads=4, index_dim=64, index_topk=512, num_experts=8, experts_per_token=2,
+                          num_shared_experts=1, expert_intermediate=256, score_func="sigmoid", route_scale=2.5,
+                          expert_format="bf16", mtp_layers=1)
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "glm.gguf")
+        mla_gguf.write_synthetic_gguf(path, cfg, {"gate_up": "Q2_K", "down": "IQ3_XXS"}, seed=6, std=0.05)
+        b = G.read_bundle(path)
+        spec = registry.detect(b)
+        got_cfg, rt = spec.build_runtime(b, "cuda", 0, 1, None, max_context=256)
+        assert got_cfg == cfg and len(rt.rt.w.mtp) == 1
+        from deepseek_v4_2080ti_b200.ops import gguf_gemm
+        assert isinstance(rt.rt.w.layers[1].wo, gguf_gemm.GGUFLinear) and rt.rt.w.layers[1].w2.wfmt == gguf_gemm.WF[G.GGMLType.IQ3_XXS]
+        deq = [(k, (v.dequant().to(torch.bfloat16) if isinstance(v, mla_gguf.RawQuant) else v))
+               for k, v in mla_gguf.read_state(TensorStore(b), cfg)]
+        ref = mg.MlaMoeGpuRuntime(cfg, mg.MlaMoeGpuWeights(cfg, iter(deq), "cuda"), max_context=256)
+        ids = torch.randint(0, cfg.vocab_size, (60,), generator=torch.Generator().manual_seed(3)).cuda()
+        got, want = rt.rt.forward(ids).float(), ref.forward(ids).float()
+        torch.cuda.synchronize()
+        _lib.check_status()
+        err = ((got - want).norm() / want.norm()).item()
+        assert err < 3e-2, err
+        # the slot interface of the GGUF drivers, and the driver itself
+        s = rt.allocate()
+        first = rt.prefill(s, ids.to(torch.int32), 32)
+        assert 0 <= int(first.item()) < cfg.vocab_size
+        nxt = rt.decode([s], first.to(torch.int32))
+        assert nxt.numel() == 1
+        rt.free(s)
+        assert generate_gguf.main(["--gguf", path, "--token-ids", "1,2,3,4,5", "--max-new-tokens", "4", "--max-context", "128"]) == 0
