@@ -33,9 +33,10 @@ struct DecodeParams {
   float scale_log2;
   int window, sinks;             // window > 0: only the first `sinks` and the last `window` keys are visible
   // KV 1 / 2: the caches hold E4M3 / INT8 bytes (same [num_blocks, Hkv, bs, D] layout) with one fp32 scale per
-  // (block, head, row)
+  // (block, head, row); KV 3: E4M3 keys, 4-bit affine values (rows of D / 2 bytes, scale and minimum per row)
   const float* k_scale;
   const float* v_scale;
+  const float* v_min;
 };
 
 __device__ __forceinline__ void e4m3x8_to_float(const uint2 u, float (&f)[8]) {
@@ -100,7 +101,15 @@ gqa_decode_kernel(DecodeParams p) {
     const size_t row = ((size_t)(blk * p.Hkv + kvh) * p.bs + (kc % p.bs)) * D + dl * 8;
     float kf[8], vf[8];
     float ks = 1.f;
-    if constexpr (KV != 0) {
+    if constexpr (KV == 3) {
+      const uint2 ku = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(p.k_cache) + row);
+      const uint32_t vn = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(p.v_cache) + (row >> 1));
+      ks = p.k_scale[row >> 7];
+      const float vs = p.v_scale[row >> 7], vm = p.v_min[row >> 7];
+      e4m3x8_to_float(ku, kf);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) vf[i] = (float)((vn >> (4 * i)) & 15) * vs + vm;
+    } else if constexpr (KV != 0) {
       const uint2 ku = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(p.k_cache) + row);
       const uint2 vu = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(p.v_cache) + row);
       ks = p.k_scale[row >> 7];
@@ -213,6 +222,7 @@ static thread_local int g_window = 0, g_sinks = 0;   // set by b200_gqa_decode_e
 // q/out/gate: [B, Hq, 128] bf16; caches [num_blocks, Hkv, block_size, 128]; workspace: fp32
 // [B * Hq * splits * 130] (used when splits > 1).
 static int decode_launch(int fmt, const void* q, const void* k_cache, const void* v_cache, const float* k_scale, const float* v_scale,
+                         const float* v_min,
                          void* out, const void* gate, const int* block_table, const int* kv_len, float* workspace, int batch,
                          int max_blocks, int block_size, int n_q_heads, int n_kv_heads, int splits, float softmax_scale,
                          cudaStream_t stream) {
@@ -237,6 +247,7 @@ static int decode_launch(int fmt, const void* q, const void* k_cache, const void
   p.sinks = g_sinks;
   p.k_scale = k_scale;
   p.v_scale = v_scale;
+  p.v_min = v_min;
   if (splits > 1 && !workspace) return -6;
   dim3 grid(splits, n_kv_heads, batch);
   cudaError_t e = cudaSuccess;
@@ -244,6 +255,7 @@ static int decode_launch(int fmt, const void* q, const void* k_cache, const void
   case g:                                                                                                     \
     e = fmt == 1   ? b200::launch_pdl(gqa_decode_kernel<g, 1>, grid, dim3(THREADS), 0, stream, p)             \
         : fmt == 2 ? b200::launch_pdl(gqa_decode_kernel<g, 2>, grid, dim3(THREADS), 0, stream, p)             \
+        : fmt == 3 ? b200::launch_pdl(gqa_decode_kernel<g, 3>, grid, dim3(THREADS), 0, stream, p)             \
                    : b200::launch_pdl(gqa_decode_kernel<g, 0>, grid, dim3(THREADS), 0, stream, p);            \
     break;
   switch (G) {
@@ -263,22 +275,22 @@ extern "C" int b200_gqa_decode(const void* q, const void* k_cache, const void* v
                                const void* gate, const int* block_table, const int* kv_len, float* workspace,
                                int batch, int max_blocks, int block_size, int n_q_heads, int n_kv_heads,
                                int splits, float softmax_scale, cudaStream_t stream) {
-  return decode_launch(0, q, k_cache, v_cache, nullptr, nullptr, out, gate, block_table, kv_len, workspace, batch, max_blocks,
+  return decode_launch(0, q, k_cache, v_cache, nullptr, nullptr, nullptr, out, gate, block_table, kv_len, workspace, batch, max_blocks,
                        block_size, n_q_heads, n_kv_heads, splits, softmax_scale, stream);
 }
 
-// Decode attention over an 8-bit cache (fmt 1 = E4M3, 2 = INT8) with per-(token, head) fp32 scales
-// [num_blocks, Hkv, bs]; the rows are dequantised in registers, so the kernel streams half the bytes of the bf16
-// cache.  window / sinks as below.
+// Decode attention over a quantised cache (fmt 1 = E4M3, 2 = INT8, 3 = E4M3 keys + 4-bit affine values with v_min)
+// with per-(token, head) fp32 scales [num_blocks, Hkv, bs]; the rows are dequantised in registers, so the kernel
+// streams half (fmt 3: three eighths) of the bytes of the bf16 cache.  window / sinks as below.
 extern "C" int b200_gqa_decode_kv8(int fmt, const void* q, const void* k8, const void* v8, const float* k_scale,
-                                   const float* v_scale, void* out, const void* gate, const int* block_table,
+                                   const float* v_scale, const float* v_min, void* out, const void* gate, const int* block_table,
                                    const int* kv_len, float* workspace, int batch, int max_blocks, int block_size,
                                    int n_q_heads, int n_kv_heads, int splits, float softmax_scale, int window, int sinks,
                                    cudaStream_t stream) {
-  if (!k_scale || !v_scale || (fmt != 1 && fmt != 2)) return -6;
+  if (!k_scale || !v_scale || fmt < 1 || fmt > 3 || (fmt == 3 && !v_min)) return -6;
   g_window = window > 0 ? window : 0;
   g_sinks = sinks > 0 ? sinks : 0;
-  const int rc = decode_launch(fmt, q, k8, v8, k_scale, v_scale, out, gate, block_table, kv_len, workspace, batch, max_blocks,
+  const int rc = decode_launch(fmt, q, k8, v8, k_scale, v_scale, v_min, out, gate, block_table, kv_len, workspace, batch, max_blocks,
                                block_size, n_q_heads, n_kv_heads, splits, softmax_scale, stream);
   g_window = g_sinks = 0;
   return rc;

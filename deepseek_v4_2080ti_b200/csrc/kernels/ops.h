@@ -138,15 +138,16 @@ int b200_gqa_decode_ex(const void* q, const void* k_cache, const void* v_cache, 
 int b200_gqa_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const void* gate,
                     const int* block_table, const int* kv_len, float* workspace, int batch, int max_blocks,
                     int block_size, int n_q_heads, int n_kv_heads, int splits, float softmax_scale, cudaStream_t stream);
-// 8-bit KV cache (fmt 1 = E4M3, 2 = INT8) with per-(token, head) fp32 scales (kv8.cu, attn_gqa_decode.cu)
+// Quantised KV cache (fmt 1 = E4M3, 2 = INT8, 3 = E4M3 keys + 4-bit values with v_min) with per-(token, head) fp32
+// scales (kv8.cu, attn_gqa_decode.cu)
 int b200_gqa_decode_kv8(int fmt, const void* q, const void* k8, const void* v8, const float* k_scale, const float* v_scale,
-                        void* out, const void* gate, const int* block_table, const int* kv_len, float* workspace, int batch,
+                        const float* v_min, void* out, const void* gate, const int* block_table, const int* kv_len, float* workspace, int batch,
                         int max_blocks, int block_size, int n_q_heads, int n_kv_heads, int splits, float softmax_scale,
                         int window, int sinks, cudaStream_t stream);
 int b200_kv8_quantize(const void* stage_k, const void* stage_v, const int* src_slots, const int* dst_slots, void* k8,
-                      void* v8, float* k_scale, float* v_scale, int bs_src, int bs_dst, int T, int Hkv, int fmt,
+                      void* v8, float* k_scale, float* v_scale, float* v_min, int bs_src, int bs_dst, int T, int Hkv, int fmt,
                       cudaStream_t stream);
-int b200_kv8_dequantize(const void* k8, const void* v8, const float* k_scale, const float* v_scale,
+int b200_kv8_dequantize(const void* k8, const void* v8, const float* k_scale, const float* v_scale, const float* v_min,
                         const int* block_table_row, void* stage_k, void* stage_v, int bs, int n_tokens, int Hkv, int fmt,
                         cudaStream_t stream);
 

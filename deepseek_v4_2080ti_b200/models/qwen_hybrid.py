@@ -369,11 +369,12 @@ class QwenHybridRuntime:
                  max_context: int = 8192 + 512, block_size: int = 64, comm=None, num_blocks: int | None = None,
                  attention_window: int = 0, attention_sink_tokens: int = 0, kv_cache_dtype: str = "bf16"):
         """``attention_window`` > 0 restricts the full-attention layers to a sliding window of that many keys plus
-        the first ``attention_sink_tokens`` keys (the cache still holds every position).  ``kv_cache_dtype`` "fp8" or
-        "int8_per_token_head" keeps the cache as E4M3 / INT8 rows with one scale per (token, head): half the bytes
-        per token, read directly by the decode kernel and staged back to bf16 per layer for the prefill kernel."""
-        if kv_cache_dtype not in ("auto", "bf16", "fp16", "fp8", "int8_per_token_head"):
-            raise ValueError(f"KV cache dtype {kv_cache_dtype!r} is not implemented (bf16, fp8, int8_per_token_head are)")
+        the first ``attention_sink_tokens`` keys (the cache still holds every position).  ``kv_cache_dtype`` "fp8",
+        "int8_per_token_head" or "turboquant_k8v4" keeps the cache as E4M3 / INT8 rows (K8V4: E4M3 keys, 4-bit
+        values) with one scale per (token, head): half (three eighths) of the bytes per token, read directly by the
+        decode kernel and staged back to bf16 per layer for the prefill kernel."""
+        if kv_cache_dtype not in ("auto", "bf16", "fp16", *attention.KV8_FORMATS):
+            raise ValueError(f"unknown KV cache dtype {kv_cache_dtype!r}")
         self.kv_cache_dtype = kv_cache_dtype if kv_cache_dtype in attention.KV8_FORMATS else "bf16"
         self.cfg, self.w, self.device = cfg, weights, weights.device
         self.attention_window, self.attention_sinks = int(attention_window), int(attention_sink_tokens)
@@ -560,20 +561,20 @@ class QwenHybridRuntime:
             return attention.decode(q, kc, vc, meta["block_table"], meta["kv_len"], gate=gate, max_kv_len=meta["max_kv_len"],
                                     window=win, sinks=sinks)
         c = self.kv8
-        k8, v8, ks, vs = c.k[idx], c.v[idx], c.k_scale[idx], c.v_scale[idx]
+        k8, v8, ks, vs, vm = c.layer(idx)
         if meta["mode"] == "prefill":
             # past rows come back dequantised, the chunk's own rows stay exact bf16; a row's position is its staging slot
-            attention.kv8_dequantize(c.fmt, k8, v8, ks, vs, meta["block_table"][0], meta["past"], self.stage_k, self.stage_v)
+            attention.kv8_dequantize(c.fmt, k8, v8, ks, vs, meta["block_table"][0], meta["past"], self.stage_k, self.stage_v, vm)
             q, gate = rope_append(positions, self.stage_k, self.stage_v)
-            attention.kv8_quantize(c.fmt, self.stage_k, self.stage_v, positions, kv_slots, k8, v8, ks, vs)
+            attention.kv8_quantize(c.fmt, self.stage_k, self.stage_v, positions, kv_slots, k8, v8, ks, vs, vm)
             with PROFILER.scope("full.attn_kernel"):
                 return attention.prefill(q, self.stage_k, self.stage_v, self._ident_bt, meta["q_start"], meta["q_len"],
                                          meta["kv_len"], meta["max_q_len"], gate=gate, window=win, sinks=sinks)
         rows = self._rows[:t]
         q, gate = rope_append(rows, self.dstage_k, self.dstage_v)
-        attention.kv8_quantize(c.fmt, self.dstage_k, self.dstage_v, rows, kv_slots, k8, v8, ks, vs)
+        attention.kv8_quantize(c.fmt, self.dstage_k, self.dstage_v, rows, kv_slots, k8, v8, ks, vs, vm)
         return attention.decode_kv8(c.fmt, q, k8, v8, ks, vs, meta["block_table"], meta["kv_len"], gate=gate,
-                                    max_kv_len=meta["max_kv_len"], window=win, sinks=sinks)
+                                    max_kv_len=meta["max_kv_len"], window=win, sinks=sinks, v_min=vm)
 
     def _full_attn(self, li: int, lw: LayerWeights, x: torch.Tensor, t: int, positions, kv_slots, meta) -> torch.Tensor:
         idx = self.full_layers.index(li)

@@ -115,49 +115,56 @@ def decode(q, k_cache, v_cache, block_table, kv_len, gate=None, scale=None, spli
     return out
 
 
-# ---------------------------------------------------------------- 8-bit KV cache
-KV8_FORMATS = {"fp8": 1, "int8_per_token_head": 2}
+# ---------------------------------------------------------------- quantised KV cache
+KV8_FORMATS = {"fp8": 1, "int8_per_token_head": 2, "turboquant_k8v4": 3}
 
 
 class Kv8Cache:
-    """8-bit paged cache of one attention layer set (``fmt`` "fp8" = E4M3, "int8_per_token_head" = INT8): ``k`` / ``v``
-    uint8 [L, num_blocks, Hkv, bs, 128] with one fp32 scale per (block, head, row) in ``k_scale`` / ``v_scale``
-    [L, num_blocks, Hkv, bs].  Rows reach it through a bf16 staging cache (the fused norm + RoPE kernel writes there)
-    and ``kv8_quantize``."""
+    """Quantised paged cache of one attention layer set: ``fmt`` "fp8" = E4M3 keys and values, "int8_per_token_head" =
+    INT8, "turboquant_k8v4" = E4M3 keys + 4-bit affine values.  ``k`` uint8 [L, num_blocks, Hkv, bs, 128], ``v`` the
+    same (64 bytes per row for 4-bit values), one fp32 scale per (block, head, row) in ``k_scale`` / ``v_scale``
+    [L, num_blocks, Hkv, bs] and, for 4-bit values, the row minimum in ``v_min``.  Rows reach it through a bf16
+    staging cache (the fused norm + RoPE kernel writes there) and ``kv8_quantize``."""
 
     def __init__(self, fmt: str, layers: int, num_blocks: int, hkv: int, block_size: int, device):
         self.fmt = KV8_FORMATS[fmt]
         self.k = torch.zeros(layers, num_blocks, hkv, block_size, D, dtype=torch.uint8, device=device)
-        self.v = torch.zeros_like(self.k)
+        self.v = torch.zeros(layers, num_blocks, hkv, block_size, D // 2 if self.fmt == 3 else D, dtype=torch.uint8,
+                             device=device)
         self.k_scale = torch.zeros(layers, num_blocks, hkv, block_size, dtype=torch.float32, device=device)
         self.v_scale = torch.zeros_like(self.k_scale)
+        self.v_min = torch.zeros_like(self.k_scale) if self.fmt == 3 else None
+
+    def layer(self, idx: int):
+        """(k, v, k_scale, v_scale, v_min) views of one layer."""
+        return self.k[idx], self.v[idx], self.k_scale[idx], self.v_scale[idx], None if self.v_min is None else self.v_min[idx]
 
     def nbytes(self) -> int:
-        return 2 * self.k.numel() + 8 * self.k_scale.numel()
+        return self.k.numel() + self.v.numel() + 4 * self.k_scale.numel() * (3 if self.fmt == 3 else 2)
 
 
-def kv8_quantize(fmt: int, stage_k, stage_v, src_slots, dst_slots, k8, v8, k_scale, v_scale):
-    """Quantise staged rows ``src_slots`` (bf16 [nb_s, Hkv, bs_s, 128]) into rows ``dst_slots`` of the 8-bit cache."""
+def kv8_quantize(fmt: int, stage_k, stage_v, src_slots, dst_slots, k8, v8, k_scale, v_scale, v_min=None):
+    """Quantise staged rows ``src_slots`` (bf16 [nb_s, Hkv, bs_s, 128]) into rows ``dst_slots`` of the cache."""
     rc = _lib.lib().b200_kv8_quantize(_lib.ptr(stage_k), _lib.ptr(stage_v), _lib.ptr(src_slots), _lib.ptr(dst_slots),
-                                      _lib.ptr(k8), _lib.ptr(v8), _lib.ptr(k_scale), _lib.ptr(v_scale), stage_k.shape[2],
-                                      k8.shape[2], src_slots.numel(), k8.shape[1], int(fmt), _lib.stream())
+                                      _lib.ptr(k8), _lib.ptr(v8), _lib.ptr(k_scale), _lib.ptr(v_scale), _lib.ptr(v_min),
+                                      stage_k.shape[2], k8.shape[2], src_slots.numel(), k8.shape[1], int(fmt), _lib.stream())
     _lib.check(rc, "kv8_quantize")
 
 
-def kv8_dequantize(fmt: int, k8, v8, k_scale, v_scale, block_table_row, n_tokens: int, stage_k, stage_v):
+def kv8_dequantize(fmt: int, k8, v8, k_scale, v_scale, block_table_row, n_tokens: int, stage_k, stage_v, v_min=None):
     """Dequantise the first ``n_tokens`` positions of one sequence into the staging caches (blocks 0, 1, 2, ...)."""
     if n_tokens <= 0:
         return
     assert stage_k.shape[2] == k8.shape[2] and stage_k.shape[0] * stage_k.shape[2] >= n_tokens
-    rc = _lib.lib().b200_kv8_dequantize(_lib.ptr(k8), _lib.ptr(v8), _lib.ptr(k_scale), _lib.ptr(v_scale),
+    rc = _lib.lib().b200_kv8_dequantize(_lib.ptr(k8), _lib.ptr(v8), _lib.ptr(k_scale), _lib.ptr(v_scale), _lib.ptr(v_min),
                                         _lib.ptr(block_table_row), _lib.ptr(stage_k), _lib.ptr(stage_v), k8.shape[2],
                                         int(n_tokens), k8.shape[1], int(fmt), _lib.stream())
     _lib.check(rc, "kv8_dequantize")
 
 
 def decode_kv8(fmt: int, q, k8, v8, k_scale, v_scale, block_table, kv_len, gate=None, scale=None, splits: int | None = None,
-               max_kv_len: int | None = None, window: int = 0, sinks: int = 0):
-    """``decode`` over an 8-bit cache; rows are dequantised in registers."""
+               max_kv_len: int | None = None, window: int = 0, sinks: int = 0, v_min=None):
+    """``decode`` over a quantised cache; rows are dequantised in registers."""
     b, hq, d = q.shape
     nb, hkv, bs, _ = k8.shape
     out = torch.empty_like(q)
@@ -174,7 +181,7 @@ def decode_kv8(fmt: int, q, k8, v8, k_scale, v_scale, block_table, kv_len, gate=
             ws = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device)
             _dec_ws[dev] = ws
     rc = _lib.lib().b200_gqa_decode_kv8(int(fmt), _lib.ptr(q), _lib.ptr(k8), _lib.ptr(v8), _lib.ptr(k_scale),
-                                        _lib.ptr(v_scale), _lib.ptr(out), _lib.ptr(gate), _lib.ptr(block_table),
+                                        _lib.ptr(v_scale), _lib.ptr(v_min), _lib.ptr(out), _lib.ptr(gate), _lib.ptr(block_table),
                                         _lib.ptr(kv_len), _lib.ptr(ws), b, block_table.shape[1], bs, hq, hkv, splits,
                                         _f(scale), int(window), int(sinks), _lib.stream())
     _lib.check(rc, "gqa_decode_kv8", 2 if splits > 1 else 1)

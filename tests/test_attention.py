@@ -167,29 +167,32 @@ def test_sliding_window_with_sinks_prefill_and_decode(window, sinks):
         assert (od.float() - want[-1:]).abs().max() < 2e-2, splits
 
 
-@pytest.mark.parametrize("fmt,tol", [("fp8", 0.04), ("int8_per_token_head", 0.006)])
-def test_kv8_cache_roundtrip_and_decode(fmt, tol):
-    """Quantising append into the 8-bit cache, its dequantisation back to staging, and decode attention reading the
-    8-bit rows directly (against the fp32 oracle on the dequantised rows)."""
+@pytest.mark.parametrize("fmt,tol_k,tol_v", [("fp8", 0.04, 0.04), ("int8_per_token_head", 0.006, 0.006),
+                                              ("turboquant_k8v4", 0.04, 0.16)])
+def test_kv8_cache_roundtrip_and_decode(fmt, tol_k, tol_v):
+    """Quantising append into the quantised cache, its dequantisation back to staging, and decode attention reading
+    the quantised rows directly (against the fp32 oracle on the dequantised rows)."""
     from deepseek_v4_2080ti_b200.ops import _lib, attention
     torch.manual_seed(5)
     hkv, hq, bs, t = 2, 6, 64, 333
     nblk = (t + bs - 1) // bs
     k = (torch.randn(t, hkv, 128, device="cuda") * torch.rand(t, hkv, 1, device="cuda") * 3).bfloat16()
-    v = torch.randn(t, hkv, 128, device="cuda").bfloat16()
+    v = (torch.randn(t, hkv, 128, device="cuda") + 0.3).bfloat16()
     stage_k = torch.zeros(nblk, hkv, bs, 128, dtype=torch.bfloat16, device="cuda")
     stage_v = torch.zeros_like(stage_k)
     pos = torch.arange(t, device="cuda")
     stage_k[pos // bs, :, pos % bs] = k
     stage_v[pos // bs, :, pos % bs] = v
     cache = attention.Kv8Cache(fmt, 1, nblk + 4, hkv, bs, "cuda")
+    k8, v8, ks, vs, vm = cache.layer(0)
+    assert v8.shape[-1] == (64 if fmt == "turboquant_k8v4" else 128)
     perm = torch.randperm(nblk + 3, device="cuda")[:nblk].to(torch.int32) + 1
     dst = (perm[(pos // bs).long()] * bs + pos % bs).to(torch.int32)
     src = pos.to(torch.int32)
     src[7], dst[7] = -1, -1                               # skipped row stays zero
-    attention.kv8_quantize(cache.fmt, stage_k, stage_v, src, dst, cache.k[0], cache.v[0], cache.k_scale[0], cache.v_scale[0])
+    attention.kv8_quantize(cache.fmt, stage_k, stage_v, src, dst, k8, v8, ks, vs, vm)
     back_k, back_v = torch.zeros_like(stage_k), torch.zeros_like(stage_v)
-    attention.kv8_dequantize(cache.fmt, cache.k[0], cache.v[0], cache.k_scale[0], cache.v_scale[0], perm, t, back_k, back_v)
+    attention.kv8_dequantize(cache.fmt, k8, v8, ks, vs, perm, t, back_k, back_v, vm)
     torch.cuda.synchronize()
     _lib.check_status()
     kd = back_k[pos // bs, :, pos % bs].float()
@@ -197,27 +200,34 @@ def test_kv8_cache_roundtrip_and_decode(fmt, tol):
     assert kd[7].abs().max().item() == 0
     keep = torch.ones(t, dtype=torch.bool, device="cuda")
     keep[7] = False
-    for got, want in ((kd, k.float()), (vd, v.float())):
+    for got, want, tol in ((kd, k.float(), tol_k), (vd, v.float(), tol_v)):
         rel = (got[keep] - want[keep]).norm(dim=-1) / want[keep].norm(dim=-1)
         assert rel.max().item() < tol, rel.max().item()
     q = torch.randn(1, hq, 128, device="cuda").bfloat16()
     gate = torch.randn(1, hq, 128, device="cuda").bfloat16()
     kv_len = torch.tensor([t], dtype=torch.int32, device="cuda")
     # the oracle sees the cache's exact values (scale * code, before the staging copy's bf16 rounding)
-    codes_k, codes_v = cache.k[0][perm.long()], cache.v[0][perm.long()]      # [nblk, hkv, bs, 128]
-    if fmt == "fp8":
-        fk, fv = codes_k.view(torch.float8_e4m3fn).float(), codes_v.view(torch.float8_e4m3fn).float()
+    pl = perm.long()
+
+    def codes(c8):
+        if fmt == "int8_per_token_head":
+            return c8[pl].view(torch.int8).float()
+        return c8[pl].view(torch.float8_e4m3fn).float()
+
+    fk = codes(k8) * ks[pl][..., None]
+    if fmt == "turboquant_k8v4":
+        nib = torch.stack([v8[pl] & 15, v8[pl] >> 4], -1).flatten(-2).float()          # even dim in the low nibble
+        fv = nib * vs[pl][..., None] + vm[pl][..., None]
     else:
-        fk, fv = codes_k.view(torch.int8).float(), codes_v.view(torch.int8).float()
-    fk = (fk * cache.k_scale[0][perm.long()][..., None]).permute(0, 2, 1, 3).reshape(-1, hkv, 128)[:t]
-    fv = (fv * cache.v_scale[0][perm.long()][..., None]).permute(0, 2, 1, 3).reshape(-1, hkv, 128)[:t]
+        fv = codes(v8) * vs[pl][..., None]
+    fk = fk.permute(0, 2, 1, 3).reshape(-1, hkv, 128)[:t]
+    fv = fv.permute(0, 2, 1, 3).reshape(-1, hkv, 128)[:t]
     ref = attention.attention_ref(q, fk, fv, t - 1, gate)
+    bt = perm[None].contiguous()
     for splits in (1, 3):
-        out = attention.decode_kv8(cache.fmt, q, cache.k[0], cache.v[0], cache.k_scale[0], cache.v_scale[0], perm[None].contiguous(),
-                                   kv_len, gate=gate, splits=splits, max_kv_len=t)
+        out = attention.decode_kv8(cache.fmt, q, k8, v8, ks, vs, bt, kv_len, gate=gate, splits=splits, max_kv_len=t, v_min=vm)
         assert (out.float() - ref).abs().max().item() < 2e-2
-    win = attention.decode_kv8(cache.fmt, q, cache.k[0], cache.v[0], cache.k_scale[0], cache.v_scale[0], perm[None].contiguous(),
-                               kv_len, splits=2, max_kv_len=t, window=64, sinks=4)
+    win = attention.decode_kv8(cache.fmt, q, k8, v8, ks, vs, bt, kv_len, splits=2, max_kv_len=t, window=64, sinks=4, v_min=vm)
     vis = torch.cat([torch.arange(4, device="cuda"), torch.arange(t - 64, t, device="cuda")])
     ref_w = attention.attention_ref(q, fk[vis], fv[vis], vis.numel() - 1)
     assert (win.float() - ref_w).abs().max().item() < 2e-2

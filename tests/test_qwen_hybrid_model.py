@@ -73,8 +73,8 @@ def test_batched_decode_equals_serial():
         assert out[1:] == [step[i] for step in batched], (i, out, batched)
 
 
-@pytest.mark.parametrize("kv", ["fp8", "int8_per_token_head"])
-def test_8bit_kv_cache_tracks_the_bf16_cache(kv):
+@pytest.mark.parametrize("kv", ["fp8", "int8_per_token_head", "turboquant_k8v4"])
+def test_quantised_kv_cache_tracks_the_bf16_cache(kv):
     """Chunked prefill + graph decode with an 8-bit KV cache: logits stay close to the bf16-cache runtime's and the
     greedy stream mostly agrees; the cache really is one byte per element."""
     from deepseek_v4_2080ti_b200.ops import _lib
@@ -89,13 +89,13 @@ def test_8bit_kv_cache_tracks_the_bf16_cache(kv):
     _lib.check_status()
     la, lb = rt.last_logits.float(), rt8.last_logits.float()
     cos = torch.nn.functional.cosine_similarity(la, lb, dim=-1).min().item()
-    assert cos > (0.995 if kv == "fp8" else 0.9995), cos
+    assert cos > {"fp8": 0.995, "int8_per_token_head": 0.9995, "turboquant_k8v4": 0.97}[kv], cos
     agree, ca, cb = int(na.item() == nb.item()), na, nb
     for _ in range(8):
         ca = rt.decode([a], ca.to(torch.int32))
         cb = rt8.decode([b], ca.to(torch.int32))       # teacher-forced with the bf16 stream
         agree += int(ca.item() == cb.item())
-    assert agree >= 7, agree
+    assert agree >= (5 if kv == "turboquant_k8v4" else 7), agree
     # batched decode through the generic path as well (two slots, second sequence short)
     c = rt8.allocate()
     rt8.prefill(c, ids[:40])
