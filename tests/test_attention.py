@@ -167,7 +167,7 @@ def test_sliding_window_with_sinks_prefill_and_decode(window, sinks):
         assert (od.float() - want[-1:]).abs().max() < 2e-2, splits
 
 
-@pytest.mark.parametrize("fmt,tol_k,tol_v", [("fp8", 0.04, 0.04), ("int8_per_token_head", 0.006, 0.006),
+@pytest.mark.parametrize("fmt,tol_k,tol_v", [("fp8", 0.04, 0.04), ("int8_per_token_head", 0.015, 0.015),
                                               ("turboquant_k8v4", 0.04, 0.16)])
 def test_kv8_cache_roundtrip_and_decode(fmt, tol_k, tol_v):
     """Quantising append into the quantised cache, its dequantisation back to staging, and decode attention reading

@@ -90,11 +90,12 @@ def test_quantised_kv_cache_tracks_the_bf16_cache(kv):
     la, lb = rt.last_logits.float(), rt8.last_logits.float()
     cos = torch.nn.functional.cosine_similarity(la, lb, dim=-1).min().item()
     assert cos > {"fp8": 0.995, "int8_per_token_head": 0.9995, "turboquant_k8v4": 0.97}[kv], cos
-    agree, ca, cb = int(na.item() == nb.item()), na, nb
+    agree, prev = int(na.item() == nb.item()), na.to(torch.int32).clone()
     for _ in range(8):
-        ca = rt.decode([a], ca.to(torch.int32))
-        cb = rt8.decode([b], ca.to(torch.int32))       # teacher-forced with the bf16 stream
+        ca = rt.decode([a], prev).clone()
+        cb = rt8.decode([b], prev)                     # teacher-forced with the bf16 stream
         agree += int(ca.item() == cb.item())
+        prev = ca.to(torch.int32)
     assert agree >= (5 if kv == "turboquant_k8v4" else 7), agree
     # batched decode through the generic path as well (two slots, second sequence short)
     c = rt8.allocate()
