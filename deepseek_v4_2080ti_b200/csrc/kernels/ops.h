@@ -138,6 +138,15 @@ int b200_gqa_decode_ex(const void* q, const void* k_cache, const void* v_cache, 
 int b200_gqa_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const void* gate,
                     const int* block_table, const int* kv_len, float* workspace, int batch, int max_blocks,
                     int block_size, int n_q_heads, int n_kv_heads, int splits, float softmax_scale, cudaStream_t stream);
+// FlashMemory retriever (flashmemory.cu): chunk scores of one scorer layer, layer ensemble, top-k, index offset
+int b200_fm_score_layer(const float* hidden, const void* wq_a, const void* wq_b, const float* q_norm, const void* weights_proj,
+                        const float* inv_freqs, const void* keys8, const float* keysf, float* q_scratch, float* qlora_scratch,
+                        float* fused_w, float* scores, int n_chunks, int heads, int q_lora, int hidden_dim, int rope_dim,
+                        float eps, long long position, int apply_sigmoid, cudaStream_t stream);
+int b200_fm_ensemble(const float* layer_scores, int n_layers, int n_chunks, int stride, int use_max, float* out,
+                     cudaStream_t stream);
+int b200_fm_topk(const float* scores, int n_chunks, int keep, int* out_idx, float* out_val, cudaStream_t stream);
+int b200_fm_write_global_indices(const int* logical, int keep, int offset, int* out, cudaStream_t stream);
 // Quantised KV cache (fmt 1 = E4M3, 2 = INT8, 3 = E4M3 keys + 4-bit values with v_min) with per-(token, head) fp32
 // scales (kv8.cu, attn_gqa_decode.cu)
 int b200_gqa_decode_kv8(int fmt, const void* q, const void* k8, const void* v8, const float* k_scale, const float* v_scale,
