@@ -277,13 +277,6 @@ gdn_prepare_kernel(const __nv_bfloat16* __restrict__ mixed, int ld, int q_off, i
   }
 }
 
-// ------------------------------------------------------------ inter-chunk scan
-constexpr int SL = 32;    // value columns per CTA
-constexpr int WS = 136;   // padded row (halves) of the [64 x 128] W / Qg tiles and of the [32 x 128] state copy
-constexpr int TS = 72;    // padded row (halves) of the [. x 64] tiles (KgT, Aqk, v_new^T)
-constexpr int SCAN_BUF_HALVES = 2 * C * WS + DK * TS + C * TS;            // W, Qg, KgT, Aqk of one chunk
-constexpr int SCAN_SMEM_BYTES = (2 * SCAN_BUF_HALVES + SL * WS + SL * TS) * 2;
-
 __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -304,6 +297,247 @@ __device__ __forceinline__ void load_a(uint32_t (&a)[4], const __half* tile, int
   a[2] = *reinterpret_cast<const uint32_t*>(p + 8);
   a[3] = *reinterpret_cast<const uint32_t*>(p + 8 * ld + 8);
 }
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Tensor-core form of gdn_prepare_kernel: the four products of a chunk (k k^T, q k^T, T (beta v), T (beta e^gc k)) run
+// as m16n8k16 MMAs on fp16 copies of the normalised rows; only the 64-step forward substitution stays scalar (warp 0,
+// fp32).  Shared memory: three [64 x 128] fp16 tiles (k_hat, q_hat, v), the fp32 triangular matrix; the two fp16
+// T tiles reuse the q_hat tile and the triangular matrix once those are dead, which keeps three CTAs on an SM.
+constexpr int LDH = 136;  // padded row (halves) of the [64 x 128] tiles: fragment loads hit 32 distinct banks
+constexpr int TSH = 72;   // padded row (halves) of the [64 x 64] T tiles
+constexpr int PREP_MMA_SMEM = 3 * C * LDH * 2 + C * AP * 4 + 2 * C * 4;
+
+__global__ void __launch_bounds__(256, 3)
+gdn_prepare_mma_kernel(const __nv_bfloat16* __restrict__ mixed, int ld, int q_off, int k_off, int v_off,
+                       const float* __restrict__ g, const float* __restrict__ beta, PrepOut o, int T, int Hv, int Hk,
+                       float q_scale) {
+  extern __shared__ __align__(16) unsigned char prep_raw[];
+  __half* sKh = reinterpret_cast<__half*>(prep_raw);   // [64][LDH] k_hat
+  __half* sQh = sKh + C * LDH;                         // [64][LDH] q_hat * scale
+  __half* sVh = sQh + C * LDH;                         // [64][LDH] v
+  float* sA = reinterpret_cast<float*>(sVh + C * LDH); // [64][AP]  T - I (strictly lower triangular)
+  float* sgc = sA + C * AP;                            // [64] cumulative log decay
+  float* sbeta = sgc + C;                              // [64]
+  __half* sTb = sQh;                                   // [64][TSH] T diag(beta)            (after the q k^T product)
+  __half* sTw = reinterpret_cast<__half*>(sA);         // [64][TSH] T diag(beta e^gc)       (after the substitution)
+  const int h = blockIdx.x, c = blockIdx.y;
+  const int kh = h / (Hv / Hk);
+  const int t0 = c * C;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tig = lane & 3;
+
+  if (warp == 0) {
+    const int ta = t0 + lane, tb = t0 + 32 + lane;
+    float ga = ta < T ? g[(size_t)ta * Hv + h] : 0.f;
+    float gb = tb < T ? g[(size_t)tb * Hv + h] : 0.f;
+#pragma unroll
+    for (int ofs = 1; ofs < 32; ofs <<= 1) {
+      const float x = __shfl_up_sync(0xffffffffu, ga, ofs);
+      const float y = __shfl_up_sync(0xffffffffu, gb, ofs);
+      if (lane >= ofs) { ga += x; gb += y; }
+    }
+    gb += __shfl_sync(0xffffffffu, ga, 31);
+    sgc[lane] = ga;
+    sgc[32 + lane] = gb;
+    sbeta[lane] = ta < T ? beta[(size_t)ta * Hv + h] : 0.f;
+    sbeta[32 + lane] = tb < T ? beta[(size_t)tb * Hv + h] : 0.f;
+  }
+  __syncthreads();
+
+  // rows: normalise, keep fp16 copies, write q_hat e^gc
+  for (int r = warp; r < C; r += 8) {
+    const int t = t0 + r;
+    float kf[4] = {0, 0, 0, 0}, qf[4] = {0, 0, 0, 0}, vf[4] = {0, 0, 0, 0};
+    if (t < T) {
+      const __nv_bfloat16* row = mixed + (size_t)t * ld;
+      const uint2 ku = *reinterpret_cast<const uint2*>(row + k_off + kh * DK + lane * 4);
+      const uint2 qu = *reinterpret_cast<const uint2*>(row + q_off + kh * DK + lane * 4);
+      const uint2 vu = *reinterpret_cast<const uint2*>(row + v_off + h * DV + lane * 4);
+      const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&ku);
+      const __nv_bfloat162* q2 = reinterpret_cast<const __nv_bfloat162*>(&qu);
+      const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vu);
+      float2 a = __bfloat1622float2(k2[0]), bb = __bfloat1622float2(k2[1]);
+      kf[0] = a.x; kf[1] = a.y; kf[2] = bb.x; kf[3] = bb.y;
+      a = __bfloat1622float2(q2[0]); bb = __bfloat1622float2(q2[1]);
+      qf[0] = a.x; qf[1] = a.y; qf[2] = bb.x; qf[3] = bb.y;
+      a = __bfloat1622float2(v2[0]); bb = __bfloat1622float2(v2[1]);
+      vf[0] = a.x; vf[1] = a.y; vf[2] = bb.x; vf[3] = bb.y;
+    }
+    const float kn = rsqrtf(warp_sum(kf[0] * kf[0] + kf[1] * kf[1] + kf[2] * kf[2] + kf[3] * kf[3]) + 1e-6f);
+    const float qn = rsqrtf(warp_sum(qf[0] * qf[0] + qf[1] * qf[1] + qf[2] * qf[2] + qf[3] * qf[3]) + 1e-6f) * q_scale;
+    uint2 pk;
+    pk.x = pack_h2(kf[0] * kn, kf[1] * kn); pk.y = pack_h2(kf[2] * kn, kf[3] * kn);
+    *reinterpret_cast<uint2*>(sKh + r * LDH + lane * 4) = pk;
+    pk.x = pack_h2(qf[0] * qn, qf[1] * qn); pk.y = pack_h2(qf[2] * qn, qf[3] * qn);
+    *reinterpret_cast<uint2*>(sQh + r * LDH + lane * 4) = pk;
+    pk.x = pack_h2(vf[0], vf[1]); pk.y = pack_h2(vf[2], vf[3]);
+    *reinterpret_cast<uint2*>(sVh + r * LDH + lane * 4) = pk;
+    const float eg = __expf(sgc[r]) * qn;
+    pk.x = pack_h2(qf[0] * eg, qf[1] * eg); pk.y = pack_h2(qf[2] * eg, qf[3] * eg);
+    *reinterpret_cast<uint2*>(o.Qg + ((size_t)(t0 + r) * Hv + h) * DK + lane * 4) = pk;
+  }
+  __syncthreads();
+
+  // k k^T and q k^T: warp -> rows [16 mt, 16 mt + 16) x columns [32 nh, 32 nh + 32); tiles above the diagonal are skipped
+  {
+    const int mt = warp & 3, nh = warp >> 2;
+    const int last = 16 * mt + 15 - 32 * nh;                 // largest useful column offset inside this warp's half
+    const int ntiles = last < 0 ? 0 : min(4, last / 8 + 1);
+    float akk[4][4], aqk[4][4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) akk[n][e] = aqk[n][e] = 0.f;
+    if (ntiles > 0) {
+#pragma unroll 2
+      for (int ks = 0; ks < DK / 16; ++ks) {
+        uint32_t ak[4], aq[4];
+        load_a(ak, sKh, LDH, 16 * mt, 16 * ks, gq, tig);
+        load_a(aq, sQh, LDH, 16 * mt, 16 * ks, gq, tig);
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+          if (n < ntiles) {
+            const __half* bp = sKh + (size_t)(32 * nh + 8 * n + gq) * LDH + 16 * ks + 2 * tig;
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(bp), b1 = *reinterpret_cast<const uint32_t*>(bp + 8);
+            mma16816(akk[n], ak, b0, b1);
+            mma16816(aqk[n], aq, b0, b1);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int i = 16 * mt + gq + 8 * hf, j = 32 * nh + 8 * n + 2 * tig;
+        const float gi = sgc[i], bi = sbeta[i];
+        float av[2], qv[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int jj = j + e;
+          const float dec = (jj <= i) ? __expf(gi - sgc[jj]) : 0.f;
+          av[e] = (jj < i) ? -bi * akk[n][2 * hf + e] * dec : 0.f;
+          qv[e] = (jj <= i) ? aqk[n][2 * hf + e] * dec : 0.f;
+        }
+        sA[i * AP + j] = av[0];
+        sA[i * AP + j + 1] = av[1];
+        *reinterpret_cast<uint32_t*>(o.Aqk + ((size_t)(t0 + i) * Hv + h) * C + j) = pack_h2(qv[0], qv[1]);
+      }
+  }
+  __syncthreads();
+
+  // forward substitution: row i <- row i + row i * A[:i, :i]   (warp 0, lanes own columns j and j + 32; four partial
+  // sums per column shorten the dependent chain)
+  if (warp == 0) {
+    for (int i = 1; i < C; ++i) {
+      float n0[4] = {0.f, 0.f, 0.f, 0.f}, n1[4] = {0.f, 0.f, 0.f, 0.f};
+      const float* Ai = sA + i * AP;
+      int m = 0;
+      for (; m + 4 <= i; m += 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float aim = Ai[m + e];
+          n0[e] += aim * sA[(m + e) * AP + lane];
+          n1[e] += aim * sA[(m + e) * AP + 32 + lane];
+        }
+      }
+      for (; m < i; ++m) {
+        const float aim = Ai[m];
+        n0[0] += aim * sA[m * AP + lane];
+        n1[0] += aim * sA[m * AP + 32 + lane];
+      }
+      __syncwarp();
+      if (lane < i) sA[i * AP + lane] += (n0[0] + n0[1]) + (n0[2] + n0[3]);
+      if (32 + lane < i) sA[i * AP + 32 + lane] += (n1[0] + n1[1]) + (n1[2] + n1[3]);
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+
+  // T = A + I as fp16 A operands with beta (and e^gc) folded into the columns
+  {
+    const int i = tid >> 2, j0 = (tid & 3) * 16;
+    float tv[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) tv[e] = sA[i * AP + j0 + e] + ((j0 + e) == i ? 1.f : 0.f);
+    __syncthreads();                                          // every read of sA is done before sTw overwrites it
+#pragma unroll
+    for (int e = 0; e < 16; e += 2) {
+      const float b0 = sbeta[j0 + e], b1 = sbeta[j0 + e + 1];
+      *reinterpret_cast<uint32_t*>(sTb + i * TSH + j0 + e) = pack_h2(tv[e] * b0, tv[e + 1] * b1);
+      *reinterpret_cast<uint32_t*>(sTw + i * TSH + j0 + e) =
+          pack_h2(tv[e] * b0 * __expf(sgc[j0 + e]), tv[e + 1] * b1 * __expf(sgc[j0 + e + 1]));
+    }
+  }
+  __syncthreads();
+
+  // W = Tw k_hat and U = Tb v: warp -> rows [16 mt, +16) x columns [64 nh, +64); k-steps past the diagonal are zero
+  {
+    const int mt = warp & 3, nh = warp >> 2;
+#pragma unroll 1
+    for (int which = 0; which < 2; ++which) {
+      const __half* tA = which ? sTb : sTw;
+      const __half* tB = which ? sVh : sKh;
+      float acc[8][4];
+#pragma unroll
+      for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
+      for (int kk = 0; kk <= mt; ++kk) {
+        uint32_t a[4];
+        load_a(a, tA, TSH, 16 * mt, 16 * kk, gq, tig);
+#pragma unroll
+        for (int n = 0; n < 8; n += 2) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, tB + (size_t)(16 * kk + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + 64 * nh + (n + (lane >> 4)) * 8);
+          mma16816(acc[n], a, b[0], b[1]);
+          mma16816(acc[n + 1], a, b[2], b[3]);
+        }
+      }
+#pragma unroll
+      for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int i = 16 * mt + gq + 8 * hf, col = 64 * nh + 8 * n + 2 * tig;
+          const size_t base = ((size_t)(t0 + i) * Hv + h) * DK + col;
+          if (which) *reinterpret_cast<float2*>(o.U + base) = make_float2(acc[n][2 * hf], acc[n][2 * hf + 1]);
+          else *reinterpret_cast<uint32_t*>(o.W + base) = pack_h2(acc[n][2 * hf], acc[n][2 * hf + 1]);
+        }
+    }
+  }
+
+  // (k_hat e^(gc_last - gc))^T: key dim major, eight tokens (16 bytes) per store, eight lanes cover one key dim's row
+  {
+    const float gl = sgc[C - 1];
+    const int seg = tid & 7;
+    float ek[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ek[e] = __expf(gl - sgc[8 * seg + e]);
+    for (int d = tid >> 3; d < DK; d += 32) {
+      float kv[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) kv[e] = __half2float(sKh[(8 * seg + e) * LDH + d]) * ek[e];
+      uint4 pk;
+      pk.x = pack_h2(kv[0], kv[1]); pk.y = pack_h2(kv[2], kv[3]); pk.z = pack_h2(kv[4], kv[5]); pk.w = pack_h2(kv[6], kv[7]);
+      *reinterpret_cast<uint4*>(o.KgT + (((size_t)c * Hv + h) * DK + d) * C + 8 * seg) = pk;
+    }
+    if (tid == 0) o.Gl[(size_t)c * Hv + h] = __expf(gl);
+  }
+}
+// ------------------------------------------------------------ inter-chunk scan
+constexpr int SL = 32;    // value columns per CTA
+constexpr int WS = 136;   // padded row (halves) of the [64 x 128] W / Qg tiles and of the [32 x 128] state copy
+constexpr int TS = 72;    // padded row (halves) of the [. x 64] tiles (KgT, Aqk, v_new^T)
+constexpr int SCAN_BUF_HALVES = 2 * C * WS + DK * TS + C * TS;            // W, Qg, KgT, Aqk of one chunk
+constexpr int SCAN_SMEM_BYTES = (2 * SCAN_BUF_HALVES + SL * WS + SL * TS) * 2;
 
 // grid (Hv, 128 / SL), 128 threads.  Warp w owns tokens [16w, 16w+16) of the chunk for v_new and O, and state rows
 // (key dims) [32w, 32w+32) for the state update.
@@ -475,7 +709,16 @@ gdn_scan_kernel(PrepOut w, float* __restrict__ state, __nv_bfloat16* __restrict_
 
 }  // namespace
 
+static int g_prepare_simt = 0;
+
 extern "C" {
+
+// 1: run the chunk preparation with the scalar fp32 kernel (kept as the numerical yardstick of the tensor-core one).
+int b200_gdn_use_simt_prepare(int on) {
+  const int was = g_prepare_simt;
+  g_prepare_simt = on ? 1 : 0;
+  return was;
+}
 
 // Floats of workspace needed by b200_gdn_chunked for T tokens and Hv value heads.
 long long b200_gdn_workspace_floats(int T, int Hv) {
@@ -506,12 +749,18 @@ int b200_gdn_chunked(const void* mixed, int ld, int q_off, int k_off, int v_off,
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gdn_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, prep_smem);
     if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gdn_prepare_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PREP_MMA_SMEM);
+    if (e == cudaSuccess)
       e = cudaFuncSetAttribute(gdn_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, scan_smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  gdn_prepare_kernel<<<dim3(Hv, nch), 256, prep_smem, stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(mixed), ld, q_off, k_off, v_off, g, beta, o, T, Hv, Hk, q_scale);
+  if (g_prepare_simt)
+    gdn_prepare_kernel<<<dim3(Hv, nch), 256, prep_smem, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(mixed), ld, q_off, k_off, v_off, g, beta, o, T, Hv, Hk, q_scale);
+  else
+    gdn_prepare_mma_kernel<<<dim3(Hv, nch), 256, PREP_MMA_SMEM, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(mixed), ld, q_off, k_off, v_off, g, beta, o, T, Hv, Hk, q_scale);
   gdn_scan_kernel<<<dim3(Hv, DV / SL), 128, scan_smem, stream>>>(o, state, reinterpret_cast<__nv_bfloat16*>(out), T,
                                                                   nch, Hv);
   return (int)cudaGetLastError();

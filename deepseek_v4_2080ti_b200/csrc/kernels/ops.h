@@ -109,6 +109,7 @@ int b200_gdn_gates(const void* ab, int ld, int a_off, int b_off, const float* a_
 int b200_argmax(const void* logits, int is_f32, int ld, int n, int rows, int index_offset, int* out_idx, float* out_val,
                 cudaStream_t stream);
 long long b200_gdn_workspace_floats(int T, int Hv);
+int b200_gdn_use_simt_prepare(int on);
 int b200_gdn_chunked(const void* mixed, int ld, int q_off, int k_off, int v_off, const float* g, const float* beta,
                      float* state, void* out, float* workspace, int T, int Hv, int Hk, cudaStream_t stream);
 int b200_qk_norm_rope_append(const void* q_src, int ldq, int q_off, int q_head_stride, int gate_in_q, const void* k_src,

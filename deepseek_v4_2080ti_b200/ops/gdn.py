@@ -33,6 +33,12 @@ def chunked(mixed, q_off, k_off, v_off, g, beta, state, hv, hk):
     return out
 
 
+def use_simt_prepare(on: bool) -> bool:
+    """Route the chunk preparation of ``chunked`` through the scalar fp32 kernel (the yardstick of the tensor-core
+    one); returns the previous setting."""
+    return bool(_lib.lib().b200_gdn_use_simt_prepare(int(bool(on))))
+
+
 def step(states, slot_ids, mixed, q_off, k_off, v_off, g, beta, hv, hk):
     """states [slots, Hv, 128, 128] fp32 in place; mixed [B, ld]; returns [B, Hv, 128] bf16."""
     b = mixed.shape[0]

@@ -35,6 +35,24 @@ def test_chunked_matches_recurrence(t, hk, hv):
     assert (s - want_s).abs().max().item() < 2e-3 * max(1.0, want_s.abs().max().item())
 
 
+def test_tensor_core_prepare_tracks_the_scalar_prepare():
+    """The m16n8k16 chunk preparation (fp16 operands) against the fp32 scalar kernel on the same inputs, ragged tail
+    and several heads included."""
+    from deepseek_v4_2080ti_b200.ops import gdn
+    mixed, g, beta, state = _inputs(1000, 2, 4, 11)
+    s_mma, s_simt = state.clone(), state.clone()
+    o_mma = gdn.chunked(mixed, 0, 256, 512, g, beta, s_mma, 4, 2)
+    was = gdn.use_simt_prepare(True)
+    try:
+        o_simt = gdn.chunked(mixed, 0, 256, 512, g, beta, s_simt, 4, 2)
+    finally:
+        gdn.use_simt_prepare(was)
+    torch.cuda.synchronize()
+    scale = max(1.0, o_simt.float().abs().max().item())
+    assert (o_mma.float() - o_simt.float()).abs().max().item() < 1e-2 * scale
+    assert (s_mma - s_simt).abs().max().item() < 2e-3 * max(1.0, s_simt.abs().max().item())
+
+
 def test_two_calls_equal_one():
     from deepseek_v4_2080ti_b200.ops import gdn
     mixed, g, beta, state = _inputs(200, 2, 4, 3)
