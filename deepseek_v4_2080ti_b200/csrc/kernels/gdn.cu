@@ -288,6 +288,7 @@ __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_1() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
 // A fragment (16 rows x 16 k) of a row-major fp16 tile with row stride `ld` halves.
 __device__ __forceinline__ void load_a(uint32_t (&a)[4], const __half* tile, int ld, int row0, int k0, int g, int tig) {
@@ -309,9 +310,10 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 }
 
 // Tensor-core form of gdn_prepare_kernel: the four products of a chunk (k k^T, q k^T, T (beta v), T (beta e^gc k)) run
-// as m16n8k16 MMAs on fp16 copies of the normalised rows; only the 64-step forward substitution stays scalar (warp 0,
-// fp32).  Shared memory: three [64 x 128] fp16 tiles (k_hat, q_hat, v), the fp32 triangular matrix; the two fp16
-// T tiles reuse the q_hat tile and the triangular matrix once those are dead, which keeps three CTAs on an SM.
+// as m16n8k16 MMAs on fp16 copies of the normalised rows; the triangular inverse stays scalar fp32 but runs by blocks
+// of 16 over the whole CTA.  Shared memory: three [64 x 128] fp16 tiles (k_hat, q_hat, v), the fp32 triangular
+// matrix; the inverse and the two fp16 T tiles reuse the q_hat tile and the triangular matrix once those are dead,
+// which keeps three CTAs on an SM.
 constexpr int LDH = 136;  // padded row (halves) of the [64 x 128] tiles: fragment loads hit 32 distinct banks
 constexpr int TSH = 72;   // padded row (halves) of the [64 x 64] T tiles
 constexpr int PREP_MMA_SMEM = 3 * C * LDH * 2 + C * AP * 4 + 2 * C * 4;
@@ -327,8 +329,8 @@ gdn_prepare_mma_kernel(const __nv_bfloat16* __restrict__ mixed, int ld, int q_of
   float* sA = reinterpret_cast<float*>(sVh + C * LDH); // [64][AP]  T - I (strictly lower triangular)
   float* sgc = sA + C * AP;                            // [64] cumulative log decay
   float* sbeta = sgc + C;                              // [64]
-  __half* sTb = sQh;                                   // [64][TSH] T diag(beta)            (after the q k^T product)
-  __half* sTw = reinterpret_cast<__half*>(sA);         // [64][TSH] T diag(beta e^gc)       (after the substitution)
+  __half* sTb = reinterpret_cast<__half*>(sA);         // [64][TSH] T diag(beta)            (after the inversion)
+  __half* sTw = sQh;                                   // [64][TSH] T diag(beta e^gc)       (after the inversion)
   const int h = blockIdx.x, c = blockIdx.y;
   const int kh = h / (Hv / Hk);
   const int t0 = c * C;
@@ -434,41 +436,72 @@ gdn_prepare_mma_kernel(const __nv_bfloat16* __restrict__ mixed, int ld, int q_of
   }
   __syncthreads();
 
-  // forward substitution: row i <- row i + row i * A[:i, :i]   (warp 0, lanes own columns j and j + 32; four partial
-  // sums per column shorten the dependent chain)
-  if (warp == 0) {
-    for (int i = 1; i < C; ++i) {
-      float n0[4] = {0.f, 0.f, 0.f, 0.f}, n1[4] = {0.f, 0.f, 0.f, 0.f};
-      const float* Ai = sA + i * AP;
-      int m = 0;
-      for (; m + 4 <= i; m += 4) {
+  // T = (I - A)^-1 by blocks of 16 (A strictly lower triangular, fp32):
+  //   T_ii = (I - A_ii)^-1                       four warps, one diagonal block each, rows in registers
+  //   T_ij = T_ii (sum_{k=j}^{i-1} A_ik T_kj)    one block sub-diagonal at a time, every thread one element per block
+  // T is built in sX (the dead q_hat tile); the inner sums are staged in the unused upper blocks of sA.
+  float* sX = reinterpret_cast<float*>(sQh);                  // [64][AP]
+  if (warp < 4) {
+    if (lane < 16) {
+      const int b0 = 16 * warp;
+      float tr[16];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float aim = Ai[m + e];
-          n0[e] += aim * sA[(m + e) * AP + lane];
-          n1[e] += aim * sA[(m + e) * AP + 32 + lane];
-        }
+      for (int r = 0; r < 16; ++r) {
+        float acc = (lane == r) ? 1.f : 0.f;
+#pragma unroll
+        for (int m = 0; m < r; ++m) acc += sA[(b0 + r) * AP + b0 + m] * tr[m];
+        tr[r] = acc;
+        sX[(b0 + r) * AP + b0 + lane] = acc;
       }
-      for (; m < i; ++m) {
-        const float aim = Ai[m];
-        n0[0] += aim * sA[m * AP + lane];
-        n1[0] += aim * sA[m * AP + 32 + lane];
-      }
-      __syncwarp();
-      if (lane < i) sA[i * AP + lane] += (n0[0] + n0[1]) + (n0[2] + n0[3]);
-      if (32 + lane < i) sA[i * AP + 32 + lane] += (n1[0] + n1[1]) + (n1[2] + n1[3]);
-      __syncwarp();
+    }
+  } else {
+    // blocks above the diagonal are zero: (0,1) (0,2) (0,3) (1,2) (1,3) (2,3)
+    for (int e = (warp - 4) * 32 + lane; e < 6 * 256; e += 128) {
+      const int blk = e >> 8, r = (e >> 4) & 15, cc = e & 15;
+      const int bi = blk < 3 ? 0 : (blk < 5 ? 1 : 2);
+      const int bj = blk < 3 ? blk + 1 : (blk < 5 ? blk - 1 : 3);
+      sX[(16 * bi + r) * AP + 16 * bj + cc] = 0.f;
     }
   }
   __syncthreads();
+  {
+    const int r = tid >> 4, cc = tid & 15;
+#pragma unroll 1
+    for (int d = 1; d < 4; ++d) {
+      float mv[3];
+      for (int b = 0; b + d < 4; ++b) {                       // block (i, j) = (b + d, b)
+        const int bi = b + d, bj = b;
+        float acc = 0.f;
+        for (int k = bj; k < bi; ++k) {
+          const float* ar = sA + (16 * bi + r) * AP + 16 * k;
+          const float* xc = sX + (16 * k) * AP + 16 * bj + cc;
+#pragma unroll
+          for (int m = 0; m < 16; ++m) acc += ar[m] * xc[m * AP];
+        }
+        mv[b] = acc;
+      }
+      for (int b = 0; b + d < 4; ++b) sA[(16 * b + r) * AP + 16 * (b + d) + cc] = mv[b];     // staged at (j, i)
+      __syncthreads();
+      for (int b = 0; b + d < 4; ++b) {
+        const int bi = b + d, bj = b;
+        const float* tr = sX + (16 * bi + r) * AP + 16 * bi;
+        const float* mc = sA + (16 * bj) * AP + 16 * bi + cc;
+        float acc = 0.f;
+#pragma unroll
+        for (int m = 0; m < 16; ++m) acc += tr[m] * mc[m * AP];
+        sX[(16 * bi + r) * AP + 16 * bj + cc] = acc;
+      }
+      __syncthreads();
+    }
+  }
 
-  // T = A + I as fp16 A operands with beta (and e^gc) folded into the columns
+  // T as fp16 A operands with beta (and e^gc) folded into the columns: sTb takes the place of A, sTw that of T
   {
     const int i = tid >> 2, j0 = (tid & 3) * 16;
     float tv[16];
 #pragma unroll
-    for (int e = 0; e < 16; ++e) tv[e] = sA[i * AP + j0 + e] + ((j0 + e) == i ? 1.f : 0.f);
-    __syncthreads();                                          // every read of sA is done before sTw overwrites it
+    for (int e = 0; e < 16; ++e) tv[e] = sX[i * AP + j0 + e];
+    __syncthreads();                                          // every read of sX is done before sTw overwrites it
 #pragma unroll
     for (int e = 0; e < 16; e += 2) {
       const float b0 = sbeta[j0 + e], b1 = sbeta[j0 + e + 1];
@@ -536,23 +569,28 @@ gdn_prepare_mma_kernel(const __nv_bfloat16* __restrict__ mixed, int ld, int q_of
 constexpr int SL = 32;    // value columns per CTA
 constexpr int WS = 136;   // padded row (halves) of the [64 x 128] W / Qg tiles and of the [32 x 128] state copy
 constexpr int TS = 72;    // padded row (halves) of the [. x 64] tiles (KgT, Aqk, v_new^T)
-constexpr int SCAN_BUF_HALVES = 2 * C * WS + DK * TS + C * TS;            // W, Qg, KgT, Aqk of one chunk
-constexpr int SCAN_SMEM_BYTES = (2 * SCAN_BUF_HALVES + SL * WS + SL * TS) * 2;
+constexpr int SCAN_WQ_HALVES = 2 * C * WS;                                // W, Qg of one chunk (double-buffered)
+constexpr int SCAN_KA_HALVES = DK * TS + C * TS;                          // KgT, Aqk of one chunk (single buffer)
+// 110.6 KB: two CTAs per SM, so that 4 x 48 heads run as one wave and one CTA's waits overlap the other's MMAs
+constexpr int SCAN_SMEM_BYTES = (2 * SCAN_WQ_HALVES + SCAN_KA_HALVES + SL * WS + SL * TS) * 2;
 
 // grid (Hv, 128 / SL), 128 threads.  Warp w owns tokens [16w, 16w+16) of the chunk for v_new and O, and state rows
 // (key dims) [32w, 32w+32) for the state update.
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(128, 2)
 gdn_scan_kernel(PrepOut w, float* __restrict__ state, __nv_bfloat16* __restrict__ out, int T, int nchunks, int Hv) {
   extern __shared__ __align__(16) __half sh[];
-  __half* sS = sh + 2 * SCAN_BUF_HALVES;   // [SL][WS]  state^T operand copy: value column major, key dim minor
+  __half* const bK = sh + 2 * SCAN_WQ_HALVES;     // [128][TS] KgT of the current chunk
+  __half* const bA = bK + DK * TS;                // [64][TS]  Aqk of the current chunk
+  __half* sS = bA + C * TS;                // [SL][WS]  state^T operand copy: value column major, key dim minor
   __half* sV = sS + SL * WS;               // [SL][TS]  v_new^T: value column major, token minor
   const int h = blockIdx.x, sl = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
   float* Sg = state + (size_t)h * DK * DV + sl * SL;
 
-  auto prefetch = [&](int c) {
-    __half* buf = sh + (c & 1) * SCAN_BUF_HALVES;
-    __half* bW = buf, *bQ = buf + C * WS, *bK = bQ + C * WS, *bA = bK + DK * TS;
+  // W / Qg are needed at the top of a step and are fetched one chunk ahead; KgT / Aqk are needed after v_new and are
+  // fetched at the top of their own step (their buffer is free once every warp has left the previous step)
+  auto prefetch_wq = [&](int c) {
+    __half* bW = sh + (c & 1) * SCAN_WQ_HALVES, *bQ = bW + C * WS;
     const size_t t0 = (size_t)c * C;
     for (int i = tid; i < C * 16; i += 128) {            // 64 rows x 16 copies of 16 bytes
       const int r = i >> 4, q = i & 15;
@@ -560,6 +598,10 @@ gdn_scan_kernel(PrepOut w, float* __restrict__ state, __nv_bfloat16* __restrict_
       cp_async16(bW + r * WS + q * 8, w.W + src);
       cp_async16(bQ + r * WS + q * 8, w.Qg + src);
     }
+    cp_async_commit();
+  };
+  auto prefetch_ka = [&](int c) {
+    const size_t t0 = (size_t)c * C;
     for (int i = tid; i < DK * 8; i += 128) {            // 128 rows x 8 copies
       const int r = i >> 3, q = i & 7;
       cp_async16(bK + r * TS + q * 8, w.KgT + (((size_t)c * Hv + h) * DK + r) * C + q * 8);
@@ -584,15 +626,16 @@ gdn_scan_kernel(PrepOut w, float* __restrict__ state, __nv_bfloat16* __restrict_
         sacc[mt][nt][e] = v;
         sS[n * WS + m] = __float2half_rn(v);
       }
-  prefetch(0);
+  prefetch_wq(0);
 
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * C;
     cp_async_wait_all();
-    __syncthreads();                       // chunk c landed; the state copy of chunk c-1 is complete; sV is free
-    if (c + 1 < nchunks) prefetch(c + 1);
-    const __half* buf = sh + (c & 1) * SCAN_BUF_HALVES;
-    const __half* bW = buf, *bQ = buf + C * WS, *bK = bQ + C * WS, *bA = bK + DK * TS;
+    __syncthreads();                       // W / Qg of chunk c landed; the state copy of chunk c-1 is complete; sV, bK, bA are free
+    prefetch_ka(c);
+    const bool more = c + 1 < nchunks;
+    if (more) prefetch_wq(c + 1);
+    const __half* bW = sh + (c & 1) * SCAN_WQ_HALVES, *bQ = bW + C * WS;
 
     float2 u[4][2];
 #pragma unroll
@@ -640,7 +683,8 @@ gdn_scan_kernel(PrepOut w, float* __restrict__ state, __nv_bfloat16* __restrict_
         mma16816(acc[nt], a, *reinterpret_cast<const uint32_t*>(bp), *reinterpret_cast<const uint32_t*>(bp + 8));
       }
     }
-    __syncthreads();                       // v_new^T complete; every warp is done reading the old state copy
+    if (more) cp_async_wait_1(); else cp_async_wait_all();   // this thread's KgT / Aqk copies (the older group) are done
+    __syncthreads();                       // v_new^T, KgT, Aqk complete; every warp is done reading the old state copy
     // O += Aqk v_new
 #pragma unroll
     for (int ks = 0; ks < C / 16; ++ks) {
