@@ -17,7 +17,7 @@
 
 namespace {
 
-constexpr int KT = 32;        // keys per tile
+constexpr int KT = 32;        // keys per tile (= threads / 4: the gather assigns four threads to a key row)
 constexpr int HG = 16;        // heads per CTA (MMA M)
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -34,6 +34,11 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -46,8 +51,10 @@ struct Layout {
   static constexpr int LD = D + 8;                           // padded row (elements): 16-byte aligned, bank-skewed
   static constexpr int Q_BYTES = HG * LD * 2;
   static constexpr int K_BYTES = KT * LD * 2;
-  static constexpr int S_BYTES = HG * (KT + 1) * 4;
-  static constexpr int TOTAL = Q_BYTES + 2 * K_BYTES + S_BYTES + 2 * KT * 4;
+  static constexpr int PLD = KT + 8;                          // padded row (elements) of the probability tile
+  static constexpr int P_BYTES = HG * PLD * 2;
+  static constexpr int STAT_BYTES = 2 * 4 * HG * 4;           // per-warp partial row maxima and row sums
+  static constexpr int TOTAL = Q_BYTES + 2 * K_BYTES + P_BYTES + STAT_BYTES + 2 * KT * 4;
 };
 
 // grid (T, ceil(H / 16)), 128 threads.
@@ -63,8 +70,10 @@ mla_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_bfl
   extern __shared__ __align__(16) uint8_t smem[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem);
   __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem + L::Q_BYTES);
-  float* sS = reinterpret_cast<float*>(smem + L::Q_BYTES + 2 * L::K_BYTES);   // [16][KT + 1]
-  int* sPos = reinterpret_cast<int*>(sS + HG * (KT + 1));                      // [2][KT] key position, -1 = masked
+  __nv_bfloat16* sP = reinterpret_cast<__nv_bfloat16*>(smem + L::Q_BYTES + 2 * L::K_BYTES);   // [16][PLD] probabilities
+  float* sMax = reinterpret_cast<float*>(smem + L::Q_BYTES + 2 * L::K_BYTES + L::P_BYTES);    // [4 warps][16 rows]
+  float* sSum = sMax + 4 * HG;                                                                // [4 warps][16 rows]
+  int* sPos = reinterpret_cast<int*>(sSum + 4 * HG);                           // [2][KT] key position, -1 = masked
   const int t = blockIdx.x, h0 = blockIdx.y * HG;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
   const int pos = positions[t];
@@ -72,18 +81,25 @@ mla_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_bfl
   const int nkeys = sel ? nsel : pos + 1;
   const int ntiles = (nkeys + KT - 1) / KT;
 
+  // four threads per key row: the row's cache address (selection entry, block table, division by the block size) is
+  // worked out once per thread and tile, then 18 copies of 16 bytes go out back to back
   auto fetch = [&](int tile) {
     __nv_bfloat16* dst = sK + (size_t)(tile & 1) * KT * LD;
     int* dpos = sPos + (tile & 1) * KT;
-    const int k0 = tile * KT;
-    for (int i = tid; i < KT * (D / 8); i += 128) {
-      const int j = i / (D / 8), c = i % (D / 8);
-      int kp = -1;
-      if (k0 + j < nkeys) kp = sel ? sel[(size_t)t * nsel + k0 + j] : k0 + j;
-      if (kp > pos) kp = -1;
-      if (c == 0) dpos[j] = kp;
-      if (kp >= 0) cp16(dst + j * LD + c * 8, cache + cache_row_of(bt, bs, kp) * D + c * 8);
-      else *reinterpret_cast<uint4*>(dst + j * LD + c * 8) = make_uint4(0, 0, 0, 0);
+    const int j = tid >> 2, part = tid & 3;
+    const int key = tile * KT + j;
+    int kp = -1;
+    if (key < nkeys) kp = sel ? sel[(size_t)t * nsel + key] : key;
+    if (kp > pos) kp = -1;
+    if (part == 0) dpos[j] = kp;
+    __nv_bfloat16* drow = dst + j * LD;
+    if (kp >= 0) {
+      const __nv_bfloat16* srow = cache + cache_row_of(bt, bs, kp) * D;
+#pragma unroll
+      for (int c = part; c < D / 8; c += 4) cp16(drow + c * 8, srow + c * 8);
+    } else {
+#pragma unroll
+      for (int c = part; c < D / 8; c += 4) *reinterpret_cast<uint4*>(drow + c * 8) = make_uint4(0, 0, 0, 0);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -111,54 +127,63 @@ mla_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_bfl
     if (tile + 1 < ntiles) fetch(tile + 1);
     const __nv_bfloat16* kt = sK + (size_t)(tile & 1) * KT * LD;
     const int* kpos = sPos + (tile & 1) * KT;
-    // ---- scores of keys [8 warp, 8 warp + 8): S[16 x 8] = Q[16 x D] K^T
+    // ---- scores of keys [8 warp, 8 warp + 8): S[16 x 8] = Q[16 x D] K^T, operands through ldmatrix (two k-steps per
+    // B load)
     float s[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-    for (int ks = 0; ks < D / 16; ++ks) {
-      uint32_t a[4];
-      const __nv_bfloat16* ap = sQ + g * LD + ks * 16 + 2 * tig;
-      a[0] = *reinterpret_cast<const uint32_t*>(ap);
-      a[1] = *reinterpret_cast<const uint32_t*>(ap + 8 * LD);
-      a[2] = *reinterpret_cast<const uint32_t*>(ap + 8);
-      a[3] = *reinterpret_cast<const uint32_t*>(ap + 8 * LD + 8);
-      const __nv_bfloat16* bp = kt + (8 * warp + g) * LD + ks * 16 + 2 * tig;
-      mma_bf16(s, a, *reinterpret_cast<const uint32_t*>(bp), *reinterpret_cast<const uint32_t*>(bp + 8));
+    {
+      const __nv_bfloat16* ap = sQ + (lane & 15) * LD + (lane >> 4) * 8;
+      const __nv_bfloat16* bp = kt + (8 * warp + (lane & 7)) * LD + (lane >> 3) * 8;
+#pragma unroll 6
+      for (int ks = 0; ks < D / 16; ks += 2) {
+        uint32_t a0[4], a1[4], b[4];
+        ldmatrix_x4(a0, ap + ks * 16);
+        ldmatrix_x4(a1, ap + ks * 16 + 16);
+        ldmatrix_x4(b, bp + ks * 16);
+        mma_bf16(s, a0, b[0], b[1]);
+        mma_bf16(s, a1, b[2], b[3]);
+      }
     }
+    // ---- soft-max, computed once: every warp owns 8 keys of the tile; row statistics are exchanged through shared memory
     {
       const int kc = 8 * warp + 2 * tig;
       const bool v0 = kpos[kc] >= 0, v1 = kpos[kc + 1] >= 0;
-      sS[g * (KT + 1) + kc] = v0 ? s[0] * scale : -INFINITY;
-      sS[g * (KT + 1) + kc + 1] = v1 ? s[1] * scale : -INFINITY;
-      sS[(g + 8) * (KT + 1) + kc] = v0 ? s[2] * scale : -INFINITY;
-      sS[(g + 8) * (KT + 1) + kc + 1] = v1 ? s[3] * scale : -INFINITY;
+      s[0] = v0 ? s[0] * scale : -INFINITY; s[1] = v1 ? s[1] * scale : -INFINITY;
+      s[2] = v0 ? s[2] * scale : -INFINITY; s[3] = v1 ? s[3] * scale : -INFINITY;
+      float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]);
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      if (tig == 0) { sMax[warp * HG + g] = mx0; sMax[warp * HG + g + 8] = mx1; }
     }
     __syncthreads();
-    // ---- running soft-max of rows g and g + 8 (every lane keeps its rows' statistics)
     float corr[2];
+    {
+      float mx[2];
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int r = g + 8 * hf;
+        mx[hf] = fmaxf(fmaxf(m_run[hf], fmaxf(sMax[r], sMax[HG + r])), fmaxf(sMax[2 * HG + r], sMax[3 * HG + r]));
+        corr[hf] = (m_run[hf] == -INFINITY) ? 0.f : __expf(m_run[hf] - mx[hf]);
+        m_run[hf] = mx[hf];
+      }
+      const float e0 = mx[0] == -INFINITY ? 0.f : __expf(s[0] - mx[0]), e1 = mx[0] == -INFINITY ? 0.f : __expf(s[1] - mx[0]);
+      const float e2 = mx[1] == -INFINITY ? 0.f : __expf(s[2] - mx[1]), e3 = mx[1] == -INFINITY ? 0.f : __expf(s[3] - mx[1]);
+      const int kc = 8 * warp + 2 * tig;
+      *reinterpret_cast<uint32_t*>(sP + g * L::PLD + kc) = pack_bf16(e0, e1);
+      *reinterpret_cast<uint32_t*>(sP + (g + 8) * L::PLD + kc) = pack_bf16(e2, e3);
+      float sm0 = e0 + e1, sm1 = e2 + e3;
+      sm0 += __shfl_xor_sync(0xffffffffu, sm0, 1); sm0 += __shfl_xor_sync(0xffffffffu, sm0, 2);
+      sm1 += __shfl_xor_sync(0xffffffffu, sm1, 1); sm1 += __shfl_xor_sync(0xffffffffu, sm1, 2);
+      if (tig == 0) { sSum[warp * HG + g] = sm0; sSum[warp * HG + g + 8] = sm1; }
+    }
+    __syncthreads();
     uint32_t pa[2][4];                                 // P as the A operand of two k-steps (16 keys each)
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
-      const float* row = sS + (g + 8 * hf) * (KT + 1);
-      float mx = m_run[hf];
-#pragma unroll
-      for (int j = 0; j < KT; ++j) mx = fmaxf(mx, row[j]);
-      corr[hf] = (m_run[hf] == -INFINITY) ? 0.f : __expf(m_run[hf] - mx);
-      float sum = 0.f;
-      if (mx != -INFINITY) {
-#pragma unroll
-        for (int j = 0; j < KT; ++j) sum += __expf(row[j] - mx);
-      }
-      l_run[hf] = l_run[hf] * corr[hf] + sum;
-      m_run[hf] = mx;
-#pragma unroll
-      for (int ks = 0; ks < 2; ++ks) {
-        const int c0 = 16 * ks + 2 * tig;
-        const float e0 = mx == -INFINITY ? 0.f : __expf(row[c0] - mx), e1 = mx == -INFINITY ? 0.f : __expf(row[c0 + 1] - mx);
-        const float e2 = mx == -INFINITY ? 0.f : __expf(row[c0 + 8] - mx), e3 = mx == -INFINITY ? 0.f : __expf(row[c0 + 9] - mx);
-        pa[ks][hf] = pack_bf16(e0, e1);                // a0 (row g) / a1 (row g + 8)
-        pa[ks][2 + hf] = pack_bf16(e2, e3);            // a2 / a3: keys + 8
-      }
+      const int r = g + 8 * hf;
+      l_run[hf] = l_run[hf] * corr[hf] + (sSum[r] + sSum[HG + r]) + (sSum[2 * HG + r] + sSum[3 * HG + r]);
     }
+    ldmatrix_x4(pa[0], sP + (lane & 15) * L::PLD + (lane >> 4) * 8);
+    ldmatrix_x4(pa[1], sP + (lane & 15) * L::PLD + 16 + (lane >> 4) * 8);
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
       o[n][0] *= corr[0]; o[n][1] *= corr[0];
