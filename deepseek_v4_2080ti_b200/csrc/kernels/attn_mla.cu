@@ -335,11 +335,18 @@ int b200_mla_q_prepare(const void* q, const int* positions, float theta, void* q
   return (int)cudaGetLastError();
 }
 
+int b200_mla_indexer_mma(const void* q_idx, const float* hw, const void* idx_cache, const int* block_table, int max_blocks,
+                         int bs, const int* positions, float* scores, int ld, int T, int HI, int DI, float scale,
+                         cudaStream_t stream);
+
 // scores fp32 [T, ld]; ld >= max position + 1.  DI must be 32, 64 or 128.
 int b200_mla_indexer(const void* q_idx, const float* hw, const void* idx_cache, const int* block_table, int max_blocks, int bs,
                      const int* positions, const int* seq_of_token, float* scores, int ld, int T, int HI, int DI, float scale,
                      cudaStream_t stream) {
   if (T <= 0 || ld <= 0 || HI <= 0) return -6;
+  // one sequence and a tensor-core-sized index width: the tiled kernel (attn_mla_indexer_mma.cu)
+  if (!seq_of_token && (DI == 64 || DI == 128))
+    return b200_mla_indexer_mma(q_idx, hw, idx_cache, block_table, max_blocks, bs, positions, scores, ld, T, HI, DI, scale, stream);
   const dim3 grid((ld + 127) / 128, T);
   const size_t smem = ((size_t)HI * DI + HI) * sizeof(float);
   auto qp = reinterpret_cast<const __nv_bfloat16*>(q_idx);

@@ -267,3 +267,29 @@ def test_runtime_from_gguf_file_follows_dequantised_bf16_runtime():
         assert nxt.numel() == 1
         rt.free(s)
         assert generate_gguf.main(["--gguf", path, "--token-ids", "1,2,3,4,5", "--max-new-tokens", "4", "--max-context", "128"]) == 0
+
+
+@pytest.mark.parametrize("t,s_ctx,hi,di,first", [(300, 700, 8, 128, 400), (130, 130, 5, 64, 0), (1, 1000, 64, 128, 999)])
+def test_tensor_core_indexer_matches_torch(t, s_ctx, hi, di, first):
+    """The tiled m16n8k16 indexer (one sequence, index width 64 / 128): causal chunk starting at ``first``, ragged
+    query and key tiles, a scrambled page table, key tiles wholly behind the frontier."""
+    from deepseek_v4_2080ti_b200.ops import _lib, mla
+    torch.manual_seed(t + di)
+    bs = 64
+    nblk = (s_ctx + bs - 1) // bs
+    perm = torch.randperm(nblk)
+    bt = perm.to(torch.int32).cuda().view(1, nblk).contiguous()
+    idx_cache = torch.zeros(nblk * bs, di, device="cuda", dtype=torch.bfloat16)
+    keys_i = torch.randn(s_ctx, di, device="cuda").bfloat16()
+    phys = (perm[torch.arange(s_ctx) // bs] * bs + torch.arange(s_ctx) % bs).cuda()
+    idx_cache[phys] = keys_i
+    pos = (first + torch.arange(t, device="cuda")).clamp_max(s_ctx - 1).to(torch.int32)
+    q_idx = torch.randn(t, hi, di, device="cuda").bfloat16()
+    hw = torch.rand(t, hi, device="cuda") - 0.3
+    scores = mla.indexer_scores(q_idx, hw, idx_cache, bt, bs, pos, s_ctx, di ** -0.5)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    ref = (torch.einsum("thd,sd->ths", q_idx.float(), keys_i.float()).relu() * hw[:, :, None]).sum(1) * di ** -0.5
+    mask = torch.arange(s_ctx, device="cuda")[None, :] <= pos[:, None]
+    assert torch.isinf(scores[~mask]).all() and (scores[~mask] < 0).all()
+    assert torch.allclose(scores[mask], ref[mask], rtol=2e-3, atol=2e-3), (scores[mask] - ref[mask]).abs().max().item()
