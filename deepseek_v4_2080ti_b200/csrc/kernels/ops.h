@@ -61,6 +61,9 @@ int b200_mla_kv_append(const void* kv, const void* gamma, float eps, const int* 
                        cudaStream_t stream);
 int b200_mla_q_prepare(const void* q, const int* positions, float theta, void* qn_t, void* q_pe, int T, int H, int N, int R,
                        cudaStream_t stream);
+int b200_mla_attention_splitkv(const void* q_lat, const void* q_pe, const void* cache, const int* block_table, int max_blocks,
+                               int bs, const int* positions, const int* seq_of_token, const int* sel, int nsel, void* o_lat,
+                               int T, int H, int C, int R, float scale, float* workspace, int splits, cudaStream_t stream);
 int b200_mla_indexer_mma(const void* q_idx, const float* hw, const void* idx_cache, const int* block_table, int max_blocks,
                          int bs, const int* positions, float* scores, int ld, int T, int HI, int DI, float scale,
                          cudaStream_t stream);

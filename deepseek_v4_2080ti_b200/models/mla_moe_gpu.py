@@ -341,7 +341,7 @@ class MlaMoeGpuRuntime:
                 scores = mla.indexer_scores(qi, hw, self.idx_cache[i], self.block_table, self.bs, pos, end, cfg.index_dim ** -0.5)
                 sel = mla.topk_rows(scores, (pos + 1).to(torch.int32), cfg.index_topk)
         o_lat = mla.attention(q_lat, q_pe, self.cache[i], self.block_table, self.bs, pos, cfg.kv_lora_rank, cfg.qk_rope_dim,
-                              cfg.qk_head_dim ** -0.5, sel)
+                              cfg.qk_head_dim ** -0.5, sel, max_keys=end)
         o = mla.transpose_heads(mla.per_head_linear(o_lat, lw.w_uv)).view(t, hl * cfg.v_head_dim)
         return self.comm.all_reduce(_mm(o, lw.wo))
 

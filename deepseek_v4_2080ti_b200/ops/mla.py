@@ -52,14 +52,33 @@ def topk_rows(vals: torch.Tensor, n_valid: torch.Tensor, k: int) -> torch.Tensor
     return idx
 
 
-def attention(q_lat, q_pe, cache, block_table, bs, positions, c, r, scale, sel=None, seq_of_token=None):
-    """q_lat [H, T, c], q_pe [T, H, r] -> o_lat [H, T, c]; ``sel`` [T, nsel] int32 cache positions or None (dense causal)."""
+_split_ws: dict[int, torch.Tensor] = {}
+
+
+def attention(q_lat, q_pe, cache, block_table, bs, positions, c, r, scale, sel=None, seq_of_token=None, max_keys: int | None = None,
+              splits: int | None = None):
+    """q_lat [H, T, c], q_pe [T, H, r] -> o_lat [H, T, c]; ``sel`` [T, nsel] int32 cache positions or None (dense causal).
+    With few query tokens (decode) the context is split over several CTAs per head group (``splits``; chosen from the
+    grid size and ``max_keys``, an upper bound of the keys a token attends to) and merged by a second kernel."""
     h, t, _ = q_lat.shape
     o = torch.empty(h, t, c, dtype=torch.bfloat16, device=q_lat.device)
-    rc = _lib.lib().b200_mla_attention(_lib.ptr(q_lat), _lib.ptr(q_pe), _lib.ptr(cache), _lib.ptr(block_table),
-                                       block_table.shape[-1], bs, _lib.ptr(positions), _lib.ptr(seq_of_token), _lib.ptr(sel),
-                                       0 if sel is None else sel.shape[1], _lib.ptr(o), t, h, c, r, _f(scale), _lib.stream())
-    _lib.check(rc, "mla_attention")
+    groups = t * ((h + 15) // 16)
+    if splits is None:
+        nk = sel.shape[1] if sel is not None else (max_keys if max_keys is not None else block_table.shape[-1] * bs)
+        splits = 1 if groups >= 148 else max(1, min(32, 296 // groups, (nk + 63) // 64))
+    ws = None
+    if splits > 1:
+        need = t * h * splits * (c + 2)
+        dev = q_lat.device.index or 0
+        ws = _split_ws.get(dev)
+        if ws is None or ws.numel() < need:
+            ws = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q_lat.device)
+            _split_ws[dev] = ws
+    rc = _lib.lib().b200_mla_attention_splitkv(_lib.ptr(q_lat), _lib.ptr(q_pe), _lib.ptr(cache), _lib.ptr(block_table),
+                                               block_table.shape[-1], bs, _lib.ptr(positions), _lib.ptr(seq_of_token),
+                                               _lib.ptr(sel), 0 if sel is None else sel.shape[1], _lib.ptr(o), t, h, c, r,
+                                               _f(scale), _lib.ptr(ws), int(splits), _lib.stream())
+    _lib.check(rc, "mla_attention", 2 if splits > 1 else 1)
     return o
 
 

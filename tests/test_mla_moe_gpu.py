@@ -202,8 +202,8 @@ def test_tensor_core_attention_matches_torch_and_scalar_kernel(h, c, r):
         sel[ti, :n] = torch.randperm(int(pos[ti]) + 1)[:n].to(torch.int32).cuda()
     mask = torch.arange(s_ctx, device="cuda")[None, :] <= pos[:, None]
     q = torch.cat([q_lat.float().permute(1, 0, 2), q_pe.float()], -1)
-    for use_sel in (False, True):
-        o = mla.attention(q_lat, q_pe, cache, bt, bs, pos, c, r, scale, sel if use_sel else None)
+    for use_sel, splits in ((False, None), (True, None), (False, 1), (True, 3)):
+        o = mla.attention(q_lat, q_pe, cache, bt, bs, pos, c, r, scale, sel if use_sel else None, splits=splits)
         o2 = torch.empty_like(o)
         rc = _lib.lib().b200_mla_attention_simt(_lib.ptr(q_lat), _lib.ptr(q_pe), _lib.ptr(cache), _lib.ptr(bt), nblk, bs,
                                                 _lib.ptr(pos), None, _lib.ptr(sel) if use_sel else None, k if use_sel else 0,
@@ -293,3 +293,30 @@ def test_tensor_core_indexer_matches_torch(t, s_ctx, hi, di, first):
     mask = torch.arange(s_ctx, device="cuda")[None, :] <= pos[:, None]
     assert torch.isinf(scores[~mask]).all() and (scores[~mask] < 0).all()
     assert torch.allclose(scores[mask], ref[mask], rtol=2e-3, atol=2e-3), (scores[mask] - ref[mask]).abs().max().item()
+
+
+@pytest.mark.parametrize("h", [64, 20, 40])
+def test_tensor_core_attention_many_tokens_shares_the_gather_across_head_groups(h):
+    """Enough tokens for the 32- and 64-head CTAs (one gather per token for all of a rank's heads): against the scalar
+    kernel, sparse selections with padding."""
+    import ctypes
+    from deepseek_v4_2080ti_b200.ops import _lib, mla
+    torch.manual_seed(h)
+    t, s_ctx, bs, k, c, r = 160, 400, 64, 96, 512, 64
+    nblk = (s_ctx + bs - 1) // bs
+    bt = torch.randperm(nblk).to(torch.int32).cuda().view(1, nblk).contiguous()
+    cache = (torch.randn(nblk * bs, c + r, device="cuda") * 0.3).bfloat16()
+    pos = torch.arange(s_ctx - t, s_ctx, dtype=torch.int32, device="cuda")
+    q_lat = (torch.randn(h, t, c, device="cuda") * 0.3).bfloat16()
+    q_pe = (torch.randn(t, h, r, device="cuda") * 0.3).bfloat16()
+    sel = torch.stack([torch.randperm(int(p) + 1)[:k] for p in pos.tolist()]).to(torch.int32).cuda()
+    sel[:, -5:] = -1
+    scale = (c + r) ** -0.5
+    o = mla.attention(q_lat, q_pe, cache, bt, bs, pos, c, r, scale, sel)
+    o2 = torch.empty_like(o)
+    rc = _lib.lib().b200_mla_attention_simt(_lib.ptr(q_lat), _lib.ptr(q_pe), _lib.ptr(cache), _lib.ptr(bt), nblk, bs, _lib.ptr(pos),
+                                            None, _lib.ptr(sel), k, _lib.ptr(o2), t, h, c, r, ctypes.c_float(scale), _lib.stream())
+    assert rc == 0
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert (o.float() - o2.float()).abs().max() < 2e-2 * o2.float().abs().max()
