@@ -299,6 +299,8 @@ class MlaMoeGpuRuntime:
         # identity page table: block b of the sequence is physical block b (one resident sequence)
         self.block_table = torch.arange(nblk, dtype=torch.int32, device=self.device).view(1, nblk).contiguous()
         self.length = 0
+        self._graphs: dict[tuple, dict] = {}
+        self.launches = 0
 
     def reset(self) -> None:
         self.length = 0
@@ -307,8 +309,13 @@ class MlaMoeGpuRuntime:
     def _swiglu(self, x, gu, down):
         return _mm(basic.silu_mul(_mm(x, gu)), down)
 
-    def _attention(self, lw: GpuLayer, i: int, x: torch.Tensor, pos: torch.Tensor, end: int) -> torch.Tensor:
+    def _attention(self, lw: GpuLayer, i: int, x: torch.Tensor, pos: torch.Tensor, end: int, ld: int | None = None,
+                   sparse: bool | None = None) -> torch.Tensor:
+        """``end``: context length after these tokens; ``ld`` / ``sparse`` override the indexer's score width and the
+        dense-or-selected decision (a captured decode step fixes both for a whole context bucket)."""
         cfg = self.cfg
+        ld = end if ld is None else ld
+        sparse = end > cfg.index_topk if sparse is None else sparse
         t = x.shape[0]
         hl = self.w.h_local
         eps = cfg.rms_norm_eps
@@ -321,7 +328,7 @@ class MlaMoeGpuRuntime:
         qn_t, q_pe = mla.q_prepare(q, pos, cfg.rope_theta, hl, cfg.qk_nope_dim, cfg.qk_rope_dim)
         q_lat = mla.per_head_linear(qn_t, lw.w_uk_t)
         sel = None
-        if lw.idx_wq is not None and end > cfg.index_topk:
+        if lw.idx_wq is not None and sparse:
             qi = _mm(qin, lw.idx_wq).view(t, cfg.index_heads, cfg.index_dim)
             hw = (_mm(x, lw.idx_wproj, out_f32=True) * cfg.index_heads ** -0.5).contiguous()
             world = getattr(self.comm, "world", 1)
@@ -334,14 +341,14 @@ class MlaMoeGpuRuntime:
                 part = torch.full((per, cfg.index_topk), -1, dtype=torch.int32, device=self.device)
                 if hi > lo:
                     sc = mla.indexer_scores(qi[lo:hi].contiguous(), hw[lo:hi].contiguous(), self.idx_cache[i], self.block_table,
-                                            self.bs, pos[lo:hi].contiguous(), end, cfg.index_dim ** -0.5)
+                                            self.bs, pos[lo:hi].contiguous(), ld, cfg.index_dim ** -0.5)
                     part[:hi - lo] = mla.topk_rows(sc, (pos[lo:hi] + 1).to(torch.int32), cfg.index_topk)
                 sel = self.comm.all_gather(part).reshape(world * per, cfg.index_topk)[:t].contiguous()
             else:
-                scores = mla.indexer_scores(qi, hw, self.idx_cache[i], self.block_table, self.bs, pos, end, cfg.index_dim ** -0.5)
+                scores = mla.indexer_scores(qi, hw, self.idx_cache[i], self.block_table, self.bs, pos, ld, cfg.index_dim ** -0.5)
                 sel = mla.topk_rows(scores, (pos + 1).to(torch.int32), cfg.index_topk)
         o_lat = mla.attention(q_lat, q_pe, self.cache[i], self.block_table, self.bs, pos, cfg.kv_lora_rank, cfg.qk_rope_dim,
-                              cfg.qk_head_dim ** -0.5, sel, max_keys=end)
+                              cfg.qk_head_dim ** -0.5, sel, max_keys=ld)
         o = mla.transpose_heads(mla.per_head_linear(o_lat, lw.w_uv)).view(t, hl * cfg.v_head_dim)
         return self.comm.all_reduce(_mm(o, lw.wo))
 
@@ -449,6 +456,7 @@ class MlaMoeGpuRuntime:
             x = basic.add_rmsnorm(h, d_attn, lw.ffn_norm, cfg.rms_norm_eps)
             delta = self._ffn(lw, x)
         self.length = end
+        self.launches = 0
         if w.layer_hi < cfg.num_layers:
             basic.add_(h, delta)
             self.pp.send_hidden(h)
@@ -456,6 +464,61 @@ class MlaMoeGpuRuntime:
         x = basic.add_rmsnorm(h, delta, w.norm, cfg.rms_norm_eps)          # h becomes the final residual stream
         logits = _mm(x, w.head, out_f32=True)
         return (logits, h) if return_hidden else logits
+
+    def _decode_body(self, ent: dict, ld: int, sparse: bool) -> torch.Tensor:
+        """One token through every layer with device-side position (static buffers: capturable)."""
+        cfg, w = self.cfg, self.w
+        pos = ent["pos"]
+        h = basic.embedding(ent["ids"], w.embed, 0, cfg.vocab_size)
+        delta = None
+        for i, lw in enumerate(w.layers):
+            x = basic.rmsnorm(h, lw.attn_norm, cfg.rms_norm_eps) if delta is None else \
+                basic.add_rmsnorm(h, delta, lw.attn_norm, cfg.rms_norm_eps)
+            d_attn = self._attention(lw, i, x, pos, ld, ld, sparse)
+            x = basic.add_rmsnorm(h, d_attn, lw.ffn_norm, cfg.rms_norm_eps)
+            delta = self._ffn(lw, x)
+        x = basic.add_rmsnorm(h, delta, w.norm, cfg.rms_norm_eps)
+        ent["logits"] = _mm(x, w.head, out_f32=True)
+        return basic.argmax(ent["logits"])
+
+    @torch.no_grad()
+    def decode_step(self, token: torch.Tensor, use_graph: bool = True) -> torch.Tensor:
+        """Append one token (int32 [1], device) and return the greedy next token [1].  The step is captured once per
+        context bucket (power of two; the indexer scores that many positions and masks by the device-side position)
+        and replayed: one graph launch instead of a few dozen kernel launches per layer.  Not for pipeline stages."""
+        assert self.pp is None and self.w.layer_lo == 0 and self.w.layer_hi == self.cfg.num_layers
+        end = self.length + 1
+        if end > self.max_context:
+            raise RuntimeError("sequence exceeds max_context")
+        rows = self.cache.shape[1]
+        ld = min(rows, 1 << max(10, (end - 1).bit_length()))
+        sparse = end > self.cfg.index_topk
+        key = (ld, sparse)
+        ent = self._graphs.get(key)
+        if ent is None:
+            ent = {"ids": torch.zeros(1, dtype=torch.int32, device=self.device),
+                   "pos": torch.zeros(1, dtype=torch.int32, device=self.device), "graph": None, "out": None}
+            self._graphs[key] = ent
+        ent["ids"].copy_(token.reshape(1))
+        ent["pos"].fill_(self.length)
+        if not use_graph:
+            out = self._decode_body(ent, ld, sparse)
+        else:
+            if ent["graph"] is None:
+                self._decode_body(ent, ld, sparse)      # warm-up outside capture; rewrites the same cache row later
+                torch.cuda.synchronize()
+                from ..ops import _lib
+                l0 = _lib.LAUNCHES
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    ent["out"] = self._decode_body(ent, ld, sparse)
+                ent["graph"], ent["launches"] = g, _lib.LAUNCHES - l0
+            ent["graph"].replay()
+            out = ent["out"]
+            self.launches = ent["launches"]
+        self.last_logits = ent["logits"]
+        self.length = end
+        return out
 
     @torch.no_grad()
     def generate(self, prompt: torch.Tensor, max_new_tokens: int, chunk: int = 2048) -> tuple[list[int], torch.Tensor]:
@@ -467,16 +530,21 @@ class MlaMoeGpuRuntime:
             out = self.forward(prompt[s:s + chunk])
             logits = out[-1:] if out is not None else None
         toks, rows = [], []
+        graph = self.pp is None and self.w.layer_lo == 0 and last_stage
         for _ in range(max_new_tokens):
             nxt = basic.argmax(logits) if last_stage else None
             if last_stage:
-                rows.append(logits[0])
+                rows.append(logits[0].clone())
             if self.pp is not None:
                 nxt = self.pp.share_token(nxt)
             toks.append(int(nxt.item()))
             if len(toks) == max_new_tokens:
                 break
-            logits = self.forward(nxt)
+            if graph:
+                self.decode_step(nxt.to(torch.int32))
+                logits = self.last_logits
+            else:
+                logits = self.forward(nxt)
         if self.pp is not None:
             self.pp.drain()
         return toks, (torch.stack(rows) if rows else torch.empty(0))

@@ -126,9 +126,17 @@ def _mla(args, rank, world, dev, glm: bool):
             return link.share_token(tok) if link is not None else tok
         tok, pre_ms = _timed(prefill)
 
+        graph = link is None and not args.eager_decode
+        if graph:                                      # capture the step of this context bucket outside the timed loop
+            rt.decode_step(tok.to(torch.int32))
+            rt.length -= 1                             # the row is written again by the first timed step
+
         def loop():
             t = tok
             for _ in range(n_decode):
+                if graph:
+                    t = rt.decode_step(t.to(torch.int32))
+                    continue
                 o = rt.forward(t.to(torch.int32))
                 t = basic.argmax(o) if last else None
                 if link is not None:
@@ -190,6 +198,7 @@ def main() -> None:
     ap.add_argument("--expert-pool", type=int, default=4)
     ap.add_argument("--pp", type=int, default=1, help="pipeline stages (glm / dsv4)")
     ap.add_argument("--mtp", action="store_true", help="dsv4: also time depth-1 speculative decoding")
+    ap.add_argument("--eager-decode", action="store_true", help="MLA families: launch every decode kernel instead of replaying a graph")
     ap.add_argument("--nccl", action="store_true", help="library collectives instead of the peer-memory kernels")
     args = ap.parse_args()
     rank, world, local = tp.init_distributed()

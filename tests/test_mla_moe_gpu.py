@@ -320,3 +320,30 @@ def test_tensor_core_attention_many_tokens_shares_the_gather_across_head_groups(
     torch.cuda.synchronize()
     _lib.check_status()
     assert (o.float() - o2.float()).abs().max() < 2e-2 * o2.float().abs().max()
+
+
+@pytest.mark.parametrize("indexer", [False, True])
+def test_graph_decode_step_equals_eager_forward(indexer):
+    """The captured decode step (device-side position, bucketed indexer width) against token-by-token ``forward``."""
+    from deepseek_v4_2080ti_b200.models import mla_moe as mm
+    from deepseek_v4_2080ti_b200.models import mla_moe_gpu as mg
+    from deepseek_v4_2080ti_b200.ops import _lib, basic
+    cfg = _cfg(indexer)
+    state = list(mm.synth_state(cfg, seed=5, std=0.05))
+    w = mg.MlaMoeGpuWeights(cfg, iter(state), "cuda")
+    a, b = mg.MlaMoeGpuRuntime(cfg, w, max_context=256), mg.MlaMoeGpuRuntime(cfg, w, max_context=256)
+    ids = torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(6)).cuda().to(torch.int32)
+    la, lb = a.forward(ids)[-1:], b.forward(ids)[-1:]
+    ta, tb = basic.argmax(la), basic.argmax(lb)
+    for step in range(6):
+        la = a.forward(ta.to(torch.int32))
+        ta = basic.argmax(la)
+        tb = b.decode_step(tb.to(torch.int32), use_graph=step != 0)     # first step eager, then captured + replayed
+        torch.cuda.synchronize()
+        _lib.check_status()
+        assert int(ta.item()) == int(tb.item()), step
+        assert (la - b.last_logits).abs().max().item() < 2e-2 * la.abs().max().item()
+    assert a.length == b.length == 46 and b.launches > 0
+    toks, rows = b.generate(ids, 5)
+    toks2, _ = a.generate(ids, 5)
+    assert toks == toks2 and rows.shape[0] == 5
