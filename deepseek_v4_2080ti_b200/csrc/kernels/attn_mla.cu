@@ -163,7 +163,7 @@ __device__ __forceinline__ uint32_t ordered_key(float f) {
 
 // One block (256 threads) per row: indices of the k largest values among the first n[row] entries.
 // Output idx [rows, k], padded with -1 when fewer than k entries exist; order inside a row is unspecified.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 topk_rows_kernel(const float* __restrict__ vals, int ld, const int* __restrict__ n_valid, int k, int* __restrict__ idx) {
   __shared__ int hist[256];
   __shared__ uint32_t s_prefix, s_mask;
@@ -178,14 +178,23 @@ topk_rows_kernel(const float* __restrict__ vals, int ld, const int* __restrict__
   }
   if (threadIdx.x == 0) { s_prefix = 0; s_mask = 0; s_need = k; }
   __syncthreads();
-  // find the key of the k-th largest value, 8 bits at a time from the top
+  const int lane = threadIdx.x & 31;
+  const int n_up = (n + blockDim.x - 1) / blockDim.x * blockDim.x;       // uniform trip count: ballots need whole warps
+  // find the key of the k-th largest value, 8 bits at a time from the top.  Scores of one row share most of their
+  // leading bits, so lanes that hit the same bin add to it once (match_any), not 32 times.
   for (int shift = 24; shift >= 0; shift -= 8) {
-    hist[threadIdx.x] = 0;
+    if (threadIdx.x < 256) hist[threadIdx.x] = 0;
     __syncthreads();
     const uint32_t prefix = s_prefix, mask = s_mask;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-      const uint32_t key = ordered_key(v[i]);
-      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFF], 1);
+    for (int i = threadIdx.x; i < n_up; i += blockDim.x) {
+      const uint32_t key = i < n ? ordered_key(v[i]) : 0u;
+      const bool in = i < n && (key & mask) == prefix;
+      const uint32_t act = __ballot_sync(0xffffffffu, in);
+      if (in) {
+        const int bin = (key >> shift) & 0xFF;
+        const uint32_t peers = __match_any_sync(act, bin);
+        if (lane == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
+      }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -204,22 +213,35 @@ topk_rows_kernel(const float* __restrict__ vals, int ld, const int* __restrict__
   const int need_eq = s_need;          // how many entries equal to the k-th key are taken (lowest indices first)
   if (threadIdx.x == 0) { s_count_gt = 0; s_count_eq = 0; }
   __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const uint32_t key = ordered_key(v[i]);
-    if (key > kth) out[atomicAdd(&s_count_gt, 1)] = i;
+  for (int i = threadIdx.x; i < n_up; i += blockDim.x) {
+    const bool gt = i < n && ordered_key(v[i]) > kth;
+    const uint32_t m = __ballot_sync(0xffffffffu, gt);
+    int base = 0;
+    if (lane == 0 && m) base = atomicAdd(&s_count_gt, __popc(m));
+    base = __shfl_sync(0xffffffffu, base, 0);
+    if (gt) out[base + __popc(m & ((1u << lane) - 1))] = i;
   }
   __syncthreads();
   const int base = s_count_gt;
-  // ties: deterministic choice of the lowest indices, scanned by one warp in order
-  if (threadIdx.x < 32) {
-    int taken = 0;
-    for (int i0 = 0; i0 < n && taken < need_eq; i0 += 32) {
-      const int i = i0 + threadIdx.x;
-      const bool eq = i < n && ordered_key(v[i]) == kth;
-      const uint32_t m = __ballot_sync(0xffffffffu, eq);
-      const int before = __popc(m & ((1u << threadIdx.x) - 1));
-      if (eq && taken + before < need_eq) out[base + taken + before] = i;
-      taken += __popc(m);
+  // ties: deterministic choice of the lowest indices.  Every thread counts the ties of one contiguous segment, the
+  // counts are scanned by thread 0, and a second pass writes the ties whose rank is below the number needed.
+  {
+    __shared__ int seg_base[1024];
+    const int seg = (n + blockDim.x - 1) / blockDim.x;
+    const int lo = min(n, (int)threadIdx.x * seg), hi = min(n, lo + seg);
+    int c = 0;
+    for (int i = lo; i < hi; ++i) c += ordered_key(v[i]) == kth;
+    seg_base[threadIdx.x] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int run = 0;
+      for (int w = 0; w < (int)blockDim.x; ++w) { const int x = seg_base[w]; seg_base[w] = run; run += x; }
+    }
+    __syncthreads();
+    int r = seg_base[threadIdx.x];
+    if (c > 0 && r < need_eq) {
+      for (int i = lo; i < hi && r < need_eq; ++i)
+        if (ordered_key(v[i]) == kth) out[base + r++] = i;
     }
   }
 }
@@ -344,8 +366,9 @@ int b200_mla_indexer(const void* q_idx, const float* hw, const void* idx_cache, 
                      const int* positions, const int* seq_of_token, float* scores, int ld, int T, int HI, int DI, float scale,
                      cudaStream_t stream) {
   if (T <= 0 || ld <= 0 || HI <= 0) return -6;
-  // one sequence and a tensor-core-sized index width: the tiled kernel (attn_mla_indexer_mma.cu)
-  if (!seq_of_token && (DI == 64 || DI == 128))
+  // one sequence, a tensor-core-sized index width and enough queries to fill the 128-query tiles: the tiled kernel
+  // (attn_mla_indexer_mma.cu); a decode step (a handful of queries) keeps one thread per key
+  if (!seq_of_token && (DI == 64 || DI == 128) && T >= 32)
     return b200_mla_indexer_mma(q_idx, hw, idx_cache, block_table, max_blocks, bs, positions, scores, ld, T, HI, DI, scale, stream);
   const dim3 grid((ld + 127) / 128, T);
   const size_t smem = ((size_t)HI * DI + HI) * sizeof(float);
@@ -370,7 +393,8 @@ int b200_mla_indexer(const void* q_idx, const float* hw, const void* idx_cache, 
 
 int b200_topk_rows(const float* vals, int ld, const int* n_valid, int rows, int k, int* idx, cudaStream_t stream) {
   if (rows <= 0 || k <= 0 || ld <= 0) return -6;
-  topk_rows_kernel<<<rows, 256, 0, stream>>>(vals, ld, n_valid, k, idx);
+  // few rows (decode): one block still owns a row, so give it the largest block
+  topk_rows_kernel<<<rows, rows < 296 ? 1024 : 256, 0, stream>>>(vals, ld, n_valid, k, idx);
   return (int)cudaGetLastError();
 }
 

@@ -232,25 +232,32 @@ mla_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_bfl
   }
 }
 
-// grid T * H, 128 threads: combine the splits' (max, sum, unnormalised output) states.
+// grid T * H, 128 threads: combine the splits' (max, sum, unnormalised output) states (splits <= 32).
 template <int C>
 __global__ void mla_attention_merge_kernel(const float* __restrict__ part, int splits, __nv_bfloat16* __restrict__ o_lat, int T, int H) {
+  __shared__ float wgt[32];
+  __shared__ float s_inv;
   const int t = blockIdx.x / H, h = blockIdx.x % H;
   const float* base = part + (size_t)blockIdx.x * splits * (C + 2);
-  float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, base[(size_t)s * (C + 2) + C]);
-  float Lsum = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float m = base[(size_t)s * (C + 2) + C];
-    if (m != -INFINITY) Lsum += base[(size_t)s * (C + 2) + C + 1] * __expf(m - M);
+  if (threadIdx.x < 32) {
+    const int s = threadIdx.x;
+    const float m = s < splits ? base[(size_t)s * (C + 2) + C] : -INFINITY;
+    const float l = s < splits ? base[(size_t)s * (C + 2) + C + 1] : 0.f;
+    float M = m;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    const float w = m == -INFINITY ? 0.f : __expf(m - M);
+    float Lsum = l * w;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) Lsum += __shfl_xor_sync(0xffffffffu, Lsum, o);
+    wgt[s] = w;
+    if (s == 0) s_inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
   }
-  const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
+  __syncthreads();
+  const float inv = s_inv;
   for (int d = threadIdx.x; d < C; d += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float m = base[(size_t)s * (C + 2) + C];
-      if (m != -INFINITY) acc += base[(size_t)s * (C + 2) + d] * __expf(m - M);
-    }
+    for (int s = 0; s < splits; ++s) acc += base[(size_t)s * (C + 2) + d] * wgt[s];
     o_lat[((size_t)h * T + t) * C + d] = __float2bfloat16(acc * inv);
   }
 }
@@ -279,7 +286,7 @@ template <int C, int R>
 int launch(const __nv_bfloat16* ql, const __nv_bfloat16* qp, const __nv_bfloat16* kc, const int* block_table, int max_blocks,
            int bs, const int* positions, const int* seq_of_token, const int* sel, int nsel, __nv_bfloat16* ol, int T, int H,
            float scale, float* part, int splits, cudaStream_t stream) {
-  if (splits < 1 || (splits > 1 && !part)) return -6;
+  if (splits < 1 || splits > 32 || (splits > 1 && !part)) return -6;
   if (splits == 1 && H > 32 && (long long)T * ((H + 63) / 64) >= 148 && Layout<C, R, 4>::TOTAL <= 227 * 1024)
     return launch_mt<C, R, 4>(ql, qp, kc, block_table, max_blocks, bs, positions, seq_of_token, sel, nsel, ol, T, H, scale, part, 1, stream);
   if (splits == 1 && H > 16 && (long long)T * ((H + 31) / 32) >= 148)

@@ -269,7 +269,7 @@ def test_runtime_from_gguf_file_follows_dequantised_bf16_runtime():
         assert generate_gguf.main(["--gguf", path, "--token-ids", "1,2,3,4,5", "--max-new-tokens", "4", "--max-context", "128"]) == 0
 
 
-@pytest.mark.parametrize("t,s_ctx,hi,di,first", [(300, 700, 8, 128, 400), (130, 130, 5, 64, 0), (1, 1000, 64, 128, 999)])
+@pytest.mark.parametrize("t,s_ctx,hi,di,first", [(300, 700, 8, 128, 400), (130, 130, 5, 64, 0), (33, 1000, 64, 128, 960)])
 def test_tensor_core_indexer_matches_torch(t, s_ctx, hi, di, first):
     """The tiled m16n8k16 indexer (one sequence, index width 64 / 128): causal chunk starting at ``first``, ragged
     query and key tiles, a scrambled page table, key tiles wholly behind the frontier."""
