@@ -92,6 +92,7 @@ int b200_hc_post(const void* y, const void* residual, const float* post, const f
 // ---- load-time weight preparation (prepack.cu)
 unsigned long long b200_prepack_fp8_bytes(int N, int K);
 int b200_prepack_fp8(const void* w_fp8, void* out, int N, int K, cudaStream_t stream);
+int b200_unpack_fp8_bf16(const void* packed, const float* scales, void* out_bf16, int N, int K, cudaStream_t stream);
 int b200_bf16_to_f32(const void* in, float* out, long long n, cudaStream_t stream);
 
 // ---- row kernels (elementwise.cu), recurrent and attention kernels (gdn.cu, rope_kv.cu, attn_gqa_*.cu)

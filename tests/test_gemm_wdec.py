@@ -134,3 +134,35 @@ def test_activation_split_reconstructs_rows():
         rec = sum(vals[:, j] / 16.0 ** j for j in range(terms)) * inv_c[:, None]
         err = ((rec - x.float()).abs().max(1).values / x.float().abs().max(1).values).max().item()
         assert err < (2e-4 if terms == 3 else 3e-3), (t, err)
+
+
+@pytest.mark.parametrize("n,k", [(256, 512), (384, 192), (128, 64)])
+def test_fp8_expansion_to_bf16_inverts_the_packing(n, k):
+    """The packed FP8 layout expanded back to row-major bf16 with its block scales, against the dequantised matrix."""
+    from deepseek_v4_2080ti_b200.ops import _lib, gemm
+    torch.manual_seed(n + k)
+    w = torch.randn(n, k, device="cuda") * 0.05
+    q, s = fp8fmt.quantize_block128(w)
+    pl = gemm.PackedLinear.from_fp8(q, s)
+    got = gemm._expanded_bf16(pl, w.device)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert got.wfmt == gemm.WF_BF16 and got.weight.shape == (n, k)
+    assert torch.equal(got.weight, fp8fmt.dequantize_block128(q, s).to(torch.bfloat16))
+
+
+def test_prefill_sized_batch_takes_the_expanded_path_and_matches():
+    from deepseek_v4_2080ti_b200.ops import _lib, gemm
+    torch.manual_seed(9)
+    t, n, k = gemm.PREDECODE_MIN_T, 384, 512
+    w = torch.randn(n, k, device="cuda") * 0.05
+    x = torch.randn(t, k, device="cuda").to(torch.bfloat16)
+    r = torch.randn(t, n, device="cuda").to(torch.bfloat16)
+    q, s = fp8fmt.quantize_block128(w)
+    pl = gemm.PackedLinear.from_fp8(q, s)
+    y = gemm.linear(x, pl, residual=r)
+    y_small = torch.cat([gemm.linear(x[i:i + 512].contiguous(), pl, residual=r[i:i + 512].contiguous()) for i in range(0, t, 512)])
+    torch.cuda.synchronize()
+    _lib.check_status()
+    ref = gemm.linear_ref(x, fp8fmt.dequantize_block128(q, s)) + r.float()
+    assert _rel_err(y, ref) < 1e-2 and _rel_err(y, y_small) < 5e-3
