@@ -104,6 +104,33 @@ extern "C" int b200_gemm_wdec_gguf(int wfmt, const void* W, const void* lut, con
   return dispatch(wfmt, BN, tmX, p, stream);
 }
 
+// As b200_gemm_wdec_gguf with split-K for small batches: `splits` CTAs share the K range of an output tile, leave fp32
+// partials in `scratch` (splits * T * N floats) and the last one to arrive (tile_counters: one zeroed int per output
+// tile, left zeroed) adds them up and writes bf16 (+ residual).  A decode-sized GEMM has too few 128-row tiles to
+// occupy the GPU otherwise (8 at N = 1024).
+extern "C" int b200_gemm_wdec_gguf_splitk(int wfmt, const void* W, const void* lut, const void* X, void* out_bf16,
+                                          float* scratch, const void* residual, int T, int N, int K, int splits,
+                                          int* tile_counters, int* status, cudaStream_t stream) {
+  GemmParams p;
+  if (!fill(p, wfmt, W, lut, out_bf16, scratch, residual, T, N, K, status) || !out_bf16 || splits < 1) return -ERR_BAD_ARG;
+  if (splits > p.kb_total) splits = p.kb_total;
+  {
+    const int per = (p.kb_total + splits - 1) / splits;      // no split may end up with an empty K range
+    splits = (p.kb_total + per - 1) / per;
+  }
+  if (splits > 1 && (!scratch || !tile_counters)) return -ERR_BAD_ARG;
+  p.splits = splits;
+  p.tile_counters = tile_counters;
+  if (splits == 1) p.out_f32 = nullptr;
+  int BN = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+  if (BN == 256 && !bn256_ok(wfmt)) BN = 128;
+  p.n_tiles = (T + BN - 1) / BN;
+  CUtensorMap tmX;
+  if (!make_tmap_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, T, K, (uint64_t)K * 2, BN, BK, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -ERR_BAD_ARG;
+  return dispatch(wfmt, BN, tmX, p, stream);
+}
+
 // Grouped form over expert-sorted rows (see b200_gemm_wdec_grouped): `groups` packed matrices back to back.
 extern "C" int b200_gemm_wdec_gguf_grouped(int wfmt, const void* W, const void* lut, const void* X, void* out_bf16,
                                            int rows_total, int N, int K, int groups, const void* work_table,

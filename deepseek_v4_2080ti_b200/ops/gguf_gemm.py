@@ -197,6 +197,16 @@ def linear(x: torch.Tensor, w: GGUFLinear, residual: torch.Tensor | None = None,
     t = x.shape[0]
     out = torch.empty(t, w.n, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
     lut = lut_for(w.ggml_type, x.device)
+    if not out_f32 and t <= 128:
+        from . import gemm
+        splits = gemm.pick_splits(t, w.n, w.k)
+        if splits > 1:
+            ws, counters = gemm._workspace(splits * t * w.n, x.device)
+            rc = _lib.lib().b200_gemm_wdec_gguf_splitk(WF[w.ggml_type], _lib.ptr(w.weight), _lib.ptr(lut), _lib.ptr(x),
+                                                       _lib.ptr(out), _lib.ptr(ws), _lib.ptr(residual), t, w.n, w.k, splits,
+                                                       _lib.ptr(counters), _lib.ptr(_lib.status_word(x.device)), _lib.stream())
+            _lib.check(rc, "gemm_wdec_gguf(split-k)")
+            return out
     rc = _lib.lib().b200_gemm_wdec_gguf(WF[w.ggml_type], _lib.ptr(w.weight), _lib.ptr(lut), _lib.ptr(x),
                                         None if out_f32 else _lib.ptr(out), _lib.ptr(out) if out_f32 else None,
                                         _lib.ptr(residual), t, w.n, w.k, _lib.ptr(_lib.status_word(x.device)), _lib.stream())

@@ -6,7 +6,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("tname", ["Q8_0", "Q4_K", "Q5_K", "Q6_K", "Q3_K", "Q2_K", "IQ1_M", "IQ2_XXS", "IQ2_XS", "IQ3_XXS", "IQ4_XS"])
-@pytest.mark.parametrize("t,n,k", [(1, 256, 512), (20, 300, 1024), (200, 128, 256), (600, 512, 768)])
+@pytest.mark.parametrize("t,n,k", [(1, 256, 512), (20, 300, 1024), (200, 128, 256), (600, 512, 768), (3, 256, 4096)])
 def test_gguf_linear_matches_dequantised_matmul(tname, t, n, k):
     from deepseek_v4_2080ti_b200.formats import gguf as G
     from deepseek_v4_2080ti_b200.ops import _lib, gguf_gemm
