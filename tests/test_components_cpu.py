@@ -20,7 +20,7 @@ def test_mailbox_round_trips_between_processes_and_times_out():
     name = f"b200_moe_test_{os.getpid()}"
     box = moe_ipc.MoEMailbox(name, 8, 2, max_tokens=4, create=True)
     try:
-        p = mp.get_context("fork").Process(target=_server, args=(name, 8, 2, 6))
+        p = mp.get_context("spawn").Process(target=_server, args=(name, 8, 2, 6))
         p.start()
         for i in range(6):
             t = 1 + i % 4

@@ -38,7 +38,7 @@ def _rank(name, rank, world, scenario, q):
 
 
 def _run(scenario, world=3):
-    ctx = mp.get_context("fork")
+    ctx = mp.get_context("spawn")      # fork from a threaded pytest process can deadlock the child
     q = ctx.Queue()
     name = f"b200_shmcomm_{os.getpid()}_{scenario}"
     ps = [ctx.Process(target=_rank, args=(name, r, world, scenario, q)) for r in range(world)]
