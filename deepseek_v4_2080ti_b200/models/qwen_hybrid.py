@@ -219,6 +219,13 @@ class QwenHybridWeights:
     def _fp8(self, base: str):
         return self._pending.pop(base + ".weight"), self._pending.pop(base + ".weight_scale_inv")
 
+    def _nvfp4(self, base: str) -> torch.Tensor:
+        """bf16 [N, K] on the device from the three NVFP4 tensors of ``base``."""
+        from ..formats import nvfp4
+        P = self._pending
+        return nvfp4.dequantize(self._dev(P.pop(base + ".weight_packed")), self._dev(P.pop(base + ".weight_scale")),
+                                self._dev(P.pop(base + ".weight_global_scale")), torch.bfloat16)
+
     def _col_fp8(self, parts: list[tuple[torch.Tensor, torch.Tensor, int]]) -> PackedLinear:
         """Concatenate column-parallel FP8 pieces (each already row-sharded) along N."""
         ws, ss = [], []
@@ -273,8 +280,13 @@ class QwenHybridWeights:
         p = f"model.language_model.layers.{i}."
         lt = cfg.layer_types[i]
         need = [p + "input_layernorm.weight", p + "post_attention_layernorm.weight"]
+        nvfp4_mlp = (p + "mlp.gate_proj.weight_packed") in P or (p + "mlp.gate_proj.weight_scale") in P or \
+            (p + "mlp.gate_proj.weight_global_scale") in P
         for m in ("gate_proj", "up_proj", "down_proj"):
-            need += [p + f"mlp.{m}.weight", p + f"mlp.{m}.weight_scale_inv"]
+            if nvfp4_mlp:
+                need += [p + f"mlp.{m}.weight_packed", p + f"mlp.{m}.weight_scale", p + f"mlp.{m}.weight_global_scale"]
+            else:
+                need += [p + f"mlp.{m}.weight", p + f"mlp.{m}.weight_scale_inv"]
         if lt == "linear_attention":
             a = p + "linear_attn."
             for m in ("in_proj_qkv", "in_proj_z", "out_proj"):
@@ -290,10 +302,20 @@ class QwenHybridWeights:
             return
         W, R = self.world, self.rank
         in_ln, post_ln = self._dev(P.pop(need[0])), self._dev(P.pop(need[1]))
-        g = self._rows_fp8(*self._fp8(p + "mlp.gate_proj"))
-        u = self._rows_fp8(*self._fp8(p + "mlp.up_proj"))
-        gate_up = self._col_fp8([g, u])
-        down = self._cols_fp8(*self._fp8(p + "mlp.down_proj"))
+        if nvfp4_mlp:
+            # NVFP4 feed-forward matrices (mixed checkpoints keep FP8 elsewhere): expanded to bf16 once, sharded like
+            # the FP8 ones, multiplied on the bf16 tile path
+            g, u, d = (self._nvfp4(p + f"mlp.{m}") for m in ("gate_proj", "up_proj", "down_proj"))
+            gate_up = PackedLinear.from_bf16(torch.cat([_shard_rows(g, R, W), _shard_rows(u, R, W)], 0))
+            kk = d.shape[1] // W
+            down = PackedLinear.from_bf16(d[:, R * kk:(R + 1) * kk])
+            for m in ("gate_proj", "up_proj", "down_proj"):
+                P.pop(p + f"mlp.{m}.input_global_scale", None)     # activations stay bf16 here
+        else:
+            g = self._rows_fp8(*self._fp8(p + "mlp.gate_proj"))
+            u = self._rows_fp8(*self._fp8(p + "mlp.up_proj"))
+            gate_up = self._col_fp8([g, u])
+            down = self._cols_fp8(*self._fp8(p + "mlp.down_proj"))
         if lt == "linear_attention":
             a = p + "linear_attn."
             kd = cfg.linear_num_key_heads * 128
@@ -428,8 +450,10 @@ class QwenHybridRuntime:
         self._graphs: dict[int, tuple] = {}
         self.launches = 0  # kernels launched by the last forward (for the bench record)
         # decode batches of <= 32 rows take the fused path; needs every FP8 K dimension to be a multiple of 128
+        from ..ops.gemm import WF_FP8_B128
         self.fused_decode = all(l.proj.k % 128 == 0 and l.out.k % 128 == 0 and l.down.k % 128 == 0 and
-                                l.gate_up.k % 128 == 0 for l in weights.layers) and \
+                                l.gate_up.k % 128 == 0 and l.gate_up.wfmt == WF_FP8_B128 and l.down.wfmt == WF_FP8_B128
+                                for l in weights.layers) and \
             (self.hv_lin // max(1, self.hk_lin)) in (1, 2, 4) and cfg.linear_conv_kernel_dim == 4
 
     # ---- slot / block management (host side)

@@ -26,9 +26,14 @@ class QwenHybridRef:
         raw = dict(state)
         self.p = {}
         for k, v in raw.items():
-            if k.endswith(".weight_scale_inv"):
+            if k.endswith((".weight_scale_inv", ".weight_scale", ".weight_global_scale", ".input_global_scale")):
                 continue
-            if v.dtype == torch.float8_e4m3fn:
+            if k.endswith(".weight_packed"):                       # NVFP4 (formats/nvfp4.py)
+                from ...formats import nvfp4
+                base = k[:-len(".weight_packed")]
+                self.p[base + ".weight"] = nvfp4.dequantize(v.cpu(), raw[base + ".weight_scale"].cpu(),
+                                                            raw[base + ".weight_global_scale"].cpu())
+            elif v.dtype == torch.float8_e4m3fn:
                 self.p[k] = fp8fmt.dequantize_block128(v, raw[k + "_scale_inv"])
             else:
                 self.p[k] = v.float()
