@@ -156,11 +156,18 @@ PYBIND11_MODULE(pocketllm_cpp, m) {
            py::keep_alive<1, 2>())
       .def_static("make_manual", &BatchScheduler::make_manual, py::arg("engine"), py::arg("options") = SchedulerOptions(),
                   py::keep_alive<0, 1>())
-      .def("submit", &BatchScheduler::submit, py::arg("prompt"), py::arg("max_new_tokens"), py::arg("stop_on_eos") = true)
-      .def("cancel", &BatchScheduler::cancel)
+      // Every call that takes the scheduler's mutex drops the GIL first: the scheduler thread may hold that mutex while
+      // it calls into a Python engine, which needs the GIL - holding both ends in different order would deadlock.
+      .def("submit", [](BatchScheduler& s, std::vector<int32_t> prompt, int max_new_tokens, bool stop_on_eos) {
+        py::gil_scoped_release rel;
+        return s.submit(std::move(prompt), max_new_tokens, stop_on_eos);
+      }, py::arg("prompt"), py::arg("max_new_tokens"), py::arg("stop_on_eos") = true)
+      .def("cancel", [](BatchScheduler& s, uint64_t id) { py::gil_scoped_release rel; return s.cancel(id); })
       .def("poll", [](BatchScheduler& s, uint64_t id) -> py::object {
         SchedulerResult r;
-        if (!s.poll(id, r)) return py::none();
+        bool ok;
+        { py::gil_scoped_release rel; ok = s.poll(id, r); }
+        if (!ok) return py::none();
         return py::cast(std::move(r));
       })
       .def("wait", [](BatchScheduler& s, uint64_t id, int timeout_ms) -> py::object {
@@ -171,7 +178,7 @@ PYBIND11_MODULE(pocketllm_cpp, m) {
         return py::cast(std::move(r));
       }, py::arg("id"), py::arg("timeout_ms") = -1)
       .def("step", [](BatchScheduler& s) { py::gil_scoped_release rel; return s.step(); })
-      .def("get_stats", &BatchScheduler::stats)
+      .def("get_stats", [](BatchScheduler& s) { py::gil_scoped_release rel; return s.stats(); })
       .def("stop", [](BatchScheduler& s) { py::gil_scoped_release rel; s.stop(); });
 
   py::class_<CmdChannel>(m, "CmdChannel")
