@@ -117,3 +117,13 @@ def test_convert_checkpoint_bf16_fp8_fp4_round_trips(capsys):
         err_a = (sb["a.weight"].float() - state["a.weight"].float()).norm() / state["a.weight"].float().norm()
         assert err_b < 0.05 and err_a < 0.2
         assert os.path.exists(os.path.join(back, "config.json"))
+        # NVFP4 as a target and as a source
+        nv, back2 = os.path.join(d, "nvfp4"), os.path.join(d, "back2")
+        assert cc.main([f8, nv, "--to", "nvfp4", "--match", "b."]) == 0
+        sn = dict(sio.read_checkpoint(nv))
+        assert sn["b.weight_packed"].shape == (128, 192) and sn["b.weight_scale"].dtype == torch.float8_e4m3fn
+        assert sn["b.weight_global_scale"].numel() == 1 and "b.weight" not in sn and sn["a.weight"].dtype == torch.float8_e4m3fn
+        assert cc.main([nv, back2, "--to", "bf16"]) == 0
+        s2 = dict(sio.read_checkpoint(back2))
+        err = (s2["b.weight"].float() - state["b.weight"].float()).norm() / state["b.weight"].float().norm()
+        assert "b.weight_packed" not in s2 and err < 0.15
