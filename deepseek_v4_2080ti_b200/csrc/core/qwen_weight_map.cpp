@@ -104,6 +104,34 @@ QwenAuditReport qwen_audit(SafetensorsModel& model, const QwenConfig& cfg, int t
     const SafeTensorInfo* info = model.find(s.name, &base);
     if (!info) {
       if (s.name == "lm_head.weight") continue;        // tied to the embedding table when absent
+      // mixed NVFP4 checkpoints hold a feed-forward matrix as weight_packed [n, k / 2] + weight_scale [n, k / 16] (E4M3)
+      // + weight_global_scale [1] (+ input_global_scale) instead of weight + weight_scale_inv
+      const bool is_weight = s.name.size() > 7 && s.name.compare(s.name.size() - 7, 7, ".weight") == 0;
+      const bool is_scale = s.name.size() > 17 && s.name.compare(s.name.size() - 17, 17, ".weight_scale_inv") == 0;
+      const std::string stem = is_weight ? s.name.substr(0, s.name.size() - 7) : is_scale ? s.name.substr(0, s.name.size() - 17) : "";
+      const SafeTensorInfo* packed = stem.empty() ? nullptr : model.find(stem + ".weight_packed", &base);
+      if (packed && s.kind == QwenLinearKind::Fp8Block128) {
+        if (is_scale) continue;                          // accounted for with the weight entry
+        const SafeTensorInfo* gs = model.find(stem + ".weight_scale", &base);
+        const SafeTensorInfo* gg = model.find(stem + ".weight_global_scale", &base);
+        known.insert(stem + ".weight_packed"); known.insert(stem + ".weight_scale");
+        known.insert(stem + ".weight_global_scale"); known.insert(stem + ".input_global_scale");
+        if (!gs) rep.missing.push_back(stem + ".weight_scale");
+        if (!gg) rep.missing.push_back(stem + ".weight_global_scale");
+        ++rep.found;
+        rep.bytes += packed->nbytes() + (gs ? gs->nbytes() : 0) + (gg ? gg->nbytes() : 0);
+        const std::vector<uint64_t> want_p = {s.shape[0], s.shape[1] / 2}, want_s = {s.shape[0], s.shape[1] / 16};
+        if (packed->shape != want_p) rep.wrong_shape.push_back(stem + ".weight_packed");
+        if (gs && gs->shape != want_s) rep.wrong_shape.push_back(stem + ".weight_scale");
+        if (packed->dtype != "U8") rep.wrong_dtype.push_back(stem + ".weight_packed (" + packed->dtype + ", expected U8)");
+        if (gs && gs->dtype != "F8_E4M3") rep.wrong_dtype.push_back(stem + ".weight_scale (" + gs->dtype + ", expected F8_E4M3)");
+        if (tp_world > 1) {
+          const size_t dim = s.rule == QwenShardRule::RowParallel ? 1 : 0;
+          if (s.shape[dim] % (uint64_t(tp_world) * 16))
+            rep.not_divisible.push_back(stem + ".weight_packed dim " + std::to_string(dim) + " = " + std::to_string(s.shape[dim]));
+        }
+        continue;
+      }
       rep.missing.push_back(s.name);
       continue;
     }

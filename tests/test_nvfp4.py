@@ -66,6 +66,25 @@ def test_oracle_reads_a_mixed_nvfp4_checkpoint():
     assert torch.isfinite(ref.forward(ids)).all()
 
 
+def test_weight_map_audit_accepts_nvfp4_feed_forward_matrices():
+    import os
+    import tempfile
+    from deepseek_v4_2080ti_b200 import pocketllm_cpp as core
+    from deepseek_v4_2080ti_b200.formats import safetensors_io
+    from deepseek_v4_2080ti_b200.models import qwen_hybrid as qh
+    cfg = qh.QwenHybridConfig.tiny(layers=2)
+    mixed = _to_nvfp4_state(list(qh.synth_state(cfg, 0, "cpu", std=0.05)), layers=(0,))
+    with tempfile.TemporaryDirectory() as d:
+        safetensors_io.write_checkpoint(d, iter(mixed), config_json=cfg.to_json())
+        rep = core.qwen_audit(d, 1)
+        assert rep["ok"] and rep["ok_strict"], rep
+    with tempfile.TemporaryDirectory() as d:
+        bad = [(k, v) for k, v in mixed if not k.endswith("layers.0.mlp.up_proj.weight_global_scale")]
+        safetensors_io.write_checkpoint(d, iter(bad), config_json=cfg.to_json())
+        rep = core.qwen_audit(d, 1)
+        assert rep["missing"] == ["model.language_model.layers.0.mlp.up_proj.weight_global_scale"]
+
+
 @pytest.mark.gpu
 def test_runtime_with_nvfp4_feed_forward_matches_the_oracle():
     from deepseek_v4_2080ti_b200.models import qwen_hybrid as qh
