@@ -50,8 +50,13 @@ def test_deepseek_earlier_reasoning_is_dropped_without_tools():
 
 @pytest.mark.parametrize("case,thinking", [(1, True), (2, True), (3, True), (4, False)])
 def test_deepseek_matches_reference_golden_files(case, thinking):
-    base = "/root/reference/tests/fixtures/encoding"
-    if not os.path.exists(f"{base}/test_input_{case}.json"):
+    # golden prompt files of the reference project (tests/fixtures/encoding there): looked for beside this repository
+    # or where POCKETLLM_REFERENCE_DIR points
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    roots = [os.environ.get("POCKETLLM_REFERENCE_DIR", ""), os.path.join(os.path.dirname(here), "reference")]
+    base = next((os.path.join(r, "tests", "fixtures", "encoding") for r in roots
+                 if r and os.path.exists(os.path.join(r, "tests", "fixtures", "encoding", f"test_input_{case}.json"))), None)
+    if base is None:
         pytest.skip("reference fixtures not mounted")
     data = json.load(open(f"{base}/test_input_{case}.json"))
     tools = None
