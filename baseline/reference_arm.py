@@ -113,20 +113,41 @@ def run(args) -> dict:
                             env=env)
     results, tail = [], []
     t_start = time.time()
+    deadline = float(os.environ.get("POCKETLLM_REFERENCE_TIMEOUT_S", "900"))
+    timed_out = []
+
+    def _watchdog():
+        # a wedged rank (a peer that died, a collective that never completes) must not block the caller for ever
+        try:
+            proc.wait(timeout=deadline)
+        except subprocess.TimeoutExpired:
+            timed_out.append(True)
+            proc.kill()
+
+    import threading
+    wd = threading.Thread(target=_watchdog, daemon=True)
+    wd.start()
     try:
         if rank == 0:
-            for _ in range(n_req):
-                proc.stdin.write(line)
-            proc.stdin.close()
+            try:
+                for _ in range(n_req):
+                    proc.stdin.write(line)
+                proc.stdin.close()
+            except (BrokenPipeError, OSError):
+                pass                                   # the engine already exited; its output says why
         for out in proc.stdout:
             tail.append(out.rstrip()[:400])
             tail = tail[-12:]
             if out.startswith("qwen_persistent_result=1"):
                 results.append(out)
-        rc = proc.wait(timeout=3600)
+        rc = proc.wait(timeout=60)
     except Exception as e:  # noqa: BLE001
         proc.kill()
-        return _unavailable(f"reference engine run failed: {type(e).__name__}: {e}")
+        return _unavailable(f"reference engine run failed: {type(e).__name__}: {e}") if rank == 0 else {}
+    if timed_out:
+        shutil.rmtree(work, ignore_errors=True) if rank == 0 else None
+        return _unavailable(f"reference engine did not finish within {int(deadline)} s at tp{world}: "
+                            + " | ".join(tail[-3:])) if rank == 0 else {}
     wall = time.time() - t_start
     if rank != 0:
         return {}
