@@ -6,6 +6,7 @@
 //   --inspect-tensor NAME      print one tensor's header and its first values
 //   --qwen-audit [--qwen-audit-strict] [--tp-world N]   check the checkpoint against the weight map (no GPU needed):
 //                              missing / unexpected tensors, shapes, dtypes, tensor-parallel divisibility
+//   --kv-cache-dtype auto|bf16|fp16   accepted; the 8-bit cache layouts are refused with a pointer to the Python runtime
 //   --context-info             bytes of KV cache / recurrent state per token and per slot
 //   --smoke-forward            run the prompt, generate --max-new-tokens tokens, print tokens and timings
 //   --resident-bench           load once, then time --bench-runs generations of the same prompt
@@ -116,6 +117,14 @@ bool parse(int argc, char** argv, Args& a) {
     else if (arg == "--tokens") a.synthetic = std::atoi(val("--tokens"));
     else if (arg == "--max-new-tokens") a.max_new = std::atoi(val("--max-new-tokens"));
     else if (arg == "--max-context") a.max_context = std::atoll(val("--max-context"));
+    else if (arg == "--kv-cache-dtype") {
+      // the executable keeps the paged cache in bf16; the 8-bit layouts (fp8, int8_per_token_head, turboquant_k8v4)
+      // are served by the Python runtime (pocketllm serve --kv-cache-dtype ...)
+      const std::string v = val("--kv-cache-dtype");
+      if (v == "fp8" || v == "int8_per_token_head" || v == "turboquant_k8v4")
+        throw std::invalid_argument("--kv-cache-dtype " + v + " is not available in this executable (bf16 cache only); use pocketllm serve");
+      if (v != "auto" && v != "bf16" && v != "fp16") throw std::invalid_argument("unknown kv cache dtype: " + v);
+    }
     else if (arg == "--prefill-chunk-tokens") a.chunk = std::atoi(val("--prefill-chunk-tokens"));
     else if (arg == "--smoke-layers") a.layers = std::atoi(val("--smoke-layers"));
     else if (arg == "--max-slots") a.slots = std::atoi(val("--max-slots"));

@@ -86,6 +86,9 @@ def test_weight_map_audit_finds_missing_misshaped_and_indivisible_tensors():
 @needs_exe
 def test_bad_arguments_exit_non_zero():
     assert _run(["--nonsense"]).returncode != 0
+    r = _run(["--ckpt", "x", "--kv-cache-dtype", "fp8", "--dump-config"])
+    assert r.returncode != 0 and "bf16 cache only" in r.stderr
+    assert "unknown kv cache dtype" in _run(["--ckpt", "x", "--kv-cache-dtype", "fp3"]).stderr
     assert _run([]).returncode == 2
     with tempfile.TemporaryDirectory() as d:
         r = _run(["--ckpt", d, "--dump-config"])
