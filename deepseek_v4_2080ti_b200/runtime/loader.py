@@ -241,6 +241,11 @@ def _device(args) -> torch.device:
 def load_runtime(args):
     """Returns (adapter, chat-template family or None, command channel)."""
     world, rank = args.tensor_parallel_size, args.tensor_parallel_rank
+    if getattr(args, "speculative_method", None):
+        # refuse rather than decode without it: the hybrid runtime has no draft / verify / state-rollback path
+        from pocketllm.api.errors import ConfigurationError
+        raise ConfigurationError(f"speculative_method={args.speculative_method!r} is not implemented for the Qwen-style "
+                                 "hybrid runtime (multi-token prediction exists for the MLA family only)")
     dev = _device(args)
     torch.cuda.set_device(dev)
     comm = None

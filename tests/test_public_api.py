@@ -229,3 +229,11 @@ def test_worker_loop_mirrors_commands_and_survives_errors():
     b.run_worker()
     assert [c[0] for c in rt.calls] == ["allocate", "prefill", "decode", "decode", "free"] or \
         [c[0] for c in rt.calls] == ["allocate", "prefill", "decode", "free"]
+
+
+def test_loader_refuses_an_unimplemented_speculative_method_before_touching_a_device():
+    from deepseek_v4_2080ti_b200.runtime import loader
+    from pocketllm.api.errors import ConfigurationError
+    args = EngineArgs(model="synthetic:qwen-tiny", speculative_method="mtp")
+    with pytest.raises(ConfigurationError, match="speculative_method"):
+        loader.load_runtime(args)
