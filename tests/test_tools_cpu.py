@@ -127,3 +127,23 @@ def test_convert_checkpoint_bf16_fp8_fp4_round_trips(capsys):
         s2 = dict(sio.read_checkpoint(back2))
         err = (s2["b.weight"].float() - state["b.weight"].float()).norm() / state["b.weight"].float().norm()
         assert "b.weight_packed" not in s2 and err < 0.15
+
+
+def test_inspect_safetensors_lists_filters_and_audits(capsys):
+    from deepseek_v4_2080ti_b200.cli import inspect_safetensors as ins
+    from deepseek_v4_2080ti_b200.formats import safetensors_io as sio
+    from deepseek_v4_2080ti_b200.models import qwen_hybrid as qh
+    cfg = qh.QwenHybridConfig.tiny(layers=2)
+    state = list(qh.synth_state(cfg, 0, "cpu", std=0.05))
+    with tempfile.TemporaryDirectory() as d:
+        sio.write_checkpoint(d, iter(state), shard_bytes=1 << 20, config_json=cfg.to_json())
+        rep = ins.scan(d)
+        assert len(rep["tensors"]) == len(state) and len(rep["shards"]) > 1 and "F8_E4M3" in rep["bytes_by_dtype"]
+        assert rep["index"]["entries"] == len(state) and not rep["index"]["missing_from_shards"] and not rep["index"]["wrong_shard"]
+        assert ins.main([d, "--grep", "layers.1.", "--audit", "--json"]) == 0
+        out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+        assert out["audit"]["ok"] and all("layers.1." in t["name"] for t in out["tensors"]) and out["tensors"]
+        assert ins.main([d, "--audit", "--tp-world", "3"]) == 3
+        assert "audit_not_divisible=" in capsys.readouterr().out
+    from deepseek_v4_2080ti_b200.cli import generate_glm, generate_gguf
+    assert generate_glm.main is generate_gguf.main
