@@ -127,6 +127,7 @@ def _minimax_runtime(bundle, device="cuda", rank=0, world=1, comm=None, **kw):
 
 class _MlaSlotAdapter:
     """The one-sequence MLA runtime behind the slot interface the GGUF drivers use (allocate / prefill / decode / free)."""
+    single_sequence = True
 
     def __init__(self, rt):
         self.rt = rt

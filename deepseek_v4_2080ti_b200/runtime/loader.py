@@ -232,6 +232,80 @@ class CppRuntimeAdapter:
         return {"kv_blocks_total": self.eng.total_blocks, "kernel_launches": st.kernel_launches, "weight_bytes": st.weight_bytes}
 
 
+class GgufRuntimeAdapter:
+    """The same surface over a GGUF family runtime (``models.registry`` builds it: GQA-MoE with paged slots, or the
+    one-sequence MLA runtime): greedy decoding, sequences admitted up to the runtime's slot count."""
+    supports_sampling = False
+    supports_prefix_cache = False
+    speculative_methods: tuple[str, ...] = ()
+
+    def __init__(self, rt, max_context: int, max_slots: int, device, eos_token_ids=()):
+        self.rt, self.max_context, self.device = rt, max_context, device
+        self.max_slots = 1 if getattr(rt, "single_sequence", False) else max(1, int(max_slots))
+        self.eos_token_ids = tuple(eos_token_ids)
+        self.last_cached_tokens = 0
+        self._active: set[int] = set()
+
+    def allocate(self) -> int:
+        if len(self._active) >= self.max_slots:
+            raise RuntimeError("no free slot")
+        slot = int(self.rt.allocate())
+        self._active.add(slot)
+        return slot
+
+    def free(self, slot: int) -> None:
+        self._active.discard(slot)
+        self.rt.free(slot)
+
+    def prefill_tokens(self, slot: int, prompt: list[int], chunk: int, sp: Any) -> int:
+        ids = torch.tensor([int(t) for t in prompt], dtype=torch.int32).to(self.device)
+        return int(self.rt.prefill(slot, ids, int(chunk) if chunk else 4096).item())
+
+    def decode_tokens(self, slots: list[int], toks: list[int], sp: Any) -> list[int]:
+        if getattr(self.rt, "single_sequence", False):
+            assert len(slots) == 1
+        t = torch.tensor([int(x) for x in toks], dtype=torch.int32).to(self.device)
+        return [int(x) for x in self.rt.decode(list(slots), t).reshape(-1).tolist()]
+
+    def generate_batch(self, prompts, max_new, eos_ids, max_batch):
+        import time
+        results: list[Any] = [None] * len(prompts)
+        pending = list(range(len(prompts)))[::-1]
+        active: dict[int, dict] = {}
+        width = max(1, min(int(max_batch), self.max_slots))
+        while pending or active:
+            while pending and len(active) < width:
+                i = pending.pop()
+                t0 = time.perf_counter()
+                slot = self.allocate()
+                first = self.prefill_tokens(slot, prompts[i], 4096, None)
+                active[i] = {"slot": slot, "out": [first], "t0": t0, "t1": time.perf_counter()}
+            for i in [i for i, a in active.items() if a["out"][-1] in eos_ids or len(a["out"]) >= max_new[i]]:
+                a = active.pop(i)
+                self.free(a["slot"])
+                eos = a["out"][-1] in eos_ids
+                now = time.perf_counter()
+                results[i] = (a["out"][:-1] if eos else a["out"], "stop" if eos else "length",
+                              {"prefill_seconds": a["t1"] - a["t0"], "decode_seconds": now - a["t1"],
+                               "total_seconds": now - a["t0"], "ttft_seconds": a["t1"] - a["t0"]})
+            if active:
+                order = list(active)
+                if getattr(self.rt, "single_sequence", False) or len(order) == 1:
+                    nxt = [self.decode_tokens([active[i]["slot"]], [active[i]["out"][-1]], None)[0] for i in order]
+                else:
+                    nxt = self.decode_tokens([active[i]["slot"] for i in order], [active[i]["out"][-1] for i in order], None)
+                for i, t in zip(order, nxt):
+                    active[i]["out"].append(t)
+        return results
+
+    def stats(self) -> dict:
+        return {"slots_free": self.max_slots - len(self._active), "slots_total": self.max_slots}
+
+
+def _is_gguf(model: str) -> bool:
+    return model.endswith(".gguf") or (os.path.isdir(model) and any(f.endswith(".gguf") for f in os.listdir(model)))
+
+
 def _device(args) -> torch.device:
     if args.device is not None:
         return torch.device(args.device if isinstance(args.device, str) else f"cuda:{args.device}")
@@ -261,6 +335,24 @@ def load_runtime(args):
     model = args.model
     max_ctx = args.max_model_len or 8192 + 512
     slots = max(1, args.max_batch_size)
+    if _is_gguf(model):
+        # MoE families from GGUF: the family registry reads the metadata, validates the tensor inventory and builds the
+        # runtime (attention heads and experts sharded over the ranks); greedy decoding through the slot interface
+        from ..encoding import family_from_architecture
+        from ..formats.gguf import read_bundle
+        from ..models import registry
+        from pocketllm.backends.native_backend import NullChannel
+        bundle = read_bundle(model)
+        spec = registry.detect(bundle)
+        report = spec.validate(bundle)
+        if not report.ok:
+            raise ValueError(f"{model}: missing {report.missing[:4]} unsupported {list(report.unsupported)[:4]}")
+        _, rt = spec.build_runtime(bundle, dev, rank, world, comm, max_slots=slots, max_context=max_ctx)
+        try:
+            family = family_from_architecture(spec.architecture)
+        except ValueError:
+            family = None
+        return GgufRuntimeAdapter(rt, max_ctx, slots, dev), family, channel or NullChannel()
     if getattr(args, "backend", "auto") == "cpp" and world == 1 and not model.startswith("synthetic:"):
         from pocketllm.backends.native_backend import NullChannel
         return CppRuntimeAdapter(args.checkpoint_dir, dev.index or 0, max_ctx, slots,

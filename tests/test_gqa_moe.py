@@ -73,3 +73,37 @@ def test_gpu_runtime_follows_fp32_oracle(types):
     _lib.check_status()
     assert ours[:3] == want[:3], (ours, want)
     assert eager[:3] == want[:3], (eager, want)
+
+
+@pytest.mark.gpu
+def test_public_api_serves_a_gguf_checkpoint():
+    """``pocketllm.LLM`` on a MiniMax-style GGUF file: the loader routes it through the family registry; greedy tokens
+    equal the runtime driven directly."""
+    import os
+    import tempfile
+    from deepseek_v4_2080ti_b200.formats import gguf as G
+    from deepseek_v4_2080ti_b200.models import gqa_moe as gm
+    from deepseek_v4_2080ti_b200.models import registry
+    from pocketllm import LLM, EngineArgs, SamplingParams
+    cfg = gm.GqaMoeConfig.tiny()
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "m.gguf")
+        gm.write_synthetic_gguf(path, cfg, seed=3)
+        b = G.read_bundle(path)
+        _, rt = registry.detect(b).build_runtime(b, "cuda", 0, 1, None, max_slots=2, max_context=256)
+        prompts = [[5, 9, 17, 3, 8], [1, 2, 3]]
+        want = []
+        for p in prompts:
+            s = rt.allocate()
+            t = rt.prefill(s, torch.tensor(p, dtype=torch.int32, device="cuda"), 64)
+            out = [int(t.item())]
+            for _ in range(4):
+                t = rt.decode([s], t.to(torch.int32))
+                out.append(int(t.item()))
+            rt.free(s)
+            want.append(out)
+        del rt
+        llm = LLM(EngineArgs(model=path, max_model_len=256, max_batch_size=2))
+        outs = llm.generate([{"prompt_token_ids": p} for p in prompts], SamplingParams(max_tokens=5))
+        assert [list(o.token_ids) for o in outs] == want
+        llm.close()

@@ -237,3 +237,49 @@ def test_loader_refuses_an_unimplemented_speculative_method_before_touching_a_de
     args = EngineArgs(model="synthetic:qwen-tiny", speculative_method="mtp")
     with pytest.raises(ConfigurationError, match="speculative_method"):
         loader.load_runtime(args)
+
+
+class _FakeGgufRuntime:
+    """next token = (last token + 1) % 50; records the largest decode batch."""
+
+    def __init__(self, single):
+        self.single_sequence = single
+        self.free_ids, self.last, self.max_batch = [2, 1, 0], {}, 0
+
+    def allocate(self):
+        return self.free_ids.pop()
+
+    def free(self, slot):
+        self.free_ids.append(slot)
+        self.last.pop(slot)
+
+    def prefill(self, slot, ids, chunk):
+        import torch
+        self.last[slot] = int(ids[-1])
+        return torch.tensor([(self.last[slot] + 1) % 50])
+
+    def decode(self, slots, toks):
+        import torch
+        self.max_batch = max(self.max_batch, len(slots))
+        return torch.tensor([(int(t) + 1) % 50 for t in toks.tolist()])
+
+
+@pytest.mark.parametrize("single", [False, True])
+def test_gguf_runtime_adapter_batches_up_to_the_runtime_slots(single):
+    from deepseek_v4_2080ti_b200.runtime.loader import GgufRuntimeAdapter, _is_gguf
+    rt = _FakeGgufRuntime(single)
+    ad = GgufRuntimeAdapter(rt, 128, 3, "cpu")
+    assert ad.max_slots == (1 if single else 3) and not ad.supports_sampling
+    res = ad.generate_batch([[1, 2, 3], [10], [48], [7, 8]], [4, 2, 5, 3], {0}, 8)
+    assert res[0][0] == [4, 5, 6, 7] and res[0][1] == "length"
+    assert res[1][0] == [11, 12] and res[3][0] == [9, 10, 11]
+    assert res[2][0] == [49] and res[2][1] == "stop"          # 48 -> 49 -> 0 (eos, dropped)
+    assert rt.max_batch == (1 if single else 3) and sorted(rt.free_ids) == [0, 1, 2] and ad.stats()["slots_free"] == ad.max_slots
+    s = ad.allocate()
+    if single:
+        with pytest.raises(RuntimeError):
+            ad.allocate()
+    ad.prefill_tokens(s, [5], 0, None)
+    assert ad.decode_tokens([s], [6], None) == [7]
+    ad.free(s)
+    assert _is_gguf("model.gguf") and not _is_gguf("/nonexistent/dir")
