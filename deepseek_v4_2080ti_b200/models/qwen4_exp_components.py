@@ -140,7 +140,8 @@ def qsa_select(q: torch.Tensor, raw_keys: torch.Tensor, k_gamma: torch.Tensor, c
     the whole context, cos / sin [B, kv_len, D] rotary tables by absolute position.  Keys are averaged in groups of
     ``ratio``, normalised, rotated at the group's first position and scored by sum_h relu(q_h . k) / sqrt(D); the top
     ``budget / ratio`` complete blocks visible to a query expand to token ids, and the ragged tail after the last
-    complete block is always kept.  Returns int32 [B, S, width], -1 = empty."""
+    complete block is always kept.  Returns int32 [B, S, width], -1 = empty; width is kv_len on the dense path and
+    min(budget // ratio, blocks) * ratio + ratio - 1 on the sparse one."""
     b, s, _, d = q.shape
     kv_len = raw_keys.shape[1]
     dev = q.device
@@ -148,10 +149,7 @@ def qsa_select(q: torch.Tensor, raw_keys: torch.Tensor, k_gamma: torch.Tensor, c
     if kv_len <= budget or kv_len // ratio == 0:
         ids = torch.arange(kv_len, device=dev).view(1, 1, -1).expand(b, s, -1)
         ids = ids.masked_fill(ids >= visible.view(1, -1, 1), -1)
-        width = kv_len if kv_len <= budget else min(kv_len, budget + ratio - 1)
-        if ids.shape[-1] < width:
-            ids = F.pad(ids, (0, width - ids.shape[-1]), value=-1)
-        return ids[..., :width].to(torch.int32)
+        return ids.to(torch.int32)
     nblk = kv_len // ratio
     block_tokens = torch.arange(nblk * ratio, device=dev).view(nblk, ratio)
     pooled = raw_keys[:, :nblk * ratio].reshape(b, nblk, ratio, d).float().mean(2)
@@ -163,13 +161,14 @@ def qsa_select(q: torch.Tensor, raw_keys: torch.Tensor, k_gamma: torch.Tensor, c
     ok = torch.arange(nblk, device=dev).view(1, -1) < blocks_visible.view(-1, 1)
     scores = scores.masked_fill(~ok.unsqueeze(0), float("-inf"))
     topk = min(budget // ratio, nblk)
-    sel = scores.topk(topk, -1).indices
+    # relu makes exact zero scores common; ties go to the lower block id so that the choice does not depend on how many
+    # later blocks exist
+    sel = torch.sort(scores, dim=-1, descending=True, stable=True).indices[..., :topk]
     sel_ok = torch.gather(ok.unsqueeze(0).expand(b, -1, -1), 2, sel)
     toks = block_tokens[sel].reshape(b, s, -1).masked_fill(~sel_ok.unsqueeze(-1).expand(-1, -1, -1, ratio).reshape(b, s, -1), -1)
     tail = (blocks_visible * ratio).view(1, s, 1) + torch.arange(ratio - 1, device=dev).view(1, 1, -1)
     tail = tail.expand(b, -1, -1).masked_fill(~(tail < visible.view(1, s, 1)).expand(b, -1, -1), -1)
-    out = torch.cat([toks, tail], -1)
-    width = min(kv_len, budget + ratio - 1)
-    if out.shape[-1] < width:
-        out = F.pad(out, (0, width - out.shape[-1]), value=-1)
-    return out[..., :width].to(torch.int32)
+    # Every slot is kept: topk * ratio block tokens then ratio - 1 tail slots.  (Cutting the row to kv_len, as the
+    # reference does when budget < kv_len < budget + ratio - 1, drops tail tokens of the early queries of a prefill
+    # chunk and makes the result depend on where the prompt was split.)
+    return torch.cat([toks, tail], -1).to(torch.int32)

@@ -1,0 +1,58 @@
+"""The assembled Qwen4-Exp-style CPU runtime: caches must reproduce the uncached forward pass, however the prompt is split."""
+import pytest
+import torch
+
+from deepseek_v4_2080ti_b200.models import qwen4_exp_ref as q4
+
+
+def _ids(cfg, n, seed=1):
+    return torch.randint(1, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(seed))
+
+
+def _chunked(m, ids, cuts):
+    m.reset()
+    out, prev = [], 0
+    for c in list(cuts) + [ids.numel()]:
+        out.append(m.forward(ids[prev:c]))
+        prev = c
+    return torch.cat(out)
+
+
+@pytest.mark.parametrize("kw", [{}, {"ple_layers": ()}, {"layer_types": ["full"] * 4}, {"layer_types": ["linear"] * 4},
+                                {"ple_layers": (0, 2), "ngram_size": 2, "ngram_head_vocab": (31, 37), "ple_conv_kernel": 3}])
+def test_cached_forward_matches_one_pass(kw):
+    cfg = q4.Qwen4ExpConfig(**kw)
+    m = q4.Qwen4ExpRef(cfg, q4.synth_weights(cfg, 0), 128)
+    ids = _ids(cfg, 45)
+    full = m.forward(ids)
+    assert full.shape == (45, cfg.vocab_size) and torch.isfinite(full).all()
+    for cuts in ([17, 18, 19, 33], [1, 2, 3], list(range(30, 45))):          # 17..19 straddle budget .. budget + ratio - 1
+        got = _chunked(m, ids, cuts)
+        assert torch.allclose(got, full, atol=2e-5, rtol=1e-4), (kw, cuts, (got - full).abs().max())
+
+
+def test_sparse_selection_changes_the_output_only_past_the_budget():
+    cfg = q4.Qwen4ExpConfig()
+    dense = q4.Qwen4ExpConfig(indexer_budget=4096)
+    w = q4.synth_weights(cfg, 3)
+    ms, md = q4.Qwen4ExpRef(cfg, w, 128), q4.Qwen4ExpRef(dense, w, 128)
+    ids = _ids(cfg, 60, seed=5)
+    a, b = ms.forward(ids), md.forward(ids)
+    # a query sees everything while its complete blocks number at most budget / ratio: positions 0 .. budget + ratio - 2
+    exact = cfg.indexer_budget + cfg.indexer_compress_ratio - 1
+    assert torch.allclose(a[:exact], b[:exact], atol=2e-5)
+    assert (a[exact:] - b[exact:]).abs().max() > 1e-4
+
+
+def test_generate_is_deterministic_and_history_feeds_the_ngram_tables():
+    cfg = q4.Qwen4ExpConfig()
+    m = q4.Qwen4ExpRef(cfg, q4.synth_weights(cfg, 0), 128)
+    prompt = _ids(cfg, 20)
+    a = m.generate(prompt, 6, chunk=7)
+    assert a == m.generate(prompt, 6, chunk=64) and len(a) == 6
+    # the n-gram injection reads the token history across calls: the same token after different prefixes differs
+    m.reset(); m.forward(torch.tensor([5, 6])); x = m.forward(torch.tensor([9]))
+    m.reset(); m.forward(torch.tensor([7, 8])); y = m.forward(torch.tensor([9]))
+    assert (x - y).abs().max() > 1e-6
+    with pytest.raises(RuntimeError):
+        q4.Qwen4ExpRef(cfg, q4.synth_weights(cfg, 0), 8).forward(_ids(cfg, 9))
