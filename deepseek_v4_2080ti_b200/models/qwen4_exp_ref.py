@@ -12,6 +12,7 @@ Gated DeltaNet mixer: attention.py:312-436; QSA attention and its block-pooled i
 """
 from __future__ import annotations
 
+import copy
 import math
 from dataclasses import dataclass, field
 
@@ -155,6 +156,15 @@ class Qwen4ExpRef:
                                    "index_k": torch.zeros(0, cfg.indexer_head_dim)})
         self.ple_conv = {i: torch.zeros(cfg.hc_count * cfg.hidden_size, (cfg.ple_conv_kernel - 1) * cfg.ngram_size)
                          for i in cfg.ple_layers}
+
+    def snapshot(self) -> dict:
+        """Copy of every cache (recurrent state, convolution tails, KV, token history): what a speculative verify pass
+        saves so that a rejected block can be undone."""
+        return copy.deepcopy({"length": self.length, "history": self.history, "cache": self.cache, "ple_conv": self.ple_conv})
+
+    def restore(self, snap: dict) -> None:
+        snap = copy.deepcopy(snap)
+        self.length, self.history, self.cache, self.ple_conv = snap["length"], snap["history"], snap["cache"], snap["ple_conv"]
 
     # ---- pieces
     def _ple(self, i: int, streams: torch.Tensor, history: torch.Tensor) -> torch.Tensor:
