@@ -257,7 +257,7 @@ class V4BlockRef:
         self.reset()
 
     def reset(self) -> None:
-        self.length, self.hidden = 0, None
+        self.length, self.hidden, self.layer_hidden = 0, None, []
         for l in self.layers + ([self.mtp] if self.mtp else []):
             l.reset()
 
@@ -279,8 +279,10 @@ class V4BlockRef:
         if start > 0 and s != 1:
             raise RuntimeError("a started sequence continues one token at a time")
         streams = self.w["embed"][ids][:, None, :].repeat(1, cfg.hc_mult, 1)              # [S, hc, D]
+        self.layer_hidden = []                                                            # per layer [S, D]: mean over the streams
         for l in self.layers:
             streams = l.forward(streams, start, ids)
+            self.layer_hidden.append(streams.mean(1))
         self.hidden, self.length = streams, start + s
         return self._head(streams, "")
 
