@@ -336,15 +336,15 @@ PYBIND11_MODULE(pocketllm_cpp, m) {
         return py::make_tuple(r.status, r.content_type, r.body);
       });
 
-  m.def("qwen_expected_tensors", [](const QwenConfig& cfg) {
+  m.def("qwen_expected_tensors", [](const QwenConfig& cfg, bool mtp) {
     py::list out;
-    for (const QwenTensorSpec& s : qwen_expected_tensors(cfg)) {
+    for (const QwenTensorSpec& s : mtp ? qwen_mtp_tensors(cfg) : qwen_expected_tensors(cfg)) {
       py::dict d;
       d["name"] = s.name; d["shape"] = s.shape; d["dtype"] = s.dtype; d["rule"] = to_string(s.rule); d["group"] = s.group;
       out.append(d);
     }
     return out;
-  });
+  }, py::arg("config"), py::arg("mtp") = false);
   m.def("qwen_audit", [](const std::string& dir, int tp_world) {
     SafetensorsModel model(dir);
     const QwenConfig cfg = QwenConfig::from_file(dir + "/config.json");
@@ -352,7 +352,7 @@ PYBIND11_MODULE(pocketllm_cpp, m) {
     py::dict d;
     d["expected"] = r.expected; d["found"] = r.found; d["bytes"] = r.bytes; d["missing"] = r.missing;
     d["unexpected"] = r.unexpected; d["wrong_shape"] = r.wrong_shape; d["wrong_dtype"] = r.wrong_dtype;
-    d["not_divisible"] = r.not_divisible; d["ok"] = r.ok(false); d["ok_strict"] = r.ok(true);
+    d["not_divisible"] = r.not_divisible; d["ok"] = r.ok(false); d["ok_strict"] = r.ok(true); d["has_mtp"] = r.has_mtp;
     return d;
   }, py::arg("checkpoint"), py::arg("tp_world") = 1);
 

@@ -71,6 +71,41 @@ std::vector<QwenTensorSpec> qwen_expected_tensors(const QwenConfig& c) {
   return out;
 }
 
+// The multi-token-prediction head: embedding and hidden state are normalised separately, concatenated and fused by
+// ``mtp.fc`` [H, 2H], then one full-attention decoder layer and ``mtp.norm`` feed the shared lm_head.  Its matrices
+// may be FP8 block-scaled like the trunk or plain BF16.
+std::vector<QwenTensorSpec> qwen_mtp_tensors(const QwenConfig& c) {
+  std::vector<QwenTensorSpec> out;
+  const uint64_t h = uint64_t(c.hidden_size), inter = uint64_t(c.intermediate_size), d = uint64_t(c.head_dim);
+  const uint64_t qd = uint64_t(c.num_attention_heads) * d, kvd = uint64_t(c.num_key_value_heads) * d;
+  auto vec = [&](const std::string& n, uint64_t len) {
+    out.push_back({n, {len}, "BF16", QwenShardRule::Replicated, QwenLinearKind::Vector, 1});
+  };
+  auto lin = [&](const std::string& base, uint64_t n, uint64_t k, QwenShardRule rule, int group) {
+    const size_t first = out.size();
+    fp8(out, base, n, k, rule, group);
+    out[first].dtype = "F8_E4M3|BF16";
+  };
+  vec("mtp.pre_fc_norm_embedding.weight", h);
+  vec("mtp.pre_fc_norm_hidden.weight", h);
+  vec("mtp.norm.weight", h);
+  lin("mtp.fc", h, 2 * h, QwenShardRule::Replicated, 1);
+  const std::string p = "mtp.layers.0.";
+  vec(p + "input_layernorm.weight", h);
+  vec(p + "post_attention_layernorm.weight", h);
+  const int qgroup = int(d) * (c.attn_output_gate ? 2 : 1);
+  lin(p + "self_attn.q_proj", qd * (c.attn_output_gate ? 2 : 1), h, QwenShardRule::ColumnParallel, qgroup);
+  lin(p + "self_attn.k_proj", kvd, h, QwenShardRule::ColumnParallel, int(d));
+  lin(p + "self_attn.v_proj", kvd, h, QwenShardRule::ColumnParallel, int(d));
+  lin(p + "self_attn.o_proj", h, qd, QwenShardRule::RowParallel, int(d));
+  vec(p + "self_attn.q_norm.weight", d);
+  vec(p + "self_attn.k_norm.weight", d);
+  lin(p + "mlp.gate_proj", inter, h, QwenShardRule::ColumnParallel, 128);
+  lin(p + "mlp.up_proj", inter, h, QwenShardRule::ColumnParallel, 128);
+  lin(p + "mlp.down_proj", h, inter, QwenShardRule::RowParallel, 128);
+  return out;
+}
+
 std::vector<uint64_t> qwen_shard_shape(const QwenTensorSpec& s, int world, int rank) {
   std::vector<uint64_t> shape = s.shape;
   if (world <= 1) return shape;
@@ -95,7 +130,14 @@ std::vector<uint64_t> qwen_shard_shape(const QwenTensorSpec& s, int world, int r
 
 QwenAuditReport qwen_audit(SafetensorsModel& model, const QwenConfig& cfg, int tp_world) {
   QwenAuditReport rep;
-  const std::vector<QwenTensorSpec> specs = qwen_expected_tensors(cfg);
+  std::vector<QwenTensorSpec> specs = qwen_expected_tensors(cfg);
+  for (const std::string& n : model.names())
+    if (n.compare(0, 4, "mtp.") == 0) {                  // a checkpoint with an MTP head must have all of it
+      const std::vector<QwenTensorSpec> mtp = qwen_mtp_tensors(cfg);
+      specs.insert(specs.end(), mtp.begin(), mtp.end());
+      rep.has_mtp = true;
+      break;
+    }
   rep.expected = specs.size();
   std::set<std::string> known;
   for (const QwenTensorSpec& s : specs) {
@@ -109,6 +151,10 @@ QwenAuditReport qwen_audit(SafetensorsModel& model, const QwenConfig& cfg, int t
       const bool is_weight = s.name.size() > 7 && s.name.compare(s.name.size() - 7, 7, ".weight") == 0;
       const bool is_scale = s.name.size() > 17 && s.name.compare(s.name.size() - 17, 17, ".weight_scale_inv") == 0;
       const std::string stem = is_weight ? s.name.substr(0, s.name.size() - 7) : is_scale ? s.name.substr(0, s.name.size() - 17) : "";
+      if (is_scale && stem.compare(0, 4, "mtp.") == 0) {   // a BF16 MTP matrix has no scale grid
+        const SafeTensorInfo* wt = model.find(stem + ".weight", &base);
+        if (wt && wt->dtype == "BF16") { --rep.expected; continue; }
+      }
       const SafeTensorInfo* packed = stem.empty() ? nullptr : model.find(stem + ".weight_packed", &base);
       if (packed && s.kind == QwenLinearKind::Fp8Block128) {
         if (is_scale) continue;                          // accounted for with the weight entry
@@ -148,7 +194,7 @@ QwenAuditReport qwen_audit(SafetensorsModel& model, const QwenConfig& cfg, int t
       if (s.rule == QwenShardRule::HeadParallel) unit = uint64_t(tp_world);   // checked per q / k / v range by the loader
       const bool scale = s.name.size() > 17 && s.name.compare(s.name.size() - 17, 17, ".weight_scale_inv") == 0;
       if (!scale && extent % unit) rep.not_divisible.push_back(s.name + " dim " + std::to_string(dim) + " = " + std::to_string(extent));
-      if (!scale && s.kind == QwenLinearKind::Fp8Block128 && (extent / uint64_t(tp_world)) % 128)
+      if (!scale && s.kind == QwenLinearKind::Fp8Block128 && info->dtype == "F8_E4M3" && (extent / uint64_t(tp_world)) % 128)
         rep.not_divisible.push_back(s.name + " shard of " + std::to_string(extent / uint64_t(tp_world)) + " splits a 128-block");
     }
   }

@@ -28,12 +28,14 @@ const char* to_string(QwenShardRule r);
 
 // Every tensor the runtime reads, in load order (FP8 matrices are followed by their ".weight_scale_inv").
 std::vector<QwenTensorSpec> qwen_expected_tensors(const QwenConfig& cfg);
+std::vector<QwenTensorSpec> qwen_mtp_tensors(const QwenConfig& cfg);
 
 // Shape of rank `rank`'s slice of a tensor under tensor parallelism of size `world`.
 std::vector<uint64_t> qwen_shard_shape(const QwenTensorSpec& spec, int world, int rank);
 
 struct QwenAuditReport {
   size_t expected = 0, found = 0;
+  bool has_mtp = false;     // the checkpoint carries mtp.* tensors, so the whole MTP head was required
   uint64_t bytes = 0;
   std::vector<std::string> missing, unexpected, wrong_shape, wrong_dtype, not_divisible;
   bool ok(bool strict) const {

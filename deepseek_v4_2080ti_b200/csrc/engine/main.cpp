@@ -212,9 +212,9 @@ int main(int argc, char** argv) {
       };
       dump("missing", r.missing); dump("unexpected", r.unexpected); dump("wrong_shape", r.wrong_shape);
       dump("wrong_dtype", r.wrong_dtype); dump("not_divisible", r.not_divisible);
-      std::printf("qwen_audit=1 ok=%d expected=%zu found=%zu bytes=%llu tp_world=%d missing=%zu unexpected=%zu\n",
+      std::printf("qwen_audit=1 ok=%d expected=%zu found=%zu bytes=%llu tp_world=%d missing=%zu unexpected=%zu mtp=%d\n",
                   int(r.ok(a.audit_strict)), r.expected, r.found, (unsigned long long)r.bytes, a.tp_world, r.missing.size(),
-                  r.unexpected.size());
+                  r.unexpected.size(), int(r.has_mtp));
       return r.ok(a.audit_strict) ? 0 : 3;
     }
     if (a.context_info) {

@@ -87,4 +87,62 @@ class QwenHybridRef:
             act = _r(F.silu(g_) * u_)
             h = _r(h + _r(self.lin(act, pre + "mlp.down_proj")))
         x = _r(rmsnorm_ref(h, p["model.language_model.norm.weight"], eps, True))
+        self.last_hidden = x                                   # final-normed trunk output [T, H]: what the MTP head consumes
         return x @ p["lm_head.weight"].t()
+
+    @torch.no_grad()
+    def mtp_forward(self, next_ids: torch.Tensor, hidden: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """Multi-token-prediction head over a whole sequence: row i fuses the embedding of ``next_ids[i]`` (the token
+        after position i) with ``hidden[i]`` and predicts the token after that.  Returns (logits [T, vocab], the head's
+        normalised hidden [T, H], which a second recursive step would consume in place of ``hidden``).
+        Reference behaviour: cpp_engine/engine/qwen_engine.cpp:3680-3730 (embedding and hidden normalised separately,
+        concatenated, ``mtp.fc``, one full-attention decoder layer, ``mtp.norm``, shared lm_head)."""
+        cfg, p = self.cfg, self.p
+        t, eps = next_ids.numel(), cfg.rms_norm_eps
+        e = _r(rmsnorm_ref(p["model.language_model.embed_tokens.weight"][next_ids.long()], p["mtp.pre_fc_norm_embedding.weight"], eps, True))
+        hn = _r(rmsnorm_ref(hidden.float(), p["mtp.pre_fc_norm_hidden.weight"], eps, True))
+        h = _r(self.lin(torch.cat([e, hn], -1), "mtp.fc"))
+        pos = torch.arange(t, device=next_ids.device)
+        inv = (1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.rotary_dim, 2, dtype=torch.float64) / cfg.rotary_dim))).float().to(next_ids.device)
+        pre, a = "mtp.layers.0.", "mtp.layers.0.self_attn."
+        hq, hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+        x = _r(rmsnorm_ref(h, p[pre + "input_layernorm.weight"], eps, True))
+        qg = _r(self.lin(x, a + "q_proj")).view(t, hq, -1)
+        q, gate = (qg[..., :128], qg[..., 128:]) if cfg.attn_output_gate else (qg, None)
+        k = _r(self.lin(x, a + "k_proj")).view(t, hkv, 128)
+        v = _r(self.lin(x, a + "v_proj")).view(t, hkv, 128)
+        q = _r(rope_ref(rmsnorm_ref(q, p[a + "q_norm.weight"], eps, True), pos, inv, cfg.rotary_dim))
+        k = _r(rope_ref(rmsnorm_ref(k, p[a + "k_norm.weight"], eps, True), pos, inv, cfg.rotary_dim))
+        h = _r(h + _r(self.lin(_r(attention_ref(q, k, v, 0, gate)).reshape(t, -1), a + "o_proj")))
+        x = _r(rmsnorm_ref(h, p[pre + "post_attention_layernorm.weight"], eps, True))
+        act = _r(F.silu(_r(self.lin(x, pre + "mlp.gate_proj"))) * _r(self.lin(x, pre + "mlp.up_proj")))
+        h = _r(h + _r(self.lin(act, pre + "mlp.down_proj")))
+        out = _r(rmsnorm_ref(h, p["mtp.norm.weight"], eps, True))
+        return out @ p["lm_head.weight"].t(), out
+
+
+def synth_mtp_state(cfg, seed: int = 0, std: float = 0.05, fp8_linears: bool = False):
+    """(name, tensor) pairs of a random MTP head for ``cfg``: bf16 vectors, matrices bf16 or FP8 block-128."""
+    g = torch.Generator().manual_seed(seed + 4242)
+    h, inter, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+    qd, kvd = cfg.num_attention_heads * d, cfg.num_key_value_heads * d
+    out = []
+    vec = lambda n, k: out.append((n, (1.0 + 0.05 * torch.randn(k, generator=g)).to(torch.bfloat16)))
+
+    def lin(base, n, k):
+        w = torch.randn(n, k, generator=g) * std
+        if fp8_linears:
+            q, s = fp8fmt.quantize_block128(w)
+            out.extend([(base + ".weight", q), (base + ".weight_scale_inv", s)])
+        else:
+            out.append((base + ".weight", w.to(torch.bfloat16)))
+
+    vec("mtp.pre_fc_norm_embedding.weight", h); vec("mtp.pre_fc_norm_hidden.weight", h); vec("mtp.norm.weight", h)
+    lin("mtp.fc", h, 2 * h)
+    p = "mtp.layers.0."
+    vec(p + "input_layernorm.weight", h); vec(p + "post_attention_layernorm.weight", h)
+    lin(p + "self_attn.q_proj", qd * (2 if cfg.attn_output_gate else 1), h)
+    lin(p + "self_attn.k_proj", kvd, h); lin(p + "self_attn.v_proj", kvd, h); lin(p + "self_attn.o_proj", h, qd)
+    vec(p + "self_attn.q_norm.weight", d); vec(p + "self_attn.k_norm.weight", d)
+    lin(p + "mlp.gate_proj", inter, h); lin(p + "mlp.up_proj", inter, h); lin(p + "mlp.down_proj", h, inter)
+    return out

@@ -84,6 +84,36 @@ def test_weight_map_audit_finds_missing_misshaped_and_indivisible_tensors():
 
 
 @needs_exe
+def test_weight_map_audit_requires_a_whole_mtp_head_when_one_is_present():
+    from deepseek_v4_2080ti_b200 import pocketllm_cpp as core
+    from deepseek_v4_2080ti_b200.formats import safetensors_io
+    from deepseek_v4_2080ti_b200.models import qwen_hybrid as qh
+    from deepseek_v4_2080ti_b200.models.reference_cpu.qwen_hybrid_ref import synth_mtp_state
+    cfg = qh.QwenHybridConfig.tiny(layers=4)
+    trunk = list(qh.synth_state(cfg, 0, "cpu", std=0.05))
+    for fp8 in (False, True):
+        with tempfile.TemporaryDirectory() as d:
+            mtp = synth_mtp_state(cfg, 0, fp8_linears=fp8)
+            safetensors_io.write_checkpoint(d, iter(trunk + mtp), config_json=cfg.to_json())
+            rep = core.qwen_audit(d, 1)
+            assert rep["ok"] and rep["ok_strict"] and rep["has_mtp"], rep
+            assert rep["found"] == rep["expected"] == len(trunk) + len(mtp)
+            names = {s["name"] for s in core.qwen_expected_tensors(core.QwenConfig.from_file(os.path.join(d, "config.json")), mtp=True)}
+            assert {n for n, _ in mtp} <= names and "mtp.fc.weight" in names
+            r = _run(["--ckpt", d, "--qwen-audit", "--qwen-audit-strict"])
+            assert r.returncode == 0 and "mtp=1" in r.stdout
+    with tempfile.TemporaryDirectory() as d:                      # half a head is an error, not an extra
+        mtp = [(n, t) for n, t in synth_mtp_state(cfg, 0) if n != "mtp.norm.weight"]
+        mtp = [(n, t[:, :-8].contiguous() if n == "mtp.fc.weight" else t) for n, t in mtp]
+        safetensors_io.write_checkpoint(d, iter(trunk + mtp), config_json=cfg.to_json())
+        rep = core.qwen_audit(d, 1)
+        assert rep["missing"] == ["mtp.norm.weight"] and rep["wrong_shape"] == ["mtp.fc.weight"] and not rep["unexpected"]
+    with tempfile.TemporaryDirectory() as d:
+        safetensors_io.write_checkpoint(d, iter(trunk), config_json=cfg.to_json())
+        assert not core.qwen_audit(d, 1)["has_mtp"]
+
+
+@needs_exe
 def test_bad_arguments_exit_non_zero():
     assert _run(["--nonsense"]).returncode != 0
     r = _run(["--ckpt", "x", "--kv-cache-dtype", "fp8", "--dump-config"])
