@@ -266,6 +266,28 @@ class Qwen4ExpRef:
         final = C.gated_residual(streams, w["final.hc_norm"], w["final.down"], w["final.up"], None, hc, h, eps)
         return F.linear(final.float(), w["lm_head"])
 
+    def prefill_cached(self, prompt: torch.Tensor, cache) -> tuple[torch.Tensor, int]:
+        """Prefill through a ``runtime.prefix_cache.PrefixCache``: resume from the longest cached prefix of ``prompt``,
+        compute the rest in pieces that end on the cache's snapshot boundaries and store a snapshot at each.  Returns
+        (logits of the last prompt position [vocab], tokens taken from the cache)."""
+        toks = [int(t) for t in prompt.reshape(-1)]
+        self.reset()
+        hit = cache.lookup(toks)
+        reused = 0
+        if hit is not None:
+            self.restore(hit.snapshot)
+            reused = hit.tokens
+        logits, pos = None, reused
+        for b in cache.boundaries(reused, len(toks)) + [len(toks)]:
+            logits = self.forward(prompt.reshape(-1)[pos:b])
+            pos = b
+            if b < len(toks) and not cache.contains(toks, b):
+                snap = self.snapshot()
+                nbytes = sum(t.numel() * t.element_size() for c in snap["cache"] for t in c.values()) + \
+                    sum(t.numel() * t.element_size() for t in snap["ple_conv"].values())
+                cache.insert(toks, b, [], snap, nbytes)
+        return logits[-1], reused
+
     def generate(self, prompt: torch.Tensor, max_new_tokens: int, chunk: int = 64) -> list[int]:
         self.reset()
         logits = None

@@ -56,3 +56,24 @@ def test_generate_is_deterministic_and_history_feeds_the_ngram_tables():
     assert (x - y).abs().max() > 1e-6
     with pytest.raises(RuntimeError):
         q4.Qwen4ExpRef(cfg, q4.synth_weights(cfg, 0), 8).forward(_ids(cfg, 9))
+
+
+def test_prefix_cache_resumes_recurrent_and_sparse_layers_exactly():
+    from deepseek_v4_2080ti_b200.runtime.prefix_cache import PrefixCache
+    cfg = q4.Qwen4ExpConfig()
+    m = q4.Qwen4ExpRef(cfg, q4.synth_weights(cfg, 0), 160)
+    cache = PrefixCache(interval=16, max_entries=8)
+    shared = _ids(cfg, 50, seed=11)
+    a = torch.cat([shared, _ids(cfg, 9, seed=12)])
+    b = torch.cat([shared, _ids(cfg, 13, seed=13)])
+    la, reused = m.prefill_cached(a, cache)
+    assert reused == 0 and len(cache) == 3                                   # snapshots after 16, 32 and 48 tokens
+    m.reset(); want_a = m.forward(a)[-1]
+    assert torch.allclose(la, want_a, atol=2e-5)
+    lb, reused = m.prefill_cached(b, cache)
+    assert reused == 48 and cache.stats.hits == 1                            # longest shared boundary
+    m.reset(); want_b = m.forward(b)[-1]
+    assert torch.allclose(lb, want_b, atol=2e-5)
+    # the same prompt again stops one boundary short of its end, so logits are still computed
+    la2, reused = m.prefill_cached(a, cache)
+    assert reused == 48 and torch.allclose(la2, want_a, atol=2e-5)
