@@ -231,6 +231,8 @@ class Qwen4ExpRef:
         val, idx = C.topk_softmax_router(x, w[p + "gate"], cfg.experts_per_token, cfg.norm_topk)
         out = torch.zeros_like(x)
         for e in range(cfg.num_experts):
+            if p + f"experts.{e}.gate_proj" not in w:                                     # another rank's expert
+                continue
             hit = (idx == e)
             rows = hit.any(-1)
             if rows.any():
@@ -301,3 +303,102 @@ class Qwen4ExpRef:
                 break
             logits = self.forward(torch.tensor([tok]))
         return out
+
+
+# ---------------------------------------------------------------------------------------------- tensor parallel
+def shard_weights(cfg: Qwen4ExpConfig, w: dict[str, torch.Tensor], rank: int, world: int) -> tuple[Qwen4ExpConfig, dict]:
+    """The slice of a checkpoint one tensor-parallel rank holds, and the configuration it runs with.
+
+    DeltaNet value heads, attention heads (queries with their gates, KV heads) and the shared expert's intermediate
+    width are split; the output projections take the matching columns, so every sub-layer yields a partial sum.  Routed
+    experts go round-robin (``id % world``), the lm_head is split by vocabulary rows, and the hyper-connection mixers,
+    the router, the sparse-attention indexer and the n-gram injection are replicated.
+    Reference behaviour: src/models/qwen4_exp/model.py:292 (TPShard), moe.py:475-501 (expert id % world)."""
+    assert cfg.linear_v_heads % world == 0 and cfg.num_heads % world == 0 and cfg.num_kv_heads % world == 0
+    assert cfg.shared_intermediate % world == 0 and cfg.vocab_size % world == 0
+    split_k = cfg.linear_k_heads % world == 0 and cfg.linear_k_heads >= world
+    kh = cfg.linear_k_heads // world if split_k else cfg.linear_k_heads
+    vh, hq, hkv, d = cfg.linear_v_heads // world, cfg.num_heads // world, cfg.num_kv_heads // world, cfg.head_dim
+    if not split_k:
+        assert vh % kh == 0 or kh % vh == 0
+    import dataclasses
+    rcfg = dataclasses.replace(cfg, linear_k_heads=kh, linear_v_heads=vh, num_heads=hq, num_kv_heads=hkv,
+                               shared_intermediate=cfg.shared_intermediate // world, layer_types=list(cfg.layer_types))
+    KD, VD = cfg.linear_k_heads * 128, cfg.linear_v_heads * 128
+    kr = torch.arange(rank * kh * 128, (rank + 1) * kh * 128) if split_k else torch.arange(KD)
+    if not split_k and cfg.linear_k_heads > 1:               # value head j reads key head j // (Hv / Hk): keep those
+        per = cfg.linear_v_heads // cfg.linear_k_heads
+        heads = sorted({(rank * vh + j) // per for j in range(vh)})
+        kr = torch.cat([torch.arange(hd * 128, (hd + 1) * 128) for hd in heads])
+        rcfg = dataclasses.replace(rcfg, linear_k_heads=len(heads))
+    vr = torch.arange(rank * vh * 128, (rank + 1) * vh * 128)
+    qkv_rows = torch.cat([kr, KD + kr, 2 * KD + vr])
+    hv_rows = torch.arange(rank * vh, (rank + 1) * vh)
+    out = {}
+    for k, t in w.items():
+        leaf = k.rsplit(".", 1)[-1]
+        if ".linear_attn." in k:
+            if leaf in ("in_proj_qkv", "conv1d"):
+                t = t[qkv_rows]
+            elif leaf == "in_proj_z":
+                t = t[vr]
+            elif leaf in ("in_proj_a", "in_proj_b", "A_log", "dt_bias"):
+                t = t[hv_rows]
+            elif leaf == "out_proj":
+                t = t[:, vr]
+        elif ".self_attn." in k:
+            if leaf == "q_proj":
+                t = t[rank * hq * 2 * d:(rank + 1) * hq * 2 * d]
+            elif leaf in ("k_proj", "v_proj"):
+                t = t[rank * hkv * d:(rank + 1) * hkv * d]
+            elif leaf == "o_proj":
+                t = t[:, rank * hq * d:(rank + 1) * hq * d]
+        elif ".mlp.experts." in k:
+            if int(k.split(".experts.")[1].split(".")[0]) % world != rank:
+                continue
+        elif ".mlp.shared." in k:
+            n = cfg.shared_intermediate // world
+            t = t[:, rank * n:(rank + 1) * n] if leaf == "down_proj" else t[rank * n:(rank + 1) * n]
+        elif k == "lm_head":
+            n = cfg.vocab_size // world
+            t = t[rank * n:(rank + 1) * n]
+        out[k] = t.contiguous()
+    return rcfg, out
+
+
+class Qwen4ExpTP:
+    """``world`` ranks of one model stepped in lock-step in this process: every sub-layer's partial outputs are summed
+    (the all-reduce), logits are concatenated (the all-gather).  The replicated parts run once, on rank 0's copy."""
+
+    def __init__(self, cfg: Qwen4ExpConfig, weights: dict, world: int, max_context: int = 512):
+        self.cfg, self.world = cfg, world
+        self.ranks = [Qwen4ExpRef(*shard_weights(cfg, weights, r, world), max_context) for r in range(world)]
+
+    def reset(self) -> None:
+        for r in self.ranks:
+            r.reset()
+
+    @torch.no_grad()
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        cfg, r0 = self.cfg, self.ranks[0]
+        w = r0.w
+        ids = ids.reshape(-1).long()
+        s, past = ids.numel(), r0.length
+        history = torch.cat([r0.history, ids[None]], 1)
+        h, hc, eps = cfg.hidden_size, cfg.hc_count, cfg.rms_norm_eps
+        streams = w["embed"][ids].repeat(1, hc)
+        for i, lt in enumerate(cfg.layer_types):
+            p = f"layers.{i}."
+            if i in cfg.ple_layers:
+                streams = streams + r0._ple(i, streams, history)
+            mixed, inject = C.gated_residual(streams, w[p + "attn_hc.hc_norm"], w[p + "attn_hc.down"], w[p + "attn_hc.up"],
+                                             w[p + "attn_hc.inject"], hc, h, eps)
+            attn = sum(r._deltanet(i, mixed.float()) if lt == "linear" else r._qsa(i, mixed.float(), past) for r in self.ranks)
+            streams = C.inject_into_streams(attn, streams, inject.float())
+            mixed, inject = C.gated_residual(streams, w[p + "mlp_hc.hc_norm"], w[p + "mlp_hc.down"], w[p + "mlp_hc.up"],
+                                             w[p + "mlp_hc.inject"], hc, h, eps)
+            streams = C.inject_into_streams(sum(r._mlp(i, mixed.float()) for r in self.ranks), streams, inject.float())
+        for r in self.ranks:
+            r.length, r.history = past + s, history[:, -(cfg.ngram_size - 1):].clone()
+        final = C.gated_residual(streams, w["final.hc_norm"], w["final.down"], w["final.up"], None, hc, h, eps).float()
+        return torch.cat([F.linear(final, r.w["lm_head"]) for r in self.ranks], -1)

@@ -77,3 +77,27 @@ def test_prefix_cache_resumes_recurrent_and_sparse_layers_exactly():
     # the same prompt again stops one boundary short of its end, so logits are still computed
     la2, reused = m.prefill_cached(a, cache)
     assert reused == 48 and torch.allclose(la2, want_a, atol=2e-5)
+
+
+@pytest.mark.parametrize("kw,world", [({}, 2), ({"linear_k_heads": 2, "linear_v_heads": 4, "num_heads": 8, "num_kv_heads": 4}, 2),
+                                      ({"linear_k_heads": 2, "linear_v_heads": 8, "num_heads": 8, "num_kv_heads": 4}, 4)])
+def test_tensor_parallel_shards_reproduce_the_unsharded_model(kw, world):
+    cfg = q4.Qwen4ExpConfig(**kw)
+    w = q4.synth_weights(cfg, 0)
+    ids = _ids(cfg, 40)
+    full = q4.Qwen4ExpRef(cfg, w, 128).forward(ids)
+    tp = q4.Qwen4ExpTP(cfg, w, world, 128)
+    got = torch.cat([tp.forward(ids[:25]), tp.forward(ids[25:])])            # prefill, then a continuation on the caches
+    assert torch.allclose(got, full, atol=2e-5, rtol=1e-4)
+    # what a rank holds: its experts only, a slice of the heads, every replicated tensor whole
+    rcfg, shard = q4.shard_weights(cfg, w, 1, world)
+    owned = {int(k.split(".experts.")[1].split(".")[0]) for k in shard if ".mlp.experts." in k}
+    assert owned == {e for e in range(cfg.num_experts) if e % world == 1}
+    assert shard["lm_head"].shape[0] == cfg.vocab_size // world and rcfg.num_heads == cfg.num_heads // world
+    assert shard["layers.1.self_attn.o_proj"].shape[1] == cfg.num_heads * cfg.head_dim // world
+    assert torch.equal(shard["layers.1.self_attn.index_qk_proj"], w["layers.1.self_attn.index_qk_proj"])
+    assert torch.equal(shard["layers.0.attn_hc.down"], w["layers.0.attn_hc.down"])
+    sizes = [sum(t.numel() for t in q4.shard_weights(cfg, w, r, world)[1].values()) for r in range(world)]
+    assert max(sizes) < sum(t.numel() for t in w.values())
+    with pytest.raises(AssertionError):
+        q4.shard_weights(q4.Qwen4ExpConfig(), q4.synth_weights(q4.Qwen4ExpConfig(), 0), 0, 3)
