@@ -9,6 +9,7 @@ Endpoints (same as the reference, pocketllm/server/openai.py:176-322):
 from __future__ import annotations
 
 import json
+import os
 import threading
 import time
 import uuid
@@ -44,8 +45,10 @@ def error_body(exc: BaseException, status: int) -> dict[str, Any]:
 
 
 class ServerState:
-    def __init__(self, backend: Any, served_model_name: str = "pocketllm", metrics: Metrics | None = None):
+    def __init__(self, backend: Any, served_model_name: str = "pocketllm", metrics: Metrics | None = None,
+                 batching: Any = None):
         self.backend = backend
+        self.batching = batching          # a BatchingQueue: non-streamed requests that arrive together share one generate call
         self.model_name = served_model_name
         self.metrics = metrics or Metrics()
         self.started = time.time()
@@ -193,7 +196,7 @@ def make_handler(state: ServerState):
                 if body.get("stream"):
                     self._stream(req, is_chat)
                 else:
-                    res = state.backend.generate([req])[0]
+                    res = state.batching.submit(req) if state.batching is not None else state.backend.generate([req])[0]
                     created = int(t0)
                     self._json(200, _chat_payload(state, res, created, had_tools) if is_chat
                                else _completion_payload(state, res, created))
@@ -274,8 +277,16 @@ def make_handler(state: ServerState):
 
 
 def make_server(backend: Any, host: str = "127.0.0.1", port: int = 8000, served_model_name: str = "pocketllm",
-                metrics: Metrics | None = None) -> tuple[ThreadingHTTPServer, ServerState]:
-    state = ServerState(backend, served_model_name, metrics)
+                metrics: Metrics | None = None, batch_requests: bool | None = None) -> tuple[ThreadingHTTPServer, ServerState]:
+    """``batch_requests`` (default: the ``POCKETLLM_SERVING_BATCHING`` environment switch) puts a ``BatchingQueue`` in
+    front of ``backend.generate`` for non-streamed requests; its limits come from ``POCKETLLM_SERVING_*``."""
+    if batch_requests is None:
+        batch_requests = os.environ.get("POCKETLLM_SERVING_BATCHING", "0").lower() in ("1", "true", "yes", "on")
+    batching = None
+    if batch_requests:
+        from .batching import BatchingQueue
+        batching = BatchingQueue.from_env(lambda reqs, emit: backend.generate(list(reqs)))
+    state = ServerState(backend, served_model_name, metrics, batching)
     httpd = ThreadingHTTPServer((host, port), make_handler(state))
     httpd.daemon_threads = True
     return httpd, state

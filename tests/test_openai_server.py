@@ -101,3 +101,33 @@ def test_metrics_registry_quantiles():
     text = m.render()
     assert 'pocketllm_lat{quantile="0.5"} 50.5' in text and "pocketllm_lat_count 100" in text
     assert 'a="x\\"y"' in text
+
+
+def test_batched_serving_groups_concurrent_requests(monkeypatch):
+    monkeypatch.setenv("POCKETLLM_SERVING_BATCH_WAIT_MS", "300")
+    backend = NativeBackend(EngineArgs(model="fake"), runtime=FakeRuntime())
+    sizes = []
+    inner = backend.generate
+
+    def spy(reqs):
+        reqs = list(reqs)
+        sizes.append(len(reqs))
+        return inner(reqs)
+    backend.generate = spy
+    httpd, state = make_server(backend, "127.0.0.1", 0, "fake-model", batch_requests=True)
+    t = threading.Thread(target=httpd.serve_forever, kwargs={"poll_interval": 0.05}, daemon=True)
+    t.start()
+    try:
+        port, out = httpd.server_address[1], [None] * 3
+        ts = [threading.Thread(target=lambda i=i: out.__setitem__(i, call(port, "POST", "/v1/completions",
+                                                                          {"prompt": "A", "max_tokens": 3}))) for i in range(3)]
+        for x in ts:
+            x.start()
+        for x in ts:
+            x.join()
+        assert all(st == 200 and json.loads(raw)["choices"][0]["text"] == "BCD" for st, raw in out)
+        assert sum(sizes) == 3 and max(sizes) >= 2 and state.batching.stats.batched_requests == 3
+    finally:
+        httpd.shutdown()
+        httpd.server_close()
+        state.batching.close()
