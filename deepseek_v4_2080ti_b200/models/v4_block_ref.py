@@ -261,6 +261,36 @@ class V4BlockRef:
         for l in self.layers + ([self.mtp] if self.mtp else []):
             l.reset()
 
+    _STATE = ("kv", "ikeys")
+
+    def snapshot(self) -> dict:
+        """Everything positional a prefix cache must keep: per layer the window ring + compressed rows, the running
+        state of the KV compressor and of the indexer's compressor, and the indexer keys."""
+        import copy
+        layers = []
+        for l in self.layers + ([self.mtp] if self.mtp else []):
+            st = {k: getattr(l, k).clone() for k in self._STATE if hasattr(l, k)}
+            for name in ("comp", "icomp"):
+                c = getattr(l, name)
+                if c is not None:
+                    st[name] = (c.kv_state.clone(), c.score_state.clone())
+            layers.append(st)
+        return {"length": self.length, "layers": layers, "hidden": copy.deepcopy(self.hidden),
+                "layer_hidden": [h.clone() for h in self.layer_hidden]}
+
+    def restore(self, snap: dict) -> None:
+        self.length = snap["length"]
+        self.hidden = None if snap["hidden"] is None else snap["hidden"].clone()
+        self.layer_hidden = [h.clone() for h in snap["layer_hidden"]]
+        for l, st in zip(self.layers + ([self.mtp] if self.mtp else []), snap["layers"]):
+            for k in self._STATE:
+                if k in st:
+                    setattr(l, k, st[k].clone())
+            for name in ("comp", "icomp"):
+                if name in st:
+                    c = getattr(l, name)
+                    c.kv_state, c.score_state = st[name][0].clone(), st[name][1].clone()
+
     def _head(self, streams: torch.Tensor, p: str) -> torch.Tensor:
         cfg, w = self.cfg, self.w
         flat = streams.flatten(1)

@@ -81,3 +81,28 @@ def test_mtp_draft_is_cache_consistent_and_speculative_loop_matches_greedy():
     assert toks == m.generate(ids[:12], 8) and 0 <= hits <= 7
     with pytest.raises(RuntimeError):
         m.forward(ids[:2])                                # a started sequence takes one token at a time
+
+
+def test_snapshot_restore_resumes_a_shared_prefix_exactly():
+    from deepseek_v4_2080ti_b200.runtime.prefix_cache import PrefixCache
+    cfg = v4.V4Config()
+    m = v4.V4BlockRef(cfg, v4.synth_weights(cfg, 0))
+    ids = _ids(cfg, 40, 8)
+    full = m.forward(ids)
+    m.reset(); m.forward(ids[:24]); snap = m.snapshot()
+    a = torch.cat([m.forward(ids[i:i + 1]) for i in range(24, 40)])
+    m.reset(); m.forward(_ids(cfg, 30, 9))                    # unrelated traffic in between
+    m.restore(snap)
+    b = torch.cat([m.forward(ids[i:i + 1]) for i in range(24, 40)])
+    assert torch.equal(a, b) and torch.allclose(a, full[24:], atol=5e-5, rtol=1e-4)
+    # through the prefix cache: the state after 24 tokens is found again for a prompt that shares them
+    cache = PrefixCache(interval=8, max_entries=4)
+    toks = ids.tolist()
+    assert cache.insert(toks, 24, [], snap, 1 << 10)
+    other = toks[:24] + _ids(cfg, 6, 10).tolist()
+    hit = cache.lookup(other)
+    assert hit is not None and hit.tokens == 24
+    m.restore(hit.snapshot)
+    got = torch.cat([m.forward(torch.tensor([t])) for t in other[24:]])
+    m.reset()
+    assert torch.allclose(got, m.forward(torch.tensor(other))[24:], atol=5e-5, rtol=1e-4)
