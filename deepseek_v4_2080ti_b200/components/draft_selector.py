@@ -83,3 +83,43 @@ def path_score(tokens: list[int], projected: torch.Tensor, candidates: torch.Ten
                               projected[p], predecessor, successor)[0, 0])
         prev = int(t)
     return total
+
+
+# ---------------------------------------------------------------------------------------------- block-drafter pieces
+def grouped_dynamic_conv(hidden: torch.Tensor, dynamic: torch.Tensor, base: torch.Tensor, group_size: int) -> torch.Tensor:
+    """Causal depthwise convolution over the rows of a drafted block whose taps are a learned base kernel plus a
+    per-row correction shared by groups of channels:
+
+        out[r, c] = sum_t hidden[r - t, c] * (base[t, c] + dynamic[r, t * G + c // group_size]),   rows before 0 are zero
+
+    hidden [rows, H], base [K, H], dynamic [rows, K * G] with G = H / group_size (the row's own projection of its hidden
+    state).  fp32 result.  Reference behaviour: qwen_dflash2_ops.cu:81-117 (grouped_dynamic_conv_kernel)."""
+    rows, h = hidden.shape
+    k = base.shape[0]
+    g = h // group_size
+    assert h % group_size == 0 and dynamic.shape == (rows, k * g)
+    x = hidden.float()
+    taps = base.float()[None, :, :] + dynamic.float().view(rows, k, g).repeat_interleave(group_size, dim=2)      # [rows, K, H]
+    out = torch.zeros(rows, h, dtype=torch.float32, device=hidden.device)
+    for t in range(min(k, rows)):
+        out[t:] += x[:rows - t] * taps[t:, t]
+    return out
+
+
+def sharded_topk(logit_shards: list[torch.Tensor], k: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-position candidates from a vocabulary-sharded head: every shard [rows, V_s] contributes its own top ``k``,
+    the winners are merged.  Returns (token ids int64 [rows, k], logits [rows, k]) sorted by descending logit, equal
+    logits by ascending token id - the ``candidates`` / ``unary`` inputs of the selector.
+    Reference behaviour: the local top-k + gather of qwen_dflash2.cpp:1100-1170."""
+    ids, vals, off = [], [], 0
+    for sh in logit_shards:
+        kk = min(k, sh.shape[1])
+        v, i = sh.float().topk(kk, -1)
+        ids.append(i + off)
+        vals.append(v)
+        off += sh.shape[1]
+    ids, vals = torch.cat(ids, -1), torch.cat(vals, -1)
+    order = torch.argsort(ids, dim=-1, stable=True)                          # ascending id first, then a stable sort by value
+    ids, vals = ids.gather(-1, order), vals.gather(-1, order)
+    order = torch.argsort(vals, dim=-1, descending=True, stable=True)[:, :k]
+    return ids.gather(-1, order), vals.gather(-1, order)

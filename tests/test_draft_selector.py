@@ -54,3 +54,38 @@ def test_ties_go_to_the_smaller_token_and_the_anchor_matters():
     pred[10, 0] = 1.0; succ[6, 0] = 2.0
     assert sel.greedy_path(proj, cand, zeros, pred, succ, 10)[0][0] == 6
     assert sel.viterbi_path(proj, cand, zeros, pred, succ, 11)[0][0] == 4
+
+
+def test_grouped_dynamic_conv_matches_the_scalar_definition():
+    g = torch.Generator().manual_seed(0)
+    rows, h, k, gs = 8, 12, 3, 4
+    hidden, base, dyn = torch.randn(rows, h, generator=g), torch.randn(k, h, generator=g), torch.randn(rows, k * (h // gs), generator=g)
+    want = torch.zeros(rows, h)
+    for r in range(rows):
+        for c in range(h):
+            for t in range(k):
+                if r - t >= 0:
+                    want[r, c] += hidden[r - t, c] * (base[t, c] + dyn[r, t * (h // gs) + c // gs])
+    got = sel.grouped_dynamic_conv(hidden, dyn, base, gs)
+    assert torch.allclose(got, want, atol=1e-5)
+    # causal: a later row does not change earlier outputs; with a zero correction it is a plain depthwise convolution
+    h2 = hidden.clone(); h2[5] += 1.0
+    assert torch.equal(sel.grouped_dynamic_conv(h2, dyn, base, gs)[:5], got[:5])
+    plain = sel.grouped_dynamic_conv(hidden, torch.zeros_like(dyn), base, gs)
+    ref = torch.nn.functional.conv1d(torch.nn.functional.pad(hidden.t()[None], (k - 1, 0)), base.flip(0).t()[:, None, :], groups=h)[0].t()
+    assert torch.allclose(plain, ref, atol=1e-5)
+
+
+def test_sharded_topk_equals_the_top_k_of_the_whole_vocabulary():
+    g = torch.Generator().manual_seed(1)
+    logits = torch.randn(5, 64, generator=g)
+    logits[0, 10] = logits[0, 50] = 9.0                      # a tie across shards goes to the smaller id
+    ids, vals = sel.sharded_topk(list(logits.split(16, -1)), 4)
+    v, i = logits.topk(4, -1)
+    assert torch.allclose(vals, v) and torch.equal(ids[1:], i[1:])
+    assert ids[0, :2].tolist() == [10, 50]
+    one, _ = sel.sharded_topk([logits], 4)
+    assert torch.equal(one[1:], i[1:])
+    # feeding the selector: with no chain term the path is the per-position arg-max
+    proj, pred, succ = torch.zeros(5, 2), torch.zeros(64, 2), torch.zeros(64, 2)
+    assert sel.viterbi_path(proj, ids, vals, pred, succ, 0)[0] == [int(ids[p, 0]) for p in range(5)]
