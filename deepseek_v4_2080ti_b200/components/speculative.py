@@ -120,3 +120,53 @@ def speculative_generate(target, drafter, prompt: torch.Tensor, max_new_tokens: 
     if gate is not None:
         st.gate = gate.stats()
     return out, st
+
+
+# ---------------------------------------------------------------------------------------------- cache-free oracles
+class WholeSequenceTarget:
+    """Adapts an oracle with only ``forward(all_ids) -> logits [T, vocab]`` (no caches) to the target protocol by
+    re-running the whole context; the state is just the token list, so snapshot / restore are exact and free.
+    ``hidden`` holds the oracle's ``last_hidden`` of the latest pass when it has one."""
+
+    def __init__(self, oracle):
+        self.oracle, self.ids, self.hidden = oracle, [], None
+
+    def reset(self) -> None:
+        self.ids, self.hidden = [], None
+
+    def snapshot(self) -> list[int]:
+        return list(self.ids)
+
+    def restore(self, snap: list[int]) -> None:
+        self.ids = list(snap)
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        n = ids.numel()
+        self.ids.extend(int(t) for t in ids.reshape(-1))
+        logits = self.oracle.forward(torch.tensor(self.ids))
+        self.hidden = getattr(self.oracle, "last_hidden", None)
+        return logits[-n:]
+
+
+class MtpDrafter:
+    """Drafts with a multi-token-prediction head applied recursively: step 1 fuses the trunk's hidden states with the
+    embeddings of the tokens that follow them (the last being the committed token), step j > 1 shifts the tokens by
+    one, appends the previous draft and consumes the head's own hidden states.  Confidence is the margin between the
+    two best draft logits.  ``target`` must be the ``WholeSequenceTarget`` of an oracle with ``mtp_forward``."""
+
+    def __init__(self, target: WholeSequenceTarget):
+        self.t = target
+
+    def propose(self, context: list[int], k: int) -> tuple[list[int], list[float]]:
+        hidden = self.t.hidden
+        if k <= 0 or hidden is None or hidden.shape[0] != len(context) - 1:
+            return [], []
+        nxt = torch.tensor(context[1:])
+        toks, conf = [], []
+        for _ in range(k):
+            logits, hidden = self.t.oracle.mtp_forward(nxt, hidden)
+            top = logits[-1].float().topk(2).values
+            toks.append(int(logits[-1].argmax()))
+            conf.append(float(top[0] - top[1]))
+            nxt = torch.cat([nxt[1:], torch.tensor([toks[-1]])])
+        return toks, conf

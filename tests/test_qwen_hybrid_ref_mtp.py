@@ -30,3 +30,26 @@ def test_mtp_head_is_causal_recursive_and_format_agnostic():
     g.forward(ids)
     out_q, _ = g.mtp_forward(nxt, g.last_hidden)
     assert (out_q - out).abs().max() < 0.15 * out.abs().max()
+
+
+def test_speculative_decoding_with_the_mtp_head_reproduces_greedy():
+    from deepseek_v4_2080ti_b200.components.spec_gate import SpecGate
+    from deepseek_v4_2080ti_b200.components.speculative import MtpDrafter, WholeSequenceTarget, speculative_generate
+    cfg = qh.QwenHybridConfig.tiny(layers=4)
+    ref = QwenHybridRef(cfg, dict(list(qh.synth_state(cfg, 0, "cpu", std=0.05)) + synth_mtp_state(cfg, 0)))
+    prompt = torch.randint(0, cfg.vocab_size, (10,), generator=torch.Generator().manual_seed(4))
+    ids, greedy = prompt.tolist(), []
+    for _ in range(8):
+        greedy.append(int(ref.forward(torch.tensor(ids))[-1].argmax()))
+        ids.append(greedy[-1])
+    tgt = WholeSequenceTarget(ref)
+    out, st = speculative_generate(tgt, MtpDrafter(tgt), prompt, 8, block=2)
+    assert out == greedy and st.rounds > 0 and st.accepted <= st.drafted <= 2 * st.rounds
+    out_g, st_g = speculative_generate(tgt, MtpDrafter(tgt), prompt, 8, block=2, gate=SpecGate(2))
+    assert out_g == greedy and st_g.gate["rounds"] >= 1
+    # the first draft is the head's own prediction for the position after the committed token
+    tgt.reset(); lg = tgt.forward(prompt)
+    committed = int(lg[-1].argmax())
+    d, conf = MtpDrafter(tgt).propose(prompt.tolist() + [committed], 2)
+    want, _ = ref.mtp_forward(torch.tensor(prompt.tolist()[1:] + [committed]), tgt.hidden)
+    assert d[0] == int(want[-1].argmax()) and len(conf) == 2 and all(c >= 0 for c in conf)
