@@ -9,7 +9,7 @@ repository carries them:
   rebuilds in seconds).
 * ``lib/libb200_core.so`` + ``pocketllm_cpp`` pybind module - the C++ runtime
   (block pool/table, scheduler, command channel, readers, tokenizer, sampler).
-* ``lib/libb200_cpu.so`` - AVX2 multi-threaded host kernels (FP4 routed experts on the CPU).
+* ``lib/libb200_cpu.so`` - AVX2 multi-threaded host kernels (FP4 and INT8 routed experts on the CPU).
 * ``bin/pocketllm_engine`` - the native executable.
 
 The reference builds its native plane with CMake for sm_75
@@ -166,7 +166,7 @@ def build_selftest(sanitizer: str = "") -> Path:
 
 
 def build_cpu() -> Path | None:
-    """AVX2 multi-threaded host kernels (csrc/cpu): the CPU oracle path for FP4 routed experts."""
+    """AVX2 multi-threaded host kernels (csrc/cpu): the CPU path for FP4 and INT8 routed experts."""
     OBJ.mkdir(exist_ok=True)
     LIB.mkdir(exist_ok=True)
     srcs = sorted((CSRC / "cpu").glob("*.cpp"))

@@ -222,6 +222,36 @@ def cpu_moe_fp4(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, w13, s13,
     return out
 
 
+def quantize_rows_int8(w: torch.Tensor, threads: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-row symmetric INT8: w [..., N, K] fp32 -> (int8 [..., N, K], fp32 scale [..., N]), scale = max|row| / 127."""
+    w = w.contiguous().float()
+    n, k = int(w.numel() // w.shape[-1]), w.shape[-1]
+    q = torch.empty(w.shape, dtype=torch.int8)
+    s = torch.empty(w.shape[:-1], dtype=torch.float32)
+    p = lambda a: ctypes.c_void_p(a.data_ptr())
+    if cpu_lib().b200_cpu_quantize_rows_int8(p(w), n, k, p(q), p(s), threads) != 0:
+        raise RuntimeError("cpu_quantize_rows_int8 rejected its arguments")
+    return q, s
+
+
+def cpu_moe_int8(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, w13: torch.Tensor, s13: torch.Tensor, w2: torch.Tensor,
+                 s2: torch.Tensor, swiglu_limit: float = 0.0, threads: int = 0) -> torch.Tensor:
+    """Routed INT8 (W8A8) experts on the host.  x [T, H] fp32; idx [T, K] int32; wts [T, K] fp32; w13 int8 [E, 2I, H] with
+    s13 [E, 2I]; w2 int8 [E, H, I] with s2 [E, H]; returns [T, H] fp32."""
+    t, h = x.shape
+    e, two_i, _ = w13.shape
+    assert w13.dtype == torch.int8 and w2.dtype == torch.int8 and w2.shape == (e, h, two_i // 2)
+    out = torch.zeros(t, h, dtype=torch.float32)
+    x, idx, wts = x.contiguous().float(), idx.contiguous().to(torch.int32), wts.contiguous().float()
+    w13, w2, s13, s2 = w13.contiguous(), w2.contiguous(), s13.contiguous().float(), s2.contiguous().float()
+    p = lambda a: ctypes.c_void_p(a.data_ptr())
+    rc = cpu_lib().b200_cpu_moe_int8_forward(p(x), t, h, p(idx), p(wts), idx.shape[1], p(w13), p(s13), p(w2), p(s2), e,
+                                             two_i // 2, ctypes.c_float(swiglu_limit), p(out), threads)
+    if rc != 0:
+        raise RuntimeError("cpu_moe_int8_forward rejected its arguments")
+    return out
+
+
 # ------------------------------------------------------------------ shared math
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     xf = x.float()

@@ -1,0 +1,76 @@
+"""Host INT8 (W8A8) routed experts against a PyTorch statement of the same quantised arithmetic."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from deepseek_v4_2080ti_b200.models import mla_moe
+
+
+def _q(x):
+    amax = x.abs().amax(-1, keepdim=True)
+    scale = amax / 127.0
+    q = torch.where(amax > 0, torch.round(x / scale.clamp_min(1e-30)).clamp(-127, 127), torch.zeros_like(x))
+    return q, scale.squeeze(-1)
+
+
+def _oracle(x, idx, wts, w13q, s13, w2q, s2, limit):
+    t, h = x.shape
+    inter = w13q.shape[1] // 2
+    xq, xs = _q(x)
+    out = torch.zeros(t, h)
+    for ti in range(t):
+        for k in range(idx.shape[1]):
+            e = int(idx[ti, k])
+            if e < 0:
+                continue
+            acc = (w13q[e].double() @ xq[ti].double()).float() * (xs[ti] * s13[e])
+            gate, up = acc[:inter], acc[inter:]
+            if limit > 0:
+                gate, up = gate.clamp(max=limit), up.clamp(-limit, limit)
+            hid = wts[ti, k] * F.silu(gate) * up
+            hq, hs = _q(hid[None])
+            out[ti] += (w2q[e].double() @ hq[0].double()).float() * (hs[0] * s2[e])
+    return out
+
+
+@pytest.mark.parametrize("t,h,inter,e,k,limit", [(5, 64, 48, 6, 2, 0.0), (3, 100, 36, 4, 3, 1.5), (1, 32, 16, 2, 1, 0.0)])
+def test_int8_moe_matches_the_quantised_statement_and_the_float_model(t, h, inter, e, k, limit):
+    g = torch.Generator().manual_seed(t + h)
+    x = torch.randn(t, h, generator=g)
+    w13, w2 = torch.randn(e, 2 * inter, h, generator=g) * 0.1, torch.randn(e, h, inter, generator=g) * 0.1
+    idx = torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(t)]).to(torch.int32)
+    if t > 1:
+        idx[1, -1] = -1                                        # an unused route
+    wts = torch.rand(t, k, generator=g)
+    w13q, s13 = mla_moe.quantize_rows_int8(w13)
+    w2q, s2 = mla_moe.quantize_rows_int8(w2)
+    rq, rs = _q(w13)
+    assert torch.equal(w13q.float(), rq) and torch.allclose(s13, rs) and w13q.dtype == torch.int8
+    got = mla_moe.cpu_moe_int8(x, idx, wts, w13q, s13, w2q, s2, limit, threads=3)
+    want = _oracle(x, idx, wts, w13q.float(), s13, w2q.float(), s2, limit)
+    assert torch.allclose(got, want, atol=2e-3 * want.abs().max().item() + 1e-6), (got - want).abs().max()
+    assert torch.equal(got, mla_moe.cpu_moe_int8(x, idx, wts, w13q, s13, w2q, s2, limit, threads=1))     # thread-count invariant
+    # and it is a faithful 8-bit approximation of the float experts
+    ref = torch.zeros(t, h)
+    for ti in range(t):
+        for kk in range(k):
+            ee = int(idx[ti, kk])
+            if ee >= 0:
+                a = w13[ee] @ x[ti]
+                gt, up = a[:inter], a[inter:]
+                if limit > 0:
+                    gt, up = gt.clamp(max=limit), up.clamp(-limit, limit)
+                ref[ti] += wts[ti, kk] * (w2[ee] @ (F.silu(gt) * up))
+    assert (got - ref).abs().max() < 0.05 * ref.abs().max() + 1e-3
+
+
+def test_int8_moe_rejects_bad_routes_and_handles_zero_rows():
+    x = torch.zeros(2, 32)
+    w13q, s13 = mla_moe.quantize_rows_int8(torch.randn(2, 32, 32))
+    w2q, s2 = mla_moe.quantize_rows_int8(torch.randn(2, 32, 16))
+    idx, wts = torch.tensor([[0], [1]], dtype=torch.int32), torch.ones(2, 1)
+    assert torch.equal(mla_moe.cpu_moe_int8(x, idx, wts, w13q, s13, w2q, s2), torch.zeros(2, 32))
+    with pytest.raises(RuntimeError):
+        mla_moe.cpu_moe_int8(x, torch.tensor([[0], [5]], dtype=torch.int32), wts, w13q, s13, w2q, s2)
+    zq, zs = mla_moe.quantize_rows_int8(torch.zeros(3, 8))
+    assert not zq.any() and not zs.any()
