@@ -127,6 +127,17 @@ def test_convert_checkpoint_bf16_fp8_fp4_round_trips(capsys):
         s2 = dict(sio.read_checkpoint(back2))
         err = (s2["b.weight"].float() - state["b.weight"].float()).norm() / state["b.weight"].float().norm()
         assert "b.weight_packed" not in s2 and err < 0.15
+        # INT8 per-row (the host expert layout) as a target and as a source
+        i8, back3 = os.path.join(d, "int8"), os.path.join(d, "back3")
+        assert cc.main([f8, i8, "--to", "int8", "--match", "a."]) == 0
+        si = dict(sio.read_checkpoint(i8))
+        assert si["a.weight"].dtype == torch.int8 and si["a.scale"].shape == (256,) and si["a.scale"].dtype == torch.float32
+        assert "a.weight_scale_inv" not in si and si["b.weight"].dtype == torch.float8_e4m3fn
+        assert int(si["a.weight"].abs().max()) == 127
+        assert cc.main([i8, back3, "--to", "bf16"]) == 0
+        s3 = dict(sio.read_checkpoint(back3))
+        err = (s3["a.weight"].float() - state["a.weight"].float()).norm() / state["a.weight"].float().norm()
+        assert s3["a.weight"].dtype == torch.bfloat16 and "a.scale" not in s3 and err < 0.06
 
 
 def test_inspect_safetensors_lists_filters_and_audits(capsys):
