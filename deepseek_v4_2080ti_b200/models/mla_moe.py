@@ -222,6 +222,20 @@ def cpu_moe_fp4(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, w13, s13,
     return out
 
 
+def cpu_gguf_linear(x: torch.Tensor, raw: torch.Tensor, ggml_type: int, threads: int = 0) -> torch.Tensor:
+    """y [T, N] = x [T, K] @ W^T on the host with W as raw GGUF blocks uint8 [N, row_bytes] (Q8_0 = 8, Q2_K = 10)."""
+    x = x.contiguous().float()
+    raw = raw.contiguous()
+    t, k = x.shape
+    n = raw.shape[0]
+    y = torch.empty(t, n, dtype=torch.float32)
+    p = lambda a: ctypes.c_void_p(a.data_ptr())
+    rc = cpu_lib().b200_cpu_gguf_linear(int(ggml_type), p(x), t, k, p(raw), n, p(y), threads)
+    if rc != 0:
+        raise RuntimeError("cpu_gguf_linear: unsupported type" if rc == -2 else "cpu_gguf_linear rejected its arguments")
+    return y
+
+
 def quantize_rows_int8(w: torch.Tensor, threads: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
     """Per-row symmetric INT8: w [..., N, K] fp32 -> (int8 [..., N, K], fp32 scale [..., N]), scale = max|row| / 127."""
     w = w.contiguous().float()

@@ -74,3 +74,24 @@ def test_int8_moe_rejects_bad_routes_and_handles_zero_rows():
         mla_moe.cpu_moe_int8(x, torch.tensor([[0], [5]], dtype=torch.int32), wts, w13q, s13, w2q, s2)
     zq, zs = mla_moe.quantize_rows_int8(torch.zeros(3, 8))
     assert not zq.any() and not zs.any()
+
+
+@pytest.mark.parametrize("tname,k", [("Q8_0", 96), ("Q8_0", 512), ("Q2_K", 256), ("Q2_K", 768)])
+def test_host_gguf_linear_matches_the_dequantised_product(tname, k):
+    from deepseek_v4_2080ti_b200.formats.gguf import quant
+    from deepseek_v4_2080ti_b200.formats.gguf.constants import GGMLType
+    t = GGMLType[tname]
+    g = torch.Generator().manual_seed(k)
+    w = torch.randn(37, k, generator=g) * 0.3
+    w[3] = 0.0                                                  # an all-zero row
+    w[5] *= 1e-6                                                # scales that are subnormal in fp16
+    raw = quant.quantize(w, t)
+    x = torch.randn(4, k, generator=g)
+    want = x @ quant.dequantize(raw, t, k).t()
+    got = mla_moe.cpu_gguf_linear(x, raw, int(t), threads=3)
+    assert got.shape == (4, 37) and torch.allclose(got, want, atol=1e-4 * want.abs().max().item() + 1e-7, rtol=1e-4)
+    assert torch.equal(got, mla_moe.cpu_gguf_linear(x, raw, int(t), threads=1))
+    with pytest.raises(RuntimeError):
+        mla_moe.cpu_gguf_linear(x, raw, 12)
+    with pytest.raises(RuntimeError):
+        mla_moe.cpu_gguf_linear(x[:, :k - 8], raw, int(t))
