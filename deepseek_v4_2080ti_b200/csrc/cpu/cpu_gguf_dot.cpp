@@ -1,5 +1,5 @@
 // Host matrix-vector products straight from raw GGUF blocks (no expansion in memory): y[t, n] = W[n, :] . x[t, :]
-// for W stored as Q8_0 (32 values: fp16 scale + 32 int8) or Q2_K (256 values: 16 packed 4-bit scale / 4-bit minimum
+// for W stored as Q8_0 (32 values: fp16 scale + 32 int8), IQ2_XXS (codebook magnitudes with sign patterns) or Q2_K (256 values: 16 packed 4-bit scale / 4-bit minimum
 // pairs, 64 bytes of 2-bit codes in two 128-value halves of four 32-value planes, fp16 d and dmin; value =
 // d * scale * code - dmin * minimum).  Per Q2_K sub-block of 16 the kernel accumulates sum(code * x) and sum(x) and
 // applies the two factors once.  Rows are split over host threads; each output is computed by one thread in a fixed
@@ -80,6 +80,37 @@ float dot_q2_k(const uint8_t* row, const float* x, int k) {
   return total;
 }
 
+// IQ2_XXS: 256 values = fp16 d + eight 8-byte groups of 32 values: four codebook indices (8 magnitudes each), then a word
+// holding four 7-bit sign-pattern indices and a 4-bit scale; value = d * (0.5 + scale) / 4 * magnitude * sign.
+// The codebook is not compiled in: the loader hands it over once.
+float g_iq2xxs_grid[256 * 8];
+uint8_t g_ksigns[128];
+bool g_iq2xxs_ready = false;
+
+float dot_iq2_xxs(const uint8_t* row, const float* x, int k) {
+  float total = 0.f;
+  for (int b = 0; b < k / 256; ++b) {
+    const uint8_t* blk = row + (size_t)b * 66;
+    const float d = half_to_float(load_u16(blk));
+    const float* xb = x + b * 256;
+    for (int g = 0; g < 8; ++g) {
+      const uint8_t* q = blk + 2 + g * 8;
+      uint32_t w1;
+      memcpy(&w1, q + 4, 4);
+      const float db = d * (0.5f + (float)(w1 >> 28)) * 0.25f;
+      float acc = 0.f;
+      for (int j = 0; j < 4; ++j) {
+        const float* mag = g_iq2xxs_grid + (size_t)q[j] * 8;
+        const uint8_t signs = g_ksigns[(w1 >> (7 * j)) & 0x7F];
+        const float* xv = xb + g * 32 + j * 8;
+        for (int i = 0; i < 8; ++i) acc += ((signs >> i) & 1 ? -mag[i] : mag[i]) * xv[i];
+      }
+      total += db * acc;
+    }
+  }
+  return total;
+}
+
 template <class F>
 void parallel_rows(long long n, int requested, F fn) {
   int nt = requested > 0 ? requested : (int)std::thread::hardware_concurrency();
@@ -103,7 +134,14 @@ void parallel_rows(long long n, int requested, F fn) {
 
 extern "C" {
 
-// ggml_type 8 = Q8_0 (K % 32 == 0), 10 = Q2_K (K % 256 == 0).  x [T, K] fp32, raw [N, row_bytes] as in the file,
+// The IQ2_XXS codebook (256 x 8 magnitudes) and the 128 sign patterns; call once before using type 16.
+void b200_cpu_gguf_set_iq2xxs_tables(const float* grid, const uint8_t* ksigns) {
+  memcpy(g_iq2xxs_grid, grid, sizeof(g_iq2xxs_grid));
+  memcpy(g_ksigns, ksigns, sizeof(g_ksigns));
+  g_iq2xxs_ready = true;
+}
+
+// ggml_type 8 = Q8_0 (K % 32 == 0), 10 = Q2_K (K % 256 == 0), 16 = IQ2_XXS (K % 256 == 0, tables set: else -3).  x [T, K] fp32, raw [N, row_bytes] as in the file,
 // y [T, N] fp32 (overwritten).  Returns 0, -1 on a bad shape, -2 on an unsupported type.
 int b200_cpu_gguf_linear(int ggml_type, const float* x, int T, int K, const uint8_t* raw, int N, float* y, int num_threads) {
   if (T <= 0 || K <= 0 || N <= 0) return -1;
@@ -114,6 +152,10 @@ int b200_cpu_gguf_linear(int ggml_type, const float* x, int T, int K, const uint
   } else if (ggml_type == 10) {
     if (K % 256) return -1;
     row_bytes = (size_t)K / 256 * 84;
+  } else if (ggml_type == 16) {
+    if (K % 256) return -1;
+    if (!g_iq2xxs_ready) return -3;
+    row_bytes = (size_t)K / 256 * 66;
   } else {
     return -2;
   }
@@ -122,7 +164,7 @@ int b200_cpu_gguf_linear(int ggml_type, const float* x, int T, int K, const uint
       const size_t t = (size_t)(u / N), n = (size_t)(u % N);
       const uint8_t* row = raw + n * row_bytes;
       const float* xr = x + t * (size_t)K;
-      y[u] = ggml_type == 8 ? dot_q8_0(row, xr, K) : dot_q2_k(row, xr, K);
+      y[u] = ggml_type == 8 ? dot_q8_0(row, xr, K) : ggml_type == 10 ? dot_q2_k(row, xr, K) : dot_iq2_xxs(row, xr, K);
     }
   });
   return 0;

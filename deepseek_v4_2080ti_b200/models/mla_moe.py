@@ -222,14 +222,24 @@ def cpu_moe_fp4(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, w13, s13,
     return out
 
 
+_iq2xxs_sent = False
+
+
 def cpu_gguf_linear(x: torch.Tensor, raw: torch.Tensor, ggml_type: int, threads: int = 0) -> torch.Tensor:
-    """y [T, N] = x [T, K] @ W^T on the host with W as raw GGUF blocks uint8 [N, row_bytes] (Q8_0 = 8, Q2_K = 10)."""
+    """y [T, N] = x [T, K] @ W^T on the host with W as raw GGUF blocks uint8 [N, row_bytes] (Q8_0 = 8, Q2_K = 10, IQ2_XXS = 16)."""
     x = x.contiguous().float()
     raw = raw.contiguous()
     t, k = x.shape
     n = raw.shape[0]
     y = torch.empty(t, n, dtype=torch.float32)
     p = lambda a: ctypes.c_void_p(a.data_ptr())
+    global _iq2xxs_sent
+    if int(ggml_type) == 16 and not _iq2xxs_sent:                 # hand the codebook to the library once
+        from ..formats.gguf import quant as _q
+        tb = _q.tables("cpu")
+        grid, ks = tb["iq2xxs"].contiguous().float(), tb["ksigns"].contiguous()
+        cpu_lib().b200_cpu_gguf_set_iq2xxs_tables(p(grid), p(ks))
+        _iq2xxs_sent = True
     rc = cpu_lib().b200_cpu_gguf_linear(int(ggml_type), p(x), t, k, p(raw), n, p(y), threads)
     if rc != 0:
         raise RuntimeError("cpu_gguf_linear: unsupported type" if rc == -2 else "cpu_gguf_linear rejected its arguments")

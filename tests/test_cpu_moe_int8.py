@@ -76,7 +76,7 @@ def test_int8_moe_rejects_bad_routes_and_handles_zero_rows():
     assert not zq.any() and not zs.any()
 
 
-@pytest.mark.parametrize("tname,k", [("Q8_0", 96), ("Q8_0", 512), ("Q2_K", 256), ("Q2_K", 768)])
+@pytest.mark.parametrize("tname,k", [("Q8_0", 96), ("Q8_0", 512), ("Q2_K", 256), ("Q2_K", 768), ("IQ2_XXS", 512)])
 def test_host_gguf_linear_matches_the_dequantised_product(tname, k):
     from deepseek_v4_2080ti_b200.formats.gguf import quant
     from deepseek_v4_2080ti_b200.formats.gguf.constants import GGMLType
