@@ -246,6 +246,26 @@ def cpu_gguf_linear(x: torch.Tensor, raw: torch.Tensor, ggml_type: int, threads:
     return y
 
 
+def cpu_moe_gguf(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, gate_raw: torch.Tensor, up_raw: torch.Tensor,
+                 down_raw: torch.Tensor, gate_type: int, down_type: int, swiglu_limit: float = 0.0, threads: int = 0) -> torch.Tensor:
+    """Routed experts on the host straight from stacked raw GGUF tensors: gate_raw / up_raw uint8 [E, I, row_bytes(H)],
+    down_raw [E, H, row_bytes(I)].  Tokens are grouped by expert, so each active expert's blocks are walked once.
+    x [T, H] fp32, idx [T, K] (negative = unused), wts [T, K]; returns [T, H] fp32."""
+    x = x.contiguous().float()
+    out = torch.zeros_like(x)
+    idx = idx.long()
+    for e in idx[idx >= 0].unique().tolist():
+        rows, slot = (idx == e).nonzero(as_tuple=True)
+        xe = x[rows]
+        g = cpu_gguf_linear(xe, gate_raw[e], gate_type, threads)
+        u = cpu_gguf_linear(xe, up_raw[e], gate_type, threads)
+        if swiglu_limit > 0:
+            g, u = g.clamp(max=swiglu_limit), u.clamp(-swiglu_limit, swiglu_limit)
+        h = torch.nn.functional.silu(g) * u * wts[rows, slot].float()[:, None]
+        out.index_add_(0, rows, cpu_gguf_linear(h, down_raw[e], down_type, threads))
+    return out
+
+
 def quantize_rows_int8(w: torch.Tensor, threads: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
     """Per-row symmetric INT8: w [..., N, K] fp32 -> (int8 [..., N, K], fp32 scale [..., N]), scale = max|row| / 127."""
     w = w.contiguous().float()

@@ -95,3 +95,29 @@ def test_host_gguf_linear_matches_the_dequantised_product(tname, k):
         mla_moe.cpu_gguf_linear(x, raw, 12)
     with pytest.raises(RuntimeError):
         mla_moe.cpu_gguf_linear(x[:, :k - 8], raw, int(t))
+
+
+def test_host_gguf_routed_experts_match_the_dequantised_experts():
+    from deepseek_v4_2080ti_b200.formats.gguf import quant
+    from deepseek_v4_2080ti_b200.formats.gguf.constants import GGMLType
+    g = torch.Generator().manual_seed(3)
+    e, h, inter, t, k = 5, 256, 256, 6, 2
+    gate, up, down = (torch.randn(e, inter, h, generator=g) * 0.1, torch.randn(e, inter, h, generator=g) * 0.1,
+                      torch.randn(e, h, inter, generator=g) * 0.1)
+    q = lambda w, ty: torch.stack([quant.quantize(w[i], ty) for i in range(e)])
+    gr, ur, dr = q(gate, GGMLType.IQ2_XXS), q(up, GGMLType.IQ2_XXS), q(down, GGMLType.Q2_K)
+    dq = lambda raw, ty, cols: torch.stack([quant.dequantize(raw[i], ty, cols) for i in range(e)])
+    gd, ud, dd = dq(gr, GGMLType.IQ2_XXS, h), dq(ur, GGMLType.IQ2_XXS, h), dq(dr, GGMLType.Q2_K, inter)
+    x = torch.randn(t, h, generator=g)
+    idx = torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(t)]).to(torch.int32)
+    idx[2, 1] = -1
+    wts = torch.rand(t, k, generator=g)
+    want = torch.zeros(t, h)
+    for ti in range(t):
+        for kk in range(k):
+            ee = int(idx[ti, kk])
+            if ee >= 0:
+                a, b = (gd[ee] @ x[ti]).clamp(max=2.0), (ud[ee] @ x[ti]).clamp(-2.0, 2.0)
+                want[ti] += dd[ee] @ (wts[ti, kk] * F.silu(a) * b)
+    got = mla_moe.cpu_moe_gguf(x, idx, wts, gr, ur, dr, int(GGMLType.IQ2_XXS), int(GGMLType.Q2_K), swiglu_limit=2.0, threads=2)
+    assert torch.allclose(got, want, atol=1e-4 * want.abs().max().item() + 1e-6, rtol=1e-3)
