@@ -121,3 +121,12 @@ def test_host_gguf_routed_experts_match_the_dequantised_experts():
                 want[ti] += dd[ee] @ (wts[ti, kk] * F.silu(a) * b)
     got = mla_moe.cpu_moe_gguf(x, idx, wts, gr, ur, dr, int(GGMLType.IQ2_XXS), int(GGMLType.Q2_K), swiglu_limit=2.0, threads=2)
     assert torch.allclose(got, want, atol=1e-4 * want.abs().max().item() + 1e-6, rtol=1e-3)
+
+
+def test_cpu_dot_bench_reports_every_kernel(capsys):
+    from deepseek_v4_2080ti_b200.utils import cpu_dot_bench
+    assert cpu_dot_bench.main(["--rows", "64", "--cols", "256", "--repeat", "1", "--threads", "2"]) == 0
+    import json
+    rows = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+    assert [r["kernel"] for r in rows] == ["gguf_q8_0_gemv", "gguf_q2_k_gemv", "gguf_iq2_xxs_gemv", "int8_w8a8_moe_decode"]
+    assert all(r["ms"] > 0 and r["weight_gbs"] > 0 for r in rows)
