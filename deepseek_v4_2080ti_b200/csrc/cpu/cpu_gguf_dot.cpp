@@ -84,7 +84,7 @@ float dot_q2_k(const uint8_t* row, const float* x, int k) {
 // holding four 7-bit sign-pattern indices and a 4-bit scale; value = d * (0.5 + scale) / 4 * magnitude * sign.
 // The codebook is not compiled in: the loader hands it over once.
 float g_iq2xxs_grid[256 * 8];
-uint8_t g_ksigns[128];
+float g_sign_rows[128 * 8];          // +1 / -1 per value for every sign pattern, so the inner loop is a plain 8-wide FMA
 bool g_iq2xxs_ready = false;
 
 float dot_iq2_xxs(const uint8_t* row, const float* x, int k) {
@@ -101,9 +101,9 @@ float dot_iq2_xxs(const uint8_t* row, const float* x, int k) {
       float acc = 0.f;
       for (int j = 0; j < 4; ++j) {
         const float* mag = g_iq2xxs_grid + (size_t)q[j] * 8;
-        const uint8_t signs = g_ksigns[(w1 >> (7 * j)) & 0x7F];
+        const float* sg = g_sign_rows + (size_t)((w1 >> (7 * j)) & 0x7F) * 8;
         const float* xv = xb + g * 32 + j * 8;
-        for (int i = 0; i < 8; ++i) acc += ((signs >> i) & 1 ? -mag[i] : mag[i]) * xv[i];
+        for (int i = 0; i < 8; ++i) acc += mag[i] * sg[i] * xv[i];
       }
       total += db * acc;
     }
@@ -137,7 +137,8 @@ extern "C" {
 // The IQ2_XXS codebook (256 x 8 magnitudes) and the 128 sign patterns; call once before using type 16.
 void b200_cpu_gguf_set_iq2xxs_tables(const float* grid, const uint8_t* ksigns) {
   memcpy(g_iq2xxs_grid, grid, sizeof(g_iq2xxs_grid));
-  memcpy(g_ksigns, ksigns, sizeof(g_ksigns));
+  for (int p = 0; p < 128; ++p)
+    for (int i = 0; i < 8; ++i) g_sign_rows[p * 8 + i] = (ksigns[p] >> i) & 1 ? -1.f : 1.f;
   g_iq2xxs_ready = true;
 }
 
