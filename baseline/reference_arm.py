@@ -17,8 +17,10 @@ import os
 import re
 import shutil
 import subprocess
+import queue
 import sys
 import tempfile
+import threading
 import time
 
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -58,6 +60,94 @@ def write_checkpoint(cfg, directory: str, device) -> float:
 def _field(line: str, key: str) -> float:
     m = re.search(rf"\b{key}=([0-9.eE+-]+)", line)
     return float(m.group(1)) if m else float("nan")
+
+
+def drive_engine(cmd, env, line: str, *, leader: bool, warmup: int, steps: int, budget: float, t_arm0: float) -> dict:
+    """Run one engine process in persistent-stdin mode under a wall-clock budget (seconds, counted from ``t_arm0``).
+
+    The leader feeds one request line at a time and waits for its ``qwen_persistent_result=1`` line, so it can stop
+    between requests when the budget runs low and still report what completed.  The first request doubles as
+    warm-up (the engine has no JIT or graph capture); the other warm-up requests asked for are sent only when all of
+    ``warmup + steps`` fit the budget, judged from the engine's own wall time of the first request.  Follower ranks
+    take their commands from the leader over the reference's own channel: they get their output drained and a bound
+    on their lifetime."""
+    proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                            env=env)
+    t_start = time.time()
+    lines: "queue.Queue[str | None]" = queue.Queue()
+    tail: list[str] = []
+
+    def _reader():
+        for out in proc.stdout:
+            lines.put(out)
+        lines.put(None)
+
+    threading.Thread(target=_reader, daemon=True).start()
+
+    def left() -> float:
+        return budget - (time.time() - t_arm0)
+
+    def next_result(limit: float):
+        """The next result line, None if the engine exited or ``limit`` seconds passed."""
+        t_end = time.time() + limit
+        while True:
+            try:
+                out = lines.get(timeout=max(0.05, t_end - time.time()))
+            except queue.Empty:
+                return None
+            if out is None:
+                return None
+            tail.append(out.rstrip()[:300])
+            del tail[:-8]
+            if out.startswith("qwen_persistent_result=1"):
+                return out
+
+    def finish(grace: float) -> int:
+        try:
+            proc.stdin.close()
+        except (BrokenPipeError, OSError):
+            pass
+        try:
+            return proc.wait(timeout=grace)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+            return proc.wait()
+
+    if not leader:
+        while proc.poll() is None and left() + 90 > 0:
+            next_result(5.0)
+        return {"rc": finish(10)}
+
+    results, req_wall = [], []
+    want_warm = max(1, warmup)
+    warm_done = None
+    why_short = ""
+    while True:
+        if warm_done is None and results:
+            per = _field(results[0], "wall") * 1.15     # the first host wall also holds the weight load
+            warm_done = want_warm if left() // per >= (want_warm - 1) + steps else 1
+        if len(results) >= (warm_done or 1) + steps:
+            break
+        if results and left() < max([_field(results[0], "wall")] + req_wall[1:]) * 1.15:
+            why_short = f"time budget of {int(budget)} s"
+            break
+        t_req = time.time()
+        try:
+            proc.stdin.write(line)
+            proc.stdin.flush()
+        except (BrokenPipeError, OSError):
+            why_short = "engine closed its input"
+            break
+        out = next_result(max(30.0, left()))
+        if out is None:
+            why_short = ("engine exited" if proc.poll() is not None
+                         else f"time budget of {int(budget)} s (request in flight)")
+            break
+        results.append(out)
+        req_wall.append(time.time() - t_req)
+    t_done = time.time()
+    return {"results": results, "req_wall": req_wall, "warm_done": warm_done or 1, "why_short": why_short,
+            "rc": finish(30), "tail": tail, "t_start": t_start, "t_done": t_done, "t_arm0": t_arm0}
 
 
 def run(args) -> dict:
@@ -108,53 +198,19 @@ def run(args) -> dict:
     gen = torch.Generator().manual_seed(1)
     prompt = torch.randint(0, cfg.vocab_size, (args.prompt,), generator=gen, dtype=torch.int32).tolist()
     line = f"{args.decode} " + " ".join(map(str, prompt)) + "\n"
-    n_req = args.warmup + args.steps
-    proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
-                            env=env)
-    results, tail = [], []
-    t_start = time.time()
-    deadline = float(os.environ.get("POCKETLLM_REFERENCE_TIMEOUT_S", "900"))
-    timed_out = []
-
-    def _watchdog():
-        # a wedged rank (a peer that died, a collective that never completes) must not block the caller for ever
-        try:
-            proc.wait(timeout=deadline)
-        except subprocess.TimeoutExpired:
-            timed_out.append(True)
-            proc.kill()
-
-    import threading
-    wd = threading.Thread(target=_watchdog, daemon=True)
-    wd.start()
-    try:
-        if rank == 0:
-            try:
-                for _ in range(n_req):
-                    proc.stdin.write(line)
-                proc.stdin.close()
-            except (BrokenPipeError, OSError):
-                pass                                   # the engine already exited; its output says why
-        for out in proc.stdout:
-            tail.append(out.rstrip()[:400])
-            tail = tail[-12:]
-            if out.startswith("qwen_persistent_result=1"):
-                results.append(out)
-        rc = proc.wait(timeout=60)
-    except Exception as e:  # noqa: BLE001
-        proc.kill()
-        return _unavailable(f"reference engine run failed: {type(e).__name__}: {e}") if rank == 0 else {}
-    if timed_out:
-        shutil.rmtree(work, ignore_errors=True) if rank == 0 else None
-        return _unavailable(f"reference engine did not finish within {int(deadline)} s at tp{world}: "
-                            + " | ".join(tail[-3:])) if rank == 0 else {}
-    wall = time.time() - t_start
+    budget = float(os.environ.get("POCKETLLM_REFERENCE_BUDGET_S", "480"))
+    run_ = drive_engine(cmd, env, line, leader=(rank == 0), warmup=args.warmup, steps=args.steps,
+                        budget=budget, t_arm0=time.time() - ckpt_s)
     if rank != 0:
         return {}
     shutil.rmtree(work, ignore_errors=True)
-    if rc != 0 or len(results) < n_req:
-        return _unavailable(f"reference engine exited rc={rc} after {len(results)}/{n_req} requests: " + " | ".join(tail[-4:]))
-    timed = results[args.warmup:]
+    results, req_wall, warm_done, why_short = run_["results"], run_["req_wall"], run_["warm_done"], run_["why_short"]
+    t_start, t_done, t_arm0 = run_["t_start"], run_["t_done"], run_["t_arm0"]
+    timed = results[warm_done:]
+    if not timed:
+        return _unavailable(f"reference engine completed {len(results)} request(s) at tp{world} ({why_short}; "
+                            f"rc={run_['rc']}): " + " | ".join(t[:200] for t in run_["tail"][-3:]))
+    eng_wall = [_field(r, "wall") for r in results]
     pre_s = [_field(r, "prefill_seconds") for r in timed]
     dec_s = [_field(r, "decode_seconds") for r in timed]
     pre = sum(pre_s) / len(pre_s)
@@ -165,7 +221,8 @@ def run(args) -> dict:
     toks = m.group(1).split(",") if m else []
     return {
         "impl": "reference", "metric": "prefill_tok_s", "value": round(prefill_tps, 1), "unit": "tok/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round((pre + dec) * 1e3, 3),
+        "n_gpus": world, "steps": len(timed), "warmup": warm_done, "steps_asked": args.steps,
+        "warmup_asked": args.warmup, "truncated": why_short or None, "ms_per_step": round((pre + dec) * 1e3, 3),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": round(prefill_tps / PUBLISHED_PREFILL_TPS, 2),
         "dtype": "fp16", "data": "synthetic (random-init FP8 block-128 weights, random token ids)",
         "prefill_ms": round(pre * 1e3, 3), "decode_tok_s": round(decode_tps, 2),
@@ -178,5 +235,10 @@ def run(args) -> dict:
         "e2e": {"value": round(prefill_tps, 1), "unit": "tok/s",
                 "what": "the engine's own request path: token ids in over stdin, H2D inside prefill, next token read back",
                 "h2d_bytes_per_step": args.prompt * 4, "d2h_bytes_per_step": 4 * args.decode},
-        "checkpoint_write_s": round(ckpt_s, 1), "wall_s": round(wall, 1), "first_tokens": [int(t) for t in toks[:16]],
+        "wall_breakdown_s": {"checkpoint_write": round(ckpt_s, 1), "engine_start_to_first_request_done": round(
+                                 (t_done - t_start) - sum(req_wall[1:]), 1),
+                             "request_host_wall_mean": round(sum(req_wall) / len(req_wall), 2),
+                             "request_engine_wall_mean": round(sum(eng_wall) / len(eng_wall), 2),
+                             "requests_done": len(results), "total": round(time.time() - t_arm0, 1)},
+        "first_tokens": [int(t) for t in toks[:16]],
     }

@@ -18,6 +18,7 @@
 // (gqa_prefill_* kernels :326-1482, online softmax, causal mask) and the paged
 // KV layout of cpp_engine/include/block_table.hpp:22-71.
 #include <cuda_bf16.h>
+#include "per_device.h"
 #include "../ptx/sm100.cuh"
 #include "tma_host.h"
 #include "ops.h"
@@ -390,7 +391,8 @@ extern "C" int b200_gqa_prefill(const void* q, const void* k_cache, const void* 
   using namespace b200::attn;
   if (block_size != 16 && block_size != 32 && block_size != 64 && block_size != 128) return -ERR_BAD_ARG;
   if (n_q_heads % n_kv_heads) return -ERR_BAD_ARG;
-  static bool configured = false;
+  static b200::PerDeviceOnce once_;
+  bool& configured = once_.slot();
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gqa_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;

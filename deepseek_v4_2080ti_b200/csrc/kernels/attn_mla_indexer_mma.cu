@@ -9,6 +9,7 @@
 // sequences (every query then has its own block table) and for index widths other than 64 / 128.
 // Reference behaviour: the DeepSeek sparse-attention indexer scoring (src/models/deepseek_v4/runtime.py:1112-1288).
 #include <cuda_bf16.h>
+#include "per_device.h"
 #include <stdint.h>
 #include "ops.h"
 
@@ -147,7 +148,8 @@ template <int DI>
 int launch(const __nv_bfloat16* q, const float* hw, const __nv_bfloat16* kc, const int* bt, int max_blocks, int bs,
            const int* positions, float* scores, int ld, int T, int HI, float scale, cudaStream_t stream) {
   constexpr int SMEM = (KT + 2 * QT) * (DI + 8) * 2;
-  static bool configured = false;
+  static b200::PerDeviceOnce once_;
+  bool& configured = once_.slot();
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(mla_indexer_mma_kernel<DI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;

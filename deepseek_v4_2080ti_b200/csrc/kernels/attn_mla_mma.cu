@@ -12,6 +12,7 @@
 // Reference behaviour: GLM MLA with absorbed k_b / v_b (src/models/glm_dsa/architecture.py:263-406) and the
 // DeepSeek sparse attention dispatcher (src/kernels/ops.py:982-1100), which run per-head SDPA / Triton kernels.
 #include <cuda_bf16.h>
+#include "per_device.h"
 #include <stdint.h>
 #include "ops.h"
 
@@ -267,7 +268,8 @@ int launch_mt(const __nv_bfloat16* ql, const __nv_bfloat16* qp, const __nv_bfloa
               int bs, const int* positions, const int* seq_of_token, const int* sel, int nsel, __nv_bfloat16* ol, int T, int H,
               float scale, float* part, int splits, cudaStream_t stream) {
   using L = Layout<C, R, MT>;
-  static bool configured = false;
+  static b200::PerDeviceOnce once_;
+  bool& configured = once_.slot();
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(mla_attention_mma_kernel<C, R, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return (int)e;

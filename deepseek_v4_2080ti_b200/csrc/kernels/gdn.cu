@@ -19,6 +19,7 @@
 // (cpp_engine/backends/cuda/kernels/qwen_half_ops.cu:2282-2600, qwen_gdn_flashqla.cu:36);
 // the math oracle is the chunked PyTorch form src/models/qwen4_exp/attention.py:184-270.
 #include <cuda_bf16.h>
+#include "per_device.h"
 #include <cuda_fp16.h>
 #include <stdint.h>
 #include "ops.h"
@@ -789,7 +790,8 @@ int b200_gdn_chunked(const void* mixed, int ld, int q_off, int k_off, int v_off,
   const float q_scale = 0.08838834764831845f;  // 1/sqrt(128)
   const int prep_smem = (2 * C * KP + C * AP + 2 * C) * 4 + C * DV * 2;
   const int scan_smem = SCAN_SMEM_BYTES;
-  static bool configured = false;
+  static b200::PerDeviceOnce once_;
+  bool& configured = once_.slot();
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gdn_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, prep_smem);
     if (e == cudaSuccess)

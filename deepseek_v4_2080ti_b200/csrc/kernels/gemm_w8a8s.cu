@@ -22,6 +22,7 @@
 // Reference behaviour covered: the FP8 block-128 matvec / small-batch kernels of the Qwen path
 // (cpp_engine/backends/cuda/kernels/qwen_half_ops.cu:130-535), which dequantise in CUDA cores.
 #include <cuda_bf16.h>
+#include "per_device.h"
 #include <cuda_fp8.h>
 #include "../ptx/sm100.cuh"
 #include "tma_host.h"
@@ -370,7 +371,8 @@ act_split_e4m3_kernel(const __nv_bfloat16* __restrict__ x, int K, uint8_t* __res
 template <int BN, int TERMS>
 static int launch(const CUtensorMap& tmX, const Params& p, cudaStream_t stream) {
   using L = Smem<BN>;
-  static bool configured = false;
+  static b200::PerDeviceOnce once_;
+  bool& configured = once_.slot();
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_w8a8s_kernel<BN, TERMS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          L::TOTAL);

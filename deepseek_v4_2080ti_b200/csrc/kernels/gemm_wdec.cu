@@ -3,12 +3,21 @@
 
 using namespace b200;
 
-// Set by b200_gemm_wdec_allreduce around its call into the common launcher (host threads that launch
-// GEMMs concurrently must serialise fused all-reduce calls; one engine thread per process does).
-static const B200Comm* g_ar_comm = nullptr;
-static unsigned long long g_ar_budget = 0;
-static int g_ar_mode = 1;
-static size_t g_ar_result_off = 0;
+// What a fused compute+collective entry point adds to the plain launch; passed down explicitly so that host
+// threads launching GEMMs side by side never see each other's collective.
+struct FusedOpts {
+  const B200Comm* comm = nullptr;
+  int ar_mode = 0;                 // 1 one-shot all-reduce, 2 two-shot, 3 reduce-scatter push
+  size_t result_off = 0;
+  unsigned long long budget_ns = 0;
+  int sp_rows = 0;                 // rows per owner shard (reduce-scatter push, all-gather wait)
+  int ag_wait = 0, ag_flag_rows = 0;
+  int bn = 0;                      // token tile forced by the collective's layout (0: by T)
+  int n_rot = 0;
+};
+static int gemm_wdec_launch(int wfmt, const void* W, const float* scales, const void* X, void* out_bf16,
+                            float* out_f32, const void* residual, int T, int N, int K, int splits,
+                            int* tile_counters, int* status, cudaStream_t stream, const FusedOpts* fo);
 
 extern "C" int b200_gemm_pick_bn(int T) {
   if (T <= 16) return 16;
@@ -42,8 +51,15 @@ extern "C" int b200_gemm_wdec(int wfmt, const void* W, const float* scales, cons
 extern "C" int b200_gemm_wdec_ex(int wfmt, const void* W, const float* scales, const void* X,
                                  void* out_bf16, float* out_f32, const void* residual, int T, int N,
                                  int K, int splits, int* tile_counters, int* status, cudaStream_t stream) {
+  return gemm_wdec_launch(wfmt, W, scales, X, out_bf16, out_f32, residual, T, N, K, splits, tile_counters, status,
+                          stream, nullptr);
+}
+
+static int gemm_wdec_launch(int wfmt, const void* W, const float* scales, const void* X, void* out_bf16,
+                            float* out_f32, const void* residual, int T, int N, int K, int splits,
+                            int* tile_counters, int* status, cudaStream_t stream, const FusedOpts* fo) {
   if (T <= 0 || N <= 0 || K <= 0 || (K % 16) != 0 || splits < 1) return -ERR_BAD_ARG;
-  const int BN = b200_gemm_pick_bn(T);
+  const int BN = (fo && fo->bn) ? fo->bn : b200_gemm_pick_bn(T);
   GemmParams p;
   p.T = T; p.N = N; p.K = K;
   p.m_tiles = (N + BM - 1) / BM;
@@ -71,16 +87,25 @@ extern "C" int b200_gemm_wdec_ex(int wfmt, const void* W, const float* scales, c
   if (splits > 1 && out_bf16 && !tile_counters) return -ERR_BAD_ARG;
   p.ar_mode = 0;
   p.ar_budget_ns = 0;
+  p.result_off = 0;
+  p.n_rot = 0;
+  p.sp_rows = 0;
+  p.ag_wait = 0;
+  p.ag_flag_rows = 0;
+  p.lut = nullptr;
   memset(&p.comm, 0, sizeof(p.comm));
-  if (g_ar_comm) {
-    if (splits != 1 || !out_bf16) return -ERR_BAD_ARG;
-    p.ar_mode = 1;
-    p.ar_budget_ns = g_ar_budget;
-    p.comm = *g_ar_comm;
-    p.ar_mode = g_ar_mode;
-    p.result_off = g_ar_result_off;
+  if (fo && fo->comm) {
+    if (splits != 1 || (!out_bf16 && fo->ar_mode != 3)) return -ERR_BAD_ARG;
+    p.ar_mode = fo->ar_mode;
+    p.ar_budget_ns = fo->budget_ns;
+    p.comm = *fo->comm;
+    p.result_off = fo->result_off;
+    p.n_rot = fo->n_rot;
+    p.sp_rows = fo->sp_rows;
+    p.ag_wait = fo->ag_wait;
+    p.ag_flag_rows = fo->ag_flag_rows;
   }
-  if ((splits > 1 || !out_bf16) && !out_f32) return -ERR_BAD_ARG;
+  if ((splits > 1 || !out_bf16) && !out_f32 && p.ar_mode != 3) return -ERR_BAD_ARG;
   if (wfmt == WF_FP8_B128) {
     // the decode warps keep at most 256 block scales (K range of 32768) per tile in registers
     const int per = (p.kb_total + splits - 1) / splits;
@@ -189,11 +214,11 @@ extern "C" int b200_gemm_wdec_allreduce(int wfmt, const void* W, const float* sc
   if ((unsigned long long)T * N > comm->slot_elems || (N % 8) != 0) return -ERR_BAD_ARG;
   const int BN = b200_gemm_pick_bn(T);
   if ((long long)((N + BM - 1) / BM) * ((T + BN - 1) / BN) > B200_FLAGS_PER_SLOT) return -ERR_BAD_ARG;
-  g_ar_comm = comm;
-  g_ar_budget = budget_ns ? budget_ns : B200_WAIT_BUDGET_NS;
-  const int rc = b200_gemm_wdec(wfmt, W, scales, X, out_bf16, nullptr, residual, T, N, K, 1, status, stream);
-  g_ar_comm = nullptr;
-  return rc;
+  FusedOpts fo;
+  fo.comm = comm;
+  fo.ar_mode = 1;
+  fo.budget_ns = budget_ns ? budget_ns : B200_WAIT_BUDGET_NS;
+  return gemm_wdec_launch(wfmt, W, scales, X, out_bf16, nullptr, residual, T, N, K, 1, nullptr, status, stream, &fo);
 }
 
 // Two-shot variant: tile w is reduced by rank w % world and the reduced tile is pushed into every rank's result
@@ -207,16 +232,68 @@ extern "C" int b200_gemm_wdec_allreduce2(int wfmt, const void* W, const float* s
   if ((unsigned long long)T * N > comm->slot_elems || (N % 8) != 0) return -ERR_BAD_ARG;
   const int BN = b200_gemm_pick_bn(T);
   if ((long long)((N + BM - 1) / BM) * ((T + BN - 1) / BN) > B200_FLAGS_PER_SLOT) return -ERR_BAD_ARG;
-  g_ar_comm = comm;
-  g_ar_budget = budget_ns ? budget_ns : B200_WAIT_BUDGET_NS;
-  g_ar_mode = 2;
-  g_ar_result_off = (size_t)result_index * comm->slot_elems;
-  void* out = reinterpret_cast<__nv_bfloat16*>(comm->result[comm->rank]) + g_ar_result_off;
-  const int rc = b200_gemm_wdec(wfmt, W, scales, X, out, nullptr, residual, T, N, K, 1, status, stream);
-  g_ar_comm = nullptr;
-  g_ar_mode = 1;
-  g_ar_result_off = 0;
-  return rc;
+  FusedOpts fo;
+  fo.comm = comm;
+  fo.ar_mode = 2;
+  fo.budget_ns = budget_ns ? budget_ns : B200_WAIT_BUDGET_NS;
+  fo.result_off = (size_t)result_index * comm->slot_elems;
+  void* out = reinterpret_cast<__nv_bfloat16*>(comm->result[comm->rank]) + fo.result_off;
+  return gemm_wdec_launch(wfmt, W, scales, X, out, nullptr, residual, T, N, K, 1, nullptr, status, stream, &fo);
+}
+
+// Token tile of the sequence-parallel GEMMs for a shard of `sp_rows` rows: the largest tile that divides the shard
+// and whose kernel instance carries the epilogue staging (0 = this shape cannot run sequence-parallel).
+extern "C" int b200_gemm_sp_bn(int wfmt, int sp_rows) {
+  if (wfmt == WF_BF16 && sp_rows % 256 == 0) return 256;
+  if ((wfmt == WF_BF16 || wfmt == WF_FP8_B128) && sp_rows % 128 == 0) return 128;
+  return 0;
+}
+
+// Row-parallel GEMM whose epilogue is the push half of a reduce-scatter (ar_mode 3 in gemm_wdec_kernel.cuh): the
+// T = world * sp_rows token rows are owned in contiguous shards; every partial tile goes only to its owner's slot
+// for source = this rank, with one flag per tile.  There is no local output: the owner's
+// b200_sp_reduce_norm_gather (comm/sp_comm.cu) sums the partials.  Returns the token tile used in *bn_out.
+extern "C" int b200_gemm_wdec_rs(int wfmt, const void* W, const float* scales, const void* X, int T, int N, int K,
+                                 const B200Comm* comm, unsigned long long budget_ns, int* bn_out, int* status,
+                                 cudaStream_t stream) {
+  if (!comm || comm->world <= 1 || T % comm->world || (N % 8) != 0) return -ERR_BAD_ARG;
+  const int sp_rows = T / comm->world;
+  const int bn = b200_gemm_sp_bn(wfmt, sp_rows);
+  if (!bn) return -ERR_BAD_ARG;
+  if ((unsigned long long)sp_rows * N > comm->slot_elems) return -ERR_BAD_ARG;
+  if ((long long)((N + BM - 1) / BM) * (sp_rows / bn) > B200_FLAGS_PER_SLOT) return -ERR_BAD_ARG;
+  FusedOpts fo;
+  fo.comm = comm;
+  fo.ar_mode = 3;
+  fo.budget_ns = budget_ns ? budget_ns : B200_WAIT_BUDGET_NS;
+  fo.sp_rows = sp_rows;
+  fo.bn = bn;
+  fo.n_rot = ((comm->rank + 1) % comm->world) * (sp_rows / bn);   // start with the next rank's shard, own shard last
+  if (bn_out) *bn_out = bn;
+  return gemm_wdec_launch(wfmt, W, scales, X, nullptr, nullptr, nullptr, T, N, K, 1, nullptr, status, stream, &fo);
+}
+
+// Column-parallel GEMM on activations that the peers gather into this rank's memory (all-gather + GEMM): X is the
+// local [T, K] buffer that b200_sp_reduce_norm_gather fills on every rank; rows of shard s != rank become valid when
+// rank s raises their flags (one per flag_rows rows), and the producer warp waits for a tile's flags before loading
+// it.  Token tiles are visited own shard first.  Everything else as b200_gemm_wdec with splits == 1.
+extern "C" int b200_gemm_wdec_ag(int wfmt, const void* W, const float* scales, const void* X, void* out_bf16, int T,
+                                 int N, int K, const B200Comm* comm, int flag_rows, unsigned long long budget_ns,
+                                 int* status, cudaStream_t stream) {
+  if (!comm || comm->world <= 1 || T % comm->world || flag_rows <= 0 || !out_bf16) return -ERR_BAD_ARG;
+  const int sp_rows = T / comm->world;
+  const int bn = b200_gemm_pick_bn(T) <= sp_rows ? b200_gemm_pick_bn(T) : 0;
+  if (!bn || sp_rows % bn || sp_rows % flag_rows || sp_rows / flag_rows > B200_FLAGS_PER_SLOT) return -ERR_BAD_ARG;
+  FusedOpts fo;
+  fo.comm = comm;
+  fo.ar_mode = 0;
+  fo.budget_ns = budget_ns ? budget_ns : B200_WAIT_BUDGET_NS;
+  fo.sp_rows = sp_rows;
+  fo.ag_wait = 1;
+  fo.ag_flag_rows = flag_rows;
+  fo.bn = bn;
+  fo.n_rot = comm->rank * (sp_rows / bn);
+  return gemm_wdec_launch(wfmt, W, scales, X, out_bf16, nullptr, nullptr, T, N, K, 1, nullptr, status, stream, &fo);
 }
 
 extern "C" int b200_splitk_reduce(const float* part, int splits, long long n, const void* residual,

@@ -25,6 +25,7 @@
 // instantiate it for their weight formats so the formats compile in parallel.)
 #pragma once
 #include <cuda_bf16.h>
+#include "per_device.h"
 #include <cuda_fp8.h>
 #include <cuda_fp16.h>
 #include <string.h>
@@ -116,9 +117,23 @@ struct GemmParams {
   // ar_mode == 2 (two-shot): tile w is owned by rank w % world; the others push their partial only to the owner,
   //   the owner reduces and pushes the finished tile into every rank's result region (`out` points into this
   //   rank's).  Traffic per rank is 2 (world-1)/world of the output instead of (world-1) times it.
+  // ar_mode == 3 (reduce-scatter push, sequence-parallel residual): token rows are owned in contiguous shards of
+  //   sp_rows rows (rank r owns rows [r*sp_rows, (r+1)*sp_rows), sp_rows % BN == 0).  The epilogue stores each
+  //   partial tile - staged through shared memory so that every thread writes 16 bytes and a token row leaves as
+  //   256 contiguous bytes - only into the owner's slot for source = this rank, then raises that tile's flag on
+  //   the owner.  Nothing waits here: the owner's reduce + norm kernel (comm/sp_comm.cu) consumes the partials.
+  //   Each partial crosses NVLink once: (world-1)/world of the output per rank.  Token tiles are visited starting
+  //   with the next rank's shard (n_rot) so that at any moment the ranks write to different owners.
   int ar_mode;
   size_t result_off;   // element offset of the output inside every rank's result region (two-shot)
   unsigned long long ar_budget_ns;
+  int n_rot;           // token-tile rotation: tile index = (n + n_rot) % n_tiles (0 outside the sequence-parallel modes)
+  int sp_rows;         // rows per owner shard (ar_mode 3, ag_wait)
+  // ag_wait (all-gather + GEMM): the activation rows of shard s != rank are pushed into this rank's X by rank s
+  //   (comm/sp_comm.cu), which then raises one flag per ag_flag_rows rows in the second flag bank.  The producer
+  //   warp waits for the flags of a token tile before its first TMA load of that tile; X itself is local memory.
+  int ag_wait;
+  int ag_flag_rows;
   B200Comm comm;
 };
 
@@ -142,7 +157,8 @@ __device__ __forceinline__ Work get_work(const GemmParams& p, int w) {
     k.group = 0;
     k.m_tile = w % p.m_tiles;
     const int rest = w / p.m_tiles;
-    const int n_tile = rest % p.n_tiles;
+    int n_tile = rest % p.n_tiles + p.n_rot;
+    if (n_tile >= p.n_tiles) n_tile -= p.n_tiles;
     k.split = rest / p.n_tiles;
     k.row0 = n_tile * BN;
     k.rows = min(BN, p.T - k.row0);
@@ -155,13 +171,17 @@ struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;       // 16 KB bf16 weights (decoded, or loaded for WF_BF16)
   static constexpr int X_BYTES = BN * BK * 2;       // activations
   static constexpr int RAW_BYTES = raw_stage_bytes(WFMT) ? raw_stage_bytes(WFMT) : BM * BK;   // raw quantised tile
-  static constexpr int BUDGET = 232448 - 1024 /*align slack*/ - 512 /*barriers*/;
+  // Epilogue staging for the reduce-scatter mode (two 32-token x 128-feature bf16 half-tiles), reserved only where
+  // it costs no decode-regime pipeline depth: the prefill-sized tiles of the bf16 and FP8 formats.
+  static constexpr int EPI_BYTES =
+      ((WFMT == WF_BF16 && BN >= 128) || (WFMT == WF_FP8_B128 && BN == 128)) ? 16384 : 0;
+  static constexpr int BUDGET = 232448 - 1024 /*align slack*/ - 512 /*barriers*/ - EPI_BYTES;
   static constexpr int SA = (WFMT == WF_BF16) ? 0 : 4;
   static constexpr int W_STAGE_BYTES = (WFMT == WF_BF16) ? A_BYTES : RAW_BYTES;
   static constexpr int STAGE_BYTES = W_STAGE_BYTES + X_BYTES;
   static constexpr int SR_RAW = (BUDGET - SA * A_BYTES) / STAGE_BYTES;
   static constexpr int SR = SR_RAW > 16 ? 16 : SR_RAW;
-  static constexpr int TOTAL = SR * STAGE_BYTES + SA * A_BYTES + 1024 + 512;
+  static constexpr int TOTAL = SR * STAGE_BYTES + SA * A_BYTES + EPI_BYTES + 1024 + 512;
   // Decode warps work in GROUPS independent groups; group g owns decoded slot g and every
   // GROUPS-th k-block, so barrier/fence latency of one stage overlaps another's ALU work.
   static constexpr int GROUPS = 4;
@@ -208,6 +228,7 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* fix_last = const_cast<int*>(abort_flag) + 1;   // split-K fix-up: "this CTA finishes the tile"
   volatile int* epi_abort = reinterpret_cast<volatile int*>(fix_last + 1);  // written by epilogue threads only
+  __nv_bfloat16* sEpi = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(bars) + 512);  // L::EPI_BYTES
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -247,10 +268,38 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 
   if (warp == TMA_WARP) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      uint32_t it = 0;
-      for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
-        const Work wk = get_work<BN>(p, w);
+    // The whole warp walks the tile list (so that its lanes can poll the all-gather flags of a tile side by side);
+    // lane 0 alone drives the pipeline.  Loop exits are taken on values broadcast from lane 0.
+    const uint32_t ag_epoch = p.ag_wait ? p.comm.ctrl[0] : 0;   // the gather kernel that ran before this one
+    // once any kernel has recorded an expired wait the step is lost: do not spend the budget again
+    const uint64_t ag_budget = (p.ag_wait && *reinterpret_cast<volatile int*>(p.status) == 0) ? p.ar_budget_ns : 1000;
+    uint32_t it = 0;
+    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+      int stop = (lane == 0) ? *abort_flag : 0;
+      stop = __shfl_sync(0xffffffffu, stop, 0);
+      if (stop) break;
+      const Work wk = get_work<BN>(p, w);
+      if (p.ag_wait) {
+        const int src = wk.row0 / p.sp_rows;
+        if (src != p.comm.rank) {
+          const int first = (wk.row0 - src * p.sp_rows) / p.ag_flag_rows;
+          const int cnt = (wk.rows + p.ag_flag_rows - 1) / p.ag_flag_rows;
+          const uint32_t* fl = p.comm.flags2[p.comm.rank] +
+                               ((size_t)(ag_epoch & 1) * B200_MAX_RANKS + src) * B200_FLAGS_PER_SLOT + first;
+          bool ok = true;
+          for (int i = lane; i < cnt; i += 32) ok = ok && wait_flag_ge(fl + i, ag_epoch, ag_budget);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) {
+            if (lane == 0) {
+              atomicExch(p.status, ERR_WAIT_PEER);
+              *abort_flag = 1;
+            }
+            break;
+          }
+        }
+      }
+      int failed = 0;
+      if (lane == 0) {
         const int m_tile = wk.m_tile;
         const int kb0 = wk.split * kb_per_split;
         const int kb1 = min(p.kb_total, kb0 + kb_per_split);
@@ -261,6 +310,7 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           if (!mbar_wait(&empty[s], ph ^ 1)) {
             atomicExch(p.status, ERR_WAIT_STAGE);
             *abort_flag = 1;
+            failed = 1;
             break;
           }
           if (WFMT == WF_BF16) {
@@ -273,9 +323,10 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
                       wbase + ((size_t)m_tile * p.kb_total + kb) * L::RAW_BYTES, L::RAW_BYTES, &tma_full[s]);
           }
           tma_load_2d(sX + s * L::X_BYTES, &tmX, &tma_full[s], kb * BK, wk.row0);
-
         }
       }
+      failed = __shfl_sync(0xffffffffu, failed, 0);
+      if (failed) break;
     }
   } else if (warp == MMA_WARP) {
     // -------------------------------------------------------------- MMA issuer
@@ -670,6 +721,54 @@ gemm_wdec_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       const bool f_ok = f < p.N;
       const uint32_t taddr = tmem_base + (uint32_t(warp * 32) << 16) + buf * BN;
       constexpr int CH = BN >= 32 ? 32 : 16;
+      if (p.ar_mode == 3) {
+        // ---- reduce-scatter push: partial tile -> the owner's slot for source = this rank ----------------------
+        if constexpr (L::EPI_BYTES > 0) {
+          const B200Comm& cm = p.comm;
+          const int parity = ar_epoch & 1;
+          const int owner = wk.row0 / p.sp_rows;
+          const int local_row0 = wk.row0 - owner * p.sp_rows;
+          __nv_bfloat16* dst_slot = reinterpret_cast<__nv_bfloat16*>(cm.data[owner]) +
+                                    ((size_t)parity * B200_MAX_RANKS + cm.rank) * cm.slot_elems;
+          const int et = threadIdx.x;            // 0..127 inside the epilogue group
+          const int chunk = et & 15, trow = et >> 4;
+          const int fc = m_tile * BM + chunk * 8;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + c0, v);
+            tmem_ld_wait();
+            __nv_bfloat16* st = sEpi + ((c0 >> 5) & 1) * (32 * BM);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) st[j * BM + row_in_tile] = __float2bfloat16(__uint_as_float(v[j]));
+            if (c0 + 32 >= BN) {
+              tc_fence_before();
+              mbar_arrive(&acc_empty[buf]);      // the accumulator is in registers / shared memory now
+            }
+            // One barrier per half-tile: it orders this half's writes before its reads, and (a thread passes it
+            // only after its reads of the previous half) the reads of a half before its rewrite two steps later.
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (fc < p.N) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int tt = c0 + trow + 8 * i;
+                if (tt < wk.rows) {
+                  const uint4 q = *reinterpret_cast<const uint4*>(st + (trow + 8 * i) * BM + chunk * 8);
+                  *reinterpret_cast<uint4*>(dst_slot + (size_t)(local_row0 + tt) * p.ldo + fc) = q;
+                }
+              }
+            }
+          }
+          __threadfence_system();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (et == 0) {
+            const int tile_local = (local_row0 / BN) * p.m_tiles + m_tile;
+            st_release_sys(cm.flags[owner] + ((size_t)parity * B200_MAX_RANKS + cm.rank) * B200_FLAGS_PER_SLOT + tile_local,
+                           ar_epoch);
+          }
+        }
+        continue;
+      }
       if (p.ar_mode != 0) {
         // ---- fused all-reduce over peer memory --------------------------------------------------
         // The accumulator is first written as bf16 into this rank's own slot (a thread owns one feature, so these
@@ -947,13 +1046,15 @@ template <int BN, int WFMT>
 static int launch_one(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p,
                       cudaStream_t stream) {
   using L = SmemLayout<BN, WFMT>;
-  static bool configured = false;
+  static b200::PerDeviceOnce once_;
+  bool& configured = once_.slot();
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_wdec_kernel<BN, WFMT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
+  if (p.ar_mode == 3 && L::EPI_BYTES == 0) return -ERR_BAD_ARG;   // this instance has no epilogue staging
   const int total = p.work_table ? sm_count() : p.m_tiles * p.n_tiles * p.splits;
   const int grid = total < sm_count() ? total : sm_count();
   gemm_wdec_kernel<BN, WFMT><<<grid, NUM_THREADS, L::TOTAL, stream>>>(tmW, tmX, p);

@@ -56,6 +56,7 @@ sample_candidates_kernel(const float* __restrict__ vals, int ld, const int* __re
     }
   }
   const float vmax = sv[0];
+  __syncthreads();   // every thread holds the top logit before the loop below overwrites sv[] in place
   const float inv_t = 1.f / temperature;
   // tempered softmax numerators
   float part = 0.f;
