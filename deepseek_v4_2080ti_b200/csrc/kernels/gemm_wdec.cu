@@ -282,8 +282,9 @@ extern "C" int b200_gemm_wdec_ag(int wfmt, const void* W, const float* scales, c
                                  int* status, cudaStream_t stream) {
   if (!comm || comm->world <= 1 || T % comm->world || flag_rows <= 0 || !out_bf16) return -ERR_BAD_ARG;
   const int sp_rows = T / comm->world;
-  const int bn = b200_gemm_pick_bn(T) <= sp_rows ? b200_gemm_pick_bn(T) : 0;
-  if (!bn || sp_rows % bn || sp_rows % flag_rows || sp_rows / flag_rows > B200_FLAGS_PER_SLOT) return -ERR_BAD_ARG;
+  int bn = b200_gemm_pick_bn(T);
+  while (bn > 16 && sp_rows % bn) bn >>= 1;     // a token tile must not straddle two owners
+  if (sp_rows % bn || sp_rows % flag_rows || sp_rows / flag_rows > B200_FLAGS_PER_SLOT) return -ERR_BAD_ARG;
   FusedOpts fo;
   fo.comm = comm;
   fo.ar_mode = 0;

@@ -199,8 +199,13 @@ class QwenHybridWeights:
     """Device-resident, TP-sharded, kernel-ready weights built from (name, tensor) pairs."""
 
     def __init__(self, cfg: QwenHybridConfig, state: Iterator[tuple[str, torch.Tensor]], device, tp_rank: int = 0,
-                 tp_world: int = 1):
+                 tp_world: int = 1, replicate_embedding: bool = True):
+        """``replicate_embedding``: every rank keeps the whole embedding table (1.5 GB at the 27B shape, nothing
+        against 180 GB), so the lookup needs no collective; False gives the vocabulary-parallel table with a masked
+        lookup + all-reduce, as the reference does on 22 GB cards (cpp_engine/engine/qwen_engine.cpp:4113-4118).
+        The output head is vocabulary-parallel either way."""
         self.cfg, self.device, self.rank, self.world = cfg, torch.device(device), tp_rank, tp_world
+        self.embed_replicated = bool(replicate_embedding) or tp_world == 1
         self.layers: list[LayerWeights | None] = [None] * cfg.num_hidden_layers
         self._pending: dict[str, torch.Tensor] = {}
         self.embed = self.lm_head = self.final_norm = None
@@ -260,6 +265,8 @@ class QwenHybridWeights:
             t = P.pop(name)
             n = (cfg.vocab_size + self.world - 1) // self.world
             self.vocab_lo, self.vocab_hi = self.rank * n, min(cfg.vocab_size, (self.rank + 1) * n)
+            if self.embed_replicated:
+                self.vocab_lo, self.vocab_hi = 0, cfg.vocab_size
             self.embed = self._dev(t[self.vocab_lo:self.vocab_hi]).contiguous()
             return
         if name == "lm_head.weight":
@@ -449,6 +456,7 @@ class QwenHybridRuntime:
         self._bt_host = torch.zeros(max_slots, self.max_blocks_per_seq, dtype=torch.int32)
         self._graphs: dict[int, tuple] = {}
         self.launches = 0  # kernels launched by the last forward (for the bench record)
+        self._sp = False   # set while a sequence-parallel prefill chunk is in flight
         # decode batches of <= 32 rows take the fused path; needs every FP8 K dimension to be a multiple of 128
         from ..ops.gemm import WF_FP8_B128
         self.fused_decode = all(l.proj.k % 128 == 0 and l.out.k % 128 == 0 and l.down.k % 128 == 0 and
@@ -525,9 +533,21 @@ class QwenHybridRuntime:
             self.block_table[st.slot].copy_(self._bt_host[st.slot], non_blocking=True)
 
     # ---- layer bodies
-    def _row_parallel(self, x: torch.Tensor, w: PackedLinear) -> torch.Tensor:
+    def _col_parallel(self, x: torch.Tensor, w: PackedLinear) -> torch.Tensor:
+        """Column-parallel projection of the normalised activations.  Sequence-parallel chunks read the gathered
+        buffer, whose rows arrive from the ranks that own them (all-gather + GEMM in one kernel)."""
+        if self._sp:
+            return self.comm.linear_ag(x, w)
+        return gemm.linear(x, w)
+
+    def _row_parallel(self, x: torch.Tensor, w: PackedLinear) -> torch.Tensor | None:
         """Row-parallel projection: this rank's K-shard GEMM + sum over ranks.  With a peer-memory communicator the
-        reduction happens in the GEMM epilogue (tile by tile over NVLink); otherwise GEMM then all-reduce."""
+        reduction happens in the GEMM epilogue (tile by tile over NVLink); otherwise GEMM then all-reduce.
+        Sequence-parallel chunks only push the partial tiles to the owners of the rows (nothing is returned: the
+        owner's reduce + norm + gather kernel picks them up)."""
+        if self._sp:
+            self.comm.linear_rs(x, w)
+            return None
         fused = getattr(self.comm, "linear_allreduce", None)
         if fused is not None and self.comm.world > 1:
             return fused(x, w)
@@ -535,9 +555,12 @@ class QwenHybridRuntime:
 
     def _mlp(self, lw: LayerWeights, h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
-        x = basic.add_rmsnorm(h, delta, lw.post_ln, cfg.rms_norm_eps, True)
+        if self._sp:
+            x = self.comm.reduce_norm_gather(h, lw.post_ln, cfg.rms_norm_eps, True)
+        else:
+            x = basic.add_rmsnorm(h, delta, lw.post_ln, cfg.rms_norm_eps, True)
         with PROFILER.scope("lin.gate_up"):
-            gu = gemm.linear(x, lw.gate_up)
+            gu = self._col_parallel(x, lw.gate_up)
         act = basic.silu_mul(gu)
         with PROFILER.scope("lin.down+ar.mlp"):
             return self._row_parallel(act, lw.down)
@@ -546,7 +569,7 @@ class QwenHybridRuntime:
                      slot: int | None) -> torch.Tensor:
         cfg = self.cfg
         with PROFILER.scope("lin.qkvz"):
-            proj = gemm.linear(x, lw.proj)                   # [T, 2kd + vd + vd]
+            proj = self._col_parallel(x, lw.proj)            # [T, 2kd + vd + vd]
         ab = gemm.linear(x, lw.ab)                           # [T, 2 hv]
         cw = 2 * self.kd + self.vd
         idx = self.lin_layers.index(li)
@@ -602,13 +625,13 @@ class QwenHybridRuntime:
 
     def _full_attn(self, li: int, lw: LayerWeights, x: torch.Tensor, t: int, positions, kv_slots, meta) -> torch.Tensor:
         idx = self.full_layers.index(li)
-        proj = gemm.linear(x, lw.proj)
+        proj = self._col_parallel(x, lw.proj)
         o = self._attend(idx, lw, proj, t, positions, kv_slots, meta, self.cfg.rms_norm_eps)
         return self._row_parallel(o.view(t, self.hq * 128), lw.out)
 
     def _embed(self, ids: torch.Tensor) -> torch.Tensor:
         h = basic.embedding(ids, self.w.embed, self.w.vocab_lo, self.w.vocab_hi)
-        return self.comm.all_reduce(h)
+        return h if self.w.embed_replicated else self.comm.all_reduce(h)
 
     def _forward(self, ids, positions, kv_slots, meta, slot, slots_t, logits_rows: torch.Tensor | None):
         cfg, w = self.cfg, self.w
@@ -633,6 +656,38 @@ class QwenHybridRuntime:
             x = basic.add_rmsnorm(h, delta, w.final_norm, cfg.rms_norm_eps, True)
         logits = gemm.linear(x, w.lm_head, out_f32=True)
         return logits
+
+    def _forward_sp(self, ids, positions, kv_slots, meta, slot, logits_rows: torch.Tensor, rows: int) -> torch.Tensor:
+        """One prefill chunk with the residual stream sharded by token rows over the tensor-parallel ranks.
+
+        Rank r keeps rows [r*rows, (r+1)*rows) of the hidden state.  Each sub-layer is: reduce (partials of the
+        previous row-parallel GEMM) + residual add + RMSNorm on the own rows, gathered into every rank's activation
+        buffer -> column-parallel GEMM that consumes the buffer tile by tile as the rows arrive -> token mixer /
+        activation on this rank's heads or features -> row-parallel GEMM that pushes its partial tiles to the row
+        owners.  The same math, with the same roundings, as ``_forward``; norms and residual adds run on T / world
+        rows and no stand-alone collective is on the path (the reference all-reduces after every row-parallel
+        projection and norms the replicated tensor, cpp_engine/engine/qwen_engine.cpp:1942-2037, 3236-3245)."""
+        cfg, w, comm = self.cfg, self.w, self.comm
+        t = ids.numel()
+        eps = cfg.rms_norm_eps
+        own = slice(comm.rank * rows, (comm.rank + 1) * rows)
+        h = self._embed(ids[own]) if w.embed_replicated else self._embed(ids)[own].clone()
+        self._sp = True
+        try:
+            first = True
+            for i, lw in enumerate(w.layers):
+                x = comm.reduce_norm_gather(h, lw.in_ln, eps, True, with_partials=not first)
+                first = False
+                if lw.kind == "linear":
+                    self._linear_attn(i, lw, x, t, None, slot)
+                else:
+                    self._full_attn(i, lw, x, t, positions, kv_slots, meta)
+                self._mlp(lw, h, None)
+            x = comm.reduce_norm_gather(h, w.final_norm, eps, True)
+            comm.wait_gather(rows)
+        finally:
+            self._sp = False
+        return gemm.linear(x.index_select(0, logits_rows), w.lm_head, out_f32=True)
 
     def _forward_decode(self, ids, positions, kv_slots, meta, slots_t) -> torch.Tensor:
         """Decode step for up to 32 sequences: FP8 projections through the weight-streaming kernel (activations
@@ -704,7 +759,11 @@ class QwenHybridRuntime:
             meta = {"mode": "prefill", "block_table": self.block_table[slot:slot + 1], "q_start": i32(0),
                     "q_len": i32(t), "kv_len": i32(st.length + t), "max_q_len": t, "past": st.length}
             rows = torch.tensor([t - 1], dtype=torch.int64, device=self.device)
-            logits = self._forward(ids, pos, kv_slots, meta, slot, None, rows)
+            sp_rows = self.comm.sp_rows(t, self.cfg.hidden_size) if hasattr(self.comm, "sp_rows") else 0
+            if sp_rows:
+                logits = self._forward_sp(ids, pos, kv_slots, meta, slot, rows, sp_rows)
+            else:
+                logits = self._forward(ids, pos, kv_slots, meta, slot, None, rows)
             self.last_logits = logits                  # last row of the latest chunk (fp32 [1, vocab])
             st.length += t
             self.prefill_tokens_computed += t

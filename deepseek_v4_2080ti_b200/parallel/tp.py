@@ -124,12 +124,7 @@ class PeerComm(TPComm):
         self.budget_ns = int(budget_ms * 1e6)
         self.device = torch.device("cuda", torch.cuda.current_device())
         L = _lib.lib()
-        L.b200_comm_buffer_bytes.restype = ctypes.c_ulonglong
-        nbytes = L.b200_comm_buffer_bytes(ctypes.c_ulonglong(self.slot_elems))
-        base = ctypes.c_void_p()
-        rc = L.b200_comm_alloc(ctypes.c_ulonglong(nbytes), ctypes.byref(base))
-        if rc != 0:
-            raise RuntimeError(f"symmetric buffer allocation failed: CUDA error {rc}")
+        base = self._alloc(self.slot_elems)
         self._base = base
         handle = ctypes.create_string_buffer(64)
         rc = L.b200_comm_ipc_handle(base, handle)
@@ -149,14 +144,54 @@ class PeerComm(TPComm):
                 raise RuntimeError(f"cudaIpcOpenMemHandle(rank {r}) failed: {rc}")
             self._peers.append(p)
             bases[r] = p.value
-        self.c = _CommStruct()
-        rc = L.b200_comm_init(ctypes.byref(self.c), self.rank, self.world, bases, ctypes.c_ulonglong(self.slot_elems))
-        if rc != 0:
-            raise RuntimeError(f"comm init failed: {rc}")
+        self._bind(bases)
         torch.cuda.synchronize()
         dist.barrier(group=self.group)
+
+    @staticmethod
+    def _alloc(slot_elems: int) -> ctypes.c_void_p:
+        L = _lib.lib()
+        L.b200_comm_buffer_bytes.restype = ctypes.c_ulonglong
+        nbytes = L.b200_comm_buffer_bytes(ctypes.c_ulonglong(slot_elems))
+        base = ctypes.c_void_p()
+        rc = L.b200_comm_alloc(ctypes.c_ulonglong(nbytes), ctypes.byref(base))
+        if rc != 0:
+            raise RuntimeError(f"symmetric buffer allocation failed: CUDA error {rc}")
+        return base
+
+    def _bind(self, bases) -> None:
+        self.c = _CommStruct()
+        rc = _lib.lib().b200_comm_init(ctypes.byref(self.c), self.rank, self.world, bases,
+                                       ctypes.c_ulonglong(self.slot_elems))
+        if rc != 0:
+            raise RuntimeError(f"comm init failed: {rc}")
         self.fused_calls = 0
+        self.standalone_calls = 0
         self._result_index = 0
+        self._rs_bn = 0
+        self.sp_enabled = os.environ.get("B200_SP", "1") != "0"
+
+    @classmethod
+    def local_group(cls, world: int, slot_elems: int, budget_ms: float = 50.0) -> list["PeerComm"]:
+        """``world`` communicators over ``world`` symmetric buffers of ONE device, in one process: the ranks of a
+        collective are then stepped one after another on one stream (phase by phase, so that every wait finds its
+        flags already raised by kernels that have completed).  For single-GPU numerics tests of the multi-rank
+        kernels and for the timeout path; the collectives that fall back to the process group are not available."""
+        bases = (ctypes.c_void_p * MAX_RANKS)()
+        raw = [cls._alloc(int(slot_elems)) for _ in range(world)]
+        for r in range(world):
+            bases[r] = raw[r].value
+        out = []
+        for r in range(world):
+            c = cls.__new__(cls)
+            c.group, c.world, c.rank, c.bytes_reduced = None, world, r, 0
+            c.slot_elems, c.budget_ns = int(slot_elems), int(budget_ms * 1e6)
+            c.device = torch.device("cuda", torch.cuda.current_device())
+            c._base, c._peers = raw[r], []
+            c._bind(bases)
+            out.append(c)
+        torch.cuda.synchronize()
+        return out
 
     def _cref(self):
         return ctypes.byref(self.c)
@@ -170,7 +205,7 @@ class PeerComm(TPComm):
                                                _lib.ptr(_lib.status_word(t.device)), ctypes.c_ulonglong(self.budget_ns),
                                                _lib.stream())
         _lib.check(rc, "allreduce_oneshot")
-        self.fused_calls += 1
+        self.standalone_calls += 1        # a peer-memory collective, but not fused into a compute kernel
         self.bytes_reduced += t.numel() * 2
         return t
 
@@ -254,6 +289,78 @@ class PeerComm(TPComm):
         _lib.check(rc, "gemm_wdec_allreduce")
         self.fused_calls += 1
         return out
+
+    # ---- sequence-parallel residual stream (csrc/comm/sp_comm.cu, gemm_wdec_kernel.cuh ar_mode 3 / ag_wait)
+    SP_FLAG_ROWS = 8
+
+    def sp_rows(self, t: int, h: int) -> int:
+        """Rows of the residual stream each rank owns when a ``t``-token chunk runs sequence-parallel, 0 when this
+        shape cannot (the shard must be a whole number of 128-token GEMM tiles and the gathered tensor must fit)."""
+        if self.world <= 1 or not self.sp_enabled or t % self.world:
+            return 0
+        rows = t // self.world
+        if rows % 128 or t * h > self.slot_elems or h % 8:
+            return 0
+        return rows
+
+    def linear_rs(self, x: torch.Tensor, w) -> None:
+        """Row-parallel GEMM whose epilogue pushes every partial tile to the rank that owns those token rows (the
+        push half of a reduce-scatter).  No local result: ``reduce_norm_gather`` on the owner sums the partials."""
+        from ..ops import gemm
+
+        t, k = x.shape
+        assert x.dtype == torch.bfloat16 and x.is_contiguous() and k == w.k and w.n % 8 == 0
+        if w.wfmt == gemm.WF_FP8_B128 and t >= gemm.PREDECODE_MIN_T and w.n % 128 == 0 and k % 64 == 0:
+            w = gemm._expanded_bf16(w, x.device)
+        bn = ctypes.c_int(0)
+        rc = _lib.lib().b200_gemm_wdec_rs(w.wfmt, _lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(x), t, w.n, k,
+                                          self._cref(), ctypes.c_ulonglong(self.budget_ns), ctypes.byref(bn),
+                                          _lib.ptr(_lib.status_word(x.device)), _lib.stream())
+        _lib.check(rc, "gemm_wdec_rs")
+        self._rs_bn = bn.value
+        self.fused_calls += 1
+        self.bytes_reduced += t * w.n * 2
+
+    def reduce_norm_gather(self, h_shard: torch.Tensor, gamma: torch.Tensor | None, eps: float,
+                           unit_offset: bool = True, with_partials: bool = True, gather: bool = True) -> torch.Tensor | None:
+        """Owner side of the reduce-scatter fused with the residual add, the RMSNorm and the all-gather: sums the
+        partials of the last ``linear_rs`` into ``h_shard`` (in place), normalises and stores the rows into every
+        rank's gathered buffer.  Returns that buffer, bf16 [world * rows, H]: rows of other ranks become valid as
+        their flags arrive (``linear_ag`` waits per tile; anything else calls ``wait_gather`` first)."""
+        rows, h = h_shard.shape
+        assert h_shard.dtype == torch.bfloat16 and h_shard.is_contiguous()
+        rc = _lib.lib().b200_sp_reduce_norm_gather(self._cref(), _lib.ptr(h_shard), _lib.ptr(gamma),
+                                                   ctypes.c_float(eps), int(unit_offset), rows, h, int(with_partials),
+                                                   self._rs_bn, 0, int(gather), _lib.ptr(_lib.status_word(h_shard.device)),
+                                                   ctypes.c_ulonglong(self.budget_ns), _lib.stream())
+        _lib.check(rc, "sp_reduce_norm_gather")
+        self.fused_calls += 1
+        return self._result_view(0, rows * self.world, h) if gamma is not None else None
+
+    def linear_ag(self, x_full: torch.Tensor, w, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Column-parallel GEMM on the gathered buffer: each token tile is loaded (from local memory) once the rank
+        that owns those rows has raised their flags; own rows first."""
+        from ..ops import gemm
+
+        t, k = x_full.shape
+        assert k == w.k
+        if w.wfmt == gemm.WF_FP8_B128 and t >= gemm.PREDECODE_MIN_T and w.n % 128 == 0 and k % 64 == 0:
+            w = gemm._expanded_bf16(w, x_full.device)
+        if out is None:
+            out = torch.empty(t, w.n, dtype=torch.bfloat16, device=x_full.device)
+        rc = _lib.lib().b200_gemm_wdec_ag(w.wfmt, _lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(x_full),
+                                          _lib.ptr(out), t, w.n, k, self._cref(), self.SP_FLAG_ROWS,
+                                          ctypes.c_ulonglong(self.budget_ns), _lib.ptr(_lib.status_word(x_full.device)),
+                                          _lib.stream())
+        _lib.check(rc, "gemm_wdec_ag")
+        self.fused_calls += 1
+        return out
+
+    def wait_gather(self, rows: int) -> None:
+        """Hold the stream until every peer's rows of the last gather are in this rank's buffer."""
+        rc = _lib.lib().b200_sp_wait_gather(self._cref(), rows, _lib.ptr(_lib.status_word(self.device)),
+                                            ctypes.c_ulonglong(self.budget_ns), _lib.stream())
+        _lib.check(rc, "sp_wait_gather")
 
     def check(self) -> None:
         try:

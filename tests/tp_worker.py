@@ -99,6 +99,32 @@ def main() -> None:
         assert ref.tolist() == out, ("ranks disagree", name)
     assert comm.fused_calls > 0
 
+    # sequence-parallel prefill (reduce-scatter GEMM -> reduce + norm + gather -> all-gather GEMM) against the
+    # all-reduce form of the same chunk: same logits within bf16 noise, same greedy continuation
+    t_sp = 256 * world
+    assert comm.sp_rows(t_sp, cfg.hidden_size) == 256
+    torch.manual_seed(11)
+    sp_prompt = torch.randint(0, cfg.vocab_size, (t_sp,), dtype=torch.int32)
+    rt = qh.QwenHybridRuntime(cfg, wt, max_slots=1, max_context=t_sp + 64, comm=comm)
+    outs = {}
+    for sp in (False, True, True):
+        comm.sp_enabled = sp
+        calls0 = comm.fused_calls
+        toks = rt.generate(sp_prompt, 6, chunk=t_sp)
+        torch.cuda.synchronize()
+        comm.check()
+        outs.setdefault(sp, []).append((toks, rt.last_logits.clone() if hasattr(rt, "last_logits") else None))
+        if sp:
+            # per layer: 2 reduce-scatter GEMMs, 2 gathers, 2 all-gather GEMMs; + the final gather
+            assert comm.fused_calls - calls0 >= 6 * cfg.num_hidden_layers + 1, comm.fused_calls - calls0
+    (ta, _), (tb, _), (tc, _) = outs[False][0], outs[True][0], outs[True][1]
+    assert tb == tc, ("sequence-parallel prefill not reproducible", tb, tc)
+    assert ta[0] == tb[0] and sum(a == b for a, b in zip(ta, tb)) >= 5, ("sp vs all-reduce", ta, tb)
+    ref = torch.tensor(tb, device=dev)
+    dist.broadcast(ref, 0)
+    assert ref.tolist() == tb, ("ranks disagree (sp)",)
+    del rt
+
     # expert-parallel combine fused with its collective (one-shot and two-shot) against combine + NCCL
     from deepseek_v4_2080ti_b200.ops import moe
     for t, k, h, rows in [(1, 4, 512, 4), (37, 4, 512, 80), (300, 8, 1024, 900)]:
