@@ -38,7 +38,73 @@ def parse():
     ap.add_argument("--layers", type=int, default=64, help="debug only; the reported config is 64")
     ap.add_argument("--chunk", type=int, default=8192)
     ap.add_argument("--tiny", action="store_true", help="debug only: 4-layer hidden-256 model")
-    return ap.parse_args()
+    ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4, 5],
+                    help="benchmark configuration: 2 Qwen-shaped FP8 hybrid (the headline, default), 3 MiniMax-shaped "
+                         "GGUF GQA-MoE, 4 DeepSeek-V4-Flash-shaped MLA + indexer + FP4 MoE, 5 GLM-shaped GGUF DSA-MoE")
+    from deepseek_v4_2080ti_b200.utils import model_bench
+    model_bench.add_arguments(ap, layers=False)
+    args = ap.parse_args()
+    args.prompt_given = "--prompt" in sys.argv
+    return args
+
+
+# configs 3-5: published numbers of the reference on 4x RTX 2080 Ti for the models these shapes follow
+MOE_CONFIGS = {
+    3: ("gqa_moe", 107.0, 10.32, "MiniMax-M2.7 UD-IQ1_M 256-token prefill / 43-layer decode (docs/models/minimax-m2.7.md:46-48)"),
+    4: ("dsv4", 402.0, 3.7, "DeepSeek-V4-Flash C++ FP4 prefill @ 32,768 / decode (docs/models/deepseek-v4.md:52-54)"),
+    5: ("glm", 0.79, 0.66, "GLM-5.2 UD-Q2_K_XL prefill / decode (docs/models/glm-5.2.md:51-52)"),
+}
+
+
+def run_moe_config(args) -> None:
+    """Configs 3-5 through utils/model_bench.py: same timing rules and JSON keys as the headline config."""
+    import torch
+    import torch.distributed as dist
+
+    from deepseek_v4_2080ti_b200.parallel import tp
+    from deepseek_v4_2080ti_b200.utils import model_bench
+    from deepseek_v4_2080ti_b200.utils.clocks import ClockSampler
+
+    family, pub_prefill, pub_decode, pub_src = MOE_CONFIGS[args.config]
+    d_prompt, d_decode, d_chunk, d_pp = model_bench.FAMILY_DEFAULTS[family]
+    args.family = family
+    args.layers = 0 if args.layers == 64 else args.layers        # 64 is the headline config's own default: all layers
+    if not args.prompt_given:
+        args.prompt = d_prompt
+    args.decode = min(args.decode, d_decode)
+    args.chunk = min(args.chunk, d_chunk)
+    if args.config == 5 and args.pp == 1 and args.gpus >= 2 and os.environ.get("B200_BENCH_GLM_PP", "0") == "1":
+        args.pp = d_pp
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "config": args.config, "unavailable":
+                          "the reference serves this family through its torch plane on real checkpoints only "
+                          "(hard-coded head counts / tensor inventories of the released models); no synthetic "
+                          "checkpoint of the benchmark shape loads there - see the record in BASELINE.md"}), flush=True)
+        return
+    rank, world, local = tp.init_distributed()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    rec = model_bench.run_family(args, rank, world, dev, steps=args.steps, warmup=args.warmup,
+                                 clock_sampler=lambda: ClockSampler(local))
+    if rec is not None:
+        out = {"metric": "prefill_tok_s", "value": rec["prefill_tok_s"], "unit": "tok/s", "n_gpus": world,
+               "steps": rec["steps"], "warmup": rec["warmup"],
+               "ms_per_step": round(rec["prefill_ms"] + rec["decode_ms_per_token"] * args.decode, 3),
+               "higher_is_better": True, "scaling": "strong", "vs_baseline": round(rec["prefill_tok_s"] / pub_prefill, 2),
+               "dtype": "bf16", "data": rec["data"], "impl": "b200", "prefill_ms": rec["prefill_ms"],
+               "decode_tok_s": rec["decode_tok_s"], "decode_ms_per_token": rec["decode_ms_per_token"],
+               "decode_vs_baseline": round(rec["decode_tok_s"] / pub_decode, 2), "baseline_source": pub_src,
+               "config": {"model": rec["model"], "global_batch": 1, "seq_len": args.prompt, "decode_tokens": args.decode,
+                          "parallelism": rec["parallelism"], "collectives": rec["collectives"],
+                          "weights_gb_per_rank": rec["weights_gb_per_rank"],
+                          "l2_policy": "inputs larger than L2: every step streams the rank's weight set"},
+               "clocks": rec.get("clocks"), "gpu_launches": None,
+               "detail": {k: v for k, v in rec.items() if k.startswith("mtp_") or k in ("plain_total_ms", "launches_per_decode_step",
+                                                                                     "build_seconds", "timing")}}
+        print(json.dumps(out), flush=True)
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def run_reference(args) -> None:
@@ -50,6 +116,9 @@ def run_reference(args) -> None:
 
 def main() -> None:
     args = parse()
+    if args.config != 2:
+        run_moe_config(args)
+        return
     if args.impl == "reference":
         run_reference(args)
         return
@@ -223,7 +292,13 @@ def main() -> None:
             bd = max_over_ranks(bd_ms)
             rec["decode_batch"] = {"batch": bdec, "ms_per_step": round(bd, 4), "tok_s": round(bdec / (bd / 1e3), 1)}
         if comm is not None:
+            # fused = kernels that carry their collective (reduce-scatter / all-gather GEMMs, the reduce + norm + gather
+            # kernel, GEMM + all-reduce epilogues); standalone = peer-memory collectives launched on their own
             rec["fused_collective_calls"] = int(comm.fused_calls)
+            rec["standalone_peer_collectives"] = int(comm.standalone_calls)
+            rec["config"]["prefill_collectives"] = ("sequence-parallel: GEMM->reduce-scatter, reduce+norm+all-gather, "
+                                                    "all-gather->GEMM over peer memory") \
+                if comm.sp_rows(min(args.chunk, args.prompt), cfg.hidden_size) else "GEMM + all-reduce"
         print(json.dumps(rec), flush=True)
     elif bd_ms is not None:
         max_over_ranks(bd_ms)

@@ -532,6 +532,14 @@ class QwenHybridRuntime:
         if changed:
             self.block_table[st.slot].copy_(self._bt_host[st.slot], non_blocking=True)
 
+    def recover_collectives(self) -> None:
+        """After a collective timed out: re-synchronise the communicator (all ranks call this) and drop the captured
+        decode graphs, which still hold the peer-memory kernels."""
+        rec = getattr(self.comm, "recover", None)
+        if rec is not None:
+            rec()
+        self._graphs.clear()
+
     # ---- layer bodies
     def _col_parallel(self, x: torch.Tensor, w: PackedLinear) -> torch.Tensor:
         """Column-parallel projection of the normalised activations.  Sequence-parallel chunks read the gathered

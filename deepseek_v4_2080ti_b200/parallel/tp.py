@@ -170,6 +170,8 @@ class PeerComm(TPComm):
         self._result_index = 0
         self._rs_bn = 0
         self.sp_enabled = os.environ.get("B200_SP", "1") != "0"
+        self.degraded = False       # after recover(): every collective goes through the process group (NCCL)
+        self.recoveries = 0
 
     @classmethod
     def local_group(cls, world: int, slot_elems: int, budget_ms: float = 50.0) -> list["PeerComm"]:
@@ -199,7 +201,7 @@ class PeerComm(TPComm):
     def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
         if self.world == 1:
             return t
-        if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.numel() > self.slot_elems:
+        if self.degraded or t.dtype != torch.bfloat16 or not t.is_contiguous() or t.numel() > self.slot_elems:
             return super().all_reduce(t)
         rc = _lib.lib().b200_allreduce_oneshot(self._cref(), _lib.ptr(t), ctypes.c_longlong(t.numel()),
                                                _lib.ptr(_lib.status_word(t.device)), ctypes.c_ulonglong(self.budget_ns),
@@ -213,7 +215,7 @@ class PeerComm(TPComm):
         if self.world == 1:
             return idx
         rows = idx.numel()
-        if rows * 4 > self.slot_elems:
+        if self.degraded or rows * 4 > self.slot_elems:
             return super().argmax_merge(idx, val)
         out = torch.empty(rows, dtype=torch.int32, device=idx.device)
         rc = _lib.lib().b200_argmax_merge(self._cref(), _lib.ptr(val.float().contiguous()),
@@ -227,6 +229,8 @@ class PeerComm(TPComm):
                     residual: torch.Tensor | None, t: int, k: int, h: int, mode: int = 0) -> torch.Tensor:
         """Expert-parallel combine fused with its collective: ``residual + sum_ranks(base_r + sum_k w * y_r[row])``.
         mode 0 picks one-shot or two-shot by payload size (csrc/comm/moe_comm.cu)."""
+        if self.degraded:
+            return super().moe_combine(y, route_row, wts, base, residual, t, k, h, mode)
         out = torch.empty(t, h, dtype=torch.bfloat16, device=y.device)
         rc = _lib.lib().b200_moe_combine_allreduce(self._cref(), _lib.ptr(y), _lib.ptr(route_row), _lib.ptr(wts),
                                                    _lib.ptr(base), _lib.ptr(residual), _lib.ptr(out), t, k, h, mode,
@@ -259,7 +263,7 @@ class PeerComm(TPComm):
         n = w.n
         bn = gemm._bn(t)
         tiles = ((n + 127) // 128) * ((t + bn - 1) // bn)
-        if self.world == 1 or t * n > self.slot_elems or tiles > 4096 or n % 8:
+        if self.world == 1 or self.degraded or t * n > self.slot_elems or tiles > 4096 or n % 8:
             return self.all_reduce(gemm.linear(x, w, residual=None)) if residual is None else \
                 self.all_reduce(gemm.linear(x, w)).add_(residual)
         if two_shot is None and self.world > 4 and t > 64:
@@ -296,7 +300,7 @@ class PeerComm(TPComm):
     def sp_rows(self, t: int, h: int) -> int:
         """Rows of the residual stream each rank owns when a ``t``-token chunk runs sequence-parallel, 0 when this
         shape cannot (the shard must be a whole number of 128-token GEMM tiles and the gathered tensor must fit)."""
-        if self.world <= 1 or not self.sp_enabled or t % self.world:
+        if self.world <= 1 or not self.sp_enabled or self.degraded or t % self.world:
             return 0
         rows = t // self.world
         if rows % 128 or t * h > self.slot_elems or h % 8:
@@ -361,6 +365,36 @@ class PeerComm(TPComm):
         rc = _lib.lib().b200_sp_wait_gather(self._cref(), rows, _lib.ptr(_lib.status_word(self.device)),
                                             ctypes.c_ulonglong(self.budget_ns), _lib.stream())
         _lib.check(rc, "sp_wait_gather")
+
+    def _ctrl_view(self) -> torch.Tensor:
+        """int32 view of this rank's control words ([0] = epoch of the last finished collective, [1] = exit counter)."""
+        ptr = int(self.c.ctrl)
+
+        class _Mem:
+            __cuda_array_interface__ = {"shape": (16,), "typestr": "<i4", "data": (ptr, False), "version": 2}
+
+        return torch.as_tensor(_Mem(), device=self.device)
+
+    def recover(self, degrade: bool = True) -> None:
+        """Collective (every rank of the group calls it once): bring the communicator back to a defined state after a
+        bounded wait expired somewhere (``CollectiveTimeoutError``).  The ranks meet on the process group, agree on an
+        epoch above every value any of them has used (stale flags and slots then belong to the past), clear the exit
+        counter and the error word.  With ``degrade`` the communicator afterwards sends every collective through the
+        process group - the step is finished on the library path, as the reference does when its custom all-reduce
+        times out (src/models/deepseek_v4/runtime.py:262-268, 4211-4217) - otherwise the peer-memory kernels stay on."""
+        torch.cuda.synchronize()
+        ctrl = self._ctrl_view()
+        top = ctrl[:1].clone().to(torch.int64)
+        if self.group is not None or dist.is_initialized():
+            dist.all_reduce(top, op=dist.ReduceOp.MAX, group=self.group)
+        ctrl[0] = (top[0] + 2).to(torch.int32)
+        ctrl[1] = 0
+        _lib.status_word(self.device).zero_()
+        torch.cuda.synchronize()
+        if dist.is_initialized():
+            dist.barrier(group=self.group)
+        self.degraded = self.degraded or degrade
+        self.recoveries += 1
 
     def check(self) -> None:
         try:

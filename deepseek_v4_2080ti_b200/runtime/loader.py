@@ -101,7 +101,30 @@ class RuntimeAdapter:
         self._rng.pop(slot, None)
         self._counts.pop(slot, None)
 
+    def _check_collectives(self) -> None:
+        """Multi-rank only: the step's tokens are on the host, so the kernels have finished - read the error word.
+        A bounded wait that expired surfaces here as ``CollectiveTimeoutError`` (see ``recover``)."""
+        chk = getattr(self.rt.comm, "check", None)
+        if chk is not None and self.rt.comm.world > 1:
+            chk()
+
+    def recover(self) -> None:
+        """Collective: every rank calls it after any rank saw ``CollectiveTimeoutError``; afterwards the collectives
+        run on the library path and the slots must be filled again (their state may hold half a step)."""
+        self.rt.recover_collectives()
+
     def prefill_tokens(self, slot: int, prompt: list[int], chunk: int, sp: Any) -> int:
+        tok = self._prefill_tokens(slot, prompt, chunk, sp)
+        self._check_collectives()
+        return tok
+
+    def decode_tokens(self, slots: list[int], toks: list[int], sp: Any) -> list[int]:
+        """``sp``: one SamplingParams for the whole batch, a list with one per slot, or None (greedy)."""
+        out = self._decode_tokens(slots, toks, sp)
+        self._check_collectives()
+        return out
+
+    def _prefill_tokens(self, slot: int, prompt: list[int], chunk: int, sp: Any) -> int:
         ids = torch.tensor(prompt, dtype=torch.int32).pin_memory().to(self.rt.device, non_blocking=True)
         ds = self._sampling(slot, sp, prompt)
         before = self.rt.prefill_tokens_computed
@@ -116,8 +139,7 @@ class RuntimeAdapter:
         self.last_cached_tokens = len(prompt) - (self.rt.prefill_tokens_computed - before)
         return tok
 
-    def decode_tokens(self, slots: list[int], toks: list[int], sp: Any) -> list[int]:
-        """``sp``: one SamplingParams for the whole batch, a list with one per slot, or None (greedy)."""
+    def _decode_tokens(self, slots: list[int], toks: list[int], sp: Any) -> list[int]:
         t = torch.tensor(toks, dtype=torch.int32, device=self.rt.device)
         sps = sp if isinstance(sp, (list, tuple)) else [sp] * len(slots)
         dss = [self._sampling(s, p, None) for s, p in zip(slots, sps)]
@@ -329,12 +351,21 @@ def load_runtime(args):
         os.environ.setdefault("WORLD_SIZE", str(world))
         os.environ.setdefault("LOCAL_RANK", str(dev.index or 0))
         tp.init_distributed("nccl")
-        comm = tp.TPComm()
         base = os.environ.get("POCKETLLM_NCCL_ID_PATH") or f"/tmp/pocketllm-{os.environ.get('MASTER_PORT', '0')}"
         channel = Channel(base, rank, world)
     model = args.model
     max_ctx = args.max_model_len or 8192 + 512
     slots = max(1, args.max_batch_size)
+    chunk = int(args.prefill_chunk_tokens or 8192)
+
+    def make_comm(hidden: int):
+        """Peer-memory communicator (fused GEMM + collective kernels over NVLink) sized for one prefill chunk of hidden
+        states; POCKETLLM_TP_COMM=nccl selects the library baseline."""
+        if world <= 1:
+            return None
+        if os.environ.get("POCKETLLM_TP_COMM", "peer") == "nccl":
+            return tp.TPComm()
+        return tp.PeerComm(slot_elems=max(1 << 20, min(chunk, max_ctx) * int(hidden)))
     if _is_gguf(model):
         # MoE families from GGUF: the family registry reads the metadata, validates the tensor inventory and builds the
         # runtime (attention heads and experts sharded over the ranks); greedy decoding through the slot interface
@@ -344,6 +375,7 @@ def load_runtime(args):
         from pocketllm.backends.native_backend import NullChannel
         bundle = read_bundle(model)
         spec = registry.detect(bundle)
+        comm = make_comm(int(bundle.metadata.get(f"{spec.architecture}.embedding_length", 8192)))
         report = spec.validate(bundle)
         if not report.ok:
             raise ValueError(f"{model}: missing {report.missing[:4]} unsupported {list(report.unsupported)[:4]}")
@@ -367,6 +399,7 @@ def load_runtime(args):
         from ..formats import safetensors_io
         state = safetensors_io.read_checkpoint(args.checkpoint_dir)
     weights = qh.QwenHybridWeights(cfg, state, dev, rank, world)
+    comm = make_comm(cfg.hidden_size)
     rt = qh.QwenHybridRuntime(cfg, weights, max_slots=slots, max_context=max_ctx, comm=comm,
                               attention_window=int(getattr(args, "attention_window", 0) or 0),
                               attention_sink_tokens=int(getattr(args, "attention_sink_tokens", 0) or 0),

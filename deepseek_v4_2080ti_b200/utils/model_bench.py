@@ -72,13 +72,13 @@ def _gqa_moe(args, rank, world, dev):
         rt.free(slot)
         return pre_ms, dec_ms
 
-    request(4, prompt[:args.chunk])                    # warm-up: one full chunk (workspaces, lazy kernel set-up, graphs)
-    pre_ms, dec_ms = request(args.decode)
+    warm = lambda: request(4, prompt[:args.chunk])     # one full chunk (workspaces, lazy kernel set-up, graphs)
+    run = lambda: request(args.decode)
     desc = {"model": f"MiniMax-M2.7-shaped GQA-MoE GGUF ({cfg.n_layers}L of 62, hidden {cfg.hidden}, {cfg.n_experts} experts top-{cfg.top_k}, "
                      f"attn {cfg.attn_type}, experts {cfg.gate_up_type}/{cfg.down_type})",
             "parallelism": f"tp{world}+ep{world}", "collectives": "nccl" if args.nccl else "peer-memory kernels",
-            "launches_per_decode_step": rt.launches}
-    return pre_ms, dec_ms, w.nbytes(), build_s, desc
+            "hidden": cfg.hidden, "launches": lambda: rt.launches}
+    return warm, run, w.nbytes(), build_s, desc
 
 
 def _mla(args, rank, world, dev, glm: bool):
@@ -147,21 +147,24 @@ def _mla(args, rank, world, dev, glm: bool):
             link.drain()
         return pre_ms, dec_ms
 
-    request(2, False, prompt[:args.chunk])             # warm-up: one full chunk
-    pre_ms, dec_ms = request(args.decode, False)
-    extra = {}
-    if args.mtp and w.mtp:
+    warm = lambda: request(2, False, prompt[:args.chunk])      # one full chunk
+    run = lambda: request(args.decode, False)
+
+    def extra_fn(pre_ms, dec_ms):
+        if not (args.mtp and w.mtp):
+            return {}
         _, spec_ms = request(args.decode, True)
-        extra = {"mtp_total_ms": round(spec_ms, 2), "mtp_steps": rt.spec_stats["steps"], "mtp_accepted": rt.spec_stats["accepted"],
-                 "plain_total_ms": round(pre_ms + dec_ms, 2)}
+        return {"mtp_total_ms": round(spec_ms, 2), "mtp_steps": rt.spec_stats["steps"],
+                "mtp_accepted": rt.spec_stats["accepted"], "plain_total_ms": round(pre_ms + dec_ms, 2)}
     name = "GLM-5.2-shaped MLA + DSA indexer MoE, GGUF mix Q8_0/Q4_K/Q2_K/IQ3_XXS" if glm else \
         "DeepSeek-V4-Flash-shaped MLA + indexer MoE, FP8 dense + FP4 experts"
     desc = {"model": f"{name} ({cfg.num_layers}L of {78 if glm else 43}, hidden {cfg.hidden_size}, {cfg.num_experts} experts top-{cfg.experts_per_token}, "
                      f"index top-{cfg.index_topk})",
             "parallelism": (f"pp{stages} x " if stages > 1 else "") + f"tp{tpw}+ep{tpw}",
-            "collectives": "nccl" if (args.nccl or stages > 1) else "peer-memory kernels", **extra}
+            "collectives": "nccl" if (args.nccl or stages > 1) else "peer-memory kernels", "hidden": cfg.hidden_size,
+            "extra": extra_fn}
     nbytes = sum(t.numel() * t.element_size() for t in _tensors(w))
-    return pre_ms, dec_ms, nbytes, build_s, desc
+    return warm, run, nbytes, build_s, desc
 
 
 def _tensors(obj, seen=None, depth=0):
@@ -188,36 +191,75 @@ def _tensors(obj, seen=None, depth=0):
             yield from _tensors(x, seen, depth + 1)
 
 
+FAMILY_DEFAULTS = {           # the benchmark shapes: (prompt, decode, chunk, pipeline stages)
+    "gqa_moe": (4096, 256, 4096, 1), "dsv4": (32768, 256, 4096, 1), "glm": (2048, 256, 2048, 2),
+}
+
+
+def add_arguments(ap: argparse.ArgumentParser, layers: bool = True) -> None:
+    if layers:
+        ap.add_argument("--layers", type=int, default=0, help="run only the first N layers (reported as such)")
+    ap.add_argument("--expert-pool", type=int, default=4)
+    ap.add_argument("--pp", type=int, default=1, help="pipeline stages (glm / dsv4)")
+    ap.add_argument("--mtp", action="store_true", help="dsv4: also time depth-1 speculative decoding")
+    ap.add_argument("--eager-decode", action="store_true", help="MLA families: launch every decode kernel instead of replaying a graph")
+    ap.add_argument("--nccl", action="store_true", help="library collectives instead of the peer-memory kernels")
+
+
+def run_family(args, rank: int, world: int, dev, steps: int = 1, warmup: int = 1, clock_sampler=None) -> dict | None:
+    """Build the family's synthetic model, run ``warmup`` untimed and ``steps`` timed requests (prefill of
+    ``args.prompt`` tokens + ``args.decode`` greedy tokens, CUDA events, max over ranks) and return the record
+    (rank 0) or None.  ``clock_sampler``: a context-manager factory sampling the GPU clocks over the timed region."""
+    import contextlib
+    with torch.no_grad():
+        build = _gqa_moe if args.family == "gqa_moe" else (lambda *a: _mla(*a, args.family == "glm"))
+        warm, run, nbytes, build_s, desc = build(args, rank, world, dev)
+        for _ in range(max(1, warmup)):
+            warm()
+        pre, dec = [], []
+        with (clock_sampler() if clock_sampler else contextlib.nullcontext()) as clk:
+            for _ in range(max(1, steps)):
+                p, d = run()
+                pre.append(p)
+                dec.append(d)
+        pre_ms, dec_ms = sum(pre) / len(pre), sum(dec) / len(dec)
+        extra = desc.pop("extra", None)
+        launches = desc.pop("launches", None)
+        more = extra(pre_ms, dec_ms) if extra else {}
+    from ..ops import _lib
+    _lib.check_status()
+    if rank != 0:
+        return None
+    rec = {"family": args.family, "n_gpus": world, "prompt_tokens": args.prompt, "decode_tokens": args.decode,
+           "steps": len(pre), "warmup": max(1, warmup),
+           "prefill_ms": round(pre_ms, 2), "prefill_tok_s": round(args.prompt / pre_ms * 1e3, 1),
+           "decode_ms_per_token": round(dec_ms / max(1, args.decode), 3),
+           "decode_tok_s": round(args.decode / dec_ms * 1e3, 2), "weights_gb_per_rank": round(nbytes / 1e9, 2),
+           "build_seconds": round(build_s, 1), "data": "synthetic random-init, expert pool %d" % args.expert_pool,
+           "timing": "CUDA events, max over ranks, after a one-chunk warm-up request", **desc, **more}
+    if launches:
+        rec["launches_per_decode_step"] = launches()
+    if clock_sampler and clk is not None:
+        rec["clocks"] = clk.summary()
+    return rec
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--family", choices=["gqa_moe", "glm", "dsv4"], required=True)
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--decode", type=int, default=64)
     ap.add_argument("--chunk", type=int, default=4096)
-    ap.add_argument("--layers", type=int, default=0, help="run only the first N layers (reported as such)")
-    ap.add_argument("--expert-pool", type=int, default=4)
-    ap.add_argument("--pp", type=int, default=1, help="pipeline stages (glm / dsv4)")
-    ap.add_argument("--mtp", action="store_true", help="dsv4: also time depth-1 speculative decoding")
-    ap.add_argument("--eager-decode", action="store_true", help="MLA families: launch every decode kernel instead of replaying a graph")
-    ap.add_argument("--nccl", action="store_true", help="library collectives instead of the peer-memory kernels")
+    ap.add_argument("--steps", type=int, default=1)
+    ap.add_argument("--warmup", type=int, default=1)
+    add_arguments(ap)
     args = ap.parse_args()
     rank, world, local = tp.init_distributed()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    with torch.no_grad():
-        if args.family == "gqa_moe":
-            pre_ms, dec_ms, nbytes, build_s, desc = _gqa_moe(args, rank, world, dev)
-        else:
-            pre_ms, dec_ms, nbytes, build_s, desc = _mla(args, rank, world, dev, args.family == "glm")
-    from ..ops import _lib
-    _lib.check_status()
-    if rank == 0:
-        print(json.dumps({"family": args.family, "n_gpus": world, "prompt_tokens": args.prompt, "decode_tokens": args.decode,
-                          "prefill_ms": round(pre_ms, 2), "prefill_tok_s": round(args.prompt / pre_ms * 1e3, 1),
-                          "decode_ms_per_token": round(dec_ms / max(1, args.decode), 3),
-                          "decode_tok_s": round(args.decode / dec_ms * 1e3, 2), "weights_gb_per_rank": round(nbytes / 1e9, 2),
-                          "build_seconds": round(build_s, 1), "data": "synthetic random-init, expert pool %d" % args.expert_pool,
-                          "timing": "CUDA events, max over ranks, after a one-chunk warm-up request", **desc}), flush=True)
+    rec = run_family(args, rank, world, dev, args.steps, args.warmup)
+    if rec is not None:
+        print(json.dumps(rec), flush=True)
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()

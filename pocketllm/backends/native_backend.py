@@ -19,7 +19,12 @@ from ..protocol.chat import held_back_suffix, truncate_at_stop
 from ..protocol.prompt import TokenizerHandle
 from .base import BackendBase
 
-OP_STOP, OP_ALLOC, OP_FREE, OP_PREFILL, OP_DECODE, OP_SAMPLING = 0, 1, 2, 3, 4, 5
+OP_STOP, OP_ALLOC, OP_FREE, OP_PREFILL, OP_DECODE, OP_SAMPLING, OP_RECOVER = 0, 1, 2, 3, 4, 5, 6
+
+
+def _is_collective_timeout(exc: BaseException) -> bool:
+    # by name: this module must stay importable without torch / the kernel package
+    return type(exc).__name__ == "CollectiveTimeoutError"
 
 
 class NullChannel:
@@ -158,10 +163,38 @@ class NativeBackend(BackendBase):
                     # must use the same settings and the same random stream: the seed is fixed here
                     sp = _with_seed(sp)
                     ch.send(OP_SAMPLING, slot, *_encode_sampling(sp))
-                ch.send(OP_PREFILL, slot, chunk, prompt)
-                tok = rt.prefill_tokens(slot, prompt, chunk, sp)
-                t1 = time.perf_counter()
                 out: list[int] = []
+                recovered = False
+
+                def step(fn):
+                    """Run one prefill / decode; if a peer-memory collective timed out, re-synchronise the ranks on
+                    the library path and rebuild the sequence (prompt + tokens so far) there, once per request."""
+                    nonlocal slot, recovered
+                    try:
+                        return fn()
+                    except Exception as exc:
+                        if recovered or not _is_collective_timeout(exc) or not hasattr(rt, "recover"):
+                            raise
+                    recovered = True
+                    self._stats["collective_recoveries"] = self._stats.get("collective_recoveries", 0) + 1
+                    ch.send(OP_RECOVER)
+                    rt.recover()
+                    ch.send(OP_FREE, slot)
+                    rt.free(slot)
+                    ch.send(OP_ALLOC)
+                    slot = rt.allocate()
+                    if not sp.greedy:
+                        ch.send(OP_SAMPLING, slot, *_encode_sampling(sp))
+                    history = prompt + out
+                    ch.send(OP_PREFILL, slot, chunk, history)
+                    return rt.prefill_tokens(slot, history, chunk, sp)
+
+                def first():
+                    ch.send(OP_PREFILL, slot, chunk, prompt)
+                    return rt.prefill_tokens(slot, prompt, chunk, sp)
+
+                tok = step(first)
+                t1 = time.perf_counter()
                 text_done = ""
                 finish = "length"
                 while True:
@@ -182,8 +215,11 @@ class NativeBackend(BackendBase):
                     if len(out) >= max_new:
                         break
                     self._check_cancel(req.request_id)
-                    ch.send(OP_DECODE, slot, tok)
-                    tok = rt.decode_tokens([slot], [tok], sp)[0]
+                    def nxt(tok=tok):
+                        ch.send(OP_DECODE, slot, tok)
+                        return rt.decode_tokens([slot], [tok], sp)[0]
+
+                    tok = step(nxt)
                 t2 = time.perf_counter()
             finally:
                 ch.send(OP_FREE, slot)
@@ -277,11 +313,21 @@ class NativeBackend(BackendBase):
         self.prepare()
         rt, ch = self.runtime, self.channel
         slot_sp: dict[int, Any] = {}
+        # After a collective timed out on THIS rank it has already joined the group's recovery on its own; commands
+        # that rank 0 sent before it noticed the failure are stale and are dropped until its OP_RECOVER arrives.
+        skipping = False
         while True:
             op, *payload = ch.recv()
             try:
                 if op == OP_STOP:
                     return
+                if op == OP_RECOVER:
+                    if not skipping and hasattr(rt, "recover"):
+                        rt.recover()
+                    skipping = False
+                    continue
+                if skipping:
+                    continue
                 if op == OP_ALLOC:
                     rt.allocate()
                 elif op == OP_FREE:
@@ -300,6 +346,9 @@ class NativeBackend(BackendBase):
             except BackendUnavailableError:
                 raise
             except Exception as exc:  # keep the group alive; rank 0 sees the failure through its own call
+                if _is_collective_timeout(exc) and hasattr(rt, "recover"):
+                    rt.recover()
+                    skipping = True
                 import sys
                 print(f"[pocketllm worker rank {self.args.tensor_parallel_rank}] command {op} failed: {exc}",
                       file=sys.stderr, flush=True)

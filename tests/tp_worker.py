@@ -125,6 +125,33 @@ def main() -> None:
     assert ref.tolist() == tb, ("ranks disagree (sp)",)
     del rt
 
+    # a collective that times out (rank 0 calls it alone: nobody raises the flags it waits for), then the group's
+    # recovery: epochs re-agreed over NCCL, peer-memory path usable again, and the degraded (library) routing
+    late = tp.PeerComm(slot_elems=1 << 16, budget_ms=30.0)
+    v = torch.full((2048,), float(rank + 1), device=dev).bfloat16()
+    if rank == 0:
+        late.all_reduce(v.clone())
+        torch.cuda.synchronize()
+        try:
+            late.check()
+            raise AssertionError("expected a collective timeout on rank 0")
+        except tp.CollectiveTimeoutError:
+            pass
+    dist.barrier()
+    late.recover(degrade=False)
+    want = float(sum(range(1, world + 1)))
+    got = late.all_reduce(v.clone())
+    torch.cuda.synchronize()
+    late.check()
+    assert not late.degraded and torch.all(got.float() == want), ("all-reduce after recovery", got[:4])
+    late.recover(degrade=True)
+    calls0 = late.standalone_calls
+    got = late.all_reduce(v.clone())
+    torch.cuda.synchronize()
+    assert late.degraded and late.standalone_calls == calls0 and torch.all(got.float() == want)
+    assert late.sp_rows(1024 * world, 64) == 0
+    late.close()
+
     # expert-parallel combine fused with its collective (one-shot and two-shot) against combine + NCCL
     from deepseek_v4_2080ti_b200.ops import moe
     for t, k, h, rows in [(1, 4, 512, 4), (37, 4, 512, 80), (300, 8, 1024, 900)]:
