@@ -76,10 +76,15 @@ def run_moe_config(args) -> None:
     if args.config == 5 and args.pp == 1 and args.gpus >= 2 and os.environ.get("B200_BENCH_GLM_PP", "0") == "1":
         args.pp = d_pp
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "config": args.config, "unavailable":
-                          "the reference serves this family through its torch plane on real checkpoints only "
-                          "(hard-coded head counts / tensor inventories of the released models); no synthetic "
-                          "checkpoint of the benchmark shape loads there - see the record in BASELINE.md"}), flush=True)
+        why = {3: "the installed reference's GGUF path does not import: `python -m src.cli.generate_gguf` on a synthetic "
+                  "minimax-m2 GGUF fails in src/components/moe/registry.py:12 with ModuleNotFoundError: No module named "
+                  "'src.models.glm_dsa' (the reference's setup.py does not list that package, so pip does not install it)",
+               5: "the installed reference has no src.models.glm_dsa package (absent from the reference's setup.py package "
+                  "list), so `python -m src.cli.generate_glm` cannot be imported from baseline/_ref",
+               4: "the reference's DeepSeek-V4 is a different architecture from this configuration (single KV head of "
+                  "dim 512 + window + learned compressor, not MLA q_lora 1024 / kv_lora 512 with a top-2048 indexer): "
+                  "none of its engines can load a checkpoint of this shape"}[args.config]
+        print(json.dumps({"impl": "reference", "config": args.config, "unavailable": why}), flush=True)
         return
     rank, world, local = tp.init_distributed()
     torch.cuda.set_device(local)

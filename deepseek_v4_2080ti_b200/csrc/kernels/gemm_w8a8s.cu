@@ -25,9 +25,12 @@
 #include "per_device.h"
 #include <cuda_fp8.h>
 #include "../ptx/sm100.cuh"
+#include <string.h>
 #include "tma_host.h"
 #include "ops.h"
 #include "launch.h"
+#include "../comm/comm.h"
+#include "../comm/comm_device.cuh"
 
 namespace b200 {
 namespace w8s {
@@ -49,6 +52,12 @@ struct Params {
   const __nv_bfloat16* residual;
   int* tile_counters;
   int* status;
+  // Fused one-shot all-reduce (row-parallel projection of a decode step under tensor parallelism): the CTA that
+  // holds a finished 128-feature tile stores it as bf16 into its own slot and every peer's slot for source = this
+  // rank, raises the tile's flag on the peers, waits for theirs and writes sum over ranks (+ residual) to `out`.
+  int ar;
+  unsigned long long ar_budget_ns;
+  B200Comm comm;
 };
 
 template <int BN>
@@ -204,8 +213,10 @@ gemm_w8a8s_kernel(const __grid_constant__ CUtensorMap tmX, Params p) {
   } else {
     // ---------------------------------------------------------------- epilogue
     const int row = warp * 32 + lane;
-    const bool sync_mode = p.splits > 1;
+    const bool sync_mode = p.splits > 1 || p.ar;
     pdl_wait();   // everything this role reads (inv_c, residual) or writes belongs after the previous kernel
+    const uint32_t ar_epoch = p.ar ? p.comm.ctrl[0] + 1 : 0;   // after the wait: the previous kernel may have advanced it
+    const int ar_parity = ar_epoch & 1;
     uint32_t blk = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
       if (sync_mode) {
@@ -278,12 +289,16 @@ gemm_w8a8s_kernel(const __grid_constant__ CUtensorMap tmX, Params p) {
           const size_t off = (size_t)t * p.N + f;
           if (p.splits > 1) {
             p.partial[(size_t)split * p.T * p.N + off] = v;
+          } else if (p.ar) {
+            const __nv_bfloat16 bv = __float2bfloat16(v);
+            for (int r = 0; r < p.comm.world; ++r) data_slot(p.comm.data[r], ar_parity, p.comm.rank, p.comm.slot_elems)[off] = bv;
           } else {
             if (p.residual) v += __bfloat162float(p.residual[off]);
             p.out[off] = __float2bfloat16(v);
           }
         }
       }
+      bool tile_final = p.splits == 1;
       if (p.splits > 1) {
         // split-K fix-up by the CTA that arrives last at this tile (sums in split order: deterministic)
         __threadfence();
@@ -294,12 +309,46 @@ gemm_w8a8s_kernel(const __grid_constant__ CUtensorMap tmX, Params p) {
           if (prev == p.splits - 1) p.tile_counters[m_tile] = 0;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
+        tile_final = *fix_last != 0;
         if (*fix_last && f_ok) {
           __threadfence();
           for (int t = 0; t < p.T; ++t) {
             const size_t off = (size_t)t * p.N + f;
-            float a = p.residual ? __bfloat162float(p.residual[off]) : 0.f;
+            float a = (p.residual && !p.ar) ? __bfloat162float(p.residual[off]) : 0.f;
             for (int sp = 0; sp < p.splits; ++sp) a += __ldcg(p.partial + (size_t)sp * p.T * p.N + off);
+            if (p.ar) {
+              const __nv_bfloat16 bv = __float2bfloat16(a);
+              for (int r = 0; r < p.comm.world; ++r) data_slot(p.comm.data[r], ar_parity, p.comm.rank, p.comm.slot_elems)[off] = bv;
+            } else {
+              p.out[off] = __float2bfloat16(a);
+            }
+          }
+        }
+      }
+      if (p.ar && tile_final) {
+        // ---- the tile's all-reduce: flags out, flags in, sum in rank order (identical bits on every rank)
+        const B200Comm& cm = p.comm;
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int et = threadIdx.x;
+        if (et < cm.world && et != cm.rank) {
+          st_release_sys(flag_slot(cm.flags[et], ar_parity, cm.rank) + m_tile, ar_epoch);
+          // once any kernel has recorded an expired wait the step is lost: do not spend the budget again
+          const uint64_t budget = *reinterpret_cast<volatile int*>(p.status) == 0 ? p.ar_budget_ns : 1000;
+          if (!wait_flag_ge(flag_slot(cm.flags[cm.rank], ar_parity, et) + m_tile, ar_epoch, budget)) {
+            atomicExch(p.status, ERR_WAIT_PEER);
+            *abort_flag = 1;
+            *epi_abort = 1;
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*epi_abort) break;
+        if (f_ok) {
+          for (int t = 0; t < p.T; ++t) {
+            const size_t off = (size_t)t * p.N + f;
+            float a = p.residual ? __bfloat162float(p.residual[off]) : 0.f;
+            for (int r = 0; r < cm.world; ++r)
+              a += __bfloat162float(__ldcg(data_slot(cm.data[cm.rank], ar_parity, r, cm.slot_elems) + off));
             p.out[off] = __float2bfloat16(a);
           }
         }
@@ -318,6 +367,17 @@ gemm_w8a8s_kernel(const __grid_constant__ CUtensorMap tmX, Params p) {
   if (warp == 5) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (p.ar && threadIdx.x == 0) {
+    // the last CTA to leave publishes the new epoch (every epilogue read the old one before any CTA could leave)
+    __threadfence();
+    const uint32_t old = p.comm.ctrl[0];
+    const uint32_t left = atomicAdd(&p.comm.ctrl[1], 1u) + 1;
+    if (left == gridDim.x) {
+      p.comm.ctrl[1] = 0;
+      __threadfence();
+      atomicExch(&p.comm.ctrl[0], old + 1);
+    }
   }
 }
 
@@ -424,9 +484,36 @@ extern "C" int b200_act_split_e4m3(const void* x_bf16, int T, int K, int terms, 
 // Y = X W^T with pre-split activations (b200_act_split_e4m3 with the layout of b200_gemm_w8a8s_layout(T)).
 // W: FP8 tile-major packed weights (layout of b200_gemm_wdec, wfmt 1), scales fp32 [ceil(N/128), K/128].
 // splits > 1 needs `partial` (splits*T*N floats) and `tile_counters` (ceil(N/128) zeroed ints, left zeroed).
+static int gemm_w8a8s_launch(const void* W, const float* scales, const void* xq, const float* inv_c,
+                             void* out_bf16, const void* residual, int T, int N, int K, int splits,
+                             float* partial, int* tile_counters, const B200Comm* comm, unsigned long long budget_ns,
+                             int* status, cudaStream_t stream);
+
 extern "C" int b200_gemm_w8a8s(const void* W, const float* scales, const void* xq, const float* inv_c,
                                void* out_bf16, const void* residual, int T, int N, int K, int splits,
                                float* partial, int* tile_counters, int* status, cudaStream_t stream) {
+  return gemm_w8a8s_launch(W, scales, xq, inv_c, out_bf16, residual, T, N, K, splits, partial, tile_counters, nullptr, 0,
+                           status, stream);
+}
+
+// Row-parallel form: every rank calls it with its K-shard; all ranks end with out = sum over ranks (+ residual), the
+// one-shot all-reduce done tile by tile in the epilogue over peer memory.  T * N <= comm->slot_elems.
+extern "C" int b200_gemm_w8a8s_allreduce(const void* W, const float* scales, const void* xq, const float* inv_c,
+                                         void* out_bf16, const void* residual, int T, int N, int K, int splits,
+                                         float* partial, int* tile_counters, const B200Comm* comm,
+                                         unsigned long long budget_ns, int* status, cudaStream_t stream) {
+  if (!comm || comm->world <= 1)
+    return gemm_w8a8s_launch(W, scales, xq, inv_c, out_bf16, residual, T, N, K, splits, partial, tile_counters, nullptr,
+                             0, status, stream);
+  if ((unsigned long long)T * N > comm->slot_elems || (N + w8s::BM - 1) / w8s::BM > B200_FLAGS_PER_SLOT) return -ERR_BAD_ARG;
+  return gemm_w8a8s_launch(W, scales, xq, inv_c, out_bf16, residual, T, N, K, splits, partial, tile_counters, comm,
+                           budget_ns ? budget_ns : B200_WAIT_BUDGET_NS, status, stream);
+}
+
+static int gemm_w8a8s_launch(const void* W, const float* scales, const void* xq, const float* inv_c,
+                             void* out_bf16, const void* residual, int T, int N, int K, int splits,
+                             float* partial, int* tile_counters, const B200Comm* comm, unsigned long long budget_ns,
+                             int* status, cudaStream_t stream) {
   int terms = 0;
   const int BN = b200_gemm_w8a8s_layout(T, &terms);
   if (T <= 0 || BN == 0 || N <= 0 || K <= 0 || (K % 128) != 0 || splits < 1 || !out_bf16) return -ERR_BAD_ARG;
@@ -450,6 +537,10 @@ extern "C" int b200_gemm_w8a8s(const void* W, const float* scales, const void* x
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.tile_counters = tile_counters;
   p.status = status;
+  p.ar = comm ? 1 : 0;
+  p.ar_budget_ns = budget_ns;
+  memset(&p.comm, 0, sizeof(p.comm));
+  if (comm) p.comm = *comm;
   CUtensorMap tmX;
   if (!make_tmap_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, (uint64_t)T * terms, K, (uint64_t)K, BN, w8s::BKB,
                     CU_TENSOR_MAP_SWIZZLE_64B))

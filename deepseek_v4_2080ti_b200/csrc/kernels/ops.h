@@ -29,6 +29,8 @@ int b200_act_split_e4m3(const void* x_bf16, int T, int K, int terms, void* xq, f
 int b200_gemm_w8a8s(const void* W, const float* scales, const void* xq, const float* inv_c, void* out_bf16,
                     const void* residual, int T, int N, int K, int splits, float* partial, int* tile_counters,
                     int* status, cudaStream_t stream);
+// b200_gemm_w8a8s_allreduce (same arguments + the peer-memory communicator) is declared beside the communicator in
+// gemm_w8a8s.cu: this header stays free of the communicator's types.
 
 // ---- fused decode-step kernels (decode_fused.cu)
 int b200_gdn_decode_fused(const void* proj, int ldp, const void* x, int hidden, const void* w_ab, const float* a_log,

@@ -195,6 +195,15 @@ class LayerWeights:
     k_norm: torch.Tensor | None = None
 
 
+@dataclass
+class MtpWeights:
+    norm_embed: torch.Tensor
+    norm_hidden: torch.Tensor
+    norm_out: torch.Tensor
+    fc: PackedLinear              # [H, 2H], replicated
+    layer: LayerWeights           # one full-attention decoder layer
+
+
 class QwenHybridWeights:
     """Device-resident, TP-sharded, kernel-ready weights built from (name, tensor) pairs."""
 
@@ -216,6 +225,7 @@ class QwenHybridWeights:
         missing = [i for i, l in enumerate(self.layers) if l is None]
         if missing or self.embed is None or self.lm_head is None or self.final_norm is None:
             raise ValueError(f"checkpoint incomplete: layers {missing[:4]}... pending {list(self._pending)[:6]}")
+        self.mtp = self._build_mtp()
 
     # -- helpers
     def _dev(self, t):
@@ -284,8 +294,14 @@ class QwenHybridWeights:
         i = int(name.split(".")[3])
         if self.layers[i] is not None:
             return
-        p = f"model.language_model.layers.{i}."
-        lt = cfg.layer_types[i]
+        lw = self._build_layer(f"model.language_model.layers.{i}.", cfg.layer_types[i])
+        if lw is not None:
+            self.layers[i] = lw
+
+    def _build_layer(self, p: str, lt: str) -> "LayerWeights | None":
+        """Kernel-ready, TP-sharded weights of the decoder layer whose tensors start with ``p``, once all of them
+        have arrived (None before that)."""
+        cfg, P = self.cfg, self._pending
         need = [p + "input_layernorm.weight", p + "post_attention_layernorm.weight"]
         nvfp4_mlp = (p + "mlp.gate_proj.weight_packed") in P or (p + "mlp.gate_proj.weight_scale") in P or \
             (p + "mlp.gate_proj.weight_global_scale") in P
@@ -306,7 +322,7 @@ class QwenHybridWeights:
                 need += [a + m + ".weight", a + m + ".weight_scale_inv"]
             need += [a + "q_norm.weight", a + "k_norm.weight"]
         if not all(n in P for n in need):
-            return
+            return None
         W, R = self.world, self.rank
         in_ln, post_ln = self._dev(P.pop(need[0])), self._dev(P.pop(need[1]))
         if nvfp4_mlp:
@@ -343,22 +359,48 @@ class QwenHybridWeights:
             wa = _shard_rows(P.pop(a + "in_proj_a.weight"), R, W)
             wb = _shard_rows(P.pop(a + "in_proj_b.weight"), R, W)
             ab = PackedLinear.from_bf16(self._dev(torch.cat([wa, wb], 0)))
-            self.layers[i] = LayerWeights(
+            assert hv * W == cfg.linear_num_value_heads
+            return LayerWeights(
                 "linear", in_ln, post_ln, proj, out, gate_up, down, ab=ab,
                 conv_w=self._dev(torch.cat(conv_parts, 0)).contiguous(),
                 a_log=self._dev(_shard_rows(P.pop(a + "A_log"), R, W)).float().contiguous(),
                 dt_bias=self._dev(_shard_rows(P.pop(a + "dt_bias"), R, W)).float().contiguous(),
                 gdn_norm=self._dev(P.pop(a + "norm.weight")))
-            assert hv * W == cfg.linear_num_value_heads
         else:
             a = p + "self_attn."
             pieces = [self._rows_fp8(*self._fp8(a + "q_proj")), self._rows_fp8(*self._fp8(a + "k_proj")),
                       self._rows_fp8(*self._fp8(a + "v_proj"))]
             proj = self._col_fp8(pieces)
             out = self._cols_fp8(*self._fp8(a + "o_proj"))
-            self.layers[i] = LayerWeights("full", in_ln, post_ln, proj, out, gate_up, down,
-                                          q_norm=self._dev(P.pop(a + "q_norm.weight")),
-                                          k_norm=self._dev(P.pop(a + "k_norm.weight")))
+            return LayerWeights("full", in_ln, post_ln, proj, out, gate_up, down,
+                                q_norm=self._dev(P.pop(a + "q_norm.weight")),
+                                k_norm=self._dev(P.pop(a + "k_norm.weight")))
+
+    def _build_mtp(self) -> "MtpWeights | None":
+        """The multi-token-prediction head, when the checkpoint carries one (``mtp.*``: two input norms, ``mtp.fc``
+        [H, 2H], one full-attention decoder layer, ``mtp.norm``; embedding and output head are the trunk's).
+        ``mtp.fc`` and the norms are replicated, the layer is sharded like the trunk's (cpp_engine/core/
+        qwen_weight_map.cpp maps the same names; a checkpoint with some but not all of them is refused)."""
+        P = self._pending
+        if not any(k.startswith("mtp.") for k in P):
+            return None
+        # a head stored in bf16 is quantised to the trunk's FP8 block-128 format here, so its layer runs through the
+        # same kernels (drafts only steer which tokens get verified; the verified output does not depend on them)
+        for k in [k for k in P if k.startswith("mtp.layers.0.") and k.endswith("_proj.weight")]:
+            if P[k].dtype != torch.float8_e4m3fn and (k + "_scale_inv") not in P:
+                q, sc = fp8fmt.quantize_block128(P[k].to(self.device, torch.float32))
+                P[k], P[k + "_scale_inv"] = q, sc
+        layer = self._build_layer("mtp.layers.0.", "full_attention")
+        names = ["mtp.pre_fc_norm_embedding.weight", "mtp.pre_fc_norm_hidden.weight", "mtp.norm.weight", "mtp.fc.weight"]
+        if layer is None or not all(n in P for n in names):
+            raise ValueError("checkpoint carries an incomplete multi-token-prediction head: "
+                             f"{sorted(k for k in P if k.startswith('mtp.'))[:6]}")
+        fc_w = P.pop("mtp.fc.weight")
+        if fc_w.dtype == torch.float8_e4m3fn:
+            fc = PackedLinear.from_fp8(self._dev(fc_w).contiguous(), self._dev(P.pop("mtp.fc.weight_scale_inv")).contiguous())
+        else:
+            fc = PackedLinear.from_bf16(self._dev(fc_w))
+        return MtpWeights(self._dev(P.pop(names[0])), self._dev(P.pop(names[1])), self._dev(P.pop(names[2])), fc, layer)
 
     def nbytes(self) -> int:
         n = self.embed.numel() * 2 + self.lm_head.nbytes()
@@ -424,6 +466,11 @@ class QwenHybridRuntime:
         self.lin_layers = [i for i, t in enumerate(cfg.layer_types) if t == "linear_attention"]
         dev = self.device
         nf, nl = len(self.full_layers), len(self.lin_layers)
+        self.mtp = getattr(weights, "mtp", None)
+        if self.mtp is not None:
+            nf += 1            # the head's attention layer keeps its keys/values as one more cache layer (index nf - 1)
+        self.keep_hidden = False   # a speculator sets it: prefill then keeps the final-normed hidden of every row
+        self.hidden_rows = None
         # block 0 is a scratch block: padded rows of a decode batch write their K/V there
         self.kv8 = None
         if self.kv_cache_dtype != "bf16":
@@ -561,6 +608,14 @@ class QwenHybridRuntime:
             return fused(x, w)
         return self.comm.all_reduce(gemm.linear(x, w))
 
+    def _stream_row_parallel(self, x: torch.Tensor | None, w: PackedLinear, xsplit=None) -> torch.Tensor:
+        """Row-parallel projection of a decode step (T <= 32): with a peer-memory communicator the all-reduce is done
+        in the epilogue of the weight-streaming GEMM, otherwise GEMM then all-reduce."""
+        fused = getattr(self.comm, "stream_allreduce", None)
+        if fused is not None and self.comm.world > 1:
+            return fused(x, w, xsplit=xsplit)
+        return self.comm.all_reduce(gemm.linear_stream(x, w, xsplit=xsplit))
+
     def _mlp(self, lw: LayerWeights, h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
         if self._sp:
@@ -656,7 +711,10 @@ class QwenHybridRuntime:
             else:
                 d_attn = self._full_attn(i, lw, x, t, positions, kv_slots, meta)
             delta = self._mlp(lw, h, d_attn)
-        if logits_rows is not None:
+        if logits_rows is not None and self.keep_hidden:
+            self.hidden_rows = basic.add_rmsnorm(h, delta, w.final_norm, cfg.rms_norm_eps, True)
+            x = self.hidden_rows.index_select(0, logits_rows)
+        elif logits_rows is not None:
             basic.add_(h, delta)
             hs = h.index_select(0, logits_rows)
             x = basic.rmsnorm(hs, w.final_norm, cfg.rms_norm_eps, True)
@@ -693,6 +751,8 @@ class QwenHybridRuntime:
                 self._mlp(lw, h, None)
             x = comm.reduce_norm_gather(h, w.final_norm, eps, True)
             comm.wait_gather(rows)
+            if self.keep_hidden:
+                self.hidden_rows = x.clone()       # the gathered buffer is overwritten by the next chunk
         finally:
             self._sp = False
         return gemm.linear(x.index_select(0, logits_rows), w.lm_head, out_f32=True)
@@ -714,13 +774,13 @@ class QwenHybridRuntime:
                 idx = self.lin_layers.index(i)
                 y = gdn.decode_fused(proj, x, lw.ab.weight, lw.a_log, lw.dt_bias, lw.conv_w, self.tails[:, idx],
                                      self.states[:, idx], slots_t, lw.gdn_norm, self.hv_lin, self.hk_lin, eps)
-                d_attn = self.comm.all_reduce(gemm.linear_stream(y, lw.out))
+                d_attn = self._stream_row_parallel(y, lw.out)
             else:
                 o = self._attend(self.full_layers.index(i), lw, proj, t, positions, kv_slots, meta, eps)
-                d_attn = self.comm.all_reduce(gemm.linear_stream(o.view(t, self.hq * 128), lw.out))
+                d_attn = self._stream_row_parallel(o.view(t, self.hq * 128), lw.out)
             _, xs2 = basic.rmsnorm_split(h, d_attn, lw.post_ln, terms, eps, True, want_bf16=False)
             gu = gemm.linear_stream(None, lw.gate_up, xsplit=xs2)
-            delta = self.comm.all_reduce(gemm.linear_stream(None, lw.down, xsplit=basic.silu_mul_split(gu, terms)))
+            delta = self._stream_row_parallel(None, lw.down, basic.silu_mul_split(gu, terms))
         x = basic.add_rmsnorm(h, delta, w.final_norm, eps, True)
         return gemm.linear(x, w.lm_head, out_f32=True)
 

@@ -183,9 +183,11 @@ def split_activations(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
 
 def linear_stream(x: torch.Tensor, w: PackedLinear, residual: torch.Tensor | None = None,
                   out: torch.Tensor | None = None, splits: int | None = None,
-                  xsplit: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
+                  xsplit: tuple[torch.Tensor, torch.Tensor] | None = None, comm=None) -> torch.Tensor:
     """Small-batch (T <= 32) FP8 projection: weights go from HBM to the tensor core untouched, the
-    activations are split into E4M3 terms instead.  ``xsplit`` reuses a previous ``split_activations(x)``."""
+    activations are split into E4M3 terms instead.  ``xsplit`` reuses a previous ``split_activations(x)``.
+    ``comm`` (a ``parallel.tp.PeerComm``): row-parallel form, the one-shot all-reduce over the ranks happens in the
+    epilogue (sum over ranks + residual in ``out`` on every rank)."""
     xq, inv_c = xsplit if xsplit is not None else split_activations(x)
     t, k = inv_c.numel(), xq.shape[1]        # x itself may be None when the split is supplied
     n = w.n
@@ -202,6 +204,14 @@ def linear_stream(x: torch.Tensor, w: PackedLinear, residual: torch.Tensor | Non
     if (n + 127) // 128 > MAX_TILE_COUNTERS:
         splits = 1
     ws, counters = _workspace(splits * t * n, dev) if splits > 1 else (None, None)
+    if comm is not None:
+        rc = _lib.lib().b200_gemm_w8a8s_allreduce(_lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(xq), _lib.ptr(inv_c),
+                                                  _lib.ptr(out), _lib.ptr(residual), t, n, k, splits, _lib.ptr(ws),
+                                                  _lib.ptr(counters), comm._cref(), ctypes.c_ulonglong(comm.budget_ns),
+                                                  _lib.ptr(_lib.status_word(dev)), _lib.stream())
+        _lib.check(rc, "gemm_w8a8s_allreduce")
+        comm.fused_calls += 1
+        return out
     rc = _lib.lib().b200_gemm_w8a8s(_lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(xq), _lib.ptr(inv_c),
                                     _lib.ptr(out), _lib.ptr(residual), t, n, k, splits, _lib.ptr(ws),
                                     _lib.ptr(counters), _lib.ptr(_lib.status_word(dev)), _lib.stream())

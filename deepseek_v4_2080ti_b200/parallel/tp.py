@@ -294,6 +294,18 @@ class PeerComm(TPComm):
         self.fused_calls += 1
         return out
 
+    def stream_allreduce(self, x: torch.Tensor | None, w, xsplit=None, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """Row-parallel decode projection (T <= 32, FP8 weights) with the one-shot all-reduce in the epilogue of the
+        weight-streaming GEMM (csrc/kernels/gemm_w8a8s.cu): one launch instead of GEMM + all-reduce kernel."""
+        from ..ops import gemm
+
+        t = (xsplit[1].numel() if xsplit is not None else x.shape[0])
+        if self.world == 1 or self.degraded or t * w.n > self.slot_elems:
+            y = gemm.linear_stream(x, w, xsplit=xsplit)
+            y = self.all_reduce(y)
+            return y if residual is None else y.add_(residual)
+        return gemm.linear_stream(x, w, residual=residual, xsplit=xsplit, comm=self)
+
     # ---- sequence-parallel residual stream (csrc/comm/sp_comm.cu, gemm_wdec_kernel.cuh ar_mode 3 / ag_wait)
     SP_FLAG_ROWS = 8
 

@@ -199,6 +199,48 @@ class RuntimeAdapter:
                 "slots_free": len(self.rt.free_slots)}
 
 
+class SpecRuntimeAdapter(RuntimeAdapter):
+    """Greedy speculative decoding behind the same surface: a decode call hands out the next token of the last
+    verified block and runs a new draft / verify round only when that block is used up.  Worker ranks mirror the same
+    calls, so their rounds stay in step with rank 0's."""
+    supports_sampling = False
+    supports_prefix_cache = False
+
+    def __init__(self, rt, spec, max_context: int, eos_token_ids=()):
+        super().__init__(rt, max_context, eos_token_ids)
+        self.spec = spec
+        self.speculative_methods = (spec.method,)
+
+    def allocate(self) -> int:
+        return self.spec.allocate()
+
+    def free(self, slot: int) -> None:
+        self.spec.free(slot)
+
+    def prefill_tokens(self, slot: int, prompt: list[int], chunk: int, sp) -> int:
+        ids = torch.tensor(prompt, dtype=torch.int32).pin_memory().to(self.rt.device, non_blocking=True)
+        tok = self.spec.prefill(slot, ids, chunk, host_tokens=prompt)
+        self.spec.seqs[slot].queue = []
+        self.last_cached_tokens = 0
+        self._check_collectives()
+        return tok
+
+    def decode_tokens(self, slots: list[int], toks: list[int], sp) -> list[int]:
+        out = []
+        for s in slots:
+            q = self.spec.seqs[s].queue
+            if not q:
+                q.extend(self.spec.step(s))
+                self._check_collectives()
+            out.append(q.pop(0))
+        return out
+
+    def stats(self) -> dict:
+        c = self.spec.stats
+        return {"spec_rounds": c.rounds, "spec_drafted": c.drafted, "spec_accepted": c.accepted,
+                "spec_accept_rate": round(c.accept_rate, 4), "spec_tokens_per_pass": round(c.tokens_per_pass, 3)}
+
+
 class CppRuntimeAdapter:
     """The same surface over the native C++ engine (``pocketllm_engine_cpp.QwenEngine``): safetensors checkpoints,
     one GPU, greedy decoding; batches go through the C++ continuous-batching scheduler."""
@@ -337,11 +379,15 @@ def _device(args) -> torch.device:
 def load_runtime(args):
     """Returns (adapter, chat-template family or None, command channel)."""
     world, rank = args.tensor_parallel_size, args.tensor_parallel_rank
-    if getattr(args, "speculative_method", None):
-        # refuse rather than decode without it: the hybrid runtime has no draft / verify / state-rollback path
+    spec_method = getattr(args, "speculative_method", None)
+    if spec_method and spec_method not in ("mtp", "ngram"):
+        # refuse rather than decode without it: the learned external drafter networks are not built
         from pocketllm.api.errors import ConfigurationError
-        raise ConfigurationError(f"speculative_method={args.speculative_method!r} is not implemented for the Qwen-style "
-                                 "hybrid runtime (multi-token prediction exists for the MLA family only)")
+        raise ConfigurationError(f"speculative_method={spec_method!r} is not implemented (available: 'mtp' with a "
+                                 "checkpoint that carries the head, 'ngram' prompt lookup)")
+    if spec_method and (_is_gguf(args.model) or getattr(args, "backend", "auto") == "cpp"):
+        from pocketllm.api.errors import ConfigurationError
+        raise ConfigurationError("speculative_method is served by the Qwen-style hybrid runtime only")
     dev = _device(args)
     torch.cuda.set_device(dev)
     comm = None
@@ -400,7 +446,8 @@ def load_runtime(args):
         state = safetensors_io.read_checkpoint(args.checkpoint_dir)
     weights = qh.QwenHybridWeights(cfg, state, dev, rank, world)
     comm = make_comm(cfg.hidden_size)
-    rt = qh.QwenHybridRuntime(cfg, weights, max_slots=slots, max_context=max_ctx, comm=comm,
+    spec_k = int(getattr(args, "speculative_tokens", 1) or 1) if spec_method else 0
+    rt = qh.QwenHybridRuntime(cfg, weights, max_slots=slots, max_context=max_ctx + (spec_k + 1 if spec_k else 0), comm=comm,
                               attention_window=int(getattr(args, "attention_window", 0) or 0),
                               attention_sink_tokens=int(getattr(args, "attention_sink_tokens", 0) or 0),
                               kv_cache_dtype=getattr(args, "kv_cache_dtype", "auto") or "auto")
@@ -409,4 +456,15 @@ def load_runtime(args):
         # (~100 MB at the 27B shape), and chunks of 2048 keep the prefill GEMMs at full efficiency
         rt.enable_prefix_cache(interval=2048, max_entries=4)
     from pocketllm.backends.native_backend import NullChannel
+    if spec_method:
+        if getattr(args, "enable_prefix_caching", False):
+            from pocketllm.api.errors import ConfigurationError
+            raise ConfigurationError("speculative decoding and prefix caching cannot be combined")
+        from ..models.qwen_spec import QwenSpeculator
+        try:
+            spec = QwenSpeculator(rt, k=spec_k, method=spec_method)
+        except ValueError as exc:
+            from pocketllm.api.errors import ConfigurationError
+            raise ConfigurationError(str(exc)) from exc
+        return SpecRuntimeAdapter(rt, spec, max_ctx), None, channel or NullChannel()
     return RuntimeAdapter(rt, max_ctx), None, channel or NullChannel()

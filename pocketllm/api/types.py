@@ -15,7 +15,7 @@ from .errors import ConfigurationError
 _TRUE = {"1", "true", "yes", "on"}
 _BACKENDS = {"auto", "b200", "torch", "cpp"}       # "torch" / "cpp" are accepted aliases of the single native backend
 _KV_DTYPES = {"auto", "bf16", "fp16", "fp8", "turboquant_k8v4", "int8_per_token_head"}
-_SPEC = {None, "mtp", "dspark", "dflash2"}
+_SPEC = {None, "mtp", "ngram", "dspark", "dflash2"}
 
 
 def _env(name: str, default, cast):
@@ -62,7 +62,7 @@ class EngineArgs:
     enable_prefix_caching: bool = True
     attention_window: int = 0
     attention_sink_tokens: int = 0
-    speculative_method: str | None = None  # mtp | dspark | dflash2
+    speculative_method: str | None = None  # mtp | ngram (prompt lookup) | dspark | dflash2
     speculative_tokens: int = 1
     max_batch_size: int = 1
     backend_options: dict[str, Any] = field(default_factory=dict)

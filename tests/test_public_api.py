@@ -234,8 +234,11 @@ def test_worker_loop_mirrors_commands_and_survives_errors():
 def test_loader_refuses_an_unimplemented_speculative_method_before_touching_a_device():
     from deepseek_v4_2080ti_b200.runtime import loader
     from pocketllm.api.errors import ConfigurationError
-    args = EngineArgs(model="synthetic:qwen-tiny", speculative_method="mtp")
+    args = EngineArgs(model="synthetic:qwen-tiny", speculative_method="dspark")
     with pytest.raises(ConfigurationError, match="speculative_method"):
+        loader.load_runtime(args)
+    args = EngineArgs(model="/nonexistent/model.gguf", speculative_method="mtp")
+    with pytest.raises(ConfigurationError, match="hybrid runtime"):
         loader.load_runtime(args)
 
 

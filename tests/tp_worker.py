@@ -75,6 +75,33 @@ def main() -> None:
             dist.broadcast(ref, 0)
             assert torch.equal(ref, got), ("fused all-reduce not identical across ranks", two_shot, t, n)
 
+    # decode-size row-parallel projection: the weight-streaming GEMM with the one-shot all-reduce in its epilogue
+    for t, n, kfull in [(1, 256, 1024), (1, 5120, 2048 * world), (8, 640, 1024), (32, 1024, 512 * world)]:
+        torch.manual_seed(9)
+        w = torch.randn(n, kfull, device=dev) * 0.05
+        x = torch.randn(t, kfull, device=dev).bfloat16()
+        r = torch.randn(t, n, device=dev).bfloat16()
+        ks = kfull // world
+        if ks % 128:
+            continue
+        q, s = fp8fmt.quantize_block128(w[:, rank * ks:(rank + 1) * ks].contiguous())
+        pl = gemm.PackedLinear.from_fp8(q, s)
+        xs = x[:, rank * ks:(rank + 1) * ks].contiguous()
+        part = gemm.linear_stream(xs, pl).float()
+        want = part.clone()
+        dist.all_reduce(want)
+        want += r.float()
+        got = comm.stream_allreduce(xs, pl, residual=r).clone()
+        got2 = comm.stream_allreduce(xs, pl, residual=r).clone()
+        torch.cuda.synchronize()
+        comm.check()
+        err = (got.float() - want).abs().max() / want.abs().max()
+        assert err < 2e-2, ("stream_allreduce", t, n, kfull, err.item())
+        assert torch.equal(got, got2)
+        ref = got.clone()
+        dist.broadcast(ref, 0)
+        assert torch.equal(ref, got), ("fused decode all-reduce not identical across ranks", t, n)
+
     # tensor-parallel model == single-rank model (greedy tokens)
     cfg = qh.QwenHybridConfig.tiny(layers=4)
     cfg = qh.QwenHybridConfig(vocab_size=512, hidden_size=256, intermediate_size=256 * world, num_hidden_layers=4,
