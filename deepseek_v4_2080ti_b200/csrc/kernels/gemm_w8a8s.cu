@@ -82,7 +82,9 @@ __device__ __forceinline__ uint64_t desc_sw64(const void* smem_tile) {
   return d;
 }
 
-template <int BN, int TERMS>
+// AR: the epilogue carries the one-shot all-reduce (instantiated for the narrow decode tiles only, so that the plain
+// instances keep the code they had without it).
+template <int BN, int TERMS, bool AR = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_w8a8s_kernel(const __grid_constant__ CUtensorMap tmX, Params p) {
   using L = Smem<BN>;
@@ -213,9 +215,9 @@ gemm_w8a8s_kernel(const __grid_constant__ CUtensorMap tmX, Params p) {
   } else {
     // ---------------------------------------------------------------- epilogue
     const int row = warp * 32 + lane;
-    const bool sync_mode = p.splits > 1 || p.ar;
+    const bool sync_mode = p.splits > 1 || AR;
     pdl_wait();   // everything this role reads (inv_c, residual) or writes belongs after the previous kernel
-    const uint32_t ar_epoch = p.ar ? p.comm.ctrl[0] + 1 : 0;   // after the wait: the previous kernel may have advanced it
+    const uint32_t ar_epoch = AR ? p.comm.ctrl[0] + 1 : 0;   // after the wait: the previous kernel may have advanced it
     const int ar_parity = ar_epoch & 1;
     uint32_t blk = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
@@ -289,7 +291,7 @@ gemm_w8a8s_kernel(const __grid_constant__ CUtensorMap tmX, Params p) {
           const size_t off = (size_t)t * p.N + f;
           if (p.splits > 1) {
             p.partial[(size_t)split * p.T * p.N + off] = v;
-          } else if (p.ar) {
+          } else if (AR) {
             const __nv_bfloat16 bv = __float2bfloat16(v);
             for (int r = 0; r < p.comm.world; ++r) data_slot(p.comm.data[r], ar_parity, p.comm.rank, p.comm.slot_elems)[off] = bv;
           } else {
@@ -314,9 +316,9 @@ gemm_w8a8s_kernel(const __grid_constant__ CUtensorMap tmX, Params p) {
           __threadfence();
           for (int t = 0; t < p.T; ++t) {
             const size_t off = (size_t)t * p.N + f;
-            float a = (p.residual && !p.ar) ? __bfloat162float(p.residual[off]) : 0.f;
+            float a = (p.residual && !AR) ? __bfloat162float(p.residual[off]) : 0.f;
             for (int sp = 0; sp < p.splits; ++sp) a += __ldcg(p.partial + (size_t)sp * p.T * p.N + off);
-            if (p.ar) {
+            if (AR) {
               const __nv_bfloat16 bv = __float2bfloat16(a);
               for (int r = 0; r < p.comm.world; ++r) data_slot(p.comm.data[r], ar_parity, p.comm.rank, p.comm.slot_elems)[off] = bv;
             } else {
@@ -325,7 +327,7 @@ gemm_w8a8s_kernel(const __grid_constant__ CUtensorMap tmX, Params p) {
           }
         }
       }
-      if (p.ar && tile_final) {
+      if (AR && tile_final) {
         // ---- the tile's all-reduce: flags out, flags in, sum in rank order (identical bits on every rank)
         const B200Comm& cm = p.comm;
         __threadfence_system();
@@ -368,7 +370,7 @@ gemm_w8a8s_kernel(const __grid_constant__ CUtensorMap tmX, Params p) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
-  if (p.ar && threadIdx.x == 0) {
+  if (AR && threadIdx.x == 0) {
     // the last CTA to leave publishes the new epoch (every epilogue read the old one before any CTA could leave)
     __threadfence();
     const uint32_t old = p.comm.ctrl[0];
@@ -428,13 +430,13 @@ act_split_e4m3_kernel(const __nv_bfloat16* __restrict__ x, int K, uint8_t* __res
   }
 }
 
-template <int BN, int TERMS>
+template <int BN, int TERMS, bool AR = false>
 static int launch(const CUtensorMap& tmX, const Params& p, cudaStream_t stream) {
   using L = Smem<BN>;
   static b200::PerDeviceOnce once_;
   bool& configured = once_.slot();
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_w8a8s_kernel<BN, TERMS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_w8a8s_kernel<BN, TERMS, AR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          L::TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
@@ -452,7 +454,7 @@ static int launch(const CUtensorMap& tmX, const Params& p, cudaStream_t stream) 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return (int)cudaLaunchKernelEx(&cfg, gemm_w8a8s_kernel<BN, TERMS>, tmX, p);
+  return (int)cudaLaunchKernelEx(&cfg, gemm_w8a8s_kernel<BN, TERMS, AR>, tmX, p);
 }
 
 }  // namespace w8s
@@ -545,6 +547,10 @@ static int gemm_w8a8s_launch(const void* W, const float* scales, const void* xq,
   if (!make_tmap_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, (uint64_t)T * terms, K, (uint64_t)K, BN, w8s::BKB,
                     CU_TENSOR_MAP_SWIZZLE_64B))
     return -ERR_BAD_ARG;
+  if (p.ar) {
+    if (BN != 16) return -ERR_BAD_ARG;       // the fused all-reduce exists for up to 8 tokens
+    return terms == 3 ? w8s::launch<16, 3, true>(tmX, p, stream) : w8s::launch<16, 2, true>(tmX, p, stream);
+  }
   if (BN == 16 && terms == 3) return w8s::launch<16, 3>(tmX, p, stream);
   if (BN == 16) return w8s::launch<16, 2>(tmX, p, stream);
   if (BN == 32) return w8s::launch<32, 2>(tmX, p, stream);

@@ -1,5 +1,6 @@
 // Entry points of the weight-decoding GEMM for bf16, FP8 block-128 and FP4 weights (kernel: gemm_wdec_kernel.cuh).
 #include "gemm_wdec_kernel.cuh"
+#include "gemm_2cta.h"
 
 using namespace b200;
 
@@ -60,6 +61,18 @@ static int gemm_wdec_launch(int wfmt, const void* W, const float* scales, const 
                             int* tile_counters, int* status, cudaStream_t stream, const FusedOpts* fo) {
   if (T <= 0 || N <= 0 || K <= 0 || (K % 16) != 0 || splits < 1) return -ERR_BAD_ARG;
   const int BN = (fo && fo->bn) ? fo->bn : b200_gemm_pick_bn(T);
+  {
+    // prefill-sized bf16 problems that tile evenly go to the CTA-pair kernel (256 x 256 tiles, gemm_bf16_2cta.cu)
+    const int mode = fo ? fo->ar_mode : 0;
+    const bool sp_ok = !fo || !fo->comm || (!fo->sp_rows && !fo->ag_wait) || (fo->sp_rows % 256 == 0);
+    if (wfmt == WF_BF16 && BN == 256 && splits == 1 && !residual && !out_f32 && (mode == 0 || mode == 3) &&
+        (out_bf16 || mode == 3) && sp_ok && b200_gemm_2cta_supported(T, N, K)) {
+      // the rotation was computed in units of this launcher's token tile, which is also 256 here
+      return b200_gemm_bf16_2cta(W, X, out_bf16, T, N, K, mode, fo ? fo->comm : nullptr, fo ? fo->sp_rows : 0,
+                                 fo ? fo->n_rot : 0, fo ? fo->ag_wait : 0, fo ? fo->ag_flag_rows : 0,
+                                 fo ? fo->budget_ns : 0, status, stream);
+    }
+  }
   GemmParams p;
   p.T = T; p.N = N; p.K = K;
   p.m_tiles = (N + BM - 1) / BM;
@@ -269,7 +282,9 @@ extern "C" int b200_gemm_wdec_rs(int wfmt, const void* W, const float* scales, c
   fo.sp_rows = sp_rows;
   fo.bn = bn;
   fo.n_rot = ((comm->rank + 1) % comm->world) * (sp_rows / bn);   // start with the next rank's shard, own shard last
-  if (bn_out) *bn_out = bn;
+  // the CTA-pair kernel (taken by the launcher for evenly tiling bf16 problems) raises its flags per 128-row block
+  const bool pair = wfmt == WF_BF16 && bn == 256 && b200_gemm_2cta_supported(T, N, K);
+  if (bn_out) *bn_out = pair ? 128 : bn;
   return gemm_wdec_launch(wfmt, W, scales, X, nullptr, nullptr, nullptr, T, N, K, 1, nullptr, status, stream, &fo);
 }
 

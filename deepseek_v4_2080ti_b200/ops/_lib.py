@@ -51,6 +51,8 @@ def lib() -> ctypes.CDLL:
             if not _LIB_PATH.exists():
                 raise KernelError(f"kernel library not built: {_LIB_PATH} (run python -m deepseek_v4_2080ti_b200.build)")
         _lib = ctypes.CDLL(str(_LIB_PATH))
+        if os.environ.get("B200_GEMM_2CTA", "1") == "0":     # A/B switch: prefill GEMMs on the one-CTA kernel only
+            _lib.b200_gemm_2cta_enable(0)
     return _lib
 
 
