@@ -130,7 +130,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
   uint64_t* acc_empty = bars + 2 * S + 2;  // [2] leader: both epilogues have drained the accumulator (8 warp arrives)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* epi_count = const_cast<int*>(abort_flag) + 1;   // epilogue warps that have stored their part of the current tile
+  // epilogue warps that have stored their part of a tile, one counter per tile_i & 3: the four warps run up to two
+  // tiles apart (the accumulator is double-buffered), so a single counter would mix arrivals of different tiles
+  int* epi_count = const_cast<int*>(abort_flag) + 1;   // [4]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -147,7 +149,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
       mbar_init(&acc_empty[b], 8);
     }
     *abort_flag = 0;
-    *epi_count = 0;
+    for (int i = 0; i < 4; ++i) epi_count[i] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 5) {
@@ -164,6 +166,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t ar_epoch = p.mode == 3 ? p.comm.ctrl[0] + 1 : 0;
+  // once any kernel has recorded an expired wait the step is lost: later kernels give up quickly instead of spending
+  // the full budget at every barrier
+  const uint64_t wait_ns = *reinterpret_cast<volatile int*>(p.status) == 0 ? p.budget_ns : 2000000ull;
 
   const int total = p.m2_tiles * p.n_tiles;
   // Tile order: bands of up to 16 feature tiles; inside a band the feature tile moves fastest, then the token tile.
@@ -184,7 +189,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
   if (warp == 4) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
     const uint32_t ag_epoch = p.ag_wait ? p.comm.ctrl[0] : 0;
-    const uint64_t ag_budget = (p.ag_wait && *reinterpret_cast<volatile int*>(p.status) == 0) ? p.budget_ns : 1000;
+    const uint64_t ag_budget = wait_ns;
     uint32_t it = 0;
     for (int w = pair; w < total; w += npairs) {
       int stop = (lane == 0) ? *abort_flag : 0;
@@ -216,7 +221,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         for (int kb = 0; kb < p.kb_total; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          if (!mbar_wait(&empty[s], ph ^ 1)) {
+          if (!mbar_wait(&empty[s], ph ^ 1, wait_ns)) {
             atomicExch(p.status, ERR_WAIT_STAGE);
             *abort_flag = 1;
             failed = 1;
@@ -234,7 +239,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     // tail: every commit aimed at this CTA's `empty` barriers must have landed before the CTA may exit
     if (lane == 0 && !*abort_flag) {
       const uint32_t done = it;
-      for (uint32_t j = (done > (uint32_t)S ? done - S : 0); j < done; ++j) mbar_wait(&empty[j % S], (j / S) & 1);
+      for (uint32_t j = (done > (uint32_t)S ? done - S : 0); j < done; ++j) mbar_wait(&empty[j % S], (j / S) & 1, wait_ns);
     }
   } else if (warp == 5) {
     // -------------------------------------------------------------- MMA issuer (leader CTA only)
@@ -243,7 +248,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
       uint32_t it = 0, tile_i = 0;
       for (int w = pair; w < total && !*abort_flag; w += npairs, ++tile_i) {
         const int buf = tile_i & 1;
-        if (!mbar_wait(&acc_empty[buf], ((tile_i >> 1) & 1) ^ 1)) {
+        if (!mbar_wait(&acc_empty[buf], ((tile_i >> 1) & 1) ^ 1, wait_ns)) {
           atomicExch(p.status, ERR_WAIT_ACC);
           *abort_flag = 1;
           break;
@@ -253,7 +258,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         bool failed = false;
         for (int kb = 0; kb < p.kb_total; ++kb, ++it) {
           const int s = it % S;
-          if (!mbar_wait(&full[s], (it / S) & 1)) {
+          if (!mbar_wait(&full[s], (it / S) & 1, wait_ns)) {
             atomicExch(p.status, ERR_WAIT_TMA);
             failed = true;
             break;
@@ -281,7 +286,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
       int m2, nt;
       tile_of(w, m2, nt);
       const int buf = tile_i & 1;
-      bool ok = mbar_wait(&acc_full[buf], (tile_i >> 1) & 1);
+      bool ok = mbar_wait(&acc_full[buf], (tile_i >> 1) & 1, wait_ns);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) atomicExch(p.status, ERR_WAIT_ACC);
@@ -329,7 +334,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         __syncwarp();
         if (lane == 0) {
           __threadfence_system();
-          if ((atomicAdd(epi_count, 1) & 3) == 3) {       // the counter only grows: four arrivals per tile
+          if ((atomicAdd(&epi_count[tile_i & 3], 1) & 3) == 3) {   // the counters only grow: four arrivals per tile
             // this CTA's 128 rows x 256 features = two 128-feature tiles of the 128-row block, as the owner counts them
             uint32_t* fl = flag_slot(p.comm.flags[owner], ar_epoch & 1, p.comm.rank) +
                            (dst_row0 / BM) * (p.m2_tiles * 2) + m2 * 2;
