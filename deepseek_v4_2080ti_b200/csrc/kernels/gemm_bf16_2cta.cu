@@ -309,25 +309,30 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
       __nv_bfloat16* drow = dst + (size_t)(dst_row0 + row_in_tile) * p.ldo + (size_t)m2 * BN;
       const uint32_t taddr = tmem_base + (uint32_t(warp * 32) << 16) + buf * BN;
       if (p.mode != 3) {
+        // two TMEM reads in flight per wait: the read latency, not the store count, paces this loop
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c0, v);
+        for (int c0 = 0; c0 < BN; c0 += 64) {
+          uint32_t v[2][32];
+          tmem_ld_32x32(taddr + c0, v[0]);
+          tmem_ld_32x32(taddr + c0 + 32, v[1]);
           tmem_ld_wait();
-          if (c0 + 32 >= BN) {
+          if (c0 + 64 >= BN) {
             // accumulator drained: one arrive per warp on the leader's barrier
             tc_fence_before();
             __syncwarp();
             if (lane == 0) remote_arrive(lead_acc_empty0 + buf * 8);
           }
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint4 o;
-            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+          for (int hh = 0; hh < 2; ++hh) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-              oh[e] = __floats2bfloat162_rn(__uint_as_float(v[q4 * 8 + 2 * e]), __uint_as_float(v[q4 * 8 + 2 * e + 1]));
-            *reinterpret_cast<uint4*>(drow + c0 + q4 * 8) = o;
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 o;
+              __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                oh[e] = __floats2bfloat162_rn(__uint_as_float(v[hh][q4 * 8 + 2 * e]), __uint_as_float(v[hh][q4 * 8 + 2 * e + 1]));
+              *reinterpret_cast<uint4*>(drow + c0 + hh * 32 + q4 * 8) = o;
+            }
           }
         }
       } else {
@@ -339,24 +344,28 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
 #pragma unroll 1
         for (int half = 0; half < 2; ++half) {
 #pragma unroll 1
-          for (int cc = 0; cc < 4; ++cc) {
-            uint32_t v[32];
-            tmem_ld_32x32(taddr + half * 128 + cc * 32, v);
+          for (int cc = 0; cc < 4; cc += 2) {
+            uint32_t v[2][32];
+            tmem_ld_32x32(taddr + half * 128 + cc * 32, v[0]);
+            tmem_ld_32x32(taddr + half * 128 + cc * 32 + 32, v[1]);
             tmem_ld_wait();
-            if (half == 1 && cc == 3) {
+            if (half == 1 && cc == 2) {
               tc_fence_before();
               __syncwarp();
               if (lane == 0) remote_arrive(lead_acc_empty0 + buf * 8);
             }
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              uint4 o;
-              __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+            for (int hh = 0; hh < 2; ++hh) {
 #pragma unroll
-              for (int e = 0; e < 4; ++e)
-                oh[e] = __floats2bfloat162_rn(__uint_as_float(v[q4 * 8 + 2 * e]), __uint_as_float(v[q4 * 8 + 2 * e + 1]));
-              const int ci = cc * 4 + q4;
-              *reinterpret_cast<uint4*>(stg + lane * 256 + ((ci ^ (lane & 7)) << 4)) = o;
+              for (int q4 = 0; q4 < 4; ++q4) {
+                uint4 o;
+                __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  oh[e] = __floats2bfloat162_rn(__uint_as_float(v[hh][q4 * 8 + 2 * e]), __uint_as_float(v[hh][q4 * 8 + 2 * e + 1]));
+                const int ci = (cc + hh) * 4 + q4;
+                *reinterpret_cast<uint4*>(stg + lane * 256 + ((ci ^ (lane & 7)) << 4)) = o;
+              }
             }
           }
           __syncwarp();
