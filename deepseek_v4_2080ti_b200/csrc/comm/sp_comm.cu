@@ -54,9 +54,11 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
 __global__ void __launch_bounds__(kThreads)
 sp_reduce_norm_gather_kernel(B200Comm c, __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ gamma,
                              float eps, int unit_offset, int rows, int H, int with_partials, int rs_bn, int rs_m_tiles,
-                             int x_index, int gather, int* status, uint64_t budget_ns) {
+                             int x_index, int gather, int epoch_word, int* status, uint64_t budget_ns) {
   const uint32_t prev = c.ctrl[0];
   const uint32_t epoch = prev + 1;
+  // deferred gather: the push kernel, on another stream, raises the flags with this call's epoch
+  if (epoch_word >= 0 && blockIdx.x == 0 && threadIdx.x == 0) c.ctrl[8 + epoch_word] = epoch;
   const int parity_p = prev & 1, parity_x = epoch & 1;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row0 = blockIdx.x * kRowsPerCta;
@@ -145,6 +147,37 @@ sp_reduce_norm_gather_kernel(B200Comm c, __nv_bfloat16* __restrict__ h, const __
   finish_epoch(c.ctrl, epoch);
 }
 
+// The all-gather push on its own: copies this rank's normalised rows (already in its own gathered buffer, written by
+// the kernel above with gather == 0) into every peer's gathered buffer and raises the per-8-row flags there, with the
+// epoch that call left in ctrl[8 + epoch_word].  Launched on a second stream, it overlaps the column-parallel GEMM
+// that has already started on this rank's own rows: that GEMM waits for the peers' flags tile by tile.
+// grid-stride over 8-row blocks; 16-byte loads of a block, W-1 stores each, one system-scope release per block.
+__global__ void __launch_bounds__(256)
+sp_push_rows_kernel(B200Comm c, int rows, int H, int x_index, int epoch_word) {
+  const uint32_t epoch = c.ctrl[8 + epoch_word];
+  const int parity_x = epoch & 1;
+  const int nvec = (kRowsPerCta * H) >> 3;            // 16-byte vectors per block (rows are contiguous)
+  const size_t base = (size_t)x_index * c.slot_elems + (size_t)c.rank * rows * H;
+  const __nv_bfloat16* src0 = reinterpret_cast<const __nv_bfloat16*>(c.result[c.rank]) + base;
+  for (int b = blockIdx.x; b < rows / kRowsPerCta; b += gridDim.x) {
+    const size_t off = (size_t)b * kRowsPerCta * H;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const uint4 q = *reinterpret_cast<const uint4*>(src0 + off + (size_t)v * 8);
+      for (int k = 1; k < c.world; ++k) {
+        const int r = (c.rank + k) % c.world;
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(c.result[r]) + base + off + (size_t)v * 8) = q;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x > 0 && threadIdx.x < c.world) {
+      __threadfence_block();
+      const int r = (c.rank + threadIdx.x) % c.world;
+      st_release_sys(flag_slot(c.flags2[r], parity_x, c.rank) + b, epoch);
+    }
+    __syncthreads();
+  }
+}
+
 // One CTA: waits until every peer has raised the flags of its `nblocks` row blocks for the gather that ran last
 // (epoch = current ctrl[0]).  After it, any kernel on this stream may read the whole gathered buffer.
 __global__ void __launch_bounds__(256)
@@ -163,10 +196,21 @@ sp_wait_gather_kernel(B200Comm c, int nblocks, int* status, uint64_t budget_ns) 
 
 extern "C" {
 
+int b200_sp_push_rows(const B200Comm* c, int rows, int H, int x_index, int epoch_word, cudaStream_t stream) {
+  if (!c || rows <= 0 || rows % kRowsPerCta || H % 8 || x_index < 0 || x_index > 1 || epoch_word < 0 || epoch_word > 3)
+    return -ERR_BAD_ARG;
+  if (c->world <= 1) return 0;
+  int blocks = rows / kRowsPerCta;
+  if (blocks > 64) blocks = 64;       // a quarter of the SMs' thread slots: the GEMM running beside it keeps the rest
+  sp_push_rows_kernel<<<blocks, 256, 0, stream>>>(*c, rows, H, x_index, epoch_word);
+  return (int)cudaGetLastError();
+}
+
 int b200_sp_reduce_norm_gather(const B200Comm* c, void* h_shard, const void* gamma, float eps, int unit_offset,
-                               int rows, int H, int with_partials, int rs_bn, int x_index, int gather, int* status,
-                               unsigned long long budget_ns, cudaStream_t stream) {
+                               int rows, int H, int with_partials, int rs_bn, int x_index, int gather, int epoch_word,
+                               int* status, unsigned long long budget_ns, cudaStream_t stream) {
   if (!c || rows <= 0 || rows % kRowsPerCta || H % 8 || x_index < 0 || x_index > 1 || !h_shard) return -ERR_BAD_ARG;
+  if (epoch_word > 3) return -ERR_BAD_ARG;
   if ((unsigned long long)rows * c->world * H > c->slot_elems) return -ERR_BAD_ARG;
   if (rows / kRowsPerCta > B200_FLAGS_PER_SLOT) return -ERR_BAD_ARG;
   const int m_tiles = (H + 127) / 128;
@@ -175,7 +219,7 @@ int b200_sp_reduce_norm_gather(const B200Comm* c, void* h_shard, const void* gam
   if (budget_ns == 0) budget_ns = B200_WAIT_BUDGET_NS;
   sp_reduce_norm_gather_kernel<<<rows / kRowsPerCta, kThreads, 0, stream>>>(
       *c, reinterpret_cast<__nv_bfloat16*>(h_shard), reinterpret_cast<const __nv_bfloat16*>(gamma), eps, unit_offset,
-      rows, H, with_partials, rs_bn, m_tiles, x_index, gather, status, budget_ns);
+      rows, H, with_partials, rs_bn, m_tiles, x_index, gather, epoch_word, status, budget_ns);
   return (int)cudaGetLastError();
 }
 

@@ -172,6 +172,12 @@ class PeerComm(TPComm):
         self.sp_enabled = os.environ.get("B200_SP", "1") != "0"
         self.degraded = False       # after recover(): every collective goes through the process group (NCCL)
         self.recoveries = 0
+        # all-gather push on a second stream, overlapping the GEMM that consumes the gathered rows (B200_SP_OVERLAP=0:
+        # the gather kernel pushes the rows itself, on the compute stream)
+        self.overlap_gather = os.environ.get("B200_SP_OVERLAP", "1") != "0"
+        self._side_stream = None
+        self._push_done = None
+        self._epoch_word = 0
 
     @classmethod
     def local_group(cls, world: int, slot_elems: int, budget_ms: float = 50.0) -> list["PeerComm"]:
@@ -191,6 +197,7 @@ class PeerComm(TPComm):
             c.device = torch.device("cuda", torch.cuda.current_device())
             c._base, c._peers = raw[r], []
             c._bind(bases)
+            c.overlap_gather = False      # one device: a kernel must never wait for a kernel of another stream
             out.append(c)
         torch.cuda.synchronize()
         return out
@@ -351,12 +358,36 @@ class PeerComm(TPComm):
         their flags arrive (``linear_ag`` waits per tile; anything else calls ``wait_gather`` first)."""
         rows, h = h_shard.shape
         assert h_shard.dtype == torch.bfloat16 and h_shard.is_contiguous()
-        rc = _lib.lib().b200_sp_reduce_norm_gather(self._cref(), _lib.ptr(h_shard), _lib.ptr(gamma),
-                                                   ctypes.c_float(eps), int(unit_offset), rows, h, int(with_partials),
-                                                   self._rs_bn, 0, int(gather), _lib.ptr(_lib.status_word(h_shard.device)),
-                                                   ctypes.c_ulonglong(self.budget_ns), _lib.stream())
+        L = _lib.lib()
+        st = _lib.ptr(_lib.status_word(h_shard.device))
+        if self._push_done is not None:
+            # the previous push reads the rows this call is about to rewrite
+            torch.cuda.current_stream().wait_event(self._push_done)
+            self._push_done = None
+        deferred = gather and gamma is not None and self.overlap_gather and self.world > 1
+        word = -1
+        if deferred:
+            word = self._epoch_word
+            self._epoch_word = (word + 1) & 3
+        rc = L.b200_sp_reduce_norm_gather(self._cref(), _lib.ptr(h_shard), _lib.ptr(gamma), ctypes.c_float(eps),
+                                          int(unit_offset), rows, h, int(with_partials), self._rs_bn, 0,
+                                          int(gather and not deferred), word, st, ctypes.c_ulonglong(self.budget_ns),
+                                          _lib.stream())
         _lib.check(rc, "sp_reduce_norm_gather")
         self.fused_calls += 1
+        if deferred:
+            # the rows are in this rank's own buffer; a second stream pushes them to the peers and raises their flags
+            # while the caller's next GEMM starts on the own rows
+            if self._side_stream is None:
+                self._side_stream = torch.cuda.Stream(device=self.device)
+            ready = torch.cuda.Event()
+            ready.record()
+            self._side_stream.wait_event(ready)
+            with torch.cuda.stream(self._side_stream):
+                rc = L.b200_sp_push_rows(self._cref(), rows, h, 0, word, _lib.stream())
+                _lib.check(rc, "sp_push_rows")
+                self._push_done = torch.cuda.Event()
+                self._push_done.record()
         return self._result_view(0, rows * self.world, h) if gamma is not None else None
 
     def linear_ag(self, x_full: torch.Tensor, w, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -424,6 +455,7 @@ class PeerComm(TPComm):
 
     def close(self) -> None:
         L = _lib.lib()
+        self._push_done = None
         torch.cuda.synchronize()
         if dist.is_initialized():
             dist.barrier(group=self.group)
