@@ -227,12 +227,28 @@ def main() -> None:
             rt.free(s)
         return e0.elapsed_time(e1) / steps
 
+    fallback = False
     for i in range(args.warmup):
         device_request()
         if i == 0:
-            # a kernel that gave up on a wait (a peer that never signalled) shows here, after one request, not after
-            # the whole run has crawled through its wait budgets
-            _lib.check_status()
+            # A kernel that gave up on a wait (a peer that never signalled) shows here, after one request, not after
+            # the whole run has crawled through its wait budgets.  All ranks agree on the outcome; if any saw an
+            # error, the group re-synchronises and the rest of the run uses the library collectives.
+            bad = int(_lib.status_word(dev).item())
+            if world > 1:
+                tb = torch.tensor([bad], device=dev, dtype=torch.int32)
+                dist.all_reduce(tb, op=dist.ReduceOp.MAX)
+                bad = int(tb.item())
+            if bad:
+                if comm is None:
+                    _lib.check_status()
+                print(f"[bench] rank {rank}: a device wait expired (status {bad}); continuing on the NCCL path",
+                      file=sys.stderr, flush=True)
+                comm.recover(degrade=True)
+                rt._graphs.clear()
+                fallback = True
+                device_request()
+                _lib.check_status()
     api_request()
     barrier()
     pre_ms, dec_ms, launches = [], [], 0
@@ -303,6 +319,7 @@ def main() -> None:
         if comm is not None:
             # fused = kernels that carry their collective (reduce-scatter / all-gather GEMMs, the reduce + norm + gather
             # kernel, GEMM + all-reduce epilogues); standalone = peer-memory collectives launched on their own
+            rec["collective_fallback"] = fallback
             rec["fused_collective_calls"] = int(comm.fused_calls)
             rec["standalone_peer_collectives"] = int(comm.standalone_calls)
             rec["config"]["prefill_collectives"] = ("sequence-parallel: GEMM->reduce-scatter, reduce+norm+all-gather, "

@@ -120,7 +120,7 @@ def build_core(jobs: int | None = None) -> dict[str, Path]:
 
     main_src = CSRC / "engine" / "main.cpp"
     if main_src.exists():
-        eng_srcs = sorted((CSRC / "engine").glob("*.cpp"))
+        eng_srcs = sorted((CSRC / "engine").glob("*.cpp")) + sorted((CSRC / "comm").glob("*.cpp"))
         eng_objs = [_compile_cpp(s, tag=".eng") for s in eng_srcs]
         exe = BIN / "pocketllm_engine"
         kern = LIB / "libb200_kernels.so"
@@ -128,7 +128,7 @@ def build_core(jobs: int | None = None) -> dict[str, Path]:
                 or (kern.exists() and kern.stat().st_mtime > exe.stat().st_mtime):
             _run([CXX, "-o", str(exe), *map(str, eng_objs), *map(str, core_objs), "-L", str(LIB),
                   "-lb200_kernels", f"-Wl,-rpath,$ORIGIN/../lib", "-L/usr/local/cuda/lib64",
-                  "-lcudart", "-ldl", "-pthread"])
+                  "-lcudart", "-lnccl", "-ldl", "-pthread"])
         products["engine"] = exe
         ebind = CSRC / "bindings" / "engine_bindings.cpp"
         if ebind.exists():
@@ -142,7 +142,8 @@ def build_core(jobs: int | None = None) -> dict[str, Path]:
             if (not emod.exists()) or any(o.stat().st_mtime > emod.stat().st_mtime for o in [eobj, *lib_objs, *core_objs]) \
                     or (kern.exists() and kern.stat().st_mtime > emod.stat().st_mtime):
                 _run([CXX, "-shared", "-o", str(emod), str(eobj), *map(str, lib_objs), *map(str, core_objs), "-L", str(LIB),
-                      "-lb200_kernels", "-Wl,-rpath,$ORIGIN/lib", "-L/usr/local/cuda/lib64", "-lcudart", "-ldl", "-pthread"])
+                      "-lb200_kernels", "-Wl,-rpath,$ORIGIN/lib", "-L/usr/local/cuda/lib64", "-lcudart", "-lnccl", "-ldl",
+                      "-pthread"])
             products["engine_pybind"] = emod
     return products
 

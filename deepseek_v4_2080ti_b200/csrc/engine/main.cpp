@@ -33,6 +33,7 @@
 #include <unistd.h>
 
 #include "../core/batch_scheduler.hpp"
+#include "../core/cmd_channel.hpp"
 #include "../core/openai_server.hpp"
 #include "../core/qwen_weight_map.hpp"
 #include "../core/safetensors_reader.hpp"
@@ -45,7 +46,8 @@ namespace {
 struct Args {
   std::string ckpt, grep, tensor, token_ids, token_file, eos, host = "127.0.0.1", python = "python", sidecar_gguf,
       chat_family = "deepseek_v4", served_name = "pocketllm";
-  int port = 8000, tp_world = 1;
+  int port = 8000, tp_world = 1, tp_rank = 0;
+  std::string nccl_id_path;
   bool serve = false, audit = false, audit_strict = false;
   bool dump_config = false, inspect = false, context_info = false, smoke = false, bench = false, persistent = false,
        serve_batch = false, json = false, verbose = false;
@@ -106,6 +108,8 @@ bool parse(int argc, char** argv, Args& a) {
     else if (arg == "--qwen-audit") a.audit = true;
     else if (arg == "--qwen-audit-strict") a.audit = a.audit_strict = true;
     else if (arg == "--tp-world") a.tp_world = std::atoi(val("--tp-world"));
+    else if (arg == "--tp-rank") a.tp_rank = std::atoi(val("--tp-rank"));
+    else if (arg == "--nccl-id-path") a.nccl_id_path = val("--nccl-id-path");
     else if (arg == "--host") a.host = val("--host");
     else if (arg == "--port") a.port = std::atoi(val("--port"));
     else if (arg == "--python") a.python = val("--python");
@@ -239,6 +243,20 @@ int main(int argc, char** argv) {
     opt.eos_tokens = parse_ids(a.eos);
     opt.sampling = a.sampling;
     opt.seed = a.seed;
+    opt.tp_world = std::max(1, a.tp_world);
+    opt.tp_rank = a.tp_rank;
+    opt.nccl_id_path = a.nccl_id_path;
+    // Multi-rank runs: one process per GPU, every rank started with the same arguments plus its --tp-rank.  Rank 0 owns
+    // stdin / HTTP and hands each request to the others over the command channel (a unix socket beside the id file),
+    // so idle workers block on a socket, not on a device collective (cpp_engine/engine/main.cpp:100-216, 640-764).
+    const bool multi = opt.tp_world > 1;
+    if (multi && (a.serve || a.serve_batch))
+      throw std::invalid_argument("--serve / --serve-batch run on one rank; multi-rank serving goes through pocketllm serve");
+    CmdChannel channel;
+    if (multi && a.persistent) {
+      if (!channel.open(a.nccl_id_path, a.tp_rank, opt.tp_world))
+        throw std::runtime_error("command channel could not be opened beside " + a.nccl_id_path);
+    }
     QwenNativeEngine eng(cfg, *ws, opt);
     if (a.verbose)
       std::fprintf(stderr, "loaded %.2f GB of weights in %.2f s; cache/state %.2f GB\n", eng.stats().weight_bytes / 1e9,
@@ -257,8 +275,24 @@ int main(int argc, char** argv) {
       std::fflush(stdout);
     };
 
+    if (a.persistent && multi && a.tp_rank > 0) {
+      // worker rank: mirror rank 0's requests ([1, max_new, tokens...] = generate, [0] = stop)
+      std::vector<int32_t> msg;
+      while (channel.receive(msg, -1)) {
+        if (msg.empty() || msg[0] == 0) break;
+        if (msg[0] == 1 && msg.size() >= 3) {
+          std::vector<int32_t> prompt(msg.begin() + 2, msg.end());
+          try {
+            eng.generate(prompt, msg[1]);
+          } catch (const std::exception& e) {
+            std::fprintf(stderr, "[rank %d] generate failed: %s\n", a.tp_rank, e.what());
+          }
+        }
+      }
+      return 0;
+    }
     if (a.persistent) {
-      std::printf("qwen_persistent_ready=1 max_context=%lld\n", a.max_context);
+      std::printf("qwen_persistent_ready=1 max_context=%lld tp_world=%d\n", a.max_context, opt.tp_world);
       std::fflush(stdout);
       std::string line;
       while (std::getline(std::cin, line)) {
@@ -269,6 +303,11 @@ int main(int argc, char** argv) {
         std::vector<int32_t> prompt(f.begin() + 1, f.end());
         try {
           double ps = 0, ds = 0;
+          if (multi) {
+            std::vector<int32_t> msg{1, max_new};
+            msg.insert(msg.end(), prompt.begin(), prompt.end());
+            if (!channel.broadcast(msg)) throw std::runtime_error("a worker rank closed its command channel");
+          }
           std::vector<int32_t> out = eng.generate(prompt, max_new, &ps, &ds);
           report(prompt, out, ps, ds, "qwen_persistent_result");
         } catch (const std::exception& e) {
@@ -276,6 +315,7 @@ int main(int argc, char** argv) {
           std::fflush(stdout);
         }
       }
+      if (multi) channel.broadcast({0});
       return 0;
     }
 

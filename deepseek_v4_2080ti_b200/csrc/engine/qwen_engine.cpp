@@ -75,7 +75,7 @@ struct QwenNativeEngine::Scratch {
   int rows = 0;                       // capacity in token rows
   DeviceBuffer ids, pos, kv_slots, meta, slot_ids, kv_len, bt_batch;
   DeviceBuffer h, x, d_attn, d_mlp, proj, mixed, core, y, ab, g, beta, q, gate, attn, gu, act;
-  DeviceBuffer logits, next_idx, next_val, status;
+  DeviceBuffer logits, next_idx, next_val, status, merge;
   DeviceBuffer gdn_ws, splitk_ws, counters, dec_ws;
   DeviceBuffer xq, inv_c, xq2, inv_c2;
   size_t splitk_floats = 0;
@@ -107,9 +107,22 @@ QwenNativeEngine::QwenNativeEngine(const QwenConfig& cfg, WeightSource& weights,
   cuda_check(cudaSetDevice(opt_.device), "cudaSetDevice");
   cuda_check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
   n_layers_ = opt_.layers > 0 ? std::min<int>(opt_.layers, cfg_.num_hidden_layers) : int(cfg_.num_hidden_layers);
-  hq_ = int(cfg_.num_attention_heads); hkv_ = int(cfg_.num_key_value_heads);
-  hv_ = int(cfg_.linear_num_value_heads); hk_ = int(cfg_.linear_num_key_heads);
+  const int W = std::max(1, opt_.tp_world), tp_r = opt_.tp_rank;
+  if (W > 1) {
+    if (cfg_.num_attention_heads % W || cfg_.num_key_value_heads % W || cfg_.linear_num_value_heads % W ||
+        cfg_.linear_num_key_heads % W || (cfg_.intermediate_size / W) % 128 || cfg_.intermediate_size % W)
+      throw std::runtime_error("head counts / feed-forward width do not divide over " + std::to_string(W) + " ranks");
+    if (opt_.sampling.temperature > 0.f)
+      throw std::runtime_error("the native engine samples on the host from full logits: multi-rank runs are greedy");
+    tp_.init(W, tp_r, opt_.device, opt_.nccl_id_path);
+  }
+  hq_ = int(cfg_.num_attention_heads) / W; hkv_ = int(cfg_.num_key_value_heads) / W;
+  hv_ = int(cfg_.linear_num_value_heads) / W; hk_ = int(cfg_.linear_num_key_heads) / W;
   kd_ = hk_ * kHead; vd_ = hv_ * kHead; cw_ = 2 * kd_ + vd_;
+  inter_ = int(cfg_.intermediate_size) / W;
+  const int vper = (int(cfg_.vocab_size) + W - 1) / W;
+  vocab_lo_ = tp_r * vper;
+  vocab_n_ = std::max(0, std::min(int(cfg_.vocab_size), vocab_lo_ + vper) - vocab_lo_);
   rot_ = int(cfg_.rotary_dim());
 
   const double t0 = now_s();
@@ -148,7 +161,7 @@ QwenNativeEngine::QwenNativeEngine(const QwenConfig& cfg, WeightSource& weights,
   Scratch& s = *s_;
   const size_t R = size_t(std::max(opt_.prefill_chunk, kStreamMaxT));
   s.rows = int(R);
-  const size_t H = size_t(cfg_.hidden_size), I = size_t(cfg_.intermediate_size), V = size_t(cfg_.vocab_size);
+  const size_t H = size_t(cfg_.hidden_size), I = size_t(inter_), V = size_t(vocab_n_);
   const size_t gate_mul = cfg_.attn_output_gate ? 2 : 1;
   const size_t proj_w = std::max<size_t>(size_t(cw_) + vd_, (size_t(hq_) * gate_mul + 2 * hkv_) * kHead);
   s.ids.reset(R * 4); s.pos.reset(R * 4); s.kv_slots.reset(R * 4); s.meta.reset(64);
@@ -160,6 +173,7 @@ QwenNativeEngine::QwenNativeEngine(const QwenConfig& cfg, WeightSource& weights,
   s.gu.reset(R * 2 * I * 2); s.act.reset(R * I * 2);
   s.logits.reset(size_t(opt_.max_slots > 64 ? opt_.max_slots : 64) * V * 4);
   s.next_idx.reset(64 * 4); s.next_val.reset(64 * 4); s.status.reset(4, true);
+  s.merge.reset(size_t(W) * 64 * 8);
   s.gdn_ws.reset(size_t(std::max<long long>(1, b200_gdn_workspace_floats(int(R), std::max(1, hv_)))) * 4);
   s.splitk_floats = size_t(1) << 24;
   s.splitk_ws.reset(s.splitk_floats * 4);
@@ -170,7 +184,7 @@ QwenNativeEngine::QwenNativeEngine(const QwenConfig& cfg, WeightSource& weights,
   s.xq2.reset(size_t(kStreamMaxT) * 3 * maxk); s.inv_c2.reset(64 * 4);
 
   // the fused decode path needs every FP8 reduction width to be a multiple of the 128-wide scale block
-  stream_ok_ = (H % 128 == 0) && (I % 128 == 0) && (vd_ % 128 == 0) && kw == 4 && hk_ > 0 &&
+  stream_ok_ = (H % 128 == 0) && (I % 128 == 0) && (vd_ % 128 == 0) && ((hq_ * kHead) % 128 == 0) && kw == 4 && hk_ > 0 &&
                (hv_ / hk_ == 1 || hv_ / hk_ == 2 || hv_ / hk_ == 4);
 }
 
@@ -179,13 +193,19 @@ QwenNativeEngine::~QwenNativeEngine() {
 }
 
 // ------------------------------------------------------------------------------------------------ loading
-DeviceBuffer QwenNativeEngine::load_vector(WeightSource& ws, const std::string& name, bool to_f32) {
+DeviceBuffer QwenNativeEngine::load_vector(WeightSource& ws, const std::string& name, bool to_f32, long long first,
+                                           long long count) {
   TensorView v = need(ws, name);
-  size_t count = 1;
-  for (auto d : v.shape) count *= d;
-  DeviceBuffer raw(v.nbytes);
-  cuda_check(cudaMemcpyAsync(raw.get(), v.data, v.nbytes, cudaMemcpyHostToDevice, stream_), name.c_str());
-  stats_.weight_bytes += v.nbytes;
+  size_t total = 1;
+  for (auto d : v.shape) total *= d;
+  const size_t esz = dtype_size(v.dtype);
+  if (count < 0) count = (long long)total - first;
+  if (first < 0 || size_t(first + count) > total) throw std::runtime_error(name + ": shard outside the tensor");
+  const size_t nbytes = size_t(count) * esz;
+  DeviceBuffer raw(nbytes);
+  cuda_check(cudaMemcpyAsync(raw.get(), reinterpret_cast<const uint8_t*>(v.data) + size_t(first) * esz, nbytes,
+                             cudaMemcpyHostToDevice, stream_), name.c_str());
+  stats_.weight_bytes += nbytes;
   if (!to_f32) {
     if (v.dtype != "BF16") throw std::runtime_error(name + ": expected BF16, found " + v.dtype);
     cuda_check(cudaStreamSynchronize(stream_), name.c_str());
@@ -193,47 +213,72 @@ DeviceBuffer QwenNativeEngine::load_vector(WeightSource& ws, const std::string& 
   }
   if (v.dtype == "F32") { cuda_check(cudaStreamSynchronize(stream_), name.c_str()); return raw; }
   if (v.dtype != "BF16") throw std::runtime_error(name + ": expected BF16 or F32, found " + v.dtype);
-  DeviceBuffer out(count * 4);
-  rc(b200_bf16_to_f32(raw.get(), out.as<float>(), (long long)count, stream_), "bf16_to_f32");
+  DeviceBuffer out(size_t(count) * 4);
+  rc(b200_bf16_to_f32(raw.get(), out.as<float>(), count, stream_), "bf16_to_f32");
   cuda_check(cudaStreamSynchronize(stream_), name.c_str());
   return out;
 }
 
-PackedMatrix QwenNativeEngine::load_bf16(WeightSource& ws, const std::vector<std::string>& names) {
+// Compact device copy of the window [row0, row0+rows) x [col0, col0+cols) of a row-major host matrix.
+DeviceBuffer QwenNativeEngine::upload_window(const TensorView& v, size_t elem, long long row0, long long rows,
+                                             long long col0, long long cols) {
+  const size_t pitch = size_t(v.shape[1]) * elem;
+  DeviceBuffer out(size_t(rows) * cols * elem);
+  const uint8_t* src = reinterpret_cast<const uint8_t*>(v.data) + size_t(row0) * pitch + size_t(col0) * elem;
+  cuda_check(cudaMemcpy2DAsync(out.get(), size_t(cols) * elem, src, pitch, size_t(cols) * elem, size_t(rows),
+                               cudaMemcpyHostToDevice, stream_), "window upload");
+  return out;
+}
+
+PackedMatrix QwenNativeEngine::load_bf16(WeightSource& ws, const std::vector<Piece>& pieces) {
   PackedMatrix m;
   m.wfmt = 0;
-  std::vector<TensorView> parts;
-  for (auto& n : names) {
-    parts.push_back(need(ws, n));
-    const TensorView& v = parts.back();
-    if (v.dtype != "BF16" || v.shape.size() != 2) throw std::runtime_error(n + ": expected a BF16 matrix");
-    if (m.k && int(v.shape[1]) != m.k) throw std::runtime_error(n + ": inner widths differ");
+  struct Part { TensorView v; long long r0, rows; };
+  std::vector<Part> parts;
+  for (auto& pc : pieces) {
+    TensorView v = need(ws, pc.name);
+    if (v.dtype != "BF16" || v.shape.size() != 2) throw std::runtime_error(pc.name + ": expected a BF16 matrix");
+    if (pc.col0 != 0 || pc.cols >= 0) throw std::runtime_error(pc.name + ": bf16 matrices are sharded by rows only");
+    const long long rows = pc.rows < 0 ? (long long)v.shape[0] - pc.row0 : pc.rows;
+    if (pc.row0 < 0 || pc.row0 + rows > (long long)v.shape[0]) throw std::runtime_error(pc.name + ": row shard outside the matrix");
+    if (m.k && int(v.shape[1]) != m.k) throw std::runtime_error(pc.name + ": inner widths differ");
     m.k = int(v.shape[1]);
-    m.n += int(v.shape[0]);
+    m.n += int(rows);
+    parts.push_back({v, pc.row0, rows});
   }
-  m.weight.reset(size_t(m.n) * m.k * 2);
+  m.weight.reset(std::max<size_t>(2, size_t(m.n) * m.k * 2));
   size_t off = 0;
-  for (auto& v : parts) {
-    cuda_check(cudaMemcpyAsync(m.weight.as<uint8_t>() + off, v.data, v.nbytes, cudaMemcpyHostToDevice, stream_), "bf16 upload");
-    off += v.nbytes;
+  for (auto& p : parts) {
+    const size_t nb = size_t(p.rows) * m.k * 2;
+    cuda_check(cudaMemcpyAsync(m.weight.as<uint8_t>() + off, reinterpret_cast<const uint8_t*>(p.v.data) + size_t(p.r0) * m.k * 2,
+                               nb, cudaMemcpyHostToDevice, stream_), "bf16 upload");
+    off += nb;
   }
   cuda_check(cudaStreamSynchronize(stream_), "bf16 upload");
   stats_.weight_bytes += off;
   return m;
 }
 
-PackedMatrix QwenNativeEngine::load_fp8(WeightSource& ws, const std::vector<std::string>& bases) {
+PackedMatrix QwenNativeEngine::load_fp8(WeightSource& ws, const std::vector<Piece>& pieces) {
   PackedMatrix m;
   m.wfmt = 1;
-  struct Part { TensorView w, s; };
+  struct Part { TensorView w, s; long long r0, rows, c0, cols; };
   std::vector<Part> parts;
-  for (auto& b : bases) {
-    Part p{need(ws, b + ".weight"), need(ws, b + ".weight_scale_inv")};
-    if (p.w.dtype != "F8_E4M3" || p.w.shape.size() != 2) throw std::runtime_error(b + ": expected an F8_E4M3 matrix");
-    if (m.k && int(p.w.shape[1]) != m.k) throw std::runtime_error(b + ": inner widths differ");
-    m.k = int(p.w.shape[1]);
-    if (bases.size() > 1 && p.w.shape[0] % 128) throw std::runtime_error(b + ": fused projections need 128-row multiples");
-    m.n += int(p.w.shape[0]);
+  for (auto& pc : pieces) {
+    Part p{need(ws, pc.name + ".weight"), need(ws, pc.name + ".weight_scale_inv"), pc.row0, pc.rows, pc.col0, pc.cols};
+    if (p.w.dtype != "F8_E4M3" || p.w.shape.size() != 2) throw std::runtime_error(pc.name + ": expected an F8_E4M3 matrix");
+    if (p.rows < 0) p.rows = (long long)p.w.shape[0] - p.r0;
+    if (p.cols < 0) p.cols = (long long)p.w.shape[1] - p.c0;
+    if (p.r0 < 0 || p.c0 < 0 || p.r0 + p.rows > (long long)p.w.shape[0] || p.c0 + p.cols > (long long)p.w.shape[1])
+      throw std::runtime_error(pc.name + ": shard outside the matrix");
+    const bool whole = p.r0 == 0 && p.c0 == 0 && p.rows == (long long)p.w.shape[0] && p.cols == (long long)p.w.shape[1];
+    if (!whole && (p.r0 % 128 || p.c0 % 128 || (p.rows % 128 && p.r0 + p.rows != (long long)p.w.shape[0]) ||
+                   (p.cols % 128 && p.c0 + p.cols != (long long)p.w.shape[1])))
+      throw std::runtime_error(pc.name + ": an FP8 shard must keep whole 128 x 128 scale blocks");
+    if (m.k && int(p.cols) != m.k) throw std::runtime_error(pc.name + ": inner widths differ");
+    m.k = int(p.cols);
+    if (pieces.size() > 1 && p.rows % 128) throw std::runtime_error(pc.name + ": fused projections need 128-row multiples");
+    m.n += int(p.rows);
     parts.push_back(p);
   }
   const int kb_total = (m.k + 63) / 64, sld = (m.k + 127) / 128;
@@ -241,12 +286,13 @@ PackedMatrix QwenNativeEngine::load_fp8(WeightSource& ws, const std::vector<std:
   m.scales.reset(size_t((m.n + 127) / 128) * sld * 4);
   int row = 0;
   for (auto& p : parts) {
-    const int n = int(p.w.shape[0]);
-    DeviceBuffer raw(p.w.nbytes), sraw(p.s.nbytes);
-    cuda_check(cudaMemcpyAsync(raw.get(), p.w.data, p.w.nbytes, cudaMemcpyHostToDevice, stream_), "fp8 upload");
-    cuda_check(cudaMemcpyAsync(sraw.get(), p.s.data, p.s.nbytes, cudaMemcpyHostToDevice, stream_), "scale upload");
+    const int n = int(p.rows);
+    const size_t ssz = dtype_size(p.s.dtype);
+    const long long srows = (p.rows + 127) / 128;
+    DeviceBuffer raw = upload_window(p.w, 1, p.r0, p.rows, p.c0, p.cols);
+    DeviceBuffer sraw = upload_window(p.s, ssz, p.r0 / 128, srows, p.c0 / 128, sld);
     rc(b200_prepack_fp8(raw.get(), m.weight.as<uint8_t>() + size_t(row / 128) * kb_total * 8192, n, m.k, stream_), "prepack_fp8");
-    const size_t sc = size_t((n + 127) / 128) * sld;
+    const size_t sc = size_t(srows) * sld;
     float* dst = m.scales.as<float>() + size_t(row / 128) * sld;
     if (p.s.dtype == "F32") {
       cuda_check(cudaMemcpyAsync(dst, sraw.get(), sc * 4, cudaMemcpyDeviceToDevice, stream_), "scale copy");
@@ -256,7 +302,7 @@ PackedMatrix QwenNativeEngine::load_fp8(WeightSource& ws, const std::vector<std:
       throw std::runtime_error("scale tensor dtype " + p.s.dtype + " is not supported");
     }
     cuda_check(cudaStreamSynchronize(stream_), "fp8 prepack");   // raw buffers die at scope end
-    stats_.weight_bytes += p.w.nbytes + sc * 4;
+    stats_.weight_bytes += size_t(p.rows) * p.cols + sc * 4;
     row += n;
   }
   return m;
@@ -264,7 +310,9 @@ PackedMatrix QwenNativeEngine::load_fp8(WeightSource& ws, const std::vector<std:
 
 void QwenNativeEngine::load(WeightSource& ws) {
   const std::string root = "model.language_model.";
+  const int W = std::max(1, opt_.tp_world), R = opt_.tp_rank;
   {
+    // the embedding table is replicated (1.5 GB at the 27B shape): the lookup then needs no collective
     TensorView e = need(ws, root + "embed_tokens.weight");
     if (e.dtype != "BF16") throw std::runtime_error("embedding table must be BF16");
     embed_.reset(e.nbytes);
@@ -273,7 +321,13 @@ void QwenNativeEngine::load(WeightSource& ws) {
   }
   final_norm_ = load_vector(ws, root + "norm.weight", false);
   TensorView probe;
-  lm_head_ = load_bf16(ws, {ws.get("lm_head.weight", probe) ? "lm_head.weight" : root + "embed_tokens.weight"});
+  lm_head_ = load_bf16(ws, {{ws.get("lm_head.weight", probe) ? "lm_head.weight" : root + "embed_tokens.weight",
+                             vocab_lo_, vocab_n_}});
+  const long long I = cfg_.intermediate_size, Il = inter_;
+  const long long kd_full = (long long)cfg_.linear_num_key_heads * kHead, vd_full = (long long)cfg_.linear_num_value_heads * kHead;
+  const int gate_mul = cfg_.attn_output_gate ? 2 : 1;
+  const long long qrows = (long long)hq_ * kHead * gate_mul, kvrows = (long long)hkv_ * kHead;
+  (void)I; (void)W;
   layers_.resize(n_layers_);
   for (int i = 0; i < n_layers_; ++i) {
     QwenLayer& L = layers_[i];
@@ -281,27 +335,50 @@ void QwenNativeEngine::load(WeightSource& ws) {
     L.linear = cfg_.layer_types.at(i) == "linear_attention";
     L.in_ln = load_vector(ws, p + "input_layernorm.weight", false);
     L.post_ln = load_vector(ws, p + "post_attention_layernorm.weight", false);
-    L.gate_up = load_fp8(ws, {p + "mlp.gate_proj", p + "mlp.up_proj"});
-    L.down = load_fp8(ws, {p + "mlp.down_proj"});
+    L.gate_up = load_fp8(ws, {{p + "mlp.gate_proj", R * Il, Il}, {p + "mlp.up_proj", R * Il, Il}});
+    L.down = load_fp8(ws, {{p + "mlp.down_proj", 0, -1, R * Il, Il}});
     if (L.linear) {
       const std::string a = p + "linear_attn.";
-      L.proj = load_fp8(ws, {a + "in_proj_qkv", a + "in_proj_z"});
-      L.out = load_fp8(ws, {a + "out_proj"});
-      L.ab = load_bf16(ws, {a + "in_proj_a.weight", a + "in_proj_b.weight"});
-      L.conv_w = load_vector(ws, a + "conv1d.weight", false);
-      L.a_log = load_vector(ws, a + "A_log", true);
-      L.dt_bias = load_vector(ws, a + "dt_bias", true);
+      // in_proj_qkv holds q | k | v row blocks: each block is split over the ranks, like the conv channels
+      L.proj = load_fp8(ws, {{a + "in_proj_qkv", R * (long long)kd_, kd_}, {a + "in_proj_qkv", kd_full + R * (long long)kd_, kd_},
+                             {a + "in_proj_qkv", 2 * kd_full + R * (long long)vd_, vd_}, {a + "in_proj_z", R * (long long)vd_, vd_}});
+      L.out = load_fp8(ws, {{a + "out_proj", 0, -1, R * (long long)vd_, vd_}});
+      L.ab = load_bf16(ws, {{a + "in_proj_a.weight", R * (long long)hv_, hv_}, {a + "in_proj_b.weight", R * (long long)hv_, hv_}});
+      {
+        // conv1d.weight [2kd + vd, 1, kw]: the same three channel blocks
+        TensorView cv = need(ws, a + "conv1d.weight");
+        if (cv.dtype != "BF16") throw std::runtime_error("conv1d.weight must be BF16");
+        const size_t kwb = size_t(cfg_.linear_conv_kernel_dim) * 2;
+        L.conv_w.reset(size_t(cw_) * kwb);
+        const long long blk[3][2] = {{R * (long long)kd_, kd_}, {kd_full + R * (long long)kd_, kd_}, {2 * kd_full + R * (long long)vd_, vd_}};
+        size_t off = 0;
+        for (auto& b : blk) {
+          cuda_check(cudaMemcpyAsync(L.conv_w.as<uint8_t>() + off, reinterpret_cast<const uint8_t*>(cv.data) + size_t(b[0]) * kwb,
+                                     size_t(b[1]) * kwb, cudaMemcpyHostToDevice, stream_), "conv upload");
+          off += size_t(b[1]) * kwb;
+        }
+        cuda_check(cudaStreamSynchronize(stream_), "conv upload");
+        stats_.weight_bytes += off;
+        (void)vd_full;
+      }
+      L.a_log = load_vector(ws, a + "A_log", true, R * (long long)hv_, hv_);
+      L.dt_bias = load_vector(ws, a + "dt_bias", true, R * (long long)hv_, hv_);
       L.gdn_norm = load_vector(ws, a + "norm.weight", false);
       L.cache_index = n_lin_++;
     } else {
       const std::string a = p + "self_attn.";
-      L.proj = load_fp8(ws, {a + "q_proj", a + "k_proj", a + "v_proj"});
-      L.out = load_fp8(ws, {a + "o_proj"});
+      L.proj = load_fp8(ws, {{a + "q_proj", R * qrows, qrows}, {a + "k_proj", R * kvrows, kvrows}, {a + "v_proj", R * kvrows, kvrows}});
+      L.out = load_fp8(ws, {{a + "o_proj", 0, -1, R * (long long)hq_ * kHead, (long long)hq_ * kHead}});
       L.q_norm = load_vector(ws, a + "q_norm.weight", false);
       L.k_norm = load_vector(ws, a + "k_norm.weight", false);
       L.cache_index = n_full_++;
     }
   }
+}
+
+// Row-parallel outputs: sum over the ranks (bf16, in place; NCCL on the engine's stream).
+void QwenNativeEngine::reduce_rows(void* buf, int T) {
+  if (tp_.active()) tp_.all_reduce_bf16(buf, size_t(T) * size_t(cfg_.hidden_size), stream_);
 }
 
 // ------------------------------------------------------------------------------------------------ slots
@@ -367,7 +444,7 @@ void QwenNativeEngine::linear_stream(const void* xq, const float* inv_c, const P
 int32_t QwenNativeEngine::forward_prefill(int slot, const int32_t* tokens, int T, int64_t pos0, bool want_token) {
   Scratch& s = *s_;
   if (T > s.rows) throw std::runtime_error("prefill chunk exceeds the scratch capacity");
-  const int bs = opt_.block_tokens, H = int(cfg_.hidden_size), I = int(cfg_.intermediate_size);
+  const int bs = opt_.block_tokens, H = int(cfg_.hidden_size), I = inter_;
   const float eps = float(cfg_.rms_norm_eps);
   upload_block_rows();
   std::vector<int32_t>& hb = s.host_i32;
@@ -405,6 +482,7 @@ int32_t QwenNativeEngine::forward_prefill(int slot, const int32_t* tokens, int T
       rc(b200_gated_rmsnorm(s.core.get(), s.proj.as<uint8_t>() + size_t(cw_) * 2, L.gdn_norm.get(), s.y.get(),
                             (long long)T * hv_, kHead, eps, hv_, ldp, stream_), "gated_rmsnorm");
       linear(s.y.get(), L.out, s.d_attn.get(), T);
+      reduce_rows(s.d_attn.get(), T);
     } else {
       const int gate_mul = cfg_.attn_output_gate ? 2 : 1;
       const int qw = hq_ * kHead * gate_mul;
@@ -419,11 +497,13 @@ int32_t QwenNativeEngine::forward_prefill(int slot, const int32_t* tokens, int T
                           meta + 1, meta + 2, 1, T, T, max_blocks_per_seq_, num_blocks_, bs, hq_, hkv_,
                           1.0f / std::sqrt(float(kHead)), s.status.as<int>(), stream_), "gqa_prefill");
       linear(s.attn.get(), L.out, s.d_attn.get(), T);
+      reduce_rows(s.d_attn.get(), T);
     }
     rc(b200_rmsnorm(s.h.get(), s.d_attn.get(), nullptr, 0, L.post_ln.get(), s.x.get(), T, H, eps, 1, 1, stream_), "rmsnorm");
     linear(s.x.get(), L.gate_up, s.gu.get(), T);
     rc(b200_silu_mul(s.gu.get(), s.act.get(), T, I, stream_), "silu_mul");
     linear(s.act.get(), L.down, s.d_mlp.get(), T);
+    reduce_rows(s.d_mlp.get(), T);
     delta = s.d_mlp.get();
   }
   lengths_[slot] = pos0 + T;
@@ -433,10 +513,14 @@ int32_t QwenNativeEngine::forward_prefill(int slot, const int32_t* tokens, int T
   const uint8_t* dlast = delta ? reinterpret_cast<const uint8_t*>(delta) + size_t(T - 1) * H * 2 : nullptr;
   rc(b200_rmsnorm(last, dlast, nullptr, 0, final_norm_.get(), s.x.get(), 1, H, eps, 1, dlast ? 1 : 0, stream_), "final norm");
   linear(s.x.get(), lm_head_, nullptr, 1, s.logits.as<float>());
-  rc(b200_argmax(s.logits.get(), 1, int(cfg_.vocab_size), int(cfg_.vocab_size), 1, 0, s.next_idx.as<int>(),
-                 s.next_val.as<float>(), stream_), "argmax", 2);
+  rc(b200_argmax(s.logits.get(), 1, vocab_n_, vocab_n_, 1, vocab_lo_, s.next_idx.as<int>(), s.next_val.as<float>(), stream_),
+     "argmax", 2);
   int32_t tok = -1;
-  cuda_check(cudaMemcpyAsync(&tok, s.next_idx.get(), 4, cudaMemcpyDeviceToHost, stream_), "token readback");
+  if (tp_.active()) {
+    tok = tp_.argmax_merge(s.next_val.as<float>(), s.next_idx.as<int32_t>(), 1, s.merge.get(), stream_).at(0);
+  } else {
+    cuda_check(cudaMemcpyAsync(&tok, s.next_idx.get(), 4, cudaMemcpyDeviceToHost, stream_), "token readback");
+  }
   check_status("prefill");
   if (opt_.sampling.temperature > 0.f) sample_rows(1, &tok);
   return tok;
@@ -448,7 +532,7 @@ void QwenNativeEngine::forward_decode(const std::vector<int>& slots, const std::
   Scratch& s = *s_;
   const int B = int(slots.size());
   if (B <= 0 || B > 64 || B > s.rows) throw std::runtime_error("decode batch must hold 1..64 sequences");
-  const int bs = opt_.block_tokens, H = int(cfg_.hidden_size), I = int(cfg_.intermediate_size), V = int(cfg_.vocab_size);
+  const int bs = opt_.block_tokens, H = int(cfg_.hidden_size), I = inter_, V = vocab_n_;
   const float eps = float(cfg_.rms_norm_eps);
   for (int i = 0; i < B; ++i)
     if (!reserve(slots[i], lengths_.at(slots[i]) + 1)) throw std::runtime_error("KV cache exhausted");
@@ -482,7 +566,7 @@ void QwenNativeEngine::forward_decode(const std::vector<int>& slots, const std::
   const int qw = hq_ * kHead * gate_mul;
   const int kw = int(cfg_.linear_conv_kernel_dim);
 
-  rc(b200_embedding(s.ids.as<int>(), embed_.get(), s.h.get(), B, H, 0, V, stream_), "embedding");
+  rc(b200_embedding(s.ids.as<int>(), embed_.get(), s.h.get(), B, H, 0, int(cfg_.vocab_size), stream_), "embedding");
   const void* delta = nullptr;
   for (int li = 0; li < n_layers_; ++li) {
     QwenLayer& L = layers_[li];
@@ -532,6 +616,7 @@ void QwenNativeEngine::forward_decode(const std::vector<int>& slots, const std::
     if (fused) {
       rc(b200_act_split_e4m3(mix_out, B, L.out.k, terms, s.xq2.get(), s.inv_c2.as<float>(), stream_), "act_split");
       linear_stream(s.xq2.get(), s.inv_c2.as<float>(), L.out, s.d_attn.get(), B);
+      reduce_rows(s.d_attn.get(), B);
       rc(b200_rmsnorm_split(s.h.get(), s.d_attn.get(), L.post_ln.get(), nullptr, s.xq.get(), s.inv_c.as<float>(), B, H, eps,
                             1, terms, stream_), "rmsnorm_split");
       linear_stream(s.xq.get(), s.inv_c.as<float>(), L.gate_up, s.gu.get(), B);
@@ -539,18 +624,24 @@ void QwenNativeEngine::forward_decode(const std::vector<int>& slots, const std::
       linear_stream(s.xq2.get(), s.inv_c2.as<float>(), L.down, s.d_mlp.get(), B);
     } else {
       linear(mix_out, L.out, s.d_attn.get(), B);
+      reduce_rows(s.d_attn.get(), B);
       rc(b200_rmsnorm(s.h.get(), s.d_attn.get(), nullptr, 0, L.post_ln.get(), s.x.get(), B, H, eps, 1, 1, stream_), "rmsnorm");
       linear(s.x.get(), L.gate_up, s.gu.get(), B);
       rc(b200_silu_mul(s.gu.get(), s.act.get(), B, I, stream_), "silu_mul");
       linear(s.act.get(), L.down, s.d_mlp.get(), B);
     }
+    reduce_rows(s.d_mlp.get(), B);
     delta = s.d_mlp.get();
   }
   rc(b200_rmsnorm(s.h.get(), delta, nullptr, 0, final_norm_.get(), s.x.get(), B, H, eps, 1, delta ? 1 : 0, stream_), "final norm");
   linear(s.x.get(), lm_head_, nullptr, B, s.logits.as<float>());
-  rc(b200_argmax(s.logits.get(), 1, V, V, B, 0, s.next_idx.as<int>(), s.next_val.as<float>(), stream_), "argmax", 2);
+  rc(b200_argmax(s.logits.get(), 1, V, V, B, vocab_lo_, s.next_idx.as<int>(), s.next_val.as<float>(), stream_), "argmax", 2);
   next.resize(B);
-  cuda_check(cudaMemcpyAsync(next.data(), s.next_idx.get(), size_t(B) * 4, cudaMemcpyDeviceToHost, stream_), "token readback");
+  if (tp_.active()) {
+    next = tp_.argmax_merge(s.next_val.as<float>(), s.next_idx.as<int32_t>(), B, s.merge.get(), stream_);
+  } else {
+    cuda_check(cudaMemcpyAsync(next.data(), s.next_idx.get(), size_t(B) * 4, cudaMemcpyDeviceToHost, stream_), "token readback");
+  }
   check_status("decode");
   if (opt_.sampling.temperature > 0.f) sample_rows(B, next.data());
   for (int i = 0; i < B; ++i) lengths_[slots[i]] += 1;
@@ -616,7 +707,8 @@ std::vector<int32_t> QwenNativeEngine::generate(const std::vector<int32_t>& prom
 }
 
 std::vector<std::pair<int32_t, float>> QwenNativeEngine::last_topk(int k) {
-  const size_t V = size_t(cfg_.vocab_size);
+  // multi-rank: this rank's vocabulary shard only (ids are global)
+  const size_t V = size_t(vocab_n_);
   std::vector<float> row(V);
   cuda_check(cudaMemcpy(row.data(), s_->logits.get(), V * 4, cudaMemcpyDeviceToHost), "logits readback");
   std::vector<int32_t> idx(V);
@@ -624,7 +716,7 @@ std::vector<std::pair<int32_t, float>> QwenNativeEngine::last_topk(int k) {
   k = int(std::min<size_t>(size_t(std::max(1, k)), V));
   std::partial_sort(idx.begin(), idx.begin() + k, idx.end(), [&](int32_t a, int32_t b) { return row[a] > row[b] || (row[a] == row[b] && a < b); });
   std::vector<std::pair<int32_t, float>> out;
-  for (int i = 0; i < k; ++i) out.emplace_back(idx[i], row[idx[i]]);
+  for (int i = 0; i < k; ++i) out.emplace_back(idx[i] + vocab_lo_, row[idx[i]]);
   return out;
 }
 

@@ -1,4 +1,8 @@
-// Native single-GPU engine for the Qwen-style hybrid model (Gated-DeltaNet + gated GQA layers, FP8 block-128
+// Native engine for the Qwen-style hybrid model, one process per GPU: with tp_world > 1 every rank loads its shard
+// (heads, feed-forward width and vocabulary rows split over the ranks, row-parallel outputs summed with NCCL, arg-max
+// merged over the vocabulary shards; sharding rules as cpp_engine/include/qwen_weights.hpp:15-31) and all ranks make the
+// same calls in the same order (rank 0 fans requests out, see main.cpp).
+// Single-GPU engine for the Qwen-style hybrid model (Gated-DeltaNet + gated GQA layers, FP8 block-128
 // weights): loads a safetensors checkpoint through WeightSource, repacks the FP8 matrices on the device into the
 // GEMM's tile-major layout, owns the paged KV cache / recurrent state and drives the kernel library through its
 // C interface.  It implements the slot / paged-KV / batch interface the scheduler drives, so the same object
@@ -18,6 +22,7 @@
 #include "../core/qwen_config.hpp"
 #include "../core/sampler.hpp"
 #include "../core/weight_source.hpp"
+#include "../comm/tp_comm.hpp"
 
 namespace pocket {
 
@@ -84,6 +89,8 @@ struct QwenEngineOptions {
   std::vector<int32_t> eos_tokens;
   HostSamplingParams sampling;   // temperature 0 = greedy (arg-max on the device, 4 bytes read back per sequence)
   uint64_t seed = 0;
+  int tp_world = 1, tp_rank = 0;   // tensor parallelism: this process is rank tp_rank of tp_world
+  std::string nccl_id_path;        // file through which rank 0 hands the NCCL id to the others
 };
 
 struct QwenEngineStats {
@@ -121,9 +128,13 @@ class QwenNativeEngine : public InferenceEngine {
  private:
   struct Scratch;
   void load(WeightSource& ws);
-  PackedMatrix load_fp8(WeightSource& ws, const std::vector<std::string>& bases);
-  PackedMatrix load_bf16(WeightSource& ws, const std::vector<std::string>& names);
-  DeviceBuffer load_vector(WeightSource& ws, const std::string& name, bool to_f32);
+  // a [rows, cols] window of a checkpoint matrix (counts in elements; n < 0 = to the end)
+  struct Piece { std::string name; long long row0 = 0, rows = -1, col0 = 0, cols = -1; };
+  PackedMatrix load_fp8(WeightSource& ws, const std::vector<Piece>& pieces);
+  PackedMatrix load_bf16(WeightSource& ws, const std::vector<Piece>& pieces);
+  DeviceBuffer load_vector(WeightSource& ws, const std::string& name, bool to_f32, long long first = 0, long long count = -1);
+  DeviceBuffer upload_window(const TensorView& v, size_t elem, long long row0, long long rows, long long col0, long long cols);
+  void reduce_rows(void* buf, int T);
   void linear(const void* x, const PackedMatrix& w, void* out, int T, float* out_f32 = nullptr);
   void linear_stream(const void* xq, const float* inv_c, const PackedMatrix& w, void* out, int T);
   int32_t forward_prefill(int slot, const int32_t* tokens, int T, int64_t pos0, bool want_token);
@@ -140,7 +151,9 @@ class QwenNativeEngine : public InferenceEngine {
   QwenEngineStats stats_;
   cudaStream_t stream_ = nullptr;
   int n_layers_ = 0, n_full_ = 0, n_lin_ = 0;
-  int hq_ = 0, hkv_ = 0, hv_ = 0, hk_ = 0, kd_ = 0, vd_ = 0, cw_ = 0, rot_ = 0;
+  int hq_ = 0, hkv_ = 0, hv_ = 0, hk_ = 0, kd_ = 0, vd_ = 0, cw_ = 0, rot_ = 0;   // per-rank head counts / widths
+  int inter_ = 0, vocab_lo_ = 0, vocab_n_ = 0;                                      // per-rank feed-forward width, vocabulary rows
+  TpComm tp_;
   bool stream_ok_ = false;
 
   std::vector<QwenLayer> layers_;

@@ -35,3 +35,51 @@ def test_pipeline_worker(world):
            "--master-addr", "127.0.0.1", "--master-port", str(29700 + world), os.path.join(HERE, "pp_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
     assert r.returncode == 0 and "PP_WORKER_OK" in r.stdout, (r.stdout[-3000:], r.stderr[-8000:])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.parametrize("world", [2])
+def test_native_executable_tensor_parallel(world):
+    """``pocketllm_engine --tp-world N``: one process per GPU, NCCL id through a file, rank 0 reads stdin and fans each
+    request out over the command channel.  Greedy tokens against the one-rank executable on the same checkpoint."""
+    import re
+    import tempfile
+
+    from deepseek_v4_2080ti_b200.formats import safetensors_io
+    from deepseek_v4_2080ti_b200.models import qwen_hybrid as qh
+
+    exe = os.path.join(os.path.dirname(HERE), "deepseek_v4_2080ti_b200", "bin", "pocketllm_engine")
+    if not os.path.isfile(exe):
+        pytest.skip("native executable not built")
+    cfg = qh.QwenHybridConfig(vocab_size=512, hidden_size=256, intermediate_size=256 * world, num_hidden_layers=4,
+                              num_attention_heads=2 * world, num_key_value_heads=world, linear_num_key_heads=world,
+                              linear_num_value_heads=2 * world, max_position_embeddings=4096, full_attention_interval=2)
+    gen = torch.Generator().manual_seed(17)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gen, dtype=torch.int32).tolist() for n in (90, 41)]
+    lines = "".join("6 " + " ".join(map(str, p)) + "\n" for p in prompts)
+    toks = lambda out: [[int(t) for t in re.search(r"(?<![a-z_])tokens=([0-9,]+)", l).group(1).split(",")]
+                        for l in out.splitlines() if l.startswith("qwen_persistent_result=1")]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    with tempfile.TemporaryDirectory() as d:
+        safetensors_io.write_checkpoint(d, qh.synth_state(cfg, 0, "cpu", std=0.05), config_json=cfg.to_json())
+        base = [exe, "--ckpt", d, "--qwen-persistent-stdin", "--max-context", "256"]
+        one = subprocess.run(base, input=lines, capture_output=True, text=True, timeout=300, env=env)
+        assert one.returncode == 0, one.stderr[-800:]
+        want = toks(one.stdout)
+        assert len(want) == 2
+        idp = os.path.join(d, "nccl_id")
+        procs = []
+        for r in range(world):
+            procs.append(subprocess.Popen(base + ["--tp-world", str(world), "--tp-rank", str(r), "--device", str(r),
+                                                  "--nccl-id-path", idp],
+                                          stdin=subprocess.PIPE if r == 0 else subprocess.DEVNULL, stdout=subprocess.PIPE,
+                                          stderr=subprocess.PIPE, text=True, env=env))
+        out0, err0 = procs[0].communicate(lines, timeout=300)
+        for p in procs[1:]:
+            p.wait(timeout=60)
+        assert procs[0].returncode == 0 and all(p.returncode == 0 for p in procs[1:]), (err0[-800:],)
+        assert f"tp_world={world}" in out0
+        got = toks(out0)
+        assert len(got) == 2 and all(len(g) == 6 for g in got)
+        # reduction order differs from the one-rank run: the first tokens agree, a later near-tie may not
+        assert [g[:2] for g in got] == [w[:2] for w in want], (got, want)
