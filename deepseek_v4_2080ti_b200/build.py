@@ -38,6 +38,10 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH + ["-lineinfo", "-O3", "-std=c++17", "--use_fast_math", "-Xcompiler", "-fPIC",
                      "-Xcompiler", "-fvisibility=default", "--expt-relaxed-constexpr"]
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-pthread"]
+# A compiler that links its C++ runtime statically would otherwise export that runtime's symbols from every module;
+# in a process that has already loaded another libstdc++ (torch) the dynamic linker then binds half of a stream or
+# locale object to one runtime and half to the other.
+PRIVATE_RUNTIME = ["-Wl,--exclude-libs,ALL"]
 
 
 def _run(cmd: list[str]) -> None:
@@ -102,7 +106,7 @@ def build_core(jobs: int | None = None) -> dict[str, Path]:
         core_objs = list(ex.map(_compile_cpp, core_srcs))
     core_lib = LIB / "libb200_core.so"
     if (not core_lib.exists()) or any(o.stat().st_mtime > core_lib.stat().st_mtime for o in core_objs):
-        _run([CXX, "-shared", "-o", str(core_lib), *map(str, core_objs), "-pthread"])
+        _run([CXX, "-shared", *PRIVATE_RUNTIME, "-o", str(core_lib), *map(str, core_objs), "-pthread"])
     products["core"] = core_lib
 
     bind_src = CSRC / "bindings" / "core_bindings.cpp"
@@ -115,7 +119,7 @@ def build_core(jobs: int | None = None) -> dict[str, Path]:
         bobj = _compile_cpp(bind_src, inc)
         if (not mod.exists()) or bobj.stat().st_mtime > mod.stat().st_mtime or \
                 core_lib.stat().st_mtime > mod.stat().st_mtime:
-            _run([CXX, "-shared", "-o", str(mod), str(bobj), *map(str, core_objs), "-pthread"])
+            _run([CXX, "-shared", *PRIVATE_RUNTIME, "-o", str(mod), str(bobj), *map(str, core_objs), "-pthread"])
         products["pybind"] = mod
 
     main_src = CSRC / "engine" / "main.cpp"
@@ -141,7 +145,7 @@ def build_core(jobs: int | None = None) -> dict[str, Path]:
             lib_objs = [o for o in eng_objs if not o.name.startswith("main.")]
             if (not emod.exists()) or any(o.stat().st_mtime > emod.stat().st_mtime for o in [eobj, *lib_objs, *core_objs]) \
                     or (kern.exists() and kern.stat().st_mtime > emod.stat().st_mtime):
-                _run([CXX, "-shared", "-o", str(emod), str(eobj), *map(str, lib_objs), *map(str, core_objs), "-L", str(LIB),
+                _run([CXX, "-shared", *PRIVATE_RUNTIME, "-o", str(emod), str(eobj), *map(str, lib_objs), *map(str, core_objs), "-L", str(LIB),
                       "-lb200_kernels", "-Wl,-rpath,$ORIGIN/lib", "-L/usr/local/cuda/lib64", "-lcudart", "-lnccl", "-ldl",
                       "-pthread"])
             products["engine_pybind"] = emod
@@ -177,7 +181,7 @@ def build_cpu() -> Path | None:
     objs = [_compile_cpp(s, flags, tag=".cpu") for s in srcs]
     out = LIB / "libb200_cpu.so"
     if (not out.exists()) or any(o.stat().st_mtime > out.stat().st_mtime for o in objs):
-        _run([CXX, "-shared", "-o", str(out), *map(str, objs), "-pthread"])
+        _run([CXX, "-shared", *PRIVATE_RUNTIME, "-o", str(out), *map(str, objs), "-pthread"])
     return out
 
 

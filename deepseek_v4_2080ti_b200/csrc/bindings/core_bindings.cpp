@@ -15,6 +15,7 @@
 #include "core/cmd_channel.hpp"
 #include "core/gguf_reader.hpp"
 #include "core/json_lite.hpp"
+#include "core/model_config.hpp"
 #include "core/qwen_config.hpp"
 #include "core/qwen_weight_map.hpp"
 #include "core/safetensors_reader.hpp"
@@ -282,6 +283,20 @@ PYBIND11_MODULE(pocketllm_cpp, m) {
       .def_readonly("partial_rotary_factor", &QwenConfig::partial_rotary_factor)
       .def_property_readonly("num_full_layers", &QwenConfig::num_full_layers)
       .def_property_readonly("num_linear_layers", &QwenConfig::num_linear_layers);
+  py::class_<MoeModelConfig>(m, "MoeModelConfig")
+      .def_static("from_gguf", [](const GGUFReader& g) { return MoeModelConfig::from_gguf(g); })
+      .def_static("from_gguf_file", [](const std::string& path) { GGUFReader g(path); return MoeModelConfig::from_gguf(g); })
+      .def_static("from_hf_json_text", [](const std::string& s) { return MoeModelConfig::from_hf_json(Json::parse(s)); })
+      .def_static("from_hf_dir", &MoeModelConfig::from_hf_dir)
+      .def("describe", &MoeModelConfig::describe)
+      .def("to_json_text", [](const MoeModelConfig& c) { return c.to_json().dump(); })
+      .def("problems", &MoeModelConfig::problems, py::arg("tp_world") = 1, py::arg("ep_world") = 1)
+      .def_property_readonly("is_mla", &MoeModelConfig::is_mla)
+      .def_property_readonly("has_indexer", &MoeModelConfig::has_indexer)
+      .def_property_readonly("kv_bytes_per_token_layer", &MoeModelConfig::kv_bytes_per_token_layer)
+      .def_readonly("architecture", &MoeModelConfig::architecture)
+      .def_readonly("compress_ratios", &MoeModelConfig::compress_ratios)
+      .def_readonly("swiglu_clamp_exp", &MoeModelConfig::swiglu_clamp_exp);
   m.def("is_qwen3_5_checkpoint", [](const std::string& dir) {
     try {
       return QwenConfig::is_qwen3_5(Json::parse(read_text_file(dir + "/config.json")));

@@ -4,6 +4,9 @@
 //   --dump-config              print the parsed model configuration and exit
 //   --inspect [--grep S]       list checkpoint tensors (name, dtype, shape, bytes)
 //   --inspect-tensor NAME      print one tensor's header and its first values
+//   --model-config PATH        describe a sparse-attention MoE checkpoint (PATH = a .gguf file or a directory with
+//                              config.json): every field that is set, then the problems of the shape on
+//                              --tp-world x --ep-world ranks; needs no --ckpt
 //   --qwen-audit [--qwen-audit-strict] [--tp-world N]   check the checkpoint against the weight map (no GPU needed):
 //                              missing / unexpected tensors, shapes, dtypes, tensor-parallel divisibility
 //   --kv-cache-dtype auto|bf16|fp16   accepted; the 8-bit cache layouts are refused with a pointer to the Python runtime
@@ -34,6 +37,8 @@
 
 #include "../core/batch_scheduler.hpp"
 #include "../core/cmd_channel.hpp"
+#include "../core/gguf_reader.hpp"
+#include "../core/model_config.hpp"
 #include "../core/openai_server.hpp"
 #include "../core/qwen_weight_map.hpp"
 #include "../core/safetensors_reader.hpp"
@@ -44,9 +49,9 @@ using namespace pocket;
 namespace {
 
 struct Args {
-  std::string ckpt, grep, tensor, token_ids, token_file, eos, host = "127.0.0.1", python = "python", sidecar_gguf,
+  std::string ckpt, model_config, grep, tensor, token_ids, token_file, eos, host = "127.0.0.1", python = "python", sidecar_gguf,
       chat_family = "deepseek_v4", served_name = "pocketllm";
-  int port = 8000, tp_world = 1, tp_rank = 0;
+  int port = 8000, tp_world = 1, tp_rank = 0, ep_world = 1;
   std::string nccl_id_path;
   bool serve = false, audit = false, audit_strict = false;
   bool dump_config = false, inspect = false, context_info = false, smoke = false, bench = false, persistent = false,
@@ -96,6 +101,8 @@ bool parse(int argc, char** argv, Args& a) {
     if (arg == "--ckpt" || arg == "--model") a.ckpt = val("--ckpt");
     else if (arg == "--dump-config") a.dump_config = true;
     else if (arg == "--inspect") a.inspect = true;
+    else if (arg == "--model-config") a.model_config = val("--model-config");
+    else if (arg == "--ep-world") a.ep_world = std::atoi(val("--ep-world"));
     else if (arg == "--grep") a.grep = val("--grep");
     else if (arg == "--inspect-tensor" || arg == "--tensor") a.tensor = val("--inspect-tensor");
     else if (arg == "--context-info") a.context_info = true;
@@ -145,7 +152,7 @@ bool parse(int argc, char** argv, Args& a) {
     else if (arg == "-h" || arg == "--help") return false;
     else throw std::runtime_error("unknown argument " + arg);
   }
-  return !a.ckpt.empty();
+  return !a.ckpt.empty() || !a.model_config.empty();
 }
 
 std::vector<int32_t> prompt_of(const Args& a, int64_t vocab) {
@@ -158,6 +165,25 @@ std::vector<int32_t> prompt_of(const Args& a, int64_t vocab) {
     p.push_back(int32_t(x % uint64_t(vocab)));
   }
   return p;
+}
+
+int describe_model(const Args& a) {
+  const std::string& p = a.model_config;
+  const bool gguf = p.size() > 5 && p.compare(p.size() - 5, 5, ".gguf") == 0;
+  MoeModelConfig c;
+  if (gguf) {
+    GGUFReader file(p);
+    c = MoeModelConfig::from_gguf(file);
+  } else {
+    c = MoeModelConfig::from_hf_dir(p);
+  }
+  std::printf("%s\n", c.describe().c_str());
+  std::printf("kv_bytes_per_token_layer=%llu mla=%d indexer=%d\n", (unsigned long long)c.kv_bytes_per_token_layer(),
+              int(c.is_mla()), int(c.has_indexer()));
+  const auto probs = c.problems(std::max(1, a.tp_world), std::max(1, a.ep_world));
+  for (const auto& q : probs) std::printf("problem: %s\n", q.c_str());
+  std::printf("model_config_ok=%d\n", int(probs.empty()));
+  return probs.empty() ? 0 : 3;
 }
 
 int inspect(const Args& a) {
@@ -194,6 +220,7 @@ int main(int argc, char** argv) {
   Args a;
   try {
     if (!parse(argc, argv, a)) { usage(); return 2; }
+    if (!a.model_config.empty()) return describe_model(a);
     if (a.inspect || !a.tensor.empty()) return inspect(a);
     QwenConfig cfg = QwenConfig::from_file(a.ckpt + "/config.json");
     if (a.dump_config) {

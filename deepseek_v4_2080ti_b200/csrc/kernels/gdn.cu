@@ -629,6 +629,21 @@ gdn_scan_kernel(PrepOut w, float* __restrict__ state, __nv_bfloat16* __restrict_
       }
   prefetch_wq(0);
 
+  // U rows of this thread and the chunk's decay are plain global loads on the serial chain: both are fetched one
+  // chunk ahead (into registers) so that their latency is paid under the previous chunk's MMAs
+  auto load_u = [&](int c, float2 (&dst)[4][2]) {
+    const int t0 = c * C;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf)
+        dst[nt][hf] = *reinterpret_cast<const float2*>(w.U + ((size_t)(t0 + 16 * warp + g + 8 * hf) * Hv + h) * DV +
+                                                        sl * SL + 8 * nt + 2 * tig);
+  };
+  float2 u_next[4][2];
+  load_u(0, u_next);
+  float gl_next = w.Gl[h];
+
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * C;
     cp_async_wait_all();
@@ -642,78 +657,50 @@ gdn_scan_kernel(PrepOut w, float* __restrict__ state, __nv_bfloat16* __restrict_
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf)
-        u[nt][hf] = *reinterpret_cast<const float2*>(w.U + ((size_t)(t0 + 16 * warp + g + 8 * hf) * Hv + h) * DV + sl * SL +
-                                                      8 * nt + 2 * tig);
-    // v_new = U - W S
-    float acc[4][4];
+      for (int hf = 0; hf < 2; ++hf) u[nt][hf] = u_next[nt][hf];
+    const float gl = gl_next;
+    if (more) {
+      load_u(c + 1, u_next);
+      gl_next = w.Gl[(size_t)(c + 1) * Hv + h];
+    }
+    // v_new = U - W S and O = Qg S read the same state operand: one pass over the key dim feeds both (eight
+    // independent accumulator chains per warp, one shared-memory read of the state fragment for two MMAs)
+    float accv[4][4], acc[4][4];
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+      for (int e = 0; e < 4; ++e) { accv[nt][e] = 0.f; acc[nt][e] = 0.f; }
 #pragma unroll
     for (int ks = 0; ks < DK / 16; ++ks) {
-      uint32_t a[4];
-      load_a(a, bW, WS, 16 * warp, 16 * ks, g, tig);
+      uint32_t aw[4], aq[4];
+      load_a(aw, bW, WS, 16 * warp, 16 * ks, g, tig);
+      load_a(aq, bQ, WS, 16 * warp, 16 * ks, g, tig);
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) {
         const __half* bp = sS + (8 * nt + g) * WS + 16 * ks + 2 * tig;
-        mma16816(acc[nt], a, *reinterpret_cast<const uint32_t*>(bp), *reinterpret_cast<const uint32_t*>(bp + 8));
+        const uint32_t s0 = *reinterpret_cast<const uint32_t*>(bp), s1 = *reinterpret_cast<const uint32_t*>(bp + 8);
+        mma16816(accv[nt], aw, s0, s1);
+        mma16816(acc[nt], aq, s0, s1);
       }
     }
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
       const int n = 8 * nt + 2 * tig, r = 16 * warp + g;
-      sV[n * TS + r] = __float2half_rn(u[nt][0].x - acc[nt][0]);
-      sV[(n + 1) * TS + r] = __float2half_rn(u[nt][0].y - acc[nt][1]);
-      sV[n * TS + r + 8] = __float2half_rn(u[nt][1].x - acc[nt][2]);
-      sV[(n + 1) * TS + r + 8] = __float2half_rn(u[nt][1].y - acc[nt][3]);
+      sV[n * TS + r] = __float2half_rn(u[nt][0].x - accv[nt][0]);
+      sV[(n + 1) * TS + r] = __float2half_rn(u[nt][0].y - accv[nt][1]);
+      sV[n * TS + r + 8] = __float2half_rn(u[nt][1].x - accv[nt][2]);
+      sV[(n + 1) * TS + r + 8] = __float2half_rn(u[nt][1].y - accv[nt][3]);
     }
-    // O = Qg S (needs only the old state: issued before the barrier so it overlaps the other warps' v_new)
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < DK / 16; ++ks) {
-      uint32_t a[4];
-      load_a(a, bQ, WS, 16 * warp, 16 * ks, g, tig);
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-        const __half* bp = sS + (8 * nt + g) * WS + 16 * ks + 2 * tig;
-        mma16816(acc[nt], a, *reinterpret_cast<const uint32_t*>(bp), *reinterpret_cast<const uint32_t*>(bp + 8));
-      }
-    }
-    if (more) cp_async_wait_1(); else cp_async_wait_all();   // this thread's KgT / Aqk copies (the older group) are done
-    __syncthreads();                       // v_new^T, KgT, Aqk complete; every warp is done reading the old state copy
-    // O += Aqk v_new
-#pragma unroll
-    for (int ks = 0; ks < C / 16; ++ks) {
-      uint32_t a[4];
-      load_a(a, bA, TS, 16 * warp, 16 * ks, g, tig);
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-        const __half* bp = sV + (8 * nt + g) * TS + 16 * ks + 2 * tig;
-        mma16816(acc[nt], a, *reinterpret_cast<const uint32_t*>(bp), *reinterpret_cast<const uint32_t*>(bp + 8));
-      }
-    }
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        const int t = t0 + 16 * warp + g + 8 * hf;
-        if (t < T)
-          *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)t * Hv + h) * DV + sl * SL + 8 * nt + 2 * tig) =
-              __floats2bfloat162_rn(acc[nt][2 * hf], acc[nt][2 * hf + 1]);
-      }
-    // S = S e^gl + KgT v_new, then refresh the fp16 operand copy
-    const float gl = w.Gl[(size_t)c * Hv + h];
+    // S e^gl before the barrier: pure register work that overlaps the other warps' v_new
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) sacc[mt][nt][e] *= gl;
+    if (more) cp_async_wait_1(); else cp_async_wait_all();   // this thread's KgT / Aqk copies (the older group) are done
+    __syncthreads();                       // v_new^T, KgT, Aqk complete; every warp is done reading the old state copy
+    // O += Aqk v_new and S += KgT v_new share the v_new^T operand: twelve independent chains over the chunk's tokens
 #pragma unroll
     for (int ks = 0; ks < C / 16; ++ks) {
       uint32_t b0[4], b1[4];
@@ -730,7 +717,12 @@ gdn_scan_kernel(PrepOut w, float* __restrict__ state, __nv_bfloat16* __restrict_
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) mma16816(sacc[mt][nt], a, b0[nt], b1[nt]);
       }
+      uint32_t aa[4];
+      load_a(aa, bA, TS, 16 * warp, 16 * ks, g, tig);
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) mma16816(acc[nt], aa, b0[nt], b1[nt]);
     }
+    // the next chunk starts from the fp16 copy of the new state: publish it first, store the outputs after
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
@@ -740,6 +732,15 @@ gdn_scan_kernel(PrepOut w, float* __restrict__ state, __nv_bfloat16* __restrict_
           const int m = 32 * warp + 16 * mt + g + (e >> 1) * 8, n = 8 * nt + 2 * tig + (e & 1);
           sS[n * WS + m] = __float2half_rn(sacc[mt][nt][e]);
         }
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int t = t0 + 16 * warp + g + 8 * hf;
+        if (t < T)
+          *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)t * Hv + h) * DV + sl * SL + 8 * nt + 2 * tig) =
+              __floats2bfloat162_rn(acc[nt][2 * hf], acc[nt][2 * hf + 1]);
+      }
   }
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt)

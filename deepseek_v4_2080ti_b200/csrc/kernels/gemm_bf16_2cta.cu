@@ -30,7 +30,11 @@
 // Reference behaviour covered: the FP8 -> fp16 dequant + cublasGemmEx prefill path
 // (cpp_engine/backends/cuda/kernels/qwen_half_ops.cu:1199-1349).
 #include <cuda_bf16.h>
+#include <stdlib.h>
 #include <string.h>
+
+#include <mutex>
+#include <vector>
 
 #include "../comm/comm.h"
 #include "../comm/comm_device.cuh"
@@ -115,11 +119,23 @@ struct Params {
   int n_rot, sp_rows;
   int ag_wait, ag_flag_rows;
   unsigned long long budget_ns;
+  int tma_push;           // mode 3: push the staged tile with bulk tensor stores through `OutMaps` (else plain stores)
+  int slot_rows;          // rows of `ldo` elements per (parity, source) data slot
   B200Comm comm;
 };
 
+// One tensor map per owner rank over that rank's whole data region, seen as [16 slots x slot_rows, ldo] bf16 with a
+// box of 32 rows x 64 features (one warp's share of half a staging patch).  Stores only: a load through these maps
+// would be a TMA load from peer memory, which this kernel never issues.
+struct OutMaps {
+  CUtensorMap m[B200_MAX_RANKS];
+};
+
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, Params p) {
+gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                      const __grid_constant__ OutMaps omaps, Params p) {
   extern __shared__ uint8_t smem_raw_base[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_base) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -335,6 +351,51 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             }
           }
         }
+      } else if (p.tma_push) {
+        // Bulk tensor stores: each warp turns 32 rows x 64 features into bf16 in one of its two 4 KB staging boxes
+        // (128-byte rows, 16-byte chunks XOR-ed with row & 7 = the layout SWIZZLE_128B expects), and lane 0 hands the
+        // box to the copy engine, which writes it into the owner's slot - 4 KB per instruction instead of 16 bytes
+        // per thread, and the warp is free for the next 64 features while the bytes cross NVLink.  A box is refilled
+        // only after the store issued from it two fills earlier has finished READING shared memory.
+        uint8_t* stg = sStage + warp * (32 * 256);
+        const CUtensorMap* om = &omaps.m[owner];
+        const int y = ((int)(ar_epoch & 1) * B200_MAX_RANKS + p.comm.rank) * p.slot_rows + dst_row0 + warp * 32;
+#pragma unroll 1
+        for (int fill = 0; fill < 4; ++fill) {
+          uint32_t v[2][32];
+          tmem_ld_32x32(taddr + fill * 64, v[0]);
+          tmem_ld_32x32(taddr + fill * 64 + 32, v[1]);
+          tmem_ld_wait();
+          if (fill == 3) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) remote_arrive(lead_acc_empty0 + buf * 8);
+          }
+          uint8_t* box = stg + (fill & 1) * 4096;
+          if (lane == 0) bulk_wait_read_1();
+          __syncwarp();
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 o;
+              __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                oh[e] = __floats2bfloat162_rn(__uint_as_float(v[hh][q4 * 8 + 2 * e]), __uint_as_float(v[hh][q4 * 8 + 2 * e + 1]));
+              const int ci = hh * 4 + q4;
+              *reinterpret_cast<uint4*>(box + lane * 128 + ((ci ^ (lane & 7)) << 4)) = o;
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(om, box, m2 * BN + fill * 64, y);
+            tma_store_commit();
+          }
+        }
+        // the tile's flags may only be raised once the bytes have landed: full completion of this warp's stores
+        if (lane == 0) tma_store_wait_all();
       } else {
         // Peer memory wants long runs: a thread's own 16-byte pieces would cross NVLink one by one.  Each warp stages
         // 32 rows x 128 features in its private shared-memory patch (16-byte chunks XOR-swizzled by row, so neither
@@ -439,6 +500,43 @@ extern "C" int b200_gemm_2cta_supported(int T, int N, int K) {
   return g_2cta_enabled && T > 0 && T % (2 * g2::BM) == 0 && N % g2::BN == 0 && K % g2::BK == 0 && K >= g2::BK;
 }
 
+// Tensor maps of the owners' data regions for the bulk-store push, cached per (regions, row length, slot size): the
+// regions of a communicator never move, and encoding eight maps per launch would cost the host ~10 us.
+static bool push_maps(const B200Comm& c, int ldo, g2::OutMaps* out) {
+  struct Entry {
+    void* data[B200_MAX_RANKS];
+    int world, ldo;
+    unsigned long long slot_elems;
+    g2::OutMaps maps;
+  };
+  static std::mutex mu;
+  static std::vector<Entry> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  for (const Entry& e : cache)
+    if (e.world == c.world && e.ldo == ldo && e.slot_elems == c.slot_elems &&
+        memcmp(e.data, c.data, sizeof(void*) * c.world) == 0) {
+      *out = e.maps;
+      return true;
+    }
+  Entry e;
+  memset(&e, 0, sizeof(e));
+  e.world = c.world;
+  e.ldo = ldo;
+  e.slot_elems = c.slot_elems;
+  const uint64_t rows = 2ull * B200_MAX_RANKS * (c.slot_elems / (unsigned long long)ldo);
+  for (int r = 0; r < c.world; ++r) {
+    e.data[r] = c.data[r];
+    if ((reinterpret_cast<uintptr_t>(c.data[r]) & 15) ||
+        !make_tmap_2d(&e.maps.m[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c.data[r], rows, (uint64_t)ldo, (uint64_t)ldo * 2,
+                      32, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+      return false;
+  }
+  if (cache.size() >= 16) cache.erase(cache.begin());
+  cache.push_back(e);
+  *out = e.maps;
+  return true;
+}
+
 // X [T, K] bf16, W [N, K] bf16 -> out [T, N] bf16 (mode 0), or the reduce-scatter push of the sequence-parallel path
 // (mode 3: out unused; comm, sp_rows and n_rot as in gemm_wdec_kernel.cuh).  ag_wait: X is the gathered buffer.
 extern "C" int b200_gemm_bf16_2cta(const void* W, const void* X, void* out_bf16, int T, int N, int K, int mode,
@@ -463,6 +561,15 @@ extern "C" int b200_gemm_bf16_2cta(const void* W, const void* X, void* out_bf16,
   p.ag_flag_rows = ag_flag_rows;
   p.budget_ns = budget_ns ? budget_ns : B200_WAIT_BUDGET_NS;
   if (comm) p.comm = *comm;
+  g2::OutMaps omaps;
+  memset(&omaps, 0, sizeof(omaps));
+  if (mode == 3) {
+    static const bool want = [] { const char* e = getenv("B200_RS_TMA"); return !(e && e[0] == '0'); }();
+    if (want && comm->slot_elems % (unsigned long long)N == 0 && push_maps(*comm, N, &omaps)) {
+      p.tma_push = 1;
+      p.slot_rows = (int)(comm->slot_elems / (unsigned long long)N);
+    }
+  }
   CUtensorMap tmW, tmX;
   if (!make_tmap_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, N, K, (uint64_t)K * 2, g2::BNH, g2::BK,
                     CU_TENSOR_MAP_SWIZZLE_128B) ||
@@ -480,6 +587,6 @@ extern "C" int b200_gemm_bf16_2cta(const void* W, const void* X, void* out_bf16,
   const int total = p.m2_tiles * p.n_tiles;
   int pairs = sm_count() / 2;
   if (pairs > total) pairs = total;
-  g2::gemm_bf16_2cta_kernel<<<2 * pairs, g2::THREADS, g2::SMEM_TOTAL, stream>>>(tmW, tmX, p);
+  g2::gemm_bf16_2cta_kernel<<<2 * pairs, g2::THREADS, g2::SMEM_TOTAL, stream>>>(tmW, tmX, omaps, p);
   return (int)cudaGetLastError();
 }
