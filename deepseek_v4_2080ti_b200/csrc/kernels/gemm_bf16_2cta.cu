@@ -132,6 +132,7 @@ struct OutMaps {
 };
 
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_4() { asm volatile("cp.async.bulk.wait_group 4;" ::: "memory"); }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
@@ -300,6 +301,29 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     const int row_in_tile = warp * 32 + lane;             // TMEM lane == token row within the CTA's half
     const uint32_t lead_acc_empty0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
     uint32_t tile_i = 0;
+    // The last of the four warps to finish a tile raises its flags on the owner (no CTA-wide barrier: a warp that has
+    // to give up does not strand the others).  Ordering: a warp's stores (complete, for bulk stores) -> __syncwarp ->
+    // its lane 0 fences at CTA scope and counts itself in; the lane that counts fourth fences again and issues ONE
+    // system-scope release, which by cumulativity covers the stores of all four warps.  (A system-scope fence per
+    // thread per tile, the obvious form, measured ~15 us per tile at 2 ranks: 0.33 ms instead of 0.20 ms for
+    // 8192 x 5120 x 2048.)  One counter per tile & 3: the warps run up to two tiles apart, and a deferred signal
+    // trails by one more.
+    auto signal_tile = [&](uint32_t t_i, int owner, int dst_row0, int m2) {
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_block();
+        if ((atomicAdd(&epi_count[t_i & 3], 1) & 3) == 3) {   // the counters only grow: four arrivals per tile
+          __threadfence_block();
+          // this CTA's 128 rows x 256 features = two 128-feature tiles of the 128-row block, as the owner counts them
+          uint32_t* fl = flag_slot(p.comm.flags[owner], ar_epoch & 1, p.comm.rank) +
+                         (dst_row0 / BM) * (p.m2_tiles * 2) + m2 * 2;
+          st_release_sys(fl, ar_epoch);
+          st_release_sys(fl + 1, ar_epoch);
+        }
+      }
+    };
+    bool have_prev = false;
+    int prev_owner = 0, prev_row0 = 0, prev_m2 = 0;
     for (int w = pair; w < total && !*abort_flag; w += npairs, ++tile_i) {
       int m2, nt;
       tile_of(w, m2, nt);
@@ -394,8 +418,6 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             tma_store_commit();
           }
         }
-        // the tile's flags may only be raised once the bytes have landed: full completion of this warp's stores
-        if (lane == 0) tma_store_wait_all();
       } else {
         // Peer memory wants long runs: a thread's own 16-byte pieces would cross NVLink one by one.  Each warp stages
         // 32 rows x 128 features in its private shared-memory patch (16-byte chunks XOR-swizzled by row, so neither
@@ -440,24 +462,28 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         }
       }
       if (p.mode == 3) {
-        // the last of the four warps to finish raises the tile's flags on the owner (no CTA-wide barrier: a warp that
-        // has to give up does not strand the others).  Ordering: each warp's stores -> __syncwarp -> its lane 0 fences at
-        // CTA scope and counts itself in; the lane that counts fourth fences again and issues ONE system-scope release,
-        // which by cumulativity covers the stores of all four warps.  (A system-scope fence per thread per tile, the
-        // obvious form, measured ~15 us per tile at 2 ranks: 0.33 ms instead of 0.20 ms for 8192 x 5120 x 2048.)
-        __syncwarp();
-        if (lane == 0) {
-          __threadfence_block();
-          if ((atomicAdd(&epi_count[tile_i & 3], 1) & 3) == 3) {   // the counters only grow: four arrivals per tile
-            __threadfence_block();
-            // this CTA's 128 rows x 256 features = two 128-feature tiles of the 128-row block, as the owner counts them
-            uint32_t* fl = flag_slot(p.comm.flags[owner], ar_epoch & 1, p.comm.rank) +
-                           (dst_row0 / BM) * (p.m2_tiles * 2) + m2 * 2;
-            st_release_sys(fl, ar_epoch);
-            st_release_sys(fl + 1, ar_epoch);
+        if (!p.tma_push) {
+          signal_tile(tile_i, owner, dst_row0, m2);
+        } else {
+          // Bulk stores complete asynchronously.  Waiting for them here would idle the warp for a link round trip per
+          // tile, so a tile's flags are raised one tile late: "at most this tile's four store groups still pending"
+          // means that every group of the previous tile has landed.
+          if (have_prev) {
+            if (lane == 0) bulk_wait_4();
+            signal_tile(tile_i - 1, prev_owner, prev_row0, prev_m2);
           }
+          have_prev = true;
+          prev_owner = owner;
+          prev_row0 = dst_row0;
+          prev_m2 = m2;
         }
       }
+    }
+    // bulk stores still in flight belong to this warp's lane 0: drain them before the shared memory goes away, then
+    // raise the last tile's flags
+    if (p.mode == 3 && p.tma_push) {
+      if (lane == 0) tma_store_wait_all();
+      if (have_prev && !*abort_flag) signal_tile(tile_i - 1, prev_owner, prev_row0, prev_m2);
     }
   }
 

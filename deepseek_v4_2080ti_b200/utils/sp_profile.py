@@ -40,6 +40,7 @@ def main() -> None:
 
     def timed(key, fn):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(1_000_000)      # ~0.5 ms on the device: the launch below is queued before the first event fires
         e0.record()
         out = fn()
         e1.record()

@@ -25,6 +25,12 @@ import torch
 import torch.distributed as dist
 
 
+# Device-side delay queued before the first event of every timed iteration (about 0.5 ms): the launches of the
+# measured function are already in the queue when the delay ends, so the interval between the events holds kernel
+# time and dependencies, not the host's launch latency (tens of microseconds per launch, comparable to the kernels).
+HEAD_START_CYCLES = 1_000_000
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--rows", dest="t", type=int, default=8192)
@@ -59,6 +65,7 @@ def main() -> None:
             dist.barrier()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda._sleep(HEAD_START_CYCLES)      # the host queues fn() while the device is still busy here
             e0.record()
             fn()
             e1.record()
@@ -111,6 +118,7 @@ def main() -> None:
             dist.barrier()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda._sleep(HEAD_START_CYCLES)
             e0.record()
             rs_only()
             e1.record()

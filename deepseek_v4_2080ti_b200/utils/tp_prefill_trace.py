@@ -5,8 +5,10 @@ peer's flags show the time they spent waiting).  Run it one process per GPU:
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         -m deepseek_v4_2080ti_b200.utils.tp_prefill_trace --prompt 8192 [--layers 64] [--out trace.json]
 
-The figures are shares of a traced step (tracing adds a few percent); the benchmark's own numbers come from CUDA
-events without a tracer.  Prints, for rank 0: the step's wall on the device, the busy time of the main stream, and
+The figures are shares of a traced step; the benchmark's own numbers come from CUDA events without a tracer.  With
+many short kernels per rank the tracer's per-launch cost is not small (at 8 ranks the traced 27B-shaped prefill took
+177 ms against 96 ms plain: the host falls behind, ranks drift apart and the flag waits inside the GEMMs grow), so read
+the table for which kernels wait, not for absolute times.  Prints, for rank 0: the step's wall on the device, the busy time of the main stream, and
 the kernels grouped by name with launches, total and mean microseconds.  The reference has phase timers around its
 prefill loop for the same purpose (cpp_engine/engine/qwen_engine.cpp: the ``ar.*`` / ``gemm.*`` counters)."""
 from __future__ import annotations
@@ -18,9 +20,9 @@ import sys
 
 
 def _short(name: str) -> str:
+    name = name.replace("(anonymous namespace)::", "").replace("<unnamed>::", "")
     name = re.sub(r"^void\s+", "", name)
     name = re.sub(r"\(.*$", "", name)
-    name = re.sub(r"\(anonymous namespace\)::", "", name)
     return name[:90]
 
 
