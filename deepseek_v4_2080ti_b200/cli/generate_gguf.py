@@ -30,8 +30,10 @@ def main(argv=None) -> int:
     from ..models import registry
     from ..parallel import tp
     rank, world, local = tp.init_distributed()
-    dev = torch.device("cuda", local)
-    torch.cuda.set_device(dev)
+    on_gpu = torch.cuda.is_available()
+    dev = torch.device("cuda", local) if on_gpu else torch.device("cpu")     # host-only families run without a GPU
+    if on_gpu:
+        torch.cuda.set_device(dev)
     b = read_bundle(a.gguf)
     if a.prewarm:
         from ..formats.gguf.prewarm import prewarm_bundle
@@ -50,7 +52,8 @@ def main(argv=None) -> int:
     load_s = time.time() - t0
     prompt = torch.tensor(ids, dtype=torch.int32, device=dev)
     slot = rt.allocate()
-    torch.cuda.synchronize()
+    sync = torch.cuda.synchronize if on_gpu else (lambda: None)
+    sync()
     t0 = time.time()
     tok = rt.prefill(slot, prompt, a.prefill_chunk_tokens)
     out = [int(tok.item())]
@@ -58,7 +61,7 @@ def main(argv=None) -> int:
     while len(out) < a.max_new_tokens:
         tok = rt.decode([slot], tok.to(torch.int32))
         out.append(int(tok.item()))
-    torch.cuda.synchronize()
+    sync()
     t2 = time.time()
     rt.free(slot)
     if rank == 0:

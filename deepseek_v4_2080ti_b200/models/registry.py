@@ -206,3 +206,62 @@ register(ModelSpec(
     n_layers=lambda p: p.num_layers + p.mtp_layers,
     routed_suffixes=("ffn_gate_exps.weight", "ffn_up_exps.weight", "ffn_down_exps.weight"), build_runtime=_glm_runtime,
     optional_suffixes=("indexer.k_norm.bias", "nextn.shared_head_norm.weight")))
+
+
+# ---- DeepSeek-V4 (window ring + compressor + hash routing + hyper-connections): served by the fp32 block runtime on
+# the host; the file's tensors are dequantised at load.  One sequence, one rank.
+def _v4_params(md, tensors):
+    from .v4_gguf import config_from_metadata
+    return config_from_metadata(md)
+
+
+def _v4_layer_tensors(cfg, i):
+    from . import v4_gguf as vg
+    if i < cfg.n_layers:
+        ratio, hashed, rows = cfg.compress_ratios[i], i < cfg.n_hash_layers, vg.LAYER_ROWS
+    else:
+        ratio, hashed, rows = 0, False, vg.LAYER_ROWS + vg.MTP_ROWS
+    return tuple(r.gguf.split("{L}.", 1)[1] for r in rows if vg._applies(r, ratio, hashed))
+
+
+class _V4HostAdapter:
+    """The block runtime behind the slot interface of the GGUF drivers; token ids come back on ``device``."""
+    single_sequence = True
+
+    def __init__(self, rt, device):
+        self.rt, self.device = rt, device
+
+    def allocate(self) -> int:
+        self.rt.reset()
+        return 0
+
+    def free(self, slot: int) -> None:
+        self.rt.reset()
+
+    def _tok(self, logits):
+        import torch
+        return torch.tensor([int(logits[-1].argmax())], dtype=torch.int64, device=self.device)
+
+    def prefill(self, slot: int, ids, chunk: int = 0):
+        return self._tok(self.rt.forward(ids.detach().cpu()))
+
+    def decode(self, slots, ids):
+        return self._tok(self.rt.forward(ids.detach().cpu()))
+
+
+def _v4_runtime(bundle, device="cpu", rank=0, world=1, comm=None, **kw):
+    from . import v4_gguf as vg
+    from .v4_block_ref import V4BlockRef
+    if world != 1:
+        raise ValueError("the deepseek4 block runtime is single-rank (fp32 on the host)")
+    cfg, weights = vg.load_bundle(bundle)
+    return cfg, _V4HostAdapter(V4BlockRef(cfg, weights), device)
+
+
+register(ModelSpec(
+    architecture="deepseek4", display_name="DeepSeek-V4 (compressed sparse attention + hyper-connections, host fp32 runtime)",
+    parse_params=_v4_params,
+    global_tensors=("token_embd.weight", "output.weight", "output_norm.weight", "output_hc_fn.weight",
+                    "output_hc_base.weight", "output_hc_scale.weight"),
+    layer_tensors=_v4_layer_tensors, n_layers=lambda p: p.n_layers + (1 if p.mtp else 0),
+    routed_suffixes=("ffn_gate_exps.weight", "ffn_up_exps.weight", "ffn_down_exps.weight"), build_runtime=_v4_runtime))

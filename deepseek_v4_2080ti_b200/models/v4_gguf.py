@@ -168,6 +168,10 @@ def config_from_metadata(md: dict[str, Any]) -> V4Config:
             raise KeyError(f"{a}.{suffix} is missing from the metadata")
         return v
 
+    def fl(suffix: str, default=None) -> float:
+        # floats are stored as 32-bit values: give back the shortest decimal that names the same 32-bit number
+        return float(f"{float(g(suffix, default)):.7g}")
+
     d = V4Config()
     return V4Config(
         vocab_size=int(g("vocab_size")), dim=int(g("embedding_length")), n_layers=int(g("block_count")),
@@ -178,16 +182,16 @@ def config_from_metadata(md: dict[str, Any]) -> V4Config:
         index_n_heads=int(g("attention.indexer.head_count")), index_head_dim=int(g("attention.indexer.key_length")),
         index_topk=int(g("attention.indexer.top_k")), hc_mult=int(g("hyper_connection.count")),
         hc_iters=int(g("hyper_connection.sinkhorn_iterations", d.hc_iters)),
-        hc_eps=float(g("hyper_connection.epsilon", d.hc_eps)), n_experts=int(g("expert_count")),
+        hc_eps=fl("hyper_connection.epsilon", d.hc_eps), n_experts=int(g("expert_count")),
         n_activated=int(g("expert_used_count")), n_shared=int(g("expert_shared_count", 1)),
         moe_inter=int(g("expert_feed_forward_length")), n_hash_layers=int(g("hash_layer_count", 0)),
         score_func=_SCORE_INV.get(int(g("expert_gating_func", _SCORE[d.score_func])), d.score_func),
-        route_scale=float(g("expert_weights_scale", d.route_scale)), swiglu_limit=float(g("swiglu_limit", d.swiglu_limit)),
-        rope_theta=float(g("rope.freq_base", d.rope_theta)),
-        compress_rope_theta=float(g("attention.compress_rope_freq_base", d.compress_rope_theta)),
-        rope_factor=float(g("rope.scaling.factor", 1.0)),
+        route_scale=fl("expert_weights_scale", d.route_scale), swiglu_limit=fl("swiglu_limit", d.swiglu_limit),
+        rope_theta=fl("rope.freq_base", d.rope_theta),
+        compress_rope_theta=fl("attention.compress_rope_freq_base", d.compress_rope_theta),
+        rope_factor=fl("rope.scaling.factor", 1.0),
         original_seq_len=int(g("rope.scaling.original_context_length", d.original_seq_len)),
-        norm_eps=float(g("attention.layer_norm_rms_epsilon", d.norm_eps)), max_seq_len=int(g("context_length", d.max_seq_len)),
+        norm_eps=fl("attention.layer_norm_rms_epsilon", d.norm_eps), max_seq_len=int(g("context_length", d.max_seq_len)),
         mtp=int(g("nextn_predict_layers", 0)) > 0)
 
 
@@ -255,7 +259,8 @@ def write_gguf(path: str, cfg: V4Config, weights: dict[str, torch.Tensor],
             continue
         done.add(e.gguf)
         if e.kind == "experts":
-            w = torch.stack([weights[e.key.replace(f".{e.expert}.", f".{k}.", 1)] for k in range(cfg.n_experts)])
+            head, tail = e.key.rsplit(f".experts.{e.expert}.", 1)
+            w = torch.stack([weights[f"{head}.experts.{k}.{tail}"] for k in range(cfg.n_experts)])
         else:
             w = weights[e.key]
         w = w.float()
@@ -269,7 +274,10 @@ def write_gguf(path: str, cfg: V4Config, weights: dict[str, torch.Tensor],
 def load(path: str, strict: bool = True) -> tuple[V4Config, dict[str, torch.Tensor]]:
     """Read a ``deepseek4`` checkpoint into (config, fp32 weight dictionary) for ``V4BlockRef``.  With ``strict`` every
     mismatch between file and table raises one error that lists them all."""
-    bundle = G.read_bundle(path)
+    return load_bundle(G.read_bundle(path), strict, path)
+
+
+def load_bundle(bundle, strict: bool = True, path: str = "checkpoint") -> tuple[V4Config, dict[str, torch.Tensor]]:
     cfg = config_from_metadata(bundle.metadata)
     v = validate(bundle.tensors, cfg)
     if strict and not v.ok:
