@@ -20,6 +20,7 @@ from ..api.errors import (BackendUnavailableError, ConfigurationError, PocketLLM
                           UnsupportedFeatureError)
 from ..api.types import GenerationRequest, GenerationResult
 from ..protocol.chat import extract_tool_calls, split_reasoning
+from ..protocol.stream import StreamSplitter
 from ..protocol.requests import build_chat_request, build_completion_request
 from .metrics import Metrics
 
@@ -194,7 +195,7 @@ def make_handler(state: ServerState):
                     req = build_completion_request(body, tok, rid)
                     had_tools, is_chat = False, False
                 if body.get("stream"):
-                    self._stream(req, is_chat)
+                    self._stream(req, is_chat, thinking=bool(is_chat and chat.thinking), tools=had_tools)
                 else:
                     res = state.batching.submit(req) if state.batching is not None else state.backend.generate([req])[0]
                     created = int(t0)
@@ -219,7 +220,7 @@ def make_handler(state: ServerState):
             m.inc("prompt_tokens_total", res.usage.prompt_tokens)
             m.inc("completion_tokens_total", res.usage.completion_tokens)
 
-        def _stream(self, req: GenerationRequest, is_chat: bool) -> None:
+        def _stream(self, req: GenerationRequest, is_chat: bool, thinking: bool = False, tools: bool = False) -> None:
             created = int(time.time())
             cid = ("chatcmpl-" if is_chat else "cmpl-") + req.request_id
             events = state.backend.stream(req)
@@ -249,17 +250,29 @@ def make_handler(state: ServerState):
                 return c
 
             try:
+                # chat streams go through the splitter: reasoning before </think>, content after it, tool-call markup
+                # held out of the visible text and delivered as one tool_calls delta at the end
+                split = StreamSplitter(thinking=thinking, tools=tools) if is_chat else None
                 if is_chat:
                     emit(chunk({"role": "assistant", "content": ""}, None))
                 ev = first
                 while ev is not None:
-                    if ev.finish_reason is None:
-                        if ev.text:
-                            emit(chunk({"content": ev.text} if is_chat else ev.text, None))
-                    else:
-                        if ev.text:
-                            emit(chunk({"content": ev.text} if is_chat else ev.text, None))
-                        emit(chunk({} if is_chat else "", ev.finish_reason, ev.usage.as_dict() if ev.usage else None))
+                    if ev.text:
+                        if split is None:
+                            emit(chunk(ev.text, None))
+                        else:
+                            for d in split.feed(ev.text):
+                                emit(chunk(d, None))
+                    if ev.finish_reason is not None:
+                        finish = ev.finish_reason
+                        if split is not None:
+                            tail, calls = split.finish()
+                            for d in tail:
+                                emit(chunk(d, None))
+                            if calls:
+                                emit(chunk({"tool_calls": [dict(c, index=i) for i, c in enumerate(calls)]}, None))
+                                finish = "tool_calls"
+                        emit(chunk({} if is_chat else "", finish, ev.usage.as_dict() if ev.usage else None))
                     ev = next(events, None)
                 emit(b"[DONE]")
             except (BrokenPipeError, ConnectionResetError):
