@@ -450,6 +450,9 @@ class QwenHybridRuntime:
         self.cfg, self.w, self.device = cfg, weights, weights.device
         self.attention_window, self.attention_sinks = int(attention_window), int(attention_sink_tokens)
         self.comm = comm or NoComm()
+        # prefill GEMMs in launch order: while one runs, the FP8 -> bf16 expansion of the next runs on a side stream
+        chain = [m for lw in weights.layers for m in (lw.proj, lw.out, lw.gate_up, lw.down)]
+        self._next_w = {id(a): b for a, b in zip(chain, chain[1:])}
         W = self.comm.world
         assert W == weights.world
         self.hq = cfg.num_attention_heads // W
@@ -591,9 +594,14 @@ class QwenHybridRuntime:
     def _col_parallel(self, x: torch.Tensor, w: PackedLinear) -> torch.Tensor:
         """Column-parallel projection of the normalised activations.  Sequence-parallel chunks read the gathered
         buffer, whose rows arrive from the ranks that own them (all-gather + GEMM in one kernel)."""
+        self._expand_ahead(x, w)
         if self._sp:
             return self.comm.linear_ag(x, w)
         return gemm.linear(x, w)
+
+    def _expand_ahead(self, x: torch.Tensor, w: PackedLinear) -> None:
+        if x.shape[0] >= gemm.PREDECODE_MIN_T:
+            gemm.prefetch_bf16(self._next_w.get(id(w)), x.device, w)
 
     def _row_parallel(self, x: torch.Tensor, w: PackedLinear) -> torch.Tensor | None:
         """Row-parallel projection: this rank's K-shard GEMM + sum over ranks.  With a peer-memory communicator the
@@ -601,11 +609,13 @@ class QwenHybridRuntime:
         Sequence-parallel chunks only push the partial tiles to the owners of the rows (nothing is returned: the
         owner's reduce + norm + gather kernel picks them up)."""
         if self._sp:
+            self._expand_ahead(x, w)
             self.comm.linear_rs(x, w)
             return None
         fused = getattr(self.comm, "linear_allreduce", None)
         if fused is not None and self.comm.world > 1:
             return fused(x, w)
+        self._expand_ahead(x, w)
         return self.comm.all_reduce(gemm.linear(x, w))
 
     def _stream_row_parallel(self, x: torch.Tensor | None, w: PackedLinear, xsplit=None) -> torch.Tensor:

@@ -8,6 +8,7 @@ and bf16 matvec/matmul (cpp_engine/backends/cuda/kernels/bf16_ops.cu:30-167).
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 
 import torch
@@ -89,21 +90,108 @@ def _workspace(nfloats: int, device) -> tuple[torch.Tensor, torch.Tensor]:
 
 
 PREDECODE_MIN_T = 2048
-_expand_buf: dict[int, torch.Tensor] = {}
+
+
+class _Expander:
+    """Two bf16 scratch buffers per device for FP8 matrices expanded ahead of a prefill-sized GEMM.  ``prefetch`` runs
+    the expansion of the NEXT matrix on a side stream while the current GEMM (tensor-bound, few registers, no spare
+    shared memory but spare threads) runs on the main one: the expansion is a pure HBM pass and hides under it.
+    A buffer is rewritten only after the GEMM that last read it: the side stream waits for an event recorded on the
+    main stream at prefetch time, which is after that GEMM's launch and before the launch of the GEMM it overlaps."""
+
+    def __init__(self, device):
+        self.device = device
+        self.bufs: list[torch.Tensor | None] = [None, None]
+        self.tags: list[tuple | None] = [None, None]
+        self.ready: list[torch.cuda.Event | None] = [None, None]
+        self.turn = 0
+        self.side: torch.cuda.Stream | None = None
+
+    def _slot(self, need: int, keep: tuple | None = None) -> int:
+        """A buffer that holds no pending expansion (never the one tagged ``keep``); both free: take turns."""
+        free = [i for i in (0, 1) if self.tags[i] is None]
+        if len(free) == 1:
+            s = free[0]
+        else:
+            s = self.turn
+            if keep is not None and self.tags[s] == keep:
+                s ^= 1
+        self.turn = s ^ 1
+        buf = self.bufs[s]
+        if buf is None or buf.numel() < need:
+            self.bufs[s] = torch.empty(max(need, 1 << 26), dtype=torch.bfloat16, device=self.device)
+        return s
+
+    @staticmethod
+    def _key(w: "PackedLinear") -> tuple:
+        return (w.weight.data_ptr(), w.n, w.k)
+
+    def _unpack(self, w: "PackedLinear", s: int) -> torch.Tensor:
+        out = self.bufs[s][:w.n * w.k].view(w.n, w.k)
+        rc = _lib.lib().b200_unpack_fp8_bf16(_lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(out), w.n, w.k, _lib.stream())
+        _lib.check(rc, "unpack_fp8_bf16")
+        return out
+
+    def prefetch(self, w: "PackedLinear", current: "PackedLinear | None" = None) -> None:
+        """``current``: the matrix of the GEMM that is about to be launched (its buffer must survive)."""
+        key = self._key(w)
+        if key in self.tags:
+            return
+        main = torch.cuda.current_stream(self.device)
+        if self.side is None:
+            self.side = torch.cuda.Stream(self.device)
+        s = self._slot(w.n * w.k, self._key(current) if current is not None else None)
+        if self.ready[s] is not None:                 # an expansion nobody used is still writing this buffer
+            self.side.wait_event(self.ready[s])
+        # everything launched on the main stream so far, the last reader of this buffer included, comes first; a
+        # buffer allocated just now was allocated on the main stream, so the wait also orders its first use
+        self.side.wait_event(main.record_event())
+        with torch.cuda.stream(self.side):
+            self._unpack(w, s)
+            self.ready[s] = self.side.record_event()
+        self.tags[s] = key
+
+    def get(self, w: "PackedLinear") -> torch.Tensor:
+        key = self._key(w)
+        main = torch.cuda.current_stream(self.device)
+        if key in self.tags:
+            s = self.tags.index(key)
+            if self.ready[s] is not None:
+                main.wait_event(self.ready[s])
+                self.ready[s] = None
+            self.tags[s] = None                       # good for this one GEMM; the next prefetch but one may reuse it
+            self.turn = s ^ 1
+            return self.bufs[s][:w.n * w.k].view(w.n, w.k)
+        s = self._slot(w.n * w.k)
+        if self.ready[s] is not None:
+            main.wait_event(self.ready[s])
+            self.ready[s] = None
+        self.tags[s] = None
+        return self._unpack(w, s)
+
+
+_expanders: dict[int, _Expander] = {}
+
+
+def _expander(device) -> _Expander:
+    key = torch.device(device).index or 0
+    e = _expanders.get(key)
+    if e is None:
+        e = _expanders[key] = _Expander(torch.device("cuda", key))
+    return e
+
+
+def prefetch_bf16(w: "PackedLinear | None", device, current: "PackedLinear | None" = None) -> None:
+    """Start expanding FP8 matrix ``w`` to bf16 on the side stream; the next prefill-sized ``linear`` on ``w`` picks
+    the result up instead of expanding on its own stream.  Call it right BEFORE launching the GEMM on ``current``, the
+    one it is meant to overlap.  No-op for other formats."""
+    if w is not None and w.wfmt == WF_FP8_B128 and os.environ.get("B200_EXPAND_PREFETCH", "1") != "0":
+        _expander(device).prefetch(w, current)
 
 
 def _expanded_bf16(w: "PackedLinear", device) -> "PackedLinear":
-    """bf16 copy of an FP8 block-128 matrix in a per-device scratch buffer (valid until the next call on the stream)."""
-    key = torch.device(device).index or 0
-    buf = _expand_buf.get(key)
-    need = w.n * w.k
-    if buf is None or buf.numel() < need:
-        buf = torch.empty(max(need, 1 << 26), dtype=torch.bfloat16, device=device)
-        _expand_buf[key] = buf
-    out = buf[:need].view(w.n, w.k)
-    rc = _lib.lib().b200_unpack_fp8_bf16(_lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(out), w.n, w.k, _lib.stream())
-    _lib.check(rc, "unpack_fp8_bf16")
-    return PackedLinear(WF_BF16, out, None, w.n, w.k)
+    """bf16 copy of an FP8 block-128 matrix in a per-device scratch buffer (valid until the next two expansions)."""
+    return PackedLinear(WF_BF16, _expander(device).get(w), None, w.n, w.k)
 
 
 def _bn(t: int) -> int:
