@@ -115,7 +115,8 @@ struct Params {
   int T, N, K, kb_total, m2_tiles, n_tiles, ldo;
   __nv_bfloat16* out;
   int* status;
-  int mode;               // 0: store to out; 3: reduce-scatter push (see gemm_wdec_kernel.cuh ar_mode 3)
+  int mode;               // 0: store to out; 3: reduce-scatter push (see gemm_wdec_kernel.cuh ar_mode 3);
+                          // 4: W rows interleaved [gate tile | up tile]: out[T, N/2] = silu(gate) * up
   int n_rot, sp_rows;
   int ag_wait, ag_flag_rows;
   unsigned long long budget_ns;
@@ -348,7 +349,35 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
       }
       __nv_bfloat16* drow = dst + (size_t)(dst_row0 + row_in_tile) * p.ldo + (size_t)m2 * BN;
       const uint32_t taddr = tmem_base + (uint32_t(warp * 32) << 16) + buf * BN;
-      if (p.mode != 3) {
+      if (p.mode == 4) {
+        // SwiGLU: accumulator columns [0, 128) are the gate and [128, 256) the up projection of the same 128
+        // features; the activation is taken on the fp32 accumulators and only the product is written
+        __nv_bfloat16* orow = p.out + (size_t)(row0 + row_in_tile) * p.ldo + (size_t)m2 * (BN / 2);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+          uint32_t v[2][32];
+          tmem_ld_32x32(taddr + c0, v[0]);
+          tmem_ld_32x32(taddr + BN / 2 + c0, v[1]);
+          tmem_ld_wait();
+          if (c0 + 32 >= BN / 2) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) remote_arrive(lead_acc_empty0 + buf * 8);
+          }
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 o;
+            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float g0 = __uint_as_float(v[0][q4 * 8 + 2 * e]), g1 = __uint_as_float(v[0][q4 * 8 + 2 * e + 1]);
+              const float u0 = __uint_as_float(v[1][q4 * 8 + 2 * e]), u1 = __uint_as_float(v[1][q4 * 8 + 2 * e + 1]);
+              oh[e] = __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+            }
+            *reinterpret_cast<uint4*>(orow + c0 + q4 * 8) = o;
+          }
+        }
+      } else if (p.mode != 3) {
         // two TMEM reads in flight per wait: the read latency, not the store count, paces this loop
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 64) {
@@ -564,11 +593,13 @@ static bool push_maps(const B200Comm& c, int ldo, g2::OutMaps* out) {
 }
 
 // X [T, K] bf16, W [N, K] bf16 -> out [T, N] bf16 (mode 0), or the reduce-scatter push of the sequence-parallel path
-// (mode 3: out unused; comm, sp_rows and n_rot as in gemm_wdec_kernel.cuh).  ag_wait: X is the gathered buffer.
+// (mode 3: out unused; comm, sp_rows and n_rot as in gemm_wdec_kernel.cuh), or out [T, N / 2] = silu(gate) * up for a
+// W whose rows are interleaved in 128-row tiles [gate | up] (mode 4).  ag_wait: X is the gathered buffer.
 extern "C" int b200_gemm_bf16_2cta(const void* W, const void* X, void* out_bf16, int T, int N, int K, int mode,
                                    const B200Comm* comm, int sp_rows, int n_rot, int ag_wait, int ag_flag_rows,
                                    unsigned long long budget_ns, int* status, cudaStream_t stream) {
-  if (!b200_gemm_2cta_supported(T, N, K) || (mode != 0 && mode != 3) || (mode == 0 && !out_bf16)) return -ERR_BAD_ARG;
+  if (!b200_gemm_2cta_supported(T, N, K) || (mode != 0 && mode != 3 && mode != 4) || (mode != 3 && !out_bf16))
+    return -ERR_BAD_ARG;
   if ((mode == 3 || ag_wait) && (!comm || sp_rows <= 0 || sp_rows % (2 * g2::BM))) return -ERR_BAD_ARG;
   if (ag_wait && (ag_flag_rows <= 0 || g2::BM % ag_flag_rows)) return -ERR_BAD_ARG;
   g2::Params p;
@@ -577,7 +608,7 @@ extern "C" int b200_gemm_bf16_2cta(const void* W, const void* X, void* out_bf16,
   p.kb_total = K / g2::BK;
   p.m2_tiles = N / g2::BN;
   p.n_tiles = T / (2 * g2::BM);
-  p.ldo = N;
+  p.ldo = mode == 4 ? N / 2 : N;
   p.out = reinterpret_cast<__nv_bfloat16*>(out_bf16);
   p.status = status;
   p.mode = mode;

@@ -312,6 +312,21 @@ extern "C" int b200_gemm_wdec_ag(int wfmt, const void* W, const float* scales, c
   return gemm_wdec_launch(wfmt, W, scales, X, out_bf16, nullptr, nullptr, T, N, K, 1, nullptr, status, stream, &fo);
 }
 
+// out [T, N / 2] = silu(gate) * up for a bf16 W [N, K] whose rows are interleaved in 128-row tiles [gate | up] (the
+// layout b200_unpack_fp8_bf16_gate_up writes): the activation of the feed-forward block happens in the epilogue of its
+// first GEMM (pair kernel only).  comm != nullptr: X is the gathered buffer of the sequence-parallel path and the
+// producer waits for the row flags (as b200_gemm_wdec_ag).
+extern "C" int b200_gemm_bf16_swiglu(const void* W, const void* X, void* out_bf16, int T, int N, int K, const B200Comm* comm,
+                                     int flag_rows, unsigned long long budget_ns, int* status, cudaStream_t stream) {
+  if (!b200_gemm_2cta_supported(T, N, K) || !out_bf16) return -ERR_BAD_ARG;
+  if (!comm) return b200_gemm_bf16_2cta(W, X, out_bf16, T, N, K, 4, nullptr, 0, 0, 0, 0, budget_ns, status, stream);
+  if (comm->world <= 1 || T % comm->world || flag_rows <= 0) return -ERR_BAD_ARG;
+  const int sp_rows = T / comm->world;
+  if (sp_rows % 256 || sp_rows % flag_rows || sp_rows / flag_rows > B200_FLAGS_PER_SLOT) return -ERR_BAD_ARG;
+  return b200_gemm_bf16_2cta(W, X, out_bf16, T, N, K, 4, comm, sp_rows, comm->rank * (sp_rows / 256), 1, flag_rows,
+                             budget_ns ? budget_ns : B200_WAIT_BUDGET_NS, status, stream);
+}
+
 extern "C" int b200_splitk_reduce(const float* part, int splits, long long n, const void* residual,
                                   void* out_bf16, cudaStream_t stream) {
   const int threads = 256;

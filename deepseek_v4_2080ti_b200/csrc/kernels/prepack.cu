@@ -41,7 +41,7 @@ __global__ void bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ in, float* 
 // Inverse of the FP8 packing, with the block-128 scales applied: one thread per 16-byte physical chunk of a
 // [128 x 64] tile -> 16 consecutive bf16 of the row-major [N, K] matrix.
 __global__ void unpack_fp8_bf16_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ scales,
-                                       __nv_bfloat16* __restrict__ out, int N, int K, int kb_total, int ksb) {
+                                       __nv_bfloat16* __restrict__ out, int N, int K, int kb_total, int ksb, int half_tiles) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;      // (tile, row, physical chunk)
   const size_t total = (size_t)((N + 127) / 128) * kb_total * 128 * 4;
   if (i >= total) return;
@@ -68,7 +68,10 @@ __global__ void unpack_fp8_bf16_kernel(const uint8_t* __restrict__ packed, const
       vals[q * 4 + e] = __float2bfloat16(__half2float(*reinterpret_cast<const __half*>(&hr)) * sc);
     }
   }
-  __nv_bfloat16* dst = out + (size_t)n * K + k0;
+  // half_tiles > 0: the matrix is [gate rows | up rows] of half_tiles 128-row tiles each; the copy interleaves them
+  // tile by tile (gate tile j, up tile j, gate tile j+1 ...), so a 256-row GEMM tile holds both halves of 128 features
+  const size_t n_out = half_tiles > 0 ? (size_t)(mt < half_tiles ? 2 * mt : 2 * (mt - half_tiles) + 1) * 128 + r : (size_t)n;
+  __nv_bfloat16* dst = out + n_out * K + k0;
   if (k0 + 16 <= K && (K & 7) == 0) {
     *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(vals);
     *reinterpret_cast<uint4*>(dst + 8) = *reinterpret_cast<const uint4*>(vals + 8);
@@ -82,13 +85,26 @@ __global__ void unpack_fp8_bf16_kernel(const uint8_t* __restrict__ packed, const
 extern "C" {
 
 // Packed FP8 block-128 weights (b200_prepack_fp8 layout) + fp32 scales [ceil(N/128), ceil(K/128)] -> bf16 [N, K].
-int b200_unpack_fp8_bf16(const void* packed, const float* scales, void* out_bf16, int N, int K, cudaStream_t stream) {
+static int unpack_fp8_bf16_launch(const void* packed, const float* scales, void* out_bf16, int N, int K, int half_tiles,
+                                  cudaStream_t stream) {
   if (N <= 0 || K <= 0 || !packed || !scales || !out_bf16) return -6;
   const int kb_total = (K + 63) / 64;
   const size_t total = (size_t)((N + 127) / 128) * kb_total * 128 * 4;
   unpack_fp8_bf16_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-      reinterpret_cast<const uint8_t*>(packed), scales, reinterpret_cast<__nv_bfloat16*>(out_bf16), N, K, kb_total, (K + 127) / 128);
+      reinterpret_cast<const uint8_t*>(packed), scales, reinterpret_cast<__nv_bfloat16*>(out_bf16), N, K, kb_total, (K + 127) / 128,
+      half_tiles);
   return (int)cudaGetLastError();
+}
+
+int b200_unpack_fp8_bf16(const void* packed, const float* scales, void* out_bf16, int N, int K, cudaStream_t stream) {
+  return unpack_fp8_bf16_launch(packed, scales, out_bf16, N, K, 0, stream);
+}
+
+// The same expansion for a [gate | up] matrix of N = 2 I rows (I a multiple of 128): output rows are interleaved in
+// 128-row tiles (gate tile 0, up tile 0, gate tile 1, ...), the layout the SwiGLU epilogue of the pair GEMM reads.
+int b200_unpack_fp8_bf16_gate_up(const void* packed, const float* scales, void* out_bf16, int N, int K, cudaStream_t stream) {
+  if (N <= 0 || N % 256) return -6;
+  return unpack_fp8_bf16_launch(packed, scales, out_bf16, N, K, N / 256, stream);
 }
 
 unsigned long long b200_prepack_fp8_bytes(int N, int K) {

@@ -453,6 +453,7 @@ class QwenHybridRuntime:
         # prefill GEMMs in launch order: while one runs, the FP8 -> bf16 expansion of the next runs on a side stream
         chain = [m for lw in weights.layers for m in (lw.proj, lw.out, lw.gate_up, lw.down)]
         self._next_w = {id(a): b for a, b in zip(chain, chain[1:])}
+        self._gate_up_ids = {id(lw.gate_up) for lw in weights.layers}
         W = self.comm.world
         assert W == weights.world
         self.hq = cfg.num_attention_heads // W
@@ -601,7 +602,16 @@ class QwenHybridRuntime:
 
     def _expand_ahead(self, x: torch.Tensor, w: PackedLinear) -> None:
         if x.shape[0] >= gemm.PREDECODE_MIN_T:
-            gemm.prefetch_bf16(self._next_w.get(id(w)), x.device, w)
+            nxt = self._next_w.get(id(w))
+            fused = nxt is not None and id(nxt) in self._gate_up_ids and self._swiglu_fused(x.shape[0], nxt)
+            gemm.prefetch_bf16(nxt, x.device, w, gate_up=fused)
+
+    def _swiglu_fused(self, t: int, w: PackedLinear) -> bool:
+        """Does the feed-forward block of a ``t``-token chunk take the GEMM with the SwiGLU epilogue?  In a
+        sequence-parallel chunk every rank's rows must also be whole 256-token tiles of that kernel."""
+        if not gemm.swiglu_fusable(t, w):
+            return False
+        return not self._sp or (hasattr(self.comm, "linear_ag_swiglu") and (t // self.comm.world) % 256 == 0)
 
     def _row_parallel(self, x: torch.Tensor, w: PackedLinear) -> torch.Tensor | None:
         """Row-parallel projection: this rank's K-shard GEMM + sum over ranks.  With a peer-memory communicator the
@@ -633,8 +643,11 @@ class QwenHybridRuntime:
         else:
             x = basic.add_rmsnorm(h, delta, lw.post_ln, cfg.rms_norm_eps, True)
         with PROFILER.scope("lin.gate_up"):
-            gu = self._col_parallel(x, lw.gate_up)
-        act = basic.silu_mul(gu)
+            if self._swiglu_fused(x.shape[0], lw.gate_up):
+                self._expand_ahead(x, lw.gate_up)
+                act = self.comm.linear_ag_swiglu(x, lw.gate_up) if self._sp else gemm.linear_swiglu(x, lw.gate_up)
+            else:
+                act = basic.silu_mul(self._col_parallel(x, lw.gate_up))
         with PROFILER.scope("lin.down+ar.mlp"):
             return self._row_parallel(act, lw.down)
 

@@ -123,36 +123,41 @@ class _Expander:
         return s
 
     @staticmethod
-    def _key(w: "PackedLinear") -> tuple:
-        return (w.weight.data_ptr(), w.n, w.k)
+    def _key(w: "PackedLinear", gate_up: bool = False) -> tuple:
+        return (w.weight.data_ptr(), w.n, w.k, gate_up)
 
-    def _unpack(self, w: "PackedLinear", s: int) -> torch.Tensor:
+    def _unpack(self, w: "PackedLinear", s: int, gate_up: bool = False) -> torch.Tensor:
         out = self.bufs[s][:w.n * w.k].view(w.n, w.k)
-        rc = _lib.lib().b200_unpack_fp8_bf16(_lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(out), w.n, w.k, _lib.stream())
+        fn = _lib.lib().b200_unpack_fp8_bf16_gate_up if gate_up else _lib.lib().b200_unpack_fp8_bf16
+        rc = fn(_lib.ptr(w.weight), _lib.ptr(w.scales), _lib.ptr(out), w.n, w.k, _lib.stream())
         _lib.check(rc, "unpack_fp8_bf16")
         return out
 
-    def prefetch(self, w: "PackedLinear", current: "PackedLinear | None" = None) -> None:
-        """``current``: the matrix of the GEMM that is about to be launched (its buffer must survive)."""
-        key = self._key(w)
+    def prefetch(self, w: "PackedLinear", current: "PackedLinear | None" = None, gate_up: bool = False) -> None:
+        """``current``: the matrix of the GEMM that is about to be launched (its buffer must survive).  ``gate_up``:
+        write the rows interleaved for the SwiGLU epilogue (``linear_swiglu``)."""
+        key = self._key(w, gate_up)
         if key in self.tags:
             return
         main = torch.cuda.current_stream(self.device)
         if self.side is None:
             self.side = torch.cuda.Stream(self.device)
-        s = self._slot(w.n * w.k, self._key(current) if current is not None else None)
+        keep = None
+        if current is not None:
+            keep = next((t for t in self.tags if t is not None and t[:3] == self._key(current)[:3]), None)
+        s = self._slot(w.n * w.k, keep)
         if self.ready[s] is not None:                 # an expansion nobody used is still writing this buffer
             self.side.wait_event(self.ready[s])
         # everything launched on the main stream so far, the last reader of this buffer included, comes first; a
         # buffer allocated just now was allocated on the main stream, so the wait also orders its first use
         self.side.wait_event(main.record_event())
         with torch.cuda.stream(self.side):
-            self._unpack(w, s)
+            self._unpack(w, s, gate_up)
             self.ready[s] = self.side.record_event()
         self.tags[s] = key
 
-    def get(self, w: "PackedLinear") -> torch.Tensor:
-        key = self._key(w)
+    def get(self, w: "PackedLinear", gate_up: bool = False) -> torch.Tensor:
+        key = self._key(w, gate_up)
         main = torch.cuda.current_stream(self.device)
         if key in self.tags:
             s = self.tags.index(key)
@@ -167,7 +172,7 @@ class _Expander:
             main.wait_event(self.ready[s])
             self.ready[s] = None
         self.tags[s] = None
-        return self._unpack(w, s)
+        return self._unpack(w, s, gate_up)
 
 
 _expanders: dict[int, _Expander] = {}
@@ -181,17 +186,43 @@ def _expander(device) -> _Expander:
     return e
 
 
-def prefetch_bf16(w: "PackedLinear | None", device, current: "PackedLinear | None" = None) -> None:
+def prefetch_bf16(w: "PackedLinear | None", device, current: "PackedLinear | None" = None, gate_up: bool = False) -> None:
     """Start expanding FP8 matrix ``w`` to bf16 on the side stream; the next prefill-sized ``linear`` on ``w`` picks
     the result up instead of expanding on its own stream.  Call it right BEFORE launching the GEMM on ``current``, the
     one it is meant to overlap.  No-op for other formats."""
     if w is not None and w.wfmt == WF_FP8_B128 and os.environ.get("B200_EXPAND_PREFETCH", "1") != "0":
-        _expander(device).prefetch(w, current)
+        _expander(device).prefetch(w, current, gate_up)
 
 
-def _expanded_bf16(w: "PackedLinear", device) -> "PackedLinear":
+def _expanded_bf16(w: "PackedLinear", device, gate_up: bool = False) -> "PackedLinear":
     """bf16 copy of an FP8 block-128 matrix in a per-device scratch buffer (valid until the next two expansions)."""
-    return PackedLinear(WF_BF16, _expander(device).get(w), None, w.n, w.k)
+    return PackedLinear(WF_BF16, _expander(device).get(w, gate_up), None, w.n, w.k)
+
+
+def swiglu_fusable(t: int, w: "PackedLinear") -> bool:
+    """Can ``linear_swiglu`` take [gate | up] matrix ``w`` for ``t`` tokens?  FP8 weights (they are re-laid-out while
+    being expanded), a prefill-sized batch, and a shape the CTA-pair kernel tiles evenly."""
+    return (w.wfmt == WF_FP8_B128 and t >= PREDECODE_MIN_T and w.n % 256 == 0 and w.k % 64 == 0 and
+            os.environ.get("B200_SWIGLU_FUSED", "1") != "0" and
+            bool(_lib.lib().b200_gemm_2cta_supported(t, w.n, w.k)))
+
+
+def linear_swiglu(x: torch.Tensor, w: "PackedLinear", comm_ref=None, flag_rows: int = 0, budget_ns: int = 0,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """``silu(x @ gate^T) * (x @ up^T)`` for ``w = [gate | up]`` ([2I, K]) in ONE kernel: the weights are expanded
+    with gate and up tiles interleaved and the activation is applied to the fp32 accumulators in the GEMM epilogue
+    (no [T, 2I] intermediate).  ``comm_ref``: ctypes reference of a ``B200Comm`` when ``x`` is the gathered buffer of
+    the sequence-parallel path.  Reference behaviour: cpp_engine's mlp gate_up GEMM followed by ``silu_mul``
+    (cpp_engine/backends/cuda/kernels/qwen_half_ops.cu:2730-2745)."""
+    t, k = x.shape
+    assert swiglu_fusable(t, w) and k == w.k and x.dtype == torch.bfloat16 and x.is_contiguous()
+    wb = _expanded_bf16(w, x.device, gate_up=True)
+    if out is None:
+        out = torch.empty(t, w.n // 2, dtype=torch.bfloat16, device=x.device)
+    rc = _lib.lib().b200_gemm_bf16_swiglu(_lib.ptr(wb.weight), _lib.ptr(x), _lib.ptr(out), t, w.n, k, comm_ref, flag_rows,
+                                          ctypes.c_ulonglong(budget_ns), _lib.ptr(_lib.status_word(x.device)), _lib.stream())
+    _lib.check(rc, "gemm_bf16_swiglu")
+    return out
 
 
 def _bn(t: int) -> int:

@@ -409,6 +409,15 @@ class PeerComm(TPComm):
         self.fused_calls += 1
         return out
 
+    def linear_ag_swiglu(self, x_full: torch.Tensor, w) -> torch.Tensor:
+        """``linear_ag`` for the [gate | up] matrix of a feed-forward block with the SwiGLU applied in the epilogue:
+        returns silu(gate) * up [T, I] (see ``ops.gemm.linear_swiglu``)."""
+        from ..ops import gemm
+
+        out = gemm.linear_swiglu(x_full, w, self._cref(), self.SP_FLAG_ROWS, self.budget_ns)
+        self.fused_calls += 1
+        return out
+
     def wait_gather(self, rows: int) -> None:
         """Hold the stream until every peer's rows of the last gather are in this rank's buffer."""
         rc = _lib.lib().b200_sp_wait_gather(self._cref(), rows, _lib.ptr(_lib.status_word(self.device)),

@@ -155,3 +155,34 @@ def test_wait_on_a_flag_nothing_sets_returns_a_status():
     assert float((torch.ones(8, device="cuda") * 2).sum().item()) == 16.0
     for c in comms:
         c.close()
+
+
+def test_all_gather_gemm_with_swiglu_epilogue():
+    """The gathered rows feed the feed-forward block's first GEMM, which applies silu(gate) * up in its epilogue."""
+    from deepseek_v4_2080ti_b200.ops import _lib, gemm
+    from deepseek_v4_2080ti_b200.parallel import tp
+
+    torch.manual_seed(11)
+    world, rows, hidden, inter = 2, 1024, 256, 256
+    t = world * rows
+    comms = tp.PeerComm.local_group(world, slot_elems=t * hidden, budget_ms=200.0)
+    gamma = _bf(torch.randn(hidden, device="cuda") * 0.1)
+    shards = [_bf(torch.randn(rows, hidden, device="cuda")) for _ in range(world)]
+    ws, refs = [], []
+    for r in range(world):
+        q, s = fp8fmt.quantize_block128(torch.randn(2 * inter, hidden, device="cuda") * 0.08)
+        ws.append(gemm.PackedLinear.from_fp8(q, s))
+        refs.append(_bf(fp8fmt.dequantize_block128(q, s)))
+    g = [comms[r].reduce_norm_gather(shards[r], gamma, 1e-6, True, with_partials=False) for r in range(world)]
+    outs = [comms[r].linear_ag_swiglu(g[r], ws[r]) for r in range(world)]
+    for r in range(world):
+        comms[r].wait_gather(rows)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    for r in range(world):
+        gu = g[0].float() @ refs[r].float().t()
+        ref = torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]
+        assert outs[r].shape == (t, inter)
+        assert ((outs[r].float() - ref).norm() / ref.norm()) < 5e-3
+    for c in comms:
+        c.close()
