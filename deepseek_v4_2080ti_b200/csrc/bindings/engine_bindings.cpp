@@ -93,6 +93,35 @@ PYBIND11_MODULE(pocketllm_engine_cpp, m) {
              return py::make_tuple(out, ps, ds);
            }, py::arg("prompt"), py::arg("max_new_tokens"))
       .def("last_topk", [](EngineHolder& h, int k) { return h.eng->last_topk(k); })
+      // the target's output head as drafters see it: shard geometry, and a host-to-host projection for tests
+      .def("target_head_info", [](EngineHolder& h) {
+             const QwenTargetHead t = h.eng->target_head();
+             py::dict d;
+             d["wfmt"] = t.wfmt; d["local_vocab"] = t.local_vocab; d["hidden"] = t.hidden;
+             d["vocab_start"] = t.vocab_start; d["valid"] = t.valid();
+             return d;
+           })
+      .def("target_head_project", [](EngineHolder& h, const std::vector<uint16_t>& hidden_bf16_bits, int rows) {
+             const QwenTargetHead t = h.eng->target_head();
+             if (rows <= 0 || hidden_bf16_bits.size() != size_t(rows) * t.hidden) throw std::runtime_error("hidden must hold rows x hidden bf16 values");
+             std::vector<float> out(size_t(rows) * t.local_vocab);
+             {
+               py::gil_scoped_release rel;
+               void* dx = nullptr; float* dl = nullptr;
+               cudaStream_t st = h.eng->stream();
+               if (cudaMalloc(&dx, hidden_bf16_bits.size() * 2) != cudaSuccess || cudaMalloc(&dl, out.size() * 4) != cudaSuccess) {
+                 cudaFree(dx);
+                 throw std::runtime_error("target_head_project: out of device memory");
+               }
+               cudaMemcpyAsync(dx, hidden_bf16_bits.data(), hidden_bf16_bits.size() * 2, cudaMemcpyHostToDevice, st);
+               const int rc = t.project(dx, dl, rows, st);
+               cudaMemcpyAsync(out.data(), dl, out.size() * 4, cudaMemcpyDeviceToHost, st);
+               const cudaError_t e = cudaStreamSynchronize(st);
+               cudaFree(dx); cudaFree(dl);
+               if (rc != 0 || e != cudaSuccess) throw std::runtime_error("target_head_project failed: rc " + std::to_string(rc));
+             }
+             return out;
+           }, py::arg("hidden_bf16_bits"), py::arg("rows"))
       .def("stats", [](EngineHolder& h) { return h.eng->stats(); })
       // continuous batching over this engine
       .def("start_scheduler", [](EngineHolder& h, int max_batch, int prefill_token_budget) {

@@ -417,6 +417,18 @@ bool QwenNativeEngine::is_eos(int32_t token) const {
 }
 
 // ------------------------------------------------------------------------------------------------ projections
+QwenTargetHead QwenNativeEngine::target_head() const {
+  QwenTargetHead h;
+  h.wfmt = lm_head_.wfmt;
+  h.weight = lm_head_.weight.get();
+  h.scales = lm_head_.scales.as<float>();
+  h.local_vocab = lm_head_.n;
+  h.hidden = lm_head_.k;
+  h.vocab_start = vocab_lo_;
+  h.status = s_->status.as<int>();
+  return h;
+}
+
 void QwenNativeEngine::linear(const void* x, const PackedMatrix& w, void* out, int T, float* out_f32) {
   Scratch& s = *s_;
   if (out_f32) {
@@ -512,7 +524,7 @@ int32_t QwenNativeEngine::forward_prefill(int slot, const int32_t* tokens, int T
   uint8_t* last = s.h.as<uint8_t>() + size_t(T - 1) * H * 2;
   const uint8_t* dlast = delta ? reinterpret_cast<const uint8_t*>(delta) + size_t(T - 1) * H * 2 : nullptr;
   rc(b200_rmsnorm(last, dlast, nullptr, 0, final_norm_.get(), s.x.get(), 1, H, eps, 1, dlast ? 1 : 0, stream_), "final norm");
-  linear(s.x.get(), lm_head_, nullptr, 1, s.logits.as<float>());
+  rc(target_head().project(s.x.get(), s.logits.as<float>(), 1, stream_), "lm_head");
   rc(b200_argmax(s.logits.get(), 1, vocab_n_, vocab_n_, 1, vocab_lo_, s.next_idx.as<int>(), s.next_val.as<float>(), stream_),
      "argmax", 2);
   int32_t tok = -1;
@@ -634,7 +646,7 @@ void QwenNativeEngine::forward_decode(const std::vector<int>& slots, const std::
     delta = s.d_mlp.get();
   }
   rc(b200_rmsnorm(s.h.get(), delta, nullptr, 0, final_norm_.get(), s.x.get(), B, H, eps, 1, delta ? 1 : 0, stream_), "final norm");
-  linear(s.x.get(), lm_head_, nullptr, B, s.logits.as<float>());
+  rc(target_head().project(s.x.get(), s.logits.as<float>(), B, stream_), "lm_head");
   rc(b200_argmax(s.logits.get(), 1, V, V, B, vocab_lo_, s.next_idx.as<int>(), s.next_val.as<float>(), stream_), "argmax", 2);
   next.resize(B);
   if (tp_.active()) {

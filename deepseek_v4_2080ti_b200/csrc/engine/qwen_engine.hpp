@@ -9,6 +9,7 @@
 // serves the command-line tool, the persistent stdin mode and the batch scheduler.
 // (Role of cpp_engine/include/qwen_engine.hpp:28-140 and cpp_engine/cuda/qwen_engine.cu.)
 #pragma once
+#include "qwen_target_head.hpp"
 #include <cuda_runtime.h>
 #include <cstdint>
 #include <memory>
@@ -109,6 +110,9 @@ class QwenNativeEngine : public InferenceEngine {
   int block_tokens() const override { return opt_.block_tokens; }
   int total_blocks() const override { return pool_->total_blocks(); }
   int64_t max_context() const override { return opt_.max_context; }
+  // View of this rank's output head for drafters and other external scorers (valid while the engine lives).
+  QwenTargetHead target_head() const;
+  cudaStream_t stream() const { return stream_; }
   int allocate_slot() override;
   void free_slot(int slot) override;
   bool reserve(int slot, int64_t tokens) override;

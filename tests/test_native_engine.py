@@ -213,6 +213,17 @@ def test_pybind_engine_and_cpp_backend_match_python_runtime():
         assert t0 == want[1][0] and eng.slot_length(s) == len(prompts[1])
         assert eng.decode_step([s], [t0])[0] == want[1][1]
         eng.free_slot(s)
+        # the target head view: shard geometry, and the projection drafters use equals the plain matrix product
+        info = eng.target_head_info()
+        assert info["valid"] and info["local_vocab"] == cfg.vocab_size and info["hidden"] == cfg.hidden_size and info["vocab_start"] == 0
+        head = dict(state).get("lm_head.weight")
+        if head is None:
+            head = dict(state)["model.language_model.embed_tokens.weight"]
+        hid = (torch.randn(3, cfg.hidden_size, generator=gen) * 0.5).to(torch.bfloat16)
+        bits = hid.view(torch.int16).to(torch.int32).bitwise_and(0xFFFF).flatten().tolist()
+        got = torch.tensor(eng.target_head_project(bits, 3)).view(3, -1)
+        ref = hid.float() @ head.detach().to("cpu", torch.bfloat16).float().t()
+        assert ((got - ref).norm() / ref.norm()) < 2e-3
         eng.start_scheduler(2, 64)
         ids = [eng.submit(p, 6) for p in prompts]
         res = [eng.wait(i, 60000) for i in ids]
