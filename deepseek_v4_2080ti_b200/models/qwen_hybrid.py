@@ -18,6 +18,7 @@ from typing import Callable, Iterator
 import torch
 
 from ..formats import fp8 as fp8fmt
+from ..utils import canary
 from ..utils.phase_profile import PROFILER
 from ..ops import _lib, attention, basic, gdn, gemm
 from ..ops.gemm import PackedLinear
@@ -491,9 +492,12 @@ class QwenHybridRuntime:
             self._ident_bt = torch.arange(self.max_blocks_per_seq, dtype=torch.int32, device=dev)[None]
             self._rows = torch.arange(drows, dtype=torch.int32, device=dev)
         else:
-            self.k_cache = torch.zeros(nf, self.num_blocks, self.hkv, block_size, 128, dtype=torch.bfloat16, device=dev)
-            self.v_cache = torch.zeros_like(self.k_cache)
-        self.states = torch.zeros(max_slots, nl, self.hv_lin, 128, 128, dtype=torch.float32, device=dev)
+            self.k_cache = canary.zeros(nf, self.num_blocks, self.hkv, block_size, 128, dtype=torch.bfloat16, device=dev,
+                                        name="paged key cache")
+            self.v_cache = canary.zeros(nf, self.num_blocks, self.hkv, block_size, 128, dtype=torch.bfloat16, device=dev,
+                                        name="paged value cache")
+        self.states = canary.zeros(max_slots, nl, self.hv_lin, 128, 128, dtype=torch.float32, device=dev,
+                                   name="gated delta-net states")
         self.tails = torch.zeros(max_slots, nl, cfg.linear_conv_kernel_dim - 1, 2 * self.kd + self.vd,
                                  dtype=torch.bfloat16, device=dev)
         self.inv_freq = attention.rope_inv_freq(cfg.rotary_dim, cfg.rope_theta, dev)

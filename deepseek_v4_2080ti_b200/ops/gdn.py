@@ -5,6 +5,7 @@ import ctypes
 
 import torch
 
+from ..utils import canary
 from . import _lib
 
 _ll = ctypes.c_longlong
@@ -15,7 +16,7 @@ def _workspace(n: int, device) -> torch.Tensor:
     dev = torch.device(device).index or 0
     ws = _ws.get(dev)
     if ws is None or ws.numel() < n:
-        ws = torch.empty(n, dtype=torch.float32, device=device)
+        ws = canary.empty(n, dtype=torch.float32, device=device, name="gdn chunk operands")
         _ws[dev] = ws
     return ws
 

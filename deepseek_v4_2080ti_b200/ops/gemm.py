@@ -13,6 +13,7 @@ from dataclasses import dataclass
 
 import torch
 
+from ..utils import canary
 from . import _lib
 
 WF_BF16 = 0
@@ -83,8 +84,9 @@ def _workspace(nfloats: int, device) -> tuple[torch.Tensor, torch.Tensor]:
     key = torch.device(device).index or 0
     ws = _workspaces.get(key)
     if ws is None or ws[0].numel() < nfloats:
-        ws = (torch.empty(max(nfloats, 1 << 22), dtype=torch.float32, device=device),
-              ws[1] if ws is not None else torch.zeros(MAX_TILE_COUNTERS, dtype=torch.int32, device=device))
+        ws = (canary.empty(max(nfloats, 1 << 22), dtype=torch.float32, device=device, name="gemm split-K partials"),
+              ws[1] if ws is not None else canary.zeros(MAX_TILE_COUNTERS, dtype=torch.int32, device=device,
+                                                        name="gemm tile counters"))
         _workspaces[key] = ws
     return ws
 
@@ -119,7 +121,8 @@ class _Expander:
         self.turn = s ^ 1
         buf = self.bufs[s]
         if buf is None or buf.numel() < need:
-            self.bufs[s] = torch.empty(max(need, 1 << 26), dtype=torch.bfloat16, device=self.device)
+            self.bufs[s] = canary.empty(max(need, 1 << 26), dtype=torch.bfloat16, device=self.device,
+                                        name=f"fp8 expansion buffer {s}")
         return s
 
     @staticmethod

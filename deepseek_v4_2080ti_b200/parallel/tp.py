@@ -126,6 +126,7 @@ class PeerComm(TPComm):
         L = _lib.lib()
         base = self._alloc(self.slot_elems)
         self._base = base
+        self._band = band = self._guard()      # the same on every rank: they share the environment
         handle = ctypes.create_string_buffer(64)
         rc = L.b200_comm_ipc_handle(base, handle)
         if rc != 0:
@@ -136,28 +137,65 @@ class PeerComm(TPComm):
         bases = (ctypes.c_void_p * MAX_RANKS)()
         for r in range(self.world):
             if r == self.rank:
-                bases[r] = base.value
+                bases[r] = base.value + band
                 continue
             p = ctypes.c_void_p()
             rc = L.b200_comm_ipc_open(ctypes.c_char_p(handles[r]), ctypes.byref(p))
             if rc != 0:
                 raise RuntimeError(f"cudaIpcOpenMemHandle(rank {r}) failed: {rc}")
             self._peers.append(p)
-            bases[r] = p.value
+            bases[r] = p.value + band
         self._bind(bases)
         torch.cuda.synchronize()
         dist.barrier(group=self.group)
 
-    @staticmethod
-    def _alloc(slot_elems: int) -> ctypes.c_void_p:
+    GUARD_BYTES = 65536      # guard band on each side of a symmetric buffer when B200_CANARY=1
+
+    @classmethod
+    def _guard(cls) -> int:
+        from ..utils import canary
+        return cls.GUARD_BYTES if canary.is_enabled() else 0
+
+    @classmethod
+    def _alloc(cls, slot_elems: int) -> ctypes.c_void_p:
+        """Allocate one symmetric buffer.  With guards on, the allocation is ``band | buffer | band``; the returned
+        pointer is that of the allocation (what the IPC handle names) and every user adds ``_guard()`` to reach the
+        buffer."""
         L = _lib.lib()
         L.b200_comm_buffer_bytes.restype = ctypes.c_ulonglong
         nbytes = L.b200_comm_buffer_bytes(ctypes.c_ulonglong(slot_elems))
+        band = cls._guard()
         base = ctypes.c_void_p()
-        rc = L.b200_comm_alloc(ctypes.c_ulonglong(nbytes), ctypes.byref(base))
+        rc = L.b200_comm_alloc(ctypes.c_ulonglong(nbytes + 2 * band), ctypes.byref(base))
         if rc != 0:
             raise RuntimeError(f"symmetric buffer allocation failed: CUDA error {rc}")
+        if band:
+            for off in (0, band + nbytes):
+                cls._bytes_view(base.value + off, band).fill_(0xA5)
         return base
+
+    @staticmethod
+    def _bytes_view(ptr: int, n: int) -> torch.Tensor:
+        class _Mem:
+            __cuda_array_interface__ = {"shape": (n,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+        return torch.as_tensor(_Mem(), device=torch.device("cuda", torch.cuda.current_device()))
+
+    def verify_guards(self) -> list[str]:
+        """Bytes next to this rank's symmetric buffer that no longer hold the guard pattern (empty without guards)."""
+        band = getattr(self, "_band", 0)
+        if not band or self._base is None:
+            return []
+        L = _lib.lib()
+        nbytes = L.b200_comm_buffer_bytes(ctypes.c_ulonglong(self.slot_elems))
+        out = []
+        for side, off in (("before", 0), ("after", band + nbytes)):
+            b = self._bytes_view(self._base.value + off, band)
+            bad = (b != 0xA5).nonzero()
+            if bad.numel():
+                out.append(f"symmetric buffer of rank {self.rank}: {bad.numel()} byte(s) {side} it overwritten, first at +{int(bad[0])}")
+                b.fill_(0xA5)
+        return out
 
     def _bind(self, bases) -> None:
         self.c = _CommStruct()
@@ -187,15 +225,16 @@ class PeerComm(TPComm):
         kernels and for the timeout path; the collectives that fall back to the process group are not available."""
         bases = (ctypes.c_void_p * MAX_RANKS)()
         raw = [cls._alloc(int(slot_elems)) for _ in range(world)]
+        band = cls._guard()
         for r in range(world):
-            bases[r] = raw[r].value
+            bases[r] = raw[r].value + band
         out = []
         for r in range(world):
             c = cls.__new__(cls)
             c.group, c.world, c.rank, c.bytes_reduced = None, world, r, 0
             c.slot_elems, c.budget_ns = int(slot_elems), int(budget_ms * 1e6)
             c.device = torch.device("cuda", torch.cuda.current_device())
-            c._base, c._peers = raw[r], []
+            c._base, c._peers, c._band = raw[r], [], band
             c._bind(bases)
             c.overlap_gather = False      # one device: a kernel must never wait for a kernel of another stream
             out.append(c)
@@ -468,9 +507,12 @@ class PeerComm(TPComm):
         torch.cuda.synchronize()
         if dist.is_initialized():
             dist.barrier(group=self.group)
+        problems = self.verify_guards()
         for p in self._peers:
             L.b200_comm_ipc_close(p)
         self._peers = []
         if self._base is not None:
             L.b200_comm_free(self._base)
             self._base = None
+        if problems:
+            raise RuntimeError("guard bands disturbed: " + "; ".join(problems))
