@@ -46,6 +46,7 @@ enum : int {
   ERR_WAIT_PEER = 4,     // a flag owned by another rank never arrived
   ERR_WAIT_DEQUANT = 5,  // the weight-decode warps never signalled
   ERR_BAD_ARG = 6,
+  ERR_BOUNDS = 7,        // an index tensor held a value outside its range (debug index checks, kernels/bounds.cu)
 };
 
 // --------------------------------------------------------------- mbarrier

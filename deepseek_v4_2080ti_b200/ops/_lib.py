@@ -25,7 +25,12 @@ ERR_NAMES = {
     4: "peer flag wait expired",
     5: "weight-decode wait expired",
     6: "bad argument",
+    7: "index out of range",
 }
+
+# sites of the debug index checks (B200_BOUNDS_CHECK=1), as recorded in the second byte of the error word
+BOUNDS_SITES = {1: "token ids", 2: "kv cache element offsets", 3: "page table", 4: "state slots", 5: "selected key rows",
+                6: "expert ids", 7: "logit rows"}
 
 
 class KernelError(RuntimeError):
@@ -84,7 +89,27 @@ def check_status(device=None) -> None:
     code = int(t.item())
     if code != 0:
         t.zero_()
+        if code & 0xFF == 7:
+            site, pos = (code >> 8) & 0xFF, (code >> 16) & 0xFFFF
+            raise KernelError(f"index out of range in {BOUNDS_SITES.get(site, f'site {site}')} at element "
+                              f"{pos}{'+' if pos == 0xFFFF else ''} (the index was replaced by a valid one before the kernel ran)")
         raise KernelError(f"device kernel reported error {code}: {ERR_NAMES.get(code, 'unknown')}")
+
+
+def bounds_checks_on() -> bool:
+    return os.environ.get("B200_BOUNDS_CHECK", "0") == "1"
+
+
+def check_indices(idx: torch.Tensor | None, lo: int, hi: int, site: int, keep: int | None = None) -> None:
+    """Debug mode only (``B200_BOUNDS_CHECK=1``): scan an int32 index tensor on the device before the kernel that
+    addresses memory through it; values outside ``[lo, hi)`` (other than the sentinel ``keep``) set the error word and
+    are replaced by ``lo``.  No-op otherwise."""
+    if idx is None or not bounds_checks_on() or idx.numel() == 0:
+        return
+    assert idx.dtype == torch.int32 and idx.is_cuda and idx.is_contiguous()
+    rc = lib().b200_check_indices(ptr(idx), ctypes.c_longlong(idx.numel()), int(lo), int(hi), int(keep or 0),
+                                  int(keep is not None), int(lo), ptr(status_word(idx.device)), int(site), stream())
+    check(rc, "check_indices")
 
 
 LAUNCHES = 0  # kernels launched through this module (eager count; graph replays are added by the caller)

@@ -29,6 +29,7 @@ def qk_norm_rope_append(q_src, q_off, q_head_stride, gate_in_q, k_src, k_off, v_
     """
     t = q_src.shape[0]
     bs = k_cache.shape[2]
+    _lib.check_indices(slots, 0, k_cache.shape[0] * bs, 2)
     q_out = torch.empty(t, n_q_heads, D, dtype=torch.bfloat16, device=q_src.device)
     gate_out = torch.empty_like(q_out) if gate_in_q else None
     rc = _lib.lib().b200_qk_norm_rope_append(
@@ -75,6 +76,7 @@ def prefill(q, k_cache, v_cache, block_table, q_start, q_len, kv_len, max_q_len,
     t, hq, d = q.shape
     assert d == D
     nb, hkv, bs, _ = k_cache.shape
+    _lib.check_indices(block_table, 0, nb, 3)
     out = torch.empty_like(q)
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     rc = _lib.lib().b200_gqa_prefill_ex(
@@ -95,6 +97,7 @@ def decode(q, k_cache, v_cache, block_table, kv_len, gate=None, scale=None, spli
     keys of each sequence are visible (sliding window with attention sinks)."""
     b, hq, d = q.shape
     nb, hkv, bs, _ = k_cache.shape
+    _lib.check_indices(block_table, 0, nb, 3)
     out = torch.empty_like(q)
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     if splits is None:

@@ -90,6 +90,10 @@ def gated_rmsnorm_ref(x, gate, gamma, eps=1e-6):
 def embedding(ids: torch.Tensor, table: torch.Tensor, vocab_lo: int = 0, vocab_hi: int | None = None) -> torch.Tensor:
     """Rows of a (possibly vocab-sharded) table; ids outside [lo, hi) give zero rows."""
     hi = vocab_lo + table.shape[0] if vocab_hi is None else vocab_hi
+    # ids of another shard give zero rows by design; negative ids or ids past the whole vocabulary are errors.  The
+    # upper end is only known to the caller of a full table, so the check covers the unsharded case.
+    if vocab_lo == 0 and vocab_hi is None:
+        _lib.check_indices(ids if ids.dtype == torch.int32 and ids.is_contiguous() else None, 0, hi, 1)
     out = torch.empty(ids.numel(), table.shape[1], dtype=torch.bfloat16, device=table.device)
     rc = _lib.lib().b200_embedding(_lib.ptr(ids), _lib.ptr(table), _lib.ptr(out), ids.numel(), table.shape[1],
                                    vocab_lo, hi, _lib.stream())

@@ -44,6 +44,7 @@ def step(states, slot_ids, mixed, q_off, k_off, v_off, g, beta, hv, hk):
     """states [slots, Hv, 128, 128] fp32 in place; mixed [B, ld]; returns [B, Hv, 128] bf16."""
     b = mixed.shape[0]
     out = torch.empty(b, hv, 128, dtype=torch.bfloat16, device=mixed.device)
+    _lib.check_indices(slot_ids, 0, states.shape[0], 4)
     rc = _lib.lib().b200_gdn_step(_lib.ptr(states), _ll(states.stride(0)), _lib.ptr(slot_ids), _lib.ptr(mixed),
                                   mixed.stride(0), q_off, k_off, v_off, _lib.ptr(g), _lib.ptr(beta), _lib.ptr(out),
                                   b, hv, hk, _lib.stream())
@@ -59,6 +60,7 @@ def decode_fused(proj, x, w_ab, a_log, dt_bias, conv_w, tails, states, slot_ids,
     [slots, Hv, 128, 128] fp32 are updated in place for ``slot_ids`` (int32 [B]).  Returns [B, Hv*128] bf16
     (gated-RMSNorm output, the input of the output projection)."""
     b = proj.shape[0]
+    _lib.check_indices(slot_ids, 0, states.shape[0], 4)
     out = torch.empty(b, hv * 128, dtype=torch.bfloat16, device=proj.device)
     rc = _lib.lib().b200_gdn_decode_fused(
         _lib.ptr(proj), proj.stride(0), _lib.ptr(x), x.shape[1], _lib.ptr(w_ab), _lib.ptr(a_log), _lib.ptr(dt_bias),

@@ -13,6 +13,7 @@ _f = ctypes.c_float
 
 def kv_append(kv, gamma, eps, positions, slots, theta, cache, c, r, kidx=None, kidx_gamma=None, idx_cache=None):
     """kv [T, c + r] bf16 -> cache rows ``slots`` [T] (normalised latent | rotated key); optional indexer keys."""
+    _lib.check_indices(slots, 0, cache.shape[0], 2)
     t = kv.shape[0]
     di = kidx.shape[1] if kidx is not None else 0
     rc = _lib.lib().b200_mla_kv_append(_lib.ptr(kv), _lib.ptr(gamma), _f(eps), _lib.ptr(positions), _lib.ptr(slots), _f(theta),
@@ -61,6 +62,9 @@ def attention(q_lat, q_pe, cache, block_table, bs, positions, c, r, scale, sel=N
     With few query tokens (decode) the context is split over several CTAs per head group (``splits``; chosen from the
     grid size and ``max_keys``, an upper bound of the keys a token attends to) and merged by a second kernel."""
     h, t, _ = q_lat.shape
+    # selected positions address the sequence's pages: [0, pages * block) with -1 = no entry; page ids address the cache
+    _lib.check_indices(sel, 0, block_table.shape[-1] * bs, 5, keep=-1)
+    _lib.check_indices(block_table, 0, max(1, cache.shape[0] // bs), 3)          # cache [rows, c + r]: rows / block pages
     o = torch.empty(h, t, c, dtype=torch.bfloat16, device=q_lat.device)
     groups = t * ((h + 15) // 16)
     if splits is None:
