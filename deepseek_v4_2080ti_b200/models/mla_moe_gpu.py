@@ -79,10 +79,18 @@ class GpuLayer:
 class MlaMoeGpuWeights:
     def __init__(self, cfg: MlaMoeConfig, state: Iterator[tuple[str, torch.Tensor]], device="cuda", rank: int = 0,
                  world: int = 1, dense_fp8: bool = False, layer_range: tuple[int, int] | None = None,
-                 gguf_mix: dict[str, str] | None = None):
+                 gguf_mix: dict[str, str] | None = None, routed_tp: bool | None = None):
         """``rank`` / ``world``: position in the tensor/expert-parallel group (of this pipeline stage);
         ``layer_range``: the layers this stage holds (embedding only with layer 0, norm + head only with the last);
-        ``gguf_mix``: GGUF types per weight class {"attn", "ffn", "gate_up", "down"} - quantised at load."""
+        ``gguf_mix``: GGUF types per weight class {"attn", "ffn", "gate_up", "down"} - quantised at load;
+        ``routed_tp``: instead of a contiguous range of whole experts, every rank holds ALL routed experts with the
+        intermediate dimension cut ``world`` ways (gate/up rows, down columns) - the reference's ``GLM_ROUTED_TP=1``
+        option (src/models/glm_dsa/spec.py:282-325): no load imbalance between ranks at small batches, the same
+        sum over ranks afterwards.  Default: the environment variable of the same name."""
+        import os
+        self.routed_tp = (os.environ.get("GLM_ROUTED_TP", "0") == "1") if routed_tp is None else bool(routed_tp)
+        if world == 1:
+            self.routed_tp = False
         self.cfg, self.device, self.rank, self.world, self.dense_fp8 = cfg, torch.device(device), rank, world, dense_fp8
         self.gguf_mix = gguf_mix
         self.layer_lo, self.layer_hi = layer_range or (0, cfg.num_layers)
@@ -90,6 +98,9 @@ class MlaMoeGpuWeights:
         self.h_local = cfg.num_heads // world
         per = cfg.num_experts // world
         self.expert_lo, self.expert_hi = rank * per, (rank + 1) * per
+        if self.routed_tp:
+            assert cfg.expert_intermediate % (world * 32) == 0, "routed-TP cuts the expert width into 32-aligned shards"
+            self.expert_lo, self.expert_hi = 0, cfg.num_experts
         sd: dict[str, torch.Tensor] = {}
         for k, v in state:
             if k.startswith("layers."):
@@ -229,40 +240,64 @@ class MlaMoeGpuWeights:
                                                      self._rows(sd[f + "shared_experts.w3.weight"])]))
             lw.shared_down = self._lin_cols(sd[f + "shared_experts.w2.weight"], "ffn")
         es = range(self.expert_lo, self.expert_hi)
+        # routed-TP: this rank's slice [r0, r1) of every expert's intermediate dimension (else the whole width)
+        inter = cfg.expert_intermediate
+        il = inter // self.world if self.routed_tp else inter
+        r0, r1 = (self.rank * il, (self.rank + 1) * il) if self.routed_tp else (0, inter)
+
+        def rows13(w):                       # gate / up: [I, ...] -> [il, ...]
+            if not self.routed_tp:
+                return w
+            return w.rows(r0, r1) if isinstance(w, RawQuant) else w[r0:r1]
+
+        def cols2(w, div: int = 1):          # down: [H, I / div] -> [H, il / div]  (div: elements per stored column)
+            return w[:, r0 // div:r1 // div] if self.routed_tp else w
+
         first = sd[f + f"experts.{self.expert_lo}.w1.weight"]
         if isinstance(first, RawQuant):
             # a GGUF file's expert blocks as they are; gate and up stack row-wise when they share a type
             up = sd[f + f"experts.{self.expert_lo}.w3.weight"]
             if up.t == first.t and first.k % 64 == 0 and first.t in gguf_gemm.WF:
-                raws = [torch.cat([sd[f + f"experts.{e}.w1.weight"].raw, sd[f + f"experts.{e}.w3.weight"].raw]).to(dev) for e in es]
-                lw.w13 = moe.ExpertWeights.from_gguf(raws, first.t, 2 * cfg.expert_intermediate, cfg.hidden_size)
+                raws = [torch.cat([rows13(sd[f + f"experts.{e}.w1.weight"]).raw, rows13(sd[f + f"experts.{e}.w3.weight"]).raw]).to(dev)
+                        for e in es]
+                lw.w13 = moe.ExpertWeights.from_gguf(raws, first.t, 2 * il, cfg.hidden_size)
             else:
-                deq = [torch.cat([sd[f + f"experts.{e}.w1.weight"].to(dev).dequant(), sd[f + f"experts.{e}.w3.weight"].to(dev).dequant()])
-                       for e in es]
+                deq = [torch.cat([rows13(sd[f + f"experts.{e}.w1.weight"]).to(dev).dequant(),
+                                  rows13(sd[f + f"experts.{e}.w3.weight"]).to(dev).dequant()]) for e in es]
                 lw.w13 = moe.ExpertWeights.from_gguf([G.quantize(x, G.GGMLType.Q8_0) for x in deq], G.GGMLType.Q8_0,
-                                                     2 * cfg.expert_intermediate, cfg.hidden_size)
+                                                     2 * il, cfg.hidden_size)
             dn = sd[f + f"experts.{self.expert_lo}.w2.weight"]
-            if dn.k % 64 == 0 and dn.t in gguf_gemm.WF:
-                lw.w2 = moe.ExpertWeights.from_gguf([sd[f + f"experts.{e}.w2.weight"].raw.to(dev) for e in es], dn.t,
-                                                    cfg.hidden_size, cfg.expert_intermediate)
+            cut = (lambda w: w.cols(r0, r1)) if self.routed_tp else (lambda w: w)
+            if il % 64 == 0 and dn.t in gguf_gemm.WF and cut(dn) is not None:
+                lw.w2 = moe.ExpertWeights.from_gguf([cut(sd[f + f"experts.{e}.w2.weight"]).raw.to(dev) for e in es], dn.t,
+                                                    cfg.hidden_size, il)
+            elif il % 64 == 0:
+                # the cut would split a block: this rank's columns are re-encoded as Q8_0 (32-wide blocks)
+                deq = [cols2(sd[f + f"experts.{e}.w2.weight"].to(dev).dequant()).contiguous() for e in es]
+                lw.w2 = moe.ExpertWeights.from_gguf([G.quantize(x, G.GGMLType.Q8_0) for x in deq], G.GGMLType.Q8_0,
+                                                    cfg.hidden_size, il)
             else:
-                lw.w2 = moe.ExpertWeights.from_bf16([sd[f + f"experts.{e}.w2.weight"].to(dev).dequant().to(torch.bfloat16) for e in es])
+                lw.w2 = moe.ExpertWeights.from_bf16([cols2(sd[f + f"experts.{e}.w2.weight"].to(dev).dequant()).to(torch.bfloat16).contiguous()
+                                                     for e in es])
         elif self.gguf_mix is not None:
             t13, t2 = G.GGMLType[self.gguf_mix["gate_up"]], G.GGMLType[self.gguf_mix["down"]]
+            if il % G.BLOCK_ELEMS[t2]:
+                t2 = G.GGMLType.Q8_0
             full = lambda e, n: self._expert_f32(sd, f + f"experts.{e}.{n}")
-            lw.w13 = moe.ExpertWeights.from_gguf([G.quantize(torch.cat([full(e, "w1"), full(e, "w3")]), t13) for e in es], t13,
-                                                 2 * cfg.expert_intermediate, cfg.hidden_size)
-            lw.w2 = moe.ExpertWeights.from_gguf([G.quantize(full(e, "w2"), t2) for e in es], t2, cfg.hidden_size,
-                                                cfg.expert_intermediate)
+            lw.w13 = moe.ExpertWeights.from_gguf([G.quantize(torch.cat([rows13(full(e, "w1")), rows13(full(e, "w3"))]), t13)
+                                                  for e in es], t13, 2 * il, cfg.hidden_size)
+            lw.w2 = moe.ExpertWeights.from_gguf([G.quantize(cols2(full(e, "w2")).contiguous(), t2) for e in es], t2,
+                                                cfg.hidden_size, il)
         elif cfg.expert_format == "fp4":
-            cat13 = lambda e, suf: torch.cat([sd[f + f"experts.{e}.w1.{suf}"], sd[f + f"experts.{e}.w3.{suf}"]]).to(dev)
+            cat13 = lambda e, suf: torch.cat([rows13(sd[f + f"experts.{e}.w1.{suf}"]), rows13(sd[f + f"experts.{e}.w3.{suf}"])]).to(dev)
             lw.w13 = moe.ExpertWeights.from_fp4([cat13(e, "weight") for e in es], [cat13(e, "scale") for e in es])
-            lw.w2 = moe.ExpertWeights.from_fp4([sd[f + f"experts.{e}.w2.weight"].to(dev) for e in es],
-                                               [sd[f + f"experts.{e}.w2.scale"].to(dev) for e in es])
+            # two codes per byte, one scale per 32 inputs
+            lw.w2 = moe.ExpertWeights.from_fp4([cols2(sd[f + f"experts.{e}.w2.weight"], 2).contiguous().to(dev) for e in es],
+                                               [cols2(sd[f + f"experts.{e}.w2.scale"], 32).contiguous().to(dev) for e in es])
         else:
-            lw.w13 = moe.ExpertWeights.from_bf16([torch.cat([sd[f + f"experts.{e}.w1.weight"], sd[f + f"experts.{e}.w3.weight"]]).to(dev)
-                                                  for e in es])
-            lw.w2 = moe.ExpertWeights.from_bf16([sd[f + f"experts.{e}.w2.weight"].to(dev) for e in es])
+            lw.w13 = moe.ExpertWeights.from_bf16([torch.cat([rows13(sd[f + f"experts.{e}.w1.weight"]),
+                                                             rows13(sd[f + f"experts.{e}.w3.weight"])]).to(dev) for e in es])
+            lw.w2 = moe.ExpertWeights.from_bf16([cols2(sd[f + f"experts.{e}.w2.weight"]).contiguous().to(dev) for e in es])
         return lw
 
 

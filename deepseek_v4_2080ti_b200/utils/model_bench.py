@@ -96,9 +96,11 @@ def _mla(args, rank, world, dev, glm: bool):
     tpw, tpr = layout.tp, layout.tp_rank
     per = cfg.num_experts // tpw
     t0 = time.time()
-    state = mm.synth_state(cfg, 0, dev, expert_range=(tpr * per, (tpr + 1) * per), expert_pool=args.expert_pool,
-                           layer_range=(lo, hi))
+    routed_tp = bool(getattr(args, "routed_tp", False)) and tpw > 1
+    state = mm.synth_state(cfg, 0, dev, expert_range=(0, cfg.num_experts) if routed_tp else (tpr * per, (tpr + 1) * per),
+                           expert_pool=args.expert_pool, layer_range=(lo, hi))
     w = mg.MlaMoeGpuWeights(cfg, state, dev, rank=tpr, world=tpw, layer_range=(lo, hi),
+                            routed_tp=True if getattr(args, "routed_tp", False) else None,
                             gguf_mix=mg.GLM_GGUF_MIX if glm else None, dense_fp8=not glm)
     torch.cuda.empty_cache()
     comm = None
@@ -201,6 +203,8 @@ def add_arguments(ap: argparse.ArgumentParser, layers: bool = True) -> None:
         ap.add_argument("--layers", type=int, default=0, help="run only the first N layers (reported as such)")
     ap.add_argument("--expert-pool", type=int, default=4)
     ap.add_argument("--pp", type=int, default=1, help="pipeline stages (glm / dsv4)")
+    ap.add_argument("--routed-tp", action="store_true",
+                    help="glm / dsv4: every rank holds all routed experts with 1/world of their width (GLM_ROUTED_TP=1)")
     ap.add_argument("--mtp", action="store_true", help="dsv4: also time depth-1 speculative decoding")
     ap.add_argument("--eager-decode", action="store_true", help="MLA families: launch every decode kernel instead of replaying a graph")
     ap.add_argument("--nccl", action="store_true", help="library collectives instead of the peer-memory kernels")

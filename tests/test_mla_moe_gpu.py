@@ -347,3 +347,40 @@ def test_graph_decode_step_equals_eager_forward(indexer):
     toks, rows = b.generate(ids, 5)
     toks2, _ = a.generate(ids, 5)
     assert toks == toks2 and rows.shape[0] == 5
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "fp4", "gguf"])
+def test_routed_tp_partials_sum_to_the_whole_expert_layer(fmt):
+    """Routed tensor parallelism: every rank holds all experts with 1/world of the intermediate width.  The ranks'
+    partial outputs (computed here one after another on one GPU) sum to the single-rank result."""
+    from deepseek_v4_2080ti_b200.models import mla_moe as mm
+    from deepseek_v4_2080ti_b200.models import mla_moe_gpu as mg
+    from deepseek_v4_2080ti_b200.ops import _lib, moe
+    cfg = mm.MlaMoeConfig(vocab_size=512, hidden_size=256, num_layers=2, first_dense_layers=1, dense_intermediate=256,
+                          q_lora_rank=128, kv_lora_rank=128, num_heads=4, qk_nope_dim=64, qk_rope_dim=32, v_head_dim=128,
+                          index_heads=0, index_dim=0, index_topk=0, num_experts=8, experts_per_token=2,
+                          num_shared_experts=1, expert_intermediate=512, score_func="sigmoid", route_scale=2.5,
+                          expert_format="fp4" if fmt == "fp4" else "bf16")
+    state = list(mm.synth_state(cfg, seed=9, std=0.05))
+    kw = {"gguf_mix": mg.GLM_GGUF_MIX} if fmt == "gguf" else {}
+    whole = mg.MlaMoeGpuWeights(cfg, iter(state), "cuda", **kw)
+    world = 2
+    parts = [mg.MlaMoeGpuWeights(cfg, iter(state), "cuda", rank=r, world=world, routed_tp=True, **kw) for r in range(world)]
+    assert all(p.routed_tp and (p.expert_lo, p.expert_hi) == (0, cfg.num_experts) for p in parts)
+    lw = whole.layers[1]
+    assert parts[0].layers[1].w13.n == lw.w13.n // world and parts[0].layers[1].w2.k == lw.w2.k // world
+    torch.manual_seed(2)
+    t = 48
+    x = (torch.randn(t, cfg.hidden_size, device="cuda") * 0.5).to(torch.bfloat16)
+    logits = torch.randn(t, cfg.num_experts, device="cuda")
+    idx, wts = moe.route(logits, lw.gate_bias, cfg.experts_per_token, cfg.score_func, cfg.norm_topk, cfg.route_scale)
+    want = moe.experts_forward(x, idx, wts, lw.w13, lw.w2, 0, cfg.swiglu_limit).float()
+    got = sum(moe.experts_forward(x, idx, wts, p.layers[1].w13, p.layers[1].w2, 0, cfg.swiglu_limit).float() for p in parts)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    # gguf: the down projection's blocks are cut along the input dimension, same blocks -> same values; gate/up are
+    # quantised per rank over fewer rows, which can move a shared super-block scale
+    tol = 3e-2 if fmt == "gguf" else 1e-2
+    assert ((got - want).norm() / want.norm()) < tol, float((got - want).norm() / want.norm())
+    # default off; the environment variable of the reference turns it on
+    assert not mg.MlaMoeGpuWeights(cfg, iter(state), "cuda", rank=0, world=world, **kw).routed_tp
