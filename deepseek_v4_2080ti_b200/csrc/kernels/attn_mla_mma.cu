@@ -317,6 +317,11 @@ extern "C" int b200_mla_attention_splitkv(const void* q_lat, const void* q_pe, c
   if (C == 128 && R == 32)
     return launch<128, 32>(ql, qp, kc, block_table, max_blocks, bs, positions, seq_of_token, sel, nsel, ol, T, H, scale, workspace,
                            splits, stream);
+  // rows [value (128) | key (128)]: grouped-query attention over selected tokens (ops/qsa.py drives it with a zero
+  // "latent" query, so the score is q . key and the output P . value)
+  if (C == 128 && R == 128)
+    return launch<128, 128>(ql, qp, kc, block_table, max_blocks, bs, positions, seq_of_token, sel, nsel, ol, T, H, scale, workspace,
+                            splits, stream);
   return -6;
 }
 
