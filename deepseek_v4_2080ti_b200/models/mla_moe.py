@@ -70,6 +70,41 @@ class MlaMoeConfig:
     def qk_head_dim(self) -> int:
         return self.qk_nope_dim + self.qk_rope_dim
 
+    # config.json in the spelling of the DeepSeek inference configs (configs/config.json of the reference:
+    # dim, n_layers, n_dense_layers, n_heads, inter_dim, moe_inter_dim, n_routed_experts, n_shared_experts,
+    # n_activated_experts, route_scale, q_lora_rank, kv_lora_rank, qk_nope_head_dim, qk_rope_head_dim, v_head_dim,
+    # index_n_heads, index_head_dim, index_topk, score_func, expert_dtype, n_mtp_layers)
+    _JSON = {"vocab_size": "vocab_size", "hidden_size": "dim", "num_layers": "n_layers", "first_dense_layers": "n_dense_layers",
+             "dense_intermediate": "inter_dim", "q_lora_rank": "q_lora_rank", "kv_lora_rank": "kv_lora_rank",
+             "num_heads": "n_heads", "qk_nope_dim": "qk_nope_head_dim", "qk_rope_dim": "qk_rope_head_dim",
+             "v_head_dim": "v_head_dim", "rope_theta": "rope_theta", "rms_norm_eps": "rms_norm_eps",
+             "index_heads": "index_n_heads", "index_dim": "index_head_dim", "index_topk": "index_topk",
+             "num_experts": "n_routed_experts", "experts_per_token": "n_activated_experts",
+             "num_shared_experts": "n_shared_experts", "expert_intermediate": "moe_inter_dim", "score_func": "score_func",
+             "route_scale": "route_scale", "norm_topk": "norm_topk_prob", "swiglu_limit": "swiglu_limit",
+             "expert_format": "expert_dtype", "mtp_layers": "n_mtp_layers"}
+
+    def to_json(self) -> dict:
+        d = {j: getattr(self, f) for f, j in self._JSON.items()}
+        d["model_type"] = "deepseek_mla_moe"
+        return d
+
+    @staticmethod
+    def is_mla_moe_json(d: dict) -> bool:
+        """Does a config.json describe this family (DeepSeek inference spelling)?"""
+        return isinstance(d, dict) and "n_routed_experts" in d and "kv_lora_rank" in d and "dim" in d
+
+    @staticmethod
+    def from_json(d: dict) -> "MlaMoeConfig":
+        kw = {}
+        base = MlaMoeConfig()
+        for f, j in MlaMoeConfig._JSON.items():
+            if j in d and d[j] is not None:
+                kw[f] = type(getattr(base, f))(d[j])
+        if "index_n_heads" not in d:              # a checkpoint without the sparse indexer
+            kw.update(index_heads=0, index_dim=0, index_topk=0)
+        return MlaMoeConfig(**kw)
+
     @staticmethod
     def tiny_cpu() -> "MlaMoeConfig":
         """2 layers, hidden 256, vocab 1024, MLA (q_lora 128, kv_lora 64, 4 heads, 32 + 16, v 32), 8 routed

@@ -76,6 +76,41 @@ class GpuLayer:
     w2: moe.ExpertWeights | None = None
 
 
+class Fp8Block:
+    """An FP8 E4M3 matrix with its block-128 scale grid as a checkpoint stores it (``.weight`` float8 + ``.scale``
+    fp32 [ceil(N / 128), ceil(K / 128)]); sliced on 128 boundaries for the tensor-parallel shards, handed to the GEMM as
+    it is (no re-quantisation).  Reference loader: src/models/deepseek_v4/loader.py:440-662."""
+
+    def __init__(self, w: torch.Tensor, scale: torch.Tensor):
+        self.w, self.scale = w, scale.float()
+        assert w.dim() == 2 and self.scale.shape == ((w.shape[0] + 127) // 128, (w.shape[1] + 127) // 128), (w.shape, scale.shape)
+
+    @property
+    def shape(self):
+        return self.w.shape
+
+    def to(self, device, *_):
+        return Fp8Block(self.w.to(device), self.scale.to(device))
+
+    def __getitem__(self, idx):
+        if isinstance(idx, slice):
+            idx = (idx, slice(None))
+        r, c = idx
+        r0, r1 = r.start or 0, self.w.shape[0] if r.stop is None else r.stop
+        c0, c1 = c.start or 0, self.w.shape[1] if c.stop is None else c.stop
+        assert r0 % 128 == 0 and c0 % 128 == 0 and (r1 % 128 == 0 or r1 == self.w.shape[0]) and \
+            (c1 % 128 == 0 or c1 == self.w.shape[1]), "FP8 block-128 matrices are cut on 128 boundaries"
+        return Fp8Block(self.w[r0:r1, c0:c1], self.scale[r0 // 128:(r1 + 127) // 128, c0 // 128:(c1 + 127) // 128])
+
+    def dequant(self) -> torch.Tensor:
+        return fp8fmt.dequantize_block128(self.w, self.scale)
+
+    @staticmethod
+    def cat(parts: list["Fp8Block"]) -> "Fp8Block":
+        assert all(p.w.shape[0] % 128 == 0 for p in parts[:-1])
+        return Fp8Block(torch.cat([p.w for p in parts]), torch.cat([p.scale for p in parts]))
+
+
 class MlaMoeGpuWeights:
     def __init__(self, cfg: MlaMoeConfig, state: Iterator[tuple[str, torch.Tensor]], device="cuda", rank: int = 0,
                  world: int = 1, dense_fp8: bool = False, layer_range: tuple[int, int] | None = None,
@@ -112,6 +147,12 @@ class MlaMoeGpuWeights:
                 if not (self.expert_lo <= e < self.expert_hi):
                     continue
             sd[k] = v
+        # FP8 matrices of a checkpoint travel with their scale grids
+        for k in [k for k, v in sd.items() if isinstance(v, torch.Tensor) and v.dtype == torch.float8_e4m3fn]:
+            sk = k[:-len("weight")] + "scale"
+            if sk not in sd:
+                raise KeyError(f"{k} is FP8 but the checkpoint has no {sk}")
+            sd[k] = Fp8Block(sd[k], sd.pop(sk))
         dev = self.device
         self.embed = sd["embed.weight"].to(dev, torch.bfloat16).contiguous() if self.layer_lo == 0 else None
         last = self.layer_hi == cfg.num_layers
@@ -138,6 +179,11 @@ class MlaMoeGpuWeights:
             if w.k % 64 == 0 and w.t in gguf_gemm.WF:
                 return gguf_gemm.GGUFLinear.from_raw(w.raw.contiguous(), w.t, w.n, w.k, self.device)
             return PackedLinear.from_bf16(w.to(self.device).dequant().to(torch.bfloat16))
+        if isinstance(w, Fp8Block):
+            w = w.to(self.device)
+            if w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0:
+                return PackedLinear.from_fp8(w.w.contiguous(), w.scale.contiguous())
+            return PackedLinear.from_bf16(w.dequant().to(torch.bfloat16))
         w = w.to(self.device)
         if self.gguf_mix is not None:
             t = G.GGMLType[self.gguf_mix[kind]]
@@ -161,6 +207,8 @@ class MlaMoeGpuWeights:
 
     def _cat_rows(self, parts: list):
         """Row-wise concatenation of two projections that share their input (gate | up)."""
+        if isinstance(parts[0], Fp8Block):
+            return Fp8Block.cat(parts)
         if isinstance(parts[0], RawQuant):
             joined = RawQuant.cat(parts)
             if joined is not None:
@@ -176,6 +224,8 @@ class MlaMoeGpuWeights:
         """Input-dimension (row-parallel) shard of a matrix.  GGUF blocks run along the input dimension, so the full
         matrix is quantised as a checkpoint would hold it and this rank takes its run of blocks; when the shard does
         not hold whole blocks its dequantised values are re-encoded as Q8_0 (32-wide blocks)."""
+        if isinstance(w, Fp8Block):
+            return self._lin(self._cols(w), kind)
         if isinstance(w, RawQuant):
             if self.world == 1:
                 return self._lin(w, kind)
@@ -212,7 +262,8 @@ class MlaMoeGpuWeights:
         b = lambda t: t.to(dev, torch.bfloat16).contiguous()
         a = p + "attn."
         hq = cfg.qk_head_dim
-        wkv_b = self._rows(sd[a + "wkv_b.weight"], cfg.qk_nope_dim + cfg.v_head_dim).to(dev, torch.bfloat16)
+        wkv_b = self._rows(sd[a + "wkv_b.weight"], cfg.qk_nope_dim + cfg.v_head_dim)
+        wkv_b = (wkv_b.to(dev).dequant() if isinstance(wkv_b, Fp8Block) else wkv_b).to(dev, torch.bfloat16)
         wkv_b = wkv_b.view(self.h_local, cfg.qk_nope_dim + cfg.v_head_dim, cfg.kv_lora_rank)
         w_uk = wkv_b[:, :cfg.qk_nope_dim]                       # [H, N, C]
         lw = GpuLayer(

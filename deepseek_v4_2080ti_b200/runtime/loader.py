@@ -435,6 +435,28 @@ def load_runtime(args):
         from pocketllm.backends.native_backend import NullChannel
         return CppRuntimeAdapter(args.checkpoint_dir, dev.index or 0, max_ctx, slots,
                                  args.prefill_chunk_tokens or 8192), None, NullChannel()
+    if not model.startswith("synthetic:"):
+        # MLA + routed-expert checkpoints (DeepSeek inference layout: FP8 block-128 or bf16 dense matrices, FP4 or
+        # bf16 experts, config.json in the dim / n_layers / n_routed_experts spelling) as safetensors shards
+        import json as _json
+        from ..models.mla_moe import MlaMoeConfig
+        cfg_path = args.config_path or os.path.join(args.checkpoint_dir, "config.json")
+        try:
+            with open(cfg_path) as f:
+                raw_cfg = _json.load(f)
+        except (OSError, ValueError):
+            raw_cfg = None
+        if MlaMoeConfig.is_mla_moe_json(raw_cfg):
+            from ..formats import safetensors_io
+            from ..models import mla_moe_gpu as mg
+            from ..models.registry import _MlaSlotAdapter
+            from pocketllm.backends.native_backend import NullChannel
+            mcfg = MlaMoeConfig.from_json(raw_cfg)
+            comm = make_comm(mcfg.hidden_size)
+            w = mg.MlaMoeGpuWeights(mcfg, safetensors_io.read_checkpoint(args.checkpoint_dir), dev, rank, world,
+                                    dense_fp8=str(raw_cfg.get("dtype", "bf16")).lower() == "fp8")
+            rt = _MlaSlotAdapter(mg.MlaMoeGpuRuntime(mcfg, w, max_context=max_ctx, comm=comm))
+            return GgufRuntimeAdapter(rt, max_ctx, slots, dev), "deepseek_v4", channel or NullChannel()
     if model.startswith("synthetic:"):
         name = model.split(":", 1)[1]
         cfg = qh.QwenHybridConfig.tiny() if name in ("qwen-tiny", "tiny") else qh.QwenHybridConfig.config2()

@@ -1,0 +1,76 @@
+"""MLA + routed-expert checkpoints as safetensors (config.json in the DeepSeek inference spelling, FP8 block-128 or
+bf16 dense matrices, FP4 experts) through the public loader: ``pocketllm.LLM(EngineArgs(model=dir))``.
+Reference: src/models/deepseek_v4/loader.py:440-662 (FP8 + FP4 shard loader)."""
+import json
+import tempfile
+
+import pytest
+import torch
+
+from deepseek_v4_2080ti_b200.models import mla_moe as mm
+
+
+def _cfg(fmt="fp4"):
+    return mm.MlaMoeConfig(vocab_size=512, hidden_size=256, num_layers=3, first_dense_layers=1, dense_intermediate=256,
+                           q_lora_rank=128, kv_lora_rank=128, num_heads=4, qk_nope_dim=64, qk_rope_dim=32, v_head_dim=128,
+                           index_heads=4, index_dim=32, index_topk=24, num_experts=8, experts_per_token=2,
+                           num_shared_experts=1, expert_intermediate=128, score_func="sqrtsoftplus", route_scale=1.5,
+                           expert_format=fmt)
+
+
+def test_config_json_round_trip_and_detection():
+    cfg = _cfg()
+    d = json.loads(json.dumps(cfg.to_json()))
+    assert d["dim"] == 256 and d["n_routed_experts"] == 8 and d["expert_dtype"] == "fp4" and d["index_n_heads"] == 4
+    assert mm.MlaMoeConfig.is_mla_moe_json(d) and mm.MlaMoeConfig.from_json(d) == cfg
+    assert not mm.MlaMoeConfig.is_mla_moe_json({"hidden_size": 5120, "num_hidden_layers": 64})
+    no_idx = {k: v for k, v in d.items() if not k.startswith("index_")}
+    assert mm.MlaMoeConfig.from_json(no_idx).index_heads == 0
+
+
+def test_fp8_block_wrapper_slices_on_the_scale_grid():
+    from deepseek_v4_2080ti_b200.formats import fp8 as fp8fmt
+    from deepseek_v4_2080ti_b200.models.mla_moe_gpu import Fp8Block
+    w = torch.randn(384, 256) * 0.1
+    q, s = fp8fmt.quantize_block128(w)
+    b = Fp8Block(q, s)
+    full = b.dequant()
+    assert torch.equal(b[128:384].dequant(), full[128:384]) and torch.equal(b[:, 128:256].dequant(), full[:, 128:256])
+    assert torch.equal(Fp8Block.cat([b[0:128], b[128:384]]).dequant(), full)
+    with pytest.raises(AssertionError):
+        b[64:128]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dense", ["bf16", "fp8"])
+def test_public_api_serves_an_mla_moe_safetensors_checkpoint(dense):
+    from deepseek_v4_2080ti_b200.formats import fp8 as fp8fmt
+    from deepseek_v4_2080ti_b200.formats import safetensors_io
+    from deepseek_v4_2080ti_b200.models import mla_moe_gpu as mg
+    from pocketllm import LLM, EngineArgs, SamplingParams
+    cfg = _cfg()
+    state = list(mm.synth_state(cfg, seed=3, std=0.05))
+    if dense == "fp8":
+        # a checkpoint that stores its dense matrices as FP8 E4M3 with block-128 scale grids
+        out = []
+        for k, v in state:
+            if k.endswith(".weight") and v.dim() == 2 and v.dtype == torch.bfloat16 and ".experts." not in k and \
+                    v.shape[0] % 128 == 0 and v.shape[1] % 128 == 0 and not k.startswith(("embed", "head")) and "gate." not in k:
+                q, s = fp8fmt.quantize_block128(v.float())
+                out += [(k, q), (k[:-len("weight")] + "scale", s)]
+            else:
+                out.append((k, v))
+        state = out
+        assert any(v.dtype == torch.float8_e4m3fn for _, v in state)
+    with tempfile.TemporaryDirectory() as d:
+        js = cfg.to_json()
+        js["dtype"] = dense
+        safetensors_io.write_checkpoint(d, iter(state), config_json=json.dumps(js))
+        direct = mg.MlaMoeGpuRuntime(cfg, mg.MlaMoeGpuWeights(cfg, safetensors_io.read_checkpoint(d), "cuda",
+                                                             dense_fp8=dense == "fp8"), max_context=256)
+        prompt = torch.randint(1, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(8), dtype=torch.int32)
+        want, _ = direct.generate(prompt.cuda(), 6)
+        llm = LLM(EngineArgs(model=d, max_model_len=256))
+        res = llm.generate([{"prompt_token_ids": prompt.tolist()}], SamplingParams(max_tokens=6, temperature=0.0))
+        assert list(res[0].token_ids) == list(want)
+        llm.close()
