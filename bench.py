@@ -103,8 +103,8 @@ def run_moe_config(args) -> None:
                           "parallelism": rec["parallelism"], "collectives": rec["collectives"],
                           "weights_gb_per_rank": rec["weights_gb_per_rank"],
                           "l2_policy": "inputs larger than L2: every step streams the rank's weight set"},
-               "clocks": rec.get("clocks"), "gpu_launches": None,
-               "detail": {k: v for k, v in rec.items() if k.startswith("mtp_") or k in ("plain_total_ms", "launches_per_decode_step",
+               "clocks": rec.get("clocks"), "gpu_launches": rec.get("gpu_launches_eager"),
+               "detail": {k: v for k, v in rec.items() if k.startswith("mtp_") or k in ("plain_total_ms", "launches_per_decode_step", "gpu_launches_eager",
                                                                                      "build_seconds", "timing")}}
         print(json.dumps(out), flush=True)
     if dist.is_initialized():

@@ -221,11 +221,14 @@ def run_family(args, rank: int, world: int, dev, steps: int = 1, warmup: int = 1
         for _ in range(max(1, warmup)):
             warm()
         pre, dec = [], []
+        from ..ops import _lib as _lib0
+        launches0 = _lib0.LAUNCHES
         with (clock_sampler() if clock_sampler else contextlib.nullcontext()) as clk:
             for _ in range(max(1, steps)):
                 p, d = run()
                 pre.append(p)
                 dec.append(d)
+        eager_launches = _lib0.LAUNCHES - launches0
         pre_ms, dec_ms = sum(pre) / len(pre), sum(dec) / len(dec)
         extra = desc.pop("extra", None)
         launches = desc.pop("launches", None)
@@ -241,6 +244,9 @@ def run_family(args, rank: int, world: int, dev, steps: int = 1, warmup: int = 1
            "decode_tok_s": round(args.decode / dec_ms * 1e3, 2), "weights_gb_per_rank": round(nbytes / 1e9, 2),
            "build_seconds": round(build_s, 1), "data": "synthetic random-init, expert pool %d" % args.expert_pool,
            "timing": "CUDA events, max over ranks, after a one-chunk warm-up request", **desc, **more}
+    # kernels of this package launched from the host inside the timed region; kernels replayed inside a captured
+    # decode graph are not in this count (launches_per_decode_step x decode tokens of them per request)
+    rec["gpu_launches_eager"] = int(eager_launches)
     if launches:
         rec["launches_per_decode_step"] = launches()
     if clock_sampler and clk is not None:
