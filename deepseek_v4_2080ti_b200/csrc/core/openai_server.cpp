@@ -99,7 +99,16 @@ void OpenAIServer::stop() {
     listen_fd_ = -1;
   }
   if (thread_.joinable()) thread_.join();
-  if (sched_) sched_->stop();
+  {
+    // no new connections from here on; unblock the ones that sit in recv / send
+    std::lock_guard<std::mutex> lock(conn_mu_);
+    for (int fd : conn_fds_) ::shutdown(fd, SHUT_RDWR);
+  }
+  if (sched_) sched_->stop();           // requests waiting for a result wake up as cancelled
+  {
+    std::unique_lock<std::mutex> lock(conn_mu_);
+    conn_cv_.wait_for(lock, std::chrono::seconds(10), [this] { return live_connections_ == 0; });
+  }
   if (sidecar_) sidecar_->shutdown();
 }
 
@@ -110,7 +119,19 @@ void OpenAIServer::accept_loop() {
     if (rc <= 0) continue;
     const int fd = ::accept(listen_fd_, nullptr, nullptr);
     if (fd < 0) continue;
-    std::thread([this, fd] { serve_connection(fd); ::close(fd); }).detach();
+    {
+      std::lock_guard<std::mutex> lock(conn_mu_);
+      conn_fds_.insert(fd);
+      ++live_connections_;
+    }
+    std::thread([this, fd] {
+      serve_connection(fd);
+      std::lock_guard<std::mutex> lock(conn_mu_);
+      conn_fds_.erase(fd);
+      ::close(fd);                      // under the lock: stop() never shuts down a descriptor that was reused
+      --live_connections_;
+      conn_cv_.notify_all();
+    }).detach();
   }
 }
 

@@ -7,6 +7,9 @@
 // (Role of cpp_engine/include/openai_server.hpp:12-35, core/openai_server.cpp:1-466; the reference uses httplib.)
 #pragma once
 #include <atomic>
+#include <condition_variable>
+#include <mutex>
+#include <set>
 #include <memory>
 #include <string>
 #include <thread>
@@ -51,6 +54,12 @@ class OpenAIServer {
   std::atomic<bool> stop_{false};
   std::atomic<uint64_t> served_{0}, next_id_{1};
   std::thread thread_;
+  // connection threads run detached but are counted: stop() closes their sockets, wakes the requests that wait on
+  // the scheduler and leaves only when the last of them has returned, so none can touch a destroyed server
+  std::mutex conn_mu_;
+  std::condition_variable conn_cv_;
+  std::set<int> conn_fds_;
+  int live_connections_ = 0;
 };
 
 }  // namespace pocket

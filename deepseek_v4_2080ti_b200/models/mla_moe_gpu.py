@@ -396,10 +396,14 @@ class MlaMoeGpuRuntime:
         return _mm(basic.silu_mul(_mm(x, gu)), down)
 
     def _attention(self, lw: GpuLayer, i: int, x: torch.Tensor, pos: torch.Tensor, end: int, ld: int | None = None,
-                   sparse: bool | None = None) -> torch.Tensor:
+                   sparse: bool | None = None, rows: torch.Tensor | None = None, seq: torch.Tensor | None = None,
+                   table: torch.Tensor | None = None) -> torch.Tensor:
         """``end``: context length after these tokens; ``ld`` / ``sparse`` override the indexer's score width and the
-        dense-or-selected decision (a captured decode step fixes both for a whole context bucket)."""
+        dense-or-selected decision (a captured decode step fixes both for a whole context bucket).  Several sequences
+        in one call: ``rows`` = physical cache row of every token, ``seq`` = its row of the page table ``table``."""
         cfg = self.cfg
+        rows = pos if rows is None else rows
+        table = self.block_table if table is None else table
         ld = end if ld is None else ld
         sparse = end > cfg.index_topk if sparse is None else sparse
         t = x.shape[0]
@@ -409,7 +413,7 @@ class MlaMoeGpuRuntime:
         q = _mm(qin, lw.wq_b)
         kv = _mm(x, lw.wkv_a)
         kidx = _mm(x, lw.idx_wk) if lw.idx_wk is not None else None
-        mla.kv_append(kv, lw.kv_norm, eps, pos, pos, cfg.rope_theta, self.cache[i], cfg.kv_lora_rank, cfg.qk_rope_dim,
+        mla.kv_append(kv, lw.kv_norm, eps, pos, rows, cfg.rope_theta, self.cache[i], cfg.kv_lora_rank, cfg.qk_rope_dim,
                       kidx, lw.idx_knorm, self.idx_cache[i] if kidx is not None else None)
         qn_t, q_pe = mla.q_prepare(q, pos, cfg.rope_theta, hl, cfg.qk_nope_dim, cfg.qk_rope_dim)
         q_lat = mla.per_head_linear(qn_t, lw.w_uk_t)
@@ -426,15 +430,16 @@ class MlaMoeGpuRuntime:
                 hi = min(t, lo + per)
                 part = torch.full((per, cfg.index_topk), -1, dtype=torch.int32, device=self.device)
                 if hi > lo:
-                    sc = mla.indexer_scores(qi[lo:hi].contiguous(), hw[lo:hi].contiguous(), self.idx_cache[i], self.block_table,
-                                            self.bs, pos[lo:hi].contiguous(), ld, cfg.index_dim ** -0.5)
+                    sc = mla.indexer_scores(qi[lo:hi].contiguous(), hw[lo:hi].contiguous(), self.idx_cache[i], table,
+                                            self.bs, pos[lo:hi].contiguous(), ld, cfg.index_dim ** -0.5,
+                                            None if seq is None else seq[lo:hi].contiguous())
                     part[:hi - lo] = mla.topk_rows(sc, (pos[lo:hi] + 1).to(torch.int32), cfg.index_topk)
                 sel = self.comm.all_gather(part).reshape(world * per, cfg.index_topk)[:t].contiguous()
             else:
-                scores = mla.indexer_scores(qi, hw, self.idx_cache[i], self.block_table, self.bs, pos, ld, cfg.index_dim ** -0.5)
+                scores = mla.indexer_scores(qi, hw, self.idx_cache[i], table, self.bs, pos, ld, cfg.index_dim ** -0.5, seq)
                 sel = mla.topk_rows(scores, (pos + 1).to(torch.int32), cfg.index_topk)
-        o_lat = mla.attention(q_lat, q_pe, self.cache[i], self.block_table, self.bs, pos, cfg.kv_lora_rank, cfg.qk_rope_dim,
-                              cfg.qk_head_dim ** -0.5, sel, max_keys=ld)
+        o_lat = mla.attention(q_lat, q_pe, self.cache[i], table, self.bs, pos, cfg.kv_lora_rank, cfg.qk_rope_dim,
+                              cfg.qk_head_dim ** -0.5, sel, seq_of_token=seq, max_keys=ld)
         o = mla.transpose_heads(mla.per_head_linear(o_lat, lw.w_uv)).view(t, hl * cfg.v_head_dim)
         return self.comm.all_reduce(_mm(o, lw.wo))
 
@@ -634,3 +639,117 @@ class MlaMoeGpuRuntime:
         if self.pp is not None:
             self.pp.drain()
         return toks, (torch.stack(rows) if rows else torch.empty(0))
+
+
+class MlaMoeBatchRuntime(MlaMoeGpuRuntime):
+    """Several sequences over ONE paged latent cache: ``max_slots`` page-table rows, pages handed out from a free list
+    as sequences grow and returned by ``free``; ``prefill`` appends a chunk to one sequence, ``decode`` advances any
+    subset of the sequences by one token each in a single pass (the GEMMs, the router and the experts see B rows; the
+    indexer, the top-k and the sparse attention address each row's own pages through ``seq_of_token``).
+    Reference behaviour: the batched decode / verify of the resident engine
+    (cpp_engine/include/persistent_engine.hpp:24-208), config rows "batch 64" (DSV4-Flash) and "batch 16" (GLM)."""
+    single_sequence = False
+
+    def __init__(self, cfg: MlaMoeConfig, weights: MlaMoeGpuWeights, max_slots: int = 4, max_context: int = 4096,
+                 block_size: int = 64, num_blocks: int | None = None, comm=None):
+        self.max_slots = int(max_slots)
+        per_seq = (max_context + block_size - 1) // block_size
+        self.num_blocks = int(num_blocks) if num_blocks else per_seq * self.max_slots
+        # the parent sizes the caches from max_context: give it the pool's capacity, then restore the per-sequence limit
+        super().__init__(cfg, weights, max_context=self.num_blocks * block_size, block_size=block_size, comm=comm)
+        assert self.pp is None and weights.layer_lo == 0 and weights.layer_hi == cfg.num_layers, "no pipeline stages here"
+        self.max_context = max_context
+        self.blocks_per_seq = per_seq
+        self.table = torch.zeros(self.max_slots, per_seq, dtype=torch.int32, device=self.device)
+        self._table_host = [[-1] * per_seq for _ in range(self.max_slots)]
+        self._free_pages = list(range(self.num_blocks - 1, -1, -1))
+        self._free_slots = list(range(self.max_slots - 1, -1, -1))
+        self.lengths = [0] * self.max_slots
+
+    # ---- slots and pages
+    def allocate(self) -> int:
+        if not self._free_slots:
+            raise RuntimeError("no free slot")
+        s = self._free_slots.pop()
+        self.lengths[s] = 0
+        return s
+
+    def free(self, slot: int) -> None:
+        for b, page in enumerate(self._table_host[slot]):
+            if page >= 0:
+                self._free_pages.append(page)
+                self._table_host[slot][b] = -1
+        self.lengths[slot] = 0
+        self._free_slots.append(slot)
+
+    def free_pages(self) -> int:
+        return len(self._free_pages)
+
+    def _ensure_pages(self, slot: int, end: int) -> None:
+        if end > self.max_context:
+            raise RuntimeError("sequence exceeds max_context")
+        need = (end + self.bs - 1) // self.bs
+        row, changed = self._table_host[slot], False
+        for b in range(need):
+            if row[b] < 0:
+                if not self._free_pages:
+                    raise RuntimeError("the latent cache has no free page")
+                row[b] = self._free_pages.pop()
+                changed = True
+        if changed:
+            self.table[slot] = torch.tensor([max(p, 0) for p in row], dtype=torch.int32).to(self.device, non_blocking=False)
+
+    def _rows_of(self, slot: int, lo: int, hi: int) -> list[int]:
+        row, bs = self._table_host[slot], self.bs
+        return [row[p // bs] * bs + p % bs for p in range(lo, hi)]
+
+    # ---- passes
+    def _run(self, ids: torch.Tensor, pos_l: list[int], rows_l: list[int], seq_l: list[int], end_max: int) -> torch.Tensor:
+        cfg, w, dev = self.cfg, self.w, self.device
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32).to(dev)
+        pos, rows, seq = i32(pos_l), i32(rows_l), i32(seq_l)
+        # the indexer scores [0, ld) of every row's sequence and masks beyond the row's own position; rows shorter than
+        # the top-k width simply select everything they can see
+        ld = min(self.blocks_per_seq * self.bs, max(64, (end_max + 63) // 64 * 64))
+        sparse = cfg.index_heads > 0 and end_max > cfg.index_topk
+        h = basic.embedding(ids.to(torch.int32), w.embed, 0, cfg.vocab_size)
+        delta = None
+        for i, lw in enumerate(w.layers):
+            x = basic.rmsnorm(h, lw.attn_norm, cfg.rms_norm_eps) if delta is None else \
+                basic.add_rmsnorm(h, delta, lw.attn_norm, cfg.rms_norm_eps)
+            d_attn = self._attention(lw, i, x, pos, end_max, ld, sparse, rows=rows, seq=seq, table=self.table)
+            x = basic.add_rmsnorm(h, d_attn, lw.ffn_norm, cfg.rms_norm_eps)
+            delta = self._ffn(lw, x)
+        x = basic.add_rmsnorm(h, delta, w.norm, cfg.rms_norm_eps)
+        return x
+
+    @torch.no_grad()
+    def prefill(self, slot: int, ids: torch.Tensor, chunk: int = 2048) -> torch.Tensor:
+        """Append ``ids`` to sequence ``slot``; returns the greedy next token [1]."""
+        ids = ids.to(self.device, torch.int32).reshape(-1)
+        x = None
+        for s0 in range(0, ids.numel(), chunk):
+            part = ids[s0:s0 + chunk]
+            lo = self.lengths[slot]
+            hi = lo + part.numel()
+            self._ensure_pages(slot, hi)
+            x = self._run(part, list(range(lo, hi)), self._rows_of(slot, lo, hi), [slot] * (hi - lo), hi)
+            self.lengths[slot] = hi
+        self.last_logits = _mm(x[-1:].contiguous(), self.w.head, out_f32=True)
+        return basic.argmax(self.last_logits)
+
+    @torch.no_grad()
+    def decode(self, slots: list[int], tokens: torch.Tensor) -> torch.Tensor:
+        """One token for each of ``slots`` (distinct); returns the greedy next tokens [B]."""
+        assert len(set(slots)) == len(slots) and tokens.numel() == len(slots)
+        pos_l, rows_l = [], []
+        for s in slots:
+            p = self.lengths[s]
+            self._ensure_pages(s, p + 1)
+            pos_l.append(p)
+            rows_l += self._rows_of(s, p, p + 1)
+        x = self._run(tokens.to(self.device, torch.int32).reshape(-1), pos_l, rows_l, list(slots), max(pos_l) + 1)
+        for s in slots:
+            self.lengths[s] += 1
+        self.last_logits = _mm(x, self.w.head, out_f32=True)
+        return basic.argmax(self.last_logits)

@@ -164,6 +164,8 @@ def _glm_runtime(bundle, device="cuda", rank=0, world=1, comm=None, max_slots=1,
     per = cfg.num_experts // world
     state = mg.read_state(TensorStore(bundle), cfg, device, expert_range=(rank * per, (rank + 1) * per))
     w = mm.MlaMoeGpuWeights(cfg, state, device, rank, world)
+    if max_slots > 1:       # several resident sequences: one page pool, batched decode
+        return cfg, mm.MlaMoeBatchRuntime(cfg, w, max_slots=max_slots, max_context=max_context, comm=comm, **kw)
     return cfg, _MlaSlotAdapter(mm.MlaMoeGpuRuntime(cfg, w, max_context=max_context, comm=comm, **kw))
 
 

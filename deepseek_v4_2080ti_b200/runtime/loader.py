@@ -455,7 +455,10 @@ def load_runtime(args):
             comm = make_comm(mcfg.hidden_size)
             w = mg.MlaMoeGpuWeights(mcfg, safetensors_io.read_checkpoint(args.checkpoint_dir), dev, rank, world,
                                     dense_fp8=str(raw_cfg.get("dtype", "bf16")).lower() == "fp8")
-            rt = _MlaSlotAdapter(mg.MlaMoeGpuRuntime(mcfg, w, max_context=max_ctx, comm=comm))
+            if slots > 1:
+                rt = mg.MlaMoeBatchRuntime(mcfg, w, max_slots=slots, max_context=max_ctx, comm=comm)
+            else:
+                rt = _MlaSlotAdapter(mg.MlaMoeGpuRuntime(mcfg, w, max_context=max_ctx, comm=comm))
             return GgufRuntimeAdapter(rt, max_ctx, slots, dev), "deepseek_v4", channel or NullChannel()
     if model.startswith("synthetic:"):
         name = model.split(":", 1)[1]

@@ -384,3 +384,56 @@ def test_routed_tp_partials_sum_to_the_whole_expert_layer(fmt):
     assert ((got - want).norm() / want.norm()) < tol, float((got - want).norm() / want.norm())
     # default off; the environment variable of the reference turns it on
     assert not mg.MlaMoeGpuWeights(cfg, iter(state), "cuda", rank=0, world=world, **kw).routed_tp
+
+
+@pytest.mark.parametrize("indexer", [False, True])
+def test_batched_decode_over_a_shared_page_pool(indexer):
+    """Three sequences of different lengths share one paged latent cache (pages handed out interleaved); their decode
+    steps run as ONE pass per step.  Teacher-forced against the single-sequence runtime: same logits per sequence."""
+    from deepseek_v4_2080ti_b200.models import mla_moe as mm
+    from deepseek_v4_2080ti_b200.models import mla_moe_gpu as mg
+    from deepseek_v4_2080ti_b200.ops import _lib
+    cfg = _cfg(indexer)
+    state = list(mm.synth_state(cfg, seed=11, std=0.05))
+    w = mg.MlaMoeGpuWeights(cfg, iter(state), "cuda")
+    single = mg.MlaMoeGpuRuntime(cfg, w, max_context=256)
+    batch = mg.MlaMoeBatchRuntime(cfg, w, max_slots=3, max_context=256)
+    gen = torch.Generator().manual_seed(12)
+    prompts = [torch.randint(1, cfg.vocab_size, (n,), generator=gen, dtype=torch.int32).cuda() for n in (100, 70, 130)]
+    steps = 5
+    want_tok, want_logits = [], []
+    for p in prompts:
+        toks, rows = single.generate(p, steps + 1, chunk=48)
+        want_tok.append(toks)
+        want_logits.append(rows)
+    slots = [batch.allocate() for _ in prompts]
+    # interleaved chunked prefill: the sequences' pages alternate in the pool
+    firsts = [None] * 3
+    cursor = [0, 0, 0]
+    while any(c < p.numel() for c, p in zip(cursor, prompts)):
+        for j, p in enumerate(prompts):
+            if cursor[j] < p.numel():
+                firsts[j] = batch.prefill(slots[j], p[cursor[j]:cursor[j] + 48], chunk=48)
+                cursor[j] += 48
+    pages = [[x for x in batch._table_host[s] if x >= 0] for s in slots]
+    assert [len(x) for x in pages] == [2, 2, 3] and sorted(sum(pages, [])) == list(range(7)) and pages[0] != [0, 1]
+    assert [int(f.item()) for f in firsts] == [t[0] for t in want_tok]
+    for step in range(steps):
+        feed = torch.tensor([want_tok[j][step] for j in range(3)], dtype=torch.int32, device="cuda")
+        nxt = batch.decode(slots, feed)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        for j in range(3):
+            ref = want_logits[j][step + 1]
+            got = batch.last_logits[j]
+            assert ((got - ref).norm() / ref.norm()) < 2e-2, (step, j)
+        assert sum(int(nxt[j].item()) == want_tok[j][step + 1] for j in range(3)) >= 2
+    assert batch.lengths[:3] == [105, 75, 135]
+    # a subset of the sequences can step on its own; freeing returns the pages
+    batch.decode([slots[1]], torch.tensor([want_tok[1][steps]], dtype=torch.int32, device="cuda"))
+    assert batch.lengths[1] == 76
+    free0 = batch.free_pages()
+    batch.free(slots[2])
+    assert batch.free_pages() == free0 + 3
+    s_new = batch.allocate()
+    assert s_new == slots[2] and int(batch.prefill(s_new, prompts[1]).item()) == want_tok[1][0]
