@@ -753,3 +753,23 @@ class MlaMoeBatchRuntime(MlaMoeGpuRuntime):
             self.lengths[s] += 1
         self.last_logits = _mm(x, self.w.head, out_f32=True)
         return basic.argmax(self.last_logits)
+
+    @torch.no_grad()
+    def verify(self, slot: int, tokens: torch.Tensor) -> tuple[int, int]:
+        """Speculative verification on one sequence: ``tokens`` = [t0, d1, ..., dK] where t0 is the last accepted token
+        (not yet in the cache) and d1..dK are drafts.  One pass scores all K + 1 rows; draft d(i+1) is accepted while
+        it equals the greedy choice after row i.  The cache keeps t0 and the accepted drafts only (the latent cache
+        rolls back by shortening the sequence; later rows are overwritten).  Returns (accepted drafts, next token)."""
+        ids = tokens.to(self.device, torch.int32).reshape(-1)
+        k1 = ids.numel()
+        lo = self.lengths[slot]
+        self._ensure_pages(slot, lo + k1)
+        x = self._run(ids, list(range(lo, lo + k1)), self._rows_of(slot, lo, lo + k1), [slot] * k1, lo + k1)
+        self.last_logits = _mm(x, self.w.head, out_f32=True)
+        choice = basic.argmax(self.last_logits).tolist()
+        drafts = ids[1:].tolist()
+        accepted = 0
+        while accepted < len(drafts) and drafts[accepted] == choice[accepted]:
+            accepted += 1
+        self.lengths[slot] = lo + 1 + accepted
+        return accepted, int(choice[accepted])

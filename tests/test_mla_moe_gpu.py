@@ -437,3 +437,22 @@ def test_batched_decode_over_a_shared_page_pool(indexer):
     assert batch.free_pages() == free0 + 3
     s_new = batch.allocate()
     assert s_new == slots[2] and int(batch.prefill(s_new, prompts[1]).item()) == want_tok[1][0]
+    # speculative verification on that sequence: two right drafts and a wrong one -> two accepted, cache rolled back
+    t = want_tok[1]
+    wrong = (t[3] + 1) % cfg.vocab_size
+    accepted, nxt = batch.verify(s_new, torch.tensor([t[0], t[1], t[2], wrong], dtype=torch.int32))
+    assert accepted == 2 and nxt == t[3] and batch.lengths[s_new] == prompts[1].numel() + 3
+    # ... and the sequence continues from there as if nothing had been drafted
+    assert int(batch.decode([s_new], torch.tensor([t[3]], dtype=torch.int32)).item()) == t[4]
+    # the same runtime behind the resident command loop
+    import io, json
+    from deepseek_v4_2080ti_b200.runtime.resident_engine import ResidentEngine
+    eng = ResidentEngine(batch, to_ids=lambda toks: torch.tensor(toks, dtype=torch.int32, device="cuda"))
+    batch.free(s_new)
+    out = io.StringIO()
+    eng.serve([json.dumps(c) for c in ({"op": "alloc"}, {"op": "prefill", "slot": s_new, "tokens": prompts[1].tolist()},
+                                       {"op": "decode", "slots": [s_new], "tokens": [t[0]]}, {"op": "prefill", "slot": 77, "tokens": [1]},
+                                       {"op": "stats"})], out, after_command=_lib.check_status)
+    rep = [json.loads(l) for l in out.getvalue().splitlines()]
+    assert rep[0] == {"ok": True, "slot": s_new} and rep[1]["token"] == t[0] and rep[2]["tokens"] == [t[1]]
+    assert not rep[3]["ok"] and rep[4]["stats"]["errors"] == 1
