@@ -38,6 +38,10 @@ def parse():
     ap.add_argument("--layers", type=int, default=64, help="debug only; the reported config is 64")
     ap.add_argument("--chunk", type=int, default=8192)
     ap.add_argument("--tiny", action="store_true", help="debug only: 4-layer hidden-256 model")
+    ap.add_argument("--spec", choices=["none", "mtp", "ngram"], default="none",
+                    help="config 2: also run greedy speculative decoding after the timed steps (mtp: a random-init "
+                         "multi-token-prediction head is added to the synthetic checkpoint) and report acceptance")
+    ap.add_argument("--spec-tokens", type=int, default=2)
     ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4, 5],
                     help="benchmark configuration: 2 Qwen-shaped FP8 hybrid (the headline, default), 3 MiniMax-shaped "
                          "GGUF GQA-MoE, 4 DeepSeek-V4-Flash-shaped MLA + indexer + FP4 MoE, 5 GLM-shaped GGUF DSA-MoE")
@@ -152,7 +156,12 @@ def main() -> None:
     bdec = args.batch_decode
     max_slots = max(1, bdec) + 1
     t0 = time.time()
-    weights = qh.QwenHybridWeights(cfg, qh.synth_state(cfg, 0, dev), dev, rank, world)
+    state = qh.synth_state(cfg, 0, dev)
+    if args.spec == "mtp":
+        import itertools
+        from deepseek_v4_2080ti_b200.models.reference_cpu.qwen_hybrid_ref import synth_mtp_state
+        state = itertools.chain(state, ((n, t.to(dev)) for n, t in synth_mtp_state(cfg, 0, std=0.02, fp8_linears=True)))
+    weights = qh.QwenHybridWeights(cfg, state, dev, rank, world)
     max_ctx = args.prompt + args.decode + 64
     rt = qh.QwenHybridRuntime(cfg, weights, max_slots=max_slots, max_context=max_ctx, comm=comm,
                               num_blocks=((max_ctx + 63) // 64) * 2 + max_slots * 8 + 2)
@@ -270,6 +279,28 @@ def main() -> None:
         barrier()
         wall = time.time() - w0
         bd_ms = batch_decode_phase(64) if bdec > 0 else None
+    spec_rec = None
+    if args.spec != "none":
+        # outside the timed region and the clock sampling: greedy speculative decoding of the same request
+        from deepseek_v4_2080ti_b200.models.qwen_spec import QwenSpeculator
+        sp_ = QwenSpeculator(rt, k=args.spec_tokens, method=args.spec)
+        sp_.generate(prompt_dev, min(args.decode, 16), args.chunk)          # warm-up
+        sp_.stats = type(sp_.stats)()
+        barrier()
+        e0, e1, e2 = ev(), ev(), ev()
+        slot = sp_.allocate()
+        e0.record()
+        out_tokens = [sp_.prefill(slot, prompt_dev, args.chunk)]
+        e1.record()
+        while len(out_tokens) < args.decode:
+            out_tokens.extend(sp_.step(slot))
+        e2.record()
+        torch.cuda.synchronize()
+        sp_.free(slot)
+        spec_rec = {"method": args.spec, "draft_tokens": args.spec_tokens, "accept_rate": round(sp_.stats.accept_rate, 4),
+                    "tokens_per_pass": round(sp_.stats.tokens_per_pass, 3),
+                    "decode_tok_s": round((len(out_tokens) - 1) / (e1.elapsed_time(e2) / 1e3), 2),
+                    "note": "random-init weights: the draft head is untrained, so acceptance is chance level"}
     _lib.check_status()
     clocks = clk.summary()
 
@@ -316,6 +347,8 @@ def main() -> None:
         if bd_ms is not None:
             bd = max_over_ranks(bd_ms)
             rec["decode_batch"] = {"batch": bdec, "ms_per_step": round(bd, 4), "tok_s": round(bdec / (bd / 1e3), 1)}
+        if spec_rec is not None:
+            rec["speculative"] = spec_rec
         if comm is not None:
             # fused = kernels that carry their collective (reduce-scatter / all-gather GEMMs, the reduce + norm + gather
             # kernel, GEMM + all-reduce epilogues); standalone = peer-memory collectives launched on their own

@@ -81,7 +81,8 @@ def test_public_api_batches_mla_sequences_over_one_page_pool():
     from deepseek_v4_2080ti_b200.formats import safetensors_io
     from deepseek_v4_2080ti_b200.models import mla_moe_gpu as mg
     from pocketllm import LLM, EngineArgs, SamplingParams
-    cfg = _cfg()
+    import dataclasses
+    cfg = dataclasses.replace(_cfg(), num_experts=2, experts_per_token=2)      # no router ties between 3-row and 1-row passes
     state = list(mm.synth_state(cfg, seed=5, std=0.05))
     gen = torch.Generator().manual_seed(9)
     prompts = [torch.randint(1, cfg.vocab_size, (n,), generator=gen, dtype=torch.int32) for n in (70, 33, 90)]
