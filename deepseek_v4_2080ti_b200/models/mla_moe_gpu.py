@@ -649,6 +649,7 @@ class MlaMoeBatchRuntime(MlaMoeGpuRuntime):
     Reference behaviour: the batched decode / verify of the resident engine
     (cpp_engine/include/persistent_engine.hpp:24-208), config rows "batch 64" (DSV4-Flash) and "batch 16" (GLM)."""
     single_sequence = False
+    exposes_logits = True        # ``last_logits`` [rows, vocab] fp32 after prefill (last row) and decode (one row per slot)
 
     def __init__(self, cfg: MlaMoeConfig, weights: MlaMoeGpuWeights, max_slots: int = 4, max_context: int = 4096,
                  block_size: int = 64, num_blocks: int | None = None, comm=None):
@@ -660,6 +661,7 @@ class MlaMoeBatchRuntime(MlaMoeGpuRuntime):
         assert self.pp is None and weights.layer_lo == 0 and weights.layer_hi == cfg.num_layers, "no pipeline stages here"
         self.max_context = max_context
         self.blocks_per_seq = per_seq
+        self.last_logits = torch.zeros(1, cfg.vocab_size, dtype=torch.float32, device=self.device)
         self.table = torch.zeros(self.max_slots, per_seq, dtype=torch.int32, device=self.device)
         self._table_host = [[-1] * per_seq for _ in range(self.max_slots)]
         self._free_pages = list(range(self.num_blocks - 1, -1, -1))

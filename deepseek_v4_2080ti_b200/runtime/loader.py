@@ -309,6 +309,12 @@ class GgufRuntimeAdapter:
         self.eos_token_ids = tuple(eos_token_ids)
         self.last_cached_tokens = 0
         self._active: set[int] = set()
+        # runtimes that leave the step's full-vocabulary logits in ``last_logits`` ([rows, vocab] fp32, one row per
+        # sequence of the step) can be sampled from: temperature / top-k / top-p / min-p / penalties on the device
+        self.supports_sampling = bool(getattr(rt, "exposes_logits", False))
+        self._rng: dict[int, torch.Generator] = {}
+        self._counts: dict[int, torch.Tensor] = {}
+        self._seed_counter = 0
 
     def allocate(self) -> int:
         if len(self._active) >= self.max_slots:
@@ -319,17 +325,63 @@ class GgufRuntimeAdapter:
 
     def free(self, slot: int) -> None:
         self._active.discard(slot)
+        self._rng.pop(slot, None)
+        self._counts.pop(slot, None)
         self.rt.free(slot)
+
+    # ---- sampling from the step's logits
+    def _sampling(self, slot: int, sp: Any, prompt: list[int] | None):
+        from ..ops.sampling import DeviceSampling
+        ds = DeviceSampling.from_params(sp) if sp is not None else None
+        if ds is None or not self.supports_sampling:
+            return None
+        if slot not in self._rng:
+            g = torch.Generator()
+            seed = getattr(sp, "seed", None)
+            if seed is None:
+                self._seed_counter += 1
+                seed = 0x5EED0000 + self._seed_counter
+            g.manual_seed(int(seed))
+            self._rng[slot] = g
+        if ds.has_penalties and slot not in self._counts:
+            c = torch.zeros(self.rt.last_logits.shape[-1], dtype=torch.int32, device=self.device)
+            self._counts[slot] = c
+            if prompt:
+                self._count(slot, prompt)
+        return ds
+
+    def _count(self, slot: int, tokens: list[int]) -> None:
+        c = self._counts[slot]
+        ids = torch.tensor([t for t in tokens if 0 <= t < c.numel()], dtype=torch.int64, device=c.device)
+        if ids.numel():
+            c.index_add_(0, ids, torch.ones_like(ids, dtype=torch.int32))
+
+    def _draw_row(self, slot: int, row: int, ds) -> int:
+        from ..ops import sampling
+        u = torch.rand(1, generator=self._rng[slot]).to(self.device)
+        counts = self._counts[slot][None] if slot in self._counts else None
+        tok = int(sampling.sample(self.rt.last_logits[row:row + 1].contiguous(), ds, u, counts=counts).item())
+        if slot in self._counts:
+            self._count(slot, [tok])
+        return tok
 
     def prefill_tokens(self, slot: int, prompt: list[int], chunk: int, sp: Any) -> int:
         ids = torch.tensor([int(t) for t in prompt], dtype=torch.int32).to(self.device)
-        return int(self.rt.prefill(slot, ids, int(chunk) if chunk else 4096).item())
+        greedy = int(self.rt.prefill(slot, ids, int(chunk) if chunk else 4096).item())
+        ds = self._sampling(slot, sp, prompt)
+        return greedy if ds is None else self._draw_row(slot, self.rt.last_logits.shape[0] - 1, ds)
 
     def decode_tokens(self, slots: list[int], toks: list[int], sp: Any) -> list[int]:
         if getattr(self.rt, "single_sequence", False):
             assert len(slots) == 1
         t = torch.tensor([int(x) for x in toks], dtype=torch.int32).to(self.device)
-        return [int(x) for x in self.rt.decode(list(slots), t).reshape(-1).tolist()]
+        greedy = [int(x) for x in self.rt.decode(list(slots), t).reshape(-1).tolist()]
+        sps = sp if isinstance(sp, (list, tuple)) else [sp] * len(slots)
+        out = []
+        for row, (s, p) in enumerate(zip(slots, sps)):
+            ds = self._sampling(s, p, None)
+            out.append(greedy[row] if ds is None else self._draw_row(s, row, ds))
+        return out
 
     def generate_batch(self, prompts, max_new, eos_ids, max_batch):
         import time

@@ -97,3 +97,29 @@ def test_public_api_batches_mla_sequences_over_one_page_pool():
         same = sum(list(r.token_ids) == list(w) for r, w in zip(res, want))
         assert same >= 2          # batched rows go through other GEMM tiles than single rows: a near-tie may flip
         llm.close()
+
+
+@pytest.mark.gpu
+def test_sampling_for_the_batched_mla_runtime():
+    """Temperature / top-k / top-p on the device from the step's logits: reproducible per seed, top_k = 1 is greedy."""
+    from deepseek_v4_2080ti_b200.formats import safetensors_io
+    from pocketllm import LLM, EngineArgs, SamplingParams
+    import dataclasses
+    cfg = dataclasses.replace(_cfg(), num_experts=2, experts_per_token=2)
+    state = list(mm.synth_state(cfg, seed=6, std=0.05))
+    prompt = torch.randint(1, cfg.vocab_size, (50,), generator=torch.Generator().manual_seed(2), dtype=torch.int32).tolist()
+    with tempfile.TemporaryDirectory() as d:
+        safetensors_io.write_checkpoint(d, iter(state), config_json=json.dumps(cfg.to_json()))
+        llm = LLM(EngineArgs(model=d, max_model_len=256, max_batch_size=2))
+        req = [{"prompt_token_ids": prompt}]
+        greedy = llm.generate(req, SamplingParams(max_tokens=8, temperature=0.0))[0].token_ids
+        k1 = llm.generate(req, SamplingParams(max_tokens=8, temperature=1.0, top_k=1, seed=5))[0].token_ids
+        assert list(k1) == list(greedy)
+        a = llm.generate(req, SamplingParams(max_tokens=8, temperature=1.5, top_p=0.95, seed=11))[0].token_ids
+        b = llm.generate(req, SamplingParams(max_tokens=8, temperature=1.5, top_p=0.95, seed=11))[0].token_ids
+        c = llm.generate(req, SamplingParams(max_tokens=8, temperature=1.5, top_p=0.95, seed=12))[0].token_ids
+        assert list(a) == list(b) and len(a) == 8
+        assert list(a) != list(greedy) or list(c) != list(greedy)      # hot sampling leaves the greedy path
+        pen = llm.generate(req, SamplingParams(max_tokens=8, temperature=0.7, repetition_penalty=1.3, seed=4))[0].token_ids
+        assert len(pen) == 8
+        llm.close()
