@@ -74,6 +74,7 @@ class GpuLayer:
     shared_down: PackedLinear | None = None
     w13: moe.ExpertWeights | None = None
     w2: moe.ExpertWeights | None = None
+    offload: "moe.OffloadedExperts | None" = None      # experts in host memory behind a hot cache instead of w13 / w2
 
 
 class Fp8Block:
@@ -114,7 +115,7 @@ class Fp8Block:
 class MlaMoeGpuWeights:
     def __init__(self, cfg: MlaMoeConfig, state: Iterator[tuple[str, torch.Tensor]], device="cuda", rank: int = 0,
                  world: int = 1, dense_fp8: bool = False, layer_range: tuple[int, int] | None = None,
-                 gguf_mix: dict[str, str] | None = None, routed_tp: bool | None = None):
+                 gguf_mix: dict[str, str] | None = None, routed_tp: bool | None = None, expert_cache_slots: int = 0):
         """``rank`` / ``world``: position in the tensor/expert-parallel group (of this pipeline stage);
         ``layer_range``: the layers this stage holds (embedding only with layer 0, norm + head only with the last);
         ``gguf_mix``: GGUF types per weight class {"attn", "ffn", "gate_up", "down"} - quantised at load;
@@ -123,6 +124,9 @@ class MlaMoeGpuWeights:
         option (src/models/glm_dsa/spec.py:282-325): no load imbalance between ranks at small batches, the same
         sum over ranks afterwards.  Default: the environment variable of the same name."""
         import os
+        # > 0: the routed experts of every layer stay in pinned host memory and only this many occupy device slots
+        # (ops.moe.OffloadedExperts); bf16, FP4 and GGUF experts
+        self.expert_cache_slots = int(expert_cache_slots)
         self.routed_tp = (os.environ.get("GLM_ROUTED_TP", "0") == "1") if routed_tp is None else bool(routed_tp)
         if world == 1:
             self.routed_tp = False
@@ -349,6 +353,9 @@ class MlaMoeGpuWeights:
             lw.w13 = moe.ExpertWeights.from_bf16([torch.cat([rows13(sd[f + f"experts.{e}.w1.weight"]),
                                                              rows13(sd[f + f"experts.{e}.w3.weight"])]).to(dev) for e in es])
             lw.w2 = moe.ExpertWeights.from_bf16([cols2(sd[f + f"experts.{e}.w2.weight"]).contiguous().to(dev) for e in es])
+        if self.expert_cache_slots > 0:
+            lw.offload = moe.OffloadedExperts(lw.w13, lw.w2, self.expert_cache_slots, dev, self.expert_lo)
+            lw.w13 = lw.w2 = None
         return lw
 
 
@@ -450,6 +457,8 @@ class MlaMoeGpuRuntime:
         logits = _mm(x, lw.gate, out_f32=True)
         idx, wts = moe.route(logits, lw.gate_bias, cfg.experts_per_token, cfg.score_func, cfg.norm_topk, cfg.route_scale)
         base = self._swiglu(x, lw.shared_gu, lw.shared_down) if lw.shared_gu is not None else None
+        if lw.offload is not None:
+            return self.comm.all_reduce(lw.offload.forward(x, idx, wts, cfg.swiglu_limit, base))
         if getattr(self.comm, "world", 1) > 1 and hasattr(self.comm, "moe_combine"):
             # weighted combine + sum over the expert-parallel ranks in one peer-memory kernel
             return moe.experts_forward(x, idx, wts, lw.w13, lw.w2, self.w.expert_lo, cfg.swiglu_limit, base, comm=self.comm)

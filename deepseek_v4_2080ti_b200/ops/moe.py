@@ -139,3 +139,60 @@ def experts_forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, w13: 
     rc = L.b200_moe_combine(_lib.ptr(y), _lib.ptr(route_row), _lib.ptr(wts), _lib.ptr(base), _lib.ptr(out), t, k, h, s)
     _lib.check(rc, "moe_combine")
     return out
+
+
+class OffloadedExperts:
+    """Routed experts of one layer kept in pinned host memory with ``capacity`` device slots per matrix
+    (``components.expert_cache.HotExpertCache``): a call copies in the experts its tokens route to (least recently
+    used ones make room), rewrites the routing ids to slot numbers and runs the ordinary grouped GEMMs over the slot
+    arrays.  For models whose experts do not fit beside the caches, and for prefill, where a chunk touches most
+    experts once and the copies overlap the previous layer.  A chunk that routes to more experts than there are slots
+    is split in halves by tokens.  Reference: GPUPrefillMoEBackend with its hot-expert cache
+    (src/components/moe/gpu_prefill_backend.py:41-104, 105-901)."""
+
+    def __init__(self, w13: ExpertWeights, w2: ExpertWeights, capacity: int, device, expert_lo: int = 0):
+        from ..components.expert_cache import HotExpertCache
+        assert w13.experts == w2.experts and (w13.scales is None or w13.wfmt >= 3) and (w2.scales is None or w2.wfmt >= 3), \
+            "per-expert scale grids (FP8) are not packed into the slabs"
+        self.experts, self.expert_lo = w13.experts, int(expert_lo)
+        self.capacity = min(int(capacity), self.experts)
+        self.dev = torch.device(device)
+
+        def split(w: ExpertWeights):
+            per = w.weight.reshape(w.experts, -1)
+            host = per.contiguous().view(torch.uint8).cpu()
+            cache = HotExpertCache(host, self.capacity, self.dev)
+            shape = (self.capacity * w.n, w.k) if w.wfmt == WF_BF16 else (self.capacity, *w.weight.shape[1:])
+            view = cache.slots.view(w.weight.dtype).view(*shape)
+            lut = w.scales.to(self.dev) if w.scales is not None else None
+            return cache, ExpertWeights(w.wfmt, view, lut, w.n, w.k, self.capacity)
+
+        self.c13, self.w13 = split(w13)
+        self.c2, self.w2 = split(w2)
+
+    def stats(self) -> dict:
+        a, b = self.c13.stats, self.c2.stats
+        return {"hits": a.hits + b.hits, "misses": a.misses + b.misses, "evictions": a.evictions + b.evictions,
+                "bytes_copied": a.bytes_copied + b.bytes_copied}
+
+    def forward(self, x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, swiglu_limit: float = 0.0,
+                base: torch.Tensor | None = None) -> torch.Tensor:
+        lo, hi = self.expert_lo, self.expert_lo + self.experts
+        local = (idx >= lo) & (idx < hi)
+        need = torch.unique(idx[local]).tolist()                       # host sync: the copies depend on the routing
+        if len(need) > self.capacity and x.shape[0] > 1:
+            h = x.shape[0] // 2
+            parts = [self.forward(x[a:b].contiguous(), idx[a:b].contiguous(), wts[a:b].contiguous(), swiglu_limit,
+                                  None if base is None else base[a:b].contiguous()) for a, b in ((0, h), (h, x.shape[0]))]
+            return torch.cat(parts)
+        if len(need) > self.capacity:
+            raise RuntimeError(f"one token routes to {len(need)} experts of this rank; the cache holds {self.capacity}")
+        local_ids = [e - lo for e in need]
+        s13, s2 = self.c13.fetch(local_ids), self.c2.fetch(local_ids)
+        assert torch.equal(s13, s2), "the two caches see the same requests and must agree on the slots"
+        table = torch.full((self.experts + 1,), self.capacity, dtype=torch.int32, device=idx.device)
+        if local_ids:
+            table[torch.tensor(local_ids, dtype=torch.long, device=idx.device)] = s13.to(idx.device)
+        # ids of other ranks' experts map to `capacity`: outside [0, capacity), so the routing plan drops them
+        slot_idx = table[torch.where(local, idx - lo, torch.full_like(idx, self.experts)).long()].contiguous()
+        return experts_forward(x, slot_idx, wts, self.w13, self.w2, 0, swiglu_limit, base)

@@ -459,3 +459,33 @@ def test_batched_decode_over_a_shared_page_pool(indexer):
     rep = [json.loads(l) for l in out.getvalue().splitlines()]
     assert rep[0] == {"ok": True, "slot": s_new} and rep[1]["token"] == t[0] and rep[2]["tokens"] == [t[1]]
     assert not rep[3]["ok"] and rep[4]["stats"]["errors"] == 1
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "fp4"])
+def test_experts_behind_the_hot_cache_give_the_resident_result(fmt):
+    """Routed experts kept in pinned host memory with 3 device slots for 8 experts: copies on a side stream, LRU
+    eviction, routing ids rewritten to slots.  Same logits as with every expert resident."""
+    from deepseek_v4_2080ti_b200.models import mla_moe as mm
+    from deepseek_v4_2080ti_b200.models import mla_moe_gpu as mg
+    from deepseek_v4_2080ti_b200.ops import _lib
+    import dataclasses
+    cfg = dataclasses.replace(_cfg(False), expert_format=fmt)
+    state = list(mm.synth_state(cfg, seed=13, std=0.05))
+    resident = mg.MlaMoeGpuRuntime(cfg, mg.MlaMoeGpuWeights(cfg, iter(state), "cuda"), max_context=256)
+    cached_w = mg.MlaMoeGpuWeights(cfg, iter(state), "cuda", expert_cache_slots=3)
+    cached = mg.MlaMoeGpuRuntime(cfg, cached_w, max_context=256)
+    moe_layers = [lw for lw in cached_w.layers if lw.offload is not None]
+    assert len(moe_layers) == cfg.num_layers - cfg.first_dense_layers and all(lw.w13 is None for lw in moe_layers)
+    ids = torch.randint(1, cfg.vocab_size, (70,), generator=torch.Generator().manual_seed(14), dtype=torch.int32).cuda()
+    want = torch.cat([resident.forward(ids[:40]), resident.forward(ids[40:])])
+    got = torch.cat([cached.forward(ids[:40]), cached.forward(ids[40:])])        # 40 tokens x top-2 touch all 8 experts: halves
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert ((got - want).norm() / want.norm()) < 2e-3
+    st = moe_layers[0].offload.stats()
+    assert st["misses"] >= 16 and st["evictions"] > 0 and st["bytes_copied"] > 0
+    # decode steps: one token routes to 2 experts, all fit
+    for _ in range(3):
+        tok = resident.forward(ids[:1])
+        tok2 = cached.forward(ids[:1])
+        assert ((tok2 - tok).norm() / tok.norm()) < 2e-3
