@@ -105,6 +105,7 @@ PYBIND11_MODULE(pocketllm_cpp, m) {
       .def_property_readonly("max_blocks_per_seq", &BlockTable::max_blocks_per_seq)
       .def("ensure_capacity", &BlockTable::ensure_capacity)
       .def("share_prefix", &BlockTable::share_prefix)
+      .def("adopt", [](BlockTable& t, int dst, const std::vector<int32_t>& blocks) { return t.adopt(dst, blocks.data(), int(blocks.size())); })
       .def("free_slot", &BlockTable::free_slot)
       .def("blocks_in", &BlockTable::blocks_in)
       .def("block_at", &BlockTable::block_at)

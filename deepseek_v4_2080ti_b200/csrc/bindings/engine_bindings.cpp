@@ -36,6 +36,8 @@ PYBIND11_MODULE(pocketllm_engine_cpp, m) {
   py::class_<QwenEngineOptions>(m, "QwenEngineOptions")
       .def(py::init<>())
       .def_readwrite("max_slots", &QwenEngineOptions::max_slots)
+      .def_readwrite("prefix_cache_interval", &QwenEngineOptions::prefix_cache_interval)
+      .def_readwrite("prefix_cache_entries", &QwenEngineOptions::prefix_cache_entries)
       .def_readwrite("max_context", &QwenEngineOptions::max_context)
       .def_readwrite("block_tokens", &QwenEngineOptions::block_tokens)
       .def_readwrite("prefill_chunk", &QwenEngineOptions::prefill_chunk)
@@ -47,6 +49,10 @@ PYBIND11_MODULE(pocketllm_engine_cpp, m) {
 
   py::class_<QwenEngineStats>(m, "QwenEngineStats")
       .def_readonly("kernel_launches", &QwenEngineStats::kernel_launches)
+      .def_readonly("prefix_hits", &QwenEngineStats::prefix_hits)
+      .def_readonly("prefix_tokens_reused", &QwenEngineStats::prefix_tokens_reused)
+      .def_readonly("prefix_snapshots", &QwenEngineStats::prefix_snapshots)
+      .def_readonly("prefix_evictions", &QwenEngineStats::prefix_evictions)
       .def_readonly("load_seconds", &QwenEngineStats::load_seconds)
       .def_readonly("weight_bytes", &QwenEngineStats::weight_bytes)
       .def_readonly("state_bytes", &QwenEngineStats::state_bytes);
@@ -92,6 +98,7 @@ PYBIND11_MODULE(pocketllm_engine_cpp, m) {
              { py::gil_scoped_release rel; out = h.eng->generate(prompt, max_new, &ps, &ds); }
              return py::make_tuple(out, ps, ds);
            }, py::arg("prompt"), py::arg("max_new_tokens"))
+      .def("prefix_entries", [](EngineHolder& h) { return h.eng->prefix_entries(); })
       .def("last_topk", [](EngineHolder& h, int k) { return h.eng->last_topk(k); })
       // the target's output head as drafters see it: shard geometry, and a host-to-host projection for tests
       .def("target_head_info", [](EngineHolder& h) {

@@ -40,6 +40,18 @@ bool BlockTable::share_prefix(int dst, int src, int n_blocks) {
   return true;
 }
 
+bool BlockTable::adopt(int dst, const int32_t* blocks, int n_blocks) {
+  if (dst < 0 || dst >= max_slots_) throw std::out_of_range("BlockTable: slot");
+  if (counts_[dst] != 0 || n_blocks < 0 || n_blocks > max_blocks_) return false;
+  for (int i = 0; i < n_blocks; ++i) {
+    pool_.retain(blocks[i]);
+    image_[static_cast<size_t>(dst) * max_blocks_ + i] = blocks[i];
+  }
+  counts_[dst] = n_blocks;
+  dirty_[dst] = 1;
+  return true;
+}
+
 void BlockTable::free_slot(int slot) {
   if (slot < 0 || slot >= max_slots_) throw std::out_of_range("BlockTable: slot");
   int32_t* r = image_.data() + static_cast<size_t>(slot) * max_blocks_;

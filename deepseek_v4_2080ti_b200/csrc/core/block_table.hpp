@@ -19,6 +19,9 @@ class BlockTable {
   bool ensure_capacity(int slot, int64_t tokens);
   // Share the first n blocks of `src` into the (empty) row of `dst` (prefix reuse): refcounts go up.
   bool share_prefix(int dst, int src, int n_blocks);
+  // Put `n_blocks` already allocated blocks (held by a prefix cache) at the start of the (empty) row of `dst`; each
+  // gains a reference that free_slot gives back.
+  bool adopt(int dst, const int32_t* blocks, int n_blocks);
   void free_slot(int slot);
   int blocks_in(int slot) const { return counts_.at(slot); }
   int32_t block_at(int slot, int i) const { return image_[static_cast<size_t>(slot) * max_blocks_ + i]; }

@@ -22,6 +22,8 @@
 //                              requests need no helper
 //   --token-ids a,b,c | --token-ids-file F | --tokens N (synthetic ids)   the prompt
 //   --max-new-tokens N --max-context C --prefill-chunk-tokens T --smoke-layers L --max-slots S --device D
+//   --prefix-cache-interval N [--prefix-cache-entries M]   keep KV blocks + recurrent state every N prompt tokens and
+//                              resume later prompts that share the prefix (--qwen-no-prefix-cache: off, the default)
 //   --qwen-temperature F --qwen-top-k K --qwen-top-p P --qwen-seed S     host-side sampling (default greedy)
 //   --eos a,b                  stop tokens;  --json  machine-readable result line
 // (Role of cpp_engine/engine/main.cpp.)
@@ -51,7 +53,7 @@ namespace {
 struct Args {
   std::string ckpt, model_config, grep, tensor, token_ids, token_file, eos, host = "127.0.0.1", python = "python", sidecar_gguf,
       chat_family = "deepseek_v4", served_name = "pocketllm";
-  int port = 8000, tp_world = 1, tp_rank = 0, ep_world = 1;
+  int port = 8000, tp_world = 1, tp_rank = 0, ep_world = 1, prefix_interval = 0, prefix_entries = 4;
   std::string nccl_id_path;
   bool serve = false, audit = false, audit_strict = false;
   bool dump_config = false, inspect = false, context_info = false, smoke = false, bench = false, persistent = false,
@@ -148,7 +150,9 @@ bool parse(int argc, char** argv, Args& a) {
     else if (arg == "--qwen-top-k") a.sampling.top_k = std::atoi(val("--qwen-top-k"));
     else if (arg == "--qwen-top-p") a.sampling.top_p = float(std::atof(val("--qwen-top-p")));
     else if (arg == "--qwen-seed") a.seed = std::strtoull(val("--qwen-seed"), nullptr, 10);
-    else if (arg == "--qwen-no-prefix-cache") {}        // accepted: this engine keeps no prefix cache between requests
+    else if (arg == "--qwen-no-prefix-cache") a.prefix_interval = 0;
+    else if (arg == "--prefix-cache-interval") a.prefix_interval = std::atoi(val("--prefix-cache-interval"));
+    else if (arg == "--prefix-cache-entries") a.prefix_entries = std::atoi(val("--prefix-cache-entries"));
     else if (arg == "-h" || arg == "--help") return false;
     else throw std::runtime_error("unknown argument " + arg);
   }
@@ -263,6 +267,8 @@ int main(int argc, char** argv) {
     std::unique_ptr<WeightSource> ws = WeightSource::open(a.ckpt);
     QwenEngineOptions opt;
     opt.max_slots = std::max(1, a.slots);
+    opt.prefix_cache_interval = std::max(0, a.prefix_interval);
+    opt.prefix_cache_entries = std::max(1, a.prefix_entries);
     opt.max_context = a.max_context;
     opt.prefill_chunk = std::max(1, a.chunk);
     opt.layers = a.layers;

@@ -133,7 +133,12 @@ QwenNativeEngine::QwenNativeEngine(const QwenConfig& cfg, WeightSource& weights,
   // ---- KV cache, recurrent state, block table
   const int bs = opt_.block_tokens;
   max_blocks_per_seq_ = int((opt_.max_context + bs - 1) / bs);
+  if (opt_.prefix_cache_interval < 0 || opt_.prefix_cache_interval % bs)
+    throw std::runtime_error("prefix_cache_interval must be a multiple of block_tokens");
   num_blocks_ = max_blocks_per_seq_ * opt_.max_slots + 1;          // block 0 is the scratch block
+  // cached prefixes keep their blocks after the sequence that wrote them is gone: room for one context per entry
+  // (entries are dropped, oldest first, when a running sequence needs the blocks)
+  if (opt_.prefix_cache_interval > 0) num_blocks_ += max_blocks_per_seq_ * std::max(1, opt_.prefix_cache_entries);
   pool_ = std::make_unique<BlockPool>(num_blocks_, bs);
   table_ = std::make_unique<BlockTable>(*pool_, opt_.max_slots, max_blocks_per_seq_);
   lengths_.assign(opt_.max_slots, 0);
@@ -668,18 +673,94 @@ void QwenNativeEngine::sample_rows(int rows, int32_t* tokens) {
 }
 
 // ------------------------------------------------------------------------------------------------ batch interface
+// ------------------------------------------------------------------------------------------------ prefix cache
+int64_t QwenNativeEngine::prefix_lookup(int slot, const std::vector<int32_t>& tokens) {
+  PrefixEntry* best = nullptr;
+  for (auto& e : prefix_) {
+    const size_t n = e->tokens.size();
+    if (n + 1 > tokens.size() || (best && n <= best->tokens.size())) continue;     // at least one token stays to compute
+    if (std::equal(e->tokens.begin(), e->tokens.end(), tokens.begin())) best = e.get();
+  }
+  if (!best) return 0;
+  if (!table_->adopt(slot, best->blocks.data(), int(best->blocks.size()))) return 0;
+  cuda_check(cudaMemcpyAsync(states_.as<float>() + state_slot_stride_ * slot, best->states.get(), state_slot_stride_ * 4,
+                             cudaMemcpyDeviceToDevice, stream_), "prefix state restore");
+  cuda_check(cudaMemcpyAsync(tails_.as<uint8_t>() + tail_slot_stride_ * slot * 2, best->tails.get(), tail_slot_stride_ * 2,
+                             cudaMemcpyDeviceToDevice, stream_), "prefix tail restore");
+  best->stamp = ++prefix_clock_;
+  lengths_[slot] = int64_t(best->tokens.size());
+  ++stats_.prefix_hits;
+  stats_.prefix_tokens_reused += best->tokens.size();
+  return lengths_[slot];
+}
+
+void QwenNativeEngine::prefix_drop(size_t i) {
+  for (int32_t b : prefix_[i]->blocks) pool_->release(b);
+  prefix_.erase(prefix_.begin() + long(i));
+  ++stats_.prefix_evictions;
+}
+
+void QwenNativeEngine::prefix_store(int slot, const int32_t* tokens, int64_t n) {
+  for (auto& e : prefix_)
+    if (int64_t(e->tokens.size()) == n && std::equal(e->tokens.begin(), e->tokens.end(), tokens)) {
+      e->stamp = ++prefix_clock_;
+      return;
+    }
+  while (int(prefix_.size()) >= std::max(1, opt_.prefix_cache_entries)) {
+    size_t oldest = 0;
+    for (size_t i = 1; i < prefix_.size(); ++i)
+      if (prefix_[i]->stamp < prefix_[oldest]->stamp) oldest = i;
+    prefix_drop(oldest);
+  }
+  auto e = std::make_unique<PrefixEntry>();
+  e->tokens.assign(tokens, tokens + n);
+  const int nb = int(n / opt_.block_tokens);
+  for (int i = 0; i < nb; ++i) {
+    const int32_t b = table_->block_at(slot, i);
+    pool_->retain(b);
+    e->blocks.push_back(b);
+  }
+  e->states = DeviceBuffer(state_slot_stride_ * 4);
+  e->tails = DeviceBuffer(tail_slot_stride_ * 2);
+  cuda_check(cudaMemcpyAsync(e->states.get(), states_.as<float>() + state_slot_stride_ * slot, state_slot_stride_ * 4,
+                             cudaMemcpyDeviceToDevice, stream_), "prefix state snapshot");
+  cuda_check(cudaMemcpyAsync(e->tails.get(), tails_.as<uint8_t>() + tail_slot_stride_ * slot * 2, tail_slot_stride_ * 2,
+                             cudaMemcpyDeviceToDevice, stream_), "prefix tail snapshot");
+  e->stamp = ++prefix_clock_;
+  prefix_.push_back(std::move(e));
+  ++stats_.prefix_snapshots;
+}
+
 StepResult QwenNativeEngine::batch_prefill(const std::vector<PrefillItem>& items) {
   StepResult r;
+  const int64_t every = opt_.prefix_cache_interval;
   for (const PrefillItem& it : items) {
     if (it.tokens.empty()) { r.next_tokens.push_back(-1); continue; }
     if (it.position != lengths_.at(it.slot)) throw std::runtime_error("prefill position does not continue the slot");
     int32_t tok = -1;
     const int total = int(it.tokens.size());
-    for (int o = 0; o < total; o += opt_.prefill_chunk) {
-      const int t = std::min(opt_.prefill_chunk, total - o);
-      if (!reserve(it.slot, it.position + o + t)) throw std::runtime_error("KV cache exhausted");
+    int o = 0;
+    // a fresh sequence may resume from a cached prefix; snapshots are taken only for prompts that arrive whole
+    // (position 0 and last_chunk), so a stored prefix is always a prefix of a complete prompt
+    const bool cacheable = every > 0 && it.position == 0 && it.last_chunk;
+    if (cacheable) o = int(prefix_lookup(it.slot, it.tokens));
+    while (o < total) {
+      int t = std::min(opt_.prefill_chunk, total - o);
+      if (cacheable) {
+        const int64_t boundary = (int64_t(o) / every + 1) * every;              // next snapshot point after o
+        if (boundary < total) t = int(std::min<int64_t>(t, boundary - o));
+      }
+      while (!reserve(it.slot, it.position + o + t)) {
+        if (prefix_.empty() || it.position + o + t > opt_.max_context) throw std::runtime_error("KV cache exhausted");
+        size_t oldest = 0;                                  // cached prefixes give way to running sequences
+        for (size_t i = 1; i < prefix_.size(); ++i)
+          if (prefix_[i]->stamp < prefix_[oldest]->stamp) oldest = i;
+        prefix_drop(oldest);
+      }
       const bool last = it.last_chunk && o + t >= total;
       tok = forward_prefill(it.slot, it.tokens.data() + o, t, it.position + o, last);
+      o += t;
+      if (cacheable && o < total && o % every == 0) prefix_store(it.slot, it.tokens.data(), o);
     }
     r.next_tokens.push_back(tok);
   }

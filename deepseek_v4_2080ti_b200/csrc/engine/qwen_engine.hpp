@@ -90,11 +90,18 @@ struct QwenEngineOptions {
   std::vector<int32_t> eos_tokens;
   HostSamplingParams sampling;   // temperature 0 = greedy (arg-max on the device, 4 bytes read back per sequence)
   uint64_t seed = 0;
+  // Prefix cache: > 0 keeps, at every multiple of this many tokens of a prompt (a multiple of block_tokens), the
+  // sequence's KV blocks (shared by reference) and a copy of its recurrent state; a later prompt that starts with
+  // the same tokens resumes from the longest such point.  Reference: the snapshot ring of the Qwen engine
+  // (cpp_engine/engine/qwen_engine.cpp:5369-5563).
+  int prefix_cache_interval = 0;
+  int prefix_cache_entries = 4;
   int tp_world = 1, tp_rank = 0;   // tensor parallelism: this process is rank tp_rank of tp_world
   std::string nccl_id_path;        // file through which rank 0 hands the NCCL id to the others
 };
 
 struct QwenEngineStats {
+  uint64_t prefix_hits = 0, prefix_tokens_reused = 0, prefix_snapshots = 0, prefix_evictions = 0;
   uint64_t kernel_launches = 0;
   double load_seconds = 0;
   size_t weight_bytes = 0, state_bytes = 0;
@@ -173,6 +180,21 @@ class QwenNativeEngine : public InferenceEngine {
   size_t kv_layer_stride_ = 0, state_slot_stride_ = 0, state_layer_stride_ = 0, tail_slot_stride_ = 0,
          tail_layer_stride_ = 0;
   std::unique_ptr<Scratch> s_;
+
+  // prefix cache
+  struct PrefixEntry {
+    std::vector<int32_t> tokens;       // the prefix itself (compared token by token: no hash collisions to reason about)
+    std::vector<int32_t> blocks;       // tokens.size() / block_tokens KV blocks, one reference held for each
+    DeviceBuffer states, tails;        // recurrent state and convolution tails after the prefix
+    uint64_t stamp = 0;
+  };
+  std::vector<std::unique_ptr<PrefixEntry>> prefix_;
+  uint64_t prefix_clock_ = 0;
+  int64_t prefix_lookup(int slot, const std::vector<int32_t>& tokens);     // adopts the longest match; returns its length
+  void prefix_store(int slot, const int32_t* tokens, int64_t n);
+  void prefix_drop(size_t i);
+ public:
+  int prefix_entries() const { return int(prefix_.size()); }
 };
 
 }  // namespace pocket

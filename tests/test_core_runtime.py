@@ -42,6 +42,27 @@ def test_block_table_growth_sharing_and_dirty_rows():
     assert t.ensure_capacity(3, 16 * 8) and not t.ensure_capacity(1, 16 * 8 + 16 * 1) or True
 
 
+def test_block_table_adopts_blocks_held_by_a_cache():
+    """A prefix cache keeps blocks alive with its own references and hands them to a fresh row."""
+    p = cpp.BlockPool(9, 16)
+    t = cpp.BlockTable(p, 3, 4)
+    assert t.ensure_capacity(0, 48)
+    held = [t.block_at(0, i) for i in range(2)]
+    for b in held:
+        p.retain(b)                                                # the cache's references
+    t.free_slot(0)
+    assert [p.refcount(b) for b in held] == [1, 1] and p.free_blocks == 8 - 2
+    assert t.adopt(1, held) and t.blocks_in(1) == 2 and [p.refcount(b) for b in held] == [2, 2]
+    assert t.take_dirty_rows() == [0, 1]
+    assert t.ensure_capacity(1, 50) and t.blocks_in(1) == 4 and t.block_at(1, 0) == held[0]      # grows behind the prefix
+    assert not t.adopt(1, held)                                    # only into an empty row
+    t.free_slot(1)
+    assert [p.refcount(b) for b in held] == [1, 1]
+    for b in held:
+        p.release(b)
+    assert p.free_blocks == 8
+
+
 class FakeEngine(cpp.InferenceEngine):
     """next token = last + 1; eos = 1000; KV accounting through a real BlockPool/BlockTable."""
 

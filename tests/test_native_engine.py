@@ -235,3 +235,46 @@ def test_pybind_engine_and_cpp_backend_match_python_runtime():
         out = llm.generate([{"prompt_token_ids": prompts[0]}], SamplingParams(max_tokens=6))
         assert list(out[0].token_ids) == want[0]
         llm.close()
+
+
+@pytest.mark.gpu
+def test_native_prefix_cache_resumes_from_shared_blocks_and_state():
+    """Prompts that share their first tokens: the second one adopts the cached KV blocks and the recurrent-state
+    snapshot of the longest common multiple of the interval and computes only the rest - same tokens as an engine
+    without the cache (reference: the Qwen engine's snapshot ring, cpp_engine/engine/qwen_engine.cpp:5369-5563)."""
+    from deepseek_v4_2080ti_b200 import pocketllm_engine_cpp as cpp
+    gen = torch.Generator().manual_seed(21)
+    with tempfile.TemporaryDirectory() as d:
+        cfg, _ = _write_tiny(d, "cuda")
+        base = torch.randint(0, cfg.vocab_size, (200,), generator=gen, dtype=torch.int32).tolist()
+        other = torch.randint(0, cfg.vocab_size, (60,), generator=gen, dtype=torch.int32).tolist()
+        prompts = [base, base[:150] + other, base[:70] + other, other + base[:100], base]
+        plain_opt = cpp.QwenEngineOptions()
+        plain_opt.max_slots, plain_opt.max_context = 2, 512
+        plain = cpp.QwenEngine(d, plain_opt)
+        want = [list(plain.generate(p, 5)[0]) for p in prompts]
+        del plain
+        opt = cpp.QwenEngineOptions()
+        opt.max_slots, opt.max_context, opt.prefix_cache_interval, opt.prefix_cache_entries = 2, 512, 64, 8
+        eng = cpp.QwenEngine(d, opt)
+        got, reused = [], []
+        for p in prompts:
+            before = eng.stats().prefix_tokens_reused
+            got.append(list(eng.generate(p, 5)[0]))
+            reused.append(eng.stats().prefix_tokens_reused - before)
+        assert got == want
+        # 200 tokens: snapshots at 64, 128, 192.  150 shared -> resumes at 128; 70 shared -> 64; a prompt that starts
+        # differently -> nothing; the first prompt again -> 192, the longest entry shorter than the prompt
+        assert reused == [0, 128, 64, 0, 192]
+        st = eng.stats()
+        assert st.prefix_hits == 3 and st.prefix_snapshots >= 6 and st.prefix_evictions == 0 and eng.prefix_entries() <= 8
+        # more distinct prompts than entries: the oldest snapshots go, results stay right
+        for k in range(3):
+            p = torch.randint(0, cfg.vocab_size, (200,), generator=gen, dtype=torch.int32).tolist()
+            assert len(eng.generate(p, 2)[0]) == 2
+        assert eng.stats().prefix_evictions > 0 and eng.prefix_entries() == 8
+        assert list(eng.generate(prompts[1], 5)[0]) == want[1]
+        with pytest.raises(Exception):
+            bad = cpp.QwenEngineOptions()
+            bad.prefix_cache_interval = 50                       # not a multiple of the block size
+            cpp.QwenEngine(d, bad)
