@@ -3,6 +3,7 @@
   python -m deepseek_v4_2080ti_b200.utils.microbench gemm --t 8192 --n 5120 --k 5120 [--fmt fp8|bf16] [--splits S]
   python -m deepseek_v4_2080ti_b200.utils.microbench attn_prefill --t 8192 --hq 40 --hkv 8
   python -m deepseek_v4_2080ti_b200.utils.microbench gdn --t 8192 --hv 32 --hk 16
+  python -m deepseek_v4_2080ti_b200.utils.microbench swiglu --t 4096 --n 17408 --k 5120     # n = I: gate_up GEMM [2I, K] + SwiGLU
 
 Used for roofline numbers and as the small-case command for ncu captures (``--iters 1 --warmup 1``).
 """
@@ -39,7 +40,7 @@ def timeit(fn, iters, warmup, flush=True):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "attn_prefill", "attn_decode", "gdn", "gdn_step"])
+    ap.add_argument("op", choices=["gemm", "swiglu", "attn_prefill", "attn_decode", "gdn", "gdn_step"])
     ap.add_argument("--t", type=int, default=8192)
     ap.add_argument("--n", type=int, default=5120)
     ap.add_argument("--k", type=int, default=5120)
@@ -80,6 +81,23 @@ def main():
         flops = 2.0 * a.t * a.n * a.k
         byts = pl.nbytes() + x.numel() * 2 + out.numel() * 2
         rec.update(t=a.t, n=a.n, k=a.k, fmt=a.fmt, kernel=a.kernel, ms=med, ms_best=best, tflops=flops / med / 1e9, gbs=byts / med / 1e6)
+    elif a.op == "swiglu":
+        # feed-forward first half: x [T, K] x [gate | up] [2I, K] -> silu(gate) * up [T, I]; fused epilogue against
+        # GEMM + silu_mul.  The FP8 -> bf16 expansion is inside both timings (it runs on every prefill call).
+        from ..ops import basic
+        w = torch.randn(2 * a.n, a.k, device="cuda") * 0.05
+        q, s = fp8fmt.quantize_block128(w)
+        pl = gemm.PackedLinear.from_fp8(q, s)
+        del w
+        x = torch.randn(a.t, a.k, device="cuda").bfloat16()
+        out = torch.empty(a.t, a.n, dtype=torch.bfloat16, device="cuda")
+        assert gemm.swiglu_fusable(a.t, pl), "shape not taken by the fused kernel"
+        fused, fbest = timeit(lambda: gemm.linear_swiglu(x, pl, out=out), a.iters, a.warmup)
+        gu = torch.empty(a.t, 2 * a.n, dtype=torch.bfloat16, device="cuda")
+        plain, pbest = timeit(lambda: basic.silu_mul(gemm.linear(x, pl, out=gu)), a.iters, a.warmup)
+        flops = 4.0 * a.t * a.n * a.k
+        rec.update(t=a.t, inter=a.n, k=a.k, ms=fused, ms_best=fbest, tflops=flops / fused / 1e9, ms_unfused=plain,
+                   ms_unfused_best=pbest, tflops_unfused=flops / plain / 1e9)
     elif a.op == "attn_prefill":
         bs = 64
         nb = (a.ctx + bs - 1) // bs
