@@ -242,6 +242,36 @@ def main() -> None:
         ref = torch.tensor(out, device=dev)
         dist.broadcast(ref, 0)
         assert ref.tolist() == out, ("gqa_moe ranks disagree", name)
+    # MLA + routed-expert family: expert-parallel ranges, and routed tensor parallelism (every rank holds all experts with
+    # 1 / world of their width), both against the single-rank model; plus the batched runtime over one page pool
+    from deepseek_v4_2080ti_b200.models import mla_moe as mm
+    from deepseek_v4_2080ti_b200.models import mla_moe_gpu as mg
+    mcfg = mm.MlaMoeConfig(vocab_size=512, hidden_size=256, num_layers=3, first_dense_layers=1, dense_intermediate=256,
+                           q_lora_rank=128, kv_lora_rank=128, num_heads=2 * world, qk_nope_dim=64, qk_rope_dim=32,
+                           v_head_dim=128, index_heads=4, index_dim=32, index_topk=24, num_experts=2 * world,
+                           experts_per_token=2 * world, num_shared_experts=1, expert_intermediate=128 * world,
+                           score_func="sigmoid", route_scale=2.5, expert_format="bf16")
+    mstate = list(mm.synth_state(mcfg, seed=12, std=0.05))
+    mprompt = torch.randint(0, mcfg.vocab_size, (80,), generator=torch.Generator().manual_seed(6), dtype=torch.int32)
+    m1, _ = mg.MlaMoeGpuRuntime(mcfg, mg.MlaMoeGpuWeights(mcfg, iter(mstate), dev), max_context=256).generate(mprompt, 6, chunk=32)
+    for routed in (False, True):
+        mw = mg.MlaMoeGpuWeights(mcfg, iter(mstate), dev, rank=rank, world=world, routed_tp=routed)
+        assert mw.routed_tp == routed and (mw.expert_hi - mw.expert_lo) == (mcfg.num_experts if routed else mcfg.num_experts // world)
+        out, _ = mg.MlaMoeGpuRuntime(mcfg, mw, max_context=256, comm=comm).generate(mprompt, 6, chunk=32)
+        torch.cuda.synchronize()
+        comm.check()
+        assert out[:3] == m1[:3], ("mla_moe", "routed_tp" if routed else "ep", out, m1)
+        ref = torch.tensor(out, device=dev)
+        dist.broadcast(ref, 0)
+        assert ref.tolist() == out, ("mla_moe ranks disagree", routed)
+        if routed:
+            brt = mg.MlaMoeBatchRuntime(mcfg, mw, max_slots=2, max_context=256, comm=comm)
+            s0, s1 = brt.allocate(), brt.allocate()
+            f0, f1 = brt.prefill(s0, mprompt.to(dev), 32), brt.prefill(s1, mprompt[:50].to(dev), 32)
+            nxt = brt.decode([s0, s1], torch.cat([f0, f1]).to(torch.int32))
+            torch.cuda.synchronize()
+            comm.check()
+            assert int(f0.item()) == m1[0] and int(nxt[0].item()) == m1[1], ("mla batch", int(f0.item()), nxt.tolist(), m1)
     comm.close()
     dist.barrier()
     if rank == 0:
