@@ -47,7 +47,32 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--speculative-method", default=None)
     s.add_argument("--speculative-tokens", type=int, default=1)
     s.add_argument("--served-model-name", default=None)
+    s.add_argument("--tensor-parallel-supervisor", action=argparse.BooleanOptionalAction, default=True,
+                   help="spawn and supervise the local ranks of a tensor-parallel group (default); with "
+                        "--no-tensor-parallel-supervisor this process is one rank (--tensor-parallel-rank)")
+    s.add_argument("--tensor-parallel-startup-timeout", type=float, default=1800.0, metavar="SECONDS",
+                   help="how long the supervisor waits for every rank to report ready")
+    s.add_argument("--tensor-parallel-shutdown-timeout", type=float, default=10.0, metavar="SECONDS",
+                   help="grace period between TERM and KILL when the group is taken down")
+    s.add_argument("--backend-option", action="append", default=[], metavar="KEY=VALUE",
+                   help="backend-specific option, repeatable; the value is parsed as JSON when it parses, else kept as text")
+    s.add_argument("--supervised-child", action="store_true", help=argparse.SUPPRESS)   # set by the supervisor on its ranks
     return p
+
+
+def parse_backend_options(items: Sequence[str]) -> dict:
+    """``KEY=VALUE`` pairs -> dict; JSON keeps numbers, booleans and nested values typed, a bare word stays a string
+    (reference: pocketllm/cli.py:84-104)."""
+    out: dict = {}
+    for item in items:
+        key, sep, raw = item.partition("=")
+        if not sep or not key:
+            raise SystemExit(f"--backend-option expects KEY=VALUE, got {item!r}")
+        try:
+            out[key] = json.loads(raw)
+        except ValueError:
+            out[key] = raw
+    return out
 
 
 def _backend_options(ns: argparse.Namespace) -> dict:
@@ -57,6 +82,7 @@ def _backend_options(ns: argparse.Namespace) -> dict:
     if ns.routed_experts_device != "cuda":
         opts["routed_experts_device"] = ns.routed_experts_device
     opts["pd_mode"] = ns.pd_mode
+    opts.update(parse_backend_options(ns.backend_option))
     return opts
 
 
@@ -101,14 +127,18 @@ def main(argv: Sequence[str] | None = None) -> int:
         if ns.command != "serve":
             raise SystemExit(2)
         tp = ns.tensor_parallel_size
-        is_child = os.environ.get(CHILD_ENV) == "1" or ns.tensor_parallel_rank is not None
+        is_child = os.environ.get(CHILD_ENV) == "1" or ns.tensor_parallel_rank is not None or ns.supervised_child
+        if tp > 1 and not is_child and not ns.tensor_parallel_supervisor:
+            raise SystemExit("pocketllm serve: --no-tensor-parallel-supervisor needs --tensor-parallel-rank (one process per rank)")
         if tp > 1 and not is_child:
             from .supervisor import TensorParallelConfig, TensorParallelSupervisor
             _args(ns, 0)  # validate before spawning anything
             cmd = [sys.executable, "-m", "pocketllm", *argv]
             cfg = TensorParallelConfig(world_size=tp, command=cmd, master_addr=ns.tensor_parallel_master_addr,
                                        master_port=ns.tensor_parallel_master_port,
-                                       rendezvous_dir=ns.tensor_parallel_rendezvous_dir, extra_env={CHILD_ENV: "1"})
+                                       rendezvous_dir=ns.tensor_parallel_rendezvous_dir, extra_env={CHILD_ENV: "1"},
+                                       ready_timeout=ns.tensor_parallel_startup_timeout,
+                                       shutdown_grace=ns.tensor_parallel_shutdown_timeout)
             return TensorParallelSupervisor(cfg).run()
         rank = ns.tensor_parallel_rank if ns.tensor_parallel_rank is not None else int(os.environ.get("TP_RANK", os.environ.get("RANK", "0")))
         return _serve_rank(ns, rank)

@@ -19,3 +19,22 @@ def test_model_is_required():
     ns = build_parser().parse_args(["serve"])
     with pytest.raises(SystemExit):
         _args(ns, 0)
+
+
+def test_backend_options_and_supervisor_flags():
+    from pocketllm import cli
+    ns = cli.build_parser().parse_args(["serve", "/m", "-tp", "2", "--backend-option", "window=512", "--backend-option",
+                                        'mix={"attn": "Q8_0"}', "--backend-option", "name=plain text",
+                                        "--tensor-parallel-startup-timeout", "90", "--tensor-parallel-shutdown-timeout", "3",
+                                        "--no-tensor-parallel-supervisor"])
+    a = cli._args(ns, 0)
+    assert a.backend_options["window"] == 512 and a.backend_options["mix"] == {"attn": "Q8_0"}
+    assert a.backend_options["name"] == "plain text" and a.backend_options["pd_mode"] == "serial"
+    assert ns.tensor_parallel_startup_timeout == 90.0 and ns.tensor_parallel_shutdown_timeout == 3.0
+    assert ns.tensor_parallel_supervisor is False and ns.supervised_child is False
+    import pytest
+    with pytest.raises(SystemExit):
+        cli.parse_backend_options(["novalue"])
+    # several ranks without the supervisor and without a rank: refused before anything is loaded
+    with pytest.raises(SystemExit, match="needs --tensor-parallel-rank"):
+        cli.main(["serve", "/m", "-tp", "2", "--no-tensor-parallel-supervisor"])
