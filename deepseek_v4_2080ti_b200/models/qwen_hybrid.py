@@ -943,6 +943,7 @@ class QwenHybridRuntime:
             out = entry["out"]
         for st in sts:
             st.length += 1
+        self.last_logits = buf["logits"]               # [B, vocab shard] fp32 of this step (log-probabilities, sampling)
         if sampling is not None:
             out = self._next_tokens(buf["logits"], sampling, u, counts)
         return out

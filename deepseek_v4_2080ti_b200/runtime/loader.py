@@ -48,6 +48,18 @@ class Channel:
         return tuple(w)
 
 
+
+def logprobs_of_row(logits_row: torch.Tensor, token: int, top_n: int) -> dict:
+    """fp32 logits [vocab] of one step -> {"logprob": of ``token``, "top": [(id, logprob)] best ``top_n``} under the
+    soft-max of the raw logits (before temperature and penalties, as the OpenAI API defines them)."""
+    lp = torch.log_softmax(logits_row.float(), -1)
+    out = {"logprob": float(lp[int(token)].item()), "top": []}
+    if top_n > 0:
+        v, i = lp.topk(min(int(top_n), lp.numel()))
+        out["top"] = [(int(a), float(b)) for a, b in zip(i.tolist(), v.tolist())]
+    return out
+
+
 class RuntimeAdapter:
     """The surface ``NativeBackend`` drives, over a ``QwenHybridRuntime``."""
     supports_sampling = True
@@ -56,6 +68,9 @@ class RuntimeAdapter:
 
     def __init__(self, rt: qh.QwenHybridRuntime, max_context: int, eos_token_ids=()):
         self.rt, self.max_context, self.eos_token_ids = rt, max_context, tuple(eos_token_ids)
+        # log-probabilities need the whole vocabulary in one place: single-rank runs (a rank of a tensor-parallel group
+        # holds a vocabulary shard of the head)
+        self.supports_logprobs = getattr(getattr(rt, "comm", None), "world", 1) == 1
         self.last_cached_tokens = 0
         self._rng: dict[int, torch.Generator] = {}      # per slot: the request's seeded generator
         self._counts: dict[int, torch.Tensor] = {}      # per slot: occurrences of each local vocabulary id
@@ -100,6 +115,10 @@ class RuntimeAdapter:
         self.rt.free(slot)
         self._rng.pop(slot, None)
         self._counts.pop(slot, None)
+
+    def token_logprobs(self, slot: int, token: int, top_n: int) -> dict:
+        """Of the token just produced for ``slot`` (after ``prefill_tokens`` or a single-slot ``decode_tokens``)."""
+        return logprobs_of_row(self.rt.last_logits[-1], token, top_n)
 
     def _check_collectives(self) -> None:
         """Multi-rank only: the step's tokens are on the host, so the kernels have finished - read the error word.
@@ -312,6 +331,7 @@ class GgufRuntimeAdapter:
         # runtimes that leave the step's full-vocabulary logits in ``last_logits`` ([rows, vocab] fp32, one row per
         # sequence of the step) can be sampled from: temperature / top-k / top-p / min-p / penalties on the device
         self.supports_sampling = bool(getattr(rt, "exposes_logits", False))
+        self.supports_logprobs = self.supports_sampling
         self._rng: dict[int, torch.Generator] = {}
         self._counts: dict[int, torch.Tensor] = {}
         self._seed_counter = 0
@@ -328,6 +348,10 @@ class GgufRuntimeAdapter:
         self._rng.pop(slot, None)
         self._counts.pop(slot, None)
         self.rt.free(slot)
+
+    def token_logprobs(self, slot: int, token: int, top_n: int) -> dict:
+        """Of the token just produced for ``slot`` (after ``prefill_tokens`` or a single-slot ``decode_tokens``)."""
+        return logprobs_of_row(self.rt.last_logits[-1], token, top_n)
 
     # ---- sampling from the step's logits
     def _sampling(self, slot: int, sp: Any, prompt: list[int] | None):

@@ -123,8 +123,8 @@ class NativeBackend(BackendBase):
 
     def _check_features(self, req: GenerationRequest) -> None:
         sp = req.sampling_params
-        if sp.logprobs or sp.top_logprobs:
-            raise UnsupportedFeatureError("logprobs are not implemented")
+        if (sp.logprobs or sp.top_logprobs) and not getattr(self.runtime, "supports_logprobs", False):
+            raise UnsupportedFeatureError("this runtime does not report log-probabilities")
         if sp.response_format and sp.response_format.get("type") not in (None, "text"):
             raise UnsupportedFeatureError("structured outputs are not implemented")
         if not sp.greedy and not getattr(self.runtime, "supports_sampling", False):
@@ -165,6 +165,9 @@ class NativeBackend(BackendBase):
                     ch.send(OP_SAMPLING, slot, *_encode_sampling(sp))
                 out: list[int] = []
                 recovered = False
+                want_lp = bool(sp.logprobs or sp.top_logprobs)
+                top_n = int(sp.top_logprobs or 0)
+                lps: list[dict] = []
 
                 def step(fn):
                     """Run one prefill / decode; if a peer-memory collective timed out, re-synchronise the ranks on
@@ -194,6 +197,8 @@ class NativeBackend(BackendBase):
                     return rt.prefill_tokens(slot, prompt, chunk, sp)
 
                 tok = step(first)
+                if want_lp:
+                    lps.append(rt.token_logprobs(slot, tok, top_n))
                 t1 = time.perf_counter()
                 text_done = ""
                 finish = "length"
@@ -220,6 +225,8 @@ class NativeBackend(BackendBase):
                         return rt.decode_tokens([slot], [tok], sp)[0]
 
                     tok = step(nxt)
+                    if want_lp:
+                        lps.append(rt.token_logprobs(slot, tok, top_n))
                 t2 = time.perf_counter()
             finally:
                 ch.send(OP_FREE, slot)
@@ -235,7 +242,13 @@ class NativeBackend(BackendBase):
         self._stats["requests"] += 1
         self._stats["prompt_tokens"] += usage.prompt_tokens
         self._stats["completion_tokens"] += usage.completion_tokens
-        return GenerationResult(req.request_id, out, text, finish, usage, timings,
+        logprobs = None
+        if want_lp:
+            # one entry per kept token (an end-of-sequence token that was cut has none)
+            logprobs = [dict(e, token_id=t, token=self.tokenizer.decode([t])) for t, e in zip(out, lps)]
+            for e in logprobs:
+                e["top_logprobs"] = [{"token_id": i, "token": self.tokenizer.decode([i]), "logprob": v} for i, v in e.pop("top", [])]
+        return GenerationResult(req.request_id, out, text, finish, usage, timings, logprobs=logprobs,
                                 metadata={"throughput": timings.throughput(usage)})
 
     def generate(self, requests: Iterable[GenerationRequest]) -> list[GenerationResult]:

@@ -64,6 +64,32 @@ class ServerState:
         m.set("requests_in_flight", 0)
 
 
+def _bytes(text: str) -> list[int]:
+    return list(text.encode("utf-8"))
+
+
+def _chat_logprobs(res: GenerationResult) -> dict[str, Any] | None:
+    """OpenAI chat form: one entry per generated token with its alternatives."""
+    if not res.logprobs:
+        return None
+    return {"content": [{"token": e["token"], "logprob": e["logprob"], "bytes": _bytes(e["token"]),
+                         "top_logprobs": [{"token": a["token"], "logprob": a["logprob"], "bytes": _bytes(a["token"])}
+                                          for a in e.get("top_logprobs", [])]} for e in res.logprobs]}
+
+
+def _completion_logprobs(res: GenerationResult) -> dict[str, Any] | None:
+    """Legacy completions form: parallel lists."""
+    if not res.logprobs:
+        return None
+    offsets, pos = [], 0
+    for e in res.logprobs:
+        offsets.append(pos)
+        pos += len(e["token"])
+    return {"tokens": [e["token"] for e in res.logprobs], "token_logprobs": [e["logprob"] for e in res.logprobs],
+            "top_logprobs": [{a["token"]: a["logprob"] for a in e.get("top_logprobs", [])} for e in res.logprobs],
+            "text_offset": offsets}
+
+
 def _chat_payload(state: ServerState, res: GenerationResult, created: int, had_tools: bool) -> dict[str, Any]:
     reasoning, answer = split_reasoning(res.text)
     calls: list[dict[str, Any]] = []
@@ -76,14 +102,16 @@ def _chat_payload(state: ServerState, res: GenerationResult, created: int, had_t
         msg["tool_calls"] = calls
     return {"id": f"chatcmpl-{res.request_id}", "object": "chat.completion", "created": created,
             "model": state.model_name,
-            "choices": [{"index": 0, "message": msg, "finish_reason": "tool_calls" if calls else res.finish_reason}],
+            "choices": [{"index": 0, "message": msg, "finish_reason": "tool_calls" if calls else res.finish_reason,
+                         "logprobs": _chat_logprobs(res)}],
             "usage": res.usage.as_dict(),
             "timings": {**res.timings.as_dict(), **res.timings.throughput(res.usage)}}
 
 
 def _completion_payload(state: ServerState, res: GenerationResult, created: int) -> dict[str, Any]:
     return {"id": f"cmpl-{res.request_id}", "object": "text_completion", "created": created, "model": state.model_name,
-            "choices": [{"index": 0, "text": res.text, "finish_reason": res.finish_reason, "logprobs": None}],
+            "choices": [{"index": 0, "text": res.text, "finish_reason": res.finish_reason,
+                         "logprobs": _completion_logprobs(res)}],
             "usage": res.usage.as_dict(),
             "timings": {**res.timings.as_dict(), **res.timings.throughput(res.usage)}}
 
