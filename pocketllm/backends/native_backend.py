@@ -104,7 +104,7 @@ class NativeBackend(BackendBase):
             model_formats=("safetensors", "gguf", "synthetic"), devices=("cuda:sm_100a",),
             supports_batch=True, supports_streaming=True, supports_cancellation=True,
             supports_prefix_caching=bool(getattr(rt, "supports_prefix_cache", False)),
-            supports_logprobs=False, supports_structured_outputs=False,
+            supports_logprobs=bool(getattr(rt, "supports_logprobs", False)), supports_structured_outputs=False,
             supports_speculative_decoding=tuple(getattr(rt, "speculative_methods", ())),
             details={"tensor_parallel_size": self.args.tensor_parallel_size})
 
