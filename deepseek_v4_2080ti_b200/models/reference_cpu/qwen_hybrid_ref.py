@@ -23,6 +23,7 @@ def _r(x):  # storage rounding
 class QwenHybridRef:
     def __init__(self, cfg, state):
         self.cfg = cfg
+        self.capture_layers: tuple[int, ...] = ()          # layers whose output hidden state ``forward`` keeps (drafter taps)
         raw = dict(state)
         self.p = {}
         for k, v in raw.items():
@@ -50,6 +51,7 @@ class QwenHybridRef:
         h = p["model.language_model.embed_tokens.weight"][ids.long()]
         pos = torch.arange(t, device=ids.device)
         inv = (1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.rotary_dim, 2, dtype=torch.float64) / cfg.rotary_dim))).float().to(ids.device)
+        taps = {}
         for i, lt in enumerate(cfg.layer_types):
             pre = f"model.language_model.layers.{i}."
             x = _r(rmsnorm_ref(h, p[pre + "input_layernorm.weight"], eps, True))
@@ -86,6 +88,10 @@ class QwenHybridRef:
             g_, u_ = gu.chunk(2, -1)
             act = _r(F.silu(g_) * u_)
             h = _r(h + _r(self.lin(act, pre + "mlp.down_proj")))
+            if i in self.capture_layers:
+                taps[i] = h
+        if self.capture_layers:                                # [T, len(capture_layers) * H], in the order asked for
+            self.last_taps = torch.cat([taps[i] for i in self.capture_layers], -1)
         x = _r(rmsnorm_ref(h, p["model.language_model.norm.weight"], eps, True))
         self.last_hidden = x                                   # final-normed trunk output [T, H]: what the MTP head consumes
         return x @ p["lm_head.weight"].t()
