@@ -114,7 +114,8 @@ def sharded_topk(logit_shards: list[torch.Tensor], k: int) -> tuple[torch.Tensor
     ids, vals, off = [], [], 0
     for sh in logit_shards:
         kk = min(k, sh.shape[1])
-        v, i = sh.float().topk(kk, -1)
+        i = torch.argsort(sh.float(), dim=-1, descending=True, stable=True)[:, :kk]       # ties at the cut: lower id stays
+        v = sh.float().gather(-1, i)
         ids.append(i + off)
         vals.append(v)
         off += sh.shape[1]

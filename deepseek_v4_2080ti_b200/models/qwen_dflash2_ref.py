@@ -36,6 +36,7 @@ from pathlib import Path
 import torch
 import torch.nn.functional as F
 
+from ..components import draft_selector as sel
 from .qwen_dspark_ref import _norm
 
 
@@ -167,16 +168,7 @@ def load_dflash2(directory: str | Path) -> tuple[QwenDFlash2Config, dict[str, to
 
 def dynamic_conv(x: torch.Tensor, dyn: torch.Tensor, base: torch.Tensor, group_size: int) -> torch.Tensor:
     """x [rows, H]; dyn [rows, K * groups] (tap-major); base [K, H].  Causal over rows, zero history."""
-    rows, h = x.shape
-    k = base.shape[0]
-    groups = h // group_size
-    out = torch.zeros_like(x)
-    for tap in range(k):
-        shifted = torch.zeros_like(x)
-        shifted[tap:] = x[:rows - tap] if tap else x
-        coeff = base[tap][None, :] + dyn[:, tap * groups:(tap + 1) * groups].repeat_interleave(group_size, 1)
-        out += shifted * coeff
-    return out
+    return sel.grouped_dynamic_conv(x, dyn, base, group_size)
 
 
 def _rope_plain(x: torch.Tensor, start: int, theta: float) -> torch.Tensor:
@@ -190,43 +182,15 @@ def _rope_plain(x: torch.Tensor, start: int, theta: float) -> torch.Tensor:
 
 def top_candidates(logits: torch.Tensor, k: int) -> tuple[torch.Tensor, torch.Tensor]:
     """Per row the ``k`` largest logits, best first; among equal logits the lower token id wins."""
-    order = torch.argsort(logits, dim=-1, descending=True, stable=True)[:, :k]     # stable: earlier index first on ties
-    return order, logits.gather(-1, order)
+    return sel.sharded_topk([logits], k)
 
 
 def select_path(proj: torch.Tensor, cand: torch.Tensor, unary: torch.Tensor, pred: torch.Tensor, succ: torch.Tensor,
                 anchor: int, viterbi: bool = False) -> list[int]:
-    """proj [rows, rank]; cand / unary [rows, k]; pred / succ [vocab, rank].  Returns one token per row."""
-    rows, k = cand.shape
-
-    def edges(prev_tokens: torch.Tensor, row: int) -> torch.Tensor:        # [len(prev), k]
-        return unary[row][None, :] + torch.einsum("pr,r,kr->pk", pred[prev_tokens], proj[row], succ[cand[row]])
-
-    def best(scores: torch.Tensor, tokens: torch.Tensor) -> int:           # arg-max, lower token id on ties
-        top = scores.max()
-        tied = (scores == top).nonzero().flatten()
-        return int(tied[tokens[tied].argmin()])
-
-    if not viterbi:
-        out, prev = [], anchor
-        for r in range(rows):
-            prev = int(cand[r, best(edges(torch.tensor([prev]), r)[0], cand[r])])
-            out.append(prev)
-        return out
-    dp = edges(torch.tensor([anchor]), 0)[0]
-    back = []
-    for r in range(1, rows):
-        total = dp[:, None] + edges(cand[r - 1], r)                        # [from, to]
-        frm = [best(total[:, j], cand[r - 1]) for j in range(k)]
-        back.append(frm)
-        dp = torch.stack([total[f, j] for j, f in enumerate(frm)])
-    j = best(dp, cand[rows - 1])
-    out = [0] * rows
-    for r in range(rows - 1, -1, -1):
-        out[r] = int(cand[r, j])
-        if r:
-            j = back[r - 1][j]
-    return out
+    """proj [rows, rank]; cand / unary [rows, k]; pred / succ [vocab, rank].  One token per row: the greedy chain (each
+    row conditioned on the previous pick, the anchor first) or the best whole path."""
+    fn = sel.viterbi_path if viterbi else sel.greedy_path
+    return fn(proj, cand, unary, pred, succ, anchor)[0]
 
 
 @dataclass
