@@ -143,11 +143,14 @@ class _Layer:
         self.cfg, self.w, self.p, self.ratio, self.hashed = cfg, w, p, ratio, hashed
         theta, factor, orig = (cfg.compress_rope_theta, cfg.rope_factor, cfg.original_seq_len) if ratio else (cfg.rope_theta, 1.0, 0)
         self.table = V.rotary_table(cfg.rope_head_dim, cfg.max_seq_len, theta, factor, orig)
+        # hooks of the long-context runtime (models/v4_flashmemory.py), ratio-4 layers only
+        self.global_pick: torch.Tensor | None = None     # compressed entries chosen for this decode step by a shared retriever
+        self.store = None                                # home of the compressed rows outside this layer (host pool + working set)
         self.reset()
 
     def reset(self) -> None:
         cfg, w, a, r = self.cfg, self.w, self.p + "attn.", self.ratio
-        self.kv = torch.zeros(cfg.window + (cfg.max_seq_len // r if r else 0), cfg.head_dim)
+        self.kv = torch.zeros(cfg.window + (cfg.max_seq_len // r if r and self.store is None else 0), cfg.head_dim)
         self.comp = self.icomp = None
         if r:
             c = a + "compressor."
@@ -191,9 +194,15 @@ class _Layer:
         kv = _rms(x @ w[a + "wkv"].t(), w[a + "kv_norm"], cfg.norm_eps)[None]
         kv = torch.cat([kv[..., :-rd], V.apply_rotary(kv[..., -rd:].contiguous(), tab)], -1)[0]
         idx = V.window_indices(win, s, start)
+        comp_idx = None
         if r:
             offset = s if start == 0 else win
-            idx = torch.cat([idx, self._index(x, qr, start, offset) if r == 4 else V.compressed_indices(r, s, start, offset)], -1)
+            comp_idx = self._index(x, qr, start, offset) if r == 4 else V.compressed_indices(r, s, start, offset)
+            if r == 4 and self.global_pick is not None and start > 0:
+                g = self.global_pick.long().reshape(1, -1)
+                if int(g.max()) >= end // r:
+                    raise RuntimeError("the shared selection names a compressed entry this layer does not have yet")
+                comp_idx = torch.where(g < 0, g, g + offset)
         if start == 0:
             if s <= win:
                 self.kv[:s] = kv
@@ -202,13 +211,27 @@ class _Layer:
                 self.kv[cut:win], self.kv[:cut] = kv[-win:].split([win - cut, cut])
             rows = kv
             if r and (new := self.comp.forward(x[None], 0)) is not None:
-                self.kv[win:win + new.shape[1]] = new[0]
+                if self.store is None:
+                    self.kv[win:win + new.shape[1]] = new[0]
+                else:
+                    for j in range(new.shape[1]):
+                        self.store.append(j, new[0, j])
                 rows = torch.cat([kv, new[0]])
         else:
             self.kv[start % win] = kv[0]
-            if r and (new := self.comp.forward(x[None], start)) is not None:
-                self.kv[win + start // r] = new[0, 0]
-            rows = self.kv
+            new = self.comp.forward(x[None], start) if r else None
+            if self.store is None:
+                if new is not None:
+                    self.kv[win + start // r] = new[0, 0]
+                rows = self.kv
+            else:
+                if new is not None:
+                    self.store.append(start // r, new[0, 0])
+                entries = torch.where(comp_idx < 0, comp_idx, comp_idx - offset)[0]
+                rows = torch.cat([self.kv[:win], self.store.gather(entries)])
+                comp_idx = torch.where(entries < 0, entries, win + torch.arange(entries.numel()))[None, :]
+        if comp_idx is not None:
+            idx = torch.cat([idx, comp_idx], -1)
         o = sparse_attention_ref(q, rows, w[a + "attn_sink"], idx, cfg.head_dim ** -0.5)
         o = torch.cat([o[..., :-rd], V.apply_rotary(o[None, ..., -rd:].contiguous(), tab, inverse=True)[0]], -1)
         o = torch.einsum("sgd,grd->sgr", o.reshape(s, cfg.o_groups, -1), w[a + "wo_a"].view(cfg.o_groups, cfg.o_lora_rank, -1))
