@@ -21,6 +21,9 @@ kernels, cpp_engine/backends/cuda/kernels/qwen_dflash2_ops.cu:82-277 and 598-848
   block (each row conditioned on the previous pick, the anchor first) or the best whole path (Viterbi).
 * ``refine_passes > 1`` feeds the drafts back in place of the mask tokens and runs the pass again until they stop
   changing.
+* ``debug`` (a callable) receives every intermediate stage under the names the reference's debug view uses
+  (``context.projected`` ... ``layer.N.attention.q_rope`` ... ``selector.path``, cpp_engine/engine/qwen_dflash2.cpp:
+  667-724 and the ``dump_*`` calls), which is what ``cli/check_drafter_fixture.py`` compares with an exported fixture.
 
 Checkpoint names (cpp_engine/engine/qwen_dflash2.cpp:450-482): ``fc.weight``, ``hidden_norm.weight``, ``norm.weight``,
 ``candidate_selector.{predecessor_codebook,successor_codebook,hidden_projection.weight}`` and per layer the eleven
@@ -215,9 +218,12 @@ class QwenDFlash2Ref:
         self.ctx_v = [torch.zeros(max_context, kvd) for _ in range(cfg.num_hidden_layers)]
         self.committed = 0
         self.prepared = 0                      # rows whose keys and values are up to date
+        self.debug = None                      # callable(name, tensor): every named stage of the next passes, as it is made
+        self.context_begin = 0                 # first context row the block attends to (fixtures that start mid-sequence)
 
-    def reset(self) -> None:
-        self.committed = self.prepared = 0
+    def reset(self, begin: int = 0) -> None:
+        """Empty context; ``begin`` > 0 starts it at that position (rows before it do not exist)."""
+        self.committed = self.prepared = self.context_begin = begin
 
     def crop_context(self, position: int) -> None:
         if not 0 <= position <= self.committed:
@@ -234,63 +240,100 @@ class QwenDFlash2Ref:
         self.taps[position_offset:position_offset + rows] = taps.float()
         self.committed += rows
 
+    def _tap(self, name: str, t) -> None:
+        if self.debug is not None:
+            self.debug(name, t if isinstance(t, torch.Tensor) else torch.tensor(t, dtype=torch.int32))
+
     @torch.no_grad()
     def _prepare_context(self) -> None:
         cfg, w, a, b = self.cfg, self.w, self.prepared, self.committed
         if a == b:
             return
-        ctx = _norm(self.taps[a:b] @ w["fc.weight"].t(), w["hidden_norm.weight"], cfg.rms_norm_eps)
+        proj = self.taps[a:b] @ w["fc.weight"].t()
+        ctx = _norm(proj, w["hidden_norm.weight"], cfg.rms_norm_eps)
+        self._tap("context.projected", proj)
+        self._tap("context.normalized", ctx)
         for i in range(cfg.num_hidden_layers):
-            p = f"layers.{i}.self_attn."
-            k = (ctx @ w[p + "k_proj.weight"].t()).view(b - a, cfg.num_key_value_heads, cfg.head_dim)
-            k = _rope_plain(_norm(k, w[p + "k_norm.weight"], cfg.rms_norm_eps), a, cfg.rope_theta)
-            self.ctx_k[i][a:b] = k.reshape(b - a, -1)
-            self.ctx_v[i][a:b] = ctx @ w[p + "v_proj.weight"].t()
+            p, t = f"layers.{i}.self_attn.", f"layer.{i}.context."
+            k = ctx @ w[p + "k_proj.weight"].t()
+            v = ctx @ w[p + "v_proj.weight"].t()
+            kn = _norm(k.view(b - a, cfg.num_key_value_heads, cfg.head_dim), w[p + "k_norm.weight"], cfg.rms_norm_eps)
+            kr = _rope_plain(kn, a, cfg.rope_theta)
+            for name, val in (("k_projection", k), ("v", v), ("k_norm", kn.reshape(b - a, -1)), ("k_rope", kr.reshape(b - a, -1))):
+                self._tap(t + name, val)
+            self.ctx_k[i][a:b] = kr.reshape(b - a, -1)
+            self.ctx_v[i][a:b] = v
         self.prepared = b
 
     @torch.no_grad()
     def denoise(self, tokens: list[int]) -> torch.Tensor:
         """Final-normed hidden rows [block_size, hidden] for the block ``tokens`` (row 0 is the anchor)."""
         self._prepare_context()
-        cfg, w, eps, n = self.cfg, self.w, self.cfg.rms_norm_eps, self.committed
+        cfg, w, eps, n, tap = self.cfg, self.w, self.cfg.rms_norm_eps, self.committed, self._tap
         b, hq, hkv, d = cfg.block_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         kg, gs, win = cfg.conv_kernel_size * cfg.conv_groups, cfg.conv_group_size, cfg.sliding_window
         r = self.embedding[torch.tensor(tokens)]
+        tap("noise.tokens", tokens)
+        tap("noise.embedding", r)
+        tap("residual.initial", r)
+        lo = self.context_begin
         qpos = n + torch.arange(b)
-        kpos = torch.cat([torch.arange(n), qpos])
-        mask = (qpos[:, None] - kpos[None, :]).abs() < win                  # [b, n + b]
+        kpos = torch.cat([torch.arange(lo, n), qpos])
+        mask = (qpos[:, None] - kpos[None, :]).abs() < win                  # [b, n - lo + b]
         for i in range(cfg.num_hidden_layers):
-            p = f"layers.{i}."
+            p, t = f"layers.{i}.", f"layer.{i}."
             x = _norm(r, w[p + "input_layernorm.weight"], eps)
             dyn = x @ w[p + "attention_conv.kernel_projection.weight"].t()
             base = w[p + "attention_conv.base_kernel"]
             c = dynamic_conv(x, dyn[:, :kg], base[0], gs)
-            q = _norm((c @ w[p + "self_attn.q_proj.weight"].t()).view(b, hq, d), w[p + "self_attn.q_norm.weight"], eps)
-            k = _norm((c @ w[p + "self_attn.k_proj.weight"].t()).view(b, hkv, d), w[p + "self_attn.k_norm.weight"], eps)
+            tap(t + "input_norm", x); tap(t + "attention.dynamic", dyn); tap(t + "attention.prepare", c)
+            q0, k0 = c @ w[p + "self_attn.q_proj.weight"].t(), c @ w[p + "self_attn.k_proj.weight"].t()
             v = (c @ w[p + "self_attn.v_proj.weight"].t()).view(b, hkv, d)
-            q, k = _rope_plain(q, n, cfg.rope_theta), _rope_plain(k, n, cfg.rope_theta)
-            keys = torch.cat([self.ctx_k[i][:n].view(n, hkv, d), k], 0).repeat_interleave(hq // hkv, 1)
-            vals = torch.cat([self.ctx_v[i][:n].view(n, hkv, d), v], 0).repeat_interleave(hq // hkv, 1)
+            q1 = _norm(q0.view(b, hq, d), w[p + "self_attn.q_norm.weight"], eps)
+            k1 = _norm(k0.view(b, hkv, d), w[p + "self_attn.k_norm.weight"], eps)
+            q, k = _rope_plain(q1, n, cfg.rope_theta), _rope_plain(k1, n, cfg.rope_theta)
+            for name, val in (("q_projection", q0), ("k_projection", k0), ("v", v), ("q_norm", q1), ("k_norm", k1),
+                              ("q_rope", q), ("k_rope", k)):
+                tap(t + "attention." + name, val.reshape(b, -1))
+            keys = torch.cat([self.ctx_k[i][lo:n].view(n - lo, hkv, d), k], 0).repeat_interleave(hq // hkv, 1)
+            vals = torch.cat([self.ctx_v[i][lo:n].view(n - lo, hkv, d), v], 0).repeat_interleave(hq // hkv, 1)
             s = torch.einsum("qhd,khd->hqk", q, keys) / math.sqrt(d)
             s = s.masked_fill(~mask[None], float("-inf"))
             o = torch.einsum("hqk,khd->qhd", s.softmax(-1), vals).reshape(b, hq * d)
-            r = r + dynamic_conv(o @ w[p + "self_attn.o_proj.weight"].t(), dyn[:, kg:], base[1], gs)
+            op = o @ w[p + "self_attn.o_proj.weight"].t()
+            fin = dynamic_conv(op, dyn[:, kg:], base[1], gs)
+            r = r + fin
+            tap(t + "attention.output", o); tap(t + "attention.o_projection", op); tap(t + "attention.finish", fin)
+            tap(t + "attention.residual", r)
             x = _norm(r, w[p + "post_attention_layernorm.weight"], eps)
             dyn = x @ w[p + "mlp_conv.kernel_projection.weight"].t()
             base = w[p + "mlp_conv.base_kernel"]
             c = dynamic_conv(x, dyn[:, :kg], base[0], gs)
-            act = F.silu(c @ w[p + "mlp.gate_proj.weight"].t()) * (c @ w[p + "mlp.up_proj.weight"].t())
-            r = r + dynamic_conv(act @ w[p + "mlp.down_proj.weight"].t(), dyn[:, kg:], base[1], gs)
-        return _norm(r, w["norm.weight"], eps)
+            gate, up = c @ w[p + "mlp.gate_proj.weight"].t(), c @ w[p + "mlp.up_proj.weight"].t()
+            act = F.silu(gate) * up
+            down = act @ w[p + "mlp.down_proj.weight"].t()
+            fin = dynamic_conv(down, dyn[:, kg:], base[1], gs)
+            r = r + fin
+            for name, val in (("post_norm", x), ("mlp.dynamic", dyn), ("mlp.prepare", c), ("mlp.gate", gate), ("mlp.up", up),
+                              ("mlp.swiglu", act), ("mlp.down", down), ("mlp.finish", fin), ("residual", r)):
+                tap(t + name, val)
+        out = _norm(r, w["norm.weight"], eps)
+        tap("final.residual", r); tap("final.norm", out)
+        return out
 
     @torch.no_grad()
     def _pass(self, anchor: int, tokens: list[int]) -> tuple[list[int], torch.Tensor, torch.Tensor]:
         cfg, w = self.cfg, self.w
         x = self.denoise(tokens)[1:]
-        cand, unary = top_candidates(x @ self.head.t(), cfg.selector_top_k)
+        logits = x @ self.head.t()
+        cand, unary = top_candidates(logits, cfg.selector_top_k)
         proj = x @ w["candidate_selector.hidden_projection.weight"].t()
         path = select_path(proj, cand, unary, w["candidate_selector.predecessor_codebook"],
                            w["candidate_selector.successor_codebook"], anchor, self.viterbi)
+        self._tap("logits.local", logits)
+        for scope in ("local", "global"):                       # one rank: the merged list is the local one
+            self._tap(f"topk.{scope}.tokens", cand.to(torch.int32)); self._tap(f"topk.{scope}.logits", unary)
+        self._tap("selector.path", path)
         return path, cand, unary
 
     @torch.no_grad()
