@@ -125,8 +125,10 @@ class NativeBackend(BackendBase):
         sp = req.sampling_params
         if (sp.logprobs or sp.top_logprobs) and not getattr(self.runtime, "supports_logprobs", False):
             raise UnsupportedFeatureError("this runtime does not report log-probabilities")
-        if sp.response_format and sp.response_format.get("type") not in (None, "text"):
-            raise UnsupportedFeatureError("structured outputs are not implemented")
+        if sp.response_format and sp.response_format.get("type") not in (None, "text") \
+                and not req.metadata.get("response_format_in_prompt"):
+            # chat requests carry the schema as an instruction in the prompt; a raw completion has nowhere to put it
+            raise UnsupportedFeatureError("response_format needs a chat request: the schema is given to the model as an instruction")
         if not sp.greedy and not getattr(self.runtime, "supports_sampling", False):
             raise UnsupportedFeatureError("this runtime only supports greedy decoding (temperature 0)")
         limit = self.args.max_model_len or getattr(self.runtime, "max_context", None)

@@ -164,11 +164,41 @@ def fallback_prompt(messages: Sequence[Mapping[str, Any]], add_generation_prompt
     return "\n".join(lines)
 
 
+def response_format_schema(response_format: Any) -> Any:
+    """What a ``response_format`` asks the reply to follow: None for plain text, ``{"type": "object"}`` for
+    ``json_object``, the schema itself for ``json_schema`` (``{"json_schema": {"schema": ...}}`` or the bare schema)."""
+    if response_format is None:
+        return None
+    if not isinstance(response_format, Mapping):
+        raise ConfigurationError("response_format must be an object")
+    kind = response_format.get("type")
+    if kind in (None, "text"):
+        return None
+    if kind == "json_object":
+        return {"type": "object"}
+    if kind == "json_schema":
+        inner = response_format.get("json_schema")
+        if not isinstance(inner, Mapping):
+            raise ConfigurationError("response_format.json_schema must be an object")
+        return inner.get("schema", inner)
+    raise ConfigurationError(f"unknown response_format type {kind!r}")
+
+
+def response_format_instruction(schema: Any) -> str:
+    """The instruction a chat family without its own response-format block carries in the system message."""
+    import json
+    if schema == {"type": "object"}:
+        return "Reply with one valid JSON object and nothing else."
+    return ("Reply with one JSON value that strictly follows this JSON schema, and nothing else:\n"
+            + json.dumps(schema, ensure_ascii=False))
+
+
 @dataclass
 class ChatRequest:
     messages: list[dict[str, Any]]
     tools: list[dict[str, Any]] = field(default_factory=list)
     tool_instruction: str = ""
+    response_schema: Any = None
     thinking: bool = False
     reasoning_effort: str | None = None
     stream: bool = False
@@ -202,14 +232,22 @@ class ChatRequest:
         thinking, effort = thinking_options(body)
         return cls(messages=msgs, tools=tools, tool_instruction=tool_choice_instruction(body.get("tool_choice"), tools),
                    thinking=thinking, reasoning_effort=effort, stream=bool(body.get("stream", False)),
-                   model=body.get("model"))
+                   model=body.get("model"), response_schema=response_format_schema(body.get("response_format")))
 
-    def messages_with_instruction(self) -> list[dict[str, Any]]:
-        if not self.tool_instruction:
+    def messages_with_instruction(self, native_response_format: bool = False) -> list[dict[str, Any]]:
+        """The messages with the tool-choice instruction and the response format folded into the system message (one is
+        added when the conversation has none).  ``native_response_format``: the chat family renders a
+        ``response_format`` key of the system message itself (DeepSeek-V4); otherwise the schema travels as text."""
+        extra = self.tool_instruction
+        if self.response_schema is not None and not native_response_format:
+            extra = (extra + "\n\n" + response_format_instruction(self.response_schema)).strip()
+        if not extra and self.response_schema is None:
             return self.messages
         msgs = [dict(m) for m in self.messages]
-        if msgs and msgs[0]["role"] == "system":
-            msgs[0]["content"] = (msgs[0]["content"] + "\n\n" + self.tool_instruction).strip()
-        else:
-            msgs.insert(0, {"role": "system", "content": self.tool_instruction})
+        if not (msgs and msgs[0]["role"] == "system"):
+            msgs.insert(0, {"role": "system", "content": ""})
+        if extra:
+            msgs[0]["content"] = (msgs[0]["content"] + "\n\n" + extra).strip()
+        if self.response_schema is not None and native_response_format:
+            msgs[0]["response_format"] = self.response_schema
         return msgs

@@ -75,7 +75,7 @@ def _encode_with_template(tok: TokenizerHandle, chat: ChatRequest) -> list[int]:
 
 def _encode_with_family(tok: TokenizerHandle, chat: ChatRequest, family: str) -> list[int]:
     from deepseek_v4_2080ti_b200 import encoding
-    text = encoding.render_chat(family, chat.messages_with_instruction(), tools=chat.tools, thinking=chat.thinking,
+    text = encoding.render_chat(family, chat.messages_with_instruction(family == "deepseek_v4"), tools=chat.tools, thinking=chat.thinking,
                                 reasoning_effort=chat.reasoning_effort,
                                 add_generation_prompt=chat.add_generation_prompt)
     return tok.encode(text)

@@ -21,7 +21,8 @@ def build_chat_request(body: Mapping[str, Any], tokenizer: TokenizerHandle, fami
         kw["request_id"] = request_id
     req = GenerationRequest(prompt_tokens=ids, sampling_params=SamplingParams.from_openai(body),
                             metadata={"kind": "chat", "tools": bool(chat.tools), "thinking": chat.thinking,
-                                      "stream": chat.stream, "model": chat.model}, **kw)
+                                      "stream": chat.stream, "model": chat.model,
+                                      "response_format_in_prompt": chat.response_schema is not None}, **kw)
     return req, chat
 
 

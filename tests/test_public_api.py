@@ -286,3 +286,39 @@ def test_gguf_runtime_adapter_batches_up_to_the_runtime_slots(single):
     assert ad.decode_tokens([s], [6], None) == [7]
     ad.free(s)
     assert _is_gguf("model.gguf") and not _is_gguf("/nonexistent/dir")
+
+
+def test_response_format_travels_as_an_instruction_in_chat_prompts_only():
+    from pocketllm.protocol.chat import ChatRequest, response_format_schema
+    from deepseek_v4_2080ti_b200 import encoding
+    schema = {"type": "object", "properties": {"x": {"type": "number"}}, "required": ["x"]}
+    assert response_format_schema(None) is None and response_format_schema({"type": "text"}) is None
+    assert response_format_schema({"type": "json_object"}) == {"type": "object"}
+    assert response_format_schema({"type": "json_schema", "json_schema": {"name": "p", "schema": schema}}) == schema
+    with pytest.raises(ConfigurationError):
+        response_format_schema({"type": "yaml"})
+    body = {"messages": [{"role": "user", "content": "a point"}],
+            "response_format": {"type": "json_schema", "json_schema": {"name": "p", "schema": schema}}}
+    chat = ChatRequest.from_body(body)
+    native = encoding.render_chat("deepseek_v4", chat.messages_with_instruction(True))
+    assert "## Response Format:" in native and '"required": ["x"]' in native and native.index("Response Format") < native.index("a point")
+    other = encoding.render_chat("glm_dsa", chat.messages_with_instruction(False))
+    assert "strictly follows this JSON schema" in other and '"required": ["x"]' in other
+    # an existing system message keeps its text; the tool instruction and the schema share it
+    body["messages"].insert(0, {"role": "system", "content": "Be brief."})
+    body["response_format"] = {"type": "json_object"}
+    msgs = ChatRequest.from_body(body).messages_with_instruction(False)
+    assert msgs[0]["content"].startswith("Be brief.") and "valid JSON object" in msgs[0]["content"] and len(msgs) == 2
+    assert ChatRequest.from_body({"messages": body["messages"]}).messages_with_instruction() == ChatRequest.from_body({"messages": body["messages"]}).messages
+    # through the builders: a chat request is accepted, a raw completion with a schema is refused
+    tok = TokenizerHandle.load(None)
+    req, _ = build_chat_request(body, tok)
+    assert req.metadata["response_format_in_prompt"] and b"valid JSON object" in bytes(req.prompt_tokens)
+    rt = FakeRuntime()
+    rt.max_context = 512
+    backend = NativeBackend(EngineArgs(model="fake"), runtime=rt)
+    req.sampling_params.max_tokens = 2
+    assert len(backend.generate([req])[0].token_ids) == 2
+    raw = build_completion_request({"prompt": "A", "response_format": {"type": "json_object"}, "max_tokens": 2}, tok)
+    with pytest.raises(UnsupportedFeatureError, match="chat request"):
+        backend.generate([raw])
