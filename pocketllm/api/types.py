@@ -127,6 +127,9 @@ class EngineArgs:
         return cls(**values)
 
 
+MAX_CHOICES = 16
+
+
 @dataclass
 class SamplingParams:
     max_tokens: int = 256
@@ -159,8 +162,8 @@ class SamplingParams:
             raise ConfigurationError("min_p must lie in [0, 1]")
         if self.repetition_penalty <= 0:
             raise ConfigurationError("repetition_penalty must be > 0")
-        if self.n != 1:
-            raise ConfigurationError("only n=1 is supported")
+        if not 1 <= self.n <= MAX_CHOICES:
+            raise ConfigurationError(f"n must lie in [1, {MAX_CHOICES}]")
         if self.top_logprobs is not None and not 0 <= self.top_logprobs <= 20:
             raise ConfigurationError("top_logprobs must lie in [0, 20]")
 
@@ -277,6 +280,7 @@ class GenerationResult:
     timings: TimingMetrics = field(default_factory=TimingMetrics)
     logprobs: Any = None
     metadata: dict[str, Any] = field(default_factory=dict)
+    choices: list["GenerationResult"] = field(default_factory=list)      # all n completions when n > 1 (this one is choices[0])
 
 
 @dataclass

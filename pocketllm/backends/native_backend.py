@@ -254,10 +254,20 @@ class NativeBackend(BackendBase):
                                 metadata={"throughput": timings.throughput(usage)})
 
     def generate(self, requests: Iterable[GenerationRequest]) -> list[GenerationResult]:
-        reqs = list(requests)
-        if len(reqs) > 1 and self.args.max_batch_size > 1 and hasattr(self.runtime, "generate_batch"):
-            return self._generate_batched(reqs)
-        return [self._run_one(r) for r in reqs]
+        from ..protocol.requests import expand_choices, merge_choices
+        asked = list(requests)
+        groups = [expand_choices(r) for r in asked]              # n > 1: n single-completion requests each
+        reqs = [r for g in groups for r in g]
+        if len(reqs) > 1 and self.args.max_batch_size > 1 and hasattr(self.runtime, "generate_batch") \
+                and all(r.sampling_params.greedy for r in reqs):
+            flat = self._generate_batched(reqs)
+        else:
+            flat = [self._run_one(r) for r in reqs]
+        out, at = [], 0
+        for r, g in zip(asked, groups):
+            out.append(merge_choices(r, flat[at:at + len(g)]))
+            at += len(g)
+        return out
 
     def _generate_batched(self, reqs: list[GenerationRequest]) -> list[GenerationResult]:
         """Continuous batching through the runtime's scheduler (greedy requests only)."""
@@ -287,6 +297,8 @@ class NativeBackend(BackendBase):
         import queue
         import threading
 
+        if request.sampling_params.n != 1:
+            raise UnsupportedFeatureError("streaming returns one completion: n must be 1")
         q: "queue.Queue[Any]" = queue.Queue()
         stops = request.sampling_params.stop
         sent = {"n": 0}

@@ -90,7 +90,7 @@ def _completion_logprobs(res: GenerationResult) -> dict[str, Any] | None:
             "text_offset": offsets}
 
 
-def _chat_payload(state: ServerState, res: GenerationResult, created: int, had_tools: bool) -> dict[str, Any]:
+def _chat_choice(index: int, res: GenerationResult, had_tools: bool) -> dict[str, Any]:
     reasoning, answer = split_reasoning(res.text)
     calls: list[dict[str, Any]] = []
     if had_tools:
@@ -100,18 +100,23 @@ def _chat_payload(state: ServerState, res: GenerationResult, created: int, had_t
         msg["reasoning_content"] = reasoning
     if calls:
         msg["tool_calls"] = calls
+    return {"index": index, "message": msg, "finish_reason": "tool_calls" if calls else res.finish_reason,
+            "logprobs": _chat_logprobs(res)}
+
+
+def _chat_payload(state: ServerState, res: GenerationResult, created: int, had_tools: bool) -> dict[str, Any]:
+    """``res.choices`` holds the n completions of a request with n > 1; usage counts the prompt once."""
     return {"id": f"chatcmpl-{res.request_id}", "object": "chat.completion", "created": created,
             "model": state.model_name,
-            "choices": [{"index": 0, "message": msg, "finish_reason": "tool_calls" if calls else res.finish_reason,
-                         "logprobs": _chat_logprobs(res)}],
+            "choices": [_chat_choice(i, r, had_tools) for i, r in enumerate(res.choices or [res])],
             "usage": res.usage.as_dict(),
             "timings": {**res.timings.as_dict(), **res.timings.throughput(res.usage)}}
 
 
 def _completion_payload(state: ServerState, res: GenerationResult, created: int) -> dict[str, Any]:
     return {"id": f"cmpl-{res.request_id}", "object": "text_completion", "created": created, "model": state.model_name,
-            "choices": [{"index": 0, "text": res.text, "finish_reason": res.finish_reason,
-                         "logprobs": _completion_logprobs(res)}],
+            "choices": [{"index": i, "text": r.text, "finish_reason": r.finish_reason, "logprobs": _completion_logprobs(r)}
+                        for i, r in enumerate(res.choices or [res])],
             "usage": res.usage.as_dict(),
             "timings": {**res.timings.as_dict(), **res.timings.throughput(res.usage)}}
 

@@ -131,3 +131,19 @@ def test_batched_serving_groups_concurrent_requests(monkeypatch):
         httpd.shutdown()
         httpd.server_close()
         state.batching.close()
+
+
+def test_n_choices_in_one_response_and_not_in_a_stream(server):
+    port, _ = server
+    st, raw = call(port, "POST", "/v1/completions", {"prompt": "A", "max_tokens": 3, "n": 3})
+    body = json.loads(raw)
+    assert st == 200 and [c["index"] for c in body["choices"]] == [0, 1, 2]
+    assert all(c["text"] == "BCD" for c in body["choices"])                  # greedy: the choices coincide
+    assert (body["usage"]["prompt_tokens"], body["usage"]["completion_tokens"], body["usage"]["total_tokens"]) == (1, 9, 10)
+    st, raw = call(port, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "max_tokens": 2, "n": 2})
+    body = json.loads(raw)
+    assert st == 200 and len(body["choices"]) == 2 and body["choices"][1]["message"]["role"] == "assistant"
+    st, raw = call(port, "POST", "/v1/completions", {"prompt": "A", "max_tokens": 3, "n": 2, "stream": True})
+    assert st in (400, 501) and b"n must be 1" in raw
+    st, raw = call(port, "POST", "/v1/completions", {"prompt": "A", "n": 99})
+    assert st == 400

@@ -85,7 +85,7 @@ def test_sampling_params():
     sp = SamplingParams.from_openai({"max_completion_tokens": 7, "temperature": 0, "stop": "END"})
     assert sp.greedy and sp.max_tokens == 7 and sp.stop == ("END",)
     assert not SamplingParams(temperature=0.8).greedy
-    for bad in ({"top_p": 0}, {"temperature": -1}, {"n": 2}, {"max_tokens": 0}, {"top_logprobs": 99}):
+    for bad in ({"top_p": 0}, {"temperature": -1}, {"n": 17}, {"max_tokens": 0}, {"top_logprobs": 99}):
         with pytest.raises(ConfigurationError):
             SamplingParams.from_openai(bad)
     with pytest.raises(ConfigurationError):
@@ -322,3 +322,25 @@ def test_response_format_travels_as_an_instruction_in_chat_prompts_only():
     raw = build_completion_request({"prompt": "A", "response_format": {"type": "json_object"}, "max_tokens": 2}, tok)
     with pytest.raises(UnsupportedFeatureError, match="chat request"):
         backend.generate([raw])
+
+
+def test_n_choices_expand_with_consecutive_seeds_and_merge():
+    from pocketllm.protocol.requests import expand_choices, merge_choices
+    req = GenerationRequest(prompt_tokens=[5], sampling_params=SamplingParams(max_tokens=2, n=3, seed=10, temperature=0.0),
+                            request_id="r")
+    parts = expand_choices(req)
+    assert [p.request_id for p in parts] == ["r-0", "r-1", "r-2"] and [p.sampling_params.seed for p in parts] == [10, 11, 12]
+    assert all(p.sampling_params.n == 1 for p in parts) and req.sampling_params.n == 3
+    assert expand_choices(GenerationRequest(prompt_tokens=[5]))[0].sampling_params.n == 1
+    b, rt = make_backend()
+    (res,) = b.generate([req])
+    assert res.request_id == "r" and len(res.choices) == 3 and res.token_ids == res.choices[0].token_ids == [6, 7]
+    assert res.usage.prompt_tokens == 1 and res.usage.completion_tokens == 6 and res.choices[1].choices == []
+    assert sum(1 for c in rt.calls if c[0] == "prefill") == 3
+    # mixed with an ordinary request: order and grouping are kept
+    a, b2 = b.generate([GenerationRequest(prompt_tokens=[1], sampling_params=SamplingParams(max_tokens=1)), req])
+    assert a.choices == [] and a.token_ids == [2] and len(b2.choices) == 3
+    with pytest.raises(ConfigurationError):
+        SamplingParams(n=0)
+    with pytest.raises(UnsupportedFeatureError):
+        list(b.stream(req))
