@@ -322,6 +322,19 @@ def make_handler(state: ServerState):
     return Handler
 
 
+class _Server(ThreadingHTTPServer):
+    daemon_threads = True
+
+    def handle_error(self, request, client_address):
+        """A client that went away mid-response is not an error worth a traceback; anything else is counted and shown."""
+        import sys
+        exc = sys.exc_info()[1]
+        if isinstance(exc, (ConnectionError, TimeoutError)):
+            self.client_disconnects = getattr(self, "client_disconnects", 0) + 1
+            return
+        super().handle_error(request, client_address)
+
+
 def make_server(backend: Any, host: str = "127.0.0.1", port: int = 8000, served_model_name: str = "pocketllm",
                 metrics: Metrics | None = None, batch_requests: bool | None = None) -> tuple[ThreadingHTTPServer, ServerState]:
     """``batch_requests`` (default: the ``POCKETLLM_SERVING_BATCHING`` environment switch) puts a ``BatchingQueue`` in
@@ -333,8 +346,7 @@ def make_server(backend: Any, host: str = "127.0.0.1", port: int = 8000, served_
         from .batching import BatchingQueue
         batching = BatchingQueue.from_env(lambda reqs, emit: backend.generate(list(reqs)))
     state = ServerState(backend, served_model_name, metrics, batching)
-    httpd = ThreadingHTTPServer((host, port), make_handler(state))
-    httpd.daemon_threads = True
+    httpd = _Server((host, port), make_handler(state))
     return httpd, state
 
 
