@@ -126,13 +126,14 @@ def speculative_generate(target, drafter, prompt: torch.Tensor, max_new_tokens: 
 class WholeSequenceTarget:
     """Adapts an oracle with only ``forward(all_ids) -> logits [T, vocab]`` (no caches) to the target protocol by
     re-running the whole context; the state is just the token list, so snapshot / restore are exact and free.
-    ``hidden`` holds the oracle's ``last_hidden`` of the latest pass when it has one."""
+    ``hidden`` / ``taps`` hold the oracle's ``last_hidden`` / ``last_taps`` of this target's latest pass when it has them
+    (several targets may share one oracle)."""
 
     def __init__(self, oracle):
-        self.oracle, self.ids, self.hidden = oracle, [], None
+        self.oracle, self.ids, self.hidden, self.taps = oracle, [], None, None
 
     def reset(self) -> None:
-        self.ids, self.hidden = [], None
+        self.ids, self.hidden, self.taps = [], None, None
 
     def snapshot(self) -> list[int]:
         return list(self.ids)
@@ -145,6 +146,7 @@ class WholeSequenceTarget:
         self.ids.extend(int(t) for t in ids.reshape(-1))
         logits = self.oracle.forward(torch.tensor(self.ids))
         self.hidden = getattr(self.oracle, "last_hidden", None)
+        self.taps = getattr(self.oracle, "last_taps", None)          # tap-layer hidden states, when the oracle keeps them
         return logits[-n:]
 
 

@@ -362,7 +362,7 @@ class QwenDFlash2Drafter:
         target.oracle.capture_layers = tuple(drafter.cfg.target_layer_ids)
 
     def propose(self, context: list[int], k: int) -> tuple[list[int], list[float]]:
-        taps = getattr(self.t.oracle, "last_taps", None)
+        taps = getattr(self.t, "taps", None)
         n = len(context) - 1
         if k <= 0 or taps is None or taps.shape[0] < n or n + self.d.cfg.block_size > self.d.max_context:
             return [], []

@@ -293,7 +293,7 @@ class QwenDSparkDrafter:
         target.oracle.capture_layers = tuple(drafter.cfg.target_layer_ids)
 
     def propose(self, context: list[int], k: int) -> tuple[list[int], list[float]]:
-        taps = getattr(self.t.oracle, "last_taps", None)
+        taps = getattr(self.t, "taps", None)
         n = len(context) - 1                                    # rows the target has run: everything before the anchor
         if k <= 0 or taps is None or taps.shape[0] < n or n + self.d.cfg.block_size > self.d.max_context:
             return [], []

@@ -452,15 +452,40 @@ def _device(args) -> torch.device:
     return torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
 
 
+def _load_host(args):
+    """The Qwen-style hybrid on the host (``device="cpu"``): fp32 oracle, one rank, every drafter
+    (``runtime/host_runtime.py``)."""
+    from pocketllm.api.errors import ConfigurationError
+    from pocketllm.backends.native_backend import NullChannel
+    from .host_runtime import build_host_adapter
+    if args.tensor_parallel_size != 1:
+        raise ConfigurationError("the host path runs on one rank")
+    model = args.model
+    if model.startswith("synthetic:"):
+        if "tiny" not in model:
+            raise ConfigurationError("the host path generates only the tiny synthetic model")
+        cfg = qh.QwenHybridConfig.tiny()
+        state = qh.synth_state(cfg, 0, "cpu", std=0.05)
+    else:
+        from ..formats import safetensors_io
+        cfg = qh.QwenHybridConfig.from_json(args.config_path or os.path.join(args.checkpoint_dir, "config.json"))
+        state = safetensors_io.read_checkpoint(args.checkpoint_dir)
+    max_ctx = args.max_model_len or 2048
+    return build_host_adapter(args, cfg, state, max_ctx, max(1, args.max_batch_size)), None, NullChannel()
+
+
 def load_runtime(args):
     """Returns (adapter, chat-template family or None, command channel)."""
     world, rank = args.tensor_parallel_size, args.tensor_parallel_rank
     spec_method = getattr(args, "speculative_method", None)
+    if str(args.device or "") == "cpu" and not _is_gguf(args.model):
+        return _load_host(args)
     if spec_method and spec_method not in ("mtp", "ngram"):
-        # refuse rather than decode without it: the learned external drafter networks are not built
+        # refuse rather than decode without it: the learned block drafters run on the host path only (device="cpu")
         from pocketllm.api.errors import ConfigurationError
-        raise ConfigurationError(f"speculative_method={spec_method!r} is not implemented (available: 'mtp' with a "
-                                 "checkpoint that carries the head, 'ngram' prompt lookup)")
+        raise ConfigurationError(f"speculative_method={spec_method!r} is not implemented on the GPU (available there: "
+                                 "'mtp' with a checkpoint that carries the head, 'ngram' prompt lookup; device='cpu' "
+                                 "serves 'dspark' and 'dflash2' from the host statements)")
     if spec_method and (_is_gguf(args.model) or getattr(args, "backend", "auto") == "cpp"):
         from pocketllm.api.errors import ConfigurationError
         raise ConfigurationError("speculative_method is served by the Qwen-style hybrid runtime only")
