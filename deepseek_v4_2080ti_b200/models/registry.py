@@ -252,11 +252,28 @@ class _V4HostAdapter:
 
 
 def _v4_runtime(bundle, device="cpu", rank=0, world=1, comm=None, **kw):
+    """Long-context options, as keywords or through the environment switches the reference's engine reads
+    (docs/FLASHMEMORY_1M_CONTEXT.md there): ``flashmemory`` / ``POCKETLLM_GGUF_FLASHMEMORY_CKPT`` (retriever checkpoint;
+    ensemble ``POCKETLLM_GGUF_FLASHMEMORY_ENSEMBLE`` = max | mean) and ``kv_swap_chunks`` /
+    ``POCKETLLM_GGUF_KV_SWAP=1`` + ``POCKETLLM_GGUF_KV_SWAP_GPU_CHUNKS`` (working-set groups of compressed rows)."""
+    import os
     from . import v4_gguf as vg
     from .v4_block_ref import V4BlockRef
     if world != 1:
         raise ValueError("the deepseek4 block runtime is single-rank (fp32 on the host)")
     cfg, weights = vg.load_bundle(bundle)
+    ckpt = kw.get("flashmemory") or os.environ.get("POCKETLLM_GGUF_FLASHMEMORY_CKPT")
+    chunks = int(kw.get("kv_swap_chunks") or (os.environ.get("POCKETLLM_GGUF_KV_SWAP_GPU_CHUNKS", "512")
+                                              if os.environ.get("POCKETLLM_GGUF_KV_SWAP", "0") == "1" else 0))
+    if ckpt or chunks:
+        from . import v4_flashmemory as lc
+        ensemble = str(kw.get("flashmemory_ensemble") or os.environ.get("POCKETLLM_GGUF_FLASHMEMORY_ENSEMBLE", "max"))
+        if ensemble not in ("max", "mean"):
+            raise ValueError("the retriever ensemble is 'max' or 'mean'")
+        rt = lc.V4LongContextRuntime(cfg, weights, retrievers=lc.load_retrievers(ckpt, cfg.dim) if ckpt else None,
+                                     use_max=ensemble == "max", swap_device_chunks=chunks,
+                                     chunk_entries=int(kw.get("kv_swap_chunk_entries", 4)))
+        return cfg, _V4HostAdapter(rt, device)
     return cfg, _V4HostAdapter(V4BlockRef(cfg, weights), device)
 
 

@@ -6,7 +6,7 @@ The two components exist on their own (``components/flashmemory.py``: scorer, en
 V4 block runtime (``models/v4_block_ref.py``), as the reference's plugin wires them into its engine:
 
 * Once per decode token, before the layers run: every retriever layer (its own ``wq_a / wq_b / q_norm / weights_proj``,
-  loaded from ``retrievers.<name>.*``) builds index queries from the token's *embedding*, scores the indexer keys of one
+  loaded from ``retrievers.l<ID>.*``) builds index queries from the token's *embedding*, scores the indexer keys of one
   source layer (the first ratio-4 layer; its keys are shared by all retriever layers), the scores are combined by max
   or mean, and the best ``index_topk`` of the ``position // ratio`` finished entries are kept.
 * Every ratio-4 layer then takes that one selection in place of its own indexer's (its indexer still appends its keys:
@@ -30,16 +30,44 @@ from .v4_block_ref import V4BlockRef, V4Config
 
 
 def synth_retriever_weights(cfg: V4Config, n_retrievers: int = 2, heads: int = 4, q_lora: int = 16, seed: int = 0) -> dict:
-    """``retrievers.<i>.{wq_a,wq_b,q_norm.weight,weights_proj}`` of a random retriever for ``cfg``."""
+    """``retrievers.l<i>.{wq_a.weight,wq_b.weight,q_norm_weight,weights_proj.weight}`` of a random retriever."""
     g = torch.Generator().manual_seed(seed + 313)
     w = {}
     for i in range(n_retrievers):
-        p = f"retrievers.{i}."
-        w[p + "wq_a"] = torch.randn(q_lora, cfg.dim, generator=g) * 0.2
-        w[p + "wq_b"] = torch.randn(heads * fm.D, q_lora, generator=g) * 0.2
-        w[p + "q_norm.weight"] = 1.0 + torch.randn(q_lora, generator=g) * 0.05
-        w[p + "weights_proj"] = torch.randn(heads, cfg.dim, generator=g) * 0.3
+        p = f"retrievers.l{i}."
+        w[p + "wq_a.weight"] = torch.randn(q_lora, cfg.dim, generator=g) * 0.2
+        w[p + "wq_b.weight"] = torch.randn(heads * fm.D, q_lora, generator=g) * 0.2
+        w[p + "q_norm_weight"] = 1.0 + torch.randn(q_lora, generator=g) * 0.05
+        w[p + "weights_proj.weight"] = torch.randn(heads, cfg.dim, generator=g) * 0.3
     return w
+
+
+RETRIEVER_TENSORS = ("wq_a.weight", "wq_b.weight", "q_norm_weight", "weights_proj.weight")
+
+
+def load_retrievers(path: str, hidden: int) -> dict:
+    """Read a retriever checkpoint (one safetensors file, ``retrievers.l<ID>.*``; f32 / bf16 / f16) and check that every
+    layer is complete and shaped for a model of width ``hidden`` with 128-wide index heads
+    (cpp_engine/engine/deepseek_v4_engine.cpp:190-240)."""
+    from ..formats.safetensors_io import SafetensorsFile
+    f = SafetensorsFile(path)
+    names = [k for k in f.keys() if k.startswith("retrievers.")]
+    layers = sorted({k.split(".")[1] for k in names})
+    if not layers:
+        raise ValueError(f"{path}: no retrievers.l<ID>.* tensors")
+    out = {}
+    for l in layers:
+        for suffix in RETRIEVER_TENSORS:
+            k = f"retrievers.{l}.{suffix}"
+            if k not in names:
+                raise ValueError(f"{path}: missing {k}")
+            out[k] = f.get(k).float()
+        a, b = out[f"retrievers.{l}.wq_a.weight"], out[f"retrievers.{l}.wq_b.weight"]
+        n, p = out[f"retrievers.{l}.q_norm_weight"], out[f"retrievers.{l}.weights_proj.weight"]
+        heads = b.shape[0] // fm.D
+        if a.shape[1] != hidden or b.shape != (heads * fm.D, a.shape[0]) or n.shape != (a.shape[0],) or p.shape != (heads, hidden):
+            raise ValueError(f"{path}: retriever {l} does not fit a model of width {hidden}")
+    return out
 
 
 class CompressedRowStore:
@@ -105,8 +133,8 @@ class V4LongContextRuntime(V4BlockRef):
             layers = []
             for n in names:
                 p = f"retrievers.{n}."
-                layers.append(fm.ScorerLayer(retrievers[p + "wq_a"].float(), retrievers[p + "wq_b"].float(),
-                                             retrievers[p + "q_norm.weight"].float(), retrievers[p + "weights_proj"].float(),
+                layers.append(fm.ScorerLayer(retrievers[p + "wq_a.weight"].float(), retrievers[p + "wq_b.weight"].float(),
+                                             retrievers[p + "q_norm_weight"].float(), retrievers[p + "weights_proj.weight"].float(),
                                              keys=self.src.ikeys))
             inv = fm.yarn_inv_freqs(cfg.rope_head_dim, cfg.compress_rope_theta, cfg.rope_factor, cfg.original_seq_len)
             self.retriever = fm.FlashMemoryRetriever(layers, inv, chunk_tokens=4, keep=cfg.index_topk, use_max=use_max,

@@ -54,8 +54,8 @@ def test_shared_selection_is_the_scorer_oracle_and_drives_every_indexer_layer():
         n = i // 4
         keys = m.src.ikeys[:n]
         inv = fm.yarn_inv_freqs(cfg.rope_head_dim, cfg.compress_rope_theta, cfg.rope_factor, cfg.original_seq_len)
-        per = torch.stack([fm.score_layer_ref(m.w["embed"][ids[i]], rw[f"retrievers.{j}.wq_a"], rw[f"retrievers.{j}.wq_b"],
-                                              rw[f"retrievers.{j}.q_norm.weight"], rw[f"retrievers.{j}.weights_proj"], inv,
+        per = torch.stack([fm.score_layer_ref(m.w["embed"][ids[i]], rw[f"retrievers.l{j}.wq_a.weight"], rw[f"retrievers.l{j}.wq_b.weight"],
+                                              rw[f"retrievers.l{j}.q_norm_weight"], rw[f"retrievers.l{j}.weights_proj.weight"], inv,
                                               keys, i, cfg.norm_eps) for j in range(2)])
         want, _ = fm.topk_ref(per.mean(0), cfg.index_topk)
         assert pick.tolist() == want.long().tolist() and int(pick.max()) < n

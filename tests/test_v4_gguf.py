@@ -146,3 +146,49 @@ def test_gguf_cli_serves_the_host_family_without_a_gpu(tmp_path):
     assert r.returncode == 0, r.stderr[-800:]
     want = V4BlockRef(cfg, w).generate(torch.tensor([3, 4, 5, 6, 7, 8]), 4)
     assert "tokens=" + ",".join(map(str, want)) in r.stdout and "family=deepseek4" in r.stdout
+
+
+def test_long_context_options_of_the_registered_family(tmp_path, monkeypatch):
+    """The host pool alone leaves the tokens unchanged; a retriever checkpoint is read, checked and used."""
+    from deepseek_v4_2080ti_b200.formats import safetensors_io
+    from deepseek_v4_2080ti_b200.models import registry
+    from deepseek_v4_2080ti_b200.models import v4_flashmemory as lc
+    cfg = _cfg()
+    w = synth_weights(cfg, seed=8)
+    path = str(tmp_path / "v4l.gguf")
+    v4_gguf.write_gguf(path, cfg, w, "F32")
+    b = G.read_bundle(path)
+    spec = registry.detect(b)
+    prompt = torch.arange(3, 27, dtype=torch.int32) % cfg.vocab_size
+
+    def run(rt, n=6):
+        slot = rt.allocate()
+        tok = rt.prefill(slot, prompt)
+        out = [int(tok)]
+        for _ in range(n - 1):
+            tok = rt.decode([slot], tok.to(torch.int32))
+            out.append(int(tok))
+        return out
+    want = V4BlockRef(cfg, w).generate(prompt, 6)
+    _, rt = spec.build_runtime(b, "cpu", kv_swap_chunks=max(cfg.index_topk, 4), kv_swap_chunk_entries=2)
+    assert isinstance(rt.rt, lc.V4LongContextRuntime) and run(rt) == want and rt.rt.swap_stats()["d2h_bytes"] > 0
+    monkeypatch.setenv("POCKETLLM_GGUF_KV_SWAP", "1")
+    monkeypatch.setenv("POCKETLLM_GGUF_KV_SWAP_GPU_CHUNKS", "64")
+    _, rt = spec.build_runtime(b, "cpu")
+    assert isinstance(rt.rt, lc.V4LongContextRuntime) and run(rt) == want
+    monkeypatch.delenv("POCKETLLM_GGUF_KV_SWAP")
+    ck = str(tmp_path / "flashmemory.safetensors")
+    rw = lc.synth_retriever_weights(cfg, n_retrievers=2, seed=4)
+    safetensors_io.write_file(ck, {k: v.to(torch.bfloat16) for k, v in rw.items()})
+    got = lc.load_retrievers(ck, cfg.dim)
+    assert set(got) == set(rw) and all(v.dtype == torch.float32 for v in got.values())
+    _, rt = spec.build_runtime(b, "cpu", flashmemory=ck, flashmemory_ensemble="mean")
+    out = run(rt)
+    assert len(out) == 6 and rt.rt.retriever is not None and rt.rt.last_selection is not None and not rt.rt.retriever.use_max
+    del rw["retrievers.l1.q_norm_weight"]
+    safetensors_io.write_file(ck, rw)
+    with pytest.raises(ValueError, match="missing retrievers.l1.q_norm_weight"):
+        spec.build_runtime(b, "cpu", flashmemory=ck)
+    safetensors_io.write_file(ck, lc.synth_retriever_weights(cfg, n_retrievers=1, seed=4))
+    with pytest.raises(ValueError, match="does not fit a model of width"):
+        lc.load_retrievers(ck, cfg.dim + 16)
