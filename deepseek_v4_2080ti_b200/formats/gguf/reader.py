@@ -39,9 +39,17 @@ class TensorInfo:
 
 class GGUFFile:
     def __init__(self, path: str):
+        """A file that does not parse raises ``ValueError`` (whatever went wrong underneath: a short read, a count that
+        does not fit, an unknown type code)."""
         self.path = path
         self._f = open(path, "rb")
-        self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
+        try:
+            self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
+            self._parse(path)
+        except (struct.error, OverflowError, KeyError, IndexError, MemoryError) as exc:
+            raise ValueError(f"{path}: malformed GGUF file ({type(exc).__name__}: {exc})") from exc
+
+    def _parse(self, path: str) -> None:
         self._pos = 0
         magic, version = struct.unpack_from("<II", self._mm, 0)
         if magic != GGUF_MAGIC:

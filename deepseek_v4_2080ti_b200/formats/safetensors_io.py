@@ -95,12 +95,29 @@ class SafetensorsFile:
         self.path = path
         self._f = open(path, "rb")
         self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
+        if len(self._mm) < 8:
+            raise ValueError(f"{path}: too short for a safetensors file")
         (hlen,) = struct.unpack("<Q", self._mm[:8])
         if hlen <= 0 or hlen > len(self._mm) - 8:
             raise ValueError(f"bad safetensors header length in {path}")
-        self.header = json.loads(self._mm[8:8 + hlen].decode())
+        self.header = json.loads(self._mm[8:8 + hlen].decode())          # JSON / UTF-8 errors are ValueErrors
+        if not isinstance(self.header, dict):
+            raise ValueError(f"{path}: the safetensors header is not an object")
         self.metadata = self.header.pop("__metadata__", {})
         self._base = 8 + hlen
+        size = len(self._mm) - self._base
+        for name, info in self.header.items():                           # every record checked once, here
+            try:
+                b, e = (int(v) for v in info["data_offsets"])
+                n = 1
+                for d in info["shape"]:
+                    n *= int(d)
+                dt = _RD.get(info["dtype"])                           # a dtype this reader has no tensor type for is
+                item = torch.empty((), dtype=dt).element_size() if dt is not None else None   # refused when it is read
+            except (KeyError, TypeError, ValueError) as exc:
+                raise ValueError(f"{path}: malformed record for tensor {name!r}") from exc
+            if not 0 <= b <= e <= size or (item is not None and (e - b) != n * item):
+                raise ValueError(f"{path}: tensor {name!r} does not fit its bytes ({b}..{e} of {size}, shape {info['shape']})")
 
     def keys(self) -> list[str]:
         return list(self.header)
@@ -108,6 +125,8 @@ class SafetensorsFile:
     def get(self, name: str) -> torch.Tensor:
         info = self.header[name]
         b, e = info["data_offsets"]
+        if info["dtype"] not in _RD:
+            raise ValueError(f"{self.path}: tensor {name!r} has dtype {info['dtype']}, which this reader does not map")
         dt = _RD[info["dtype"]]
         buf = torch.frombuffer(self._mm, dtype=torch.uint8, count=e - b, offset=self._base + b) if e > b else torch.empty(0, dtype=torch.uint8)
         return buf.view(dt).reshape(info["shape"])

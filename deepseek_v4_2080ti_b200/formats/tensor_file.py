@@ -73,17 +73,22 @@ def read(path: str | Path) -> TensorFile:
         off += _REC.size
         if code not in _CODES or not 1 <= ndim <= 8 or reserved != 0 or not 1 <= name_len <= 4096:
             raise ValueError(f"malformed tensor record in {path}")
-        name = data[off:off + name_len].decode()
+        name = data[off:off + name_len].decode()                          # a bad name is a UnicodeDecodeError, a ValueError
         off += name_len
+        if off + 8 * ndim > len(data):
+            raise ValueError(f"truncated tensor shape in {path}")
         shape = struct.unpack_from(f"<{ndim}Q", data, off)
         off += 8 * ndim
         np_dtype = _CODES[code][0]
-        want = int(np.prod(shape)) * np_dtype.itemsize
+        count = 1
+        for d in shape:
+            count *= int(d)                                              # Python integers: no wrap-around on hostile extents
+        want = count * np_dtype.itemsize
         if want != nbytes or off + nbytes > len(data):
             raise ValueError(f"tensor {name!r}: payload size does not match its shape in {path}")
         if name in out.tensors:
             raise ValueError(f"tensor {name!r} appears twice in {path}")
-        out.tensors[name] = torch.from_numpy(np.frombuffer(data, np_dtype, int(np.prod(shape)), off).reshape(shape).copy())
+        out.tensors[name] = torch.from_numpy(np.frombuffer(data, np_dtype, count, off).reshape(shape).copy())
         off += nbytes
     if off != len(data):
         raise ValueError(f"trailing bytes after the last record in {path}")
