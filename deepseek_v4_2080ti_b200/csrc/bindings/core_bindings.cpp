@@ -46,6 +46,7 @@ class PyEngine : public InferenceEngine {
     PYBIND11_OVERRIDE_PURE(StepResult, InferenceEngine, batch_decode, slots, tokens);
   }
   bool is_eos(int32_t token) const override { PYBIND11_OVERRIDE_PURE(bool, InferenceEngine, is_eos, token); }
+  int64_t vocab_size() const override { PYBIND11_OVERRIDE(int64_t, InferenceEngine, vocab_size); }
 };
 
 py::object value_to_py(const GGUFValue& v) {
@@ -125,7 +126,10 @@ PYBIND11_MODULE(pocketllm_cpp, m) {
       .def(py::init<>())
       .def(py::init([](std::vector<int32_t> t) { StepResult r; r.next_tokens = std::move(t); return r; }))
       .def_readwrite("next_tokens", &StepResult::next_tokens);
-  py::class_<InferenceEngine, PyEngine>(m, "InferenceEngine").def(py::init<>());
+  py::class_<InferenceEngine, PyEngine>(m, "InferenceEngine")
+      .def(py::init<>())
+      .def("vocab_size", [](const InferenceEngine& e) { return e.InferenceEngine::vocab_size(); },
+           "0: the engine does not say how many token ids it knows (override to let front ends refuse foreign ids)");
 
   py::class_<SchedulerOptions>(m, "SchedulerOptions")
       .def(py::init<>())

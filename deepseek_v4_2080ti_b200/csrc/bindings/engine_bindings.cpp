@@ -79,6 +79,7 @@ PYBIND11_MODULE(pocketllm_engine_cpp, m) {
       .def_property_readonly("max_slots", [](EngineHolder& h) { return h.eng->max_slots(); })
       .def_property_readonly("max_context", [](EngineHolder& h) { return h.eng->max_context(); })
       .def_property_readonly("total_blocks", [](EngineHolder& h) { return h.eng->total_blocks(); })
+      .def_property_readonly("vocab_size", [](EngineHolder& h) { return h.eng->vocab_size(); })
       .def("allocate_slot", [](EngineHolder& h) { return h.eng->allocate_slot(); })
       .def("free_slot", [](EngineHolder& h, int s) { h.eng->free_slot(s); })
       .def("slot_length", [](EngineHolder& h, int s) { return h.eng->slot_length(s); })

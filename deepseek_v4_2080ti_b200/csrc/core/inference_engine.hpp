@@ -33,6 +33,9 @@ class InferenceEngine {
   virtual StepResult batch_prefill(const std::vector<PrefillItem>& items) = 0;
   virtual StepResult batch_decode(const std::vector<int>& slots, const std::vector<int32_t>& tokens) = 0;
   virtual bool is_eos(int32_t token) const = 0;
+  // Number of token ids the model knows (ids are 0 .. vocab_size - 1); 0 when the engine cannot say.  Front ends use it
+  // to refuse a request whose token ids the model has no row for, before anything reaches a device.
+  virtual int64_t vocab_size() const { return 0; }
 };
 
 }  // namespace pocket

@@ -1,5 +1,6 @@
 #include "openai_server.hpp"
 
+#include <cmath>
 #include <arpa/inet.h>
 #include <cerrno>
 #include <chrono>
@@ -161,7 +162,24 @@ void OpenAIServer::serve_connection(int fd) {
     std::string lower = head;
     for (auto& c : lower) c = char(tolower(c));
     const size_t p = lower.find("content-length:");
-    if (p != std::string::npos) content_length = size_t(std::strtoull(lower.c_str() + p + 15, nullptr, 10));
+    if (p != std::string::npos) {
+      // digits only (after optional blanks), up to the end of the line: "-5", "abc" and "12x" are refused, not guessed
+      size_t q = p + 15;
+      while (q < lower.size() && (lower[q] == ' ' || lower[q] == '\t')) ++q;
+      const size_t first = q;
+      unsigned long long v = 0;
+      bool ok = true;
+      while (q < lower.size() && lower[q] >= '0' && lower[q] <= '9') {
+        if (v > (1ull << 40)) { ok = false; break; }
+        v = v * 10 + unsigned(lower[q] - '0');
+        ++q;
+      }
+      while (ok && q < lower.size() && (lower[q] == ' ' || lower[q] == '\t')) ++q;
+      ok = ok && q > first && (q >= lower.size() || lower[q] == '\r' || lower[q] == '\n');
+      if (!ok && q > first && v > (1ull << 40)) { send_all(fd, http_response(413, "text/plain", "body too large")); return; }
+      if (!ok) { send_all(fd, http_response(400, "text/plain", "bad content-length")); return; }
+      content_length = size_t(v);
+    }
   }
   if (content_length > (64u << 20)) { send_all(fd, http_response(413, "text/plain", "body too large")); return; }
   std::string body = buf.substr(header_end + 4);
@@ -230,8 +248,22 @@ OpenAIServer::Reply OpenAIServer::completion(const Json& body, bool chat, int fd
   // ---- prompt -> token ids
   std::vector<int32_t> prompt;
   const bool thinking = body["thinking"].as_bool(false);
+  // every id must be a whole number the model has a row for: a kernel indexes tables with it
+  const int64_t vocab = eng_.vocab_size();
+  auto take_token = [&](const Json& t) {
+    if (!t.is_number()) return false;
+    const double d = t.as_double();
+    if (!(d >= 0.0) || d > 2147483647.0 || d != std::floor(d)) return false;
+    if (vocab > 0 && d >= double(vocab)) return false;
+    prompt.push_back(int32_t(d));
+    return true;
+  };
   if (body.contains("prompt_token_ids")) {
-    for (const Json& t : body["prompt_token_ids"].items()) prompt.push_back(int32_t(t.as_int()));
+    if (!body["prompt_token_ids"].is_array())
+      return {400, "application/json", error_body("prompt_token_ids must be a list of token ids", "invalid_request_error").dump()};
+    for (const Json& t : body["prompt_token_ids"].items())
+      if (!take_token(t))
+        return {400, "application/json", error_body("prompt_token_ids holds a value that is not a token id of this model", "invalid_request_error").dump()};
   } else {
     if (!sidecar_) return {501, "application/json", error_body("text prompts need the templating sidecar; send prompt_token_ids", "unsupported_feature").dump()};
     Json req = Json::object();
@@ -252,11 +284,19 @@ OpenAIServer::Reply OpenAIServer::completion(const Json& body, bool chat, int fd
     const Json enc = sidecar_->call(req);
     if (!enc["ok"].as_bool(false)) return {400, "application/json", error_body(enc["error"].as_string(), "invalid_request_error").dump()};
     if (!enc.contains("token_ids")) return {501, "application/json", error_body("the sidecar has no tokenizer; send prompt_token_ids", "unsupported_feature").dump()};
-    for (const Json& t : enc["token_ids"].items()) prompt.push_back(int32_t(t.as_int()));
+    for (const Json& t : enc["token_ids"].items())
+      if (!take_token(t))
+        return {400, "application/json", error_body("the tokenizer produced an id outside this model's vocabulary", "invalid_request_error").dump()};
   }
   if (prompt.empty()) return {400, "application/json", error_body("empty prompt", "invalid_request_error").dump()};
-  const int max_new = int(body["max_tokens"].as_int(opt_.default_max_tokens));
-  if (max_new < 1) return {400, "application/json", error_body("max_tokens must be >= 1", "invalid_request_error").dump()};
+  int max_new = opt_.default_max_tokens;
+  if (body.contains("max_tokens") && !body["max_tokens"].is_null()) {
+    const Json& m = body["max_tokens"];
+    const double d = m.is_number() ? m.as_double() : -1.0;
+    if (!(d >= 1.0) || d > 1.0e9 || d != std::floor(d))
+      return {400, "application/json", error_body("max_tokens must be a whole number >= 1", "invalid_request_error").dump()};
+    max_new = int(d);
+  }
   if (int64_t(prompt.size()) + 1 > eng_.max_context())
     return {400, "application/json", error_body("prompt does not fit the context window", "invalid_request_error").dump()};
 

@@ -126,6 +126,7 @@ class QwenNativeEngine : public InferenceEngine {
   StepResult batch_prefill(const std::vector<PrefillItem>& items) override;
   StepResult batch_decode(const std::vector<int>& slots, const std::vector<int32_t>& tokens) override;
   bool is_eos(int32_t token) const override;
+  int64_t vocab_size() const override { return int64_t(cfg_.vocab_size); }
 
   // Convenience: greedy generation for one prompt on a fresh slot.
   std::vector<int32_t> generate(const std::vector<int32_t>& prompt, int max_new_tokens, double* prefill_s = nullptr,

@@ -47,6 +47,7 @@ class HostQwenAdapter:
         self.oracle, self.max_context, self.max_slots = oracle, int(max_context), int(max_slots)
         self.method, self.block, self._make_drafter = method, max(1, int(block)), make_drafter
         self.eos_token_ids = tuple(eos_token_ids)
+        self.vocab_size = int(oracle.cfg.vocab_size)
         self.speculative_methods = (method,) if method else ()
         self.seqs: dict[int, _Seq] = {}
         self.last_cached_tokens = 0

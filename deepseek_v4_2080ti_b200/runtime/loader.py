@@ -71,6 +71,7 @@ class RuntimeAdapter:
         # log-probabilities need the whole vocabulary in one place: single-rank runs (a rank of a tensor-parallel group
         # holds a vocabulary shard of the head)
         self.supports_logprobs = getattr(getattr(rt, "comm", None), "world", 1) == 1
+        self.vocab_size = int(rt.cfg.vocab_size)
         self.last_cached_tokens = 0
         self._rng: dict[int, torch.Generator] = {}      # per slot: the request's seeded generator
         self._counts: dict[int, torch.Tensor] = {}      # per slot: occurrences of each local vocabulary id
@@ -275,6 +276,7 @@ class CppRuntimeAdapter:
         opt.eos_tokens = list(eos_token_ids)
         self.eng = cpp.QwenEngine(checkpoint_dir, opt)
         self.max_context, self.eos_token_ids = max_context, tuple(eos_token_ids)
+        self.vocab_size = int(getattr(self.eng, "vocab_size", 0) or 0)
         self.last_cached_tokens = 0
         self._sched_batch = 0
 
@@ -332,6 +334,8 @@ class GgufRuntimeAdapter:
         # sequence of the step) can be sampled from: temperature / top-k / top-p / min-p / penalties on the device
         self.supports_sampling = bool(getattr(rt, "exposes_logits", False))
         self.supports_logprobs = self.supports_sampling
+        cfg = getattr(rt, "cfg", None)
+        self.vocab_size = int(getattr(cfg, "vocab_size", 0) or getattr(cfg, "vocab", 0) or 0)
         self._rng: dict[int, torch.Generator] = {}
         self._counts: dict[int, torch.Tensor] = {}
         self._seed_counter = 0

@@ -132,7 +132,14 @@ class NativeBackend(BackendBase):
         if not sp.greedy and not getattr(self.runtime, "supports_sampling", False):
             raise UnsupportedFeatureError("this runtime only supports greedy decoding (temperature 0)")
         limit = self.args.max_model_len or getattr(self.runtime, "max_context", None)
-        n = len(self._tokens(req))
+        toks = self._tokens(req)
+        n = len(toks)
+        # token ids index embedding and count tables on the device: refuse anything the model has no row for
+        vocab = int(getattr(self.runtime, "vocab_size", 0) or 0)
+        for t in toks:
+            if isinstance(t, bool) or not isinstance(t, int) or t < 0 or t > 0x7FFFFFFF or (vocab and t >= vocab):
+                raise ConfigurationError(f"prompt holds {t!r}, which is not a token id of this model"
+                                         + (f" (vocabulary {vocab})" if vocab else ""))
         if limit and n + 1 > limit:
             raise ConfigurationError(f"prompt of {n} tokens does not fit max_model_len {limit}")
 

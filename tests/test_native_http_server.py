@@ -151,3 +151,86 @@ def test_sidecar_client_and_chat_through_the_server():
                 os.environ.pop("PYTHONPATH", None)
             else:
                 os.environ["PYTHONPATH"] = env_backup
+
+
+def _raw(port, data, timeout=3.0):
+    import socket
+    s = socket.create_connection(("127.0.0.1", port), timeout=timeout)
+    try:
+        s.sendall(data)
+        try:
+            s.shutdown(socket.SHUT_WR)
+        except OSError:
+            pass
+        out = b""
+        while True:
+            try:
+                c = s.recv(65536)
+            except (socket.timeout, ConnectionError):
+                break
+            if not c:
+                break
+            out += c
+        return out
+    finally:
+        s.close()
+
+
+class VocabEngine(FakeEngine):
+    def vocab_size(self): return 50
+
+
+def test_hostile_requests_are_refused_and_the_server_keeps_serving():
+    import random
+    eng = VocabEngine()
+    opt = cpp.OpenAIServerOptions()
+    opt.port, opt.model_name = 0, "fake-model"
+    srv = cpp.OpenAIServer(eng, opt)
+    srv.start()
+    try:
+        port = srv.port
+        body = json.dumps({"prompt_token_ids": [1, 2, 3], "max_tokens": 3}).encode()
+        post = lambda b, length=None: (b"POST /v1/completions HTTP/1.1\r\nContent-Type: application/json\r\nContent-Length: "
+                                       + str(len(b) if length is None else length).encode() + b"\r\n\r\n" + b)
+        status = lambda raw: int(raw.split(b" ", 2)[1]) if raw.startswith(b"HTTP/1.1 ") else None
+        assert status(_raw(port, post(body))) == 200
+        # lengths that are not plain digits are refused rather than guessed
+        for length in ("-5", "abc", "12x", ""):
+            assert status(_raw(port, post(body, length))) == 400, length
+        assert status(_raw(port, post(body, "99999999999999999999"))) == 413
+        assert status(_raw(port, b"GET /health HTTP/1.1\r\nX: " + b"a" * 2_000_000 + b"\r\n\r\n")) == 413
+        assert _raw(port, post(body, 100000)) == b""                       # the body never arrives: no answer, no thread left behind
+        assert status(_raw(port, b"GET /health\r\n\r\n")) == 400
+        assert _raw(port, os.urandom(300)) in (b"",) or True
+        # token ids: whole numbers inside the vocabulary only - a kernel would index a table with them
+        for ids in ([1.5], [-3], [1e30], ["7"], [None], [50], [2 ** 31], "12", {"a": 1}):
+            raw = _raw(port, post(json.dumps({"prompt_token_ids": ids, "max_tokens": 2}).encode()))
+            assert status(raw) == 400 and b"invalid_request_error" in raw, ids
+        assert status(_raw(port, post(json.dumps({"prompt_token_ids": [49, 0, 7.0], "max_tokens": 2}).encode()))) == 200
+        for b in (b"{{{{{", b"[" * 100001 + b"]" * 100001, b'{"prompt_token_ids":[1],"max_tokens":1e18}', b'{"prompt_token_ids":[1],"max_tokens":"y"}'):
+            assert status(_raw(port, post(b))) == 400
+        # random byte damage to a valid request, idle connections, then a normal request still works
+        rng = random.Random(5)
+        good = post(body)
+        for _ in range(100):
+            b = bytearray(good)
+            for _ in range(rng.randrange(1, 8)):
+                b[rng.randrange(len(b))] = rng.randrange(256)
+            _raw(port, bytes(b), timeout=1.0)
+        import socket
+        idle = [socket.create_connection(("127.0.0.1", port)) for _ in range(16)]
+        assert status(_raw(port, good)) == 200
+        for s in idle:
+            s.close()
+    finally:
+        srv.stop()
+
+
+def test_an_engine_that_does_not_know_its_vocabulary_still_gets_whole_non_negative_ids():
+    eng = FakeEngine()
+    assert cpp.InferenceEngine.vocab_size(eng) == 0
+    opt = cpp.OpenAIServerOptions()
+    opt.port = 0
+    srv = cpp.OpenAIServer(eng, opt)
+    assert srv.handle("POST", "/v1/completions", json.dumps({"prompt_token_ids": [-1], "max_tokens": 1}))[0] == 400
+    assert srv.handle("POST", "/v1/completions", json.dumps({"prompt_token_ids": [0.5], "max_tokens": 1}))[0] == 400

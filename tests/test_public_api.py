@@ -344,3 +344,18 @@ def test_n_choices_expand_with_consecutive_seeds_and_merge():
         SamplingParams(n=0)
     with pytest.raises(UnsupportedFeatureError):
         list(b.stream(req))
+
+
+def test_token_ids_outside_the_vocabulary_never_reach_the_runtime():
+    b, rt = make_backend()
+    rt.vocab_size = 250
+    for bad in ([1, -1], [250], [2 ** 31]):                        # refused by the request type or by the backend
+        with pytest.raises(ConfigurationError):
+            b.generate([GenerationRequest(prompt_tokens=bad, sampling_params=SamplingParams(max_tokens=1))])
+    with pytest.raises(ConfigurationError, match="not a token id of this model"):
+        b.generate([GenerationRequest(prompt_tokens=[3, 250], sampling_params=SamplingParams(max_tokens=1))])
+    assert not any(c[0] == "prefill" for c in rt.calls)
+    assert b.generate([GenerationRequest(prompt_tokens=[0, 249], sampling_params=SamplingParams(max_tokens=1))])[0].token_ids == [0]
+    del rt.vocab_size                                    # a runtime that does not say: still whole and non-negative
+    with pytest.raises(ConfigurationError):
+        b.generate([GenerationRequest(prompt_tokens=[-5], sampling_params=SamplingParams(max_tokens=1))])
