@@ -162,12 +162,23 @@ def make_handler(state: ServerState):
                 pass
 
         def _body(self) -> dict[str, Any]:
-            n = int(self.headers.get("Content-Length") or 0)
+            raw_len = (self.headers.get("Content-Length") or "").strip()
+            if not raw_len.isdigit():                          # "-5", "abc", "" are refused rather than guessed
+                raise ConfigurationError("Content-Length must be a whole number")
+            n = int(raw_len)
             if n <= 0:
                 raise ConfigurationError("request body is empty")
             if n > MAX_BODY:
                 raise ConfigurationError("request body too large")
-            obj = json.loads(self.rfile.read(n).decode("utf-8"))
+            data = self.rfile.read(n)
+            if len(data) != n:
+                raise ConfigurationError("request body is shorter than its Content-Length")
+            try:
+                obj = json.loads(data.decode("utf-8"))
+            except RecursionError as exc:                      # thousands of nested brackets
+                raise ConfigurationError("request body is nested too deeply") from exc
+            except ValueError as exc:                          # malformed JSON or UTF-8
+                raise ConfigurationError(f"request body is not valid JSON: {exc}") from exc
             if not isinstance(obj, dict):
                 raise ConfigurationError("request body must be a JSON object")
             return obj

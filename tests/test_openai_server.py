@@ -147,3 +147,34 @@ def test_n_choices_in_one_response_and_not_in_a_stream(server):
     assert st in (400, 501) and b"n must be 1" in raw
     st, raw = call(port, "POST", "/v1/completions", {"prompt": "A", "n": 99})
     assert st == 400
+
+
+def test_malformed_bodies_are_client_errors(server):
+    import socket
+    port, _ = server
+
+    def raw(data):
+        s = socket.create_connection(("127.0.0.1", port), timeout=5)
+        try:
+            s.sendall(data)
+            s.shutdown(socket.SHUT_WR)
+            out = b""
+            while True:
+                c = s.recv(65536)
+                if not c:
+                    break
+                out += c
+            return int(out.split(b" ", 2)[1]) if out.startswith(b"HTTP/1.") else None
+        finally:
+            s.close()
+    body = json.dumps({"prompt": [1, 2, 3], "max_tokens": 2}).encode()
+    post = lambda b, n=None: (b"POST /v1/completions HTTP/1.1\r\nContent-Type: application/json\r\nContent-Length: "
+                              + str(len(b) if n is None else n).encode() + b"\r\n\r\n" + b)
+    assert raw(post(body)) == 200
+    for n in ("-5", "abc", "", 100000):                         # not a number; or a body that stops short of it
+        assert raw(post(body, n)) == 400, n
+    assert raw(post(b"[" * 100001 + b"]" * 100001)) == 400     # nesting that exhausts the parser's stack
+    assert raw(post(b"{{{{")) == 400 and raw(post(b"[1, 2]")) == 400 and raw(post(b"\xff\xfe{}")) == 400
+    assert raw(post(b'{"prompt": [1.5, -3], "max_tokens": 2}')) == 400
+    assert raw(post(b'{"prompt": [1], "max_tokens": "y"}')) == 400
+    assert raw(post(body)) == 200
