@@ -50,6 +50,11 @@ def main(argv=None) -> int:
     t0 = time.time()
     cfg, rt = spec.build_runtime(b, dev, rank, world, comm, max_slots=1, max_context=a.max_context)
     load_s = time.time() - t0
+    vocab = int(getattr(cfg, "vocab_size", 0) or getattr(cfg, "vocab", 0) or 0)
+    bad = [t for t in ids if t < 0 or (vocab and t >= vocab)]
+    if bad or not ids:                                    # kernels index tables with the ids: refuse before the device sees them
+        raise SystemExit(f"--token-ids: {bad[:4] if bad else 'empty'} is not a token id of this model"
+                         + (f" (vocabulary {vocab})" if vocab else ""))
     prompt = torch.tensor(ids, dtype=torch.int32, device=dev)
     slot = rt.allocate()
     sync = torch.cuda.synchronize if on_gpu else (lambda: None)

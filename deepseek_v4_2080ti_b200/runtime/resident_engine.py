@@ -33,6 +33,18 @@ class ResidentEngine:
         self.stats = {"commands": 0, "errors": 0, "prefill_tokens": 0, "decode_tokens": 0, "drafted": 0, "accepted": 0,
                       "busy_seconds": 0.0}
         self._live: set[int] = set()
+        cfg = getattr(runtime, "cfg", None)
+        self.vocab = int(getattr(runtime, "vocab_size", 0) or getattr(cfg, "vocab_size", 0) or getattr(cfg, "vocab", 0) or 0)
+
+    def _tokens(self, cmd: dict) -> list[int]:
+        """The command's token ids, each a whole number the model has a row for: kernels index tables with them."""
+        out = []
+        for t in cmd["tokens"]:
+            if isinstance(t, bool) or not isinstance(t, (int, float)) or t != int(t) or t < 0 or t > 0x7FFFFFFF \
+                    or (self.vocab and t >= self.vocab):
+                raise ValueError(f"{t!r} is not a token id of this model" + (f" (vocabulary {self.vocab})" if self.vocab else ""))
+            out.append(int(t))
+        return out
 
     # ---- one command
     def _scalar(self, t: Any) -> int:
@@ -65,14 +77,14 @@ class ResidentEngine:
             self._live.clear()
             return {}
         if op == "prefill":
-            s, toks = self._slot(cmd), [int(t) for t in cmd["tokens"]]
+            s, toks = self._slot(cmd), self._tokens(cmd)
             if not toks:
                 raise ValueError("prefill needs at least one token")
             tok = self._scalar(rt.prefill(s, self.to_ids(toks), int(cmd.get("chunk", self.chunk))))
             self.stats["prefill_tokens"] += len(toks)
             return {"token": tok, "length": int(rt.lengths[s])}
         if op == "decode":
-            slots, toks = [int(s) for s in cmd["slots"]], [int(t) for t in cmd["tokens"]]
+            slots, toks = [int(s) for s in cmd["slots"]], self._tokens(cmd)
             if len(slots) != len(toks) or not slots or len(set(slots)) != len(slots):
                 raise ValueError("decode takes one token for each of a set of distinct slots")
             for s in slots:
@@ -81,7 +93,7 @@ class ResidentEngine:
             self.stats["decode_tokens"] += len(slots)
             return {"tokens": out}
         if op == "verify":
-            s, toks = self._slot(cmd), [int(t) for t in cmd["tokens"]]
+            s, toks = self._slot(cmd), self._tokens(cmd)
             if not toks:
                 raise ValueError("verify needs the last accepted token and the drafts")
             accepted, tok = rt.verify(s, self.to_ids(toks))

@@ -81,12 +81,26 @@ def test_loop_survives_failing_commands():
     eng, failed, r = _run([{"op": "prefill", "slot": 0, "tokens": [1]},           # not allocated
                            "this is not json", [1, 2], {"op": "launch"},
                            {"op": "alloc"}, {"op": "alloc"}, {"op": "alloc"},        # third: no free slot
-                           {"op": "prefill", "slot": 0, "tokens": [-1]},            # the runtime raises
+                           {"op": "prefill", "slot": 0, "tokens": [-1]},            # refused before the runtime sees it
                            {"op": "decode", "slots": [0, 0], "tokens": [1, 2]},      # duplicate slot
                            {"op": "prefill", "slot": 0, "tokens": [5, 6]},           # and the engine still works
                            {"op": "reset"}, {"op": "stats"}])
     oks = [x["ok"] for x in r]
     assert oks == [False, False, False, False, True, True, False, False, False, True, True, True]
     assert failed == 7 and "not allocated" in r[0]["error"] and "JSONDecodeError" in r[1]["error"]
-    assert "unknown op" in r[3]["error"] and "no free slot" in r[6]["error"] and "negative token" in r[7]["error"]
+    assert "unknown op" in r[3]["error"] and "no free slot" in r[6]["error"] and "not a token id" in r[7]["error"]
     assert r[9]["token"] == 11 and r[11]["live_slots"] == [] and r[11]["stats"]["errors"] == 7
+
+
+def test_token_ids_are_checked_against_the_vocabulary():
+    class Rt(FakeRuntime):
+        vocab_size = 100
+    from deepseek_v4_2080ti_b200.runtime.resident_engine import ResidentEngine
+    eng = ResidentEngine(Rt())
+    s = eng.execute({"op": "alloc"})["slot"]
+    for bad in ([100], [3, 1.5], ["7"], [True], [2 ** 31], [-2]):
+        with __import__("pytest").raises(ValueError, match="not a token id"):
+            eng.execute({"op": "prefill", "slot": s, "tokens": bad})
+    assert eng.execute({"op": "prefill", "slot": s, "tokens": [99, 7.0]})["length"] >= 2
+    with __import__("pytest").raises(ValueError, match="not a token id"):
+        eng.execute({"op": "decode", "slots": [s], "tokens": [100]})
