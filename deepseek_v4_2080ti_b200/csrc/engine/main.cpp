@@ -27,6 +27,7 @@
 //   --qwen-temperature F --qwen-top-k K --qwen-top-p P --qwen-seed S     host-side sampling (default greedy)
 //   --eos a,b                  stop tokens;  --json  machine-readable result line
 // (Role of cpp_engine/engine/main.cpp.)
+#include <cerrno>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -64,18 +65,45 @@ struct Args {
   unsigned long long seed = 0;
 };
 
-std::vector<int32_t> parse_ids(const std::string& s) {
-  std::vector<int32_t> out;
+// Whole numbers separated by commas or blanks.  Anything else ("abc", "1.5", a value that does not fit 32 bits) makes the
+// line invalid as a whole: `err` says which field, nothing is guessed.
+bool parse_ids_checked(const std::string& s, std::vector<int32_t>& out, std::string& err) {
+  out.clear();
   std::string cur;
   for (char c : s + ",") {
-    if (c == ',' || c == ' ' || c == '\n' || c == '\t') {
-      if (!cur.empty()) out.push_back(int32_t(std::stol(cur)));
+    if (c == ',' || c == ' ' || c == '\n' || c == '\t' || c == '\r') {
+      if (!cur.empty()) {
+        errno = 0;
+        char* end = nullptr;
+        const long long v = std::strtoll(cur.c_str(), &end, 10);
+        if (end == cur.c_str() || *end != '\0' || errno != 0 || v < -2147483648ll || v > 2147483647ll) {
+          err = "not a whole 32-bit number: " + cur.substr(0, 32);
+          return false;
+        }
+        out.push_back(int32_t(v));
+      }
       cur.clear();
     } else {
       cur.push_back(c);
     }
   }
+  return true;
+}
+
+std::vector<int32_t> parse_ids(const std::string& s) {
+  std::vector<int32_t> out;
+  std::string err;
+  if (!parse_ids_checked(s, out, err)) throw std::runtime_error(err);
   return out;
+}
+
+// Empty when every id is a row of the model's tables (0 .. vocab - 1), else what is wrong.  Kernels index the embedding
+// with these ids, so a foreign one is refused here.
+std::string bad_token(const std::vector<int32_t>& ids, int64_t vocab) {
+  for (int32_t t : ids)
+    if (t < 0 || (vocab > 0 && int64_t(t) >= vocab))
+      return "token id " + std::to_string(t) + " is outside the vocabulary (" + std::to_string(vocab) + ")";
+  return "";
 }
 
 std::string join(const std::vector<int32_t>& v) {
@@ -160,8 +188,12 @@ bool parse(int argc, char** argv, Args& a) {
 }
 
 std::vector<int32_t> prompt_of(const Args& a, int64_t vocab) {
-  if (!a.token_ids.empty()) return parse_ids(a.token_ids);
-  if (!a.token_file.empty()) return parse_ids(read_text_file(a.token_file));
+  if (!a.token_ids.empty() || !a.token_file.empty()) {
+    std::vector<int32_t> p = parse_ids(a.token_ids.empty() ? read_text_file(a.token_file) : a.token_ids);
+    const std::string why = bad_token(p, vocab);
+    if (!why.empty()) throw std::runtime_error(why);
+    return p;
+  }
   std::vector<int32_t> p;
   uint64_t x = 0x9E3779B97F4A7C15ull;
   for (int i = 0; i < std::max(1, a.synthetic); ++i) {
@@ -330,10 +362,14 @@ int main(int argc, char** argv) {
       std::string line;
       while (std::getline(std::cin, line)) {
         if (line == "quit" || line == "exit") break;
-        std::vector<int32_t> f = parse_ids(line);
-        if (f.size() < 2) { std::printf("qwen_persistent_error=1 message=expected <max_new_tokens> tok...\n"); std::fflush(stdout); continue; }
+        std::vector<int32_t> f;
+        std::string why;
+        if (!parse_ids_checked(line, f, why)) { std::printf("qwen_persistent_error=1 message=%s\n", why.c_str()); std::fflush(stdout); continue; }
+        if (f.size() < 2 || f[0] < 1) { std::printf("qwen_persistent_error=1 message=expected <max_new_tokens> tok...\n"); std::fflush(stdout); continue; }
         const int max_new = f[0];
         std::vector<int32_t> prompt(f.begin() + 1, f.end());
+        why = bad_token(prompt, cfg.vocab_size);
+        if (!why.empty()) { std::printf("qwen_persistent_error=1 message=%s\n", why.c_str()); std::fflush(stdout); continue; }
         try {
           double ps = 0, ds = 0;
           if (multi) {
@@ -386,8 +422,13 @@ int main(int argc, char** argv) {
       std::vector<std::pair<uint64_t, size_t>> ids;
       std::string line;
       while (std::getline(std::cin, line)) {
-        std::vector<int32_t> f = parse_ids(line);
-        if (f.size() < 2) continue;
+        std::vector<int32_t> f;
+        std::string why;
+        if (!parse_ids_checked(line, f, why) || f.size() < 2 || f[0] < 1 ||
+            !(why = bad_token(std::vector<int32_t>(f.begin() + 1, f.end()), cfg.vocab_size)).empty()) {
+          std::fprintf(stderr, "skipped a request line: %s\n", why.empty() ? "expected <max_new_tokens> tok..." : why.c_str());
+          continue;
+        }
         ids.emplace_back(sched.submit(std::vector<int32_t>(f.begin() + 1, f.end()), f[0]), f.size() - 1);
       }
       for (auto& [id, n_prompt] : ids) {
