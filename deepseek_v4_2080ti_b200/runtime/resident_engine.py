@@ -80,7 +80,10 @@ class ResidentEngine:
             s, toks = self._slot(cmd), self._tokens(cmd)
             if not toks:
                 raise ValueError("prefill needs at least one token")
-            tok = self._scalar(rt.prefill(s, self.to_ids(toks), int(cmd.get("chunk", self.chunk))))
+            chunk = cmd.get("chunk", self.chunk)
+            if isinstance(chunk, bool) or not isinstance(chunk, int) or not 1 <= chunk <= 1 << 20:
+                raise ValueError("chunk must be a whole number of tokens in [1, 1048576]")
+            tok = self._scalar(rt.prefill(s, self.to_ids(toks), chunk))
             self.stats["prefill_tokens"] += len(toks)
             return {"token": tok, "length": int(rt.lengths[s])}
         if op == "decode":
