@@ -199,6 +199,15 @@ def make_handler(state: ServerState):
                     self._json(200 if ok else 503, h.as_dict())
                 elif path == "/metrics":
                     state.metrics.set("uptime_seconds", time.time() - state.started)
+                    # the runtime's own counters (speculation rounds / accepted drafts, prefix-cache hits, collective
+                    # recoveries, swap traffic ...) as gauges named runtime_<key>
+                    try:
+                        details = state.backend.health().details or {}
+                    except Exception:
+                        details = {}
+                    for k, v in details.items():
+                        if isinstance(v, (int, float)) and not isinstance(v, bool):
+                            state.metrics.set("runtime_" + "".join(c if c.isalnum() else "_" for c in str(k)), float(v))
                     self._text(200, state.metrics.render())
                 elif path == "/v1/models":
                     self._json(200, {"object": "list", "data": [{"id": state.model_name, "object": "model",

@@ -178,3 +178,11 @@ def test_malformed_bodies_are_client_errors(server):
     assert raw(post(b'{"prompt": [1.5, -3], "max_tokens": 2}')) == 400
     assert raw(post(b'{"prompt": [1], "max_tokens": "y"}')) == 400
     assert raw(post(body)) == 200
+
+
+def test_runtime_counters_are_exported_as_gauges(server):
+    port, _ = server
+    call(port, "POST", "/v1/completions", {"prompt": "A", "max_tokens": 3})
+    st, raw = call(port, "GET", "/metrics")
+    text = raw.decode()
+    assert st == 200 and "pocketllm_runtime_requests 1" in text and "pocketllm_runtime_completion_tokens 3" in text
