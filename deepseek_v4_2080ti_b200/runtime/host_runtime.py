@@ -7,7 +7,8 @@ GPU, on small models: the oracle keeps no caches and re-runs the whole sequence 
 
 A decode call hands out the next token of the last verified block and runs a new draft / verify round only when the
 block is used up (the same contract as the GPU speculative adapter); greedy acceptance, so the tokens are exactly the
-oracle's greedy tokens.  The learned drafters come from ``backend_options["drafter"]`` (a checkpoint directory, read by
+oracle's greedy tokens.  ``backend_options["spec_gate"]`` puts the adaptive draft-length gate in front of every round.
+The learned drafters come from ``backend_options["drafter"]`` (a checkpoint directory, read by
 ``load_dspark`` / ``load_dflash2``); a ``synthetic:`` model without that option gets a seeded random drafter of a small
 shape, which proposes poorly but exercises the same code.
 
@@ -43,9 +44,10 @@ class HostQwenAdapter:
     supports_prefix_cache = False
 
     def __init__(self, oracle: QwenHybridRef, max_context: int, max_slots: int = 1, method: str | None = None,
-                 block: int = 4, make_drafter=None, eos_token_ids=()):
+                 block: int = 4, make_drafter=None, eos_token_ids=(), gate=None):
         self.oracle, self.max_context, self.max_slots = oracle, int(max_context), int(max_slots)
         self.method, self.block, self._make_drafter = method, max(1, int(block)), make_drafter
+        self.gate = gate                       # SpecGate: how much of each block to verify, learnt from acceptance
         self.eos_token_ids = tuple(eos_token_ids)
         self.vocab_size = int(oracle.cfg.vocab_size)
         self.speculative_methods = (method,) if method else ()
@@ -88,8 +90,19 @@ class HostQwenAdapter:
         committed = st.context[-1]
         room = self.max_context - len(st.context) - 1
         draft: list[int] = []
+        conf: list[float] = []
+        gate = self.gate
         if st.drafter is not None and room > 1:
-            draft, _ = st.drafter.propose(st.context, min(self.block, room - 1))
+            if gate is not None and st.last_row is not None and not gate.should_draft(st.last_row.float().topk(2).values.tolist()):
+                gate.note_skipped(by_margin=True)               # the target itself is unsure: a plain step
+            else:
+                draft, conf = st.drafter.propose(st.context, min(self.block, room - 1))
+                if gate is not None and draft:
+                    pad = list(conf) + [conf[-1]] * (gate.block - len(draft))
+                    n = min(gate.choose(pad), len(draft))
+                    if n == 0:
+                        gate.note_skipped()
+                    draft, conf = draft[:n], list(conf)[:n]
         if not draft:
             logits = self._forward(st, [committed])
             st.queue.append((int(logits[-1].argmax()), logits[-1]))
@@ -103,6 +116,8 @@ class HostQwenAdapter:
         self.rounds += 1
         self.drafted += len(draft)
         self.accepted += a
+        if gate is not None:
+            gate.observe(conf, a, len(draft))
         st.queue.extend((t, ver[i]) for i, t in enumerate(draft[:a] + [pred[a]]))
         if a < len(draft):                                   # undo the rejected tail: the oracle's state is its token list
             st.target.restore(snap)
@@ -121,9 +136,12 @@ class HostQwenAdapter:
         return out
 
     def stats(self) -> dict:
-        return {"target_passes": self.passes, "spec_rounds": self.rounds, "spec_drafted": self.drafted,
-                "spec_accepted": self.accepted,
-                "spec_accept_rate": round(self.accepted / self.drafted, 4) if self.drafted else 0.0}
+        out = {"target_passes": self.passes, "spec_rounds": self.rounds, "spec_drafted": self.drafted,
+               "spec_accepted": self.accepted,
+               "spec_accept_rate": round(self.accepted / self.drafted, 4) if self.drafted else 0.0}
+        if self.gate is not None:
+            out.update({"spec_gate_" + k: v for k, v in self.gate.stats().items() if isinstance(v, (int, float))})
+        return out
 
 
 def _tap_layers(cfg: qh.QwenHybridConfig, n: int = 2) -> list[int]:
@@ -185,4 +203,8 @@ def build_host_adapter(args, cfg: qh.QwenHybridConfig, state, max_context: int, 
             viterbi = str(opts.get("viterbi", "0")).lower() in ("1", "true", "yes")
             make = lambda tgt: df.QwenDFlash2Drafter(tgt, df.QwenDFlash2Ref(dcfg, w, emb, head, max_context=max_context,
                                                                               viterbi=viterbi))
-    return HostQwenAdapter(oracle, max_context, max_slots, method, block, make)
+    gate = None
+    if method and str(opts.get("spec_gate", "0")).lower() in ("1", "true", "yes", "on"):
+        from ..components.spec_gate import SpecGate
+        gate = SpecGate.from_env(block)                      # constants from POCKETLLM_SPEC_GATE_* when set
+    return HostQwenAdapter(oracle, max_context, max_slots, method, block, make, gate=gate)

@@ -68,3 +68,14 @@ def test_drafter_checkpoint_from_a_directory_and_refusals(tmp_path, greedy):
                        backend_options={"drafter": str(tmp_path)})).generate([PROMPT], SamplingParams(max_tokens=1))
     with pytest.raises(UnsupportedFeatureError, match="greedy"):
         LLM(EngineArgs(model="synthetic:qwen-tiny", device="cpu")).generate([PROMPT], SamplingParams(max_tokens=2, temperature=0.8))
+
+
+@pytest.mark.parametrize("method", ["mtp", "dspark"])
+def test_the_adaptive_gate_changes_the_passes_not_the_tokens(method, greedy):
+    llm = LLM(EngineArgs(model="synthetic:qwen-tiny", device="cpu", max_model_len=128, speculative_method=method,
+                         speculative_tokens=3, backend_options={"spec_gate": "1"}))
+    (res,) = llm.generate([PROMPT], SamplingParams(max_tokens=9))
+    assert res.token_ids == greedy
+    st = llm.backend.runtime.stats()
+    assert any(k.startswith("spec_gate_") for k in st) and st["spec_gate_rounds"] + st.get("spec_gate_skipped", 0) >= 1
+    llm.close()
