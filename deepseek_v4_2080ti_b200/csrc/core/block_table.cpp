@@ -43,10 +43,15 @@ bool BlockTable::share_prefix(int dst, int src, int n_blocks) {
 bool BlockTable::adopt(int dst, const int32_t* blocks, int n_blocks) {
   if (dst < 0 || dst >= max_slots_) throw std::out_of_range("BlockTable: slot");
   if (counts_[dst] != 0 || n_blocks < 0 || n_blocks > max_blocks_) return false;
-  for (int i = 0; i < n_blocks; ++i) {
-    pool_.retain(blocks[i]);
-    image_[static_cast<size_t>(dst) * max_blocks_ + i] = blocks[i];
+  // all or nothing: a block that is not live (a stale cache entry, a foreign id) leaves the row and the pool untouched
+  int held = 0;
+  try {
+    for (; held < n_blocks; ++held) pool_.retain(blocks[held]);
+  } catch (const std::invalid_argument&) {
+    for (int i = 0; i < held; ++i) pool_.release(blocks[i]);
+    return false;
   }
+  for (int i = 0; i < n_blocks; ++i) image_[static_cast<size_t>(dst) * max_blocks_ + i] = blocks[i];
   counts_[dst] = n_blocks;
   dirty_[dst] = 1;
   return true;

@@ -94,12 +94,14 @@ void OpenAIServer::stop() {
     if (thread_.joinable()) thread_.join();
     return;
   }
+  // wake the accept thread, let it leave, and only then give the descriptor back: closing it first would let the
+  // thread poll or accept on a number that another socket of the process may already have been given
+  if (listen_fd_ >= 0) ::shutdown(listen_fd_, SHUT_RDWR);
+  if (thread_.joinable()) thread_.join();
   if (listen_fd_ >= 0) {
-    ::shutdown(listen_fd_, SHUT_RDWR);
     ::close(listen_fd_);
     listen_fd_ = -1;
   }
-  if (thread_.joinable()) thread_.join();
   {
     // no new connections from here on; unblock the ones that sit in recv / send
     std::lock_guard<std::mutex> lock(conn_mu_);
