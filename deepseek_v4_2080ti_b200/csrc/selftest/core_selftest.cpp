@@ -24,6 +24,7 @@
 #include "../core/openai_server.hpp"
 #include "../core/safetensors_reader.hpp"
 #include "../core/sampler.hpp"
+#include "../core/tokenizer.hpp"
 
 #include <arpa/inet.h>
 #include <cstring>
@@ -389,7 +390,31 @@ static void test_file_readers() {
   }
 }
 
+// ---- tokenizer: arbitrary bytes in, arbitrary ids back; merges that name unknown pieces are ignored
+static void test_tokenizer() {
+  std::vector<std::string> toks;
+  for (int c = 33; c < 127; ++c) toks.emplace_back(1, char(c));
+  toks.insert(toks.end(), {"\xC4\xA0", "hi", "th", "the", "<eos>"});
+  const std::vector<std::string> merges = {"h i", "t h", "th e", "zz qq", "", "a", "a b c"};
+  const Tokenizer t = Tokenizer::from_vocab(toks, merges, -1, int32_t(toks.size()) - 1);
+  CHECK(t.find("the") >= 0 && t.find("nope") == -1);
+  const std::vector<int32_t> ids = t.encode_basic("hi the");
+  CHECK(!ids.empty() && t.decode(ids).find("hi") != std::string::npos);
+  std::mt19937 rng(3);
+  for (int i = 0; i < 300; ++i) {
+    std::string text(rng() % 64, '\0');
+    for (char& c : text) c = char(rng() & 0xFF);
+    const std::vector<int32_t> e = t.encode_basic(text, i & 1);
+    for (int32_t id : e) CHECK(id >= 0 && id < int32_t(toks.size()));
+    (void)t.decode(e);
+    std::vector<int32_t> wild(rng() % 16);
+    for (int32_t& id : wild) id = int32_t(rng());
+    (void)t.decode(wild);                                    // ids outside the vocabulary decode to nothing
+  }
+}
+
 int main() {
+  test_tokenizer();
   test_blocks();
   test_scheduler();
   test_cmd_channel();
