@@ -170,6 +170,19 @@ def build_selftest(sanitizer: str = "") -> Path:
     return exe
 
 
+def build_cpu_selftest(sanitizer: str = "") -> Path:
+    """Memory-safety self-test of the AVX2 host kernels (csrc/selftest/cpu_selftest.cpp with csrc/cpu), plain or under
+    AddressSanitizer + UBSan: ``bin/cpu_selftest[_asan]``."""
+    BIN.mkdir(exist_ok=True)
+    flags = {"": [], "address": ["-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-g"]}[sanitizer]
+    exe = BIN / ("cpu_selftest" + ("_asan" if sanitizer else ""))
+    srcs = sorted((CSRC / "cpu").glob("*.cpp")) + [CSRC / "selftest" / "cpu_selftest.cpp"]
+    cxx = "/usr/bin/g++" if sanitizer and os.path.exists("/usr/bin/g++") else CXX
+    if (not exe.exists()) or any(s.stat().st_mtime > exe.stat().st_mtime for s in srcs):
+        _run([cxx, "-std=c++17", "-O2", "-mavx2", "-mfma", *flags, "-I", str(CSRC), *map(str, srcs), "-o", str(exe), "-pthread"])
+    return exe
+
+
 def build_cpu() -> Path | None:
     """AVX2 multi-threaded host kernels (csrc/cpu): the CPU path for FP4 and INT8 routed experts."""
     OBJ.mkdir(exist_ok=True)
