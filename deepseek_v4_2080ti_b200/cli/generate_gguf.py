@@ -19,6 +19,9 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="generate_gguf")
     ap.add_argument("--gguf", required=True)
     ap.add_argument("--token-ids", default="")
+    ap.add_argument("--runtime-option", action="append", default=[], metavar="KEY=VALUE",
+                    help="family-specific runtime option, repeatable (deepseek4: dspark=PATH|synthetic, dspark_block=N, "
+                         "spec_gate=1, flashmemory=CKPT, flashmemory_ensemble=max|mean, kv_swap_chunks=N, kv_swap_chunk_entries=G)")
     ap.add_argument("--prompt", default="", help="text, encoded with the checkpoint's own BPE tokenizer")
     ap.add_argument("--max-new-tokens", type=int, default=32)
     ap.add_argument("--max-context", type=int, default=4096)
@@ -48,7 +51,13 @@ def main(argv=None) -> int:
     if world > 1:
         comm = tp.TPComm() if a.nccl else tp.PeerComm(slot_elems=max(1 << 20, a.prefill_chunk_tokens * 8192))
     t0 = time.time()
-    cfg, rt = spec.build_runtime(b, dev, rank, world, comm, max_slots=1, max_context=a.max_context)
+    extra = {}
+    for item in a.runtime_option:
+        if "=" not in item:
+            raise SystemExit(f"--runtime-option {item!r}: expected KEY=VALUE")
+        k, v = item.split("=", 1)
+        extra[k.strip()] = v.strip()
+    cfg, rt = spec.build_runtime(b, dev, rank, world, comm, max_slots=1, max_context=a.max_context, **extra)
     load_s = time.time() - t0
     vocab = int(getattr(cfg, "vocab_size", 0) or getattr(cfg, "vocab", 0) or 0)
     bad = [t for t in ids if t < 0 or (vocab and t >= vocab)]
@@ -71,6 +80,8 @@ def main(argv=None) -> int:
     rt.free(slot)
     if rank == 0:
         print("tokens=" + ",".join(map(str, out)))
+        if hasattr(rt, "stats"):
+            print("runtime_stats " + " ".join(f"{k}={v}" for k, v in rt.stats().items()))
         print(f"RESULT family={spec.architecture} world={world} load_seconds={load_s:.2f} prompt_tokens={len(ids)} "
               f"prefill_tps={len(ids) / max(t1 - t0, 1e-9):.2f} decode_tps={(len(out) - 1) / max(t2 - t1, 1e-9):.2f}", flush=True)
     if world > 1:

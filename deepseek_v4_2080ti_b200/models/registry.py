@@ -251,11 +251,41 @@ class _V4HostAdapter:
         return self._tok(self.rt.forward(ids.detach().cpu()))
 
 
+class _V4SpecHostAdapter(_V4HostAdapter):
+    """The block runtime with the DSpark block drafter in front of it (``models/v4_dspark_ref.py``): ``decode`` hands out
+    one committed token per call and runs a new draft / verify round when the committed ones are used up.  Greedy: the
+    tokens are the plain runtime's tokens."""
+
+    def __init__(self, loop, device):
+        super().__init__(loop.t, device)
+        self.loop, self.stream, self.pos = loop, [], 0
+
+    def _one(self, tok: int):
+        import torch
+        return torch.tensor([tok], dtype=torch.int64, device=self.device)
+
+    def prefill(self, slot: int, ids, chunk: int = 0):
+        self.stream, self.pos = [self.loop.prefill(ids.detach().cpu())], 1
+        return self._one(self.stream[0])
+
+    def decode(self, slots, ids):
+        while self.pos >= len(self.stream):
+            toks, _ = self.loop.step()                    # [the pending token, accepted drafts ...]; a new one is pending
+            self.stream += toks[1:] + [self.loop.committed]
+        self.pos += 1
+        return self._one(self.stream[self.pos - 1])
+
+    def stats(self) -> dict:
+        lp = self.loop
+        return {"spec_rounds": lp.rounds, "spec_drafted": lp.drafted, "spec_accepted": lp.accepted, "target_steps": lp.target_steps}
+
+
 def _v4_runtime(bundle, device="cpu", rank=0, world=1, comm=None, **kw):
     """Long-context options, as keywords or through the environment switches the reference's engine reads
     (docs/FLASHMEMORY_1M_CONTEXT.md there): ``flashmemory`` / ``POCKETLLM_GGUF_FLASHMEMORY_CKPT`` (retriever checkpoint;
     ensemble ``POCKETLLM_GGUF_FLASHMEMORY_ENSEMBLE`` = max | mean) and ``kv_swap_chunks`` /
-    ``POCKETLLM_GGUF_KV_SWAP=1`` + ``POCKETLLM_GGUF_KV_SWAP_GPU_CHUNKS`` (working-set groups of compressed rows)."""
+    ``POCKETLLM_GGUF_KV_SWAP=1`` + ``POCKETLLM_GGUF_KV_SWAP_GPU_CHUNKS`` (working-set groups of compressed rows).
+    Speculation: ``dspark`` / ``POCKETLLM_GGUF_DSPARK_CKPT`` (drafter file or "synthetic"), ``dspark_block``, ``spec_gate``."""
     import os
     from . import v4_gguf as vg
     from .v4_block_ref import V4BlockRef
@@ -274,6 +304,27 @@ def _v4_runtime(bundle, device="cpu", rank=0, world=1, comm=None, **kw):
                                      use_max=ensemble == "max", swap_device_chunks=chunks,
                                      chunk_entries=int(kw.get("kv_swap_chunk_entries", 4)))
         return cfg, _V4HostAdapter(rt, device)
+    drafter = kw.get("dspark") or os.environ.get("POCKETLLM_GGUF_DSPARK_CKPT")
+    if drafter:
+        # ``dspark``: a safetensors file of ``dspark.*`` tensors (metadata ``target_layer_ids``: "1,2"), or "synthetic"
+        from ..components.spec_gate import SpecGate
+        from . import v4_dspark_ref as vd
+        block = int(kw.get("dspark_block", 4))
+        if drafter == "synthetic":
+            layer_ids = tuple(sorted({max(0, cfg.n_layers // 2 - 1), cfg.n_layers - 1}))
+            dw = vd.synth_dspark_weights(cfg, n_stages=2, n_target=len(layer_ids), seed=0)
+        else:
+            from ..formats.safetensors_io import SafetensorsFile
+            f = SafetensorsFile(drafter)
+            dw = {k: f.get(k) for k in f.keys()}
+            raw = kw.get("dspark_target_layers") or f.metadata.get("target_layer_ids", "")
+            layer_ids = tuple(int(x) for x in str(raw).replace(" ", "").split(",") if x)
+            if not layer_ids or max(layer_ids) >= cfg.n_layers or "dspark.main_proj" not in dw \
+                    or dw["dspark.main_proj"].shape[1] != cfg.dim * len(layer_ids):
+                raise ValueError("the DSpark drafter file does not match this model (target_layer_ids / dspark.main_proj)")
+        gate = SpecGate.from_env(block) if str(kw.get("spec_gate", "0")) in ("1", "true") else None
+        loop = vd.DSparkLoop(vd.DSparkRef(V4BlockRef(cfg, weights), dw, layer_ids, block=block), gate)
+        return cfg, _V4SpecHostAdapter(loop, device)
     return cfg, _V4HostAdapter(V4BlockRef(cfg, weights), device)
 
 

@@ -192,3 +192,36 @@ def test_long_context_options_of_the_registered_family(tmp_path, monkeypatch):
     safetensors_io.write_file(ck, lc.synth_retriever_weights(cfg, n_retrievers=1, seed=4))
     with pytest.raises(ValueError, match="does not fit a model of width"):
         lc.load_retrievers(ck, cfg.dim + 16)
+
+
+def test_block_drafter_in_front_of_the_registered_family(tmp_path):
+    from deepseek_v4_2080ti_b200.formats import safetensors_io
+    from deepseek_v4_2080ti_b200.models import registry, v4_dspark_ref as vd
+    cfg = _cfg()
+    w = synth_weights(cfg, seed=9)
+    path = str(tmp_path / "v4s.gguf")
+    v4_gguf.write_gguf(path, cfg, w, "F32")
+    b = G.read_bundle(path)
+    spec = registry.detect(b)
+    prompt = torch.arange(5, 21, dtype=torch.int32) % cfg.vocab_size
+    want = V4BlockRef(cfg, w).generate(prompt, 9)
+
+    def run(rt, n=9):
+        slot = rt.allocate()
+        tok = rt.prefill(slot, prompt)
+        out = [int(tok)]
+        for _ in range(n - 1):
+            tok = rt.decode([slot], tok.to(torch.int32))
+            out.append(int(tok))
+        return out
+    _, rt = spec.build_runtime(b, "cpu", dspark="synthetic", dspark_block=3)
+    assert run(rt) == want and rt.stats()["spec_rounds"] > 0 and rt.stats()["spec_drafted"] >= rt.stats()["spec_accepted"]
+    assert run(rt) == want                                           # a second sequence on the same adapter
+    layer_ids = (0, cfg.n_layers - 1)
+    dw = vd.synth_dspark_weights(cfg, n_stages=1, n_target=2, seed=4)
+    ck = str(tmp_path / "dspark.safetensors")
+    safetensors_io.write_file(ck, dw, metadata={"target_layer_ids": ",".join(map(str, layer_ids))})
+    _, rt = spec.build_runtime(b, "cpu", dspark=ck, spec_gate="1")
+    assert run(rt) == want
+    with pytest.raises(ValueError, match="does not match"):
+        spec.build_runtime(b, "cpu", dspark=ck, dspark_target_layers="0")
