@@ -131,6 +131,7 @@ class _MlaSlotAdapter:
 
     def __init__(self, rt):
         self.rt = rt
+        self.cfg = getattr(rt, "cfg", None)               # front ends read the vocabulary size from it
         from ..ops import basic
         self._argmax = basic.argmax
 
@@ -231,7 +232,7 @@ class _V4HostAdapter:
     single_sequence = True
 
     def __init__(self, rt, device):
-        self.rt, self.device = rt, device
+        self.rt, self.device, self.cfg = rt, device, rt.cfg
 
     def allocate(self) -> int:
         self.rt.reset()
@@ -249,6 +250,10 @@ class _V4HostAdapter:
 
     def decode(self, slots, ids):
         return self._tok(self.rt.forward(ids.detach().cpu()))
+
+    def stats(self) -> dict:
+        swap = getattr(self.rt, "swap_stats", None)
+        return {"kv_swap_" + k: v for k, v in swap().items()} if callable(swap) else {}
 
 
 class _V4SpecHostAdapter(_V4HostAdapter):

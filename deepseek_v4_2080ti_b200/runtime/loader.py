@@ -443,7 +443,11 @@ class GgufRuntimeAdapter:
         return results
 
     def stats(self) -> dict:
-        return {"slots_free": self.max_slots - len(self._active), "slots_total": self.max_slots}
+        out = {"slots_free": self.max_slots - len(self._active), "slots_total": self.max_slots}
+        inner = getattr(self.rt, "stats", None)
+        if callable(inner):                                  # speculation / swap counters of runtimes that keep them
+            out.update({k: v for k, v in inner().items() if isinstance(v, (int, float))})
+        return out
 
 
 def _is_gguf(model: str) -> bool:
@@ -494,7 +498,11 @@ def load_runtime(args):
         from pocketllm.api.errors import ConfigurationError
         raise ConfigurationError("speculative_method is served by the Qwen-style hybrid runtime only")
     dev = _device(args)
-    torch.cuda.set_device(dev)
+    if dev.type == "cuda":
+        torch.cuda.set_device(dev)
+    elif not _is_gguf(args.model):
+        from pocketllm.api.errors import ConfigurationError
+        raise ConfigurationError(f"device {dev} cannot run this model")
     comm = None
     channel = None
     if world > 1:
@@ -530,7 +538,14 @@ def load_runtime(args):
         report = spec.validate(bundle)
         if not report.ok:
             raise ValueError(f"{model}: missing {report.missing[:4]} unsupported {list(report.unsupported)[:4]}")
-        _, rt = spec.build_runtime(bundle, dev, rank, world, comm, max_slots=slots, max_context=max_ctx)
+        if dev.type != "cuda" and spec.architecture != "deepseek4":
+            from pocketllm.api.errors import ConfigurationError
+            raise ConfigurationError(f"the {spec.architecture} family needs a GPU; only deepseek4 files run on the host")
+        # family-specific runtime options travel as backend options (deepseek4: dspark=..., flashmemory=..., kv_swap_chunks=...)
+        extra = {k: v for k, v in (getattr(args, "backend_options", None) or {}).items()
+                 if k in ("dspark", "dspark_block", "dspark_target_layers", "spec_gate", "flashmemory", "flashmemory_ensemble",
+                          "kv_swap_chunks", "kv_swap_chunk_entries")} if spec.architecture == "deepseek4" else {}
+        _, rt = spec.build_runtime(bundle, dev, rank, world, comm, max_slots=slots, max_context=max_ctx, **extra)
         try:
             family = family_from_architecture(spec.architecture)
         except ValueError:

@@ -225,3 +225,23 @@ def test_block_drafter_in_front_of_the_registered_family(tmp_path):
     assert run(rt) == want
     with pytest.raises(ValueError, match="does not match"):
         spec.build_runtime(b, "cpu", dspark=ck, dspark_target_layers="0")
+
+
+def test_public_api_serves_the_host_family_with_its_options(tmp_path):
+    from pocketllm import LLM, ConfigurationError, EngineArgs, SamplingParams
+    cfg = _cfg()
+    w = synth_weights(cfg, seed=7)
+    path = str(tmp_path / "v4api.gguf")
+    v4_gguf.write_gguf(path, cfg, w, "F32")
+    prompt = [3, 4, 5, 6, 7, 8]
+    want = V4BlockRef(cfg, w).generate(torch.tensor(prompt), 6)
+    for opts, key in (({}, None), ({"dspark": "synthetic", "dspark_block": 3}, "spec_rounds"),
+                      ({"kv_swap_chunks": 8, "kv_swap_chunk_entries": 2}, "kv_swap_d2h_bytes")):
+        llm = LLM(EngineArgs(model=path, device="cpu", max_model_len=64, backend_options=opts))
+        res = llm.generate([{"prompt_token_ids": prompt}], SamplingParams(max_tokens=6))[0]
+        assert res.token_ids == want, opts
+        if key:                                               # the pool's counters restart with every sequence
+            assert key in llm.health().details and (key.startswith("kv_swap") or llm.health().details[key] > 0)
+        with pytest.raises(ConfigurationError, match="not a token id"):
+            llm.generate([{"prompt_token_ids": [cfg.vocab_size]}], SamplingParams(max_tokens=1))
+        llm.close()
