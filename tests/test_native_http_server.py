@@ -153,14 +153,17 @@ def test_sidecar_client_and_chat_through_the_server():
                 os.environ["PYTHONPATH"] = env_backup
 
 
-def _raw(port, data, timeout=3.0):
+def _raw(port, data, timeout=10.0):
     import socket
-    s = socket.create_connection(("127.0.0.1", port), timeout=timeout)
     try:
-        s.sendall(data)
+        s = socket.create_connection(("127.0.0.1", port), timeout=timeout)
+    except OSError:
+        return b""
+    try:
         try:
+            s.sendall(data)
             s.shutdown(socket.SHUT_WR)
-        except OSError:
+        except OSError:                                     # the server may answer and close before the body is out
             pass
         out = b""
         while True:
