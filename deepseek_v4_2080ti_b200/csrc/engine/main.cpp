@@ -179,8 +179,14 @@ bool parse(int argc, char** argv, Args& a) {
     else if (arg == "--qwen-top-p") a.sampling.top_p = float(std::atof(val("--qwen-top-p")));
     else if (arg == "--qwen-seed") a.seed = std::strtoull(val("--qwen-seed"), nullptr, 10);
     else if (arg == "--qwen-no-prefix-cache") a.prefix_interval = 0;
-    else if (arg == "--prefix-cache-interval") a.prefix_interval = std::atoi(val("--prefix-cache-interval"));
-    else if (arg == "--prefix-cache-entries") a.prefix_entries = std::atoi(val("--prefix-cache-entries"));
+    else if (arg == "--prefix-cache-interval" || arg == "--qwen-snapshot-interval") a.prefix_interval = std::atoi(val(arg.c_str()));
+    else if (arg == "--prefix-cache-entries" || arg == "--qwen-max-snapshots") a.prefix_entries = std::atoi(val(arg.c_str()));
+    else if (arg == "--qwen-mtp" || arg == "--qwen-mtp-adaptive" || arg == "--qwen-dspark" || arg == "--qwen-dflash2" ||
+             arg == "--qwen-mtp-tokens" || arg == "--qwen-attention-window" || arg == "--qwen-attention-sink-tokens")
+      // options of the reference executable that this one leaves to the Python runtime: say where they live
+      throw std::invalid_argument(arg + " is not available in this executable: speculative decoding and windowed attention are "
+                                  "served by `pocketllm serve --speculative-method mtp|ngram|dspark|dflash2 --speculative-tokens N "
+                                  "--attention-window W --attention-sink-tokens S`");
     else if (arg == "-h" || arg == "--help") return false;
     else throw std::runtime_error("unknown argument " + arg);
   }

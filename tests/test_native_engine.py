@@ -120,6 +120,12 @@ def test_bad_arguments_exit_non_zero():
     assert r.returncode != 0 and "bf16 cache only" in r.stderr
     assert "unknown kv cache dtype" in _run(["--ckpt", "x", "--kv-cache-dtype", "fp3"]).stderr
     assert _run([]).returncode == 2
+    for flag in ("--qwen-dspark", "--qwen-mtp", "--qwen-attention-window"):      # options the reference executable has
+        r = _run(["--ckpt", "x", flag])
+        assert r.returncode != 0 and "pocketllm serve --speculative-method" in r.stderr, flag
+    with tempfile.TemporaryDirectory() as d:
+        # the reference's names for the snapshot settings are accepted
+        assert "unknown argument" not in _run(["--ckpt", d, "--qwen-snapshot-interval", "64", "--qwen-max-snapshots", "4", "--dump-config"]).stderr
     with tempfile.TemporaryDirectory() as d:
         r = _run(["--ckpt", d, "--dump-config"])
         assert r.returncode == 1 and "pocketllm_engine:" in r.stderr
