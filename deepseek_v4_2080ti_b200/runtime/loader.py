@@ -466,8 +466,13 @@ def _load_host(args):
     from pocketllm.api.errors import ConfigurationError
     from pocketllm.backends.native_backend import NullChannel
     from .host_runtime import build_host_adapter
-    if args.tensor_parallel_size != 1:
-        raise ConfigurationError("the host path runs on one rank")
+    world, rank = args.tensor_parallel_size, args.tensor_parallel_rank
+    channel = None
+    if world > 1:
+        # replicated ranks: every rank holds the whole (small) model and mirrors rank 0's commands over the command
+        # channel - no collective is needed, but the supervisor, the fan-out and the worker loop run as on the GPUs
+        base = os.environ.get("POCKETLLM_NCCL_ID_PATH") or f"/tmp/pocketllm-{os.environ.get('MASTER_PORT', '0')}"
+        channel = Channel(base, rank, world)
     model = args.model
     if model.startswith("synthetic:"):
         if "tiny" not in model:
@@ -479,7 +484,7 @@ def _load_host(args):
         cfg = qh.QwenHybridConfig.from_json(args.config_path or os.path.join(args.checkpoint_dir, "config.json"))
         state = safetensors_io.read_checkpoint(args.checkpoint_dir)
     max_ctx = args.max_model_len or 2048
-    return build_host_adapter(args, cfg, state, max_ctx, max(1, args.max_batch_size)), None, NullChannel()
+    return build_host_adapter(args, cfg, state, max_ctx, max(1, args.max_batch_size)), None, channel or NullChannel()
 
 
 def load_runtime(args):
