@@ -92,3 +92,43 @@ def test_two_host_ranks_under_the_supervisor_serve_and_stop(tmp_path):
     # the tokens: decode the byte-level text back through the same fallback tokenizer the server used
     from pocketllm.protocol.prompt import TokenizerHandle
     assert TokenizerHandle.load(None).decode(want) == out["choices"][0]["text"]
+
+
+@pytest.mark.timeout(300)
+def test_a_rank_that_dies_takes_the_service_down(tmp_path):
+    """Failure made on the host: one rank process is killed between requests; the supervisor notices, ends the other
+    rank and exits non-zero, so whatever restarts services sees the failure."""
+    port = _free_port()
+    log = open(tmp_path / "serve.log", "wb")
+    proc = subprocess.Popen([sys.executable, "-m", "pocketllm", "serve", "synthetic:qwen-tiny", "--device", "cpu", "-tp", "2",
+                             "--port", str(port), "--max-model-len", "64", "--tensor-parallel-rendezvous-dir", str(tmp_path),
+                             "--tensor-parallel-startup-timeout", "120", "--tensor-parallel-shutdown-timeout", "5"],
+                            stdout=log, stderr=subprocess.STDOUT, env=dict(os.environ, PYTHONPATH=ROOT), start_new_session=True)
+    try:
+        deadline = time.time() + 150
+        while time.time() < deadline:
+            assert proc.poll() is None, (tmp_path / "serve.log").read_text()[-2000:]
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/ready", timeout=2) as r:
+                    if r.status == 200:
+                        break
+            except OSError:
+                time.sleep(0.5)
+        assert _post(port, {"prompt": PROMPT, "max_tokens": 2})["usage"]["completion_tokens"] == 2
+        kids = [int(k) for k in subprocess.run(["ps", "-o", "pid=", "--ppid", str(proc.pid)], capture_output=True, text=True).stdout.split()]
+        assert len(kids) == 2
+        # the worker rank is the one that does not listen on the port: kill the child whose command line says rank 1,
+        # or simply the younger one (rank 1 is started after rank 0)
+        os.kill(max(kids), signal.SIGKILL)
+        code = proc.wait(timeout=60)
+        assert code != 0
+        t0 = time.time()
+        while any(_alive(k) for k in kids) and time.time() - t0 < 30:
+            time.sleep(0.2)
+        assert not any(_alive(k) for k in kids)
+        with pytest.raises(OSError):
+            urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=2)
+    finally:
+        if proc.poll() is None:
+            os.killpg(proc.pid, signal.SIGKILL)
+        log.close()
