@@ -36,7 +36,8 @@ class Channel:
             else:
                 words.append(int(p))
         if not self._ch.broadcast(words):
-            raise RuntimeError("a worker rank closed its command channel")
+            from pocketllm.api.errors import BackendUnavailableError     # 503 to the client: the group is going down
+            raise BackendUnavailableError("a worker rank closed its command channel")
 
     def recv(self):
         w = self._ch.receive(-1)
