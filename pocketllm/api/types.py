@@ -193,7 +193,9 @@ class SamplingParams:
                 stop=_stops(pick("stop")),
                 n=int(pick("n", default=1)),
                 logprobs=bool(pick("logprobs", default=False)),
-                top_logprobs=None if pick("top_logprobs") is None else int(pick("top_logprobs")),
+                # the completions API gives the number of alternatives as an integer "logprobs"; chat uses "top_logprobs"
+                top_logprobs=int(pick("top_logprobs")) if pick("top_logprobs") is not None else
+                (int(pick("logprobs")) if isinstance(pick("logprobs"), int) and not isinstance(pick("logprobs"), bool) else None),
                 response_format=pick("response_format"),
             )
         except (TypeError, ValueError) as exc:

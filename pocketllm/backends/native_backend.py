@@ -333,8 +333,10 @@ class NativeBackend(BackendBase):
                 yield item
             elif isinstance(item, GenerationResult):
                 tail = item.text[sent["n"]:] if len(item.text) > sent["n"] else ""
-                yield TokenEvent(request.request_id, None, tail, item.finish_reason, item.usage,
-                                 {"timings": item.timings.as_dict()})
+                meta = {"timings": item.timings.as_dict()}
+                if item.logprobs:
+                    meta["logprobs"] = item.logprobs          # a stream delivers them with its last event
+                yield TokenEvent(request.request_id, None, tail, item.finish_reason, item.usage, meta)
                 return
             else:
                 raise item

@@ -325,7 +325,11 @@ def make_handler(state: ServerState):
                             if calls:
                                 emit(chunk({"tool_calls": [dict(c, index=i) for i, c in enumerate(calls)]}, None))
                                 finish = "tool_calls"
-                        emit(chunk({} if is_chat else "", finish, ev.usage.as_dict() if ev.usage else None))
+                        last = chunk({} if is_chat else "", finish, ev.usage.as_dict() if ev.usage else None)
+                        if ev.metadata.get("logprobs"):     # asked for with "logprobs": delivered once, with the closing chunk
+                            shim = GenerationResult(req.request_id, logprobs=ev.metadata["logprobs"])
+                            last["choices"][0]["logprobs"] = _chat_logprobs(shim) if is_chat else _completion_logprobs(shim)
+                        emit(last)
                     ev = next(events, None)
                 emit(b"[DONE]")
             except (BrokenPipeError, ConnectionResetError):

@@ -79,3 +79,27 @@ def test_the_adaptive_gate_changes_the_passes_not_the_tokens(method, greedy):
     st = llm.backend.runtime.stats()
     assert any(k.startswith("spec_gate_") for k in st) and st["spec_gate_rounds"] + st.get("spec_gate_skipped", 0) >= 1
     llm.close()
+
+
+def test_a_stream_delivers_log_probabilities_with_its_closing_chunk():
+    import http.client
+    import threading
+    from pocketllm.server.openai import make_server
+    llm = LLM(EngineArgs(model="synthetic:qwen-tiny", device="cpu", max_model_len=128))
+    httpd, _ = make_server(llm.backend, "127.0.0.1", 0, "tiny")
+    threading.Thread(target=httpd.serve_forever, kwargs={"poll_interval": 0.05}, daemon=True).start()
+    try:
+        c = http.client.HTTPConnection("127.0.0.1", httpd.server_address[1], timeout=60)
+        c.request("POST", "/v1/completions", body=json.dumps({"prompt": PROMPT, "max_tokens": 4, "stream": True, "logprobs": 2}),
+                  headers={"Content-Type": "application/json"})
+        raw = c.getresponse().read().decode()
+        c.close()
+        chunks = [json.loads(l[6:]) for l in raw.splitlines() if l.startswith("data: ") and l != "data: [DONE]"]
+        last = chunks[-1]["choices"][0]
+        assert last["finish_reason"] == "length" and len(last["logprobs"]["token_logprobs"]) == 4
+        assert all(lp <= 0 for lp in last["logprobs"]["token_logprobs"]) and len(last["logprobs"]["top_logprobs"][0]) == 2
+        assert all("logprobs" not in ch["choices"][0] or ch is chunks[-1] for ch in chunks)
+    finally:
+        httpd.shutdown()
+        httpd.server_close()
+        llm.close()
