@@ -136,10 +136,14 @@ class NativeBackend(BackendBase):
         n = len(toks)
         # token ids index embedding and count tables on the device: refuse anything the model has no row for
         vocab = int(getattr(self.runtime, "vocab_size", 0) or 0)
-        for t in toks:
-            if isinstance(t, bool) or not isinstance(t, int) or t < 0 or t > 0x7FFFFFFF or (vocab and t >= vocab):
-                raise ConfigurationError(f"prompt holds {t!r}, which is not a token id of this model"
-                                         + (f" (vocabulary {vocab})" if vocab else ""))
+        try:
+            lo, hi = (min(toks), max(toks)) if toks else (0, 0)          # two C-speed passes, also for 64K-token prompts
+        except TypeError:
+            lo, hi = -1, -1
+        if not isinstance(lo, int) or not isinstance(hi, int) or lo < 0 or hi > 0x7FFFFFFF or (vocab and hi >= vocab):
+            bad = next((t for t in toks if not isinstance(t, int) or t < 0 or t > 0x7FFFFFFF or (vocab and t >= vocab)), lo)
+            raise ConfigurationError(f"prompt holds {bad!r}, which is not a token id of this model"
+                                     + (f" (vocabulary {vocab})" if vocab else ""))
         if limit and n + 1 > limit:
             raise ConfigurationError(f"prompt of {n} tokens does not fit max_model_len {limit}")
 
