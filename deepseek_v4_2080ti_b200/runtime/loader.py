@@ -447,7 +447,12 @@ class GgufRuntimeAdapter:
         out = {"slots_free": self.max_slots - len(self._active), "slots_total": self.max_slots}
         inner = getattr(self.rt, "stats", None)
         if callable(inner):                                  # speculation / swap counters of runtimes that keep them
-            out.update({k: v for k, v in inner().items() if isinstance(v, (int, float))})
+            try:
+                got = inner()
+            except Exception:
+                got = None
+            if isinstance(got, dict):
+                out.update({k: v for k, v in got.items() if isinstance(v, (int, float))})
         return out
 
 
