@@ -8,6 +8,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200, sm_100a)")
+    # pytest-timeout registers this itself; without the plugin the mark is inert instead of unknown
+    config.addinivalue_line("markers", "timeout(seconds): per-test time limit (pytest-timeout)")
 
 
 def pytest_collection_modifyitems(config, items):
