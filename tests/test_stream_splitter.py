@@ -158,3 +158,36 @@ def test_sse_route_splits_reasoning_content_and_tool_calls(scripted):
     chunks = _sse(scripted("just text"), {"messages": [{"role": "user", "content": "hi"}], "stream": True})
     assert "".join(c["choices"][0]["delta"].get("content", "") for c in chunks) == "just text"
     assert chunks[-1]["choices"][0]["finish_reason"] == "stop"
+
+
+def test_any_chunking_gives_the_same_reasoning_content_and_tool_calls():
+    """Property: how the text is cut into deltas never changes what comes out in total."""
+    import random
+    from pocketllm.protocol.stream import StreamSplitter
+    texts = [
+        ("<think>step one\nstep two</think>\n\nThe answer is 4.", True, False),
+        ("plain answer with a < sign and </thin almost-marker", False, False),
+        ("<think>plan</think>ok<tool_call>{\"name\": \"f\", \"arguments\": {\"x\": 1}}</tool_call>", False, True),
+        ("reasoning continues</think>visible\n\n<｜DSML｜tool_calls>\n<｜DSML｜invoke name=\"g\">\n<｜DSML｜parameter name=\"q\" string=\"true\">hi</｜DSML｜parameter>\n</｜DSML｜invoke>\n</｜DSML｜tool_calls>", True, True),
+        ("text <tool_cal not a call> more text", False, True),
+    ]
+    rng = random.Random(9)
+
+    def run(text, thinking, tools, cuts):
+        sp = StreamSplitter(thinking=thinking, tools=tools)
+        deltas, last = [], 0
+        for c in cuts + [len(text)]:
+            deltas += sp.feed(text[last:c])
+            last = c
+        tail, calls = sp.finish()
+        deltas += tail
+        reasoning = "".join(d.get("reasoning_content", "") for d in deltas)
+        content = "".join(d.get("content", "") for d in deltas)
+        return reasoning, content, [(c["function"]["name"], c["function"]["arguments"]) for c in calls]
+    for text, thinking, tools in texts:
+        whole = run(text, thinking, tools, [])
+        for _ in range(60):
+            k = rng.randrange(1, min(12, len(text)))
+            cuts = sorted(rng.sample(range(1, len(text)), k))
+            assert run(text, thinking, tools, cuts) == whole, (text, cuts)
+        assert run(text, thinking, tools, list(range(1, len(text)))) == whole          # one character at a time
