@@ -64,16 +64,25 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     if a.gguf:
         from deepseek_v4_2080ti_b200.encoding.gguf_tokenizer import GGUFTokenizer
         tok = GGUFTokenizer.from_gguf(a.gguf)
-    for line in stdin:
-        line = line.strip()
+    # bytes in, bytes out: a line that is not UTF-8 is answered with an error like any other bad request, whatever the
+    # locale's error handler for the standard streams is; exactly one answer per line that holds anything
+    raw_in = getattr(stdin, "buffer", stdin)
+    raw_out = getattr(stdout, "buffer", None)
+    for raw in raw_in:
+        line = (raw.decode("utf-8", errors="replace") if isinstance(raw, bytes) else raw).strip()
         if not line:
             continue
         try:
             resp = handle(json.loads(line), tok)
         except Exception as exc:                       # a bad request must not end the helper
-            resp = {"ok": False, "error": f"{type(exc).__name__}: {exc}"}
-        stdout.write(json.dumps(resp, ensure_ascii=False) + "\n")
-        stdout.flush()
+            resp = {"ok": False, "error": f"{type(exc).__name__}: {exc}"[:500]}
+        text = json.dumps(resp, ensure_ascii=False) + "\n"
+        if raw_out is not None:
+            raw_out.write(text.encode("utf-8", errors="replace"))
+            raw_out.flush()
+        else:
+            stdout.write(text)
+            stdout.flush()
         if resp.get("shutdown"):
             break
     return 0

@@ -52,3 +52,42 @@ def test_sidecar_protocol():
     assert lines[3]["message"]["reasoning_content"] == "plan" and lines[3]["message"]["content"] == "answer"
     assert lines[4]["ok"] and "[gMASK]" in lines[4]["prompt"]
     assert not lines[5]["ok"] and not lines[6]["ok"] and lines[7].get("shutdown")
+
+
+def test_sidecar_answers_every_line_whatever_bytes_it_holds():
+    """One answer per non-empty line, errors included: invalid UTF-8, random bytes, JSON that is not an object, nesting
+    that exhausts the parser; the helper stays alive and still answers a ping afterwards."""
+    import os
+    import random
+    import select
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.Popen([sys.executable, "-m", "pocketllm.sidecar"], stdin=subprocess.PIPE, stdout=subprocess.PIPE,
+                         stderr=subprocess.PIPE, env=dict(os.environ, PYTHONPATH=root))
+    try:
+        rng = random.Random(1)
+        lines = [b'{"op":"ping"}', b"garbage", b"[1,2]", b'{"op":"encode"}', b'{"op":"encode","family":"zzz","messages":[]}',
+                 b'{"op":"decode","token_ids":"abc"}', b"\xff\xfe\x00", b'{"op":' + b"[" * 50000]
+        for _ in range(40):
+            lines.append(bytes(rng.randrange(256) for _ in range(rng.randrange(1, 80))).replace(b"\n", b" ").replace(b"\r", b" "))
+        lines.append(b'{"op":"ping"}')
+        answers = []
+        for l in lines:
+            p.stdin.write(l + b"\n")
+            p.stdin.flush()
+            if not l.decode("utf-8", "replace").strip():
+                continue
+            ready, _, _ = select.select([p.stdout], [], [], 20)
+            assert ready, f"no answer for {l[:40]!r}"
+            answers.append(json.loads(p.stdout.readline()))
+        assert answers[0] == {"ok": True} and answers[-1] == {"ok": True}
+        assert answers[3]["ok"] is True                      # an encode request without messages renders the bare prefix
+        assert all(a["ok"] is False and a["error"] for i, a in enumerate(answers[1:-1], 1) if i != 3)
+        assert p.poll() is None
+    finally:
+        p.stdin.close()
+        try:
+            p.wait(timeout=10)
+        except subprocess.TimeoutExpired:
+            p.kill()
