@@ -30,7 +30,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--tensor-parallel-master-addr", default="127.0.0.1")
     s.add_argument("--tensor-parallel-master-port", type=int, default=0)
     s.add_argument("--tensor-parallel-rendezvous-dir")
-    s.add_argument("--device")
+    s.add_argument("--device", help="cuda index or 'cuda:N'; 'cpu' serves small models from the fp32 host runtimes")
     s.add_argument("--max-model-len", type=int)
     s.add_argument("--dtype")
     s.add_argument("--kv-cache-dtype", default="auto")
@@ -44,7 +44,9 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--pd-mode", default="serial", choices=["serial", "interleave"])
     s.add_argument("--attention-window", type=int, default=0)
     s.add_argument("--attention-sink-tokens", type=int, default=0)
-    s.add_argument("--speculative-method", default=None)
+    s.add_argument("--speculative-method", default=None,
+                   help="mtp | ngram on the GPU; the host path (--device cpu) also serves dspark | dflash2 "
+                        "(--backend-option drafter=DIR)")
     s.add_argument("--speculative-tokens", type=int, default=1)
     s.add_argument("--served-model-name", default=None)
     s.add_argument("--tensor-parallel-supervisor", action=argparse.BooleanOptionalAction, default=True,
