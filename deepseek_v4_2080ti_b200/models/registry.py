@@ -319,14 +319,7 @@ def _v4_runtime(bundle, device="cpu", rank=0, world=1, comm=None, **kw):
             layer_ids = tuple(sorted({max(0, cfg.n_layers // 2 - 1), cfg.n_layers - 1}))
             dw = vd.synth_dspark_weights(cfg, n_stages=2, n_target=len(layer_ids), seed=0)
         else:
-            from ..formats.safetensors_io import SafetensorsFile
-            f = SafetensorsFile(drafter)
-            dw = {k: f.get(k) for k in f.keys()}
-            raw = kw.get("dspark_target_layers") or f.metadata.get("target_layer_ids", "")
-            layer_ids = tuple(int(x) for x in str(raw).replace(" ", "").split(",") if x)
-            if not layer_ids or max(layer_ids) >= cfg.n_layers or "dspark.main_proj" not in dw \
-                    or dw["dspark.main_proj"].shape[1] != cfg.dim * len(layer_ids):
-                raise ValueError("the DSpark drafter file does not match this model (target_layer_ids / dspark.main_proj)")
+            dw, layer_ids = vd.load_dspark_weights(drafter, cfg, kw.get("dspark_target_layers"))
         gate = SpecGate.from_env(block) if str(kw.get("spec_gate", "0")) in ("1", "true") else None
         loop = vd.DSparkLoop(vd.DSparkRef(V4BlockRef(cfg, weights), dw, layer_ids, block=block), gate)
         return cfg, _V4SpecHostAdapter(loop, device)

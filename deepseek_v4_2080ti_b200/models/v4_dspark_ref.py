@@ -43,6 +43,28 @@ def synth_dspark_weights(cfg: V4Config, n_stages: int = 3, n_target: int = 2, ma
     return w
 
 
+def save_dspark_weights(path: str, weights: dict, target_layer_ids) -> int:
+    """One safetensors file of the ``dspark.*`` tensors; the target layers whose hidden states feed the drafter travel
+    in the file's metadata (``target_layer_ids``: "1,2")."""
+    from ..formats import safetensors_io
+    ids = ",".join(str(int(i)) for i in target_layer_ids)
+    return safetensors_io.write_file(path, {k: v for k, v in weights.items() if k.startswith("dspark.")},
+                                     metadata={"target_layer_ids": ids})
+
+
+def load_dspark_weights(path: str, cfg: V4Config, target_layer_ids=None) -> tuple[dict, tuple[int, ...]]:
+    """(weights, target layer ids) of a drafter file, checked against the target's shape."""
+    from ..formats.safetensors_io import SafetensorsFile
+    f = SafetensorsFile(path)
+    w = {k: f.get(k) for k in f.keys()}
+    raw = target_layer_ids if target_layer_ids is not None else f.metadata.get("target_layer_ids", "")
+    ids = tuple(int(x) for x in (raw if not isinstance(raw, str) else raw.replace(" ", "").split(",")) if str(x) != "")
+    if not ids or max(ids) >= cfg.n_layers or min(ids) < 0 or "dspark.main_proj" not in w \
+            or tuple(w["dspark.main_proj"].shape) != (cfg.dim, cfg.dim * len(ids)):
+        raise ValueError("the DSpark drafter file does not match this model (target_layer_ids / dspark.main_proj)")
+    return w, ids
+
+
 class _DraftStage(_Layer):
     """A V4 block whose attention reads the committed context from target-model hidden states."""
 

@@ -220,7 +220,9 @@ def test_block_drafter_in_front_of_the_registered_family(tmp_path):
     layer_ids = (0, cfg.n_layers - 1)
     dw = vd.synth_dspark_weights(cfg, n_stages=1, n_target=2, seed=4)
     ck = str(tmp_path / "dspark.safetensors")
-    safetensors_io.write_file(ck, dw, metadata={"target_layer_ids": ",".join(map(str, layer_ids))})
+    vd.save_dspark_weights(ck, dw, layer_ids)
+    back, ids = vd.load_dspark_weights(ck, cfg)
+    assert ids == layer_ids and set(back) == set(dw)
     _, rt = spec.build_runtime(b, "cpu", dspark=ck, spec_gate="1")
     assert run(rt) == want
     with pytest.raises(ValueError, match="does not match"):
