@@ -192,3 +192,33 @@ def test_runtime_counters_are_exported_as_gauges(server):
     st, raw = call(port, "GET", "/metrics")
     text = raw.decode()
     assert st == 200 and "pocketllm_runtime_requests 1" in text and "pocketllm_runtime_completion_tokens 3" in text
+
+
+def test_random_byte_damage_never_takes_the_server_down(server):
+    import random
+    import socket
+    port, _ = server
+    body = json.dumps({"prompt": [1, 2, 3], "max_tokens": 2}).encode()
+    good = (b"POST /v1/completions HTTP/1.1\r\nContent-Type: application/json\r\nContent-Length: " + str(len(body)).encode()
+            + b"\r\n\r\n" + body)
+    rng = random.Random(3)
+    for _ in range(80):
+        b = bytearray(good)
+        for _ in range(rng.randrange(1, 8)):
+            b[rng.randrange(len(b))] = rng.randrange(256)
+        try:
+            s = socket.create_connection(("127.0.0.1", port), timeout=5)
+            s.settimeout(2)
+            try:
+                s.sendall(bytes(b))
+                s.shutdown(socket.SHUT_WR)
+                while s.recv(65536):
+                    pass
+            except OSError:
+                pass
+            finally:
+                s.close()
+        except OSError:
+            pass
+    st, raw = call(port, "POST", "/v1/completions", {"prompt": "A", "max_tokens": 2})
+    assert st == 200 and json.loads(raw)["choices"][0]["text"] == "BC"
