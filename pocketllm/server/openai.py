@@ -125,6 +125,8 @@ def make_handler(state: ServerState):
     class Handler(BaseHTTPRequestHandler):
         protocol_version = "HTTP/1.1"
         server_version = "pocketllm-b200"
+        # a client that connects and then says nothing (or stops reading) gives its thread back after this many seconds
+        timeout = float(os.environ.get("POCKETLLM_HTTP_IDLE_TIMEOUT", "120"))
 
         def log_message(self, fmt, *args):  # quiet by default
             pass
@@ -170,7 +172,11 @@ def make_handler(state: ServerState):
                 raise ConfigurationError("request body is empty")
             if n > MAX_BODY:
                 raise ConfigurationError("request body too large")
-            data = self.rfile.read(n)
+            try:
+                data = self.rfile.read(n)
+            except (TimeoutError, ConnectionError) as exc:     # the idle timeout: the client stopped sending
+                self.close_connection = True
+                raise ConfigurationError("request body did not arrive in time") from exc
             if len(data) != n:
                 raise ConfigurationError("request body is shorter than its Content-Length")
             try:

@@ -222,3 +222,25 @@ def test_random_byte_damage_never_takes_the_server_down(server):
             pass
     st, raw = call(port, "POST", "/v1/completions", {"prompt": "A", "max_tokens": 2})
     assert st == 200 and json.loads(raw)["choices"][0]["text"] == "BC"
+
+
+def test_idle_connections_are_dropped(monkeypatch):
+    import socket
+    import time
+    monkeypatch.setenv("POCKETLLM_HTTP_IDLE_TIMEOUT", "1")
+    backend = NativeBackend(EngineArgs(model="fake"), runtime=FakeRuntime())
+    httpd, _ = make_server(backend, "127.0.0.1", 0, "fake-model")
+    t = threading.Thread(target=httpd.serve_forever, kwargs={"poll_interval": 0.05}, daemon=True)
+    t.start()
+    try:
+        port = httpd.server_address[1]
+        s = socket.create_connection(("127.0.0.1", port), timeout=10)
+        s.sendall(b"POST /v1/completions HTTP/1.1\r\nContent-Length: 50\r\n\r\n{")       # and then nothing
+        t0 = time.time()
+        data = s.recv(4096)                                   # the server gives up on the body and closes
+        assert time.time() - t0 < 8 and (data == b"" or data.startswith(b"HTTP/1.1 4"))
+        s.close()
+        assert call(port, "POST", "/v1/completions", {"prompt": "A", "max_tokens": 1})[0] == 200
+    finally:
+        httpd.shutdown()
+        httpd.server_close()
