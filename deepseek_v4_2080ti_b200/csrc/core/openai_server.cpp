@@ -145,6 +145,7 @@ void OpenAIServer::serve_connection(int fd) {
   const double t0 = now_s();
   while (header_end == std::string::npos) {
     pollfd pfd{fd, POLLIN, 0};
+    if (now_s() - t0 > 30) return;                      // a header that trickles in is given up on as well
     if (poll(&pfd, 1, 1000) <= 0) { if (now_s() - t0 > 10) return; continue; }
     const ssize_t n = ::recv(fd, tmp, sizeof tmp, 0);
     if (n <= 0) return;
