@@ -27,21 +27,26 @@ def _quantile(xs: list[float], q: float) -> float:
     return s[min(len(s) - 1, int(q * (len(s) - 1) + 0.5))]
 
 
-def one_request(host: str, port: int, prompt: list[int], max_tokens: int, stream: bool, timeout: float) -> dict:
-    """Returns {"ok", "ttft", "latency", "tokens", "error"}; ``ttft`` is measured at the first streamed text."""
-    body = json.dumps({"prompt": prompt, "max_tokens": max_tokens, "stream": stream, "temperature": 0})
+def one_request(host: str, port: int, prompt: list[int], max_tokens: int, stream: bool, timeout: float,
+                route: str = "/v1/completions") -> dict:
+    """Returns {"ok", "ttft", "latency", "tokens", "error"}; ``ttft`` is measured at the first streamed text (or token
+    ids, for a server that has no tokenizer).  The prompt travels under both spellings servers use for token ids."""
+    body = json.dumps({"prompt": prompt, "prompt_token_ids": prompt, "max_tokens": max_tokens, "stream": stream, "temperature": 0})
     t0 = time.perf_counter()
     out = {"ok": False, "ttft": 0.0, "latency": 0.0, "tokens": 0, "error": ""}
     try:
         c = http.client.HTTPConnection(host, port, timeout=timeout)
-        c.request("POST", "/v1/completions", body=body, headers={"Content-Type": "application/json"})
+        c.request("POST", route, body=body, headers={"Content-Type": "application/json"})
         r = c.getresponse()
         if r.status != 200:
             out["error"] = f"HTTP {r.status}: {r.read()[:200].decode(errors='replace')}"
             return out
         if not stream:
             data = json.loads(r.read())
-            out.update(ok=True, tokens=int(data["usage"]["completion_tokens"]))
+            n_tok = data.get("usage", {}).get("completion_tokens")
+            if n_tok is None:
+                n_tok = len(data["choices"][0].get("token_ids", []))
+            out.update(ok=True, tokens=int(n_tok))
             out["ttft"] = float(data.get("timings", {}).get("ttft_seconds", 0.0) or 0.0)
         else:
             first = None
@@ -54,10 +59,13 @@ def one_request(host: str, port: int, prompt: list[int], max_tokens: int, stream
                     out["error"] = str(ev["error"].get("message", ev["error"]))[:200]
                     return out
                 ch = ev["choices"][0]
-                if first is None and ch.get("text"):
+                delta = ch.get("delta") or {}
+                if first is None and (ch.get("text") or delta.get("content") or ch.get("token_ids")):
                     first = time.perf_counter() - t0
                 if ev.get("usage"):
                     out["tokens"] = int(ev["usage"]["completion_tokens"])
+                elif ch.get("token_ids") and not out["tokens"]:
+                    out["tokens"] = len(ch["token_ids"])
             out.update(ok=True, ttft=first if first is not None else time.perf_counter() - t0)
         c.close()
     except (OSError, ValueError, KeyError) as exc:
@@ -68,7 +76,7 @@ def one_request(host: str, port: int, prompt: list[int], max_tokens: int, stream
 
 
 def run_level(host: str, port: int, concurrency: int, requests: int, prompt_tokens: int, max_tokens: int, vocab: int,
-              seed: int, stream: bool = True, timeout: float = 600.0) -> dict:
+              seed: int, stream: bool = True, timeout: float = 600.0, route: str = "/v1/completions") -> dict:
     rng = random.Random(seed)
     prompts = [[rng.randrange(1, vocab) for _ in range(prompt_tokens)] for _ in range(requests)]
     results: list[dict] = []
@@ -81,7 +89,7 @@ def run_level(host: str, port: int, concurrency: int, requests: int, prompt_toke
                 if not todo:
                     return
                 i = todo.pop()
-            res = one_request(host, port, prompts[i], max_tokens, stream, timeout)
+            res = one_request(host, port, prompts[i], max_tokens, stream, timeout, route)
             with lock:
                 results.append(res)
 
@@ -115,12 +123,14 @@ def main(argv=None) -> int:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-stream", action="store_true")
     ap.add_argument("--timeout", type=float, default=600.0)
+    ap.add_argument("--route", default="/v1/completions", help="/v1/completions or /v1/chat/completions")
     a = ap.parse_args(argv)
     u = urllib.parse.urlparse(a.url)
     host, port = u.hostname or "127.0.0.1", u.port or 80
     base = None
     for c in [int(x) for x in a.concurrency.split(",") if x]:
-        row = run_level(host, port, c, a.requests, a.prompt_tokens, a.max_tokens, a.vocab, a.seed, not a.no_stream, a.timeout)
+        row = run_level(host, port, c, a.requests, a.prompt_tokens, a.max_tokens, a.vocab, a.seed, not a.no_stream, a.timeout,
+                        a.route)
         if base is None and row["requests_per_second"]:
             base = row["requests_per_second"]
         row["speedup_vs_first_level"] = round(row["requests_per_second"] / base, 3) if base else 0.0

@@ -30,3 +30,20 @@ def test_levels_against_the_host_server(capsys):
         httpd.server_close()
         llm.close()
     assert sb.run_level("127.0.0.1", port, 1, 1, 4, 2, 100, 0, timeout=2)["errors"] == 1      # nobody listens any more
+
+
+def test_against_the_native_server_with_token_id_answers():
+    import pytest
+    cpp = pytest.importorskip("deepseek_v4_2080ti_b200.pocketllm_cpp")
+    from tests.test_native_http_server import FakeEngine
+    eng = FakeEngine()
+    opt = cpp.OpenAIServerOptions()
+    opt.port = 0
+    srv = cpp.OpenAIServer(eng, opt)
+    srv.start()
+    try:
+        for stream, route in ((False, "/v1/completions"), (True, "/v1/chat/completions")):
+            row = sb.run_level("127.0.0.1", srv.port, 3, 6, prompt_tokens=5, max_tokens=4, vocab=40, seed=2, stream=stream, route=route)
+            assert row["ok"] == 6 and row["errors"] == 0 and row["generated_tokens_per_second"] > 0, row
+    finally:
+        srv.stop()
