@@ -140,6 +140,10 @@ def drive_engine(cmd, env, line: str, *, leader: bool, warmup: int, steps: int, 
             break
         out = next_result(max(30.0, left()))
         if out is None:
+            try:                                        # end of output can be seen a moment before the process is gone
+                proc.wait(timeout=1.0)
+            except subprocess.TimeoutExpired:
+                pass
             why_short = ("engine exited" if proc.poll() is not None
                          else f"time budget of {int(budget)} s (request in flight)")
             break
