@@ -12,7 +12,7 @@ from deepseek_v4_2080ti_b200.parallel.tp import CollectiveTimeoutError
 
 def _rank(name, rank, world, scenario, q):
     try:
-        c = ShmPeerComm(name, rank, world, slot_elems=1024, budget_s=1.0 if scenario == "missing" else 5.0)
+        c = ShmPeerComm(name, rank, world, slot_elems=1024, budget_s=1.0 if scenario == "missing" else 60.0)    # generous: a loaded machine starts ranks seconds apart
         c.connect()
         out = []
         for it in range(6):
@@ -44,7 +44,7 @@ def _run(scenario, world=3):
     ps = [ctx.Process(target=_rank, args=(name, r, world, scenario, q)) for r in range(world)]
     for p in ps:
         p.start()
-    res = dict(q.get(timeout=60) for _ in range(world))
+    res = dict(q.get(timeout=240) for _ in range(world))
     for p in ps:
         p.join(30)
     return res
