@@ -12,7 +12,7 @@ from deepseek_v4_2080ti_b200.parallel.tp import CollectiveTimeoutError
 
 def _rank(name, rank, world, scenario, q):
     try:
-        c = ShmPeerComm(name, rank, world, slot_elems=1024, budget_s=1.0 if scenario == "missing" else 60.0)    # generous: a loaded machine starts ranks seconds apart
+        c = ShmPeerComm(name, rank, world, slot_elems=1024, budget_s=2.5 if scenario == "missing" else 60.0)    # generous: a loaded machine starts ranks seconds apart
         c.connect()
         out = []
         for it in range(6):
