@@ -13,7 +13,7 @@ from deepseek_v4_2080ti_b200.parallel.tp import CollectiveTimeoutError
 def _rank(name, rank, world, scenario, q):
     try:
         c = ShmPeerComm(name, rank, world, slot_elems=1024, budget_s=2.5 if scenario == "missing" else 60.0)    # generous: a loaded machine starts ranks seconds apart
-        c.connect()
+        c.connect(timeout_s=180.0)                              # a loaded machine starts the ranks many seconds apart
         out = []
         for it in range(6):
             x = np.full(300 + it, float(rank + 1) * (it + 1), dtype=np.float32)
