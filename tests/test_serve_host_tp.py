@@ -33,6 +33,20 @@ def _post(port, body, timeout=60):
         return json.loads(r.read())
 
 
+def _children(pid):
+    """Direct children of ``pid`` from /proc (no dependence on a ``ps`` binary)."""
+    out = []
+    for d in os.listdir("/proc"):
+        if d.isdigit():
+            try:
+                stat = open(f"/proc/{d}/stat").read()
+                if int(stat.rsplit(")", 1)[1].split()[1]) == pid:
+                    out.append(int(d))
+            except (OSError, ValueError, IndexError):
+                pass
+    return sorted(out)
+
+
 def _alive(pid):
     try:
         os.kill(pid, 0)
@@ -76,8 +90,7 @@ def test_two_host_ranks_under_the_supervisor_serve_and_stop(tmp_path):
         text = (tmp_path / "serve.log").read_text()
         assert "[rank 0] pocketllm: serving" in text                        # the supervisor relays its ranks' output
         # the ranks are children of the supervisor: find them, stop the supervisor, and see them all leave
-        kids = subprocess.run(["ps", "-o", "pid=", "--ppid", str(proc.pid)], capture_output=True, text=True).stdout.split()
-        kids = [int(k) for k in kids]
+        kids = _children(proc.pid)
         assert len(kids) == 2
         proc.send_signal(signal.SIGTERM)
         proc.wait(timeout=60)
@@ -115,7 +128,7 @@ def test_a_rank_that_dies_takes_the_service_down(tmp_path):
             except OSError:
                 time.sleep(0.5)
         assert _post(port, {"prompt": PROMPT, "max_tokens": 2})["usage"]["completion_tokens"] == 2
-        kids = [int(k) for k in subprocess.run(["ps", "-o", "pid=", "--ppid", str(proc.pid)], capture_output=True, text=True).stdout.split()]
+        kids = _children(proc.pid)
         assert len(kids) == 2
         # the worker rank is the one that does not listen on the port: kill the child whose command line says rank 1,
         # or simply the younger one (rank 1 is started after rank 0)
